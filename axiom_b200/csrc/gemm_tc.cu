@@ -1,0 +1,451 @@
+// gemm_tc.cu — the tcgen05 GEMM core.
+//
+// One persistent, warp-specialised kernel computes
+//     D[M,N] = sum over products (pa,pb) of  Aplane[pa][M,K] . Bplane[pb][N,K]^T
+// with every operand plane K-major.  A single product of bf16 planes is the
+// fast bf16 mode; (hi,hi),(hi,lo),(lo,hi) over tf32 planes is 3xTF32; one
+// product of int8 planes with s32 accumulators is the quantised GEMM.
+//
+//   warp 0 (one lane)  TMA producer: cp.async.bulk.tensor tiles with the 128-byte
+//                      or 64-byte swizzle into a ring of shared-memory stages,
+//                      completion counted in bytes on a per-stage mbarrier
+//   warp 1 (one lane)  issues tcgen05.mma (M = 128, N = BN) into one of two
+//                      TMEM accumulators; tcgen05.commit releases the stage
+//                      and, after the last k-block, publishes the accumulator
+//   warps 2..5         epilogue: tcgen05.ld the finished accumulator (each warp
+//                      owns its 32-lane quarter), apply alpha/beta/bias/
+//                      activation or the int8 requantisation, store to global;
+//                      the second accumulator lets this overlap the next tile
+//
+// Tiles are walked in a grouped raster (GROUP_M row-tiles per column sweep) so
+// the CTAs running at one time share operand panels in L2.  Edge tiles rely
+// on TMA zero fill for loads and on masking for stores.
+#include "gemm_tc.cuh"
+#include "ptx.cuh"
+
+#include <cuda.h>
+#include <stdio.h>
+#include <string.h>
+
+namespace axb {
+
+static constexpr int BM = 128;
+static constexpr int GROUP_M = 16;
+static constexpr int NUM_THREADS = 192;
+static constexpr int HEADER_BYTES = 1024;
+static constexpr int MAX_STAGES = 8;
+static constexpr int SMEM_BUDGET = 227 * 1024;
+
+struct alignas(64) TmapPack {
+    CUtensorMap a[TC_MAX_PLANES];
+    CUtensorMap b[TC_MAX_PLANES];
+};
+
+struct KernelArgs {
+    int M, N, K;
+    int npa, npb, nprod;
+    int8_t pa[TC_MAX_PRODUCTS], pb[TC_MAX_PRODUCTS];
+    int m_tiles, n_tiles, k_blocks, stages;
+    float alpha, beta;
+    const float *bias;
+    const float *colscale;
+    int act, out_mode;
+    void *C;
+    int32_t *acc_out;
+    long long ldc;
+    int *err;
+};
+
+// error words written to *err (first writer wins)
+enum { ERR_PRODUCER_WAIT = 1, ERR_MMA_WAIT_FULL = 2, ERR_MMA_WAIT_TMEM = 3, ERR_EPI_WAIT = 4 };
+
+__device__ __forceinline__ void report(int *err, int code)
+{
+    if (err) atomicCAS(err, 0, code);
+}
+
+__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int &mt, int &nt)
+{
+    const int per_group = GROUP_M * n_tiles;
+    const int g = t / per_group;
+    const int first_m = g * GROUP_M;
+    const int gm = min(GROUP_M, m_tiles - first_m);
+    const int r = t - g * per_group;
+    mt = first_m + r % gm;
+    nt = r / gm;
+}
+
+__device__ __forceinline__ float gelu_tanh(float v)
+{
+    const float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+    return 0.5f * v * (1.0f + tanhf(inner));
+}
+
+template <int KIND, int BN, int SWB>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
+{
+    constexpr int A_BYTES = BM * SWB;   // one A plane of one stage
+    constexpr int B_BYTES = BN * SWB;
+    constexpr int ES = KIND == KIND_TF32 ? 4 : (KIND == KIND_BF16 ? 2 : 1);
+    constexpr int BKE = SWB / ES;       // k elements per stage
+    constexpr int KSTEPS = SWB / 32;    // one MMA consumes 32 bytes of K
+    constexpr int TMEM_COLS = 2 * BN;
+    constexpr uint32_t IDESC = make_idesc<KIND>(BM, BN);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bar_full = base;                 // MAX_STAGES x 8 B
+    const uint32_t bar_empty = base + 64;           // MAX_STAGES x 8 B
+    const uint32_t bar_tfull = base + 128;          // 2 x 8 B
+    const uint32_t bar_tempty = base + 144;         // 2 x 8 B
+    const uint32_t tmem_slot = base + 160;
+    const uint32_t stage0 = base + HEADER_BYTES;
+    const int stage_bytes = p.npa * A_BYTES + p.npb * B_BYTES;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int total_tiles = p.m_tiles * p.n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(bar_tfull + 8 * a, 1);
+            mbar_init(bar_tempty + 8 * a, 4);
+        }
+        mbar_fence_init();
+        for (int i = 0; i < p.npa; ++i) tma_prefetch_desc(&tm.a[i]);
+        for (int i = 0; i < p.npb; ++i) tma_prefetch_desc(&tm.b[i]);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(gen_base + 160);
+
+    if (warp == 0) {
+        // ------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                int mt, nt;
+                tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
+                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                    if (!mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1u)) {
+                        report(p.err, ERR_PRODUCER_WAIT);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t fb = bar_full + 8 * s;
+                    mbar_arrive_expect_tx(fb, (uint32_t)stage_bytes);
+                    uint32_t dst = stage0 + s * stage_bytes;
+                    for (int i = 0; i < p.npa; ++i, dst += A_BYTES)
+                        tma_load_2d(dst, &tm.a[i], fb, kb * BKE, mt * BM);
+                    for (int i = 0; i < p.npb; ++i, dst += B_BYTES)
+                        tma_load_2d(dst, &tm.b[i], fb, kb * BKE, nt * BN);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            uint32_t it = 0, lt = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
+                const uint32_t acc = lt & 1u, aph = (lt >> 1) & 1u;
+                if (!mbar_wait_bounded(bar_tempty + 8 * acc, aph ^ 1u)) {
+                    report(p.err, ERR_MMA_WAIT_TMEM);
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                    if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
+                        report(p.err, ERR_MMA_WAIT_FULL);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t sa = stage0 + s * stage_bytes;
+                    const uint32_t sb = sa + p.npa * A_BYTES;
+                    for (int pr = 0; pr < p.nprod; ++pr) {
+                        const uint64_t da = smem_desc_kmajor(sa + p.pa[pr] * A_BYTES, SWB);
+                        const uint64_t db = smem_desc_kmajor(sb + p.pb[pr] * B_BYTES, SWB);
+#pragma unroll
+                        for (int ks = 0; ks < KSTEPS; ++ks)
+                            tc_mma<KIND>(d_tmem, da + 2u * ks, db + 2u * ks, IDESC,
+                                         (uint32_t)((kb | pr | ks) != 0));
+                    }
+                    tc_commit(bar_empty + 8 * s);
+                }
+                if (ok) tc_commit(bar_tfull + 8 * acc);
+            }
+        }
+    } else {
+        // ---------------------------------------------------------- epilogue
+        const int q = warp & 3;  // TMEM lane quarter this warp may read
+        uint32_t lt = 0;
+        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++lt) {
+            int mt, nt;
+            tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
+            const uint32_t acc = lt & 1u, aph = (lt >> 1) & 1u;
+            const bool got = mbar_wait_bounded(bar_tfull + 8 * acc, aph);
+            if (!__all_sync(0xffffffffu, got)) {
+                report(p.err, ERR_EPI_WAIT);
+                break;
+            }
+            tc_fence_after_sync();
+            const long long row = (long long)mt * BM + q * 32 + lane;
+            const bool row_ok = row < p.M;
+            const int col_base = nt * BN;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                const int col0 = col_base + c * 32;
+                if (col0 >= p.N) break;  // warp-uniform
+                uint32_t r[32];
+                __syncwarp();  // the TMEM load is warp-collective: reconverge after masked stores
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
+                tmem_ld_wait();
+                const bool full = col0 + 32 <= p.N;
+                if (!row_ok) {
+                    // rows past M: nothing to store
+                } else if constexpr (KIND == KIND_I8) {
+                    if (p.acc_out) {
+                        int32_t *dst = p.acc_out + row * p.ldc + col0;
+                        if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<int4 *>(dst + j) =
+                                    make_int4((int)r[j], (int)r[j + 1], (int)r[j + 2], (int)r[j + 3]);
+                        } else {
+                            for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = (int32_t)r[j];
+                        }
+                    }
+                    if (p.out_mode == OUT_I8_REQUANT) {
+                        int8_t *dst = reinterpret_cast<int8_t *>(p.C) + row * p.ldc + col0;
+                        uint32_t packed[8];
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) {
+                            const float mult = (col0 + j < p.N) ? __ldg(p.colscale + col0 + j) : 0.0f;
+                            const float y = __fmul_rn(__int2float_rn((int32_t)r[j]), mult);
+                            int v = __float2int_rn(y);
+                            v = max(-127, min(127, v));
+                            if ((j & 3) == 0) packed[j >> 2] = 0;
+                            packed[j >> 2] |= (uint32_t)(v & 0xff) << (8 * (j & 3));
+                        }
+                        if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+                            *reinterpret_cast<uint4 *>(dst) =
+                                make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                            *reinterpret_cast<uint4 *>(dst + 16) =
+                                make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                        } else {
+                            for (int j = 0; j < 32 && col0 + j < p.N; ++j)
+                                dst[j] = (int8_t)((packed[j >> 2] >> (8 * (j & 3))) & 0xff);
+                        }
+                    }
+                } else {
+                    float *dst = reinterpret_cast<float *>(p.C) + row * p.ldc + col0;
+                    const bool vec = full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const bool in = full || (col0 + j < p.N);
+                        float x = __uint_as_float(r[j]) * p.alpha;
+                        if (p.colscale) x *= in ? __ldg(p.colscale + col0 + j) : 0.0f;
+                        if (p.beta != 0.0f) x += p.beta * (in ? dst[j] : 0.0f);
+                        if (p.bias) x += in ? __ldg(p.bias + col0 + j) : 0.0f;
+                        if (p.act == ACT_RELU) x = fmaxf(x, 0.0f);
+                        else if (p.act == ACT_GELU) x = gelu_tanh(x);
+                        v[j] = x;
+                    }
+                    if (vec) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4)
+                            *reinterpret_cast<float4 *>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else {
+                        for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = v[j];
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    // After a wait that ran out, give copies still in flight time to land in
+    // this CTA's shared memory before it is released.
+    if (p.err && *reinterpret_cast<volatile int *>(p.err) != 0) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------- host
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
+                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
+                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static char g_err[256] = "";
+const char *gemm_tc_last_error() { return g_err; }
+
+static EncodeTiledFn encode_fn()
+{
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            return nullptr;
+        fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+static int encode_plane(CUtensorMap *out, int kind, const void *ptr, int64_t rows, int64_t k,
+                        int64_t pitch_elems, int box_rows, int swb)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled entry point not found");
+        return (int)cudaErrorSymbolNotFound;
+    }
+    const int es = kind == KIND_TF32 ? 4 : (kind == KIND_BF16 ? 2 : 1);
+    const CUtensorMapDataType dt = kind == KIND_TF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : kind == KIND_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                     : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    cuuint64_t dims[2] = { (cuuint64_t)k, (cuuint64_t)rows };
+    cuuint64_t strides[1] = { (cuuint64_t)pitch_elems * es };
+    cuuint32_t box[2] = { (cuuint32_t)(swb / es), (cuuint32_t)box_rows };
+    cuuint32_t estr[2] = { 1, 1 };
+    CUresult r = fn(out, dt, 2, const_cast<void *>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swb == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_err, sizeof g_err,
+                 "cuTensorMapEncodeTiled failed (%d): ptr=%p rows=%lld k=%lld pitch=%lld box=%ux%u", (int)r, ptr,
+                 (long long)rows, (long long)k, (long long)pitch_elems, box[0], box[1]);
+        return (int)cudaErrorInvalidValue;
+    }
+    return 0;
+}
+
+template <int KIND, int BN, int SWB>
+static int launch_inst(const TmapPack &tm, KernelArgs &ka, int stage_bytes, int grid, cudaStream_t stream)
+{
+    int stages = (SMEM_BUDGET - HEADER_BYTES - 1024) / stage_bytes;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages < 2) {
+        snprintf(g_err, sizeof g_err, "stage of %d bytes leaves fewer than 2 pipeline stages", stage_bytes);
+        return (int)cudaErrorInvalidConfiguration;
+    }
+    ka.stages = stages;
+    const int smem = HEADER_BYTES + 1024 + stages * stage_bytes;
+    auto kern = gemm_tc_kernel<KIND, BN, SWB>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET);
+        if (e != cudaSuccess) {
+            snprintf(g_err, sizeof g_err, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        attr_set = true;
+    }
+    kern<<<grid, NUM_THREADS, smem, stream>>>(tm, ka);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) snprintf(g_err, sizeof g_err, "gemm_tc launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+
+template <int KIND, int SWB>
+static int launch_bn(int bn, const TmapPack &tm, KernelArgs &ka, int npa, int npb, int grid, cudaStream_t st)
+{
+    const int sb = npa * BM * SWB + npb * bn * SWB;
+    switch (bn) {
+    case 256: return launch_inst<KIND, 256, SWB>(tm, ka, sb, grid, st);
+    case 128: return launch_inst<KIND, 128, SWB>(tm, ka, sb, grid, st);
+    default: return launch_inst<KIND, 64, SWB>(tm, ka, sb, grid, st);
+    }
+}
+
+int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcProducts &prod,
+                   int64_t M, int64_t N, int64_t K, const TcEpilogue &ep, int *err_word,
+                   int sm_count, cudaStream_t stream)
+{
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || A.nplanes < 1 || B.nplanes < 1 || A.nplanes > TC_MAX_PLANES || B.nplanes > TC_MAX_PLANES ||
+        prod.n < 1 || prod.n > TC_MAX_PRODUCTS) {
+        snprintf(g_err, sizeof g_err, "launch_gemm_tc: bad operand description");
+        return (int)cudaErrorInvalidValue;
+    }
+    // Column-tile width: the widest that still gives every SM a tile; small
+    // problems take narrower tiles so more SMs take part.
+    const int64_t mt = (M + BM - 1) / BM;
+    int bn = 256;
+    if (mt * ((N + 255) / 256) < sm_count) bn = 128;
+    if (bn == 128 && mt * ((N + 127) / 128) < sm_count) bn = 64;
+    if (N <= 64) bn = 64;
+    else if (N <= 128 && bn > 128) bn = 128;
+    const int64_t nt = (N + bn - 1) / bn;
+    // Swizzle width: 64-byte rows halve the stage so the split-precision modes
+    // (four planes per stage) still get a four-deep ring.
+    const int planes = A.nplanes + B.nplanes;
+    const int swb = (kind != KIND_I8 && planes > 2) ? 64 : 128;
+    const int es = kind == KIND_TF32 ? 4 : (kind == KIND_BF16 ? 2 : 1);
+    const int bke = swb / es;
+
+    TmapPack tm;
+    memset(&tm, 0, sizeof tm);
+    for (int i = 0; i < A.nplanes; ++i) {
+        int e = encode_plane(&tm.a[i], kind, A.plane[i], M, K, A.pitch_elems, BM, swb);
+        if (e) return e;
+    }
+    for (int i = 0; i < B.nplanes; ++i) {
+        int e = encode_plane(&tm.b[i], kind, B.plane[i], N, K, B.pitch_elems, bn, swb);
+        if (e) return e;
+    }
+    KernelArgs ka;
+    memset(&ka, 0, sizeof ka);
+    ka.M = (int)M; ka.N = (int)N; ka.K = (int)K;
+    ka.npa = A.nplanes; ka.npb = B.nplanes; ka.nprod = prod.n;
+    for (int i = 0; i < prod.n; ++i) { ka.pa[i] = prod.a[i]; ka.pb[i] = prod.b[i]; }
+    ka.m_tiles = (int)mt; ka.n_tiles = (int)nt;
+    ka.k_blocks = (int)((K + bke - 1) / bke);
+    ka.alpha = ep.alpha; ka.beta = ep.beta; ka.bias = ep.bias; ka.colscale = ep.colscale;
+    ka.act = ep.act; ka.out_mode = ep.out_mode; ka.C = ep.C; ka.acc_out = ep.acc_out;
+    ka.ldc = ep.ldc; ka.err = err_word;
+    const int64_t tiles = mt * nt;
+    const int grid = (int)(tiles < sm_count ? tiles : sm_count);
+
+    if (kind == KIND_TF32)
+        return swb == 128 ? launch_bn<KIND_TF32, 128>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream)
+                          : launch_bn<KIND_TF32, 64>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream);
+    if (kind == KIND_BF16)
+        return swb == 128 ? launch_bn<KIND_BF16, 128>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream)
+                          : launch_bn<KIND_BF16, 64>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream);
+    return launch_bn<KIND_I8, 128>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream);
+}
+
+}  // namespace axb

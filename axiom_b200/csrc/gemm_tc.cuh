@@ -1,0 +1,48 @@
+// gemm_tc.cuh — interface between the tcgen05 GEMM core (gemm_tc.cu) and the
+// C-ABI layer (api.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace axb {
+
+enum { TC_MAX_PLANES = 3, TC_MAX_PRODUCTS = 6 };
+enum { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2 };
+enum { OUT_F32 = 0, OUT_I8_REQUANT = 1, OUT_S32_ONLY = 2 };
+
+// One logical operand = up to three K-major planes [rows, k] whose sum is the
+// value (a single plane for bf16 / int8; hi+lo for the split-precision modes).
+struct TcOperand {
+    const void *plane[TC_MAX_PLANES];
+    int nplanes;
+    int64_t rows;         // M for the A side, N for the B side
+    int64_t pitch_elems;  // row pitch in elements (pitch * element size % 16 == 0)
+};
+
+struct TcEpilogue {
+    float alpha, beta;      // f32 kinds: v = alpha * acc (* colscale[n]) (+ beta * C) (+ bias[n]) -> act
+    const float *bias;      // [N] or null
+    const float *colscale;  // [N] or null; int8 requant: the per-column multiplier
+    int act;                // ACT_*
+    int out_mode;           // OUT_*
+    void *C;                // float* (OUT_F32) / int8_t* (OUT_I8_REQUANT) / unused
+    int32_t *acc_out;       // int8 kind: raw s32 accumulators, or null
+    int64_t ldc;            // row pitch of C and acc_out in elements
+};
+
+struct TcProducts {
+    int n;
+    int8_t a[TC_MAX_PRODUCTS], b[TC_MAX_PRODUCTS];  // plane index pairs, issued in order
+};
+
+// kind: MmaKind (0 tf32, 1 bf16, 2 int8).  Returns cudaError_t as int; a device
+// side wait that ran out is reported through *err_word (0 = clean).
+int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcProducts &prod,
+                   int64_t M, int64_t N, int64_t K, const TcEpilogue &ep, int *err_word,
+                   int sm_count, cudaStream_t stream);
+
+// Number of kernels the last launch_gemm_tc enqueued (always 1); kept so the
+// caller can count launches without knowing the core's structure.
+const char *gemm_tc_last_error();
+
+}  // namespace axb

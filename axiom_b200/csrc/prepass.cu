@@ -1,0 +1,291 @@
+// prepass.cu — operand preparation for the tcgen05 GEMM core, all HBM-bound:
+//   * split an fp32 matrix into K-major tensor-core planes (tf32 hi/lo, or
+//     bf16 hi/mid/lo), transposing on the way when the source is stored with
+//     the contraction index outermost;
+//   * widen int8 weights to an (exact) bf16 plane for the W8A32 path;
+//   * re-pitch int8 operands whose row length is not a multiple of 16 bytes;
+//   * the per-column requantisation multiplier and the row quantiser.
+#include "prepass.cuh"
+
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+namespace axb {
+
+__device__ __forceinline__ float tf32_round(float x)
+{
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+// value -> planes; MODE as SplitMode.  Every residual is exact in fp32, so the
+// planes sum to the input up to the rounding of the LAST plane only.
+template <int MODE>
+__device__ __forceinline__ void split1(float x, float &t0, float &t1, __nv_bfloat16 &b0,
+                                       __nv_bfloat16 &b1, __nv_bfloat16 &b2)
+{
+    if constexpr (MODE == SPLIT_TF32X2) {
+        t0 = tf32_round(x);
+        t1 = tf32_round(x - t0);
+    } else {
+        b0 = __float2bfloat16_rn(x);
+        if constexpr (MODE >= SPLIT_BF16X2) {
+            const float r1 = x - __bfloat162float(b0);
+            b1 = __float2bfloat16_rn(r1);
+            if constexpr (MODE >= SPLIT_BF16X3) b2 = __float2bfloat16_rn(r1 - __bfloat162float(b1));
+        }
+    }
+}
+
+template <int MODE>
+__device__ __forceinline__ void store1(void *const *pl, int64_t idx, float x)
+{
+    float t0 = 0, t1 = 0;
+    __nv_bfloat16 b0, b1, b2;
+    split1<MODE>(x, t0, t1, b0, b1, b2);
+    if constexpr (MODE == SPLIT_TF32X2) {
+        reinterpret_cast<float *>(pl[0])[idx] = t0;
+        reinterpret_cast<float *>(pl[1])[idx] = t1;
+    } else {
+        reinterpret_cast<__nv_bfloat16 *>(pl[0])[idx] = b0;
+        if constexpr (MODE >= SPLIT_BF16X2) reinterpret_cast<__nv_bfloat16 *>(pl[1])[idx] = b1;
+        if constexpr (MODE >= SPLIT_BF16X3) reinterpret_cast<__nv_bfloat16 *>(pl[2])[idx] = b2;
+    }
+}
+
+// two k-adjacent values at an even index: one 8-byte (tf32) or 4-byte (bf16) store per plane
+template <int MODE>
+__device__ __forceinline__ void store2(void *const *pl, int64_t idx, float x, float y)
+{
+    float xt0 = 0, xt1 = 0, yt0 = 0, yt1 = 0;
+    __nv_bfloat16 xb[3], yb[3];
+    split1<MODE>(x, xt0, xt1, xb[0], xb[1], xb[2]);
+    split1<MODE>(y, yt0, yt1, yb[0], yb[1], yb[2]);
+    if constexpr (MODE == SPLIT_TF32X2) {
+        *reinterpret_cast<float2 *>(reinterpret_cast<float *>(pl[0]) + idx) = make_float2(xt0, yt0);
+        *reinterpret_cast<float2 *>(reinterpret_cast<float *>(pl[1]) + idx) = make_float2(xt1, yt1);
+    } else {
+        constexpr int NP = MODE == SPLIT_BF16X1 ? 1 : (MODE == SPLIT_BF16X2 ? 2 : 3);
+#pragma unroll
+        for (int q = 0; q < NP; ++q)
+            *reinterpret_cast<uint32_t *>(reinterpret_cast<__nv_bfloat16 *>(pl[q]) + idx) =
+                (uint32_t)__bfloat16_as_ushort(xb[q]) | ((uint32_t)__bfloat16_as_ushort(yb[q]) << 16);
+    }
+}
+
+struct PlanePtrs {
+    void *p[3];
+};
+
+// in [rows, k] (k contiguous, row pitch ld) -> planes [rows, pitch]; 4 elements / thread
+template <int MODE>
+__global__ void __launch_bounds__(256) split_rows_kernel(const float *__restrict__ in, int64_t rows,
+                                                         int64_t k, int64_t ld, PlanePtrs pl, int64_t pitch)
+{
+    const int64_t k4 = (k + 3) / 4;
+    const int64_t total = rows * k4;
+    const bool vec = (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / k4, c = (i - r * k4) * 4;
+        const float *src = in + r * ld + c;
+        float x[4];
+        if (vec && c + 4 <= k) {
+            const float4 v = __ldg(reinterpret_cast<const float4 *>(src));
+            x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) x[j] = (c + j < k) ? __ldg(src + j) : 0.0f;
+        }
+        const int64_t o = r * pitch + c;  // pitch % 16 == 0, so 4-element groups never straddle
+        if constexpr (MODE == SPLIT_TF32X2) {
+            float4 hi, lo;
+            hi.x = tf32_round(x[0]); lo.x = tf32_round(x[0] - hi.x);
+            hi.y = tf32_round(x[1]); lo.y = tf32_round(x[1] - hi.y);
+            hi.z = tf32_round(x[2]); lo.z = tf32_round(x[2] - hi.z);
+            hi.w = tf32_round(x[3]); lo.w = tf32_round(x[3] - hi.w);
+            *reinterpret_cast<float4 *>(reinterpret_cast<float *>(pl.p[0]) + o) = hi;
+            *reinterpret_cast<float4 *>(reinterpret_cast<float *>(pl.p[1]) + o) = lo;
+        } else {
+            __nv_bfloat16 b[3][4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float t0, t1;
+                split1<MODE>(x[j], t0, t1, b[0][j], b[1][j], b[2][j]);
+            }
+            constexpr int NP = MODE == SPLIT_BF16X1 ? 1 : (MODE == SPLIT_BF16X2 ? 2 : 3);
+#pragma unroll
+            for (int q = 0; q < NP; ++q) {
+                uint2 w;
+                w.x = (uint32_t)__bfloat16_as_ushort(b[q][0]) | ((uint32_t)__bfloat16_as_ushort(b[q][1]) << 16);
+                w.y = (uint32_t)__bfloat16_as_ushort(b[q][2]) | ((uint32_t)__bfloat16_as_ushort(b[q][3]) << 16);
+                *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(pl.p[q]) + o) = w;
+            }
+        }
+    }
+}
+
+// in [k, rows] (rows contiguous, pitch ld) -> planes [rows, pitch] (k contiguous):
+// 64(k) x 32(rows) tiles through shared memory.
+template <int MODE>
+__global__ void __launch_bounds__(256) split_transpose_kernel(const float *__restrict__ in, int64_t rows,
+                                                              int64_t k, int64_t ld, PlanePtrs pl,
+                                                              int64_t pitch)
+{
+    __shared__ float tile[64][33];
+    const int64_t tiles_r = (rows + 31) / 32, tiles_k = (k + 63) / 64;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+    for (int64_t t = blockIdx.x; t < tiles_r * tiles_k; t += gridDim.x) {
+        const int64_t tr = t % tiles_r, tk = t / tiles_r;
+        const int64_t r0 = tr * 32, k0 = tk * 64;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int kk = ty + 8 * j;
+            const int64_t gk = k0 + kk, gr = r0 + tx;
+            tile[kk][tx] = (gk < k && gr < rows) ? __ldg(in + gk * ld + gr) : 0.0f;
+        }
+        __syncthreads();
+        // each warp writes 4 rows; a lane covers k = 2*tx, 2*tx+1
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int rr = ty * 4 + j;
+            const int64_t gr = r0 + rr;
+            if (gr < rows) {
+                const int kk = 2 * tx;
+                if (k0 + kk + 1 < k) store2<MODE>(pl.p, gr * pitch + k0 + kk, tile[kk][rr], tile[kk + 1][rr]);
+                else if (k0 + kk < k) store1<MODE>(pl.p, gr * pitch + k0 + kk, tile[kk][rr]);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+// int8 [rows, k] -> bf16 plane [rows, pitch] (every int8 is exact in bf16)
+__global__ void __launch_bounds__(256) widen_i8_bf16_kernel(const int8_t *__restrict__ in, int64_t rows,
+                                                            int64_t k, __nv_bfloat16 *out, int64_t pitch)
+{
+    const int64_t total = rows * k;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / k, c = i - r * k;
+        out[r * pitch + c] = __float2bfloat16_rn((float)in[i]);
+    }
+}
+
+__global__ void __launch_bounds__(256) repitch_i8_kernel(const int8_t *__restrict__ in, int64_t rows,
+                                                         int64_t k, int8_t *out, int64_t pitch)
+{
+    const int64_t total = rows * k;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t r = i / k, c = i - r * k;
+        out[r * pitch + c] = in[i];
+    }
+}
+
+// mult[n] = (a_scale * b_scales[n]) / out_scale with one rounding per operation
+__global__ void requant_mult_kernel(float a_scale, const float *__restrict__ b_scales, float out_scale,
+                                    int64_t n, float *mult)
+{
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) mult[i] = __fdiv_rn(__fmul_rn(a_scale, b_scales[i]), out_scale);
+}
+
+// one CTA per row: absmax, scale = absmax/127 (1 for a zero row), q = clamp(rint(w * (1/scale)))
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const float *__restrict__ w, int64_t k,
+                                                            int8_t *q, float *scales)
+{
+    __shared__ float red[8];
+    __shared__ float s_inv;
+    const int64_t n = blockIdx.x;
+    const float *row = w + n * k;
+    float m = 0.0f;
+    for (int64_t i = threadIdx.x; i < k; i += blockDim.x) m = fmaxf(m, fabsf(row[i]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float a = red[0];
+        for (int i = 1; i < (int)(blockDim.x >> 5); ++i) a = fmaxf(a, red[i]);
+        const float scale = a > 0.0f ? __fdiv_rn(a, 127.0f) : 1.0f;
+        scales[n] = scale;
+        s_inv = __fdiv_rn(1.0f, scale);
+    }
+    __syncthreads();
+    const float inv = s_inv;
+    for (int64_t i = threadIdx.x; i < k; i += blockDim.x) {
+        int v = __float2int_rn(__fmul_rn(row[i], inv));
+        v = max(-127, min(127, v));
+        q[n * k + i] = (int8_t)v;
+    }
+}
+
+// ---------------------------------------------------------------------- host
+
+static inline int grid_for(int64_t work_items, int threads, int sm_count)
+{
+    int64_t blocks = (work_items + threads - 1) / threads;
+    const int64_t cap = (int64_t)sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return (int)blocks;
+}
+
+int split_planes(int mode, const float *in, int64_t rows, int64_t k, int64_t ld, bool in_is_k_major_outer,
+                 void *const planes[3], int64_t pitch, int sm_count, cudaStream_t st)
+{
+    PlanePtrs pl;
+    for (int i = 0; i < 3; ++i) pl.p[i] = planes[i];
+    if (!in_is_k_major_outer) {
+        const int g = grid_for(rows * ((k + 3) / 4), 256, sm_count);
+        switch (mode) {
+        case SPLIT_TF32X2: split_rows_kernel<SPLIT_TF32X2><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch); break;
+        case SPLIT_BF16X1: split_rows_kernel<SPLIT_BF16X1><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch); break;
+        case SPLIT_BF16X2: split_rows_kernel<SPLIT_BF16X2><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch); break;
+        default: split_rows_kernel<SPLIT_BF16X3><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch); break;
+        }
+    } else {
+        const int64_t tiles = ((rows + 31) / 32) * ((k + 63) / 64);
+        const int64_t cap = (int64_t)sm_count * 8;
+        const int g = (int)(tiles < cap ? (tiles > 0 ? tiles : 1) : cap);
+        switch (mode) {
+        case SPLIT_TF32X2: split_transpose_kernel<SPLIT_TF32X2><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch); break;
+        case SPLIT_BF16X1: split_transpose_kernel<SPLIT_BF16X1><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch); break;
+        case SPLIT_BF16X2: split_transpose_kernel<SPLIT_BF16X2><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch); break;
+        default: split_transpose_kernel<SPLIT_BF16X3><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch); break;
+        }
+    }
+    return (int)cudaGetLastError();
+}
+
+int widen_i8_to_bf16(const int8_t *in, int64_t rows, int64_t k, void *out, int64_t pitch, int sm_count,
+                     cudaStream_t st)
+{
+    widen_i8_bf16_kernel<<<grid_for(rows * k, 256, sm_count), 256, 0, st>>>(
+        in, rows, k, reinterpret_cast<__nv_bfloat16 *>(out), pitch);
+    return (int)cudaGetLastError();
+}
+
+int repitch_i8(const int8_t *in, int64_t rows, int64_t k, int8_t *out, int64_t pitch, int sm_count,
+               cudaStream_t st)
+{
+    repitch_i8_kernel<<<grid_for(rows * k, 256, sm_count), 256, 0, st>>>(in, rows, k, out, pitch);
+    return (int)cudaGetLastError();
+}
+
+int requant_mult(float a_scale, const float *b_scales, float out_scale, int64_t n, float *mult,
+                 cudaStream_t st)
+{
+    requant_mult_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a_scale, b_scales, out_scale, n, mult);
+    return (int)cudaGetLastError();
+}
+
+int quantize_rows(const float *w, int64_t n, int64_t k, int8_t *q, float *scales, cudaStream_t st)
+{
+    quantize_rows_kernel<<<(unsigned)n, 256, 0, st>>>(w, k, q, scales);
+    return (int)cudaGetLastError();
+}
+
+}  // namespace axb

@@ -1,0 +1,25 @@
+// prepass.cuh — operand-preparation launchers (see prepass.cu).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace axb {
+
+enum SplitMode { SPLIT_TF32X2 = 0, SPLIT_BF16X1 = 1, SPLIT_BF16X2 = 2, SPLIT_BF16X3 = 3 };
+
+static inline int split_num_planes(int mode) { return mode == SPLIT_BF16X1 ? 1 : (mode == SPLIT_BF16X3 ? 3 : 2); }
+static inline int split_elem_bytes(int mode) { return mode == SPLIT_TF32X2 ? 4 : 2; }
+
+// in: fp32, either [rows, k] with pitch ld (in_is_k_major_outer = false) or
+// [k, rows] with pitch ld (true).  planes: [rows, pitch] each, k contiguous.
+int split_planes(int mode, const float *in, int64_t rows, int64_t k, int64_t ld, bool in_is_k_major_outer,
+                 void *const planes[3], int64_t pitch, int sm_count, cudaStream_t st);
+int widen_i8_to_bf16(const int8_t *in, int64_t rows, int64_t k, void *out, int64_t pitch, int sm_count,
+                     cudaStream_t st);
+int repitch_i8(const int8_t *in, int64_t rows, int64_t k, int8_t *out, int64_t pitch, int sm_count,
+               cudaStream_t st);
+int requant_mult(float a_scale, const float *b_scales, float out_scale, int64_t n, float *mult,
+                 cudaStream_t st);
+int quantize_rows(const float *w, int64_t n, int64_t k, int8_t *q, float *scales, cudaStream_t st);
+
+}  // namespace axb

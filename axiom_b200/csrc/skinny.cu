@@ -1,0 +1,202 @@
+// skinny.cu — the bandwidth-bound skinny-M route (M <= 32, bs=1 GEMV included):
+//     Y[M,N] = act(alpha * X[M,K] . W[K,N] + beta * Y + bias[n])
+// W is streamed from HBM exactly once with 128-bit loads; everything else is
+// small.  A CTA owns a 128-column strip and a slice of K: its 8 warps walk
+// interleaved rows of the slice (one float4 of W per lane per row, all M
+// outputs of those 4 columns accumulated in registers, X broadcast from shared
+// memory), then the warps' sums are combined through shared memory in a fixed
+// order.  When K is split across CTAs each CTA writes its partial strip to
+// scratch and the LAST CTA to arrive for a strip (a counter per strip) adds
+// the partials in slice order and applies the epilogue, so results do not
+// depend on scheduling: repeated calls are bitwise identical.
+#include "skinny.cuh"
+
+#include <stdint.h>
+
+namespace axb {
+
+static constexpr int SK_THREADS = 256;
+static constexpr int SK_WARPS = 8;
+static constexpr int SK_STRIP = 128;  // columns per CTA
+
+__device__ __forceinline__ float sk_gelu(float v)
+{
+    const float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+    return 0.5f * v * (1.0f + tanhf(inner));
+}
+
+__device__ __forceinline__ float sk_epilogue(const SkinnyArgs &a, float v, int m, int col)
+{
+    v *= a.alpha;
+    if (a.beta != 0.0f) v += a.beta * a.Y[(int64_t)m * a.N + col];
+    if (a.bias) v += __ldg(a.bias + col);
+    if (a.act == 1) v = fmaxf(v, 0.0f);
+    else if (a.act == 2) v = sk_gelu(v);
+    return v;
+}
+
+template <int MT, bool VEC>
+__global__ void __launch_bounds__(SK_THREADS) skinny_kernel(const SkinnyArgs a)
+{
+    constexpr int RM = MT < 8 ? MT : 8;          // rows combined per reduction round
+    constexpr int UNROLL = MT >= 32 ? 2 : (MT >= 16 ? 4 : 8);
+    extern __shared__ float smem[];
+    __shared__ int s_last;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int strip = blockIdx.x, ks = blockIdx.y;
+    const int64_t k_begin = (int64_t)ks * a.kchunk;
+    const int kc = (int)min((int64_t)a.kchunk, a.K - k_begin);  // rows of this slice (may be <= 0)
+    const int col = strip * SK_STRIP + lane * 4;
+
+    // X slice -> shared, transposed to [k][MT] so one k reads MT contiguous floats
+    float *xs = smem;
+    for (int i = tid; i < kc * MT; i += SK_THREADS) {
+        const int m = i / kc, kk = i - m * kc;
+        xs[kk * MT + m] = (m < a.M) ? __ldg(a.X + (int64_t)m * a.K + k_begin + kk) : 0.0f;
+    }
+    __syncthreads();
+
+    float acc[MT][4];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.0f;
+
+    if (col < a.N) {
+        const float *wp = a.W + k_begin * a.N + col;
+        for (int kk0 = warp; kk0 < kc; kk0 += SK_WARPS * UNROLL) {
+            float4 w[UNROLL];
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int kk = kk0 + u * SK_WARPS;
+                if (kk < kc) {
+                    const float *src = wp + (int64_t)kk * a.N;
+                    if constexpr (VEC) {
+                        w[u] = __ldcs(reinterpret_cast<const float4 *>(src));
+                    } else {
+                        w[u].x = __ldcs(src);
+                        w[u].y = (col + 1 < a.N) ? __ldcs(src + 1) : 0.0f;
+                        w[u].z = (col + 2 < a.N) ? __ldcs(src + 2) : 0.0f;
+                        w[u].w = (col + 3 < a.N) ? __ldcs(src + 3) : 0.0f;
+                    }
+                } else {
+                    w[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < UNROLL; ++u) {
+                const int kk = kk0 + u * SK_WARPS;
+                if (kk < kc) {
+                    const float *xr = xs + kk * MT;
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        const float xv = xr[m];
+                        acc[m][0] = fmaf(xv, w[u].x, acc[m][0]);
+                        acc[m][1] = fmaf(xv, w[u].y, acc[m][1]);
+                        acc[m][2] = fmaf(xv, w[u].z, acc[m][2]);
+                        acc[m][3] = fmaf(xv, w[u].w, acc[m][3]);
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();  // xs is dead from here: the same shared memory holds the warp sums
+
+    float *red = smem;  // [SK_WARPS][RM][SK_STRIP]
+    float *part = a.partial ? a.partial + (int64_t)ks * a.M * a.N : nullptr;
+#pragma unroll 1
+    for (int m0 = 0; m0 < MT; m0 += RM) {
+#pragma unroll
+        for (int mi = 0; mi < RM; ++mi)
+            *reinterpret_cast<float4 *>(red + ((warp * RM + mi) * SK_STRIP + lane * 4)) =
+                make_float4(acc[m0 + mi][0], acc[m0 + mi][1], acc[m0 + mi][2], acc[m0 + mi][3]);
+        __syncthreads();
+        for (int o = tid; o < RM * SK_STRIP; o += SK_THREADS) {
+            const int mi = o / SK_STRIP, c = o - mi * SK_STRIP;
+            const int m = m0 + mi, gc = strip * SK_STRIP + c;
+            if (m < a.M && gc < a.N) {
+                float s = 0.0f;
+#pragma unroll
+                for (int w = 0; w < SK_WARPS; ++w) s += red[(w * RM + mi) * SK_STRIP + c];
+                if (a.ksplit == 1) a.Y[(int64_t)m * a.N + gc] = sk_epilogue(a, s, m, gc);
+                else part[(int64_t)m * a.N + gc] = s;
+            }
+        }
+        __syncthreads();
+    }
+
+    if (a.ksplit > 1) {
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const int prev = atomicAdd(a.counters + strip, 1);
+            s_last = (prev == a.ksplit - 1);
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            const int ncols = min(SK_STRIP, (int)(a.N - (int64_t)strip * SK_STRIP));
+            for (int o = tid; o < a.M * ncols; o += SK_THREADS) {
+                const int m = o / ncols, gc = strip * SK_STRIP + (o - m * ncols);
+                float s = 0.0f;
+                for (int q = 0; q < a.ksplit; ++q)
+                    s += __ldcg(a.partial + ((int64_t)q * a.M + m) * a.N + gc);
+                a.Y[(int64_t)m * a.N + gc] = sk_epilogue(a, s, m, gc);
+            }
+            if (tid == 0) a.counters[strip] = 0;  // ready for the next call
+        }
+    }
+}
+
+template <int MT>
+static int launch_mt(const SkinnyArgs &a, bool vec, dim3 grid, size_t smem, cudaStream_t st)
+{
+    auto kv = skinny_kernel<MT, true>;
+    auto ks = skinny_kernel<MT, false>;
+    if (smem > 48 * 1024) {
+        cudaFuncSetAttribute(kv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaFuncSetAttribute(ks, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    }
+    if (vec) kv<<<grid, SK_THREADS, smem, st>>>(a);
+    else ks<<<grid, SK_THREADS, smem, st>>>(a);
+    return (int)cudaGetLastError();
+}
+
+static int mt_for(int64_t M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : M <= 16 ? 16 : 32; }
+
+void skinny_plan(int64_t M, int64_t N, int64_t K, int sm_count, SkinnyPlan *plan)
+{
+    const int mt = mt_for(M);
+    const int strips = (int)((N + SK_STRIP - 1) / SK_STRIP);
+    int64_t ksplit = (2 * (int64_t)sm_count) / strips;
+    if (ksplit < 1) ksplit = 1;
+    const int64_t max_split = (K + 63) / 64;  // at least 8 rows per warp
+    if (ksplit > max_split) ksplit = max_split;
+    int64_t kchunk = (K + ksplit - 1) / ksplit;
+    const int64_t max_chunk = (64 * 1024) / (4 * mt);  // keep the X slice within 64 KB of shared memory
+    if (kchunk > max_chunk) kchunk = max_chunk;
+    ksplit = (K + kchunk - 1) / kchunk;
+    plan->mt = mt;
+    plan->strips = strips;
+    plan->ksplit = (int)ksplit;
+    plan->kchunk = (int)kchunk;
+    plan->partial_floats = ksplit > 1 ? ksplit * M * N : 0;
+    const int rm = mt < 8 ? mt : 8;
+    size_t sx = (size_t)kchunk * mt * 4, sr = (size_t)SK_WARPS * rm * SK_STRIP * 4;
+    plan->smem_bytes = sx > sr ? sx : sr;
+}
+
+int launch_skinny(const SkinnyArgs &args, const SkinnyPlan &plan, cudaStream_t st)
+{
+    const bool vec = (args.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.W) & 15) == 0);
+    dim3 grid((unsigned)plan.strips, (unsigned)plan.ksplit);
+    switch (plan.mt) {
+    case 1: return launch_mt<1>(args, vec, grid, plan.smem_bytes, st);
+    case 2: return launch_mt<2>(args, vec, grid, plan.smem_bytes, st);
+    case 4: return launch_mt<4>(args, vec, grid, plan.smem_bytes, st);
+    case 8: return launch_mt<8>(args, vec, grid, plan.smem_bytes, st);
+    case 16: return launch_mt<16>(args, vec, grid, plan.smem_bytes, st);
+    default: return launch_mt<32>(args, vec, grid, plan.smem_bytes, st);
+    }
+}
+
+}  // namespace axb

@@ -1,0 +1,32 @@
+// skinny.cuh — launcher interface of the skinny-M (GEMV) route, see skinny.cu.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace axb {
+
+struct SkinnyArgs {
+    const float *X;     // [M,K]
+    const float *W;     // [K,N]
+    const float *bias;  // [N] or null
+    float *Y;           // [M,N]
+    int M;
+    int64_t N, K;
+    float alpha, beta;
+    int act;
+    int ksplit, kchunk;
+    float *partial;     // [ksplit][M][N] scratch when ksplit > 1
+    int *counters;      // [strips] zero between calls
+};
+
+struct SkinnyPlan {
+    int mt, strips, ksplit, kchunk;
+    int64_t partial_floats;  // scratch the plan needs (0 when K is not split)
+    size_t smem_bytes;
+};
+
+void skinny_plan(int64_t M, int64_t N, int64_t K, int sm_count, SkinnyPlan *plan);
+int launch_skinny(const SkinnyArgs &args, const SkinnyPlan &plan, cudaStream_t st);
+
+}  // namespace axb

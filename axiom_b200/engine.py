@@ -1,0 +1,188 @@
+"""ctypes binding of libaxiom_b200.so for Python callers (tests, bench, multi-GPU drivers).
+
+The functions mirror the C ABI in include/axiom_b200.h one to one and take
+torch CUDA tensors (or raw device pointers as ints) for the buffers.  torch is
+used only to own device memory; every computation is a kernel of the library.
+There is no fallback: if the shared library is missing, loading raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+ENGINE_SO = os.path.join(PKG, "lib", "libaxiom_b200.so")
+
+ACT = {"none": 0, None: 0, "relu": 1, "gelu": 2}
+FP32_MODES = {"3xtf32": 0, "bf16x3": 1, "bf16": 2}
+
+# every symbol include/axiom_b200.h declares
+EXPORTS = [
+    "axb_init", "axb_shutdown", "axb_device_count", "axb_synchronize", "axb_storage_alloc",
+    "axb_storage_free", "axb_memcpy_h2d", "axb_memcpy_d2h", "axb_memcpy_d2d", "axb_set_stream",
+    "axb_set_fp32_mode", "axb_get_fp32_mode", "axb_last_error", "axb_device_error", "axb_launch_count",
+    "axb_set_profiling", "axb_last_timing",
+    "axb_gemm", "axb_gemm_nt", "axb_gemm_tn", "axb_gemm_ex", "axb_gemm_relu", "axb_gemm_bias_act",
+    "axb_bias_add", "axb_relu", "axb_gelu", "axb_qgemm_w8a32", "axb_qgemm_w8a8", "axb_quantize_rows",
+    "axb_sdpa_fwd",
+]
+
+
+class EngineError(RuntimeError):
+    def __init__(self, status, message):
+        super().__init__(f"axiom_b200 status {status}: {message}")
+        self.status = status
+
+
+def _ptr(t):
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return C.c_void_p(t)
+    return C.c_void_p(t.data_ptr())
+
+
+_i64 = C.c_int64
+_f = C.c_float
+
+
+class Engine:
+    """One engine per process (one process per GPU)."""
+
+    def __init__(self, device: int | None = None, so_path: str = ENGINE_SO):
+        if not os.path.exists(so_path):
+            raise FileNotFoundError(
+                f"{so_path} is missing: build it with `python -m axiom_b200.build` (no CPU fallback exists)")
+        self.lib = C.CDLL(so_path)
+        L = self.lib
+        L.axb_last_error.restype = C.c_char_p
+        L.axb_storage_alloc.restype = C.c_void_p
+        L.axb_storage_alloc.argtypes = [C.c_size_t]
+        L.axb_storage_free.argtypes = [C.c_void_p]
+        L.axb_launch_count.restype = C.c_int64
+        L.axb_set_stream.argtypes = [C.c_void_p]
+        for name in ("axb_memcpy_h2d", "axb_memcpy_d2h", "axb_memcpy_d2d"):
+            getattr(L, name).argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+        if device is not None:
+            self._check(L.axb_init(int(device)))
+
+    # ---- plumbing ------------------------------------------------------
+    def _check(self, status):
+        if status != 0:
+            raise EngineError(status, self.lib.axb_last_error().decode())
+
+    def init(self, device=-1):
+        self._check(self.lib.axb_init(int(device)))
+
+    def synchronize(self):
+        self.lib.axb_synchronize()
+
+    def device_error(self):
+        return int(self.lib.axb_device_error())
+
+    def launch_count(self, reset=False):
+        return int(self.lib.axb_launch_count(int(reset)))
+
+    def set_profiling(self, on=True):
+        self.lib.axb_set_profiling(int(bool(on)))
+
+    def last_timing(self):
+        """(prepass_ms, core_ms) of the last timed call; blocks until it has finished."""
+        a, b = C.c_float(0), C.c_float(0)
+        self._check(self.lib.axb_last_timing(C.byref(a), C.byref(b)))
+        return a.value, b.value
+
+    def set_fp32_mode(self, mode):
+        self._check(self.lib.axb_set_fp32_mode(FP32_MODES[mode] if isinstance(mode, str) else int(mode)))
+
+    def set_stream(self, stream_ptr):
+        self.lib.axb_set_stream(C.c_void_p(stream_ptr))
+
+    def last_error(self):
+        return self.lib.axb_last_error().decode()
+
+    def memcpy_h2d(self, dst, src_host_ptr, nbytes):
+        self._check(self.lib.axb_memcpy_h2d(_ptr(dst), C.c_void_p(src_host_ptr), nbytes))
+
+    def memcpy_d2h(self, dst_host_ptr, src, nbytes):
+        self._check(self.lib.axb_memcpy_d2h(C.c_void_p(dst_host_ptr), _ptr(src), nbytes))
+
+    # ---- GEMM family (out is caller-allocated, as in the reference) -----
+    def gemm(self, A, B, out, variant="nn"):
+        if variant == "nn":
+            M, K = A.shape; N = B.shape[1]
+            self._check(self.lib.axb_gemm(_ptr(A), _ptr(B), _ptr(out), _i64(M), _i64(N), _i64(K)))
+        elif variant == "nt":
+            M, K = A.shape; N = B.shape[0]
+            self._check(self.lib.axb_gemm_nt(_ptr(A), _ptr(B), _ptr(out), _i64(M), _i64(N), _i64(K)))
+        else:
+            K, M = A.shape; N = B.shape[1]
+            self._check(self.lib.axb_gemm_tn(_ptr(A), _ptr(B), _ptr(out), _i64(M), _i64(N), _i64(K)))
+        return out
+
+    def gemm_ex(self, A, B, alpha, beta, out):
+        M, K = A.shape; N = B.shape[1]
+        self._check(self.lib.axb_gemm_ex(_ptr(A), _ptr(B), _f(alpha), _f(beta), _ptr(out), _i64(M), _i64(N), _i64(K)))
+        return out
+
+    def gemm_relu(self, A, B, bias, out):
+        M, K = A.shape; N = B.shape[1]
+        self._check(self.lib.axb_gemm_relu(_ptr(A), _ptr(B), _ptr(bias), _ptr(out), _i64(M), _i64(N), _i64(K)))
+        return out
+
+    def gemm_bias_act(self, A, B, bias, out, M, N, K, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, act="none"):
+        self._check(self.lib.axb_gemm_bias_act(_ptr(A), _ptr(B), _ptr(bias), _ptr(out), _i64(M), _i64(N), _i64(K),
+                                               int(trans_a), int(trans_b), _f(alpha), _f(beta), ACT[act]))
+        return out
+
+    # ---- elementwise ---------------------------------------------------
+    def bias_add(self, X, bias, axis, out):
+        M, N = X.shape
+        self._check(self.lib.axb_bias_add(_ptr(X), _ptr(bias), int(axis), _ptr(out), _i64(M), _i64(N)))
+        return out
+
+    def relu(self, X, out):
+        self._check(self.lib.axb_relu(_ptr(X), _ptr(out), _i64(X.numel())))
+        return out
+
+    def gelu(self, X, out):
+        self._check(self.lib.axb_gelu(_ptr(X), _ptr(out), _i64(X.numel())))
+        return out
+
+    # ---- quantised -----------------------------------------------------
+    def qgemm_w8a32(self, a, q, scales, out):
+        M, K = a.shape; N = q.shape[0]
+        self._check(self.lib.axb_qgemm_w8a32(_ptr(a), _ptr(q), _ptr(scales), _ptr(out), _i64(M), _i64(N), _i64(K)))
+        return out
+
+    def qgemm_w8a8(self, a_q, a_scale, b_q, b_scales, out_scale, out_q=None, acc_out=None):
+        M, K = a_q.shape; N = b_q.shape[0]
+        self._check(self.lib.axb_qgemm_w8a8(_ptr(a_q), _f(a_scale), _ptr(b_q), _ptr(b_scales), _f(out_scale),
+                                            _ptr(out_q), _ptr(acc_out), _i64(M), _i64(N), _i64(K)))
+        return out_q, acc_out
+
+    def quantize_rows(self, W, q, scales):
+        N, K = W.shape
+        self._check(self.lib.axb_quantize_rows(_ptr(W), _i64(N), _i64(K), _ptr(q), _ptr(scales)))
+        return q, scales
+
+    # ---- attention -----------------------------------------------------
+    def sdpa_fwd(self, Q, K, V, out, L, scale, causal):
+        BH, S, dk = Q.shape
+        self._check(self.lib.axb_sdpa_fwd(_ptr(Q), _ptr(K), _ptr(V), _ptr(out), _ptr(L), _i64(BH), _i64(S), _i64(dk),
+                                          _f(scale), int(bool(causal)), None))
+        return out, L
+
+
+_engine = None
+
+
+def get_engine(device: int | None = None) -> Engine:
+    """Process-wide engine, initialised on `device` (default: torch's current device)."""
+    global _engine
+    if _engine is None:
+        if device is None:
+            import torch
+            device = torch.cuda.current_device()
+        _engine = Engine(device)
+    return _engine

@@ -1,0 +1,152 @@
+/* axiom_b200.h — C ABI of libaxiom_b200.so, a Blackwell (sm_100a) engine for
+   axiom's matmul-dispatch hot path.
+
+   Every entry point takes plain pointers and sizes.  Unless a parameter is
+   named *_host, data pointers are DEVICE pointers on the device chosen by
+   axb_init; matrices are dense row-major.  Work is enqueued asynchronously on
+   the engine's stream (the legacy default stream unless axb_set_stream was
+   called), exactly like the reference CUDA backend; results become visible to
+   the host after axb_synchronize() or a blocking axb_memcpy_d2h().
+
+   Return values are axiom's status codes (include/axiom/types.h:89-103 of the
+   reference): 0 = AX_OK, 1 = NULL_ARG, 2 = ALLOC, 3 = SHAPE_MISMATCH,
+   7 = INVALID_DTYPE, 9 = BACKEND, 10 = NOT_IMPLEMENTED ...  The engine never
+   aborts and never falls back to host arithmetic; axb_last_error() returns
+   the message of the most recent failure on the calling thread's engine.
+
+   Each declaration cites the reference interface it replaces as
+   file:line within the axiom source tree. */
+#ifndef AXIOM_B200_H
+#define AXIOM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* exported from the shared library (everything else in it is hidden) */
+#define AXB_API __attribute__((visibility("default")))
+
+#define AXB_OK 0
+#define AXB_ERR_NULL_ARG 1
+#define AXB_ERR_ALLOC 2
+#define AXB_ERR_SHAPE_MISMATCH 3
+#define AXB_ERR_INVALID_AXIS 5
+#define AXB_ERR_INVALID_SHAPE 6
+#define AXB_ERR_BACKEND 9
+#define AXB_ERR_NOT_IMPLEMENTED 10
+
+/* activation selectors for the fused epilogues */
+#define AXB_ACT_NONE 0
+#define AXB_ACT_RELU 1
+#define AXB_ACT_GELU 2 /* tanh approximation, src/core/activations.c:23-25 */
+
+/* how fp32 GEMMs are computed on the tensor cores */
+#define AXB_FP32_3XTF32 0 /* hi/lo TF32 split, 3 products: normalised error <= 1e-5 (default) */
+#define AXB_FP32_BF16X3 1 /* hi/lo bf16 split, 3 products: same bound on well-scaled data, 2x faster */
+#define AXB_FP32_BF16 2   /* single bf16 product: normalised error <= 5e-3 */
+
+/* ---- lifecycle and device-owner hooks ------------------------------------
+   Replace cuda_init_hook / cuda_shutdown_hook / cuda_sync_hook /
+   cuda_device_count_hook (src/compute/backends/cuda/backend.cu:56-116) and the
+   storage + memcpy hooks (src/compute/backends/cuda/memory.cu:80-140), i.e. the
+   device-owner slots of ax_backend_ops_t
+   (include/axiom/internal/backend_ops.h:262-296). */
+AXB_API int axb_init(int device);      /* idempotent; also reads AX_B200_FP32_MODE = 3xtf32|bf16x3|bf16 */
+AXB_API void axb_shutdown(void);
+AXB_API int axb_device_count(void);
+AXB_API void axb_synchronize(void);    /* blocks; afterwards axb_device_error() is current */
+AXB_API void *axb_storage_alloc(size_t bytes);   /* zero-filled, like the reference's pool allocator */
+AXB_API void axb_storage_free(void *ptr);
+AXB_API int axb_memcpy_h2d(void *dst, const void *src_host, size_t bytes); /* blocking */
+AXB_API int axb_memcpy_d2h(void *dst_host, const void *src, size_t bytes); /* blocking */
+AXB_API int axb_memcpy_d2d(void *dst, const void *src, size_t bytes);
+AXB_API void axb_set_stream(void *cuda_stream); /* NULL = legacy default stream */
+AXB_API int axb_set_fp32_mode(int mode);        /* AXB_FP32_* */
+AXB_API int axb_get_fp32_mode(void);
+AXB_API const char *axb_last_error(void);
+/* Non-zero when a kernel gave up on a bounded wait (its code); reading clears it. */
+AXB_API int axb_device_error(void);
+/* Kernels enqueued by this library since the counter was last reset. */
+AXB_API int64_t axb_launch_count(int reset);
+/* Measurement aid (no reference counterpart): with profiling on, every GEMM-family,
+   quantised-GEMM and attention call records CUDA events on the engine's stream
+   around its operand pre-pass and around its main kernel; axb_last_timing blocks
+   on the last such call and returns both durations in milliseconds. */
+AXB_API void axb_set_profiling(int on);
+AXB_API int axb_last_timing(float *prepass_ms, float *core_ms);
+
+/* ---- dense fp32 GEMM family ----------------------------------------------
+   Slots gemm / gemm_nt / gemm_tn / gemm_ex / gemm_relu of ax_backend_ops_t
+   (backend_ops.h:54-65,156-165), reference CUDA implementations
+   src/compute/backends/cuda/ops_gemm.cu:15-126 (cuBLAS) and CPU
+   src/compute/backends/cpu_opt.c:3446,4842,5660,7401,7442. */
+
+/* C[M,N] = A[M,K] . B[K,N]                        (ax_compute_gemm, dispatch.c:414) */
+AXB_API int axb_gemm(const float *A, const float *B, float *C, int64_t M, int64_t N, int64_t K);
+/* C[M,N] = A[M,K] . B[N,K]^T                      (ax_compute_gemm_nt, dispatch.c:419) */
+AXB_API int axb_gemm_nt(const float *A, const float *B, float *C, int64_t M, int64_t N, int64_t K);
+/* C[M,N] = A[K,M]^T . B[K,N]                      (ax_compute_gemm_tn, dispatch.c:430) */
+AXB_API int axb_gemm_tn(const float *A, const float *B, float *C, int64_t M, int64_t N, int64_t K);
+/* C = alpha * A.B + beta * C; beta == 0 never reads C   (ax_compute_gemm_ex, dispatch.c:642) */
+AXB_API int axb_gemm_ex(const float *A, const float *B, float alpha, float beta, float *C,
+                int64_t M, int64_t N, int64_t K);
+/* C = max(A.B + bias[n], 0); bias may be NULL      (ax_compute_gemm_relu, dispatch.c:443) */
+AXB_API int axb_gemm_relu(const float *A, const float *B, const float *bias, float *C,
+                  int64_t M, int64_t N, int64_t K);
+/* The general form all of the above reduce to:
+     C = act(alpha * op(A).op(B) + beta * C + bias[n])
+   trans_a: A stored [K,M]; trans_b: B stored [N,K]; act = AXB_ACT_*.
+   This is the dense-layer path of src/core/ops.c:295-440 (matmul, bias, activation)
+   in one launch; act = GELU fuses the separate ax_gelu pass
+   (src/core/layer.c:110-114).  M <= 32 with B stored [K,N] takes the
+   bandwidth-bound skinny route (the reference's tiny-M AXPY path,
+   cpu_opt.c:3499-3567). */
+AXB_API int axb_gemm_bias_act(const float *A, const float *B, const float *bias, float *C,
+                      int64_t M, int64_t N, int64_t K, int trans_a, int trans_b,
+                      float alpha, float beta, int act);
+
+/* ---- elementwise slots that remain as separate calls ---------------------- */
+/* out = in + bias broadcast along axis (0: bias[M], 1: bias[N]); out may alias in.
+   (bias_add slot, backend_ops.h:190; src/compute/backends/cuda/ops_fused.cu:260-292) */
+AXB_API int axb_bias_add(const float *in, const float *bias, int axis, float *out, int64_t M, int64_t N);
+/* (relu slot, backend_ops.h:235) */
+AXB_API int axb_relu(const float *in, float *out, int64_t n);
+/* (gelu_op slot, backend_ops.h:244; src/compute/backends/cuda/ops_activations.cu:12-24) */
+AXB_API int axb_gelu(const float *in, float *out, int64_t n);
+
+/* ---- quantised GEMM -------------------------------------------------------- */
+/* W8A32: out[M,N] = scales[n] * sum_k a[m,k] * q[n,k], q int8 [N,K], fp32 result.
+   Device-pointer form of ax_qgemm_w8a32 (include/axiom/quantize.h:75-79,
+   src/core/quantize.c:100-177); q/scales/N/K are the fields of ax_qweight_t. */
+AXB_API int axb_qgemm_w8a32(const float *a, const int8_t *q, const float *scales, float *out,
+                    int64_t M, int64_t N, int64_t K);
+/* W8A8: acc[m,n] = sum_k a_q[m,k] * b_q[n,k] in int32 (exact), then
+     out_q[m,n] = clamp(rint(acc * ((a_scale * b_scales[n]) / out_scale)), -127, 127).
+   acc_out (int32 [M,N]) and out_q (int8 [M,N]) may each be NULL.
+   No counterpart in the reference (it has no int8 x int8 kernel); rounding and
+   clamp follow its quantiser, src/core/quantize.c:45-54. */
+AXB_API int axb_qgemm_w8a8(const int8_t *a_q, float a_scale, const int8_t *b_q, const float *b_scales,
+                   float out_scale, int8_t *out_q, int32_t *acc_out,
+                   int64_t M, int64_t N, int64_t K);
+/* Per-row symmetric int8 quantiser on the device: scales[n] = absmax/127 (1 for a
+   zero row), q = clamp(rint(w / scale)).  (ax_qweight_create_from_fp32,
+   src/core/quantize.c:21-57) */
+AXB_API int axb_quantize_rows(const float *w, int64_t N, int64_t K, int8_t *q, float *scales);
+
+/* ---- attention ------------------------------------------------------------- */
+/* O = softmax(scale * Q.K^T [+ causal mask]) . V per head on head-major
+   [BH,S,dk] buffers; L[BH,S] = log-sum-exp per row or NULL.  P_save must be NULL
+   (returns NOT_IMPLEMENTED otherwise, which the caller treats as "no saved P").
+   (sdpa_fwd slot of ax_cuda_extension_t, include/axiom/internal/cuda_extension.h:89-92;
+   src/compute/backends/cuda/ops_attention.cu:299-392; public CPU form
+   ax_fused_attention_fwd[_causal], include/axiom/attention.h:273-280) */
+AXB_API int axb_sdpa_fwd(const float *Q, const float *K, const float *V, float *out, float *L,
+                 int64_t BH, int64_t S, int64_t dk, float scale, int causal, float *P_save);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AXIOM_B200_H */

@@ -1,0 +1,276 @@
+"""Parity of the CUDA path with the CPU oracle, through the C ABI.
+
+Integer work (int32 accumulators, requantised int8, the row quantiser) must be
+bit-exact.  fp32 results are held to the normalised error
+max|gpu - ref| / max|ref| <= 1e-5 in the split-precision modes and <= 5e-3 in
+bf16 mode, against a double-precision restatement, and to the reference's own
+test tolerances against its golden outputs.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle_lib import nerr
+
+pytestmark = pytest.mark.gpu
+
+TOL_SPLIT = 1e-5
+TOL_BF16 = 5e-3
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x)).cuda()
+
+
+def host(t):
+    return t.cpu().numpy()
+
+
+def run_gemm(engine, A, B, variant="nn"):
+    M = A.shape[1] if variant == "tn" else A.shape[0]
+    N = B.shape[0] if variant == "nt" else B.shape[1]
+    out = torch.full((M, N), float("nan"), device="cuda")
+    engine.gemm(dev(A), dev(B), out, variant)
+    return host(out)
+
+
+def test_known_answers(engine, golden):
+    for tag in ("kat_gemm_2x3x2", "kat_gemm_2x2"):
+        np.testing.assert_allclose(run_gemm(engine, golden[tag + "_a"], golden[tag + "_b"]), golden[tag + "_c"], atol=1e-4)
+
+
+@pytest.mark.parametrize("name", ["g_small", "g_cuda_test", "g_odd", "g_96", "g_k1", "g_skinny1", "g_skinny8"])
+def test_gemm_family_vs_golden(engine, oracle, golden, name):
+    M, N, K = (int(v) for v in golden[name + "_shape"])
+    A, B, bias, Cin = oracle.uniform((M, K), 7), oracle.uniform((K, N), 13), oracle.uniform((N,), 29), oracle.uniform((M, N), 5)
+    tol = dict(atol=1e-3, rtol=1e-4)   # the reference's property-test tolerance
+    np.testing.assert_allclose(run_gemm(engine, A, B), golden[name + "_nn"], **tol)
+    np.testing.assert_allclose(run_gemm(engine, A, np.ascontiguousarray(B.T), "nt"), golden[name + "_nt"], **tol)
+    np.testing.assert_allclose(run_gemm(engine, np.ascontiguousarray(A.T), B, "tn"), golden[name + "_tn"], **tol)
+    out = torch.empty((M, N), device="cuda")
+    engine.gemm_relu(dev(A), dev(B), dev(bias), out)
+    np.testing.assert_allclose(host(out), golden[name + "_relu"], **tol)
+    engine.gemm_bias_act(dev(A), dev(B), dev(bias), out, M, N, K, act="gelu")
+    np.testing.assert_allclose(host(out), golden[name + "_gelu"], **tol)
+    c = dev(Cin)
+    engine.gemm_ex(dev(A), dev(B), 0.5, 2.0, c)
+    np.testing.assert_allclose(host(c), golden[name + "_ex"], **tol)
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_gemm_property_small_shapes(engine, oracle, seed):
+    # mirrors tests/test_property.c:176-209 of the reference: 1 <= M,N,K <= 96, U[-2,2]
+    rng = np.random.RandomState(1000 + seed)
+    M, N, K = (int(v) for v in rng.randint(1, 97, size=3))
+    A, B = 2 * oracle.uniform((M, K), 11 + seed), 2 * oracle.uniform((K, N), 77 + seed)
+    ref = oracle.gemm(A, B)
+    for variant, a, b in (("nn", A, B), ("nt", A, np.ascontiguousarray(B.T)), ("tn", np.ascontiguousarray(A.T), B)):
+        np.testing.assert_allclose(run_gemm(engine, a, b, variant), ref, atol=1e-3, rtol=1e-4)
+
+
+@pytest.mark.parametrize("shape", [(128, 256, 32), (129, 257, 33), (300, 520, 1000), (257, 64, 4100), (1024, 1024, 1024)])
+@pytest.mark.parametrize("mode", ["3xtf32", "bf16x3", "bf16"])
+def test_gemm_modes_normalised_error(engine, oracle, shape, mode):
+    M, N, K = shape
+    A, B = oracle.uniform((M, K), 7), oracle.uniform((K, N), 13)
+    ref64 = oracle.gemm_f64(A, B)
+    engine.set_fp32_mode(mode)
+    try:
+        got = run_gemm(engine, A, B)
+    finally:
+        engine.set_fp32_mode("3xtf32")
+    assert np.isfinite(got).all()
+    assert nerr(got, ref64) <= (TOL_BF16 if mode == "bf16" else TOL_SPLIT), (mode, nerr(got, ref64))
+
+
+def test_config1_dense_relu_1024(engine, oracle):
+    """BASELINE config 1: C = ReLU(A.B + bias), M=N=K=1024, U[-1,1] seeds 7/13/29."""
+    A, B, bias = oracle.uniform((1024, 1024), 7), oracle.uniform((1024, 1024), 13), oracle.uniform((1024,), 29)
+    ref = oracle.bias_act(oracle.gemm(A, B), bias, "relu")
+    ref64 = np.maximum(oracle.gemm_f64(A, B) + bias.astype(np.float64), 0)
+    out = torch.empty((1024, 1024), device="cuda")
+    engine.gemm_relu(dev(A), dev(B), dev(bias), out)
+    got = host(out)
+    assert nerr(got, ref64) <= TOL_SPLIT
+    assert nerr(got, ref) <= TOL_SPLIT
+    np.testing.assert_allclose(got, ref, atol=1e-3, rtol=1e-4)
+
+
+def test_gemm_is_bitwise_deterministic(engine, oracle):
+    # tests/test_optimization_paths.c:265-295 of the reference: 10 runs, identical bits
+    A, B = oracle.uniform((200, 300), 3), oracle.uniform((300, 170), 4)
+    first = run_gemm(engine, A, B)
+    for _ in range(9):
+        np.testing.assert_array_equal(run_gemm(engine, A, B), first)
+
+
+def test_gemm_edge_values(engine):
+    # tests/test_numerical_edge.c:310-372: zeros, large values, K = 1
+    z = np.zeros((7, 9), np.float32)
+    np.testing.assert_array_equal(run_gemm(engine, z, np.zeros((9, 5), np.float32)), np.zeros((7, 5), np.float32))
+    big = np.full((40, 64), 1e18, np.float32)
+    got = run_gemm(engine, big, np.full((64, 40), 1e18, np.float32))
+    np.testing.assert_allclose(got, np.full((40, 40), 64e36, np.float32), rtol=1e-5)
+    a = np.arange(1, 41, dtype=np.float32).reshape(40, 1)
+    b = np.arange(1, 51, dtype=np.float32).reshape(1, 50)
+    np.testing.assert_allclose(run_gemm(engine, a, b), a @ b, rtol=1e-6)
+
+
+def test_empty_shapes(engine):
+    out = torch.zeros((0, 5), device="cuda")
+    engine.gemm(torch.zeros((0, 3), device="cuda"), torch.zeros((3, 5), device="cuda"), out)
+    out = torch.full((4, 5), 7.0, device="cuda")
+    engine.gemm(torch.zeros((4, 0), device="cuda"), torch.zeros((0, 5), device="cuda"), out)
+    np.testing.assert_array_equal(host(out), np.zeros((4, 5), np.float32))
+
+
+def test_null_and_bad_arguments(engine):
+    from axiom_b200.engine import EngineError
+    a = torch.zeros((4, 4), device="cuda")
+    with pytest.raises(EngineError) as e:
+        engine.gemm(a, a, None)
+    assert e.value.status == 1                      # AX_ERR_NULL_ARG
+    with pytest.raises(EngineError) as e:
+        engine.bias_add(a, a[0], 2, a)
+    assert e.value.status == 5                      # AX_ERR_INVALID_AXIS
+
+
+@pytest.mark.parametrize("M", [1, 2, 5, 8, 32])
+@pytest.mark.parametrize("NK", [(4096, 4096), (1000, 777), (130, 257)])
+def test_skinny_route(engine, oracle, M, NK):
+    """BASELINE config 2 (x[M,4096].W[4096,4096] + bias -> GELU, M in {1,8,32}) and ragged shapes."""
+    N, K = NK
+    x = oracle.normal((M, K), 31)
+    W = oracle.normal((K, N), 13, sigma=1.0 / np.sqrt(K))
+    bias = oracle.uniform((N,), 29)
+    pre64 = oracle.gemm_f64(x, W) + bias.astype(np.float64)
+    ref = oracle.bias_act(oracle.gemm(x, W), bias, "gelu")
+    out = torch.empty((M, N), device="cuda")
+    xd, Wd, bd = dev(x), dev(W), dev(bias)
+    engine.gemm_bias_act(xd, Wd, bd, out, M, N, K, act="gelu")
+    got = host(out)
+    assert nerr(got, ref) <= TOL_SPLIT
+    ref64 = 0.5 * pre64 * (1 + np.tanh(0.7978845608028654 * (pre64 + 0.044715 * pre64 ** 3)))
+    assert nerr(got, ref64) <= TOL_SPLIT
+    # bitwise run-to-run determinism of the split-K reduction
+    out2 = torch.empty((M, N), device="cuda")
+    for _ in range(3):
+        engine.gemm_bias_act(xd, Wd, bd, out2, M, N, K, act="gelu")
+        np.testing.assert_array_equal(host(out2), got)
+    # plain gemm / alpha-beta forms of the same route
+    c = dev(oracle.uniform((M, N), 5))
+    cin = host(c).copy()
+    engine.gemm_ex(xd, Wd, 0.5, 2.0, c)
+    assert nerr(host(c), 0.5 * oracle.gemm_f64(x, W) + 2.0 * cin) <= TOL_SPLIT
+
+
+def test_elementwise_slots(engine, oracle, golden):
+    X, bias_n, bias_m = oracle.uniform((37, 52), 3), oracle.uniform((52,), 4), oracle.uniform((37,), 6)
+    out = torch.empty((37, 52), device="cuda")
+    np.testing.assert_array_equal(host(engine.bias_add(dev(X), dev(bias_n), 1, out)), oracle.bias_add_axis(X, bias_n, 1))
+    np.testing.assert_array_equal(host(engine.bias_add(dev(X), dev(bias_m), 0, out)), oracle.bias_add_axis(X, bias_m, 0))
+    xd = dev(X)
+    engine.bias_add(xd, dev(bias_n), 1, xd)          # out may alias in
+    np.testing.assert_array_equal(host(xd), oracle.bias_add_axis(X, bias_n, 1))
+    np.testing.assert_array_equal(host(engine.relu(dev(X), out)), oracle.relu(X))
+    gx = golden["gelu_x"]
+    g = torch.empty(gx.shape, device="cuda")
+    np.testing.assert_allclose(host(engine.gelu(dev(gx), g)), golden["gelu_y"], atol=2e-6)
+    np.testing.assert_allclose(host(g), oracle.gelu(gx), atol=1e-6)
+
+
+def test_w8a8_known_answers_bit_exact(engine, golden):
+    for i in range(3):
+        a, b, bs = golden[f"w8a8_{i}_a"], golden[f"w8a8_{i}_b"], golden[f"w8a8_{i}_bs"]
+        a_scale, out_scale = (float(v) for v in golden[f"w8a8_{i}_scales"])
+        M, N = a.shape[0], b.shape[0]
+        q = torch.zeros((M, N), dtype=torch.int8, device="cuda")
+        acc = torch.zeros((M, N), dtype=torch.int32, device="cuda")
+        engine.qgemm_w8a8(dev(a), a_scale, dev(b), dev(bs), out_scale, q, acc)
+        np.testing.assert_array_equal(host(acc), golden[f"w8a8_{i}_acc"])
+        np.testing.assert_array_equal(host(q), golden[f"w8a8_{i}_q"])
+
+
+@pytest.mark.parametrize("shape", [(512, 4096, 4096), (130, 200, 1000), (128, 256, 128), (1, 64, 48), (300, 33, 4112)])
+def test_w8a8_bit_exact_vs_oracle(engine, oracle, shape):
+    """BASELINE config 3 first: A int8 [512,4096], B int8 [4096,4096], scales U[0.001,0.02]."""
+    M, N, K = shape
+    a, b = oracle.int8((M, K), 7), oracle.int8((N, K), 13)
+    bs = oracle.frange((N,), 17, 0.001, 0.02)
+    a_scale = 0.02
+    # acc has std ~ 5373*sqrt(K) (two U{-127..127} factors): scale so outputs span the int8 range, few saturate
+    out_scale = float(a_scale * 0.0105 * 5373.0 * np.sqrt(K) / 50.0)
+    acc_ref, q_ref = oracle.qgemm_w8a8(a, a_scale, b, bs, out_scale)
+    q = torch.zeros((M, N), dtype=torch.int8, device="cuda")
+    acc = torch.zeros((M, N), dtype=torch.int32, device="cuda")
+    engine.qgemm_w8a8(dev(a), a_scale, dev(b), dev(bs), out_scale, q, acc)
+    np.testing.assert_array_equal(host(acc), acc_ref)
+    np.testing.assert_array_equal(host(q), q_ref)
+    assert 0.001 < np.mean(np.abs(q_ref.astype(np.int32)) == 127) < 0.2 or M * N < 1000
+    # each output alone
+    q2 = torch.zeros_like(q)
+    engine.qgemm_w8a8(dev(a), a_scale, dev(b), dev(bs), out_scale, q2, None)
+    np.testing.assert_array_equal(host(q2), q_ref)
+    acc2 = torch.zeros_like(acc)
+    engine.qgemm_w8a8(dev(a), a_scale, dev(b), None, 1.0, None, acc2)
+    np.testing.assert_array_equal(host(acc2), acc_ref)
+
+
+@pytest.mark.parametrize("shape", [(8, 8), (128, 128), (64, 1024), (33, 1001)])
+def test_quantize_rows_bit_exact(engine, oracle, shape):
+    N, K = shape
+    W = oracle.uniform((N, K), 42)
+    W[N // 2] = 0.0                                   # an all-zero row takes scale 1
+    q_ref, s_ref = oracle.quantize_rows(W)
+    q = torch.zeros((N, K), dtype=torch.int8, device="cuda")
+    s = torch.zeros((N,), device="cuda")
+    engine.quantize_rows(dev(W), q, s)
+    np.testing.assert_array_equal(host(s), s_ref)
+    np.testing.assert_array_equal(host(q), q_ref)
+
+
+@pytest.mark.parametrize("shape", [(1, 8, 8), (4, 16, 32), (8, 64, 128), (32, 128, 512), (16, 256, 1024), (512, 1024, 1024)])
+def test_w8a32_vs_oracle_and_golden(engine, oracle, golden, shape):
+    M, N, K = shape
+    a, w = oracle.uniform((M, K), 7), oracle.uniform((N, K), 13)
+    q, s = oracle.quantize_rows(w)
+    out = torch.empty((M, N), device="cuda")
+    engine.qgemm_w8a32(dev(a), dev(q), dev(s), out)
+    got = host(out)
+    assert nerr(got, oracle.qgemm_w8a32_f64(a, q, s)) <= TOL_SPLIT
+    tag = f"q_{M}_{N}_{K}_out"
+    ref = golden[tag] if tag in golden.files else oracle.qgemm_w8a32(a, q, s)
+    diff = np.abs(got - ref)
+    rel = diff / (np.abs(ref) + 1e-5)
+    assert not np.any((diff > 1e-2) & (rel > 1e-3))   # tests/test_quantize.c:109-113
+
+
+@pytest.mark.parametrize("name", ["s_test", "s_c4like"])
+@pytest.mark.parametrize("causal", [0, 1])
+def test_sdpa_vs_golden(engine, oracle, golden, name, causal):
+    BH, S, dk = (int(v) for v in golden[name + "_shape"])
+    scale = float(golden[name + "_scale"][0])
+    Q, K, V = oracle.normal((BH, S, dk), 41), oracle.normal((BH, S, dk), 43), oracle.normal((BH, S, dk), 47)
+    O = torch.full((BH, S, dk), float("nan"), device="cuda")
+    L = torch.full((BH, S), float("nan"), device="cuda")
+    engine.sdpa_fwd(dev(Q), dev(K), dev(V), O, L, scale, causal)
+    assert np.abs(host(O) - golden[f"{name}_c{causal}_O"]).max() < 1e-4   # tests/test_attention.c:54-131
+    assert np.abs(host(L) - golden[f"{name}_c{causal}_L"]).max() < 1e-4
+    O2 = torch.empty_like(O)
+    engine.sdpa_fwd(dev(Q), dev(K), dev(V), O2, None, scale, causal)       # L is optional
+    np.testing.assert_array_equal(host(O2), host(O))
+
+
+@pytest.mark.parametrize("shape", [(4, 1024, 64), (2, 333, 64), (3, 200, 128), (2, 129, 40), (5, 64, 16)])
+@pytest.mark.parametrize("causal", [0, 1])
+def test_sdpa_vs_oracle(engine, oracle, shape, causal):
+    """BASELINE config 4 per-head shape (S=1024, dk=64, scale 1/8, causal) on a few heads, plus ragged ones."""
+    BH, S, dk = shape
+    Q, K, V = oracle.normal((BH, S, dk), 41), oracle.normal((BH, S, dk), 43), oracle.normal((BH, S, dk), 47)
+    scale = 1.0 / np.sqrt(dk)
+    O64, L64 = oracle.sdpa_fwd_f64(Q, K, V, scale, causal)
+    O = torch.empty((BH, S, dk), device="cuda")
+    L = torch.empty((BH, S), device="cuda")
+    engine.sdpa_fwd(dev(Q), dev(K), dev(V), O, L, scale, causal)
+    assert np.abs(host(O) - O64).max() < 1e-5
+    assert np.abs(host(L) - L64).max() < 1e-5
