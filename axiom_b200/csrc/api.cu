@@ -27,6 +27,8 @@ struct Engine {
     int sm_count = 148;
     cudaStream_t stream = 0;
     int fp32_mode = AXB_FP32_3XTF32;
+    // K elements accumulated inside the tensor core per chunk in the split-precision modes
+    int chunk_tf32 = 256, chunk_bf16 = 512;
     // grow-only scratch for operand planes (backend-owned, like the reference's
     // device scratch arena, src/compute/backends/cuda/internal.h:57-90)
     void *ws = nullptr;
@@ -40,8 +42,9 @@ struct Engine {
     int64_t launches = 0;
     // optional timing of the last GEMM-family call: events around its pre-pass and its core kernel
     bool profiling = false;
-    cudaEvent_t ev[3] = { nullptr, nullptr, nullptr };
-    bool ev_valid = false;
+    static constexpr int EV_RING = 256;
+    cudaEvent_t ev[EV_RING][3] = {};
+    int ev_count = 0;   // calls recorded since the last summary (ring keeps the newest EV_RING)
     char msg[320] = "";
 };
 
@@ -66,10 +69,11 @@ inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 inline void mark(int i)
 {
-    if (g.profiling && g.ev[i]) {
-        cudaEventRecord(g.ev[i], g.stream);
-        if (i == 2) g.ev_valid = true;
-    }
+    if (!g.profiling) return;
+    cudaEvent_t *slot = g.ev[g.ev_count % Engine::EV_RING];
+    if (!slot[i]) cudaEventCreate(&slot[i]);
+    cudaEventRecord(slot[i], g.stream);
+    if (i == 2) g.ev_count++;
 }
 
 int ensure_ready()
@@ -150,15 +154,18 @@ int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int
     case AXB_FP32_BF16:
         split_mode = SPLIT_BF16X1; kind = KIND_BF16;
         prod.n = 1; prod.a[0] = 0; prod.b[0] = 0;
+        prod.chunk_k = 0;
         break;
     case AXB_FP32_BF16X3:
         split_mode = SPLIT_BF16X2; kind = KIND_BF16;
         prod.n = 3; prod.a[0] = 1; prod.b[0] = 0; prod.a[1] = 0; prod.b[1] = 1; prod.a[2] = 0; prod.b[2] = 0;
+        prod.chunk_k = g.chunk_bf16;
         break;
     default:
         split_mode = SPLIT_TF32X2; kind = KIND_TF32;
         // small cross terms first, the hi.hi product last
         prod.n = 3; prod.a[0] = 1; prod.b[0] = 0; prod.a[1] = 0; prod.b[1] = 1; prod.a[2] = 0; prod.b[2] = 0;
+        prod.chunk_k = g.chunk_tf32;
         break;
     }
     const SplitOperand sa = plan_split(split_mode, M, K), sb = plan_split(split_mode, N, K);
@@ -249,6 +256,8 @@ extern "C" int axb_init(int device)
         else if (!strcmp(mode, "bf16x3")) g.fp32_mode = AXB_FP32_BF16X3;
         else if (!strcmp(mode, "3xtf32")) g.fp32_mode = AXB_FP32_3XTF32;
     }
+    if (const char *c = getenv("AX_B200_CHUNK_TF32")) g.chunk_tf32 = atoi(c);
+    if (const char *c = getenv("AX_B200_CHUNK_BF16")) g.chunk_bf16 = atoi(c);
     g.ready = true;
     if (getenv("AX_B200_VERBOSE"))
         fprintf(stderr, "axiom: b200 engine on device %d (%s, %d SMs), fp32 mode %d\n", device, prop.name,
@@ -264,6 +273,9 @@ extern "C" void axb_shutdown(void)
     if (g.sk_partial) cudaFree(g.sk_partial);
     if (g.sk_counters) cudaFree(g.sk_counters);
     if (g.err_word) cudaFree(g.err_word);
+    for (auto &slot : g.ev)
+        for (auto &e : slot)
+            if (e) cudaEventDestroy(e);
     g = Engine();
 }
 
@@ -352,22 +364,28 @@ extern "C" int axb_device_error(void)
 extern "C" void axb_set_profiling(int on)
 {
     g.profiling = on != 0;
-    g.ev_valid = false;
-    if (g.profiling)
-        for (int i = 0; i < 3; ++i)
-            if (!g.ev[i]) cudaEventCreate(&g.ev[i]);
+    g.ev_count = 0;
 }
 
-extern "C" int axb_last_timing(float *prepass_ms, float *core_ms)
+extern "C" int axb_timing_summary(int *calls, float *prepass_ms_total, float *core_ms_total)
 {
-    if (!g.profiling || !g.ev_valid) return fail(AXB_ERR_BACKEND, "last_timing: profiling is off or no call was timed");
-    cudaError_t e = cudaEventSynchronize(g.ev[2]);
-    if (e != cudaSuccess) return cuda_fail("last_timing", e);
-    float a = 0.f, b = 0.f;
-    cudaEventElapsedTime(&a, g.ev[0], g.ev[1]);
-    cudaEventElapsedTime(&b, g.ev[1], g.ev[2]);
-    if (prepass_ms) *prepass_ms = a;
-    if (core_ms) *core_ms = b;
+    if (!g.profiling) return fail(AXB_ERR_BACKEND, "timing_summary: profiling is off");
+    const int n = g.ev_count < Engine::EV_RING ? g.ev_count : Engine::EV_RING;
+    float pre = 0.f, core = 0.f;
+    for (int i = 0; i < n; ++i) {
+        cudaEvent_t *slot = g.ev[(g.ev_count - 1 - i) % Engine::EV_RING];
+        cudaError_t e = cudaEventSynchronize(slot[2]);
+        if (e != cudaSuccess) return cuda_fail("timing_summary", e);
+        float a = 0.f, b = 0.f;
+        cudaEventElapsedTime(&a, slot[0], slot[1]);
+        cudaEventElapsedTime(&b, slot[1], slot[2]);
+        pre += a;
+        core += b;
+    }
+    if (calls) *calls = n;
+    if (prepass_ms_total) *prepass_ms_total = pre;
+    if (core_ms_total) *core_ms_total = core;
+    g.ev_count = 0;
     return AXB_OK;
 }
 
@@ -384,13 +402,13 @@ extern "C" int axb_gemm_bias_act(const float *A, const float *B, const float *bi
                                  int64_t N, int64_t K, int trans_a, int trans_b, float alpha, float beta,
                                  int act)
 {
-    if (!A || !B || !C) return fail(AXB_ERR_NULL_ARG, "gemm: NULL operand");
     if (M < 0 || N < 0 || K < 0) return fail(AXB_ERR_INVALID_SHAPE, "gemm: negative dimension");
+    if (M == 0 || N == 0) return AXB_OK;  // nothing to write; empty operands may legitimately be NULL
+    if (!C || (K > 0 && (!A || !B))) return fail(AXB_ERR_NULL_ARG, "gemm: NULL operand");
     if (act < AXB_ACT_NONE || act > AXB_ACT_GELU) return fail(AXB_ERR_INVALID_SHAPE, "gemm: unknown activation %d", act);
     if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "gemm: dimension exceeds 2^31-1");
     int st = ensure_ready();
     if (st) return st;
-    if (M == 0 || N == 0) return AXB_OK;
     if (K == 0) {
         // empty contraction: C = act(beta*C + bias) via the skinny kernel's epilogue is not
         // reachable (no rows to stream); express it as the bias/activation passes
@@ -497,6 +515,7 @@ extern "C" int axb_qgemm_w8a32(const float *a, const int8_t *q, const float *sca
     memset(&prod, 0, sizeof prod);
     prod.n = opa.nplanes;
     for (int i = 0; i < prod.n; ++i) { prod.a[i] = (int8_t)(prod.n - 1 - i); prod.b[i] = 0; }  // smallest plane first
+    prod.chunk_k = prod.n > 1 ? g.chunk_bf16 : 0;
     TcEpilogue ep;
     ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = nullptr; ep.colscale = scales; ep.act = ACT_NONE;
     ep.out_mode = OUT_F32; ep.C = out; ep.acc_out = nullptr; ep.ldc = N;

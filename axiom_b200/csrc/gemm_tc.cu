@@ -12,10 +12,13 @@
 //   warp 1 (one lane)  issues tcgen05.mma (M = 128, N = BN) into one of two
 //                      TMEM accumulators; tcgen05.commit releases the stage
 //                      and, after the last k-block, publishes the accumulator
-//   warps 2..5         epilogue: tcgen05.ld the finished accumulator (each warp
-//                      owns its 32-lane quarter), apply alpha/beta/bias/
+//   warps 2..9         epilogue: tcgen05.ld the finished accumulator (a warp may
+//                      read the 32-lane quarter warp%4; two warps share a
+//                      quarter and split the columns), apply alpha/beta/bias/
 //                      activation or the int8 requantisation, store to global;
-//                      the second accumulator lets this overlap the next tile
+//                      the second accumulator lets this overlap the MMAs that
+//                      follow.  For the fp32 kinds K is cut into chunks that are
+//                      summed in registers (see the MMA issuer).
 //
 // Tiles are walked in a grouped raster (GROUP_M row-tiles per column sweep) so
 // the CTAs running at one time share operand panels in L2.  Edge tiles rely
@@ -31,7 +34,7 @@ namespace axb {
 
 static constexpr int BM = 128;
 static constexpr int GROUP_M = 16;
-static constexpr int NUM_THREADS = 192;
+static constexpr int NUM_THREADS = 320;  // producer warp, MMA warp, 8 epilogue warps
 static constexpr int HEADER_BYTES = 1024;
 static constexpr int MAX_STAGES = 8;
 static constexpr int SMEM_BUDGET = 227 * 1024;
@@ -46,6 +49,7 @@ struct KernelArgs {
     int npa, npb, nprod;
     int8_t pa[TC_MAX_PRODUCTS], pb[TC_MAX_PRODUCTS];
     int m_tiles, n_tiles, k_blocks, stages;
+    int chunk_kb;  // k-blocks accumulated in TMEM before the epilogue warps drain them
     float alpha, beta;
     const float *bias;
     const float *colscale;
@@ -115,7 +119,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(bar_tfull + 8 * a, 1);
-            mbar_init(bar_tempty + 8 * a, 4);
+            mbar_init(bar_tempty + 8 * a, 8);
         }
         mbar_fence_init();
         for (int i = 0; i < p.npa; ++i) tma_prefetch_desc(&tm.a[i]);
@@ -157,129 +161,190 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
         }
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
+        // K is cut into chunks of p.chunk_kb k-blocks; every chunk starts a
+        // fresh TMEM accumulator (ping-pong) that the epilogue warps drain and
+        // add up in registers.  The tensor core truncates when it accumulates,
+        // an error that grows with the number of steps; bounding the steps per
+        // chunk and summing the chunks with rounded fp32 adds keeps the result
+        // inside the fp32 tolerance for any K.  Integer and plain bf16 runs use
+        // a single chunk.
         if (lane == 0) {
-            uint32_t it = 0, lt = 0;
+            uint32_t it = 0, vt = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++lt) {
-                const uint32_t acc = lt & 1u, aph = (lt >> 1) & 1u;
-                if (!mbar_wait_bounded(bar_tempty + 8 * acc, aph ^ 1u)) {
-                    report(p.err, ERR_MMA_WAIT_TMEM);
-                    break;
-                }
-                tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-                    const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
-                    if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
-                        report(p.err, ERR_MMA_WAIT_FULL);
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += p.chunk_kb, ++vt) {
+                    const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
+                    if (!mbar_wait_bounded(bar_tempty + 8 * acc, aph ^ 1u)) {
+                        report(p.err, ERR_MMA_WAIT_TMEM);
                         ok = false;
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t sa = stage0 + s * stage_bytes;
-                    const uint32_t sb = sa + p.npa * A_BYTES;
-                    for (int pr = 0; pr < p.nprod; ++pr) {
-                        const uint64_t da = smem_desc_kmajor(sa + p.pa[pr] * A_BYTES, SWB);
-                        const uint64_t db = smem_desc_kmajor(sb + p.pb[pr] * B_BYTES, SWB);
+                    const uint32_t d_tmem = tmem_base + acc * BN;
+                    const int kb1 = min(p.k_blocks, kb0 + p.chunk_kb);
+                    for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                        const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                        if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
+                            report(p.err, ERR_MMA_WAIT_FULL);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        const uint32_t sa = stage0 + s * stage_bytes;
+                        const uint32_t sb = sa + p.npa * A_BYTES;
+                        for (int pr = 0; pr < p.nprod; ++pr) {
+                            const uint64_t da = smem_desc_kmajor(sa + p.pa[pr] * A_BYTES, SWB);
+                            const uint64_t db = smem_desc_kmajor(sb + p.pb[pr] * B_BYTES, SWB);
 #pragma unroll
-                        for (int ks = 0; ks < KSTEPS; ++ks)
-                            tc_mma<KIND>(d_tmem, da + 2u * ks, db + 2u * ks, IDESC,
-                                         (uint32_t)((kb | pr | ks) != 0));
+                            for (int ks = 0; ks < KSTEPS; ++ks)
+                                tc_mma<KIND>(d_tmem, da + 2u * ks, db + 2u * ks, IDESC,
+                                             (uint32_t)(((kb - kb0) | pr | ks) != 0));
+                        }
+                        tc_commit(bar_empty + 8 * s);
                     }
-                    tc_commit(bar_empty + 8 * s);
+                    if (ok) tc_commit(bar_tfull + 8 * acc);
                 }
-                if (ok) tc_commit(bar_tfull + 8 * acc);
             }
         }
     } else {
         // ---------------------------------------------------------- epilogue
-        const int q = warp & 3;  // TMEM lane quarter this warp may read
-        uint32_t lt = 0;
-        for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++lt) {
+        // 8 warps: warp % 4 picks the TMEM lane quarter (a hardware rule), the
+        // two warps of a quarter split the tile's columns in halves.
+        constexpr int HALF = BN / 2;
+        constexpr int PIECES = HALF / 32;
+        const int q = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int nchunks = (p.k_blocks + p.chunk_kb - 1) / p.chunk_kb;
+        uint32_t vt = 0;
+        bool alive = true;
+        for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
             int mt, nt;
             tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
-            const uint32_t acc = lt & 1u, aph = (lt >> 1) & 1u;
-            const bool got = mbar_wait_bounded(bar_tfull + 8 * acc, aph);
-            if (!__all_sync(0xffffffffu, got)) {
-                report(p.err, ERR_EPI_WAIT);
-                break;
-            }
-            tc_fence_after_sync();
             const long long row = (long long)mt * BM + q * 32 + lane;
             const bool row_ok = row < p.M;
-            const int col_base = nt * BN;
+            const int col_base = nt * BN + half * HALF;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + half * HALF;
+
+            if constexpr (KIND == KIND_I8) {
+                // one chunk, exact integers: stream 32 columns at a time
+                const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
+                ++vt;
+                const bool got = mbar_wait_bounded(bar_tfull + 8 * acc, aph);
+                if (!__all_sync(0xffffffffu, got)) {
+                    report(p.err, ERR_EPI_WAIT);
+                    alive = false;
+                    break;
+                }
+                tc_fence_after_sync();
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                const int col0 = col_base + c * 32;
-                if (col0 >= p.N) break;  // warp-uniform
-                uint32_t r[32];
-                __syncwarp();  // the TMEM load is warp-collective: reconverge after masked stores
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN + c * 32, r);
-                tmem_ld_wait();
-                const bool full = col0 + 32 <= p.N;
-                if (!row_ok) {
-                    // rows past M: nothing to store
-                } else if constexpr (KIND == KIND_I8) {
-                    if (p.acc_out) {
-                        int32_t *dst = p.acc_out + row * p.ldc + col0;
-                        if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+                for (int c = 0; c < PIECES; ++c) {
+                    const int col0 = col_base + c * 32;
+                    if (col0 >= p.N) break;  // warp-uniform
+                    uint32_t r[32];
+                    __syncwarp();  // the TMEM load is warp-collective: reconverge after masked stores
+                    tmem_ld_32x32(lane_addr + acc * BN + c * 32, r);
+                    tmem_ld_wait();
+                    const bool full = col0 + 32 <= p.N;
+                    if (row_ok) {
+                        if (p.acc_out) {
+                            int32_t *dst = p.acc_out + row * p.ldc + col0;
+                            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<int4 *>(dst + j) =
-                                    make_int4((int)r[j], (int)r[j + 1], (int)r[j + 2], (int)r[j + 3]);
-                        } else {
-                            for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = (int32_t)r[j];
+                                for (int j = 0; j < 32; j += 4)
+                                    *reinterpret_cast<int4 *>(dst + j) =
+                                        make_int4((int)r[j], (int)r[j + 1], (int)r[j + 2], (int)r[j + 3]);
+                            } else {
+                                for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = (int32_t)r[j];
+                            }
+                        }
+                        if (p.out_mode == OUT_I8_REQUANT) {
+                            int8_t *dst = reinterpret_cast<int8_t *>(p.C) + row * p.ldc + col0;
+                            uint32_t packed[8];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const float mult = (col0 + j < p.N) ? __ldg(p.colscale + col0 + j) : 0.0f;
+                                const float y = __fmul_rn(__int2float_rn((int32_t)r[j]), mult);
+                                int v = __float2int_rn(y);
+                                v = max(-127, min(127, v));
+                                if ((j & 3) == 0) packed[j >> 2] = 0;
+                                packed[j >> 2] |= (uint32_t)(v & 0xff) << (8 * (j & 3));
+                            }
+                            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+                                *reinterpret_cast<uint4 *>(dst) =
+                                    make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                                *reinterpret_cast<uint4 *>(dst + 16) =
+                                    make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                            } else {
+                                for (int j = 0; j < 32 && col0 + j < p.N; ++j)
+                                    dst[j] = (int8_t)((packed[j >> 2] >> (8 * (j & 3))) & 0xff);
+                            }
                         }
                     }
-                    if (p.out_mode == OUT_I8_REQUANT) {
-                        int8_t *dst = reinterpret_cast<int8_t *>(p.C) + row * p.ldc + col0;
-                        uint32_t packed[8];
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+            } else {
+                // fp32 kinds: add the chunks up in registers, then the fused epilogue
+                float sum[HALF];
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) {
-                            const float mult = (col0 + j < p.N) ? __ldg(p.colscale + col0 + j) : 0.0f;
-                            const float y = __fmul_rn(__int2float_rn((int32_t)r[j]), mult);
-                            int v = __float2int_rn(y);
-                            v = max(-127, min(127, v));
-                            if ((j & 3) == 0) packed[j >> 2] = 0;
-                            packed[j >> 2] |= (uint32_t)(v & 0xff) << (8 * (j & 3));
-                        }
-                        if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-                            *reinterpret_cast<uint4 *>(dst) =
-                                make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                            *reinterpret_cast<uint4 *>(dst + 16) =
-                                make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                        } else {
-                            for (int j = 0; j < 32 && col0 + j < p.N; ++j)
-                                dst[j] = (int8_t)((packed[j >> 2] >> (8 * (j & 3))) & 0xff);
-                        }
+                for (int j = 0; j < HALF; ++j) sum[j] = 0.0f;
+                for (int ch = 0; ch < nchunks; ++ch, ++vt) {
+                    const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
+                    const bool got = mbar_wait_bounded(bar_tfull + 8 * acc, aph);
+                    if (!__all_sync(0xffffffffu, got)) {
+                        report(p.err, ERR_EPI_WAIT);
+                        alive = false;
+                        break;
                     }
-                } else {
-                    float *dst = reinterpret_cast<float *>(p.C) + row * p.ldc + col0;
-                    const bool vec = full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
-                    float v[32];
+                    tc_fence_after_sync();
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const bool in = full || (col0 + j < p.N);
-                        float x = __uint_as_float(r[j]) * p.alpha;
-                        if (p.colscale) x *= in ? __ldg(p.colscale + col0 + j) : 0.0f;
-                        if (p.beta != 0.0f) x += p.beta * (in ? dst[j] : 0.0f);
-                        if (p.bias) x += in ? __ldg(p.bias + col0 + j) : 0.0f;
-                        if (p.act == ACT_RELU) x = fmaxf(x, 0.0f);
-                        else if (p.act == ACT_GELU) x = gelu_tanh(x);
-                        v[j] = x;
+                    for (int c = 0; c < PIECES; ++c) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(lane_addr + acc * BN + c * 32, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) sum[c * 32 + j] += __uint_as_float(r[j]);
                     }
-                    if (vec) {
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+                }
+                if (!alive) break;
+                if (row_ok) {
 #pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                            *reinterpret_cast<float4 *>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                    } else {
-                        for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = v[j];
+                    for (int c = 0; c < PIECES; ++c) {
+                        const int col0 = col_base + c * 32;
+                        if (col0 < p.N) {
+                            const bool full = col0 + 32 <= p.N;
+                            float *dst = reinterpret_cast<float *>(p.C) + row * p.ldc + col0;
+                            const bool vec = full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+                            float v[32];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const bool in = full || (col0 + j < p.N);
+                                float x = sum[c * 32 + j] * p.alpha;
+                                if (p.colscale) x *= in ? __ldg(p.colscale + col0 + j) : 0.0f;
+                                if (p.beta != 0.0f) x += p.beta * (in ? dst[j] : 0.0f);
+                                if (p.bias) x += in ? __ldg(p.bias + col0 + j) : 0.0f;
+                                if (p.act == ACT_RELU) x = fmaxf(x, 0.0f);
+                                else if (p.act == ACT_GELU) x = gelu_tanh(x);
+                                v[j] = x;
+                            }
+                            if (vec) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 4)
+                                    *reinterpret_cast<float4 *>(dst + j) =
+                                        make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j)
+                                    if (col0 + j < p.N) dst[j] = v[j];
+                            }
+                        }
                     }
                 }
             }
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
         }
     }
 
@@ -433,6 +498,12 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
     for (int i = 0; i < prod.n; ++i) { ka.pa[i] = prod.a[i]; ka.pb[i] = prod.b[i]; }
     ka.m_tiles = (int)mt; ka.n_tiles = (int)nt;
     ka.k_blocks = (int)((K + bke - 1) / bke);
+    ka.chunk_kb = ka.k_blocks;
+    if (kind != KIND_I8 && prod.chunk_k > 0) {
+        ka.chunk_kb = prod.chunk_k / bke;
+        if (ka.chunk_kb < 1) ka.chunk_kb = 1;
+        if (ka.chunk_kb > ka.k_blocks) ka.chunk_kb = ka.k_blocks;
+    }
     ka.alpha = ep.alpha; ka.beta = ep.beta; ka.bias = ep.bias; ka.colscale = ep.colscale;
     ka.act = ep.act; ka.out_mode = ep.out_mode; ka.C = ep.C; ka.acc_out = ep.acc_out;
     ka.ldc = ep.ldc; ka.err = err_word;

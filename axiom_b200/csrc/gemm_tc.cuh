@@ -33,6 +33,10 @@ struct TcEpilogue {
 struct TcProducts {
     int n;
     int8_t a[TC_MAX_PRODUCTS], b[TC_MAX_PRODUCTS];  // plane index pairs, issued in order
+    // fp32 kinds: K elements accumulated inside the tensor core before the partial
+    // sum is moved to registers (0 = the whole K in one go).  The tensor core
+    // truncates on accumulation, so the error of one chunk grows with its length.
+    int chunk_k;
 };
 
 // kind: MmaKind (0 tf32, 1 bf16, 2 int8).  Returns cudaError_t as int; a device

@@ -222,11 +222,19 @@ int launch_sdpa_fwd(const float *Q, const float *K, const float *V, float *O, fl
     dim3 grid((unsigned)((S + BQ - 1) / BQ), (unsigned)BH);
     if (dk <= 64) {
         const size_t smem = (size_t)(BQ * 64 + 64 * BKV + BKV * 64 + BQ * PS_PITCH) * 4;
-        cudaFuncSetAttribute(sdpa_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        static bool attr64 = false;
+        if (!attr64) {
+            cudaFuncSetAttribute(sdpa_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            attr64 = true;
+        }
         sdpa_fwd_kernel<64><<<grid, SD_THREADS, smem, st>>>(Q, K, V, O, L, (int)S, (int)dk, scale, causal);
     } else {
         const size_t smem = (size_t)(BQ * 128 + 128 * BKV + BKV * 128 + BQ * PS_PITCH) * 4;
-        cudaFuncSetAttribute(sdpa_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        static bool attr128 = false;
+        if (!attr128) {
+            cudaFuncSetAttribute(sdpa_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            attr128 = true;
+        }
         sdpa_fwd_kernel<128><<<grid, SD_THREADS, smem, st>>>(Q, K, V, O, L, (int)S, (int)dk, scale, causal);
     }
     return (int)cudaGetLastError();

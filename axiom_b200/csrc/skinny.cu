@@ -152,9 +152,11 @@ static int launch_mt(const SkinnyArgs &a, bool vec, dim3 grid, size_t smem, cuda
 {
     auto kv = skinny_kernel<MT, true>;
     auto ks = skinny_kernel<MT, false>;
-    if (smem > 48 * 1024) {
-        cudaFuncSetAttribute(kv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        cudaFuncSetAttribute(ks, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static bool attr_set = false;  // the X slice is capped at 64 KB by skinny_plan
+    if (!attr_set) {
+        cudaFuncSetAttribute(kv, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+        cudaFuncSetAttribute(ks, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
+        attr_set = true;
     }
     if (vec) kv<<<grid, SK_THREADS, smem, st>>>(a);
     else ks<<<grid, SK_THREADS, smem, st>>>(a);

@@ -21,7 +21,7 @@ EXPORTS = [
     "axb_init", "axb_shutdown", "axb_device_count", "axb_synchronize", "axb_storage_alloc",
     "axb_storage_free", "axb_memcpy_h2d", "axb_memcpy_d2h", "axb_memcpy_d2d", "axb_set_stream",
     "axb_set_fp32_mode", "axb_get_fp32_mode", "axb_last_error", "axb_device_error", "axb_launch_count",
-    "axb_set_profiling", "axb_last_timing",
+    "axb_set_profiling", "axb_timing_summary",
     "axb_gemm", "axb_gemm_nt", "axb_gemm_tn", "axb_gemm_ex", "axb_gemm_relu", "axb_gemm_bias_act",
     "axb_bias_add", "axb_relu", "axb_gelu", "axb_qgemm_w8a32", "axb_qgemm_w8a8", "axb_quantize_rows",
     "axb_sdpa_fwd",
@@ -86,11 +86,11 @@ class Engine:
     def set_profiling(self, on=True):
         self.lib.axb_set_profiling(int(bool(on)))
 
-    def last_timing(self):
-        """(prepass_ms, core_ms) of the last timed call; blocks until it has finished."""
-        a, b = C.c_float(0), C.c_float(0)
-        self._check(self.lib.axb_last_timing(C.byref(a), C.byref(b)))
-        return a.value, b.value
+    def timing_summary(self):
+        """(calls, prepass_ms_total, core_ms_total) since profiling was switched on or last summarised."""
+        n, a, b = C.c_int(0), C.c_float(0), C.c_float(0)
+        self._check(self.lib.axb_timing_summary(C.byref(n), C.byref(a), C.byref(b)))
+        return n.value, a.value, b.value
 
     def set_fp32_mode(self, mode):
         self._check(self.lib.axb_set_fp32_mode(FP32_MODES[mode] if isinstance(mode, str) else int(mode)))

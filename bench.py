@@ -1,0 +1,376 @@
+#!/usr/bin/env python
+"""Benchmark of the axiom matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Headline (one JSON line on stdout): fp32-accurate GEMM, M=N=K=8192 per GPU
+(rows sharded across GPUs, weights replicated, no data-path collective: weak
+scaling), in TFLOP/s through the C ABI (operand split pre-pass + tcgen05
+kernel, both inside the timed step).  `extra` carries the other metrics of
+the suite on the same box: int8 TOPS at 16384^3, the bs=1 / 8 / 32 skinny-M
+route in GB/s of weight traffic, the 1024^3 dense+ReLU, the 512x4096x4096
+quantised GEMM and causal attention, each with its own roofline fraction.
+
+`--impl reference` times the reference's own CPU path (the compiled axiom
+library under oracle/_ref, OpenMP over the box's host cores) on a bounded
+sample of the same workload and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "tests")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+GEMM_N = 8192
+FLOP_HEADLINE = 2.0 * GEMM_N ** 3
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clock and throttle reasons while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- reference arm
+
+def cpu_reference_gemm(steps, warmup, autotune=True):
+    """axiom's own OpenMP/AVX2 GEMM (ax_compute_gemm) on a row slice of the 8192^3 problem."""
+    import numpy as np
+    from oracle_lib import Oracle, Reference
+    if not Reference.available():
+        return None
+    ref = Reference(autotune=autotune)   # tuning happens here, outside the timing
+    o = Oracle()
+    rows = 1024
+    A = o.uniform((rows, GEMM_N), 7)
+    B = o.uniform((GEMM_N, GEMM_N), 13)
+    for _ in range(max(1, warmup)):
+        ref.gemm(A, B)
+    times = []
+    for _ in range(max(1, steps)):
+        t0 = time.perf_counter()
+        ref.gemm(A, B)
+        times.append(time.perf_counter() - t0)
+    flop = 2.0 * rows * GEMM_N * GEMM_N
+    t = sum(times) / len(times)
+    return {"value": flop / t / 1e12, "unit": "TFLOP/s", "cores": ref.num_threads(), "kind": "reference",
+            "sample": f"ax_compute_gemm on a {rows}x{GEMM_N}x{GEMM_N} row slice of the 8192^3 problem "
+                      f"(includes the shim's operand copies), mean of {len(times)} runs, host has {os.cpu_count()} cpus",
+            "ms_per_step": t * 1e3}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = min(args.steps, 5)
+    cb = cpu_reference_gemm(steps, min(args.warmup, 2))
+    if cb is None:
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libaxiom_ref.so was not built"}))
+        return
+    line = {
+        "impl": "reference", "metric": "gemm_fp32_tflops", "value": cb["value"], "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": min(args.warmup, 2), "ms_per_step": cb["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "fp32 GEMM M=N=K=8192 per GPU (reference: 1024-row slice on host cores)"},
+        "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------- our arm
+
+def timed(torch, dist, world, fn, steps, warmup):
+    """W warm-ups, then exactly `steps` calls between barrier+synchronize pairs; max over ranks, ms."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.barrier()
+        ms = float(t.item())
+    return ms
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+    from axiom_b200.engine import get_engine
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    eng = get_engine(local)
+    peaks = measured_peaks()
+    K, W = args.steps, max(args.warmup, 3)
+    gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
+
+    def uniform(shape):
+        return torch.rand(shape, device="cuda", generator=gen) * 2 - 1
+
+    # ---------------- headline: fp32-accurate GEMM 8192^3 per GPU (3xTF32)
+    A, B = uniform((GEMM_N, GEMM_N)), uniform((GEMM_N, GEMM_N))
+    Cout = torch.empty((GEMM_N, GEMM_N), device="cuda")
+    step = lambda: eng.gemm(A, B, Cout)
+    for _ in range(W):
+        step()
+    eng.set_profiling(True)
+    try:
+        gpu_id = "GPU-" + str(torch.cuda.get_device_properties(local).uuid)
+    except Exception:
+        gpu_id = str(local)
+    sampler = ClockSampler(gpu_id)
+    if rank == 0:
+        sampler.start()
+    eng.launch_count(reset=True)
+    ms = timed(torch, dist, world, step, K, 0)
+    launches = eng.launch_count()
+    clocks = sampler.stop() if rank == 0 else None
+    calls, pre_ms, core_ms = eng.timing_summary()
+    eng.set_profiling(False)
+    ms_per_step = ms / K
+    value = world * FLOP_HEADLINE / (ms_per_step * 1e-3) / 1e12
+    core_avg_ms = core_ms / max(calls, 1)
+    tf32_split_peak = peaks["bf16_tflops"] / 2.0 / 3.0   # TF32 issues at half the bf16 rate; 3 products per result
+    achieved = FLOP_HEADLINE / (core_avg_ms * 1e-3) / 1e12
+    roofline = {"bound": "tensor", "achieved": achieved, "peak": tf32_split_peak, "unit": "TFLOP/s",
+                "frac": achieved / tf32_split_peak, "traffic": None,
+                "kernel": "gemm_tc_kernel<tf32,BN=256,SW64>", "kernel_ms": core_avg_ms, "prepass_ms": pre_ms / max(calls, 1),
+                "peak_source": f"{peaks['source']} bf16 burst {peaks['bf16_tflops']} TFLOP/s / 2 (tf32 rate) / 3 (products)"}
+
+    # ---------------- end to end: pinned host operands in, result out, every step
+    e2e = None
+    hA = torch.empty((GEMM_N, GEMM_N), pin_memory=True).copy_(A.cpu())
+    hB = torch.empty((GEMM_N, GEMM_N), pin_memory=True).copy_(B.cpu())
+    hC = torch.empty((GEMM_N, GEMM_N), pin_memory=True)
+    nbytes = GEMM_N * GEMM_N * 4
+
+    def e2e_step():
+        eng.memcpy_h2d(A, hA.data_ptr(), nbytes)
+        eng.memcpy_h2d(B, hB.data_ptr(), nbytes)
+        eng.gemm(A, B, Cout)
+        eng.memcpy_d2h(hC.data_ptr(), Cout, nbytes)
+
+    e2e_steps = max(1, min(K, 8))
+    ms_e2e = timed(torch, dist, world, e2e_step, e2e_steps, 1)
+    e2e = {"value": world * FLOP_HEADLINE / (ms_e2e / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+           "h2d_bytes_per_step": 2 * nbytes, "d2h_bytes_per_step": nbytes, "ms_per_step": ms_e2e / e2e_steps,
+           "steps": e2e_steps}
+    del hA, hB, hC
+
+    extra = []
+    if not args.headline_only:
+        extra = extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K)
+
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cb = cpu_reference_gemm(3, 1)
+        if cb:
+            cpu_baseline = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+
+    err = eng.device_error()
+    if rank == 0:
+        line = {
+            "metric": "gemm_fp32_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "fp32-accurate GEMM C=A.B, M=N=K=8192 per GPU, U[-1,1], rows sharded across GPUs "
+                                   "(weights replicated, no collective)", "fp32_mode": "3xtf32",
+                       "l2": "inputs (512 MiB fp32 + 1 GiB operand planes) larger than L2", "parallelism": f"m-shard x{world}"},
+            "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches,
+            "clocks": clocks, "device_error": err, "extra": extra,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
+    """The other metrics of the suite; each entry: workload, value, unit, ms, roofline fraction."""
+    out = []
+    hbm = peaks["hbm_gbs"]
+    bf16 = peaks["bf16_tflops"]
+
+    def core_time(fn, steps, warmup=3):
+        for _ in range(warmup):
+            fn()
+        eng.set_profiling(True)
+        ms = timed(torch, dist, world, fn, steps, 0)
+        calls, pre, core = eng.timing_summary()
+        eng.set_profiling(False)
+        return ms / steps, core / max(calls, 1), pre / max(calls, 1)
+
+    # fp32 GEMM 8192^3 in the two faster modes
+    for mode, peak, note in (("bf16x3", bf16 / 3.0, "bf16 burst / 3 products"), ("bf16", bf16, "bf16 burst")):
+        eng.set_fp32_mode(mode)
+        step_ms, core_ms, pre_ms = core_time(lambda: eng.gemm(A, B, Cout), max(3, K // 2))
+        eng.set_fp32_mode("3xtf32")
+        tf = FLOP_HEADLINE / (core_ms * 1e-3) / 1e12
+        out.append({"workload": f"fp32 GEMM 8192^3, mode {mode}", "value": world * FLOP_HEADLINE / (step_ms * 1e-3) / 1e12,
+                    "unit": "TFLOP/s", "ms_per_step": step_ms, "kernel_ms": core_ms, "prepass_ms": pre_ms,
+                    "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "frac": tf / peak, "peak_source": note}})
+
+    # int8 GEMM 16384^3 -> requantised int8 (BASELINE config 5b)
+    n8 = 16384
+    a8 = torch.randint(-127, 128, (n8, n8), device="cuda", dtype=torch.int8)
+    b8 = torch.randint(-127, 128, (n8, n8), device="cuda", dtype=torch.int8)
+    bs = torch.rand((n8,), device="cuda") * 0.019 + 0.001
+    q8 = torch.empty((n8, n8), device="cuda", dtype=torch.int8)
+    ops = 2.0 * n8 ** 3
+    step_ms, core_ms, pre_ms = core_time(lambda: eng.qgemm_w8a8(a8, 0.02, b8, bs, 40.0, q8, None), max(3, K // 2), 2)
+    tops = ops / (core_ms * 1e-3) / 1e12
+    out.append({"workload": "int8 GEMM 16384^3, s32 accumulate, requantised int8 out", "value": world * ops / (step_ms * 1e-3) / 1e12,
+                "unit": "TOPS", "ms_per_step": step_ms, "kernel_ms": core_ms,
+                "roofline": {"bound": "tensor", "achieved": tops, "peak": 2 * bf16, "frac": tops / (2 * bf16),
+                             "peak_source": "2 x measured bf16 burst (int8 issues at twice the bf16 rate)"}})
+    del a8, b8, q8
+
+    # skinny-M route: x[M,4096].W[4096,4096] + bias -> GELU (BASELINE config 2); 8 rotating weight
+    # buffers (512 MiB > L2) so every step streams W from HBM
+    n = 4096
+    Ws = [torch.randn((n, n), device="cuda") / 64 for _ in range(8)]
+    bias = uniform((n,))
+    for M in (1, 8, 32):
+        x = torch.randn((M, n), device="cuda")
+        y = torch.empty((M, n), device="cuda")
+        state = {"i": 0}
+
+        def sk():
+            eng.gemm_bias_act(x, Ws[state["i"] % 8], bias, y, M, n, n, act="gelu")
+            state["i"] += 1
+        step_ms, core_ms, _ = core_time(sk, 64, 8)
+        nbytes = n * n * 4 + 2 * M * n * 4 + n * 4
+        gbs = nbytes / (core_ms * 1e-3) / 1e9
+        out.append({"workload": f"skinny-M dense+bias+GELU, x[{M}x4096].W[4096x4096]", "value": nbytes / (step_ms * 1e-3) / 1e9,
+                    "unit": "GB/s", "ms_per_step": step_ms, "kernel_ms": core_ms,
+                    "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "frac": gbs / hbm,
+                                 "peak_source": f"{peaks['source']} HBM copy bandwidth"}})
+    del Ws
+
+    # dense + bias + ReLU 1024^3 (BASELINE config 1)
+    a1, b1, bias1 = uniform((1024, 1024)), uniform((1024, 1024)), uniform((1024,))
+    c1 = torch.empty((1024, 1024), device="cuda")
+    step_ms, core_ms, pre_ms = core_time(lambda: eng.gemm_relu(a1, b1, bias1, c1), 50, 5)
+    out.append({"workload": "fp32 GEMM+bias+ReLU 1024^3 (3xTF32)", "value": 2.0 * 1024 ** 3 / (step_ms * 1e-3) / 1e12,
+                "unit": "TFLOP/s", "ms_per_step": step_ms, "kernel_ms": core_ms, "prepass_ms": pre_ms})
+
+    # quantised GEMM 512x4096x4096 (BASELINE config 3): W8A8 and the reference's W8A32
+    a3 = torch.randint(-127, 128, (512, 4096), device="cuda", dtype=torch.int8)
+    b3 = torch.randint(-127, 128, (4096, 4096), device="cuda", dtype=torch.int8)
+    s3 = torch.rand((4096,), device="cuda") * 0.019 + 0.001
+    q3 = torch.empty((512, 4096), device="cuda", dtype=torch.int8)
+    step_ms, core_ms, _ = core_time(lambda: eng.qgemm_w8a8(a3, 0.02, b3, s3, 20.0, q3, None), 50, 5)
+    out.append({"workload": "int8 W8A8 GEMM 512x4096x4096 -> int8", "value": 2.0 * 512 * 4096 * 4096 / (step_ms * 1e-3) / 1e12,
+                "unit": "TOPS", "ms_per_step": step_ms, "kernel_ms": core_ms})
+    af = uniform((512, 4096))
+    of = torch.empty((512, 4096), device="cuda")
+    step_ms, core_ms, pre_ms = core_time(lambda: eng.qgemm_w8a32(af, b3, s3, of), 30, 3)
+    out.append({"workload": "W8A32 GEMM 512x4096x4096 (fp32 activations, int8 weights)",
+                "value": 2.0 * 512 * 4096 * 4096 / (step_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": step_ms,
+                "kernel_ms": core_ms, "prepass_ms": pre_ms})
+
+    # causal attention B=8,H=16,S=1024,dk=64 (BASELINE config 4); FLOPs by the reference's 4*BH*S^2*dk convention
+    BH, S, dk = 128, 1024, 64
+    Q, Kt, V = (torch.randn((BH, S, dk), device="cuda") for _ in range(3))
+    O = torch.empty((BH, S, dk), device="cuda")
+    L = torch.empty((BH, S), device="cuda")
+    step_ms, core_ms, _ = core_time(lambda: eng.sdpa_fwd(Q, Kt, V, O, L, 0.125, True), 20, 3)
+    out.append({"workload": "causal SDPA fwd BH=128 S=1024 dk=64 (fp32)", "value": 4.0 * BH * S * S * dk / (step_ms * 1e-3) / 1e12,
+                "unit": "TFLOP/s (4*BH*S^2*dk convention; causal does half)", "ms_per_step": step_ms, "kernel_ms": core_ms})
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--headline-only", action="store_true", help="skip the extra workloads")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

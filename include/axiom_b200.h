@@ -73,10 +73,12 @@ AXB_API int axb_device_error(void);
 AXB_API int64_t axb_launch_count(int reset);
 /* Measurement aid (no reference counterpart): with profiling on, every GEMM-family,
    quantised-GEMM and attention call records CUDA events on the engine's stream
-   around its operand pre-pass and around its main kernel; axb_last_timing blocks
-   on the last such call and returns both durations in milliseconds. */
+   around its operand pre-pass and around its main kernel (the newest 256 calls
+   are kept).  axb_timing_summary blocks until they have finished, returns how
+   many calls it covers and their summed pre-pass and main-kernel times in
+   milliseconds, and starts a new window.  axb_set_profiling also starts one. */
 AXB_API void axb_set_profiling(int on);
-AXB_API int axb_last_timing(float *prepass_ms, float *core_ms);
+AXB_API int axb_timing_summary(int *calls, float *prepass_ms_total, float *core_ms_total);
 
 /* ---- dense fp32 GEMM family ----------------------------------------------
    Slots gemm / gemm_nt / gemm_tn / gemm_ex / gemm_relu of ax_backend_ops_t
