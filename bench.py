@@ -357,6 +357,49 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
     return out
 
 
+def run_profile_case(args):
+    """A short, small run of one route for capture under a profiler: 1 warm-up + 2 calls, then exit.
+    Not a benchmark: prints nothing that should be read as a measurement."""
+    import torch
+    from axiom_b200.engine import get_engine
+    torch.cuda.set_device(0)
+    eng = get_engine(0)
+    n = args.size
+    case = args.profile_case
+    if case.startswith("gemm_fp32"):
+        mode = case.split(":")[1] if ":" in case else "3xtf32"
+        eng.set_fp32_mode(mode)
+        A, B = torch.rand((n, n), device="cuda") * 2 - 1, torch.rand((n, n), device="cuda") * 2 - 1
+        C = torch.empty((n, n), device="cuda")
+        fn = lambda: eng.gemm(A, B, C)
+    elif case == "gemm_int8":
+        a = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8)
+        b = torch.randint(-127, 128, (n, n), device="cuda", dtype=torch.int8)
+        bs = torch.rand((n,), device="cuda") * 0.019 + 0.001
+        q = torch.empty((n, n), device="cuda", dtype=torch.int8)
+        fn = lambda: eng.qgemm_w8a8(a, 0.02, b, bs, 40.0, q, None)
+    elif case.startswith("skinny"):
+        M = int(case.split(":")[1]) if ":" in case else 1
+        Ws = [torch.randn((4096, 4096), device="cuda") / 64 for _ in range(4)]
+        x, bias, y = torch.randn((M, 4096), device="cuda"), torch.rand((4096,), device="cuda"), torch.empty((M, 4096), device="cuda")
+        state = {"i": 0}
+
+        def fn():
+            eng.gemm_bias_act(x, Ws[state["i"] % 4], bias, y, M, 4096, 4096, act="gelu")
+            state["i"] += 1
+    elif case == "sdpa":
+        Q, K, V = (torch.randn((128, 1024, 64), device="cuda") for _ in range(3))
+        O, L = torch.empty((128, 1024, 64), device="cuda"), torch.empty((128, 1024), device="cuda")
+        fn = lambda: eng.sdpa_fwd(Q, K, V, O, L, 0.125, True)
+    else:
+        raise SystemExit(f"unknown profile case {case}")
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    assert eng.device_error() == 0
+    print(json.dumps({"profile_case": case, "size": n, "calls": 3, "note": "not a measurement"}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -365,8 +408,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--headline-only", action="store_true", help="skip the extra workloads")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profile-case", default=None,
+                    help="gemm_fp32[:mode] | gemm_int8 | skinny[:M] | sdpa — 3 calls of one route on a small case, for ncu")
+    ap.add_argument("--size", type=int, default=4096, help="matrix size of --profile-case")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile_case:
+        run_profile_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
