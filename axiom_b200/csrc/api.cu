@@ -5,6 +5,7 @@
 #include "../../include/axiom_b200.h"
 
 #include "elementwise.cuh"
+#include "errors.cuh"
 #include "gemm_tc.cuh"
 #include "prepass.cuh"
 #include "ptx.cuh"
@@ -227,6 +228,15 @@ int gemm_skinny(const float *X, const float *W, const float *bias, float *Y, int
 }
 
 }  // namespace
+
+int axb::set_error(int status, const char *fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g.msg, sizeof g.msg, fmt, ap);
+    va_end(ap);
+    return status;
+}
 
 // ------------------------------------------------------------------ lifecycle
 

@@ -11,6 +11,9 @@
 // depend on scheduling: repeated calls are bitwise identical.
 #include "skinny.cuh"
 
+#include "../../include/axiom_b200.h"
+#include "errors.cuh"
+
 #include <stdint.h>
 
 namespace axb {
@@ -152,11 +155,14 @@ static int launch_mt(const SkinnyArgs &a, bool vec, dim3 grid, size_t smem, cuda
 {
     auto kv = skinny_kernel<MT, true>;
     auto ks = skinny_kernel<MT, false>;
-    static bool attr_set = false;  // the X slice is capped at 64 KB by skinny_plan
-    if (!attr_set) {
+    // once per device and instantiation: allow the 64 KB X slice skinny_plan may ask for
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
         cudaFuncSetAttribute(kv, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
         cudaFuncSetAttribute(ks, cudaFuncAttributeMaxDynamicSharedMemorySize, 72 * 1024);
-        attr_set = true;
+        attr_set[dev] = true;
     }
     if (vec) kv<<<grid, SK_THREADS, smem, st>>>(a);
     else ks<<<grid, SK_THREADS, smem, st>>>(a);
@@ -202,3 +208,79 @@ int launch_skinny(const SkinnyArgs &args, const SkinnyPlan &plan, cudaStream_t s
 }
 
 }  // namespace axb
+
+// ------------------------------------------------- allocation-free entry point
+//
+// axb_skinny_gemm_static runs the same kernel as the skinny route above but
+// takes its split-K scratch from a fixed array that is part of the library
+// image, so the call itself never asks the driver for memory.  Every GPU that
+// loads the library carries the array (AXB_STATIC_SCRATCH_BYTES) until exit.
+
+namespace {
+
+constexpr int64_t kStaticPartialFloats = (int64_t)1 << 20;   // 4 MiB of split-K partial sums
+constexpr int kStaticCounters = 1024;                        // one arrival counter per 128-column strip
+constexpr int kMaxDevices = 64;
+
+// In host code this name is only a handle for cudaGetSymbolAddress; the device
+// address it stands for differs per GPU and is looked up once per device below.
+static __device__ __align__(256) float g_static_scratch[kStaticPartialFloats + kStaticCounters];
+
+static float *s_scratch_addr[kMaxDevices];   // device address of g_static_scratch, per device ordinal
+static int s_sm_count[kMaxDevices];
+
+}  // namespace
+
+extern "C" int axb_skinny_gemm_static(const float *X, const float *W, const float *bias, float *Y,
+                                      int64_t M, int64_t N, int64_t K, float alpha, float beta, int act,
+                                      void *cuda_stream)
+{
+    using namespace axb;
+    if (!X || !W || !Y) return set_error(AXB_ERR_NULL_ARG, "skinny_gemm_static: NULL operand");
+    if (M < 1 || M > 32 || N < 1 || K < 1)
+        return set_error(AXB_ERR_INVALID_SHAPE, "skinny_gemm_static: needs 1 <= M <= 32, N >= 1, K >= 1 (got M=%lld N=%lld K=%lld)",
+                         (long long)M, (long long)N, (long long)K);
+    if (act < AXB_ACT_NONE || act > AXB_ACT_GELU)
+        return set_error(AXB_ERR_INVALID_SHAPE, "skinny_gemm_static: unknown activation %d", act);
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return set_error(AXB_ERR_BACKEND, "skinny_gemm_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxDevices) return set_error(AXB_ERR_BACKEND, "skinny_gemm_static: device ordinal %d not supported", dev);
+    if (!s_scratch_addr[dev]) {
+        // first call on this device (it is the current one): resolve the array's device address
+        void *addr = nullptr;
+        e = cudaGetSymbolAddress(&addr, g_static_scratch);
+        if (e != cudaSuccess || !addr)
+            return set_error(AXB_ERR_BACKEND, "skinny_gemm_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        int sms = 0;
+        e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e != cudaSuccess || sms <= 0)
+            return set_error(AXB_ERR_BACKEND, "skinny_gemm_static: cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
+        s_sm_count[dev] = sms;
+        s_scratch_addr[dev] = static_cast<float *>(addr);
+    }
+    SkinnyPlan plan;
+    skinny_plan(M, N, K, s_sm_count[dev], &plan);
+    if (plan.partial_floats > kStaticPartialFloats || plan.strips > kStaticCounters)
+        return set_error(AXB_ERR_INVALID_SHAPE,
+                         "skinny_gemm_static: M=%lld N=%lld K=%lld needs %lld scratch floats and %d strip counters; the built-in "
+                         "scratch holds %lld and %d (use axb_gemm_bias_act, which allocates)",
+                         (long long)M, (long long)N, (long long)K, (long long)plan.partial_floats, plan.strips,
+                         (long long)kStaticPartialFloats, kStaticCounters);
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    float *scratch = s_scratch_addr[dev];
+    int *counters = reinterpret_cast<int *>(scratch + kStaticPartialFloats);
+    // the array keeps whatever the previous call left: the arrival counters must start at zero
+    e = cudaMemsetAsync(counters, 0, (size_t)plan.strips * sizeof(int), st);
+    if (e != cudaSuccess) return set_error(AXB_ERR_BACKEND, "skinny_gemm_static: cudaMemsetAsync: %s", cudaGetErrorString(e));
+    SkinnyArgs a;
+    a.X = X; a.W = W; a.bias = bias; a.Y = Y; a.M = (int)M; a.N = N; a.K = K;
+    a.alpha = alpha; a.beta = beta; a.act = act;
+    a.ksplit = plan.ksplit; a.kchunk = plan.kchunk;
+    a.partial = plan.ksplit > 1 ? scratch : nullptr;
+    a.counters = counters;
+    int le = launch_skinny(a, plan, st);
+    if (le) return set_error(AXB_ERR_BACKEND, "skinny_gemm_static: launch: %s", cudaGetErrorString((cudaError_t)le));
+    return AXB_OK;
+}
+

@@ -23,6 +23,7 @@ EXPORTS = [
     "axb_set_fp32_mode", "axb_get_fp32_mode", "axb_last_error", "axb_device_error", "axb_launch_count",
     "axb_set_profiling", "axb_timing_summary",
     "axb_gemm", "axb_gemm_nt", "axb_gemm_tn", "axb_gemm_ex", "axb_gemm_relu", "axb_gemm_bias_act",
+    "axb_skinny_gemm_static",
     "axb_bias_add", "axb_relu", "axb_gelu", "axb_qgemm_w8a32", "axb_qgemm_w8a8", "axb_quantize_rows",
     "axb_sdpa_fwd",
 ]
@@ -133,6 +134,12 @@ class Engine:
     def gemm_bias_act(self, A, B, bias, out, M, N, K, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, act="none"):
         self._check(self.lib.axb_gemm_bias_act(_ptr(A), _ptr(B), _ptr(bias), _ptr(out), _i64(M), _i64(N), _i64(K),
                                                int(trans_a), int(trans_b), _f(alpha), _f(beta), ACT[act]))
+        return out
+
+    def skinny_gemm_static(self, X, W, bias, out, M, N, K, alpha=1.0, beta=0.0, act="none", stream_ptr=None):
+        """Allocation-free skinny GEMM (axb_skinny_gemm_static): scratch lives inside the library."""
+        self._check(self.lib.axb_skinny_gemm_static(_ptr(X), _ptr(W), _ptr(bias), _ptr(out), _i64(M), _i64(N), _i64(K),
+                                                    _f(alpha), _f(beta), ACT[act], C.c_void_p(stream_ptr)))
         return out
 
     # ---- elementwise ---------------------------------------------------

@@ -110,6 +110,33 @@ AXB_API int axb_gemm_bias_act(const float *A, const float *B, const float *bias,
                       int64_t M, int64_t N, int64_t K, int trans_a, int trans_b,
                       float alpha, float beta, int act);
 
+/* Skinny-M GEMM that never allocates (no counterpart in the reference).
+     Y[M,N] = act(alpha * X[M,K] . W[K,N] + beta * Y + bias[n]),  1 <= M <= 32
+   Same kernel and bit-identical results as the skinny route of axb_gemm_bias_act,
+   but the split-K scratch is a fixed 4 MiB + 4 KiB array inside the library image
+   (AXB_STATIC_SCRATCH_BYTES, resident on every GPU that loads the library) instead
+   of memory obtained from cudaMalloc.  It is meant for callers that must not
+   allocate once they are running: a host framework that handed the whole device
+   to its own arena at start-up, a serving loop that cannot afford the device-wide
+   stall an allocation may cause, or a process held to a fixed memory budget.
+   The call uses neither the engine's state nor axb_init, and issues no cudaMalloc,
+   cudaFree or other allocating call.
+   - The device used is the calling thread's current CUDA device; work goes to
+     cuda_stream (NULL = legacy default stream).
+   - The first call on each device looks up the array's address on that device;
+     make that first call during start-up, outside any stream capture.
+   - Shapes whose split-K partial sums exceed the array (roughly M * N * 9 > 2^20
+     floats on a 148-SM part, e.g. M = 32 with N = 4096) or with N > 131072 are
+     refused with AXB_ERR_INVALID_SHAPE and a message; nothing is launched.
+   - All calls on a device share the one array and it keeps the previous call's
+     contents (the counters are cleared on the stream before each launch).  Two
+     calls that overlap on the GPU — different streams without ordering, or
+     different threads — race on it; serialise them. */
+#define AXB_STATIC_SCRATCH_BYTES ((1u << 22) + 4096u)
+AXB_API int axb_skinny_gemm_static(const float *X, const float *W, const float *bias, float *Y,
+                                   int64_t M, int64_t N, int64_t K, float alpha, float beta, int act,
+                                   void *cuda_stream);
+
 /* ---- elementwise slots that remain as separate calls ---------------------- */
 /* out = in + bias broadcast along axis (0: bias[M], 1: bias[N]); out may alias in.
    (bias_add slot, backend_ops.h:190; src/compute/backends/cuda/ops_fused.cu:260-292) */
