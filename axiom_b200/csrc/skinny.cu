@@ -106,7 +106,7 @@ __global__ void __launch_bounds__(SK_THREADS) skinny_kernel(const SkinnyArgs a)
 
     float *red = smem;  // [SK_WARPS][RM][SK_STRIP]
     float *part = a.partial ? a.partial + (int64_t)ks * a.M * a.N : nullptr;
-#pragma unroll 1
+#pragma unroll  // m0 must be a compile-time constant: acc[] is indexed with it and has to stay in registers
     for (int m0 = 0; m0 < MT; m0 += RM) {
 #pragma unroll
         for (int mi = 0; mi < RM; ++mi)

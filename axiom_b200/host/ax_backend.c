@@ -1,0 +1,213 @@
+/* ax_backend.c — the host side of the drop-in: axiom's backend vtable and CUDA
+   extension table, filled in plain C on top of the C ABI of libaxiom_b200.so.
+
+   Each function does what the corresponding function of the reference CUDA
+   backend does before it reaches its kernel — validate the tensors, resolve
+   `(float *)storage->data + offset`, read the sizes (for example
+   src/compute/backends/cuda/ops_gemm.cu:15-37) — and then makes exactly one
+   call into the engine.  No arithmetic happens here. */
+#include "axiom_b200_backend.h"
+#include "axiom_b200.h"
+
+#include <stdio.h>
+
+/* axiom status codes used below (include/axiom/types.h:89-103) */
+enum { ST_OK = 0, ST_NULL_ARG = 1, ST_SHAPE = 3, ST_DTYPE = 4, ST_AXIS = 5, ST_INVALID_SHAPE = 6, ST_BACKEND = 9 };
+
+static int (*hook_skip_init)(void);
+static void (*hook_set_err)(int, const char *);
+
+void axb_backend_set_hooks(int (*skip_init)(void), void (*set_err)(int status, const char *msg))
+{
+    hook_skip_init = skip_init;
+    hook_set_err = set_err;
+}
+
+static axb_status report(axb_status st, const char *msg)
+{
+    if (st != ST_OK && hook_set_err) hook_set_err(st, msg);
+    return st;
+}
+
+/* forward the engine's status together with its message */
+static axb_status done(int st)
+{
+    return st == AXB_OK ? ST_OK : report(st, axb_last_error());
+}
+
+static int64_t numel(const axb_ax_tensor_t *t)
+{
+    int64_t n = 1;
+    for (int i = 0; i < t->ndim; ++i) n *= t->shape[i];
+    return n;
+}
+
+static int is_contiguous(const axb_ax_tensor_t *t)
+{
+    int64_t expect = 1;
+    for (int i = t->ndim - 1; i >= 0; --i) {
+        if (t->shape[i] != 1 && t->strides[i] != expect) return 0;
+        expect *= t->shape[i];
+    }
+    return 1;
+}
+
+/* the reference's contract for every GEMM slot: fp32, contiguous, resident on the device */
+static axb_status check_f32(const axb_ax_tensor_t *t, const char *what, int want_ndim)
+{
+    char msg[160];
+    if (!t || !t->storage) {
+        snprintf(msg, sizeof msg, "%s: NULL tensor", what);
+        return report(ST_NULL_ARG, msg);
+    }
+    if (t->dtype != AXB_AX_FLOAT32) {
+        snprintf(msg, sizeof msg, "%s: only float32 is supported", what);
+        return report(ST_DTYPE, msg);
+    }
+    if (want_ndim > 0 && t->ndim != want_ndim) {
+        snprintf(msg, sizeof msg, "%s: expected a %d-d tensor, got %d-d", what, want_ndim, t->ndim);
+        return report(ST_SHAPE, msg);
+    }
+    if (!is_contiguous(t)) {
+        snprintf(msg, sizeof msg, "%s: tensor must be contiguous", what);
+        return report(ST_INVALID_SHAPE, msg);
+    }
+    if (t->storage->device != AXB_AX_DEVICE_CUDA) {
+        snprintf(msg, sizeof msg, "%s: tensor is not on the CUDA device", what);
+        return report(ST_BACKEND, msg);
+    }
+    return ST_OK;
+}
+
+static float *fptr(const axb_ax_tensor_t *t) { return (float *)t->storage->data + t->offset; }
+
+/* shared body of gemm / gemm_nt / gemm_tn / gemm_relu / gemm_ex */
+static axb_status gemm_common(const char *what, const axb_ax_tensor_t *a, const axb_ax_tensor_t *b,
+                              const axb_ax_tensor_t *bias, axb_ax_tensor_t *out, int ta, int tb, float alpha,
+                              float beta, int act)
+{
+    axb_status st;
+    if ((st = check_f32(a, what, 2)) || (st = check_f32(b, what, 2)) || (st = check_f32(out, what, 2))) return st;
+    const int64_t M = ta ? a->shape[1] : a->shape[0];
+    const int64_t K = ta ? a->shape[0] : a->shape[1];
+    const int64_t Kb = tb ? b->shape[1] : b->shape[0];
+    const int64_t N = tb ? b->shape[0] : b->shape[1];
+    if (K != Kb || out->shape[0] != M || out->shape[1] != N) {
+        char msg[200];
+        snprintf(msg, sizeof msg, "%s shape mismatch: op(a)=[%lld,%lld] op(b)=[%lld,%lld] out=[%lld,%lld]", what,
+                 (long long)M, (long long)K, (long long)Kb, (long long)N, (long long)out->shape[0],
+                 (long long)out->shape[1]);
+        return report(ST_SHAPE, msg);
+    }
+    const float *bias_p = NULL;
+    if (bias) {
+        if ((st = check_f32(bias, what, 1))) return st;
+        if (bias->shape[0] != N) return report(ST_SHAPE, "gemm bias length must equal the output columns");
+        bias_p = fptr(bias);
+    }
+    return done(axb_gemm_bias_act(fptr(a), fptr(b), bias_p, fptr(out), M, N, K, ta, tb, alpha, beta, act));
+}
+
+static float accumulate_beta(void) { return (hook_skip_init && hook_skip_init()) ? 1.0f : 0.0f; }
+
+static axb_status be_gemm(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, axb_ax_tensor_t *out)
+{
+    return gemm_common("gemm", a, b, NULL, out, 0, 0, 1.0f, accumulate_beta(), AXB_ACT_NONE);
+}
+
+static axb_status be_gemm_nt(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, axb_ax_tensor_t *out)
+{
+    return gemm_common("gemm_nt", a, b, NULL, out, 0, 1, 1.0f, accumulate_beta(), AXB_ACT_NONE);
+}
+
+static axb_status be_gemm_tn(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, axb_ax_tensor_t *out)
+{
+    return gemm_common("gemm_tn", a, b, NULL, out, 1, 0, 1.0f, accumulate_beta(), AXB_ACT_NONE);
+}
+
+static axb_status be_gemm_relu(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, const axb_ax_tensor_t *bias,
+                               axb_ax_tensor_t *out)
+{
+    return gemm_common("gemm_relu", a, b, bias, out, 0, 0, 1.0f, 0.0f, AXB_ACT_RELU);
+}
+
+static axb_status be_gemm_ex(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, float alpha, float beta,
+                             axb_ax_tensor_t *out)
+{
+    return gemm_common("gemm_ex", a, b, NULL, out, 0, 0, alpha, beta, AXB_ACT_NONE);
+}
+
+static axb_status be_bias_add(const axb_ax_tensor_t *in, const axb_ax_tensor_t *bias, int axis, axb_ax_tensor_t *out)
+{
+    axb_status st;
+    if ((st = check_f32(in, "bias_add", 2)) || (st = check_f32(out, "bias_add", 2)) ||
+        (st = check_f32(bias, "bias_add", 1)))
+        return st;
+    if (axis < 0) axis += 2;
+    if (axis != 0 && axis != 1) return report(ST_AXIS, "bias_add: axis out of range for a 2-d tensor");
+    if (out->shape[0] != in->shape[0] || out->shape[1] != in->shape[1] || bias->shape[0] != in->shape[axis])
+        return report(ST_SHAPE, "bias_add: bias length must equal in->shape[axis] and out must match in");
+    return done(axb_bias_add(fptr(in), fptr(bias), axis, fptr(out), in->shape[0], in->shape[1]));
+}
+
+static axb_status unary(const char *what, const axb_ax_tensor_t *in, axb_ax_tensor_t *out, int gelu)
+{
+    axb_status st;
+    if ((st = check_f32(in, what, 0)) || (st = check_f32(out, what, 0))) return st;
+    if (numel(in) != numel(out)) return report(ST_SHAPE, "unary op: in and out must have the same number of elements");
+    return done(gelu ? axb_gelu(fptr(in), fptr(out), numel(in)) : axb_relu(fptr(in), fptr(out), numel(in)));
+}
+
+static axb_status be_relu(const axb_ax_tensor_t *in, axb_ax_tensor_t *out) { return unary("relu", in, out, 0); }
+static axb_status be_gelu(const axb_ax_tensor_t *in, axb_ax_tensor_t *out) { return unary("gelu", in, out, 1); }
+
+/* ---- device-owner hooks (src/compute/backends/cuda/backend.cu:56-116, memory.cu:80-140) ---- */
+
+static axb_status be_init(void) { return done(axb_init(-1)); }
+static void be_shutdown(void) { axb_shutdown(); }
+static void be_synchronize(void)
+{
+    axb_synchronize();
+    if (axb_device_error() != 0) report(ST_BACKEND, axb_last_error());
+}
+static int be_device_count(void) { return axb_device_count(); }
+static void *be_alloc(size_t bytes) { return axb_storage_alloc(bytes); }
+static void be_free(void *p) { axb_storage_free(p); }
+static axb_status be_h2d(void *dst, const void *src, size_t bytes) { return done(axb_memcpy_h2d(dst, src, bytes)); }
+static axb_status be_d2h(void *dst, const void *src, size_t bytes) { return done(axb_memcpy_d2h(dst, src, bytes)); }
+static axb_status be_d2d(void *dst, const void *src, size_t bytes) { return done(axb_memcpy_d2d(dst, src, bytes)); }
+
+static axb_status ext_sdpa_fwd(const float *Q, const float *K, const float *V, float *out, float *L, int64_t BH,
+                               int64_t S, int64_t dk, float scale, bool causal, float *P_save)
+{
+    return done(axb_sdpa_fwd(Q, K, V, out, L, BH, S, dk, scale, causal ? 1 : 0, P_save));
+}
+
+static const axb_ax_backend_ops_t ops_table = {
+    .name = "b200_tcgen05",
+    .gemm = be_gemm,
+    .gemm_nt = be_gemm_nt,
+    .gemm_tn = be_gemm_tn,
+    .gemm_relu = be_gemm_relu,
+    .gemm_ex = be_gemm_ex,
+    .bias_add = be_bias_add,
+    .relu = be_relu,
+    .gelu_op = be_gelu,
+    .device = AXB_AX_DEVICE_CUDA,
+    .init = be_init,
+    .shutdown = be_shutdown,
+    .synchronize = be_synchronize,
+    .device_count = be_device_count,
+    .storage_alloc = be_alloc,
+    .storage_free = be_free,
+    .memcpy_h2d = be_h2d,
+    .memcpy_d2h = be_d2h,
+    .memcpy_d2d = be_d2d,
+};
+
+static const axb_ax_cuda_extension_t extension_table = {
+    .sdpa_fwd = ext_sdpa_fwd,
+};
+
+const axb_ax_backend_ops_t *axb_backend_ops(void) { return &ops_table; }
+const axb_ax_cuda_extension_t *axb_cuda_extension(void) { return &extension_table; }

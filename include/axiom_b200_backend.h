@@ -1,0 +1,120 @@
+/* axiom_b200_backend.h — the axiom plug-in tables, as filled by libaxiom_b200_backend.so.
+
+   axiom (v0.10.0) talks to a compute backend through two tables of function
+   pointers: `ax_backend_ops_t` (include/axiom/internal/backend_ops.h:30-298) and
+   `ax_cuda_extension_t` (include/axiom/internal/cuda_extension.h:41-130), whose
+   operands are `ax_tensor_t` / `ax_storage_t` (include/axiom/tensor.h:29-70).
+   This header describes the same binary layouts under `axb_`-prefixed names so
+   that the host layer can be compiled without the axiom tree and so that both
+   sets of headers can be included in one translation unit (tests do that to
+   check every offset with _Static_assert).  Slots this engine does not provide
+   are kept as opaque pointers so the layout stays identical; they are NULL in
+   the exported table. */
+#ifndef AXIOM_B200_BACKEND_H
+#define AXIOM_B200_BACKEND_H
+
+#include <stdbool.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AXB_AX_MAX_DIMS 8        /* AX_MAX_DIMS, include/axiom/types.h */
+#define AXB_AX_FLOAT32 0         /* ax_dtype_t, include/axiom/types.h:52-60 */
+#define AXB_AX_DEVICE_CPU 0      /* ax_device_t, include/axiom/types.h:105-110 */
+#define AXB_AX_DEVICE_CUDA 1
+#define AXB_AX_BACKEND_CUDA 3    /* ax_backend_id_t, include/axiom/compute.h:46-52 */
+
+/* ax_storage_t (include/axiom/tensor.h:29-45) */
+typedef struct {
+    void *data;
+    size_t size_bytes;
+    int refcount;          /* atomic_int in axiom */
+    int device;            /* ax_device_t */
+    bool is_arena_temp;
+    uint64_t generation;
+} axb_ax_storage_t;
+
+/* ax_tensor_t (include/axiom/tensor.h:53-70) */
+typedef struct axb_ax_tensor {
+    axb_ax_storage_t *storage;
+    int64_t shape[AXB_AX_MAX_DIMS];
+    int64_t strides[AXB_AX_MAX_DIMS];   /* in elements */
+    int ndim;
+    int dtype;                          /* ax_dtype_t */
+    int64_t offset;                     /* in elements */
+    bool requires_grad;
+    struct axb_ax_tensor *grad;
+    void *grad_fn;
+    int layout;                         /* ax_layout_t */
+} axb_ax_tensor_t;
+
+typedef void (*axb_opaque_fn)(void);    /* a slot this engine leaves NULL */
+typedef int axb_status;                 /* ax_status_t */
+
+/* ax_backend_ops_t: one member per slot of the reference struct, in its order. */
+typedef struct {
+    const char *name;
+    axb_opaque_fn add, sub, mul, div_op;
+    axb_opaque_fn neg, abs_op, exp_op, log_op, sqrt_op, square;
+    axb_opaque_fn add_scalar, mul_scalar;
+    axb_status (*gemm)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, axb_ax_tensor_t *out);
+    axb_status (*gemm_nt)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, axb_ax_tensor_t *out);
+    axb_status (*gemm_tn)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, axb_ax_tensor_t *out);
+    axb_opaque_fn dwqkv_split_acc, dwqkv_split_acc_hm, qkv_head_gemm, dattn_head_gemm_nt, mha_output_proj_fused;
+    axb_status (*gemm_relu)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, const axb_ax_tensor_t *bias,
+                            axb_ax_tensor_t *out);
+    axb_status (*gemm_ex)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, float alpha, float beta,
+                          axb_ax_tensor_t *out);
+    axb_opaque_fn add_relu, axpy, softmax_rowwise;
+    axb_status (*bias_add)(const axb_ax_tensor_t *in, const axb_ax_tensor_t *bias, int axis, axb_ax_tensor_t *out);
+    axb_opaque_fn conv_gemm, conv_gemm_nt_dw;
+    axb_opaque_fn sum, mean, max_op, min_op, argmax;
+    axb_opaque_fn equal, greater;
+    axb_opaque_fn fill, copy;
+    axb_status (*relu)(const axb_ax_tensor_t *in, axb_ax_tensor_t *out);
+    axb_opaque_fn sigmoid, tanh_op, leaky_relu, elu_op;
+    axb_status (*gelu_op)(const axb_ax_tensor_t *in, axb_ax_tensor_t *out);
+    axb_opaque_fn swish_op, adam_update, sgd_update;
+    int device;                          /* ax_device_t this backend owns */
+    axb_status (*init)(void);
+    void (*shutdown)(void);
+    void (*synchronize)(void);
+    int (*device_count)(void);
+    void *(*storage_alloc)(size_t size_bytes);
+    void (*storage_free)(void *ptr);
+    axb_status (*memcpy_h2d)(void *dst, const void *src, size_t bytes);
+    axb_status (*memcpy_d2h)(void *dst, const void *src, size_t bytes);
+    axb_status (*memcpy_d2d)(void *dst, const void *src, size_t bytes);
+} axb_ax_backend_ops_t;
+
+/* ax_cuda_extension_t: only sdpa_fwd is provided. */
+typedef struct {
+    axb_opaque_fn head_interleave_qkv_split, head_interleave_qkv_split_bias, head_interleave, head_deinterleave,
+        head_deinterleave_qkv_merge;
+    axb_opaque_fn qkv_cache_build, bias_cache_build;
+    axb_status (*sdpa_fwd)(const float *Q, const float *K, const float *V, float *out, float *L, int64_t BH,
+                           int64_t S, int64_t dk, float scale, bool causal, float *P_save);
+    axb_opaque_fn sdpa_bwd, conv_gemm_batched, conv_winograd_f23, winograd_f23_prefer;
+} axb_ax_cuda_extension_t;
+
+#define AXB_BACKEND_API __attribute__((visibility("default")))
+
+/* The tables.  Cast to `const ax_backend_ops_t *` / `const ax_cuda_extension_t *` on the
+   axiom side (same layout) and hand them to ax_compute_register_backend(AX_BACKEND_CUDA, ...)
+   (src/compute/dispatch.c:302-315) and ax_compute_register_cuda_extension (dispatch.c:290-296). */
+AXB_BACKEND_API const axb_ax_backend_ops_t *axb_backend_ops(void);
+AXB_BACKEND_API const axb_ax_cuda_extension_t *axb_cuda_extension(void);
+
+/* Optional hooks into the host framework:
+   skip_init  returns non-zero while the caller wants gemm/gemm_nt/gemm_tn to ACCUMULATE into
+              `out` (axiom's ax_gemm_get_skip_init(), src/compute/dispatch.c:1284-1285);
+   set_err    receives every failure (axiom's ax_err_set, src/core/error.c:23-38). */
+AXB_BACKEND_API void axb_backend_set_hooks(int (*skip_init)(void), void (*set_err)(int status, const char *msg));
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AXIOM_B200_BACKEND_H */

@@ -176,6 +176,146 @@ SHIM_API int ref_qgemm_w8a32(const float *a, const int8_t *q, const float *scale
     return (int)ax_qgemm_w8a32(a, &qw, out, M);
 }
 
+/* ---- the reference's dispatcher driving an EXTERNAL backend -------------------
+   These doors exist to prove the drop-in: a vtable from another library is
+   registered with the reference's own ax_compute_register_backend, operands go
+   to the device through the reference's ax_tensor_to_cuda (the backend's
+   storage_alloc / memcpy_h2d hooks) and the reference's ax_compute_* wrappers
+   dispatch into the registered slots. */
+#include "axiom/internal/compute_internal.h"
+#include "axiom/internal/cuda_extension.h"
+
+SHIM_API int ref_register_cuda_backend(const void *ops, const void *ext)
+{
+    ax_status_t st = ax_compute_register_backend(AX_BACKEND_CUDA, (const ax_backend_ops_t *)ops);
+    if (st != AX_OK) return (int)st;
+    return (int)ax_compute_register_cuda_extension((const ax_cuda_extension_t *)ext);
+}
+
+SHIM_API int ref_skip_init_flag(void) { return ax_gemm_get_skip_init() ? 1 : 0; }
+SHIM_API void ref_err_set(int st, const char *msg) { ax_err_set((ax_status_t)st, "%s", msg); }
+SHIM_API const char *ref_last_error(void) { return ax_err_last_message(); }
+
+static void use_cuda(int on)
+{
+    ax_compute_set_backend(on ? AX_BACKEND_CUDA : AX_BACKEND_CPU_SIMD);
+    ax_set_default_device(on ? AX_DEVICE_CUDA : AX_DEVICE_CPU);
+}
+
+static ax_tensor_t *to_dev(ax_tensor_t *host)
+{
+    ax_tensor_t *d = ax_tensor_to_cuda(host);
+    ax_tensor_destroy(host);
+    return d;
+}
+
+static int copy_back(ax_tensor_t *dev, float *dst, int64_t n)
+{
+    ax_tensor_t *h = ax_tensor_to_cpu(dev);
+    if (!h) return 1;
+    memcpy(dst, tdata(h), (size_t)n * sizeof(float));
+    ax_tensor_destroy(h);
+    return 0;
+}
+
+/* op: 0 gemm, 1 gemm_nt, 2 gemm_tn, 3 gemm_relu (bias nullable), 4 gemm_ex(alpha,beta; C read),
+   5 gemm with ax_gemm_set_skip_init(true) (C += A.B), 6 ax_matmul_bias_relu (the dense-layer op). */
+SHIM_API int ref_device_gemm_op(int op, const float *A, const float *B, const float *bias, float *C,
+                                int64_t M, int64_t N, int64_t K, float alpha, float beta)
+{
+    use_cuda(1);
+    ax_tensor_t *a = to_dev(op == 2 ? t2(A, K, M) : t2(A, M, K));
+    ax_tensor_t *b = to_dev(op == 1 ? t2(B, N, K) : t2(B, K, N));
+    ax_tensor_t *bs = bias ? to_dev(t1(bias, N)) : NULL;
+    ax_tensor_t *o = NULL;
+    int rc = 0;
+    if (!a || !b || (bias && !bs)) rc = 100;
+    if (!rc && op == 6) {
+        o = ax_matmul_bias_relu(a, b, bs);
+        if (!o) rc = 101;
+    } else if (!rc) {
+        o = to_dev(t2(C, M, N));
+        if (!o) rc = 102;
+        else if (op == 0) rc = (int)ax_compute_gemm(a, b, o);
+        else if (op == 1) rc = (int)ax_compute_gemm_nt(a, b, o);
+        else if (op == 2) rc = (int)ax_compute_gemm_tn(a, b, o);
+        else if (op == 3) rc = (int)ax_compute_gemm_relu(a, b, bs, o);
+        else if (op == 4) rc = (int)ax_compute_gemm_ex(a, b, alpha, beta, o);
+        else if (op == 5) {
+            ax_gemm_set_skip_init(true);
+            rc = (int)ax_compute_gemm(a, b, o);
+            ax_gemm_set_skip_init(false);
+        }
+    }
+    if (!rc) {
+        ax_device_synchronize(AX_DEVICE_CUDA);
+        rc = copy_back(o, C, M * N);
+    }
+    if (a) ax_tensor_destroy(a);
+    if (b) ax_tensor_destroy(b);
+    if (bs) ax_tensor_destroy(bs);
+    if (o) ax_tensor_destroy(o);
+    use_cuda(0);
+    return rc;
+}
+
+/* bias_add / relu / gelu slots through ax_compute_bias_add, ax_compute_relu and the gelu_op slot on device tensors.
+   op: 0 bias_add(axis), 1 relu, 2 gelu (the gelu_op slot). */
+SHIM_API int ref_device_elementwise(int op, const float *in, const float *bias, int axis, float *out,
+                                    int64_t M, int64_t N)
+{
+    use_cuda(1);
+    ax_tensor_t *x = to_dev(t2(in, M, N));
+    ax_tensor_t *o = to_dev(t2(in, M, N));
+    ax_tensor_t *b = bias ? to_dev(t1(bias, axis == 0 ? M : N)) : NULL;
+    int rc = (!x || !o) ? 100 : 0;
+    if (!rc && op == 0) rc = (int)ax_compute_bias_add(x, b, axis, o);
+    else if (!rc && op == 1) rc = (int)ax_compute_relu(x, o);
+    else if (!rc) {
+        /* the dispatcher has no wrapper for gelu_op: reach the slot through the active vtable */
+        const ax_backend_ops_t *ops = ax_compute_get_ops();
+        rc = (ops && ops->gelu_op) ? (int)ops->gelu_op(x, o) : (int)AX_ERR_NOT_IMPLEMENTED;
+    }
+    if (!rc) {
+        ax_device_synchronize(AX_DEVICE_CUDA);
+        rc = copy_back(o, out, M * N);
+    }
+    if (x) ax_tensor_destroy(x);
+    if (o) ax_tensor_destroy(o);
+    if (b) ax_tensor_destroy(b);
+    use_cuda(0);
+    return rc;
+}
+
+/* the sdpa_fwd slot of the registered extension table, on device buffers made by the reference */
+SHIM_API int ref_device_sdpa_fwd(const float *Q, const float *K, const float *V, float *O, float *L,
+                                 int64_t BH, int64_t S, int64_t dk, float scale, int causal)
+{
+    const ax_cuda_extension_t *ext = ax_compute_get_cuda_extension();
+    if (!ext || !ext->sdpa_fwd) return 200;
+    use_cuda(1);
+    int64_t sh[3] = { BH, S, dk }, shl[2] = { BH, S };
+    ax_tensor_t *q = to_dev(ax_tensor_from_array(Q, sh, 3, AX_FLOAT32));
+    ax_tensor_t *k = to_dev(ax_tensor_from_array(K, sh, 3, AX_FLOAT32));
+    ax_tensor_t *v = to_dev(ax_tensor_from_array(V, sh, 3, AX_FLOAT32));
+    ax_tensor_t *o = to_dev(ax_tensor_from_array(Q, sh, 3, AX_FLOAT32));
+    ax_tensor_t *l = to_dev(ax_tensor_zeros(shl, 2, AX_FLOAT32));
+    int rc = (!q || !k || !v || !o || !l) ? 100 : 0;
+    if (!rc)
+        rc = (int)ext->sdpa_fwd(tdata(q), tdata(k), tdata(v), tdata(o), tdata(l), BH, S, dk, scale, causal != 0, NULL);
+    if (!rc) {
+        ax_device_synchronize(AX_DEVICE_CUDA);
+        rc = copy_back(o, O, BH * S * dk) || copy_back(l, L, BH * S);
+    }
+    if (q) ax_tensor_destroy(q);
+    if (k) ax_tensor_destroy(k);
+    if (v) ax_tensor_destroy(v);
+    if (o) ax_tensor_destroy(o);
+    if (l) ax_tensor_destroy(l);
+    use_cuda(0);
+    return rc;
+}
+
 /* ax_fused_attention_fwd / _causal on head-major [BH,S,dk] buffers. */
 SHIM_API int ref_sdpa_fwd(const float *Q, const float *K, const float *V, float *O, float *L,
                           int64_t BH, int64_t S, int64_t dk, float scale, int causal)

@@ -1,0 +1,106 @@
+"""Drop-in proof: the UNMODIFIED reference dispatcher (oracle/_ref) drives this engine.
+
+The vtable of libaxiom_b200_backend.so is registered with the reference's own
+ax_compute_register_backend; operands reach the GPU through the reference's
+ax_tensor_to_cuda (our storage_alloc / memcpy_h2d hooks); ax_compute_gemm*,
+ax_compute_gemm_relu, ax_compute_gemm_ex, ax_compute_bias_add, ax_compute_relu,
+ax_matmul_bias_relu and the sdpa_fwd extension slot dispatch into our kernels.
+Results are compared with the same reference running its CPU backend.
+"""
+import ctypes
+
+import numpy as np
+import pytest
+
+from oracle_lib import nerr
+
+pytestmark = pytest.mark.gpu
+f32p = ctypes.POINTER(ctypes.c_float)
+i64 = ctypes.c_int64
+
+
+def p(a):
+    return None if a is None else a.ctypes.data_as(f32p)
+
+
+@pytest.fixture(scope="module")
+def dropin(engine, reference):
+    from axiom_b200 import build
+    backend = ctypes.CDLL(build.BACKEND_SO)
+    lib = reference.lib
+    backend.axb_backend_ops.restype = ctypes.c_void_p
+    backend.axb_cuda_extension.restype = ctypes.c_void_p
+    SKIP = ctypes.CFUNCTYPE(ctypes.c_int)
+    ERR = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_char_p)
+    cbs = (SKIP(lambda: lib.ref_skip_init_flag()), ERR(lambda st, msg: lib.ref_err_set(st, msg)))
+    backend.axb_backend_set_hooks(*cbs)
+    assert lib.ref_register_cuda_backend(ctypes.c_void_p(backend.axb_backend_ops()),
+                                         ctypes.c_void_p(backend.axb_cuda_extension())) == 0
+    lib.ref_last_error.restype = ctypes.c_char_p
+    lib._keep = (backend, cbs)
+    return lib
+
+
+def gemm_op(lib, op, A, B, bias, C, M, N, K, alpha=1.0, beta=0.0):
+    rc = lib.ref_device_gemm_op(op, p(A), p(B), p(bias), p(C), i64(M), i64(N), i64(K), ctypes.c_float(alpha), ctypes.c_float(beta))
+    assert rc == 0, (rc, lib.ref_last_error())
+    return C
+
+
+@pytest.mark.parametrize("shape", [(2, 2, 2), (64, 32, 128), (200, 300, 170), (1, 256, 384), (8, 100, 64)])
+def test_gemm_slots_through_reference_dispatcher(dropin, reference, oracle, shape):
+    M, N, K = shape
+    A, B, bias, C0 = oracle.uniform((M, K), 7), oracle.uniform((K, N), 13), oracle.uniform((N,), 29), oracle.uniform((M, N), 5)
+    want = reference.gemm(A, B)
+    tol = dict(atol=1e-3, rtol=1e-4)   # tests/test_cuda.c:213-244 of the reference uses abs 1e-3 for GPU-vs-CPU
+    np.testing.assert_allclose(gemm_op(dropin, 0, A, B, None, np.zeros((M, N), np.float32), M, N, K), want, **tol)
+    np.testing.assert_allclose(gemm_op(dropin, 1, A, np.ascontiguousarray(B.T), None, np.zeros((M, N), np.float32), M, N, K), want, **tol)
+    np.testing.assert_allclose(gemm_op(dropin, 2, np.ascontiguousarray(A.T), B, None, np.zeros((M, N), np.float32), M, N, K), want, **tol)
+    np.testing.assert_allclose(gemm_op(dropin, 3, A, B, bias, np.zeros((M, N), np.float32), M, N, K), reference.gemm_relu(A, B, bias), **tol)
+    np.testing.assert_allclose(gemm_op(dropin, 4, A, B, None, C0.copy(), M, N, K, 0.5, 2.0), reference.gemm_ex(A, B, 0.5, 2.0, C0), **tol)
+    # ax_gemm_set_skip_init(true): C += A.B (cpu_opt honours it; the stock CUDA backend does not)
+    np.testing.assert_allclose(gemm_op(dropin, 5, A, B, None, C0.copy(), M, N, K), want + C0, **tol)
+    # the dense-layer op itself: ax_matmul_bias_relu allocates its output on the device through our hook
+    np.testing.assert_allclose(gemm_op(dropin, 6, A, B, bias, np.zeros((M, N), np.float32), M, N, K), reference.matmul_bias_relu(A, B, bias), **tol)
+    assert nerr(gemm_op(dropin, 0, A, B, None, np.zeros((M, N), np.float32), M, N, K), oracle.gemm_f64(A, B)) <= 1e-5
+
+
+def test_known_answer_of_the_reference_cuda_test(dropin):
+    # tests/test_cuda.c:169-191
+    A = np.array([[1, 2], [3, 4]], np.float32)
+    B = np.array([[5, 6], [7, 8]], np.float32)
+    C = gemm_op(dropin, 0, A, B, None, np.zeros((2, 2), np.float32), 2, 2, 2)
+    np.testing.assert_allclose(C, [[19, 22], [43, 50]], atol=1e-3)
+
+
+def test_elementwise_slots_through_reference_dispatcher(dropin, oracle):
+    X, bn, bm = oracle.uniform((37, 52), 3), oracle.uniform((52,), 4), oracle.uniform((37,), 6)
+    out = np.zeros_like(X)
+    for axis, b in ((1, bn), (0, bm)):
+        rc = dropin.ref_device_elementwise(0, p(X), p(b), axis, p(out), i64(37), i64(52))
+        assert rc == 0, dropin.ref_last_error()
+        np.testing.assert_array_equal(out, oracle.bias_add_axis(X, b, axis))
+    assert dropin.ref_device_elementwise(1, p(X), None, 0, p(out), i64(37), i64(52)) == 0
+    np.testing.assert_array_equal(out, oracle.relu(X))
+    assert dropin.ref_device_elementwise(2, p(X), None, 0, p(out), i64(37), i64(52)) == 0
+    np.testing.assert_allclose(out, oracle.gelu(X), atol=1e-6)
+
+
+@pytest.mark.parametrize("causal", [0, 1])
+def test_sdpa_extension_slot(dropin, reference, oracle, causal):
+    BH, S, dk = 6, 24, 16                                   # tests/test_attention.c:54-131 shape
+    Q, K, V = oracle.normal((BH, S, dk), 41), oracle.normal((BH, S, dk), 43), oracle.normal((BH, S, dk), 47)
+    O, L = np.zeros_like(Q), np.zeros((BH, S), np.float32)
+    rc = dropin.ref_device_sdpa_fwd(p(Q), p(K), p(V), p(O), p(L), i64(BH), i64(S), i64(dk), ctypes.c_float(0.25), causal)
+    assert rc == 0, dropin.ref_last_error()
+    O_ref, L_ref = reference.sdpa_fwd(Q, K, V, 0.25, causal)
+    assert np.abs(O - O_ref).max() < 1e-4 and np.abs(L - L_ref).max() < 1e-4
+
+
+def test_bias_add_axis0_is_per_row(dropin, oracle):
+    """axis 0 broadcasts one value per ROW (the documented meaning of the slot), also for M != N."""
+    M, N = 4, 6
+    X, row_bias = oracle.uniform((M, N), 3), oracle.uniform((M,), 4)
+    out = np.zeros((M, N), np.float32)
+    assert dropin.ref_device_elementwise(0, p(X), p(row_bias), 0, p(out), i64(M), i64(N)) == 0
+    np.testing.assert_array_equal(out, oracle.bias_add_axis(X, row_bias, 0))
