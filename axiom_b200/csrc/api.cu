@@ -196,7 +196,7 @@ int gemm_skinny(const float *X, const float *W, const float *bias, float *Y, int
                 float alpha, float beta, int act)
 {
     SkinnyPlan plan;
-    skinny_plan(M, N, K, g.sm_count, &plan);
+    skinny_plan(M, N, K, W, g.sm_count, &plan);
     if ((size_t)plan.partial_floats > g.sk_partial_floats) {
         if (g.sk_partial) { cudaStreamSynchronize(g.stream); cudaFree(g.sk_partial); g.sk_partial = nullptr; }
         const size_t want = (size_t)plan.partial_floats + (size_t)plan.partial_floats / 4;
@@ -218,6 +218,7 @@ int gemm_skinny(const float *X, const float *W, const float *bias, float *Y, int
     a.ksplit = plan.ksplit; a.kchunk = plan.kchunk;
     a.partial = plan.ksplit > 1 ? g.sk_partial : nullptr;
     a.counters = g.sk_counters;
+    a.err = g.err_word;
     mark(0);
     mark(1);
     int e = launch_skinny(a, plan, g.stream);

@@ -417,6 +417,30 @@ static int encode_plane(CUtensorMap *out, int kind, const void *ptr, int64_t row
     return 0;
 }
 
+// Plain (unswizzled) fp32 matrix [rows, cols] with row pitch `pitch_elems`, box = box_cols x box_rows.
+int encode_f32_matrix_tmap(void *tmap_out, const float *ptr, int64_t rows, int64_t cols, int64_t pitch_elems,
+                           int box_cols, int box_rows)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled entry point not found");
+        return (int)cudaErrorSymbolNotFound;
+    }
+    cuuint64_t dims[2] = { (cuuint64_t)cols, (cuuint64_t)rows };
+    cuuint64_t strides[1] = { (cuuint64_t)pitch_elems * 4 };
+    cuuint32_t box[2] = { (cuuint32_t)box_cols, (cuuint32_t)box_rows };
+    cuuint32_t estr[2] = { 1, 1 };
+    CUresult r = fn(reinterpret_cast<CUtensorMap *>(tmap_out), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                    const_cast<float *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled (fp32 matrix) failed (%d): ptr=%p rows=%lld cols=%lld box=%dx%d",
+                 (int)r, (const void *)ptr, (long long)rows, (long long)cols, box_cols, box_rows);
+        return (int)cudaErrorInvalidValue;
+    }
+    return 0;
+}
+
 template <int KIND, int BN, int SWB>
 static int launch_inst(const TmapPack &tm, KernelArgs &ka, int stage_bytes, int grid, cudaStream_t stream)
 {

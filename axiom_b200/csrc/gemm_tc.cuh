@@ -45,8 +45,13 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
                    int64_t M, int64_t N, int64_t K, const TcEpilogue &ep, int *err_word,
                    int sm_count, cudaStream_t stream);
 
-// Number of kernels the last launch_gemm_tc enqueued (always 1); kept so the
-// caller can count launches without knowing the core's structure.
+// Message of the last failure in this translation unit (tensor-map encoding, launch).
 const char *gemm_tc_last_error();
+
+// Tiled tensor map (128 bytes, 64-byte aligned storage at tmap_out) over a plain
+// fp32 matrix [rows, cols] with row pitch pitch_elems; no swizzle; out-of-range
+// elements read as zero.  pitch_elems * 4 and the base must be multiples of 16 bytes.
+int encode_f32_matrix_tmap(void *tmap_out, const float *ptr, int64_t rows, int64_t cols, int64_t pitch_elems,
+                           int box_cols, int box_rows);
 
 }  // namespace axb

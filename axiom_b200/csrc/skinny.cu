@@ -171,8 +171,37 @@ static int launch_mt(const SkinnyArgs &a, bool vec, dim3 grid, size_t smem, cuda
 
 static int mt_for(int64_t M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <= 8 ? 8 : M <= 16 ? 16 : 32; }
 
-void skinny_plan(int64_t M, int64_t N, int64_t K, int sm_count, SkinnyPlan *plan)
+// The TMA-staged kernel needs what a tensor map needs: a 16-byte aligned base and row pitch.
+static void skinny_plan_tma(int64_t M, int64_t N, int64_t K, int sm_count, SkinnyPlan *plan)
 {
+    const int mt = mt_for(M);
+    const int cols = skinny_tma_strip_cols(mt), rows = skinny_tma_stage_rows(mt);
+    const int strips = (int)((N + cols - 1) / cols);
+    int64_t ksplit = (2 * (int64_t)sm_count) / strips;
+    if (ksplit < 1) ksplit = 1;
+    const int64_t max_split = (K + 4 * rows - 1) / (4 * rows);  // at least one trip round the ring
+    if (ksplit > max_split) ksplit = max_split;
+    int64_t kchunk = (K + ksplit - 1) / ksplit;
+    kchunk = (kchunk + rows - 1) / rows * rows;
+    const int64_t max_chunk = (48 * 1024) / (4 * mt) / rows * rows;  // X slice within 48 KB
+    if (kchunk > max_chunk) kchunk = max_chunk;
+    ksplit = (K + kchunk - 1) / kchunk;
+    plan->use_tma = 1;
+    plan->mt = mt;
+    plan->strips = strips;
+    plan->ksplit = (int)ksplit;
+    plan->kchunk = (int)kchunk;
+    plan->partial_floats = ksplit > 1 ? ksplit * M * N : 0;
+    plan->smem_bytes = skinny_tma_smem_bytes(mt, (int)kchunk);
+}
+
+void skinny_plan(int64_t M, int64_t N, int64_t K, const float *W, int sm_count, SkinnyPlan *plan)
+{
+    if ((N % 4 == 0) && ((reinterpret_cast<uintptr_t>(W) & 15) == 0)) {
+        skinny_plan_tma(M, N, K, sm_count, plan);
+        return;
+    }
+    plan->use_tma = 0;
     const int mt = mt_for(M);
     const int strips = (int)((N + SK_STRIP - 1) / SK_STRIP);
     int64_t ksplit = (2 * (int64_t)sm_count) / strips;
@@ -195,6 +224,7 @@ void skinny_plan(int64_t M, int64_t N, int64_t K, int sm_count, SkinnyPlan *plan
 
 int launch_skinny(const SkinnyArgs &args, const SkinnyPlan &plan, cudaStream_t st)
 {
+    if (plan.use_tma) return launch_skinny_tma(args, plan, st);
     const bool vec = (args.N % 4 == 0) && ((reinterpret_cast<uintptr_t>(args.W) & 15) == 0);
     dim3 grid((unsigned)plan.strips, (unsigned)plan.ksplit);
     switch (plan.mt) {
@@ -260,7 +290,7 @@ extern "C" int axb_skinny_gemm_static(const float *X, const float *W, const floa
         s_scratch_addr[dev] = static_cast<float *>(addr);
     }
     SkinnyPlan plan;
-    skinny_plan(M, N, K, s_sm_count[dev], &plan);
+    skinny_plan(M, N, K, W, s_sm_count[dev], &plan);
     if (plan.partial_floats > kStaticPartialFloats || plan.strips > kStaticCounters)
         return set_error(AXB_ERR_INVALID_SHAPE,
                          "skinny_gemm_static: M=%lld N=%lld K=%lld needs %lld scratch floats and %d strip counters; the built-in "
@@ -279,6 +309,7 @@ extern "C" int axb_skinny_gemm_static(const float *X, const float *W, const floa
     a.ksplit = plan.ksplit; a.kchunk = plan.kchunk;
     a.partial = plan.ksplit > 1 ? scratch : nullptr;
     a.counters = counters;
+    a.err = nullptr;
     int le = launch_skinny(a, plan, st);
     if (le) return set_error(AXB_ERR_BACKEND, "skinny_gemm_static: launch: %s", cudaGetErrorString((cudaError_t)le));
     return AXB_OK;

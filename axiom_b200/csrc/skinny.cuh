@@ -18,15 +18,23 @@ struct SkinnyArgs {
     int ksplit, kchunk;
     float *partial;     // [ksplit][M][N] scratch when ksplit > 1
     int *counters;      // [strips] zero between calls
+    int *err;           // device word that receives a code when a bounded wait runs out, or null
 };
 
 struct SkinnyPlan {
+    int use_tma;             // 1: TMA-staged kernel (skinny_tma.cu), 0: plain-load kernel (skinny.cu)
     int mt, strips, ksplit, kchunk;
     int64_t partial_floats;  // scratch the plan needs (0 when K is not split)
     size_t smem_bytes;
 };
 
-void skinny_plan(int64_t M, int64_t N, int64_t K, int sm_count, SkinnyPlan *plan);
+void skinny_plan(int64_t M, int64_t N, int64_t K, const float *W, int sm_count, SkinnyPlan *plan);
 int launch_skinny(const SkinnyArgs &args, const SkinnyPlan &plan, cudaStream_t st);
+
+// TMA-staged variant (skinny_tma.cu)
+int skinny_tma_strip_cols(int mt);
+int skinny_tma_stage_rows(int mt);
+size_t skinny_tma_smem_bytes(int mt, int kchunk);
+int launch_skinny_tma(const SkinnyArgs &args, const SkinnyPlan &plan, cudaStream_t st);
 
 }  // namespace axb

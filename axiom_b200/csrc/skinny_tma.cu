@@ -1,0 +1,246 @@
+// skinny_tma.cu — the skinny-M route with the weight stream staged by TMA.
+//
+// Same arithmetic and the same fixed-order split-K reduction as skinny.cu, but
+// W[K,N] reaches the SM through cp.async.bulk.tensor into a ring of 16 KB
+// shared-memory stages filled by one producer thread.  The copy engine keeps
+// the whole ring (64 KB per CTA) in flight no matter how many registers the
+// FMA warps hold, which is what a stream of this size needs to get near the
+// HBM rate: with plain loads the bytes in flight were capped by
+// registers x occupancy and the kernel sat at ~45% of the copy bandwidth.
+//
+//   warp 8 (one lane)  producer: box = 16 rows x 256 columns (M <= 8) or
+//                      32 rows x 128 columns (M > 8), completion on full[s]
+//   warps 0..7         consumers: warp w takes rows w, w+8, .. of a stage; a lane
+//                      reads its 4 (or 8) columns with 128-bit shared loads, X is
+//                      broadcast from shared memory, all M outputs accumulate in
+//                      registers; one arrive per warp on empty[s]
+// Rows past K and columns past N are zero-filled by the tensor map.
+#include "skinny.cuh"
+
+#include "gemm_tc.cuh"
+#include "ptx.cuh"
+
+#include <cuda.h>
+#include <stdint.h>
+
+namespace axb {
+
+static constexpr int ST_THREADS = 288;
+static constexpr int ST_CONSUMERS = 8;
+static constexpr int ST_STAGES = 4;
+static constexpr int ST_STAGE_BYTES = 16384;
+static constexpr int ST_HEADER = 128;
+
+__device__ __forceinline__ float st_gelu(float v)
+{
+    const float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+    return 0.5f * v * (1.0f + tanhf(inner));
+}
+
+__device__ __forceinline__ float st_epilogue(const SkinnyArgs &a, float v, int m, int64_t col)
+{
+    v *= a.alpha;
+    if (a.beta != 0.0f) v += a.beta * a.Y[(int64_t)m * a.N + col];
+    if (a.bias) v += __ldg(a.bias + col);
+    if (a.act == 1) v = fmaxf(v, 0.0f);
+    else if (a.act == 2) v = st_gelu(v);
+    return v;
+}
+
+template <int MT, int CPL>
+__global__ void __launch_bounds__(ST_THREADS) skinny_tma_kernel(const __grid_constant__ CUtensorMap tmW,
+                                                                const SkinnyArgs a)
+{
+    constexpr int COLS = 128 * CPL;                     // columns of a strip
+    constexpr int R = ST_STAGE_BYTES / (COLS * 4);      // rows per stage
+    constexpr int RM = MT < 8 ? MT : 8;
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __shared__ int s_last;
+    const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
+    uint8_t *gbase = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bar_full = base, bar_empty = base + 8 * ST_STAGES;
+    const uint32_t ring = base + ST_HEADER;
+    float *ring_g = reinterpret_cast<float *>(gbase + ST_HEADER);
+    float *xs = ring_g + ST_STAGES * ST_STAGE_BYTES / 4;  // [kchunk][MT]
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int strip = blockIdx.x, ks = blockIdx.y;
+    const int64_t k_begin = (int64_t)ks * a.kchunk;
+    const int kc = (int)min((int64_t)a.kchunk, a.K - k_begin);
+    const int nst = (kc + R - 1) / R;
+
+    if (tid == 0) {
+        for (int s = 0; s < ST_STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, ST_CONSUMERS);
+        }
+        mbar_fence_init();
+        tma_prefetch_desc(&tmW);
+    }
+    __syncthreads();
+
+    // the producer puts the first stages in flight before anyone touches X
+    if (warp == ST_CONSUMERS && lane == 0) {
+        for (int st = 0; st < nst && st < ST_STAGES; ++st) {
+            mbar_arrive_expect_tx(bar_full + 8 * st, ST_STAGE_BYTES);
+            tma_load_2d(ring + st * ST_STAGE_BYTES, &tmW, bar_full + 8 * st, strip * COLS, (int)(k_begin + st * R));
+        }
+    }
+    for (int i = tid; i < kc * MT; i += ST_THREADS) {
+        const int m = i / kc, kk = i - m * kc;
+        xs[kk * MT + m] = (m < a.M) ? __ldg(a.X + (int64_t)m * a.K + k_begin + kk) : 0.0f;
+    }
+    __syncthreads();
+
+    float acc[MT][4 * CPL];
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+#pragma unroll
+        for (int c = 0; c < 4 * CPL; ++c) acc[m][c] = 0.0f;
+
+    bool ok = true;
+    if (warp == ST_CONSUMERS) {
+        if (lane == 0) {
+            for (int st = ST_STAGES; st < nst; ++st) {
+                const uint32_t s = st % ST_STAGES, ph = (st / ST_STAGES) & 1u;
+                if (!mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1u)) {
+                    if (a.err) atomicCAS(a.err, 0, 11);
+                    break;
+                }
+                mbar_arrive_expect_tx(bar_full + 8 * s, ST_STAGE_BYTES);
+                tma_load_2d(ring + s * ST_STAGE_BYTES, &tmW, bar_full + 8 * s, strip * COLS, (int)(k_begin + st * R));
+            }
+        }
+    } else {
+        for (int st = 0; st < nst; ++st) {
+            const uint32_t s = st % ST_STAGES, ph = (st / ST_STAGES) & 1u;
+            const bool got = mbar_wait_bounded(bar_full + 8 * s, ph);
+            if (!__all_sync(0xffffffffu, got)) {
+                if (a.err && lane == 0) atomicCAS(a.err, 0, 12);
+                ok = false;
+                break;
+            }
+            const float *stage = ring_g + s * (ST_STAGE_BYTES / 4);
+#pragma unroll
+            for (int rr = 0; rr < R / ST_CONSUMERS; ++rr) {
+                const int r = warp + rr * ST_CONSUMERS;
+                const int kk = st * R + r;
+                if (kk < kc) {
+                    float4 w[CPL];
+#pragma unroll
+                    for (int c = 0; c < CPL; ++c)
+                        w[c] = *reinterpret_cast<const float4 *>(stage + r * COLS + c * 128 + lane * 4);
+                    const float *xr = xs + kk * MT;
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        const float xv = xr[m];
+#pragma unroll
+                        for (int c = 0; c < CPL; ++c) {
+                            acc[m][4 * c + 0] = fmaf(xv, w[c].x, acc[m][4 * c + 0]);
+                            acc[m][4 * c + 1] = fmaf(xv, w[c].y, acc[m][4 * c + 1]);
+                            acc[m][4 * c + 2] = fmaf(xv, w[c].z, acc[m][4 * c + 2]);
+                            acc[m][4 * c + 3] = fmaf(xv, w[c].w, acc[m][4 * c + 3]);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+        }
+    }
+    (void)ok;
+    __syncthreads();  // every stage consumed, no copy in flight: the ring now holds the warp sums
+
+    float *red = ring_g;  // [ST_CONSUMERS][RM][COLS]
+    float *part = a.partial ? a.partial + (int64_t)ks * a.M * a.N : nullptr;
+#pragma unroll
+    for (int m0 = 0; m0 < MT; m0 += RM) {
+        if (warp < ST_CONSUMERS) {
+#pragma unroll
+            for (int mi = 0; mi < RM; ++mi)
+#pragma unroll
+                for (int c = 0; c < CPL; ++c)
+                    *reinterpret_cast<float4 *>(red + ((warp * RM + mi) * COLS + c * 128 + lane * 4)) =
+                        make_float4(acc[m0 + mi][4 * c], acc[m0 + mi][4 * c + 1], acc[m0 + mi][4 * c + 2],
+                                    acc[m0 + mi][4 * c + 3]);
+        }
+        __syncthreads();
+        for (int o = tid; o < RM * COLS; o += ST_THREADS) {
+            const int mi = o / COLS, c = o - mi * COLS;
+            const int m = m0 + mi;
+            const int64_t gc = (int64_t)strip * COLS + c;
+            if (m < a.M && gc < a.N) {
+                float s = 0.0f;
+#pragma unroll
+                for (int w = 0; w < ST_CONSUMERS; ++w) s += red[(w * RM + mi) * COLS + c];
+                if (a.ksplit == 1) a.Y[(int64_t)m * a.N + gc] = st_epilogue(a, s, m, gc);
+                else part[(int64_t)m * a.N + gc] = s;
+            }
+        }
+        __syncthreads();
+    }
+
+    if (a.ksplit > 1) {
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const int prev = atomicAdd(a.counters + strip, 1);
+            s_last = (prev == a.ksplit - 1);
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            const int ncols = (int)min((int64_t)COLS, a.N - (int64_t)strip * COLS);
+            for (int o = tid; o < a.M * ncols; o += ST_THREADS) {
+                const int m = o / ncols;
+                const int64_t gc = (int64_t)strip * COLS + (o - m * ncols);
+                float s = 0.0f;
+                for (int q = 0; q < a.ksplit; ++q) s += __ldcg(a.partial + ((int64_t)q * a.M + m) * a.N + gc);
+                a.Y[(int64_t)m * a.N + gc] = st_epilogue(a, s, m, gc);
+            }
+            if (tid == 0) a.counters[strip] = 0;
+        }
+    }
+}
+
+template <int MT, int CPL>
+static int launch_tma_inst(const CUtensorMap &tm, const SkinnyArgs &a, dim3 grid, size_t smem, cudaStream_t st)
+{
+    auto k = skinny_tma_kernel<MT, CPL>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+        attr_set[dev] = true;
+    }
+    k<<<grid, ST_THREADS, smem, st>>>(tm, a);
+    return (int)cudaGetLastError();
+}
+
+int skinny_tma_strip_cols(int mt) { return mt <= 8 ? 256 : 128; }
+int skinny_tma_stage_rows(int mt) { return ST_STAGE_BYTES / (skinny_tma_strip_cols(mt) * 4); }
+size_t skinny_tma_smem_bytes(int mt, int kchunk)
+{
+    return (size_t)ST_HEADER + 128 + (size_t)ST_STAGES * ST_STAGE_BYTES + (size_t)kchunk * mt * 4;
+}
+
+int launch_skinny_tma(const SkinnyArgs &a, const SkinnyPlan &plan, cudaStream_t st)
+{
+    alignas(64) CUtensorMap tm;
+    const int cols = skinny_tma_strip_cols(plan.mt), rows = skinny_tma_stage_rows(plan.mt);
+    int e = encode_f32_matrix_tmap(&tm, a.W, a.K, a.N, a.N, cols, rows);
+    if (e) return e;
+    dim3 grid((unsigned)plan.strips, (unsigned)plan.ksplit);
+    const size_t smem = plan.smem_bytes;
+    switch (plan.mt) {
+    case 1: return launch_tma_inst<1, 2>(tm, a, grid, smem, st);
+    case 2: return launch_tma_inst<2, 2>(tm, a, grid, smem, st);
+    case 4: return launch_tma_inst<4, 2>(tm, a, grid, smem, st);
+    case 8: return launch_tma_inst<8, 2>(tm, a, grid, smem, st);
+    case 16: return launch_tma_inst<16, 1>(tm, a, grid, smem, st);
+    default: return launch_tma_inst<32, 1>(tm, a, grid, smem, st);
+    }
+}
+
+}  // namespace axb

@@ -299,7 +299,8 @@ SHIM_API int ref_device_sdpa_fwd(const float *Q, const float *K, const float *V,
     ax_tensor_t *k = to_dev(ax_tensor_from_array(K, sh, 3, AX_FLOAT32));
     ax_tensor_t *v = to_dev(ax_tensor_from_array(V, sh, 3, AX_FLOAT32));
     ax_tensor_t *o = to_dev(ax_tensor_from_array(Q, sh, 3, AX_FLOAT32));
-    ax_tensor_t *l = to_dev(ax_tensor_zeros(shl, 2, AX_FLOAT32));
+    /* built from host data: ax_tensor_zeros on the device would need the backend's optional fill slot */
+    ax_tensor_t *l = to_dev(ax_tensor_from_array(L, shl, 2, AX_FLOAT32));
     int rc = (!q || !k || !v || !o || !l) ? 100 : 0;
     if (!rc)
         rc = (int)ext->sdpa_fwd(tdata(q), tdata(k), tdata(v), tdata(o), tdata(l), BH, S, dk, scale, causal != 0, NULL);
