@@ -317,9 +317,40 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
             state["i"] += 1
         step_ms, core_ms, _ = core_time(sk, 64, 8)
         nbytes = n * n * 4 + 2 * M * n * 4 + n * 4
-        gbs = nbytes / (core_ms * 1e-3) / 1e9
+        # A ~10 us kernel is launch-bound when driven call by call from Python, so the kernel's own
+        # duration is taken from a CUDA graph of 64 calls (rotating weights) replayed on a side stream.
+        graph_ms = None
+        try:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            eng.set_stream(side.cuda_stream)
+            with torch.cuda.stream(side):
+                sk()
+                side.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    for _ in range(64):
+                        sk()
+                for _ in range(3):
+                    g.replay()
+                side.synchronize()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(side)
+                for _ in range(4):
+                    g.replay()
+                e1.record(side)
+                side.synchronize()
+                graph_ms = e0.elapsed_time(e1) / (4 * 64)
+        except Exception as exc:  # capture is an optimisation of the measurement, not of the product
+            sys.stderr.write(f"bench: graph timing unavailable ({exc})\n")
+        finally:
+            eng.set_stream(0)
+            torch.cuda.synchronize()
+        kern_ms = graph_ms if graph_ms else core_ms
+        gbs = nbytes / (kern_ms * 1e-3) / 1e9
         out.append({"workload": f"skinny-M dense+bias+GELU, x[{M}x4096].W[4096x4096]", "value": nbytes / (step_ms * 1e-3) / 1e9,
-                    "unit": "GB/s", "ms_per_step": step_ms, "kernel_ms": core_ms,
+                    "unit": "GB/s", "ms_per_step": step_ms, "kernel_ms": kern_ms, "kernel_ms_eager_events": core_ms,
+                    "timing": "kernel_ms: mean over a replayed CUDA graph of 64 calls; value/ms_per_step: eager calls from Python",
                     "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "frac": gbs / hbm,
                                  "peak_source": f"{peaks['source']} HBM copy bandwidth"}})
     del Ws
