@@ -86,17 +86,26 @@ __global__ void __launch_bounds__(ST_THREADS) skinny_tma_kernel(const __grid_con
             tma_load_2d(ring + st * ST_STAGE_BYTES, &tmW, bar_full + 8 * st, strip * COLS, (int)(k_begin + st * R));
         }
     }
-    for (int i = tid; i < kc * MT; i += ST_THREADS) {
-        const int m = i / kc, kk = i - m * kc;
-        xs[kk * MT + m] = (m < a.M) ? __ldg(a.X + (int64_t)m * a.K + k_begin + kk) : 0.0f;
+    // X slice -> shared as [k][MT]; for MT >= 8 the float4 groups of a row are XOR-permuted with k so
+    // the transposing stores spread over the banks (a lane stores one k, lanes differ in k)
+    for (int kk = tid; kk < kc; kk += ST_THREADS) {
+        const int swz = MT >= 4 ? ((kk & 7) & (MT / 4 - 1)) : 0;
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+            const float v = (m < a.M) ? __ldg(a.X + (int64_t)m * a.K + k_begin + kk) : 0.0f;
+            const int pm = MT >= 4 ? ((((m >> 2) ^ swz) << 2) | (m & 3)) : m;
+            xs[kk * MT + pm] = v;
+        }
     }
     __syncthreads();
 
-    float acc[MT][4 * CPL];
+    // accumulators: rows m = 2p and 2p+1 share one packed register pair, so one fma.rn.f32x2 feeds both
+    constexpr int MP = MT >= 2 ? MT / 2 : 1;
+    float2 acc[MP][4 * CPL];
 #pragma unroll
-    for (int m = 0; m < MT; ++m)
+    for (int p = 0; p < MP; ++p)
 #pragma unroll
-        for (int c = 0; c < 4 * CPL; ++c) acc[m][c] = 0.0f;
+        for (int c = 0; c < 4 * CPL; ++c) acc[p][c] = make_float2(0.0f, 0.0f);
 
     bool ok = true;
     if (warp == ST_CONSUMERS) {
@@ -131,15 +140,40 @@ __global__ void __launch_bounds__(ST_THREADS) skinny_tma_kernel(const __grid_con
                     for (int c = 0; c < CPL; ++c)
                         w[c] = *reinterpret_cast<const float4 *>(stage + r * COLS + c * 128 + lane * 4);
                     const float *xr = xs + kk * MT;
-#pragma unroll
-                    for (int m = 0; m < MT; ++m) {
-                        const float xv = xr[m];
+                    if constexpr (MT == 1) {
+                        const float xv = xr[0];
 #pragma unroll
                         for (int c = 0; c < CPL; ++c) {
-                            acc[m][4 * c + 0] = fmaf(xv, w[c].x, acc[m][4 * c + 0]);
-                            acc[m][4 * c + 1] = fmaf(xv, w[c].y, acc[m][4 * c + 1]);
-                            acc[m][4 * c + 2] = fmaf(xv, w[c].z, acc[m][4 * c + 2]);
-                            acc[m][4 * c + 3] = fmaf(xv, w[c].w, acc[m][4 * c + 3]);
+                            acc[0][4 * c + 0].x = fmaf(xv, w[c].x, acc[0][4 * c + 0].x);
+                            acc[0][4 * c + 1].x = fmaf(xv, w[c].y, acc[0][4 * c + 1].x);
+                            acc[0][4 * c + 2].x = fmaf(xv, w[c].z, acc[0][4 * c + 2].x);
+                            acc[0][4 * c + 3].x = fmaf(xv, w[c].w, acc[0][4 * c + 3].x);
+                        }
+                    } else {
+                        float2 wd[4 * CPL];  // each weight duplicated into both halves of a pair
+#pragma unroll
+                        for (int c = 0; c < CPL; ++c) {
+                            wd[4 * c + 0] = make_float2(w[c].x, w[c].x);
+                            wd[4 * c + 1] = make_float2(w[c].y, w[c].y);
+                            wd[4 * c + 2] = make_float2(w[c].z, w[c].z);
+                            wd[4 * c + 3] = make_float2(w[c].w, w[c].w);
+                        }
+                        if constexpr (MT == 2) {
+                            const float2 xp = *reinterpret_cast<const float2 *>(xr);
+#pragma unroll
+                            for (int c = 0; c < 4 * CPL; ++c) acc[0][c] = __ffma2_rn(xp, wd[c], acc[0][c]);
+                        } else {
+                            const int swz = (kk & 7) & (MT / 4 - 1);
+#pragma unroll
+                            for (int g = 0; g < MT / 4; ++g) {
+                                const float4 x4 = *reinterpret_cast<const float4 *>(xr + ((g ^ swz) << 2));
+                                const float2 x01 = make_float2(x4.x, x4.y), x23 = make_float2(x4.z, x4.w);
+#pragma unroll
+                                for (int c = 0; c < 4 * CPL; ++c) {
+                                    acc[2 * g][c] = __ffma2_rn(x01, wd[c], acc[2 * g][c]);
+                                    acc[2 * g + 1][c] = __ffma2_rn(x23, wd[c], acc[2 * g + 1][c]);
+                                }
+                            }
                         }
                     }
                 }
@@ -160,9 +194,14 @@ __global__ void __launch_bounds__(ST_THREADS) skinny_tma_kernel(const __grid_con
             for (int mi = 0; mi < RM; ++mi)
 #pragma unroll
                 for (int c = 0; c < CPL; ++c)
+                {
+                    const int m = m0 + mi;
+                    const float2 *row = acc[MT >= 2 ? m / 2 : 0];
+                    const bool hi = (m & 1) != 0;
                     *reinterpret_cast<float4 *>(red + ((warp * RM + mi) * COLS + c * 128 + lane * 4)) =
-                        make_float4(acc[m0 + mi][4 * c], acc[m0 + mi][4 * c + 1], acc[m0 + mi][4 * c + 2],
-                                    acc[m0 + mi][4 * c + 3]);
+                        hi ? make_float4(row[4 * c].y, row[4 * c + 1].y, row[4 * c + 2].y, row[4 * c + 3].y)
+                           : make_float4(row[4 * c].x, row[4 * c + 1].x, row[4 * c + 2].x, row[4 * c + 3].x);
+                }
         }
         __syncthreads();
         for (int o = tid; o < RM * COLS; o += ST_THREADS) {
