@@ -24,66 +24,15 @@
 // the CTAs running at one time share operand panels in L2.  Edge tiles rely
 // on TMA zero fill for loads and on masking for stores.
 #include "gemm_tc.cuh"
+#include "gemm_tc_internal.cuh"
 #include "ptx.cuh"
 
 #include <cuda.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 namespace axb {
-
-static constexpr int BM = 128;
-static constexpr int GROUP_M = 16;
-static constexpr int NUM_THREADS = 320;  // producer warp, MMA warp, 8 epilogue warps
-static constexpr int HEADER_BYTES = 1024;
-static constexpr int MAX_STAGES = 8;
-static constexpr int SMEM_BUDGET = 227 * 1024;
-
-struct alignas(64) TmapPack {
-    CUtensorMap a[TC_MAX_PLANES];
-    CUtensorMap b[TC_MAX_PLANES];
-};
-
-struct KernelArgs {
-    int M, N, K;
-    int npa, npb, nprod;
-    int8_t pa[TC_MAX_PRODUCTS], pb[TC_MAX_PRODUCTS];
-    int m_tiles, n_tiles, k_blocks, stages;
-    int chunk_kb;  // k-blocks accumulated in TMEM before the epilogue warps drain them
-    float alpha, beta;
-    const float *bias;
-    const float *colscale;
-    int act, out_mode;
-    void *C;
-    int32_t *acc_out;
-    long long ldc;
-    int *err;
-};
-
-// error words written to *err (first writer wins)
-enum { ERR_PRODUCER_WAIT = 1, ERR_MMA_WAIT_FULL = 2, ERR_MMA_WAIT_TMEM = 3, ERR_EPI_WAIT = 4 };
-
-__device__ __forceinline__ void report(int *err, int code)
-{
-    if (err) atomicCAS(err, 0, code);
-}
-
-__device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int &mt, int &nt)
-{
-    const int per_group = GROUP_M * n_tiles;
-    const int g = t / per_group;
-    const int first_m = g * GROUP_M;
-    const int gm = min(GROUP_M, m_tiles - first_m);
-    const int r = t - g * per_group;
-    mt = first_m + r % gm;
-    nt = r / gm;
-}
-
-__device__ __forceinline__ float gelu_tanh(float v)
-{
-    const float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
-    return 0.5f * v * (1.0f + tanhf(inner));
-}
 
 template <int KIND, int BN, int SWB>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
@@ -491,12 +440,21 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
     }
     // Column-tile width: the widest that still gives every SM a tile; small
     // problems take narrower tiles so more SMs take part.
-    const int64_t mt = (M + BM - 1) / BM;
+    int64_t mt = (M + BM - 1) / BM;
     int bn = 256;
     if (mt * ((N + 255) / 256) < sm_count) bn = 128;
     if (bn == 128 && mt * ((N + 127) / 128) < sm_count) bn = 64;
     if (N <= 64) bn = 64;
     else if (N <= 128 && bn > 128) bn = 128;
+    // CTA pairs (256 x 256 tiles, gemm_tc2.cu) when there are enough such tiles to fill the machine
+    static const int pair_env = [] { const char *e = getenv("AX_B200_PAIR"); return e ? atoi(e) : -1; }();
+    bool use_pair = ((M + 255) / 256) * ((N + 255) / 256) >= sm_count / 2 && N >= 256 && M >= 256;
+    if (pair_env == 0) use_pair = false;
+    if (pair_env == 1 && N >= 256 && M >= 256) use_pair = true;
+    if (use_pair) {
+        bn = 256;
+        mt = (M + 255) / 256;
+    }
     const int64_t nt = (N + bn - 1) / bn;
     // Swizzle width: 64-byte rows halve the stage so the split-precision modes
     // (four planes per stage) still get a four-deep ring.
@@ -512,7 +470,7 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
         if (e) return e;
     }
     for (int i = 0; i < B.nplanes; ++i) {
-        int e = encode_plane(&tm.b[i], kind, B.plane[i], N, K, B.pitch_elems, bn, swb);
+        int e = encode_plane(&tm.b[i], kind, B.plane[i], N, K, B.pitch_elems, use_pair ? bn / 2 : bn, swb);
         if (e) return e;
     }
     KernelArgs ka;
@@ -533,6 +491,8 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
     ka.ldc = ep.ldc; ka.err = err_word;
     const int64_t tiles = mt * nt;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
+    if (use_pair)
+        return launch_gemm_tc_pair(kind, swb, tm, ka, A.nplanes, B.nplanes, sm_count, stream, g_err, sizeof g_err);
 
     if (kind == KIND_TF32)
         return swb == 128 ? launch_bn<KIND_TF32, 128>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream)

@@ -1,0 +1,374 @@
+// gemm_tc2.cu — the tcgen05 GEMM core on CTA pairs (cta_group::2).
+//
+// Same contract as gemm_tc.cu, but a cluster of two CTAs computes one
+// 256 x 256 output tile with MMAs of M = 256: each CTA stages ITS 128 rows of
+// the A tile and ITS 128 rows of the B tile, and holds its 128 accumulator
+// rows in its own TMEM.  Per SM this halves the shared-memory traffic of the B
+// operand (both the TMA writes and the tensor-core reads), which is what
+// limits the single-CTA kernel on int8 and bf16.
+//
+//   both CTAs, warp 0   TMA producer for the CTA's own halves; the byte counts
+//                       of both CTAs land on the LEADER's full[s] barrier
+//   leader, warp 1      issues tcgen05.mma.cta_group::2; tcgen05.commit with a
+//                       two-CTA mask frees stage s in both CTAs and publishes
+//                       the accumulator to both epilogues
+//   both CTAs, warps 2..9  epilogue over the CTA's own 128 rows; accumulator
+//                       release is an arrive on the leader's barrier (remote for
+//                       the peer CTA)
+// No multicast copies are used: every CTA fetches its own operand tiles.
+#include "gemm_tc.cuh"
+#include "gemm_tc_internal.cuh"
+#include "ptx.cuh"
+
+#include <cuda.h>
+#include <stdio.h>
+
+namespace axb {
+
+static constexpr int PAIR_BN = 256;
+static constexpr int PAIR_TILE_M = 256;
+
+template <int KIND, int SWB>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
+{
+    constexpr int BN = PAIR_BN;
+    constexpr int A_BYTES = BM * SWB;          // this CTA's 128 rows of an A plane
+    constexpr int B_BYTES = (BN / 2) * SWB;    // this CTA's 128 rows of a B plane
+    constexpr int ES = KIND == KIND_TF32 ? 4 : (KIND == KIND_BF16 ? 2 : 1);
+    constexpr int BKE = SWB / ES;
+    constexpr int KSTEPS = SWB / 32;
+    constexpr int TMEM_COLS = 2 * BN;
+    constexpr uint32_t IDESC = make_idesc<KIND>(PAIR_TILE_M, BN);
+
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t *gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bar_full = base;            // leader's copy is the one in use
+    const uint32_t bar_empty = base + 64;      // one per CTA, freed by the two-CTA commit
+    const uint32_t bar_tfull = base + 128;     // one per CTA
+    const uint32_t bar_tempty = base + 144;    // leader's copy is the one in use (16 arrivals)
+    const uint32_t tmem_slot = base + 160;
+    const uint32_t stage0 = base + HEADER_BYTES;
+    const int stage_bytes = p.npa * A_BYTES + p.npb * B_BYTES;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int total_tiles = p.m_tiles * p.n_tiles;   // 256-row tiles
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(bar_tfull + 8 * a, 1);
+            mbar_init(bar_tempty + 8 * a, 16);
+        }
+        mbar_fence_init();
+        for (int i = 0; i < p.npa; ++i) tma_prefetch_desc(&tm.a[i]);
+        for (int i = 0; i < p.npb; ++i) tma_prefetch_desc(&tm.b[i]);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();   // both CTAs' barriers exist before anyone signals across the pair
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(gen_base + 160);
+
+    if (warp == 0) {
+        // ------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = pair; t < total_tiles && ok; t += npairs) {
+                int mt, nt;
+                tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
+                const int row_a = mt * PAIR_TILE_M + (int)rank * BM;
+                const int row_b = nt * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                    if (!mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1u)) {
+                        report(p.err, ERR_PRODUCER_WAIT);
+                        ok = false;
+                        break;
+                    }
+                    // the leader's barrier collects the bytes of both CTAs
+                    const uint32_t fb = map_to_cta(bar_full + 8 * s, 0);
+                    if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, 2u * (uint32_t)stage_bytes);
+                    uint32_t dst = stage0 + s * stage_bytes;
+                    for (int i = 0; i < p.npa; ++i, dst += A_BYTES)
+                        tma_load_2d_pair(dst, &tm.a[i], fb, kb * BKE, row_a);
+                    for (int i = 0; i < p.npb; ++i, dst += B_BYTES)
+                        tma_load_2d_pair(dst, &tm.b[i], fb, kb * BKE, row_b);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------- MMA issuer
+        if (leader && lane == 0) {
+            uint32_t it = 0, vt = 0;
+            bool ok = true;
+            for (int t = pair; t < total_tiles && ok; t += npairs) {
+                for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += p.chunk_kb, ++vt) {
+                    const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
+                    if (!mbar_wait_bounded(bar_tempty + 8 * acc, aph ^ 1u)) {
+                        report(p.err, ERR_MMA_WAIT_TMEM);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t d_tmem = tmem_base + acc * BN;
+                    const int kb1 = min(p.k_blocks, kb0 + p.chunk_kb);
+                    for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                        const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                        if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
+                            report(p.err, ERR_MMA_WAIT_FULL);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after_sync();
+                        const uint32_t sa = stage0 + s * stage_bytes;
+                        const uint32_t sb = sa + p.npa * A_BYTES;
+                        for (int pr = 0; pr < p.nprod; ++pr) {
+                            const uint64_t da = smem_desc_kmajor(sa + p.pa[pr] * A_BYTES, SWB);
+                            const uint64_t db = smem_desc_kmajor(sb + p.pb[pr] * B_BYTES, SWB);
+#pragma unroll
+                            for (int ks = 0; ks < KSTEPS; ++ks)
+                                tc_mma_pair<KIND>(d_tmem, da + 2u * ks, db + 2u * ks, IDESC,
+                                                  (uint32_t)(((kb - kb0) | pr | ks) != 0));
+                        }
+                        tc_commit_pair(bar_empty + 8 * s, 0x3);
+                    }
+                    if (ok) tc_commit_pair(bar_tfull + 8 * acc, 0x3);
+                }
+            }
+        }
+    } else {
+        // ---------------------------------------------------------- epilogue
+        constexpr int HALF = BN / 2;
+        constexpr int PIECES = HALF / 32;
+        const int q = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int nchunks = (p.k_blocks + p.chunk_kb - 1) / p.chunk_kb;
+        uint32_t vt = 0;
+        bool alive = true;
+        for (int t = pair; t < total_tiles && alive; t += npairs) {
+            int mt, nt;
+            tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
+            const long long row = (long long)mt * PAIR_TILE_M + (long long)rank * BM + q * 32 + lane;
+            const bool row_ok = row < p.M;
+            const int col_base = nt * BN + half * HALF;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + half * HALF;
+
+            if constexpr (KIND == KIND_I8) {
+                const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
+                ++vt;
+                const bool got = mbar_wait_bounded(bar_tfull + 8 * acc, aph);
+                if (!__all_sync(0xffffffffu, got)) {
+                    report(p.err, ERR_EPI_WAIT);
+                    alive = false;
+                    break;
+                }
+                tc_fence_after_sync();
+#pragma unroll 1
+                for (int c = 0; c < PIECES; ++c) {
+                    const int col0 = col_base + c * 32;
+                    if (col0 >= p.N) break;
+                    uint32_t r[32];
+                    __syncwarp();
+                    tmem_ld_32x32(lane_addr + acc * BN + c * 32, r);
+                    tmem_ld_wait();
+                    const bool full = col0 + 32 <= p.N;
+                    if (row_ok) {
+                        if (p.acc_out) {
+                            int32_t *dst = p.acc_out + row * p.ldc + col0;
+                            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 4)
+                                    *reinterpret_cast<int4 *>(dst + j) =
+                                        make_int4((int)r[j], (int)r[j + 1], (int)r[j + 2], (int)r[j + 3]);
+                            } else {
+                                for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = (int32_t)r[j];
+                            }
+                        }
+                        if (p.out_mode == OUT_I8_REQUANT) {
+                            int8_t *dst = reinterpret_cast<int8_t *>(p.C) + row * p.ldc + col0;
+                            uint32_t packed[8];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const float mult = (col0 + j < p.N) ? __ldg(p.colscale + col0 + j) : 0.0f;
+                                const float y = __fmul_rn(__int2float_rn((int32_t)r[j]), mult);
+                                int v = __float2int_rn(y);
+                                v = max(-127, min(127, v));
+                                if ((j & 3) == 0) packed[j >> 2] = 0;
+                                packed[j >> 2] |= (uint32_t)(v & 0xff) << (8 * (j & 3));
+                            }
+                            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+                                *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                                *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+                            } else {
+                                for (int j = 0; j < 32 && col0 + j < p.N; ++j)
+                                    dst[j] = (int8_t)((packed[j >> 2] >> (8 * (j & 3))) & 0xff);
+                            }
+                        }
+                    }
+                }
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    if (leader) mbar_arrive(bar_tempty + 8 * acc);
+                    else mbar_arrive_cluster(map_to_cta(bar_tempty + 8 * acc, 0));
+                }
+            } else {
+                float sum[HALF];
+#pragma unroll
+                for (int j = 0; j < HALF; ++j) sum[j] = 0.0f;
+                for (int ch = 0; ch < nchunks; ++ch, ++vt) {
+                    const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
+                    const bool got = mbar_wait_bounded(bar_tfull + 8 * acc, aph);
+                    if (!__all_sync(0xffffffffu, got)) {
+                        report(p.err, ERR_EPI_WAIT);
+                        alive = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+#pragma unroll
+                    for (int c = 0; c < PIECES; ++c) {
+                        uint32_t r[32];
+                        tmem_ld_32x32(lane_addr + acc * BN + c * 32, r);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) sum[c * 32 + j] += __uint_as_float(r[j]);
+                    }
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (leader) mbar_arrive(bar_tempty + 8 * acc);
+                        else mbar_arrive_cluster(map_to_cta(bar_tempty + 8 * acc, 0));
+                    }
+                }
+                if (!alive) break;
+                if (row_ok) {
+#pragma unroll
+                    for (int c = 0; c < PIECES; ++c) {
+                        const int col0 = col_base + c * 32;
+                        if (col0 < p.N) {
+                            const bool full = col0 + 32 <= p.N;
+                            float *dst = reinterpret_cast<float *>(p.C) + row * p.ldc + col0;
+                            const bool vec = full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
+                            float v[32];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                const bool in = full || (col0 + j < p.N);
+                                float x = sum[c * 32 + j] * p.alpha;
+                                if (p.colscale) x *= in ? __ldg(p.colscale + col0 + j) : 0.0f;
+                                if (p.beta != 0.0f) x += p.beta * (in ? dst[j] : 0.0f);
+                                if (p.bias) x += in ? __ldg(p.bias + col0 + j) : 0.0f;
+                                if (p.act == ACT_RELU) x = fmaxf(x, 0.0f);
+                                else if (p.act == ACT_GELU) x = gelu_tanh(x);
+                                v[j] = x;
+                            }
+                            if (vec) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 4)
+                                    *reinterpret_cast<float4 *>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j)
+                                    if (col0 + j < p.N) dst[j] = v[j];
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    if (p.err && *reinterpret_cast<volatile int *>(p.err) != 0) {
+        const uint64_t t0 = global_timer_ns();
+        while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();   // the peer's shared memory and barriers stay alive until both CTAs are done
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after_sync();
+        tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
+template <int KIND, int SWB>
+static int launch_pair_inst(const TmapPack &tm, KernelArgs &ka, int npa, int npb, int sm_count, cudaStream_t stream,
+                            char *err, size_t err_len)
+{
+    const int stage_bytes = npa * BM * SWB + npb * (PAIR_BN / 2) * SWB;
+    int stages = (SMEM_BUDGET - HEADER_BYTES - 1024) / stage_bytes;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages < 2) {
+        snprintf(err, err_len, "pair kernel: stage of %d bytes leaves fewer than 2 pipeline stages", stage_bytes);
+        return (int)cudaErrorInvalidConfiguration;
+    }
+    ka.stages = stages;
+    const int smem = HEADER_BYTES + 1024 + stages * stage_bytes;
+    auto kern = gemm_tc_pair_kernel<KIND, SWB>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET);
+        if (e != cudaSuccess) {
+            snprintf(err, err_len, "pair kernel: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+            return (int)e;
+        }
+        attr_set = true;
+    }
+    // how many CTA pairs the device can hold at once (an SM without a free partner in its
+    // cluster-scheduling group cannot host half a pair): persistent grid = that many pairs
+    static int resident_pairs = 0;
+    if (resident_pairs == 0) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(sm_count / 2 * 2));
+        cfg.blockDim = dim3(NUM_THREADS);
+        cfg.dynamicSmemBytes = (size_t)smem;
+        cudaLaunchAttribute at;
+        at.id = cudaLaunchAttributeClusterDimension;
+        at.val.clusterDim.x = 2;
+        at.val.clusterDim.y = 1;
+        at.val.clusterDim.z = 1;
+        cfg.attrs = &at;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) == cudaSuccess && n > 0) resident_pairs = n;
+        else resident_pairs = sm_count / 2;
+        (void)cudaGetLastError();
+    }
+    const long long tiles = (long long)ka.m_tiles * ka.n_tiles;
+    long long pairs = resident_pairs;
+    if (pairs > sm_count / 2) pairs = sm_count / 2;
+    if (pairs > tiles) pairs = tiles;
+    kern<<<(unsigned)(2 * pairs), NUM_THREADS, smem, stream>>>(tm, ka);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) snprintf(err, err_len, "pair kernel launch: %s", cudaGetErrorString(e));
+    return (int)e;
+}
+
+int launch_gemm_tc_pair(int kind, int swb, const TmapPack &tm, KernelArgs &ka, int npa, int npb, int sm_count,
+                        cudaStream_t stream, char *err, size_t err_len)
+{
+    if (kind == KIND_TF32)
+        return swb == 128 ? launch_pair_inst<KIND_TF32, 128>(tm, ka, npa, npb, sm_count, stream, err, err_len)
+                          : launch_pair_inst<KIND_TF32, 64>(tm, ka, npa, npb, sm_count, stream, err, err_len);
+    if (kind == KIND_BF16)
+        return swb == 128 ? launch_pair_inst<KIND_BF16, 128>(tm, ka, npa, npb, sm_count, stream, err, err_len)
+                          : launch_pair_inst<KIND_BF16, 64>(tm, ka, npa, npb, sm_count, stream, err, err_len);
+    return launch_pair_inst<KIND_I8, 128>(tm, ka, npa, npb, sm_count, stream, err, err_len);
+}
+
+}  // namespace axb

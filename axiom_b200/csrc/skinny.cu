@@ -183,7 +183,7 @@ static void skinny_plan_tma(int64_t M, int64_t N, int64_t K, int sm_count, Skinn
     if (ksplit > max_split) ksplit = max_split;
     int64_t kchunk = (K + ksplit - 1) / ksplit;
     kchunk = (kchunk + rows - 1) / rows * rows;
-    const int64_t max_chunk = (48 * 1024) / (4 * mt) / rows * rows;  // X slice within 48 KB
+    const int64_t max_chunk = (64 * 1024) / (4 * mt) / rows * rows;  // X slice within 64 KB
     if (kchunk > max_chunk) kchunk = max_chunk;
     ksplit = (K + kchunk - 1) / kchunk;
     plan->use_tma = 1;

@@ -250,7 +250,7 @@ static int launch_tma_inst(const CUtensorMap &tm, const SkinnyArgs &a, dim3 grid
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
         attr_set[dev] = true;
     }
     k<<<grid, ST_THREADS, smem, st>>>(tm, a);
