@@ -34,7 +34,7 @@
 
 namespace axb {
 
-template <int KIND, int BN, int SWB>
+template <int KIND, int BN, int SWB, int NPROD>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
 {
@@ -99,6 +99,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                         break;
                     }
                     const uint32_t fb = bar_full + 8 * s;
+                    if (p.dbg & 1) { mbar_arrive(fb); continue; }
                     mbar_arrive_expect_tx(fb, (uint32_t)stage_bytes);
                     uint32_t dst = stage0 + s * stage_bytes;
                     for (int i = 0; i < p.npa; ++i, dst += A_BYTES)
@@ -118,10 +119,15 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
         // inside the fp32 tolerance for any K.  Integer and plain bf16 runs use
         // a single chunk.
         if (lane == 0) {
-            uint32_t it = 0, vt = 0;
+            uint32_t s = 0, ph = 0, vt = 0;
             bool ok = true;
+            // everything the issue loop needs lives in registers
+            const int k_blocks = p.k_blocks, chunk_kb = p.chunk_kb, stages = p.stages;
+            const uint32_t prod_a = p.prod_a, prod_b = p.prod_b;
+            const uint64_t desc_hi = smem_desc_kmajor(0, SWB);
+            const uint32_t npa_bytes = p.npa * A_BYTES, sbytes = (uint32_t)stage_bytes;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += p.chunk_kb, ++vt) {
+                for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += chunk_kb, ++vt) {
                     const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
                     if (!mbar_wait_bounded(bar_tempty + 8 * acc, aph ^ 1u)) {
                         report(p.err, ERR_MMA_WAIT_TMEM);
@@ -130,26 +136,22 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                     }
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + acc * BN;
-                    const int kb1 = min(p.k_blocks, kb0 + p.chunk_kb);
-                    for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                        const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                    const int kb1 = min(k_blocks, kb0 + chunk_kb);
+                    for (int kb = kb0; kb < kb1; ++kb) {
                         if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
                             report(p.err, ERR_MMA_WAIT_FULL);
                             ok = false;
                             break;
                         }
                         tc_fence_after_sync();
-                        const uint32_t sa = stage0 + s * stage_bytes;
-                        const uint32_t sb = sa + p.npa * A_BYTES;
-                        for (int pr = 0; pr < p.nprod; ++pr) {
-                            const uint64_t da = smem_desc_kmajor(sa + p.pa[pr] * A_BYTES, SWB);
-                            const uint64_t db = smem_desc_kmajor(sb + p.pb[pr] * B_BYTES, SWB);
-#pragma unroll
-                            for (int ks = 0; ks < KSTEPS; ++ks)
-                                tc_mma<KIND>(d_tmem, da + 2u * ks, db + 2u * ks, IDESC,
-                                             (uint32_t)(((kb - kb0) | pr | ks) != 0));
-                        }
+                        const uint32_t sa = stage0 + s * sbytes;
+                        issue_stage_mmas<KIND, SWB, NPROD, false, A_BYTES, B_BYTES>(
+                            d_tmem, sa, sa + npa_bytes, prod_a, prod_b, desc_hi, IDESC, kb == kb0);
                         tc_commit(bar_empty + 8 * s);
+                        if (++s == (uint32_t)stages) {
+                            s = 0;
+                            ph ^= 1u;
+                        }
                     }
                     if (ok) tc_commit(bar_tfull + 8 * acc);
                 }
@@ -390,18 +392,20 @@ int encode_f32_matrix_tmap(void *tmap_out, const float *ptr, int64_t rows, int64
     return 0;
 }
 
-template <int KIND, int BN, int SWB>
+template <int KIND, int BN, int SWB, int NPROD>
 static int launch_inst(const TmapPack &tm, KernelArgs &ka, int stage_bytes, int grid, cudaStream_t stream)
 {
     int stages = (SMEM_BUDGET - HEADER_BYTES - 1024) / stage_bytes;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
+    static const int stages_env = [] { const char *e = getenv("AX_B200_STAGES"); return e ? atoi(e) : 0; }();
+    if (stages_env >= 2 && stages_env < stages) stages = stages_env;
     if (stages < 2) {
         snprintf(g_err, sizeof g_err, "stage of %d bytes leaves fewer than 2 pipeline stages", stage_bytes);
         return (int)cudaErrorInvalidConfiguration;
     }
     ka.stages = stages;
     const int smem = HEADER_BYTES + 1024 + stages * stage_bytes;
-    auto kern = gemm_tc_kernel<KIND, BN, SWB>;
+    auto kern = gemm_tc_kernel<KIND, BN, SWB, NPROD>;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET);
@@ -417,14 +421,14 @@ static int launch_inst(const TmapPack &tm, KernelArgs &ka, int stage_bytes, int 
     return (int)e;
 }
 
-template <int KIND, int SWB>
+template <int KIND, int SWB, int NPROD>
 static int launch_bn(int bn, const TmapPack &tm, KernelArgs &ka, int npa, int npb, int grid, cudaStream_t st)
 {
     const int sb = npa * BM * SWB + npb * bn * SWB;
     switch (bn) {
-    case 256: return launch_inst<KIND, 256, SWB>(tm, ka, sb, grid, st);
-    case 128: return launch_inst<KIND, 128, SWB>(tm, ka, sb, grid, st);
-    default: return launch_inst<KIND, 64, SWB>(tm, ka, sb, grid, st);
+    case 256: return launch_inst<KIND, 256, SWB, NPROD>(tm, ka, sb, grid, st);
+    case 128: return launch_inst<KIND, 128, SWB, NPROD>(tm, ka, sb, grid, st);
+    default: return launch_inst<KIND, 64, SWB, NPROD>(tm, ka, sb, grid, st);
     }
 }
 
@@ -446,6 +450,8 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
     if (bn == 128 && mt * ((N + 127) / 128) < sm_count) bn = 64;
     if (N <= 64) bn = 64;
     else if (N <= 128 && bn > 128) bn = 128;
+    static const int bn_env = [] { const char *e = getenv("AX_B200_BN"); return e ? atoi(e) : 0; }();
+    if (bn_env == 64 || bn_env == 128 || bn_env == 256) bn = bn_env;
     // CTA pairs (256 x 256 tiles, gemm_tc2.cu) when there are enough such tiles to fill the machine
     static const int pair_env = [] { const char *e = getenv("AX_B200_PAIR"); return e ? atoi(e) : -1; }();
     bool use_pair = ((M + 255) / 256) * ((N + 255) / 256) >= sm_count / 2 && N >= 256 && M >= 256;
@@ -459,7 +465,8 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
     // Swizzle width: 64-byte rows halve the stage so the split-precision modes
     // (four planes per stage) still get a four-deep ring.
     const int planes = A.nplanes + B.nplanes;
-    const int swb = (kind != KIND_I8 && planes > 2) ? 64 : 128;
+    const int swb = (kind != KIND_I8 && prod.n > 1) ? 64 : 128;
+    (void)planes;
     const int es = kind == KIND_TF32 ? 4 : (kind == KIND_BF16 ? 2 : 1);
     const int bke = swb / es;
 
@@ -477,7 +484,10 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
     memset(&ka, 0, sizeof ka);
     ka.M = (int)M; ka.N = (int)N; ka.K = (int)K;
     ka.npa = A.nplanes; ka.npb = B.nplanes; ka.nprod = prod.n;
-    for (int i = 0; i < prod.n; ++i) { ka.pa[i] = prod.a[i]; ka.pb[i] = prod.b[i]; }
+    for (int i = 0; i < prod.n; ++i) {
+        ka.prod_a |= (uint32_t)(prod.a[i] & 15) << (4 * i);
+        ka.prod_b |= (uint32_t)(prod.b[i] & 15) << (4 * i);
+    }
     ka.m_tiles = (int)mt; ka.n_tiles = (int)nt;
     ka.k_blocks = (int)((K + bke - 1) / bke);
     ka.chunk_kb = ka.k_blocks;
@@ -489,18 +499,25 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
     ka.alpha = ep.alpha; ka.beta = ep.beta; ka.bias = ep.bias; ka.colscale = ep.colscale;
     ka.act = ep.act; ka.out_mode = ep.out_mode; ka.C = ep.C; ka.acc_out = ep.acc_out;
     ka.ldc = ep.ldc; ka.err = err_word;
+    static const int dbg_env = [] { const char *e = getenv("AX_B200_DBG"); return e ? atoi(e) : 0; }();
+    ka.dbg = dbg_env;
     const int64_t tiles = mt * nt;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
     if (use_pair)
-        return launch_gemm_tc_pair(kind, swb, tm, ka, A.nplanes, B.nplanes, sm_count, stream, g_err, sizeof g_err);
+        return launch_gemm_tc_pair(kind, swb, prod.n, tm, ka, A.nplanes, B.nplanes, sm_count, stream, g_err, sizeof g_err);
 
-    if (kind == KIND_TF32)
-        return swb == 128 ? launch_bn<KIND_TF32, 128>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream)
-                          : launch_bn<KIND_TF32, 64>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream);
-    if (kind == KIND_BF16)
-        return swb == 128 ? launch_bn<KIND_BF16, 128>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream)
-                          : launch_bn<KIND_BF16, 64>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream);
-    return launch_bn<KIND_I8, 128>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream);
+    // instantiated combinations: split-precision modes (three products, 64-byte swizzle) and
+    // single-product modes (128-byte swizzle)
+    if (kind == KIND_TF32 && prod.n == 3 && swb == 64)
+        return launch_bn<KIND_TF32, 64, 3>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream);
+    if (kind == KIND_BF16 && prod.n == 3 && swb == 64)
+        return launch_bn<KIND_BF16, 64, 3>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream);
+    if (kind == KIND_BF16 && prod.n == 1 && swb == 128)
+        return launch_bn<KIND_BF16, 128, 1>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream);
+    if (kind == KIND_I8 && prod.n == 1)
+        return launch_bn<KIND_I8, 128, 1>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream);
+    snprintf(g_err, sizeof g_err, "launch_gemm_tc: no kernel for kind %d with %d products", kind, prod.n);
+    return (int)cudaErrorInvalidValue;
 }
 
 }  // namespace axb

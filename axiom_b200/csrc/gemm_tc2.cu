@@ -28,7 +28,7 @@ namespace axb {
 static constexpr int PAIR_BN = 256;
 static constexpr int PAIR_TILE_M = 256;
 
-template <int KIND, int SWB>
+template <int KIND, int SWB, int NPROD>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
 {
@@ -101,6 +101,7 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                     }
                     // the leader's barrier collects the bytes of both CTAs
                     const uint32_t fb = map_to_cta(bar_full + 8 * s, 0);
+                    if (p.dbg & 1) { if (leader) mbar_arrive(bar_full + 8 * s); continue; }
                     if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, 2u * (uint32_t)stage_bytes);
                     uint32_t dst = stage0 + s * stage_bytes;
                     for (int i = 0; i < p.npa; ++i, dst += A_BYTES)
@@ -113,10 +114,15 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
     } else if (warp == 1) {
         // -------------------------------------------------------- MMA issuer
         if (leader && lane == 0) {
-            uint32_t it = 0, vt = 0;
+            uint32_t s = 0, ph = 0, vt = 0;
             bool ok = true;
+            // everything the issue loop needs lives in registers
+            const int k_blocks = p.k_blocks, chunk_kb = p.chunk_kb, stages = p.stages;
+            const uint32_t prod_a = p.prod_a, prod_b = p.prod_b;
+            const uint64_t desc_hi = smem_desc_kmajor(0, SWB);
+            const uint32_t npa_bytes = p.npa * A_BYTES, sbytes = (uint32_t)stage_bytes;
             for (int t = pair; t < total_tiles && ok; t += npairs) {
-                for (int kb0 = 0; kb0 < p.k_blocks && ok; kb0 += p.chunk_kb, ++vt) {
+                for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += chunk_kb, ++vt) {
                     const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
                     if (!mbar_wait_bounded(bar_tempty + 8 * acc, aph ^ 1u)) {
                         report(p.err, ERR_MMA_WAIT_TMEM);
@@ -125,26 +131,22 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                     }
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + acc * BN;
-                    const int kb1 = min(p.k_blocks, kb0 + p.chunk_kb);
-                    for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                        const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                    const int kb1 = min(k_blocks, kb0 + chunk_kb);
+                    for (int kb = kb0; kb < kb1; ++kb) {
                         if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
                             report(p.err, ERR_MMA_WAIT_FULL);
                             ok = false;
                             break;
                         }
                         tc_fence_after_sync();
-                        const uint32_t sa = stage0 + s * stage_bytes;
-                        const uint32_t sb = sa + p.npa * A_BYTES;
-                        for (int pr = 0; pr < p.nprod; ++pr) {
-                            const uint64_t da = smem_desc_kmajor(sa + p.pa[pr] * A_BYTES, SWB);
-                            const uint64_t db = smem_desc_kmajor(sb + p.pb[pr] * B_BYTES, SWB);
-#pragma unroll
-                            for (int ks = 0; ks < KSTEPS; ++ks)
-                                tc_mma_pair<KIND>(d_tmem, da + 2u * ks, db + 2u * ks, IDESC,
-                                                  (uint32_t)(((kb - kb0) | pr | ks) != 0));
-                        }
+                        const uint32_t sa = stage0 + s * sbytes;
+                        issue_stage_mmas<KIND, SWB, NPROD, true, A_BYTES, B_BYTES>(
+                            d_tmem, sa, sa + npa_bytes, prod_a, prod_b, desc_hi, IDESC, kb == kb0);
                         tc_commit_pair(bar_empty + 8 * s, 0x3);
+                        if (++s == (uint32_t)stages) {
+                            s = 0;
+                            ph ^= 1u;
+                        }
                     }
                     if (ok) tc_commit_pair(bar_tfull + 8 * acc, 0x3);
                 }
@@ -306,7 +308,7 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
     }
 }
 
-template <int KIND, int SWB>
+template <int KIND, int SWB, int NPROD>
 static int launch_pair_inst(const TmapPack &tm, KernelArgs &ka, int npa, int npb, int sm_count, cudaStream_t stream,
                             char *err, size_t err_len)
 {
@@ -319,7 +321,7 @@ static int launch_pair_inst(const TmapPack &tm, KernelArgs &ka, int npa, int npb
     }
     ka.stages = stages;
     const int smem = HEADER_BYTES + 1024 + stages * stage_bytes;
-    auto kern = gemm_tc_pair_kernel<KIND, SWB>;
+    auto kern = gemm_tc_pair_kernel<KIND, SWB, NPROD>;
     static bool attr_set = false;
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET);
@@ -359,16 +361,19 @@ static int launch_pair_inst(const TmapPack &tm, KernelArgs &ka, int npa, int npb
     return (int)e;
 }
 
-int launch_gemm_tc_pair(int kind, int swb, const TmapPack &tm, KernelArgs &ka, int npa, int npb, int sm_count,
-                        cudaStream_t stream, char *err, size_t err_len)
+int launch_gemm_tc_pair(int kind, int swb, int nprod, const TmapPack &tm, KernelArgs &ka, int npa, int npb,
+                        int sm_count, cudaStream_t stream, char *err, size_t err_len)
 {
-    if (kind == KIND_TF32)
-        return swb == 128 ? launch_pair_inst<KIND_TF32, 128>(tm, ka, npa, npb, sm_count, stream, err, err_len)
-                          : launch_pair_inst<KIND_TF32, 64>(tm, ka, npa, npb, sm_count, stream, err, err_len);
-    if (kind == KIND_BF16)
-        return swb == 128 ? launch_pair_inst<KIND_BF16, 128>(tm, ka, npa, npb, sm_count, stream, err, err_len)
-                          : launch_pair_inst<KIND_BF16, 64>(tm, ka, npa, npb, sm_count, stream, err, err_len);
-    return launch_pair_inst<KIND_I8, 128>(tm, ka, npa, npb, sm_count, stream, err, err_len);
+    if (kind == KIND_TF32 && nprod == 3 && swb == 64)
+        return launch_pair_inst<KIND_TF32, 64, 3>(tm, ka, npa, npb, sm_count, stream, err, err_len);
+    if (kind == KIND_BF16 && nprod == 3 && swb == 64)
+        return launch_pair_inst<KIND_BF16, 64, 3>(tm, ka, npa, npb, sm_count, stream, err, err_len);
+    if (kind == KIND_BF16 && nprod == 1 && swb == 128)
+        return launch_pair_inst<KIND_BF16, 128, 1>(tm, ka, npa, npb, sm_count, stream, err, err_len);
+    if (kind == KIND_I8 && nprod == 1)
+        return launch_pair_inst<KIND_I8, 128, 1>(tm, ka, npa, npb, sm_count, stream, err, err_len);
+    snprintf(err, err_len, "pair kernel: no instantiation for kind %d with %d products", kind, nprod);
+    return (int)cudaErrorInvalidValue;
 }
 
 }  // namespace axb

@@ -23,7 +23,7 @@ struct alignas(64) TmapPack {
 struct KernelArgs {
     int M, N, K;
     int npa, npb, nprod;
-    int8_t pa[TC_MAX_PRODUCTS], pb[TC_MAX_PRODUCTS];
+    uint32_t prod_a, prod_b;  // plane index of product i in bits [4i, 4i+4): registers, never indexed memory
     int m_tiles, n_tiles, k_blocks, stages;
     int chunk_kb;  // k-blocks accumulated in TMEM before the epilogue warps drain them
     float alpha, beta;
@@ -34,6 +34,7 @@ struct KernelArgs {
     int32_t *acc_out;
     long long ldc;
     int *err;
+    int dbg;  // measurement experiments only (AX_B200_DBG): bit 0 = the producer signals stages without copying
 };
 
 // error words written to *err (first writer wins)
@@ -61,8 +62,32 @@ __device__ __forceinline__ float gelu_tanh(float v)
     return 0.5f * v * (1.0f + tanhf(inner));
 }
 
+
+// All MMAs of one pipeline stage, fully unrolled.  tcgen05.mma holds the issuing thread while
+// the tensor pipe is busy and the pipe queues next to nothing, so every scalar instruction
+// between two MMAs is time the pipe idles: descriptors are one OR and one ADD away from
+// registers, the product list is a bitfield, there are no loops, divisions or memory accesses.
+template <int KIND, int SWB, int NPROD, bool PAIR, int A_BYTES, int B_BYTES>
+__device__ __forceinline__ void issue_stage_mmas(uint32_t d_tmem, uint32_t sa, uint32_t sb, uint32_t prod_a,
+                                                 uint32_t prod_b, uint64_t desc_hi, uint32_t idesc, bool first)
+{
+    constexpr int KSTEPS = SWB / 32;
+#pragma unroll
+    for (int pr = 0; pr < NPROD; ++pr) {
+        const uint32_t ia = (prod_a >> (4 * pr)) & 15u, ib = (prod_b >> (4 * pr)) & 15u;
+        const uint64_t da = desc_hi | (uint64_t)((sa + ia * A_BYTES) >> 4);
+        const uint64_t db = desc_hi | (uint64_t)((sb + ib * B_BYTES) >> 4);
+#pragma unroll
+        for (int ks = 0; ks < KSTEPS; ++ks) {
+            const uint32_t accumulate = (pr == 0 && ks == 0) ? (first ? 0u : 1u) : 1u;
+            if constexpr (PAIR) tc_mma_pair<KIND>(d_tmem, da + 2u * ks, db + 2u * ks, idesc, accumulate);
+            else tc_mma<KIND>(d_tmem, da + 2u * ks, db + 2u * ks, idesc, accumulate);
+        }
+    }
+}
+
 // gemm_tc2.cu: the CTA-pair kernel (256 x 256 tiles; ka.m_tiles counts 256-row tiles, the B maps have 128-row boxes)
-int launch_gemm_tc_pair(int kind, int swb, const TmapPack &tm, KernelArgs &ka, int npa, int npb, int sm_count,
+int launch_gemm_tc_pair(int kind, int swb, int nprod, const TmapPack &tm, KernelArgs &ka, int npa, int npb, int sm_count,
                         cudaStream_t stream, char *err, size_t err_len);
 
 }  // namespace axb
