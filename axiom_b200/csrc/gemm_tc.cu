@@ -86,26 +86,37 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
         if (lane == 0) {
-            uint32_t it = 0;
+            // ring position kept incrementally and every loop invariant in a register: the producer
+            // has to turn a stage around faster than the tensor pipe drains one
+            uint32_t s = 0, ph = 0;
             bool ok = true;
+            const int k_blocks = p.k_blocks, stages = p.stages, npa = p.npa, npb = p.npb;
+            const uint32_t sbytes = (uint32_t)stage_bytes;
+            const bool no_copy = (p.dbg & 1) != 0;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 int mt, nt;
                 tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
-                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-                    const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                const int row_a = mt * BM, row_b = nt * BN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1u)) {
                         report(p.err, ERR_PRODUCER_WAIT);
                         ok = false;
                         break;
                     }
                     const uint32_t fb = bar_full + 8 * s;
-                    if (p.dbg & 1) { mbar_arrive(fb); continue; }
-                    mbar_arrive_expect_tx(fb, (uint32_t)stage_bytes);
-                    uint32_t dst = stage0 + s * stage_bytes;
-                    for (int i = 0; i < p.npa; ++i, dst += A_BYTES)
-                        tma_load_2d(dst, &tm.a[i], fb, kb * BKE, mt * BM);
-                    for (int i = 0; i < p.npb; ++i, dst += B_BYTES)
-                        tma_load_2d(dst, &tm.b[i], fb, kb * BKE, nt * BN);
+                    if (no_copy) {
+                        mbar_arrive(fb);
+                    } else {
+                        mbar_arrive_expect_tx(fb, sbytes);
+                        uint32_t dst = stage0 + s * sbytes;
+                        const int kcrd = kb * BKE;
+                        for (int i = 0; i < npa; ++i, dst += A_BYTES) tma_load_2d(dst, &tm.a[i], fb, kcrd, row_a);
+                        for (int i = 0; i < npb; ++i, dst += B_BYTES) tma_load_2d(dst, &tm.b[i], fb, kcrd, row_b);
+                    }
+                    if (++s == (uint32_t)stages) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
                 }
             }
         }
@@ -180,7 +191,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                 // one chunk, exact integers: stream 32 columns at a time
                 const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
                 ++vt;
-                const bool got = mbar_wait_bounded(bar_tfull + 8 * acc, aph);
+                const bool got = mbar_wait_warp_bounded(bar_tfull + 8 * acc, aph);
                 if (!__all_sync(0xffffffffu, got)) {
                     report(p.err, ERR_EPI_WAIT);
                     alive = false;
@@ -242,7 +253,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                 for (int j = 0; j < HALF; ++j) sum[j] = 0.0f;
                 for (int ch = 0; ch < nchunks; ++ch, ++vt) {
                     const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
-                    const bool got = mbar_wait_bounded(bar_tfull + 8 * acc, aph);
+                    const bool got = mbar_wait_warp_bounded(bar_tfull + 8 * acc, aph);
                     if (!__all_sync(0xffffffffu, got)) {
                         report(p.err, ERR_EPI_WAIT);
                         alive = false;

@@ -85,15 +85,17 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
     if (warp == 0) {
         // ------------------------------------------------------ TMA producer
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t s = 0, ph = 0;
             bool ok = true;
+            const int k_blocks = p.k_blocks, stages = p.stages, npa = p.npa, npb = p.npb;
+            const uint32_t sbytes = (uint32_t)stage_bytes;
+            const bool no_copy = (p.dbg & 1) != 0;
             for (int t = pair; t < total_tiles && ok; t += npairs) {
                 int mt, nt;
                 tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
                 const int row_a = mt * PAIR_TILE_M + (int)rank * BM;
                 const int row_b = nt * BN + (int)rank * (BN / 2);
-                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
-                    const uint32_t s = it % p.stages, ph = (it / p.stages) & 1u;
+                for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1u)) {
                         report(p.err, ERR_PRODUCER_WAIT);
                         ok = false;
@@ -101,13 +103,19 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                     }
                     // the leader's barrier collects the bytes of both CTAs
                     const uint32_t fb = map_to_cta(bar_full + 8 * s, 0);
-                    if (p.dbg & 1) { if (leader) mbar_arrive(bar_full + 8 * s); continue; }
-                    if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, 2u * (uint32_t)stage_bytes);
-                    uint32_t dst = stage0 + s * stage_bytes;
-                    for (int i = 0; i < p.npa; ++i, dst += A_BYTES)
-                        tma_load_2d_pair(dst, &tm.a[i], fb, kb * BKE, row_a);
-                    for (int i = 0; i < p.npb; ++i, dst += B_BYTES)
-                        tma_load_2d_pair(dst, &tm.b[i], fb, kb * BKE, row_b);
+                    if (no_copy) {
+                        if (leader) mbar_arrive(bar_full + 8 * s);
+                    } else {
+                        if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, 2u * sbytes);
+                        uint32_t dst = stage0 + s * sbytes;
+                        const int kcrd = kb * BKE;
+                        for (int i = 0; i < npa; ++i, dst += A_BYTES) tma_load_2d_pair(dst, &tm.a[i], fb, kcrd, row_a);
+                        for (int i = 0; i < npb; ++i, dst += B_BYTES) tma_load_2d_pair(dst, &tm.b[i], fb, kcrd, row_b);
+                    }
+                    if (++s == (uint32_t)stages) {
+                        s = 0;
+                        ph ^= 1u;
+                    }
                 }
             }
         }
@@ -172,7 +180,7 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
             if constexpr (KIND == KIND_I8) {
                 const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
                 ++vt;
-                const bool got = mbar_wait_bounded(bar_tfull + 8 * acc, aph);
+                const bool got = mbar_wait_warp_bounded(bar_tfull + 8 * acc, aph);
                 if (!__all_sync(0xffffffffu, got)) {
                     report(p.err, ERR_EPI_WAIT);
                     alive = false;
@@ -234,7 +242,7 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                 for (int j = 0; j < HALF; ++j) sum[j] = 0.0f;
                 for (int ch = 0; ch < nchunks; ++ch, ++vt) {
                     const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
-                    const bool got = mbar_wait_bounded(bar_tfull + 8 * acc, aph);
+                    const bool got = mbar_wait_warp_bounded(bar_tfull + 8 * acc, aph);
                     if (!__all_sync(0xffffffffu, got)) {
                         report(p.err, ERR_EPI_WAIT);
                         alive = false;

@@ -75,6 +75,26 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity)
     }
 }
 
+// Whole-warp wait for warps that wait long (epilogue warps wait a whole K loop): only lane 0
+// polls, with a sleep between polls, so the waiters do not compete with the MMA-issuing
+// thread for the barrier unit; the outcome is broadcast to the warp.
+__device__ __forceinline__ bool mbar_wait_warp_bounded(uint32_t bar, uint32_t parity)
+{
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) {
+        if (!mbar_try_wait(bar, parity)) {
+            const uint64_t t0 = global_timer_ns();
+            for (;;) {
+                __nanosleep(200);
+                if (mbar_try_wait(bar, parity)) break;
+                if (global_timer_ns() - t0 > AXB_WAIT_LIMIT_NS) { ok = 0; break; }
+            }
+        }
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok != 0;
+}
+
 // ----------------------------------------------------------------------- TMA
 // 2-D tiled load global -> this CTA's shared memory, completion counted in
 // bytes on an mbarrier of the same CTA.  crd0 is the innermost (contiguous)
