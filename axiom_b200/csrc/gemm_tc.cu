@@ -83,8 +83,11 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(gen_base + 160);
 
-    if (warp == 0) {
-        // ------------------------------------------------------ TMA producer
+    if (warp == 0 || warp == B_PRODUCER_WARP) {
+        // ----------------------------------------------------- TMA producers
+        // warp 0 fetches the A planes and posts the stage's byte count, warp 10 fetches the B
+        // planes: two issuing threads keep up with the tensor pipe where one could not
+        const bool do_a = warp == 0;
         if (lane == 0) {
             // ring position kept incrementally and every loop invariant in a register: the producer
             // has to turn a stage around faster than the tensor pipe drains one
@@ -92,7 +95,6 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
             bool ok = true;
             const int k_blocks = p.k_blocks, stages = p.stages, npa = p.npa, npb = p.npb;
             const uint32_t sbytes = (uint32_t)stage_bytes;
-            const bool no_copy = (p.dbg & 1) != 0;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 int mt, nt;
                 tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
@@ -104,14 +106,16 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                         break;
                     }
                     const uint32_t fb = bar_full + 8 * s;
-                    if (no_copy) {
-                        mbar_arrive(fb);
-                    } else {
-                        mbar_arrive_expect_tx(fb, sbytes);
-                        uint32_t dst = stage0 + s * sbytes;
+                    {
                         const int kcrd = kb * BKE;
-                        for (int i = 0; i < npa; ++i, dst += A_BYTES) tma_load_2d(dst, &tm.a[i], fb, kcrd, row_a);
-                        for (int i = 0; i < npb; ++i, dst += B_BYTES) tma_load_2d(dst, &tm.b[i], fb, kcrd, row_b);
+                        if (do_a) {
+                            mbar_arrive_expect_tx(fb, sbytes);
+                            uint32_t dst = stage0 + s * sbytes;
+                            for (int i = 0; i < npa; ++i, dst += A_BYTES) tma_load_2d(dst, &tm.a[i], fb, kcrd, row_a);
+                        } else {
+                            uint32_t dst = stage0 + s * sbytes + npa * A_BYTES;
+                            for (int i = 0; i < npb; ++i, dst += B_BYTES) tma_load_2d(dst, &tm.b[i], fb, kcrd, row_b);
+                        }
                     }
                     if (++s == (uint32_t)stages) {
                         s = 0;
@@ -168,7 +172,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                 }
             }
         }
-    } else {
+    } else if (warp < B_PRODUCER_WARP) {
         // ---------------------------------------------------------- epilogue
         // 8 warps: warp % 4 picks the TMEM lane quarter (a hardware rule), the
         // two warps of a quarter split the tile's columns in halves.
@@ -510,8 +514,6 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
     ka.alpha = ep.alpha; ka.beta = ep.beta; ka.bias = ep.bias; ka.colscale = ep.colscale;
     ka.act = ep.act; ka.out_mode = ep.out_mode; ka.C = ep.C; ka.acc_out = ep.acc_out;
     ka.ldc = ep.ldc; ka.err = err_word;
-    static const int dbg_env = [] { const char *e = getenv("AX_B200_DBG"); return e ? atoi(e) : 0; }();
-    ka.dbg = dbg_env;
     const int64_t tiles = mt * nt;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
     if (use_pair)

@@ -82,14 +82,16 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
     tc_fence_after_sync();
     const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t *>(gen_base + 160);
 
-    if (warp == 0) {
-        // ------------------------------------------------------ TMA producer
+    if (warp == 0 || warp == B_PRODUCER_WARP) {
+        // ----------------------------------------------------- TMA producers
+        // warp 0 fetches the A planes and posts the stage's byte count, warp 10 fetches the B
+        // planes: two issuing threads keep up with the tensor pipe where one could not
+        const bool do_a = warp == 0;
         if (lane == 0) {
             uint32_t s = 0, ph = 0;
             bool ok = true;
             const int k_blocks = p.k_blocks, stages = p.stages, npa = p.npa, npb = p.npb;
             const uint32_t sbytes = (uint32_t)stage_bytes;
-            const bool no_copy = (p.dbg & 1) != 0;
             for (int t = pair; t < total_tiles && ok; t += npairs) {
                 int mt, nt;
                 tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
@@ -103,14 +105,16 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                     }
                     // the leader's barrier collects the bytes of both CTAs
                     const uint32_t fb = map_to_cta(bar_full + 8 * s, 0);
-                    if (no_copy) {
-                        if (leader) mbar_arrive(bar_full + 8 * s);
-                    } else {
-                        if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, 2u * sbytes);
-                        uint32_t dst = stage0 + s * sbytes;
+                    {
                         const int kcrd = kb * BKE;
-                        for (int i = 0; i < npa; ++i, dst += A_BYTES) tma_load_2d_pair(dst, &tm.a[i], fb, kcrd, row_a);
-                        for (int i = 0; i < npb; ++i, dst += B_BYTES) tma_load_2d_pair(dst, &tm.b[i], fb, kcrd, row_b);
+                        if (do_a) {
+                            if (leader) mbar_arrive_expect_tx(bar_full + 8 * s, 2u * sbytes);
+                            uint32_t dst = stage0 + s * sbytes;
+                            for (int i = 0; i < npa; ++i, dst += A_BYTES) tma_load_2d_pair(dst, &tm.a[i], fb, kcrd, row_a);
+                        } else {
+                            uint32_t dst = stage0 + s * sbytes + npa * A_BYTES;
+                            for (int i = 0; i < npb; ++i, dst += B_BYTES) tma_load_2d_pair(dst, &tm.b[i], fb, kcrd, row_b);
+                        }
                     }
                     if (++s == (uint32_t)stages) {
                         s = 0;
@@ -160,7 +164,7 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                 }
             }
         }
-    } else {
+    } else if (warp < B_PRODUCER_WARP) {
         // ---------------------------------------------------------- epilogue
         constexpr int HALF = BN / 2;
         constexpr int PIECES = HALF / 32;

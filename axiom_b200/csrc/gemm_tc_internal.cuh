@@ -10,7 +10,8 @@ namespace axb {
 
 static constexpr int BM = 128;
 static constexpr int GROUP_M = 16;
-static constexpr int NUM_THREADS = 320;  // producer warp, MMA warp, 8 epilogue warps
+static constexpr int NUM_THREADS = 352;  // A-producer warp, MMA warp, 8 epilogue warps, B-producer warp
+static constexpr int B_PRODUCER_WARP = 10;
 static constexpr int HEADER_BYTES = 1024;
 static constexpr int MAX_STAGES = 8;
 static constexpr int SMEM_BUDGET = 227 * 1024;
@@ -34,7 +35,6 @@ struct KernelArgs {
     int32_t *acc_out;
     long long ldc;
     int *err;
-    int dbg;  // measurement experiments only (AX_B200_DBG): bit 0 = the producer signals stages without copying
 };
 
 // error words written to *err (first writer wins)
