@@ -62,7 +62,7 @@ class ClockSampler:
             os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.gpu), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+                 "-lms", "20"], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
@@ -377,6 +377,14 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
                 "value": 2.0 * 512 * 4096 * 4096 / (step_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": step_ms,
                 "kernel_ms": core_ms, "prepass_ms": pre_ms})
 
+    # 3-layer MLP 8192 -> 16384 -> 16384 -> 8192 at batch 16384, bias + GELU fused (BASELINE config 5c):
+    # rows of the batch sharded over the ranks (no collective), and, with more than one rank, output
+    # columns sharded with one all-gather per layer.  Fixed total batch: strong scaling for this line.
+    try:
+        out.extend(mlp_extras(torch, dist, world, eng, K))
+    except Exception as exc:
+        out.append({"workload": "3-layer MLP batch 16384", "error": repr(exc)})
+
     # causal attention B=8,H=16,S=1024,dk=64 (BASELINE config 4); FLOPs by the reference's 4*BH*S^2*dk convention
     BH, S, dk = 128, 1024, 64
     Q, Kt, V = (torch.randn((BH, S, dk), device="cuda") for _ in range(3))
@@ -429,6 +437,42 @@ def run_profile_case(args):
     torch.cuda.synchronize()
     assert eng.device_error() == 0
     print(json.dumps({"profile_case": case, "size": n, "calls": 3, "note": "not a measurement"}))
+
+
+def mlp_extras(torch, dist, world, eng, K):
+    from axiom_b200.multi_gpu import ColumnShardedMLP, RowShardedMLP, shard_bounds
+    rank = dist.get_rank() if world > 1 else 0
+    dims = [8192, 16384, 16384, 8192]
+    batch = 16384
+    flop = 2.0 * batch * sum(dims[i] * dims[i + 1] for i in range(3))
+    gen = torch.Generator(device="cuda").manual_seed(99)          # same weights on every rank
+    Ws = [torch.randn((dims[i], dims[i + 1]), device="cuda", generator=gen) / (dims[i] ** 0.5) for i in range(3)]
+    bs = [torch.rand((dims[i + 1],), device="cuda", generator=gen) * 2 - 1 for i in range(3)]
+    x = torch.rand((batch, dims[0]), device="cuda", generator=gen) * 2 - 1
+    new_empty = lambda shape: torch.empty(shape, device="cuda", dtype=torch.float32)
+    steps = max(2, min(K, 3))
+    res = []
+    r0, r1 = shard_bounds(batch, world, rank)
+    rows = RowShardedMLP(eng, Ws, bs, act="gelu")
+    xr = x[r0:r1].contiguous()
+    ms = timed(torch, dist, world, lambda: rows.forward(xr, new_empty), steps, 1) / steps
+    res.append({"workload": f"3-layer MLP 8192-16384-16384-8192, batch 16384, rows sharded x{world} (no collective)",
+                "value": flop / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "kernel_ms": ms, "scaling": "strong"})
+    if world > 1:
+        slabs, bias_slabs = [], []
+        for W, b in zip(Ws, bs):
+            c0, c1 = shard_bounds(W.shape[1], world, rank)
+            slabs.append(W[:, c0:c1].contiguous())
+            bias_slabs.append(b[c0:c1].contiguous())
+        del Ws
+        torch.cuda.empty_cache()
+        ag = lambda dst, src: dist.all_gather_into_tensor(dst.view(-1, dst.shape[-1]), src)
+        cols = ColumnShardedMLP(eng, slabs, bias_slabs, world, rank, ag, act="gelu")
+        ms = timed(torch, dist, world, lambda: cols.forward(x, new_empty), steps, 1) / steps
+        res.append({"workload": f"3-layer MLP, batch 16384, output columns sharded x{world}, NCCL all-gather per layer",
+                    "value": flop / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "kernel_ms": ms,
+                    "scaling": "strong", "allgather_bytes_per_rank_per_layer": [batch * d // world * 4 for d in dims[1:]]})
+    return res
 
 
 def main():
