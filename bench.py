@@ -211,8 +211,12 @@ def run_ours(args):
     tf32_split_peak = peaks["bf16_tflops"] / 2.0 / 3.0   # TF32 issues at half the bf16 rate; 3 products per result
     achieved = FLOP_HEADLINE / (core_avg_ms * 1e-3) / 1e12
     roofline = {"bound": "tensor", "achieved": achieved, "peak": tf32_split_peak, "unit": "TFLOP/s",
-                "frac": achieved / tf32_split_peak, "traffic": None,
-                "kernel": "gemm_tc_kernel<tf32,BN=256,SW64>", "kernel_ms": core_avg_ms, "prepass_ms": pre_ms / max(calls, 1),
+                "frac": achieved / tf32_split_peak,
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload
+                # (profiles/gemm_tc_pair_tf32_8192.md); algorithmic bytes are 1.34e9 (4 operand planes + C)
+                "traffic": 5.42e9, "algorithmic_bytes": 1.34e9,
+                "kernel": "gemm_tc_pair_kernel<tf32,SW64,3 products> (CTA pairs, 256x256 tiles)", "kernel_ms": core_avg_ms,
+                "prepass_ms": pre_ms / max(calls, 1),
                 "peak_source": f"{peaks['source']} bf16 burst {peaks['bf16_tflops']} TFLOP/s / 2 (tf32 rate) / 3 (products)"}
 
     # ---------------- end to end: pinned host operands in, result out, every step
