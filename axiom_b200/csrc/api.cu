@@ -215,8 +215,8 @@ int gemm_skinny(const float *X, const float *W, const float *bias, float *Y, int
     SkinnyArgs a;
     a.X = X; a.W = W; a.bias = bias; a.Y = Y; a.M = (int)M; a.N = N; a.K = K;
     a.alpha = alpha; a.beta = beta; a.act = act;
-    a.ksplit = plan.ksplit; a.kchunk = plan.kchunk;
-    a.partial = plan.ksplit > 1 ? g.sk_partial : nullptr;
+    a.ksplit = plan.ksplit; a.kchunk = plan.kchunk; a.stages = plan.stages; a.cluster = plan.cluster;
+    a.partial = (plan.ksplit > 1 && !plan.cluster) ? g.sk_partial : nullptr;
     a.counters = g.sk_counters;
     a.err = g.err_word;
     mark(0);

@@ -15,6 +15,7 @@
 #include "errors.cuh"
 
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace axb {
 
@@ -175,9 +176,39 @@ static int mt_for(int64_t M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <
 static void skinny_plan_tma(int64_t M, int64_t N, int64_t K, int sm_count, SkinnyPlan *plan)
 {
     const int mt = mt_for(M);
-    const int cols = skinny_tma_strip_cols(mt), rows = skinny_tma_stage_rows(mt);
+    static const int env_ctas = [] { const char *e = getenv("AX_B200_SK_CTAS_PER_SM"); return e ? atoi(e) : 0; }();
+    static const int env_stages = [] { const char *e = getenv("AX_B200_SK_STAGES"); return e ? atoi(e) : 0; }();
+    static const int env_cluster = [] { const char *e = getenv("AX_B200_SK_CLUSTER"); return e ? atoi(e) : -1; }();
+    const int stages = env_stages >= 2 && env_stages <= 8 ? env_stages : 4;
+    plan->use_tma = 1;
+    plan->mt = mt;
+    plan->stages = stages;
+    // Preferred: 128-column strips whose 8 K-slices form one cluster and reduce through shared memory
+    // (no global scratch).  Needs enough strips to fill the machine and an X slice that fits.
+    {
+        const int rows = skinny_tma_stage_rows(mt, 1);
+        const int strips = (int)((N + 127) / 128);
+        int64_t ksplit = 8;
+        int64_t kchunk = ((K + ksplit - 1) / ksplit + rows - 1) / rows * rows;
+        ksplit = (K + kchunk - 1) / kchunk;
+        const bool fits = kchunk * mt * 4 <= 64 * 1024 && kchunk >= 128;
+        const bool fills = (int64_t)strips * ksplit >= sm_count;
+        // (M > 8 holds one CTA per SM for its registers: a 256-CTA cluster grid would run in two waves)
+        if (env_cluster != 0 && mt <= 8 && ksplit >= 2 && ksplit <= 8 && fits && (fills || env_cluster == 1)) {
+            plan->cluster = 1;
+            plan->strips = strips;
+            plan->ksplit = (int)ksplit;
+            plan->kchunk = (int)kchunk;
+            plan->partial_floats = 0;
+            plan->smem_bytes = skinny_tma_smem_bytes(mt, (int)kchunk, stages);
+            return;
+        }
+    }
+    plan->cluster = 0;
+    const int cols = skinny_tma_strip_cols(mt, 0), rows = skinny_tma_stage_rows(mt, 0);
     const int strips = (int)((N + cols - 1) / cols);
-    int64_t ksplit = (2 * (int64_t)sm_count) / strips;
+    const int ctas_per_sm = env_ctas > 0 ? env_ctas : 2;
+    int64_t ksplit = (ctas_per_sm * (int64_t)sm_count) / strips;
     if (ksplit < 1) ksplit = 1;
     const int64_t max_split = (K + 4 * rows - 1) / (4 * rows);  // at least one trip round the ring
     if (ksplit > max_split) ksplit = max_split;
@@ -186,13 +217,11 @@ static void skinny_plan_tma(int64_t M, int64_t N, int64_t K, int sm_count, Skinn
     const int64_t max_chunk = (64 * 1024) / (4 * mt) / rows * rows;  // X slice within 64 KB
     if (kchunk > max_chunk) kchunk = max_chunk;
     ksplit = (K + kchunk - 1) / kchunk;
-    plan->use_tma = 1;
-    plan->mt = mt;
     plan->strips = strips;
     plan->ksplit = (int)ksplit;
     plan->kchunk = (int)kchunk;
     plan->partial_floats = ksplit > 1 ? ksplit * M * N : 0;
-    plan->smem_bytes = skinny_tma_smem_bytes(mt, (int)kchunk);
+    plan->smem_bytes = skinny_tma_smem_bytes(mt, (int)kchunk, stages);
 }
 
 void skinny_plan(int64_t M, int64_t N, int64_t K, const float *W, int sm_count, SkinnyPlan *plan)
@@ -202,6 +231,8 @@ void skinny_plan(int64_t M, int64_t N, int64_t K, const float *W, int sm_count, 
         return;
     }
     plan->use_tma = 0;
+    plan->cluster = 0;
+    plan->stages = 0;
     const int mt = mt_for(M);
     const int strips = (int)((N + SK_STRIP - 1) / SK_STRIP);
     int64_t ksplit = (2 * (int64_t)sm_count) / strips;
@@ -306,8 +337,8 @@ extern "C" int axb_skinny_gemm_static(const float *X, const float *W, const floa
     SkinnyArgs a;
     a.X = X; a.W = W; a.bias = bias; a.Y = Y; a.M = (int)M; a.N = N; a.K = K;
     a.alpha = alpha; a.beta = beta; a.act = act;
-    a.ksplit = plan.ksplit; a.kchunk = plan.kchunk;
-    a.partial = plan.ksplit > 1 ? scratch : nullptr;
+    a.ksplit = plan.ksplit; a.kchunk = plan.kchunk; a.stages = plan.stages; a.cluster = plan.cluster;
+    a.partial = (plan.ksplit > 1 && !plan.cluster) ? scratch : nullptr;
     a.counters = counters;
     a.err = nullptr;
     int le = launch_skinny(a, plan, st);

@@ -16,6 +16,8 @@ struct SkinnyArgs {
     float alpha, beta;
     int act;
     int ksplit, kchunk;
+    int stages;         // TMA ring depth (skinny_tma.cu)
+    int cluster;        // 1: the K-slices of a strip are one thread-block cluster and reduce through shared memory
     float *partial;     // [ksplit][M][N] scratch when ksplit > 1
     int *counters;      // [strips] zero between calls
     int *err;           // device word that receives a code when a bounded wait runs out, or null
@@ -23,7 +25,7 @@ struct SkinnyArgs {
 
 struct SkinnyPlan {
     int use_tma;             // 1: TMA-staged kernel (skinny_tma.cu), 0: plain-load kernel (skinny.cu)
-    int mt, strips, ksplit, kchunk;
+    int mt, strips, ksplit, kchunk, stages, cluster;
     int64_t partial_floats;  // scratch the plan needs (0 when K is not split)
     size_t smem_bytes;
 };
@@ -32,9 +34,9 @@ void skinny_plan(int64_t M, int64_t N, int64_t K, const float *W, int sm_count, 
 int launch_skinny(const SkinnyArgs &args, const SkinnyPlan &plan, cudaStream_t st);
 
 // TMA-staged variant (skinny_tma.cu)
-int skinny_tma_strip_cols(int mt);
-int skinny_tma_stage_rows(int mt);
-size_t skinny_tma_smem_bytes(int mt, int kchunk);
+int skinny_tma_strip_cols(int mt, int cluster);
+int skinny_tma_stage_rows(int mt, int cluster);
+size_t skinny_tma_smem_bytes(int mt, int kchunk, int stages);
 int launch_skinny_tma(const SkinnyArgs &args, const SkinnyPlan &plan, cudaStream_t st);
 
 }  // namespace axb

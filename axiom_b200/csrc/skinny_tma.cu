@@ -27,7 +27,7 @@ namespace axb {
 
 static constexpr int ST_THREADS = 288;
 static constexpr int ST_CONSUMERS = 8;
-static constexpr int ST_STAGES = 4;
+static constexpr int ST_MAX_STAGES = 8;
 static constexpr int ST_STAGE_BYTES = 16384;
 static constexpr int ST_HEADER = 128;
 
@@ -58,7 +58,8 @@ __global__ void __launch_bounds__(ST_THREADS) skinny_tma_kernel(const __grid_con
     __shared__ int s_last;
     const uint32_t base = (smem_u32(smem_raw) + 127u) & ~127u;
     uint8_t *gbase = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t bar_full = base, bar_empty = base + 8 * ST_STAGES;
+    const int ST_STAGES = a.stages;  // ring depth chosen by the planner (<= ST_MAX_STAGES)
+    const uint32_t bar_full = base, bar_empty = base + 8 * ST_MAX_STAGES;
     const uint32_t ring = base + ST_HEADER;
     float *ring_g = reinterpret_cast<float *>(gbase + ST_HEADER);
     float *xs = ring_g + ST_STAGES * ST_STAGE_BYTES / 4;  // [kchunk][MT]
@@ -213,13 +214,34 @@ __global__ void __launch_bounds__(ST_THREADS) skinny_tma_kernel(const __grid_con
 #pragma unroll
                 for (int w = 0; w < ST_CONSUMERS; ++w) s += red[(w * RM + mi) * COLS + c];
                 if (a.ksplit == 1) a.Y[(int64_t)m * a.N + gc] = st_epilogue(a, s, m, gc);
+                else if (a.cluster) xs[m * COLS + c] = s;   // X is dead: its space carries this CTA's strip sums
                 else part[(int64_t)m * a.N + gc] = s;
             }
         }
         __syncthreads();
     }
 
-    if (a.ksplit > 1) {
+    if (a.ksplit > 1 && a.cluster) {
+        // The K-slices of this strip are the CTAs of one cluster: CTA 0 adds the slices' sums straight
+        // out of their shared memory, in slice order, so no scratch in global memory is touched.
+        cluster_sync_all();
+        if (cluster_cta_rank() == 0) {
+            const int ncols = (int)min((int64_t)COLS, a.N - (int64_t)strip * COLS);
+            for (int o = tid; o < a.M * ncols; o += ST_THREADS) {
+                const int m = o / ncols, c = o - m * ncols;
+                const uint32_t local = smem_u32(xs + m * COLS + c);
+                float s = 0.0f;
+                for (int q = 0; q < a.ksplit; ++q) {
+                    float v;
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(map_to_cta(local, (uint32_t)q)));
+                    s += v;
+                }
+                const int64_t gc = (int64_t)strip * COLS + c;
+                a.Y[(int64_t)m * a.N + gc] = st_epilogue(a, s, m, gc);
+            }
+        }
+        cluster_sync_all();   // the other CTAs' shared memory must outlive the reads above
+    } else if (a.ksplit > 1) {
         __threadfence();
         __syncthreads();
         if (tid == 0) {
@@ -250,35 +272,58 @@ static int launch_tma_inst(const CUtensorMap &tm, const SkinnyArgs &a, dim3 grid
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
         attr_set[dev] = true;
+    }
+    if (a.cluster) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(ST_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute at;
+        at.id = cudaLaunchAttributeClusterDimension;
+        at.val.clusterDim.x = 1;
+        at.val.clusterDim.y = grid.y;   // all K-slices of a strip
+        at.val.clusterDim.z = 1;
+        cfg.attrs = &at;
+        cfg.numAttrs = 1;
+        return (int)cudaLaunchKernelEx(&cfg, k, tm, a);
     }
     k<<<grid, ST_THREADS, smem, st>>>(tm, a);
     return (int)cudaGetLastError();
 }
 
-int skinny_tma_strip_cols(int mt) { return mt <= 8 ? 256 : 128; }
-int skinny_tma_stage_rows(int mt) { return ST_STAGE_BYTES / (skinny_tma_strip_cols(mt) * 4); }
-size_t skinny_tma_smem_bytes(int mt, int kchunk)
+int skinny_tma_strip_cols(int mt, int cluster) { return (mt <= 8 && !cluster) ? 256 : 128; }
+int skinny_tma_stage_rows(int mt, int cluster) { return ST_STAGE_BYTES / (skinny_tma_strip_cols(mt, cluster) * 4); }
+size_t skinny_tma_smem_bytes(int mt, int kchunk, int stages)
 {
-    return (size_t)ST_HEADER + 128 + (size_t)ST_STAGES * ST_STAGE_BYTES + (size_t)kchunk * mt * 4;
+    return (size_t)ST_HEADER + 128 + (size_t)stages * ST_STAGE_BYTES + (size_t)kchunk * mt * 4;
 }
 
 int launch_skinny_tma(const SkinnyArgs &a, const SkinnyPlan &plan, cudaStream_t st)
 {
     alignas(64) CUtensorMap tm;
-    const int cols = skinny_tma_strip_cols(plan.mt), rows = skinny_tma_stage_rows(plan.mt);
+    const int cols = skinny_tma_strip_cols(plan.mt, plan.cluster), rows = skinny_tma_stage_rows(plan.mt, plan.cluster);
     int e = encode_f32_matrix_tmap(&tm, a.W, a.K, a.N, a.N, cols, rows);
     if (e) return e;
     dim3 grid((unsigned)plan.strips, (unsigned)plan.ksplit);
     const size_t smem = plan.smem_bytes;
+    if (plan.cluster || plan.mt > 8) {
+        switch (plan.mt) {
+        case 1: return launch_tma_inst<1, 1>(tm, a, grid, smem, st);
+        case 2: return launch_tma_inst<2, 1>(tm, a, grid, smem, st);
+        case 4: return launch_tma_inst<4, 1>(tm, a, grid, smem, st);
+        case 8: return launch_tma_inst<8, 1>(tm, a, grid, smem, st);
+        case 16: return launch_tma_inst<16, 1>(tm, a, grid, smem, st);
+        default: return launch_tma_inst<32, 1>(tm, a, grid, smem, st);
+        }
+    }
     switch (plan.mt) {
     case 1: return launch_tma_inst<1, 2>(tm, a, grid, smem, st);
     case 2: return launch_tma_inst<2, 2>(tm, a, grid, smem, st);
     case 4: return launch_tma_inst<4, 2>(tm, a, grid, smem, st);
-    case 8: return launch_tma_inst<8, 2>(tm, a, grid, smem, st);
-    case 16: return launch_tma_inst<16, 1>(tm, a, grid, smem, st);
-    default: return launch_tma_inst<32, 1>(tm, a, grid, smem, st);
+    default: return launch_tma_inst<8, 2>(tm, a, grid, smem, st);
     }
 }
 

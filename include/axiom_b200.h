@@ -125,9 +125,10 @@ AXB_API int axb_gemm_bias_act(const float *A, const float *B, const float *bias,
      cuda_stream (NULL = legacy default stream).
    - The first call on each device looks up the array's address on that device;
      make that first call during start-up, outside any stream capture.
-   - Shapes whose split-K partial sums exceed the array (roughly M * N * 9 > 2^20
-     floats on a 148-SM part, e.g. M = 32 with N = 4096) or with N > 131072 are
-     refused with AXB_ERR_INVALID_SHAPE and a message; nothing is launched.
+   - Most shapes reduce their K-slices inside a thread-block cluster and need no scratch at all.  Shapes
+     that do need it (K too long for a cluster of 8 slices, i.e. roughly K * M > 131072, or N < 2400)
+     and whose split-K partial sums exceed the array (slices * M * N > 2^20 floats), or with more than
+     1024 column strips, are refused with AXB_ERR_INVALID_SHAPE and a message; nothing is launched.
    - All calls on a device share the one array and it keeps the previous call's
      contents (the counters are cleared on the stream before each launch).  Two
      calls that overlap on the GPU — different streams without ordering, or

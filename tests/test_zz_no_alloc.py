@@ -22,7 +22,7 @@ def dev(x):
     return torch.from_numpy(np.ascontiguousarray(x)).cuda()
 
 
-@pytest.mark.parametrize("shape", [(1, 4096, 4096), (8, 4096, 4096), (5, 1000, 777)])
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (8, 4096, 4096), (5, 1000, 777), (2, 512, 8192)])
 def test_static_scratch_matches_regular_entry_point(engine, oracle, shape):
     M, N, K = shape
     W = dev(oracle.normal((K, N), 13, sigma=1.0 / np.sqrt(K)))
@@ -44,7 +44,7 @@ def test_static_scratch_matches_regular_entry_point(engine, oracle, shape):
 
 def test_static_scratch_refuses_oversized_shapes(engine):
     from axiom_b200.engine import EngineError
-    M, N, K = 32, 8192, 4096                                    # partial sums would not fit the 4 MiB array
+    M, N, K = 32, 8192, 16384                                   # needs split-K scratch, and more than the 4 MiB array holds
     x = torch.zeros((M, K), device="cuda")
     W = torch.zeros((K, N), device="cuda")
     y = torch.zeros((M, N), device="cuda")
