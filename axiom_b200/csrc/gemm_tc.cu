@@ -477,10 +477,13 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
         mt = (M + 255) / 256;
     }
     const int64_t nt = (N + bn - 1) / bn;
-    // Swizzle width: 64-byte rows halve the stage so the split-precision modes
-    // (four planes per stage) still get a four-deep ring.
     const int planes = A.nplanes + B.nplanes;
-    const int swb = (kind != KIND_I8 && prod.n > 1) ? 64 : 128;
+    static const int swb_env = [] { const char *e = getenv("AX_B200_SWB"); return e ? atoi(e) : 0; }();
+    // 128-byte rows everywhere (fewer, larger stages: half the TMA and barrier traffic per unit of K) except
+    // for the split-precision modes on single-CTA 128 x 256 tiles, where four operand planes of 128-byte rows
+    // would leave a two-stage ring: those take 64-byte rows and keep four stages.
+    int swb = (kind != KIND_I8 && prod.n > 1 && !use_pair && bn == 256) ? 64 : 128;
+    if (swb_env == 128 || (swb_env == 64 && kind != KIND_I8 && prod.n > 1)) swb = swb_env;
     (void)planes;
     const int es = kind == KIND_TF32 ? 4 : (kind == KIND_BF16 ? 2 : 1);
     const int bke = swb / es;
@@ -525,6 +528,10 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
         return launch_bn<KIND_TF32, 64, 3>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream);
     if (kind == KIND_BF16 && prod.n == 3 && swb == 64)
         return launch_bn<KIND_BF16, 64, 3>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream);
+    if (kind == KIND_TF32 && prod.n == 3 && swb == 128)
+        return launch_bn<KIND_TF32, 128, 3>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream);
+    if (kind == KIND_BF16 && prod.n == 3 && swb == 128)
+        return launch_bn<KIND_BF16, 128, 3>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream);
     if (kind == KIND_BF16 && prod.n == 1 && swb == 128)
         return launch_bn<KIND_BF16, 128, 1>(bn, tm, ka, A.nplanes, B.nplanes, grid, stream);
     if (kind == KIND_I8 && prod.n == 1)

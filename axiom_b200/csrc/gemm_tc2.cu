@@ -380,6 +380,10 @@ int launch_gemm_tc_pair(int kind, int swb, int nprod, const TmapPack &tm, Kernel
         return launch_pair_inst<KIND_TF32, 64, 3>(tm, ka, npa, npb, sm_count, stream, err, err_len);
     if (kind == KIND_BF16 && nprod == 3 && swb == 64)
         return launch_pair_inst<KIND_BF16, 64, 3>(tm, ka, npa, npb, sm_count, stream, err, err_len);
+    if (kind == KIND_TF32 && nprod == 3 && swb == 128)
+        return launch_pair_inst<KIND_TF32, 128, 3>(tm, ka, npa, npb, sm_count, stream, err, err_len);
+    if (kind == KIND_BF16 && nprod == 3 && swb == 128)
+        return launch_pair_inst<KIND_BF16, 128, 3>(tm, ka, npa, npb, sm_count, stream, err, err_len);
     if (kind == KIND_BF16 && nprod == 1 && swb == 128)
         return launch_pair_inst<KIND_BF16, 128, 1>(tm, ka, npa, npb, sm_count, stream, err, err_len);
     if (kind == KIND_I8 && nprod == 1)
