@@ -146,7 +146,7 @@ int run_split(const SplitOperand &s, const float *src, int64_t ld, bool transpos
 
 // the dense fp32 contraction on the tensor cores
 int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int64_t M, int64_t N, int64_t K,
-                int ta, int tb, float alpha, float beta, int act)
+                int ta, int tb, float alpha, float beta, int act, float *const *extra = nullptr, int n_extra = 0)
 {
     int split_mode, kind;
     TcProducts prod;
@@ -182,8 +182,11 @@ int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int
     e = run_split(sb, B, tb ? K : N, tb == 0, carve, opb);
     if (e) return cuda_fail("split B", e);
     TcEpilogue ep;
+    ep.n_extra = 0;
     ep.alpha = alpha; ep.beta = beta; ep.bias = bias; ep.colscale = nullptr; ep.act = act;
     ep.out_mode = OUT_F32; ep.C = C; ep.acc_out = nullptr; ep.ldc = N;
+    ep.n_extra = n_extra;
+    for (int i = 0; i < n_extra && i < TC_MAX_EXTRA; ++i) ep.c_extra[i] = extra[i];
     mark(1);
     e = launch_gemm_tc(kind, opa, opb, prod, M, N, K, ep, g.err_word, g.sm_count, g.stream);
     mark(2);
@@ -433,6 +436,53 @@ extern "C" int axb_gemm_bias_act(const float *A, const float *B, const float *bi
     return gemm_tc_f32(A, B, bias, C, M, N, K, trans_a, trans_b, alpha, beta, act);
 }
 
+extern "C" int axb_gemm_bias_act_scatter(const float *A, const float *B, const float *bias, float *C,
+                                         float *const *C_more, int n_more, int64_t M, int64_t N, int64_t K,
+                                         int trans_a, int trans_b, float alpha, float beta, int act)
+{
+    if (M < 0 || N < 0 || K <= 0) return fail(AXB_ERR_INVALID_SHAPE, "gemm_scatter: bad shape");
+    if (M == 0 || N == 0) return AXB_OK;
+    if (!A || !B || !C || (n_more > 0 && !C_more)) return fail(AXB_ERR_NULL_ARG, "gemm_scatter: NULL operand");
+    if (n_more < 0 || n_more > TC_MAX_EXTRA) return fail(AXB_ERR_INVALID_SHAPE, "gemm_scatter: at most %d extra destinations", TC_MAX_EXTRA);
+    for (int i = 0; i < n_more; ++i)
+        if (!C_more[i]) return fail(AXB_ERR_NULL_ARG, "gemm_scatter: NULL destination %d", i);
+    if (act < AXB_ACT_NONE || act > AXB_ACT_GELU) return fail(AXB_ERR_INVALID_SHAPE, "gemm_scatter: unknown activation %d", act);
+    if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "gemm_scatter: dimension exceeds 2^31-1");
+    int st = ensure_ready();
+    if (st) return st;
+    return gemm_tc_f32(A, B, bias, C, M, N, K, trans_a, trans_b, alpha, beta, act, C_more, n_more);
+}
+
+extern "C" int axb_ipc_get_handle(const void *dev_ptr, void *handle_64_bytes)
+{
+    if (!dev_ptr || !handle_64_bytes) return fail(AXB_ERR_NULL_ARG, "ipc_get_handle: NULL");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    cudaIpcMemHandle_t h;
+    cudaError_t e = cudaIpcGetMemHandle(&h, const_cast<void *>(dev_ptr));
+    if (e != cudaSuccess) return cuda_fail("cudaIpcGetMemHandle", e);
+    memcpy(handle_64_bytes, &h, 64);
+    return AXB_OK;
+}
+
+extern "C" int axb_ipc_open_handle(const void *handle_64_bytes, void **dev_ptr_out)
+{
+    if (!handle_64_bytes || !dev_ptr_out) return fail(AXB_ERR_NULL_ARG, "ipc_open_handle: NULL");
+    int st = ensure_ready();
+    if (st) return st;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle_64_bytes, 64);
+    cudaError_t e = cudaIpcOpenMemHandle(dev_ptr_out, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return cuda_fail("cudaIpcOpenMemHandle", e);
+    return AXB_OK;
+}
+
+extern "C" int axb_ipc_close_handle(void *dev_ptr)
+{
+    if (!dev_ptr) return AXB_OK;
+    cudaError_t e = cudaIpcCloseMemHandle(dev_ptr);
+    return e == cudaSuccess ? AXB_OK : cuda_fail("cudaIpcCloseMemHandle", e);
+}
+
 extern "C" int axb_gemm(const float *A, const float *B, float *C, int64_t M, int64_t N, int64_t K)
 {
     return axb_gemm_bias_act(A, B, nullptr, C, M, N, K, 0, 0, 1.0f, 0.0f, AXB_ACT_NONE);
@@ -528,6 +578,7 @@ extern "C" int axb_qgemm_w8a32(const float *a, const int8_t *q, const float *sca
     for (int i = 0; i < prod.n; ++i) { prod.a[i] = (int8_t)(prod.n - 1 - i); prod.b[i] = 0; }  // smallest plane first
     prod.chunk_k = prod.n > 1 ? g.chunk_bf16 : 0;
     TcEpilogue ep;
+    ep.n_extra = 0;
     ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = nullptr; ep.colscale = scales; ep.act = ACT_NONE;
     ep.out_mode = OUT_F32; ep.C = out; ep.acc_out = nullptr; ep.ldc = N;
     mark(1);
@@ -590,6 +641,7 @@ extern "C" int axb_qgemm_w8a8(const int8_t *a_q, float a_scale, const int8_t *b_
     memset(&prod, 0, sizeof prod);
     prod.n = 1;
     TcEpilogue ep;
+    ep.n_extra = 0;
     ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = nullptr; ep.colscale = mult; ep.act = ACT_NONE;
     ep.out_mode = out_q ? OUT_I8_REQUANT : OUT_S32_ONLY; ep.C = out_q; ep.acc_out = acc_out; ep.ldc = N;
     mark(1);

@@ -307,6 +307,19 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                                 for (int j = 0; j < 32; ++j)
                                     if (col0 + j < p.N) dst[j] = v[j];
                             }
+                            // the same tile to every further destination (peer gather buffers)
+                            for (int x = 0; x < p.n_extra; ++x) {
+                                float *dx = p.c_extra[x] + row * p.ldc + col0;
+                                if (full && ((reinterpret_cast<uintptr_t>(dx) & 15) == 0)) {
+#pragma unroll
+                                    for (int j = 0; j < 32; j += 4)
+                                        *reinterpret_cast<float4 *>(dx + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                } else {
+#pragma unroll
+                                    for (int j = 0; j < 32; ++j)
+                                        if (col0 + j < p.N) dx[j] = v[j];
+                                }
+                            }
                         }
                     }
                 }
@@ -517,6 +530,8 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
     ka.alpha = ep.alpha; ka.beta = ep.beta; ka.bias = ep.bias; ka.colscale = ep.colscale;
     ka.act = ep.act; ka.out_mode = ep.out_mode; ka.C = ep.C; ka.acc_out = ep.acc_out;
     ka.ldc = ep.ldc; ka.err = err_word;
+    ka.n_extra = ep.n_extra < 0 ? 0 : (ep.n_extra > TC_MAX_EXTRA ? TC_MAX_EXTRA : ep.n_extra);
+    for (int i = 0; i < ka.n_extra; ++i) ka.c_extra[i] = ep.c_extra[i];
     const int64_t tiles = mt * nt;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
     if (use_pair)

@@ -6,7 +6,7 @@
 
 namespace axb {
 
-enum { TC_MAX_PLANES = 3, TC_MAX_PRODUCTS = 6 };
+enum { TC_MAX_PLANES = 3, TC_MAX_PRODUCTS = 6, TC_MAX_EXTRA = 8 };
 enum { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2 };
 enum { OUT_F32 = 0, OUT_I8_REQUANT = 1, OUT_S32_ONLY = 2 };
 
@@ -28,6 +28,10 @@ struct TcEpilogue {
     void *C;                // float* (OUT_F32) / int8_t* (OUT_I8_REQUANT) / unused
     int32_t *acc_out;       // int8 kind: raw s32 accumulators, or null
     int64_t ldc;            // row pitch of C and acc_out in elements
+    // fp32 kinds: further destinations that receive the same tile as C (same pitch); used to store a
+    // rank's output slab straight into its peers' gather buffers over NVLink
+    float *c_extra[TC_MAX_EXTRA];
+    int n_extra;
 };
 
 struct TcProducts {

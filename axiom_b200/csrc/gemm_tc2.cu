@@ -298,6 +298,19 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                                 for (int j = 0; j < 32; ++j)
                                     if (col0 + j < p.N) dst[j] = v[j];
                             }
+                            // the same tile to every further destination (peer gather buffers)
+                            for (int x = 0; x < p.n_extra; ++x) {
+                                float *dx = p.c_extra[x] + row * p.ldc + col0;
+                                if (full && ((reinterpret_cast<uintptr_t>(dx) & 15) == 0)) {
+#pragma unroll
+                                    for (int j = 0; j < 32; j += 4)
+                                        *reinterpret_cast<float4 *>(dx + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                                } else {
+#pragma unroll
+                                    for (int j = 0; j < 32; ++j)
+                                        if (col0 + j < p.N) dx[j] = v[j];
+                                }
+                            }
                         }
                     }
                 }

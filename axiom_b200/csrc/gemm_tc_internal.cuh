@@ -35,6 +35,8 @@ struct KernelArgs {
     int32_t *acc_out;
     long long ldc;
     int *err;
+    float *c_extra[TC_MAX_EXTRA];
+    int n_extra;
 };
 
 // error words written to *err (first writer wins)

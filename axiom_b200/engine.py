@@ -23,7 +23,8 @@ EXPORTS = [
     "axb_set_fp32_mode", "axb_get_fp32_mode", "axb_last_error", "axb_device_error", "axb_launch_count",
     "axb_set_profiling", "axb_timing_summary",
     "axb_gemm", "axb_gemm_nt", "axb_gemm_tn", "axb_gemm_ex", "axb_gemm_relu", "axb_gemm_bias_act",
-    "axb_skinny_gemm_static",
+    "axb_skinny_gemm_static", "axb_gemm_bias_act_scatter", "axb_ipc_get_handle", "axb_ipc_open_handle",
+    "axb_ipc_close_handle",
     "axb_bias_add", "axb_relu", "axb_gelu", "axb_qgemm_w8a32", "axb_qgemm_w8a8", "axb_quantize_rows",
     "axb_sdpa_fwd",
 ]
@@ -135,6 +136,36 @@ class Engine:
         self._check(self.lib.axb_gemm_bias_act(_ptr(A), _ptr(B), _ptr(bias), _ptr(out), _i64(M), _i64(N), _i64(K),
                                                int(trans_a), int(trans_b), _f(alpha), _f(beta), ACT[act]))
         return out
+
+    def gemm_bias_act_scatter(self, A, B, bias, out, more, M, N, K, trans_a=False, trans_b=False, alpha=1.0, beta=0.0,
+                              act="none"):
+        """GEMM whose epilogue also stores the result to every buffer in `more` (tensors or raw device pointers)."""
+        arr = (C.c_void_p * max(len(more), 1))(*[(_ptr(m).value if m is not None else None) for m in more])
+        self._check(self.lib.axb_gemm_bias_act_scatter(_ptr(A), _ptr(B), _ptr(bias), _ptr(out), arr, len(more), _i64(M), _i64(N),
+                                                       _i64(K), int(trans_a), int(trans_b), _f(alpha), _f(beta), ACT[act]))
+        return out
+
+    def storage_alloc(self, nbytes):
+        p = self.lib.axb_storage_alloc(nbytes)
+        if not p:
+            raise EngineError(2, self.last_error())
+        return int(p)
+
+    def storage_free(self, ptr):
+        self.lib.axb_storage_free(C.c_void_p(ptr))
+
+    def ipc_get_handle(self, ptr):
+        buf = C.create_string_buffer(64)
+        self._check(self.lib.axb_ipc_get_handle(C.c_void_p(ptr), buf))
+        return buf.raw
+
+    def ipc_open_handle(self, handle):
+        out = C.c_void_p(0)
+        self._check(self.lib.axb_ipc_open_handle(C.create_string_buffer(handle, 64), C.byref(out)))
+        return int(out.value)
+
+    def ipc_close_handle(self, ptr):
+        self._check(self.lib.axb_ipc_close_handle(C.c_void_p(ptr)))
 
     def skinny_gemm_static(self, X, W, bias, out, M, N, K, alpha=1.0, beta=0.0, act="none", stream_ptr=None):
         """Allocation-free skinny GEMM (axb_skinny_gemm_static): scratch lives inside the library."""

@@ -82,3 +82,73 @@ def gathered_to_full(gathered):
     """[g, M, n] -> [M, g*n] (a copy; for checking results, not part of the data path)."""
     g, M, n = gathered.shape
     return gathered.permute(1, 0, 2).reshape(M, g * n)
+
+
+class PeerScatterColumnMLP:
+    """Column-sharded MLP whose GEMM epilogue does the all-gather: the last accumulating call of a layer
+    stores this rank's finished slab straight into EVERY rank's ``[g][M][n]`` gather buffer (peer stores
+    over NVLink from the tensor-core kernel's epilogue, ``axb_gemm_bias_act_scatter``), so the transfer
+    overlaps the MMAs tile by tile and no separate collective moves data.  One tiny all-reduce per layer
+    orders the peers' reads after everybody's stores.
+
+    Gather buffers are plain device allocations (``axb_storage_alloc``) shared through CUDA IPC handles that
+    the ranks exchange once with ``all_gather_object``; they are reused every step (a rank can only start
+    the next step after the last layer's synchronisation, by which time every rank has finished reading)."""
+
+    def __init__(self, engine, weight_slabs, bias_slabs, world, rank, batch, dist, act="gelu"):
+        import torch
+        self.engine, self.world, self.rank, self.act, self.dist = engine, world, rank, act, dist
+        self.weight_slabs, self.bias_slabs, self.batch = list(weight_slabs), list(bias_slabs), batch
+        self._token = torch.zeros(1, device="cuda")
+        self.local, self.peers, self._opened = [], [], []
+        for W in self.weight_slabs:
+            n = W.shape[1]
+            nbytes = world * batch * n * 4
+            ptr = engine.storage_alloc(nbytes)
+            handles = [None] * world
+            dist.all_gather_object(handles, engine.ipc_get_handle(ptr))
+            ptrs = []
+            for r, h in enumerate(handles):
+                if r == rank:
+                    ptrs.append(ptr)
+                else:
+                    q = engine.ipc_open_handle(h)
+                    self._opened.append(q)
+                    ptrs.append(q)
+            self.local.append(ptr)
+            self.peers.append(ptrs)
+        dist.barrier()
+
+    def forward(self, x_full, new_empty):
+        """x_full: the full [M, K_0] input on every rank; returns the device pointer of the gathered
+        [g, M, n_last] output in this rank's memory and n_last."""
+        g, M = self.world, self.batch
+        chunks = [(x_full, x_full.shape[1])]          # (tensor or raw pointer, k extent)
+        n = 0
+        for l, (W, b) in enumerate(zip(self.weight_slabs, self.bias_slabs)):
+            n = W.shape[1]
+            slab = new_empty((M, n))
+            # every rank's buffer, at the slab this rank owns
+            dests = [p + self.rank * M * n * 4 for p in self.peers[l]]
+            k0 = 0
+            for c, (xc, kc) in enumerate(chunks):
+                last = c == len(chunks) - 1
+                if last:
+                    self.engine.gemm_bias_act_scatter(xc, W[k0:k0 + kc], b, slab, dests, M, n, kc,
+                                                      beta=0.0 if c == 0 else 1.0, act=self.act)
+                else:
+                    self.engine.gemm_bias_act(xc, W[k0:k0 + kc], None, slab, M, n, kc,
+                                              beta=0.0 if c == 0 else 1.0, act="none")
+                k0 += kc
+            self.dist.all_reduce(self._token)           # everybody's stores are done before anybody reads
+            chunks = [(self.local[l] + r * M * n * 4, n) for r in range(g)]
+        return self.local[-1], n
+
+    def close(self):
+        self.dist.barrier()
+        for q in self._opened:
+            self.engine.ipc_close_handle(q)
+        self.dist.barrier()
+        for p in self.local:
+            self.engine.storage_free(p)
+        self._opened, self.local = [], []

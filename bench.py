@@ -473,6 +473,20 @@ def mlp_extras(torch, dist, world, eng, K):
         ag = lambda dst, src: dist.all_gather_into_tensor(dst.view(-1, dst.shape[-1]), src)
         cols = ColumnShardedMLP(eng, slabs, bias_slabs, world, rank, ag, act="gelu")
         ms = timed(torch, dist, world, lambda: cols.forward(x, new_empty), steps, 1) / steps
+        fused = None
+        try:
+            from axiom_b200.multi_gpu import PeerScatterColumnMLP
+            fused = PeerScatterColumnMLP(eng, slabs, bias_slabs, world, rank, batch, dist, act="gelu")
+            ms_f = timed(torch, dist, world, lambda: fused.forward(x, new_empty), steps, 1) / steps
+            res.append({"workload": f"3-layer MLP, batch 16384, output columns sharded x{world}, gather fused into the GEMM "
+                                    "epilogue as peer stores over NVLink (one 4-byte all-reduce per layer to order reads)",
+                        "value": flop / (ms_f * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_f, "kernel_ms": ms_f,
+                        "scaling": "strong"})
+        except Exception as exc:
+            res.append({"workload": "3-layer MLP, peer-store gather", "error": repr(exc)})
+        finally:
+            if fused is not None:
+                fused.close()
         res.append({"workload": f"3-layer MLP, batch 16384, output columns sharded x{world}, NCCL all-gather per layer",
                     "value": flop / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "kernel_ms": ms,
                     "scaling": "strong", "allgather_bytes_per_rank_per_layer": [batch * d // world * 4 for d in dims[1:]]})

@@ -110,6 +110,22 @@ AXB_API int axb_gemm_bias_act(const float *A, const float *B, const float *bias,
                       int64_t M, int64_t N, int64_t K, int trans_a, int trans_b,
                       float alpha, float beta, int act);
 
+/* ---- multi-GPU building blocks (no counterpart in the reference, which is single-device) ----
+   axb_gemm_bias_act_scatter is axb_gemm_bias_act on the tensor cores whose epilogue stores each finished tile to C
+   AND to n_more further buffers of the same shape and pitch (at most 8).  With C_more pointing into peers' gather
+   buffers (mapped through the axb_ipc_* calls) a rank's output slab reaches every GPU over NVLink while the GEMM is
+   still running, replacing the separate all-gather of a column-sharded layer; the caller still needs one small
+   cross-rank synchronisation before the peers read.  beta reads C only. */
+AXB_API int axb_gemm_bias_act_scatter(const float *A, const float *B, const float *bias, float *C,
+                                      float *const *C_more, int n_more, int64_t M, int64_t N, int64_t K,
+                                      int trans_a, int trans_b, float alpha, float beta, int act);
+/* Share a device allocation made with axb_storage_alloc with the other processes of the box:
+   the owner exports a 64-byte handle, a peer opens it (peer access is enabled on first use) and gets a
+   pointer valid on ITS device context; close before the owner frees. */
+AXB_API int axb_ipc_get_handle(const void *dev_ptr, void *handle_64_bytes);
+AXB_API int axb_ipc_open_handle(const void *handle_64_bytes, void **dev_ptr_out);
+AXB_API int axb_ipc_close_handle(void *dev_ptr);
+
 /* Skinny-M GEMM that never allocates (no counterpart in the reference).
      Y[M,N] = act(alpha * X[M,K] . W[K,N] + beta * Y + bias[n]),  1 <= M <= 32
    Same kernel and bit-identical results as the skinny route of axb_gemm_bias_act,

@@ -121,3 +121,21 @@ def test_mlp_chain_rows_vs_columns_single_gpu(engine, oracle):
         gathered = torch.stack(outs)
         chunks = [gathered[r] for r in range(world)]
     assert nerr(gathered_to_full(gathered).cpu().numpy(), h) <= 1e-5
+
+
+def test_scatter_epilogue_writes_every_destination(engine, oracle):
+    """axb_gemm_bias_act_scatter on one GPU: the extra destinations (stand-ins for peers' gather buffers)
+    receive exactly what C receives, for an accumulating call with bias and activation, ragged shape included."""
+    for (M, N, K) in [(512, 768, 320), (300, 520, 200)]:
+        A, B, bias, C0 = oracle.uniform((M, K), 7), oracle.uniform((K, N), 13), oracle.uniform((N,), 29), oracle.uniform((M, N), 5)
+        dA, dB, db = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda(), torch.from_numpy(bias).cuda()
+        C = torch.from_numpy(C0).cuda()
+        extras = [torch.full((M, N), float("nan"), device="cuda") for _ in range(3)]
+        engine.gemm_bias_act_scatter(dA, dB, db, C, extras, M, N, K, beta=1.0, act="gelu")
+        want = torch.from_numpy(C0).cuda()
+        engine.gemm_bias_act(dA, dB, db, want, M, N, K, beta=1.0, act="gelu")
+        assert torch.equal(C, want)
+        for e in extras:
+            assert torch.equal(e, want)
+        ref = oracle.gelu(np.ascontiguousarray((oracle.gemm_f64(A, B) + C0 + bias).astype(np.float32)))
+        assert nerr(C.cpu().numpy(), ref) <= 1e-5
