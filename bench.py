@@ -18,6 +18,7 @@ sample of the same workload and prints the same line with "impl": "reference".
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import statistics
@@ -478,10 +479,17 @@ def mlp_extras(torch, dist, world, eng, K):
             from axiom_b200.multi_gpu import PeerScatterColumnMLP
             fused = PeerScatterColumnMLP(eng, slabs, bias_slabs, world, rank, batch, dist, act="gelu")
             ms_f = timed(torch, dist, world, lambda: fused.forward(x, new_empty), steps, 1) / steps
+            # the two data paths must agree bit for bit (same kernels, same operands; only the route of the slabs differs)
+            y_ref = cols.forward(x, new_empty)
+            out_ptr, n_last = fused.forward(x, new_empty)
+            y_fused = torch.empty_like(y_ref)
+            eng._check(eng.lib.axb_memcpy_d2d(ctypes.c_void_p(y_fused.data_ptr()), ctypes.c_void_p(out_ptr), y_ref.numel() * 4))
+            torch.cuda.synchronize()
+            fused_equal = bool(torch.equal(y_fused, y_ref))
             res.append({"workload": f"3-layer MLP, batch 16384, output columns sharded x{world}, gather fused into the GEMM "
                                     "epilogue as peer stores over NVLink (one 4-byte all-reduce per layer to order reads)",
                         "value": flop / (ms_f * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_f, "kernel_ms": ms_f,
-                        "scaling": "strong"})
+                        "scaling": "strong", "bit_identical_to_nccl_path": fused_equal})
         except Exception as exc:
             res.append({"workload": "3-layer MLP, peer-store gather", "error": repr(exc)})
         finally:
