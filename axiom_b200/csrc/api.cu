@@ -129,7 +129,8 @@ SplitOperand plan_split(int mode, int64_t rows, int64_t k)
     return s;
 }
 
-int run_split(const SplitOperand &s, const float *src, int64_t ld, bool transposed, Carver &c, TcOperand &op)
+int run_split(const SplitOperand &s, const float *src, int64_t ld, bool transposed, Carver &c, TcOperand &op,
+              int64_t chunk_k = 0, int64_t chunk_stride = 0)
 {
     void *planes[3] = { nullptr, nullptr, nullptr };
     op.nplanes = split_num_planes(s.mode);
@@ -139,14 +140,16 @@ int run_split(const SplitOperand &s, const float *src, int64_t ld, bool transpos
     }
     op.rows = s.rows;
     op.pitch_elems = s.pitch;
-    int e = split_planes(s.mode, src, s.rows, s.k, ld, transposed, planes, s.pitch, g.sm_count, g.stream);
+    int e = split_planes(s.mode, src, s.rows, s.k, ld, transposed, planes, s.pitch, g.sm_count, g.stream, chunk_k,
+                         chunk_stride);
     g.launches++;
     return e;
 }
 
 // the dense fp32 contraction on the tensor cores
 int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int64_t M, int64_t N, int64_t K,
-                int ta, int tb, float alpha, float beta, int act, float *const *extra = nullptr, int n_extra = 0)
+                int ta, int tb, float alpha, float beta, int act, float *const *extra = nullptr, int n_extra = 0,
+                int64_t a_chunk_k = 0, int64_t a_chunk_stride = 0)
 {
     int split_mode, kind;
     TcProducts prod;
@@ -177,7 +180,7 @@ int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int
     mark(0);
     // A is [M,K] (k contiguous) unless trans_a, where it is stored [K,M];
     // B is [K,N] (k outermost) unless trans_b, where it is stored [N,K].
-    int e = run_split(sa, A, ta ? M : K, ta != 0, carve, opa);
+    int e = run_split(sa, A, ta ? M : K, ta != 0, carve, opa, a_chunk_k, a_chunk_stride);
     if (e) return cuda_fail("split A", e);
     e = run_split(sb, B, tb ? K : N, tb == 0, carve, opb);
     if (e) return cuda_fail("split B", e);
@@ -451,6 +454,26 @@ extern "C" int axb_gemm_bias_act_scatter(const float *A, const float *B, const f
     int st = ensure_ready();
     if (st) return st;
     return gemm_tc_f32(A, B, bias, C, M, N, K, trans_a, trans_b, alpha, beta, act, C_more, n_more);
+}
+
+extern "C" int axb_gemm_gathered_scatter(const float *A_gathered, int chunks, int64_t chunk_k, const float *B,
+                                         const float *bias, float *C, float *const *C_more, int n_more, int64_t M,
+                                         int64_t N, float alpha, float beta, int act)
+{
+    if (chunks < 1 || chunk_k < 1 || (chunk_k % 4) != 0)
+        return fail(AXB_ERR_INVALID_SHAPE, "gemm_gathered: needs chunks >= 1 and chunk_k a positive multiple of 4");
+    if (M < 0 || N < 0) return fail(AXB_ERR_INVALID_SHAPE, "gemm_gathered: negative dimension");
+    if (M == 0 || N == 0) return AXB_OK;
+    if (!A_gathered || !B || !C || (n_more > 0 && !C_more)) return fail(AXB_ERR_NULL_ARG, "gemm_gathered: NULL operand");
+    if (n_more < 0 || n_more > TC_MAX_EXTRA) return fail(AXB_ERR_INVALID_SHAPE, "gemm_gathered: at most %d extra destinations", TC_MAX_EXTRA);
+    for (int i = 0; i < n_more; ++i)
+        if (!C_more[i]) return fail(AXB_ERR_NULL_ARG, "gemm_gathered: NULL destination %d", i);
+    if (act < AXB_ACT_NONE || act > AXB_ACT_GELU) return fail(AXB_ERR_INVALID_SHAPE, "gemm_gathered: unknown activation %d", act);
+    const int64_t K = (int64_t)chunks * chunk_k;
+    if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "gemm_gathered: dimension exceeds 2^31-1");
+    int st = ensure_ready();
+    if (st) return st;
+    return gemm_tc_f32(A_gathered, B, bias, C, M, N, K, 0, 0, alpha, beta, act, C_more, n_more, chunk_k, M * chunk_k);
 }
 
 extern "C" int axb_ipc_get_handle(const void *dev_ptr, void *handle_64_bytes)

@@ -81,7 +81,8 @@ struct PlanePtrs {
 // in [rows, k] (k contiguous, row pitch ld) -> planes [rows, pitch]; 4 elements / thread
 template <int MODE>
 __global__ void __launch_bounds__(256) split_rows_kernel(const float *__restrict__ in, int64_t rows,
-                                                         int64_t k, int64_t ld, PlanePtrs pl, int64_t pitch)
+                                                         int64_t k, int64_t ld, PlanePtrs pl, int64_t pitch,
+                                                         int64_t chunk_k, int64_t chunk_stride)
 {
     const int64_t k4 = (k + 3) / 4;
     const int64_t total = rows * k4;
@@ -89,7 +90,9 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const float *__restrict
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t r = i / k4, c = (i - r * k4) * 4;
-        const float *src = in + r * ld + c;
+        // chunk_k > 0: the k range is cut into chunks stored as separate [rows, chunk_k] blocks chunk_stride
+        // apart (the layout an all-gather of column slabs leaves behind); chunk_k % 4 == 0
+        const float *src = chunk_k > 0 ? in + (c / chunk_k) * chunk_stride + r * chunk_k + (c % chunk_k) : in + r * ld + c;
         float x[4];
         if (vec && c + 4 <= k) {
             const float4 v = __ldg(reinterpret_cast<const float4 *>(src));
@@ -234,17 +237,18 @@ static inline int grid_for(int64_t work_items, int threads, int sm_count)
 }
 
 int split_planes(int mode, const float *in, int64_t rows, int64_t k, int64_t ld, bool in_is_k_major_outer,
-                 void *const planes[3], int64_t pitch, int sm_count, cudaStream_t st)
+                 void *const planes[3], int64_t pitch, int sm_count, cudaStream_t st, int64_t chunk_k,
+                 int64_t chunk_stride)
 {
     PlanePtrs pl;
     for (int i = 0; i < 3; ++i) pl.p[i] = planes[i];
     if (!in_is_k_major_outer) {
         const int g = grid_for(rows * ((k + 3) / 4), 256, sm_count);
         switch (mode) {
-        case SPLIT_TF32X2: split_rows_kernel<SPLIT_TF32X2><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch); break;
-        case SPLIT_BF16X1: split_rows_kernel<SPLIT_BF16X1><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch); break;
-        case SPLIT_BF16X2: split_rows_kernel<SPLIT_BF16X2><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch); break;
-        default: split_rows_kernel<SPLIT_BF16X3><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch); break;
+        case SPLIT_TF32X2: split_rows_kernel<SPLIT_TF32X2><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch, chunk_k, chunk_stride); break;
+        case SPLIT_BF16X1: split_rows_kernel<SPLIT_BF16X1><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch, chunk_k, chunk_stride); break;
+        case SPLIT_BF16X2: split_rows_kernel<SPLIT_BF16X2><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch, chunk_k, chunk_stride); break;
+        default: split_rows_kernel<SPLIT_BF16X3><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch, chunk_k, chunk_stride); break;
         }
     } else {
         const int64_t tiles = ((rows + 31) / 32) * ((k + 63) / 64);

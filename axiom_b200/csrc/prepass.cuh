@@ -11,9 +11,11 @@ static inline int split_num_planes(int mode) { return mode == SPLIT_BF16X1 ? 1 :
 static inline int split_elem_bytes(int mode) { return mode == SPLIT_TF32X2 ? 4 : 2; }
 
 // in: fp32, either [rows, k] with pitch ld (in_is_k_major_outer = false) or
-// [k, rows] with pitch ld (true).  planes: [rows, pitch] each, k contiguous.
+// [k, rows] with pitch ld (true).  chunk_k > 0 (row-major source only): k is cut into chunks held as
+// separate [rows, chunk_k] blocks chunk_stride elements apart.  planes: [rows, pitch] each, k contiguous.
 int split_planes(int mode, const float *in, int64_t rows, int64_t k, int64_t ld, bool in_is_k_major_outer,
-                 void *const planes[3], int64_t pitch, int sm_count, cudaStream_t st);
+                 void *const planes[3], int64_t pitch, int sm_count, cudaStream_t st, int64_t chunk_k = 0,
+                 int64_t chunk_stride = 0);
 int widen_i8_to_bf16(const int8_t *in, int64_t rows, int64_t k, void *out, int64_t pitch, int sm_count,
                      cudaStream_t st);
 int repitch_i8(const int8_t *in, int64_t rows, int64_t k, int8_t *out, int64_t pitch, int sm_count,

@@ -23,7 +23,7 @@ EXPORTS = [
     "axb_set_fp32_mode", "axb_get_fp32_mode", "axb_last_error", "axb_device_error", "axb_launch_count",
     "axb_set_profiling", "axb_timing_summary",
     "axb_gemm", "axb_gemm_nt", "axb_gemm_tn", "axb_gemm_ex", "axb_gemm_relu", "axb_gemm_bias_act",
-    "axb_skinny_gemm_static", "axb_gemm_bias_act_scatter", "axb_ipc_get_handle", "axb_ipc_open_handle",
+    "axb_skinny_gemm_static", "axb_gemm_bias_act_scatter", "axb_gemm_gathered_scatter", "axb_ipc_get_handle", "axb_ipc_open_handle",
     "axb_ipc_close_handle",
     "axb_bias_add", "axb_relu", "axb_gelu", "axb_qgemm_w8a32", "axb_qgemm_w8a8", "axb_quantize_rows",
     "axb_sdpa_fwd",
@@ -143,6 +143,13 @@ class Engine:
         arr = (C.c_void_p * max(len(more), 1))(*[(_ptr(m).value if m is not None else None) for m in more])
         self._check(self.lib.axb_gemm_bias_act_scatter(_ptr(A), _ptr(B), _ptr(bias), _ptr(out), arr, len(more), _i64(M), _i64(N),
                                                        _i64(K), int(trans_a), int(trans_b), _f(alpha), _f(beta), ACT[act]))
+        return out
+
+    def gemm_gathered_scatter(self, A_gathered, chunks, chunk_k, B, bias, out, more, M, N, alpha=1.0, beta=0.0, act="none"):
+        """GEMM whose left operand is a [chunks][M][chunk_k] gather buffer; result to `out` and every buffer in `more`."""
+        arr = (C.c_void_p * max(len(more), 1))(*[(_ptr(m).value if m is not None else None) for m in more])
+        self._check(self.lib.axb_gemm_gathered_scatter(_ptr(A_gathered), int(chunks), _i64(chunk_k), _ptr(B), _ptr(bias), _ptr(out),
+                                                       arr, len(more), _i64(M), _i64(N), _f(alpha), _f(beta), ACT[act]))
         return out
 
     def storage_alloc(self, nbytes):

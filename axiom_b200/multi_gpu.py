@@ -9,9 +9,9 @@ One process per GPU (torch.distributed).  Two partitions are offered:
   the GEMM epilogue, and ONE all-gather per layer makes the full activation
   available to every rank for the next layer.  The gather lands in a
   ``[g][M][N_l/g]`` buffer — each rank's slab contiguous, so the collective is a
-  plain contiguous all-gather — and the next layer consumes that buffer as g
-  chunks of its K dimension (g accumulating GEMM calls, bias + activation on
-  the last), so no re-layout pass is needed.
+  plain contiguous all-gather — and the next layer reads that buffer in place as
+  its [M, N_l] operand (the operand-split pre-pass walks the g chunks), so no
+  re-layout pass and no accumulating calls are needed.
 
 The reference is single-device: this module has no counterpart there.  The
 GEMMs are always the engine's kernels; ``torch`` only owns buffers and the
@@ -57,24 +57,26 @@ class ColumnShardedMLP:
     def forward(self, x_full, new_empty):
         """x_full: the full [M, K_0] input on every rank.  Returns the gathered [g, M, N_last/g] output."""
         g = self.world
-        chunks = [x_full]                     # the current layer's input as a list of K-chunks [M, k_c]
         gathered = None
         for W, b in zip(self.weight_slabs, self.bias_slabs):
-            M = chunks[0].shape[0]
             n = W.shape[1]
-            slab = new_empty((M, n))
-            k0 = 0
-            for c, xc in enumerate(chunks):
-                kc = xc.shape[1]
-                last = c == len(chunks) - 1
-                # rows k0 .. k0+kc of this rank's weight slab (a contiguous block of rows)
-                self.engine.gemm_bias_act(xc, W[k0:k0 + kc], b if last else None, slab, M, n, kc,
-                                          beta=0.0 if c == 0 else 1.0, act=self.act if last else "none")
-                k0 += kc
-            assert k0 == W.shape[0]
-            gathered = new_empty((g, M, n))
+            if gathered is None:
+                M, K = x_full.shape
+                slab = new_empty((M, n))
+                self.engine.gemm_bias_act(x_full, W, b, slab, M, n, K, act=self.act)
+            else:
+                # the previous layer's gather buffer [g][M][k] is read in place as the [M, g*k] operand
+                _, M, kc = gathered.shape
+                slab = new_empty((M, n))
+                if hasattr(self.engine, "gemm_gathered_scatter"):
+                    self.engine.gemm_gathered_scatter(gathered, g, kc, W, b, slab, [], M, n, act=self.act)
+                else:   # engines without the gathered-operand entry: g accumulating calls over the K-chunks
+                    for c in range(g):
+                        last = c == g - 1
+                        self.engine.gemm_bias_act(gathered[c], W[c * kc:(c + 1) * kc], b if last else None, slab, M, n, kc,
+                                                  beta=0.0 if c == 0 else 1.0, act=self.act if last else "none")
+            gathered = new_empty((g, slab.shape[0], n))
             self.all_gather(gathered, slab)
-            chunks = [gathered[r] for r in range(g)]
         return gathered
 
 
@@ -123,25 +125,18 @@ class PeerScatterColumnMLP:
         """x_full: the full [M, K_0] input on every rank; returns the device pointer of the gathered
         [g, M, n_last] output in this rank's memory and n_last."""
         g, M = self.world, self.batch
-        chunks = [(x_full, x_full.shape[1])]          # (tensor or raw pointer, k extent)
-        n = 0
+        n, prev_n = 0, 0
         for l, (W, b) in enumerate(zip(self.weight_slabs, self.bias_slabs)):
             n = W.shape[1]
             slab = new_empty((M, n))
-            # every rank's buffer, at the slab this rank owns
+            # every rank's gather buffer, at the slab this rank owns
             dests = [p + self.rank * M * n * 4 for p in self.peers[l]]
-            k0 = 0
-            for c, (xc, kc) in enumerate(chunks):
-                last = c == len(chunks) - 1
-                if last:
-                    self.engine.gemm_bias_act_scatter(xc, W[k0:k0 + kc], b, slab, dests, M, n, kc,
-                                                      beta=0.0 if c == 0 else 1.0, act=self.act)
-                else:
-                    self.engine.gemm_bias_act(xc, W[k0:k0 + kc], None, slab, M, n, kc,
-                                              beta=0.0 if c == 0 else 1.0, act="none")
-                k0 += kc
+            if l == 0:
+                self.engine.gemm_bias_act_scatter(x_full, W, b, slab, dests, M, n, x_full.shape[1], act=self.act)
+            else:
+                self.engine.gemm_gathered_scatter(self.local[l - 1], g, prev_n, W, b, slab, dests, M, n, act=self.act)
             self.dist.all_reduce(self._token)           # everybody's stores are done before anybody reads
-            chunks = [(self.local[l] + r * M * n * 4, n) for r in range(g)]
+            prev_n = n
         return self.local[-1], n
 
     def close(self):

@@ -119,6 +119,14 @@ AXB_API int axb_gemm_bias_act(const float *A, const float *B, const float *bias,
 AXB_API int axb_gemm_bias_act_scatter(const float *A, const float *B, const float *bias, float *C,
                                       float *const *C_more, int n_more, int64_t M, int64_t N, int64_t K,
                                       int trans_a, int trans_b, float alpha, float beta, int act);
+/* The same GEMM reading its left operand straight out of a gather buffer: A_gathered is [chunks][M][chunk_k]
+   (what an all-gather of column slabs leaves behind) and stands for the [M, chunks*chunk_k] matrix whose
+   columns chunk c occupy [c*chunk_k, (c+1)*chunk_k); B is [chunks*chunk_k, N].  No re-layout pass and no
+   accumulating calls: the operand split reads the chunks in place.  chunk_k % 4 == 0.  C_more / n_more as above
+   (n_more = 0 for a plain GEMM). */
+AXB_API int axb_gemm_gathered_scatter(const float *A_gathered, int chunks, int64_t chunk_k, const float *B,
+                                      const float *bias, float *C, float *const *C_more, int n_more, int64_t M,
+                                      int64_t N, float alpha, float beta, int act);
 /* Share a device allocation made with axb_storage_alloc with the other processes of the box:
    the owner exports a 64-byte handle, a peer opens it (peer access is enabled on first use) and gets a
    pointer valid on ITS device context; close before the owner frees. */

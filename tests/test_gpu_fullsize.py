@@ -139,3 +139,20 @@ def test_scatter_epilogue_writes_every_destination(engine, oracle):
             assert torch.equal(e, want)
         ref = oracle.gelu(np.ascontiguousarray((oracle.gemm_f64(A, B) + C0 + bias).astype(np.float32)))
         assert nerr(C.cpu().numpy(), ref) <= 1e-5
+
+
+def test_gathered_operand_gemm(engine, oracle):
+    """axb_gemm_gathered_scatter reads a [g][M][kc] gather buffer in place as the [M, g*kc] operand."""
+    g, M, kc, N = 4, 300, 96, 200
+    A = oracle.uniform((M, g * kc), 7)
+    B, bias = oracle.uniform((g * kc, N), 13), oracle.uniform((N,), 29)
+    gathered = np.ascontiguousarray(A.reshape(M, g, kc).transpose(1, 0, 2))     # [g][M][kc]
+    out = torch.full((M, N), float("nan"), device="cuda")
+    extra = torch.full((M, N), float("nan"), device="cuda")
+    engine.gemm_gathered_scatter(torch.from_numpy(gathered).cuda(), g, kc, torch.from_numpy(B).cuda(),
+                                 torch.from_numpy(bias).cuda(), out, [extra], M, N, act="relu")
+    want = torch.empty((M, N), device="cuda")
+    engine.gemm_bias_act(torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda(), torch.from_numpy(bias).cuda(), want, M, N, g * kc,
+                         act="relu")
+    assert torch.equal(out, want) and torch.equal(extra, want)
+    assert nerr(out.cpu().numpy(), np.maximum(oracle.gemm_f64(A, B) + bias, 0)) <= 1e-5
