@@ -9,6 +9,7 @@
 #include "gemm_tc.cuh"
 #include "prepass.cuh"
 #include "ptx.cuh"
+#include "qgemv.cuh"
 #include "sdpa.cuh"
 #include "skinny.cuh"
 
@@ -578,6 +579,15 @@ extern "C" int axb_qgemm_w8a32(const float *a, const int8_t *q, const float *sca
     int st = ensure_ready();
     if (st) return st;
     if (M == 0) return AXB_OK;
+    if (qgemv_w8a32_applicable(M, N, K, q)) {
+        // skinny activations: stream the int8 rows once, fp32 FMA (the reference's own arithmetic)
+        mark(0);
+        mark(1);
+        int e = launch_qgemv_w8a32(a, q, scales, out, M, N, K, g.sm_count, g.stream);
+        mark(2);
+        g.launches++;
+        return e ? cuda_fail("w8a32 gemv", e) : AXB_OK;
+    }
     // activations: bf16 hi/mid/lo (exact to 24 bits); weights: int8 widened to bf16 (exact)
     const int amode = g.fp32_mode == AXB_FP32_BF16 ? SPLIT_BF16X1 : SPLIT_BF16X3;
     const SplitOperand sa = plan_split(amode, M, K);

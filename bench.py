@@ -390,6 +390,26 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
     except Exception as exc:
         out.append({"workload": "3-layer MLP batch 16384", "error": repr(exc)})
 
+    # W8A32 at bs=1: the case the reference's quantised path exists for (int8 weights streamed once)
+    try:
+        w8 = [torch.randint(-127, 128, (4096, 4096), device="cuda", dtype=torch.int8) for _ in range(16)]   # 256 MiB > L2
+        x1, o1 = uniform((1, 4096)), torch.empty((1, 4096), device="cuda")
+        st8 = {"i": 0}
+
+        def qv():
+            eng.qgemm_w8a32(x1, w8[st8["i"] % 16], s3, o1)
+            st8["i"] += 1
+        step_ms, core_ms, _ = core_time(qv, 64, 8)
+        nb = 4096 * 4096 + 3 * 4096 * 4
+        out.append({"workload": "W8A32 GEMV bs=1, int8 W[4096x4096] (rotating 16 weight buffers)", "value": nb / (step_ms * 1e-3) / 1e9,
+                    "unit": "GB/s", "ms_per_step": step_ms, "kernel_ms": core_ms,
+                    "roofline": {"bound": "hbm", "achieved": nb / (core_ms * 1e-3) / 1e9, "peak": hbm,
+                                 "frac": nb / (core_ms * 1e-3) / 1e9 / hbm, "peak_source": f"{peaks['source']} HBM copy bandwidth",
+                                 "note": "eager calls from Python: launch-bound at this size"}})
+        del w8
+    except Exception as exc:
+        out.append({"workload": "W8A32 GEMV bs=1", "error": repr(exc)})
+
     # causal attention B=8,H=16,S=1024,dk=64 (BASELINE config 4); FLOPs by the reference's 4*BH*S^2*dk convention
     BH, S, dk = 128, 1024, 64
     Q, Kt, V = (torch.randn((BH, S, dk), device="cuda") for _ in range(3))

@@ -229,7 +229,8 @@ def test_quantize_rows_bit_exact(engine, oracle, shape):
     np.testing.assert_array_equal(host(q), q_ref)
 
 
-@pytest.mark.parametrize("shape", [(1, 8, 8), (4, 16, 32), (8, 64, 128), (32, 128, 512), (16, 256, 1024), (512, 1024, 1024)])
+@pytest.mark.parametrize("shape", [(1, 8, 8), (4, 16, 32), (8, 64, 128), (32, 128, 512), (16, 256, 1024), (512, 1024, 1024),
+                                   (1, 4096, 4096), (3, 1000, 2048), (8, 4096, 4096)])
 def test_w8a32_vs_oracle_and_golden(engine, oracle, golden, shape):
     M, N, K = shape
     a, w = oracle.uniform((M, K), 7), oracle.uniform((N, K), 13)
