@@ -579,7 +579,7 @@ extern "C" int axb_qgemm_w8a32(const float *a, const int8_t *q, const float *sca
     int st = ensure_ready();
     if (st) return st;
     if (M == 0) return AXB_OK;
-    if (qgemv_w8a32_applicable(M, N, K, q)) {
+    if (qgemv_w8a32_applicable(M, N, K, q) && (reinterpret_cast<uintptr_t>(a) & 15) == 0) {
         // skinny activations: stream the int8 rows once, fp32 FMA (the reference's own arithmetic)
         mark(0);
         mark(1);

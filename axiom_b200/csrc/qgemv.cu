@@ -14,63 +14,98 @@ namespace axb {
 static constexpr int QV_THREADS = 256;
 static constexpr int QV_WARPS = 8;
 
+// int8 -> fp32 without the conversion pipe: flip the sign bits (s + 128 as an unsigned byte), drop the byte
+// into the mantissa of 2^23 and subtract 2^23 + 128.  Exact for every int8 value.
 __device__ __forceinline__ void unpack16(const uint4 &w, float (&f)[16])
 {
-    const uint32_t v[4] = { w.x, w.y, w.z, w.w };
+    const uint32_t v[4] = { w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u };
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        f[4 * i + 0] = (float)(int8_t)(v[i] & 0xff);
-        f[4 * i + 1] = (float)(int8_t)((v[i] >> 8) & 0xff);
-        f[4 * i + 2] = (float)(int8_t)((v[i] >> 16) & 0xff);
-        f[4 * i + 3] = (float)(int8_t)(v[i] >> 24);
+        f[4 * i + 0] = __uint_as_float(__byte_perm(v[i], 0x4B000000u, 0x7540)) - 8388736.0f;
+        f[4 * i + 1] = __uint_as_float(__byte_perm(v[i], 0x4B000000u, 0x7541)) - 8388736.0f;
+        f[4 * i + 2] = __uint_as_float(__byte_perm(v[i], 0x4B000000u, 0x7542)) - 8388736.0f;
+        f[4 * i + 3] = __uint_as_float(__byte_perm(v[i], 0x4B000000u, 0x7543)) - 8388736.0f;
     }
 }
 
-// K % 16 == 0, q 16-byte aligned.  Shared memory: a as [MT][K] floats.
+static constexpr int QV_UNROLL = 8;   // 128-bit weight loads a lane keeps in flight
+
+// K % 16 == 0, q 16-byte aligned, a 16-byte aligned.  Shared memory: a as [MT][K] floats.
 template <int MT>
 __global__ void __launch_bounds__(QV_THREADS) qgemv_w8a32_kernel(const float *__restrict__ a,
                                                                  const int8_t *__restrict__ q,
                                                                  const float *__restrict__ scales,
-                                                                 float *__restrict__ out, int M, int64_t N, int64_t K)
+                                                                 float *__restrict__ out, int M, int64_t N, int K)
 {
     extern __shared__ __align__(16) float xs[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int pieces = K >> 4;                             // 16-element pieces per row
+    const int64_t row_stride = (int64_t)gridDim.x * QV_WARPS;
+    int64_t n = (int64_t)blockIdx.x * QV_WARPS + warp;
+
+    // the first weight loads leave before the activations are staged
+    uint4 w[QV_UNROLL];
+    if (n < N) {
+        const uint4 *row = reinterpret_cast<const uint4 *>(q + n * (int64_t)K);
+#pragma unroll
+        for (int u = 0; u < QV_UNROLL; ++u) {
+            const int p = lane + 32 * u;
+            w[u] = p < pieces ? __ldcs(row + p) : make_uint4(0, 0, 0, 0);
+        }
+    }
+
     // activations as [MT][K]; inside every 16-element piece p the four float4 are rotated by p/2 so that the
     // lanes of a quarter-warp (consecutive pieces, 64 bytes apart) hit eight different bank groups
-    for (int64_t i = tid; i < (int64_t)MT * K; i += QV_THREADS) {
-        const int m = (int)(i / K);
-        const int64_t k = i - (int64_t)m * K, pc = k >> 4;
-        const int j = (int)((k >> 2) & 3), e = (int)(k & 3);
-        xs[(int64_t)m * K + pc * 16 + (((j + (int)(pc >> 1)) & 3) << 2) + e] = m < M ? __ldg(a + i) : 0.0f;
-    }
-    __syncthreads();
-
-    const int64_t pieces = K / 16;                         // 16-element pieces per row
-    const int64_t row_stride = (int64_t)gridDim.x * QV_WARPS;
-    for (int64_t n = (int64_t)blockIdx.x * QV_WARPS + warp; n < N; n += row_stride) {
-        const uint4 *row = reinterpret_cast<const uint4 *>(q + n * K);
-        float acc[MT];
-#pragma unroll
-        for (int m = 0; m < MT; ++m) acc[m] = 0.0f;
-        for (int64_t p0 = lane; p0 < pieces; p0 += 32 * 4) {
-            uint4 w[4];
+    {
+        const int k4n = K >> 2, total = MT * k4n;
+        float4 *xs4 = reinterpret_cast<float4 *>(xs);
+        for (int i0 = tid; i0 < total; i0 += QV_THREADS * 4) {
+            float4 v[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const int64_t p = p0 + 32 * u;
-                w[u] = p < pieces ? __ldcs(row + p) : make_uint4(0, 0, 0, 0);
+                const int i = i0 + u * QV_THREADS;
+                const int m = i / k4n;
+                v[u] = (i < total && m < M) ? __ldg(reinterpret_cast<const float4 *>(a) + i)
+                                            : make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-                const int64_t p = p0 + 32 * u;
+                const int i = i0 + u * QV_THREADS;
+                if (i < total) {
+                    const int m = i / k4n, k4 = i - m * k4n, pc = k4 >> 2, j = k4 & 3;
+                    xs4[m * k4n + pc * 4 + ((j + (pc >> 1)) & 3)] = v[u];
+                }
+            }
+        }
+    }
+    __syncthreads();
+
+    for (; n < N; n += row_stride) {
+        const uint4 *row = reinterpret_cast<const uint4 *>(q + n * (int64_t)K);
+        float acc[MT];
+#pragma unroll
+        for (int m = 0; m < MT; ++m) acc[m] = 0.0f;
+#pragma unroll 1
+        for (int p0 = lane; p0 < pieces; p0 += 32 * QV_UNROLL) {
+            if (p0 != lane) {
+#pragma unroll
+                for (int u = 0; u < QV_UNROLL; ++u) {
+                    const int p = p0 + 32 * u;
+                    w[u] = p < pieces ? __ldcs(row + p) : make_uint4(0, 0, 0, 0);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < QV_UNROLL; ++u) {
+                const int p = p0 + 32 * u;
                 if (p < pieces) {
                     float f[16];
                     unpack16(w[u], f);
 #pragma unroll
                     for (int m = 0; m < MT; ++m) {
-                        const float4 *xv = reinterpret_cast<const float4 *>(xs + (int64_t)m * K + p * 16);
+                        const float4 *xv = reinterpret_cast<const float4 *>(xs + m * K + p * 16);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            const float4 x4 = xv[(j + (int)(p >> 1)) & 3];
+                            const float4 x4 = xv[(j + (p >> 1)) & 3];
                             acc[m] = fmaf(x4.x, f[4 * j + 0], acc[m]);
                             acc[m] = fmaf(x4.y, f[4 * j + 1], acc[m]);
                             acc[m] = fmaf(x4.z, f[4 * j + 2], acc[m]);
@@ -78,6 +113,16 @@ __global__ void __launch_bounds__(QV_THREADS) qgemv_w8a32_kernel(const float *__
                         }
                     }
                 }
+            }
+        }
+        // the next row's first loads go out before this row's reduction
+        const int64_t nn = n + row_stride;
+        if (nn < N) {
+            const uint4 *nrow = reinterpret_cast<const uint4 *>(q + nn * (int64_t)K);
+#pragma unroll
+            for (int u = 0; u < QV_UNROLL; ++u) {
+                const int p = lane + 32 * u;
+                w[u] = p < pieces ? __ldcs(nrow + p) : make_uint4(0, 0, 0, 0);
             }
         }
         const float sc = __ldg(scales + n);
@@ -96,7 +141,7 @@ bool qgemv_w8a32_applicable(int64_t M, int64_t N, int64_t K, const void *q)
     (void)N;
     const int64_t mt = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
     return M >= 1 && M <= 8 && K % 16 == 0 && K * mt * 4 <= 160 * 1024 &&
-           (reinterpret_cast<uintptr_t>(q) & 15) == 0;
+           (reinterpret_cast<uintptr_t>(q) & 15) == 0;   // the caller checks the activations' alignment
 }
 
 template <int MT>
@@ -115,7 +160,7 @@ static int launch_qv(const float *a, const int8_t *q, const float *scales, float
     int64_t blocks = (N + QV_WARPS - 1) / QV_WARPS;
     const int64_t cap = (int64_t)sm_count * (smem > 48 * 1024 ? 2 : 4);
     if (blocks > cap) blocks = cap;
-    k<<<(unsigned)blocks, QV_THREADS, smem, st>>>(a, q, scales, out, M, N, K);
+    k<<<(unsigned)blocks, QV_THREADS, smem, st>>>(a, q, scales, out, M, N, (int)K);
     return (int)cudaGetLastError();
 }
 
