@@ -420,6 +420,34 @@ int encode_f32_matrix_tmap(void *tmap_out, const float *ptr, int64_t rows, int64
     return 0;
 }
 
+// fp32 planes [batch][rows][pitch] with `cols` valid elements per row, 128-byte swizzle, box = 32 x box_rows x 1.
+// Rows past `rows` inside a batch entry and columns past `cols` read as zero.  atom32: swizzle 32-byte chunks
+// (the layout an MN-major tf32 MMA operand needs) instead of 16-byte chunks.
+int encode_f32_batched_tmap(void *tmap_out, const void *ptr, int64_t batch, int64_t rows, int64_t cols,
+                            int64_t pitch_elems, int box_rows, bool atom32)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled entry point not found");
+        return (int)cudaErrorSymbolNotFound;
+    }
+    cuuint64_t dims[3] = { (cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch };
+    cuuint64_t strides[2] = { (cuuint64_t)pitch_elems * 4, (cuuint64_t)rows * (cuuint64_t)pitch_elems * 4 };
+    cuuint32_t box[3] = { 32, (cuuint32_t)box_rows, 1 };
+    cuuint32_t estr[3] = { 1, 1, 1 };
+    CUresult r = fn(reinterpret_cast<CUtensorMap *>(tmap_out), CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3,
+                    const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_err, sizeof g_err,
+                 "cuTensorMapEncodeTiled (batched planes) failed (%d): ptr=%p batch=%lld rows=%lld cols=%lld pitch=%lld",
+                 (int)r, ptr, (long long)batch, (long long)rows, (long long)cols, (long long)pitch_elems);
+        return (int)cudaErrorInvalidValue;
+    }
+    return 0;
+}
+
 template <int KIND, int BN, int SWB, int NPROD>
 static int launch_inst(const TmapPack &tm, KernelArgs &ka, int stage_bytes, int grid, cudaStream_t stream)
 {

@@ -58,4 +58,10 @@ const char *gemm_tc_last_error();
 int encode_f32_matrix_tmap(void *tmap_out, const float *ptr, int64_t rows, int64_t cols, int64_t pitch_elems,
                            int box_cols, int box_rows);
 
+// Tiled tensor map over fp32 planes [batch][rows][pitch_elems] (cols valid elements per row), 128-byte swizzle,
+// box = 32 elements x box_rows x 1; out-of-range rows / columns read as zero.  atom32 selects the variant of
+// the swizzle that moves 32-byte chunks (for MN-major tf32 MMA operands).
+int encode_f32_batched_tmap(void *tmap_out, const void *ptr, int64_t batch, int64_t rows, int64_t cols,
+                            int64_t pitch_elems, int box_rows, bool atom32);
+
 }  // namespace axb

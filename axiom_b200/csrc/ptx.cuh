@@ -232,6 +232,79 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n)
            ((uint32_t)(m >> 4) << 24);
 }
 
+// 3-D tiled load (innermost coordinate first); same alignment rule as the 2-D form.
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tmap, uint32_t bar, int32_t crd0,
+                                            int32_t crd1, int32_t crd2)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5}], [%2];"
+        :
+        : "r"(dst), "l"(tmap), "r"(bar), "r"(crd0), "r"(crd1), "r"(crd2)
+        : "memory");
+}
+
+// D[tmem] (+)= A[tmem] . B[smem]: the A operand is read from tensor memory (128 lanes = rows,
+// consecutive 32-bit columns = K), B through a shared-memory descriptor.  kind::tf32.
+__device__ __forceinline__ void tc_mma_ts_tf32(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t}"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate));
+}
+
+// registers -> tensor memory, the mirror image of tmem_ld_32x32
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        :
+        : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_st_wait()
+{
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory descriptor for an MN-major tf32 operand tile: rows of 128 bytes run along M/N (32 elements),
+// consecutive K indices are consecutive rows, and the 128-byte swizzle moves 32-byte chunks by (row % 4) — the
+// only layout an MN-major 32-bit operand may have (TMA: the 128B swizzle with 32-byte atoms).  A swizzle atom is
+// 4 rows.  lbo_bytes: distance between 128-byte column groups along M/N; sbo_bytes: distance between 4-row K
+// groups.  Layout type 1 in bits [61,64).
+__device__ __forceinline__ uint64_t smem_desc_mnmajor_sw128_32b(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes)
+{
+    uint64_t d = (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)1 << 61;
+    return d;
+}
+
+__device__ __forceinline__ float ex2_approx(float x)
+{
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__device__ __forceinline__ float tf32_rna(float x)
+{
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
 }  // namespace axb
 
 // ---------------------------------------------------------------------------
