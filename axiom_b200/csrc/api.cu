@@ -709,7 +709,7 @@ extern "C" int axb_sdpa_fwd(const float *Q, const float *K, const float *V, floa
     if (st) return st;
     if (BH == 0 || S == 0) return AXB_OK;
     static const int route_env = [] { const char *e = getenv("AX_B200_SDPA"); return e ? (strcmp(e, "fma") == 0 ? 1 : 2) : 0; }();
-    if (route_env != 1 && sdpa_tc_applicable(BH, S, dk)) {
+    if (route_env != 1 && sdpa_tc_applicable(BH, S, dk, scale)) {
         // tensor cores: split pre-pass into the scratch arena, then the fused kernel
         st = ensure_ws(sdpa_tc_workspace_bytes(BH, S, dk));
         if (st) return st;

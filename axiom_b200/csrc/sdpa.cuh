@@ -11,7 +11,7 @@ int launch_sdpa_fwd(const float *Q, const float *K, const float *V, float *O, fl
 // Tensor-core route (sdpa_tc.cu): head dim <= 64.  The split pre-pass writes six tf32 planes (Q, K, V as hi/lo)
 // into `workspace` (sdpa_tc_workspace_bytes); the attention kernel reads them through TMA.  A bounded wait that
 // runs out inside the kernel is reported through *err_word.
-bool sdpa_tc_applicable(int64_t BH, int64_t S, int64_t dk);
+bool sdpa_tc_applicable(int64_t BH, int64_t S, int64_t dk, float scale);
 size_t sdpa_tc_workspace_bytes(int64_t BH, int64_t S, int64_t dk);
 int launch_sdpa_tc_split(const float *Q, const float *K, const float *V, int64_t BH, int64_t S, int64_t dk,
                          void *workspace, int sm_count, cudaStream_t st);
