@@ -709,17 +709,12 @@ extern "C" int axb_sdpa_fwd(const float *Q, const float *K, const float *V, floa
     if (st) return st;
     if (BH == 0 || S == 0) return AXB_OK;
     static const int route_env = [] { const char *e = getenv("AX_B200_SDPA"); return e ? (strcmp(e, "fma") == 0 ? 1 : 2) : 0; }();
-    if (route_env != 1 && sdpa_tc_applicable(BH, S, dk, scale)) {
-        // tensor cores: split pre-pass into the scratch arena, then the fused kernel
-        st = ensure_ws(sdpa_tc_workspace_bytes(BH, S, dk));
-        if (st) return st;
+    if (route_env != 1 && sdpa_tc_applicable(Q, K, V, BH, S, dk, scale)) {
         mark(0);
-        int e = launch_sdpa_tc_split(Q, K, V, BH, S, dk, g.ws, g.sm_count, g.stream);
-        if (e) return cuda_fail("sdpa_fwd split", e);
         mark(1);
-        e = launch_sdpa_tc(g.ws, out, L, BH, S, dk, scale, causal, g.err_word, g.stream);
+        int e = launch_sdpa_tc(Q, K, V, out, L, BH, S, dk, scale, causal, g.err_word, g.stream);
         mark(2);
-        g.launches += 2;
+        g.launches++;
         return e ? cuda_fail("sdpa_fwd", e) : AXB_OK;
     }
     mark(0);

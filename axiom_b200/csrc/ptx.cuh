@@ -244,6 +244,14 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tmap, uint
         : "memory");
 }
 
+// Ask for a tile to be brought into L2 (no shared-memory destination, no completion to wait for).
+__device__ __forceinline__ void tma_prefetch_3d(const void *tmap, int32_t crd0, int32_t crd1, int32_t crd2)
+{
+    asm volatile("cp.async.bulk.prefetch.tensor.3d.L2.global [%0, {%1, %2, %3}];" ::"l"(tmap), "r"(crd0), "r"(crd1),
+                 "r"(crd2)
+                 : "memory");
+}
+
 // D[tmem] (+)= A[tmem] . B[smem]: the A operand is read from tensor memory (128 lanes = rows,
 // consecutive 32-bit columns = K), B through a shared-memory descriptor.  kind::tf32.
 __device__ __forceinline__ void tc_mma_ts_tf32(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,

@@ -39,7 +39,9 @@ __global__ void __launch_bounds__(SD_THREADS) sdpa_fwd_kernel(const float *__res
     const float *Kh = K + head * (int64_t)S * dk;
     const float *Vh = V + head * (int64_t)S * dk;
     const int q0 = qb * BQ;
-    const bool vec = (dk % 4 == 0);
+    // 128-bit accesses need rows that are multiples of 16 bytes on 16-byte aligned bases
+    const bool vec = (dk % 4 == 0) && (((reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(K) |
+                                         reinterpret_cast<uintptr_t>(V) | reinterpret_cast<uintptr_t>(O)) & 15) == 0);
 
     // Q block -> shared (rows past S and columns past dk are zero)
     for (int i = tid; i < BQ * (DKP / 4); i += SD_THREADS) {

@@ -5,22 +5,28 @@
 // result at fp32 accuracy (the reference computes this path in fp32, src/compute/backends/cpu_opt.c:7828-8071;
 // its CUDA path uses one TF32 product and a materialised S x S buffer, cuda/ops_attention.cu:224-392).
 //
-// A pre-pass splits Q, K and V into planes [BH][S][pitch].  One CTA owns 128 query rows of one head and walks
+// There is no pre-pass and no scratch: TMA loads the caller's fp32 tiles straight into the place of the hi
+// plane, and converter warps split them where they lie (hi = the value cut to tf32, written back; lo = the
+// exact remainder, rounded to tf32, written to the lo plane at the same swizzled offset).  Loading planes that
+// a pre-pass had split cost 8 bytes per element from L2 for every key block of every query tile — the kernel
+// was L2-bound on it — plus a pass over HBM; this costs 4.  One CTA owns 128 query rows of one head and walks
 // the keys in blocks of 128:
-//   warp 4  : TMA producer — the Q tile once, then one K and one V block at a time (128-byte swizzle; V with
-//             the 32-byte-chunk variant, the one layout an MN-major tf32 operand may have);
-//   warp 5  : one thread issues tcgen05.mma.  S_j = Q.K_j^T (M128 x N128, operands from shared memory, both
-//             K-major) goes to one of two TMEM score buffers; O_j = P_j.V_j takes P from TENSOR MEMORY (the TS
-//             form) and V as an MN-major shared-memory operand, i.e. exactly as the TMA load leaves it — V is
-//             never transposed.  N = 128 runs the tf32 pipe at its full rate (N = 64 does not: measured 48
-//             cycles per instruction instead of 32), which is why the key block is 128 wide;
+//   warp 4   : TMA producer — the Q tile once, then one K and one V block at a time (128-byte swizzle; V with
+//              the 32-byte-chunk variant, the one layout an MN-major tf32 operand may have);
+//   warps 6-9: converters (above);
+//   warp 5   : one thread issues tcgen05.mma.  S_j = Q.K_j^T (M128 x N128, operands from shared memory, both
+//              K-major) goes to one of two TMEM score buffers; O_j = P_j.V_j takes P from TENSOR MEMORY (the
+//              TS form) and V as an MN-major shared-memory operand, i.e. exactly as the TMA load leaves it — V
+//              is never transposed.  N = 128 runs the tf32 pipe at its full rate (N = 64 does not: measured
+//              48 cycles per instruction instead of 32), which is why the key block is 128 wide;
 //   warps 0-3: thread t owns query row t.  Pass 1 reads the score row from TMEM in 32-column chunks and takes
-//             the maximum; pass 2 re-reads it, forms p = 2^(c*s - m), and writes P back as tf32 hi (over the
-//             scores it came from) and lo (a third buffer).  Every block's O_j lands in a fresh accumulator
-//             (the tensor core's truncating accumulation never spans more than one block) and is folded into
-//             the thread's fp32 register row with the usual rescale.  The chunk loops are rolled: the body
-//             stays small enough for the instruction cache, which a fully unrolled row (the first version)
-//             did not — its warps spent most of their time waiting for instructions.
+//              the maximum; pass 2 re-reads it, forms p = 2^(c*s - m), and writes P back as tf32 hi (over the
+//              scores it came from) and lo (a third buffer).  Every block's O_j lands in a fresh accumulator
+//              (the tensor core's truncating accumulation never spans more than one block) and is folded into
+//              the thread's fp32 register row with the usual rescale.  The chunk loops are rolled: the body
+//              stays small enough for the instruction cache, which a fully unrolled row (the first version)
+//              did not — its warps spent most of their time waiting for instructions.  The split of P uses
+//              integer masking, not cvt: conversions share the 16-lane pipe with ex2 and halved its rate.
 // The score matrix never leaves the SM.  Issue order S_0 S_1 O_0 S_2 O_1 ...: the pipe computes the next
 // block's scores while the softmax warps work on this one; in-order execution of the MMAs is what makes the
 // score buffer (aliased by P hi) safe to overwrite two blocks later.
@@ -34,12 +40,12 @@
 
 namespace axb {
 
-static constexpr int TQ = 128, TKV = 128, ST_THREADS = 192;
+static constexpr int TQ = 128, TKV = 128, ST_THREADS = 320;
 static constexpr int ST_HEADER = 1024;
 static constexpr int SLAB = 128 * 128;  // bytes of one 32-column slab of a 128-row tile
 
 struct alignas(64) SdpaTmaps {
-    CUtensorMap q[2], k[2], v[2];  // hi, lo
+    CUtensorMap q, k, v;  // the caller's fp32 tensors [BH][S][dk]
 };
 
 struct SdpaTcArgs {
@@ -52,7 +58,7 @@ struct SdpaTcArgs {
     int *err;
 };
 
-enum { SERR_PRODUCER = 11, SERR_MMA = 12, SERR_SOFTMAX = 13 };
+enum { SERR_PRODUCER = 11, SERR_MMA = 12, SERR_SOFTMAX = 13, SERR_CONVERT = 14 };
 
 __device__ __forceinline__ void report_err(int *err, int code)
 {
@@ -60,8 +66,8 @@ __device__ __forceinline__ void report_err(int *err, int code)
 }
 
 enum {
-    B_Q_FULL = 0, B_K_FULL = 1, B_K_EMPTY = 2, B_V_FULL = 3, B_V_EMPTY = 4,
-    B_S_FULL = 5, B_P_FULL = 7, B_O_FULL = 9, B_O_EMPTY = 11, B_COUNT = 13
+    B_Q_RAW = 0, B_Q_FULL = 1, B_K_RAW = 2, B_K_FULL = 3, B_K_EMPTY = 4, B_V_RAW = 5, B_V_FULL = 6, B_V_EMPTY = 7,
+    B_S_FULL = 8, B_P_FULL = 10, B_O_FULL = 12, B_O_EMPTY = 14, B_COUNT = 16
 };
 
 // TMEM columns: two score buffers (P hi is written over the scores), P lo, two output buffers
@@ -106,15 +112,17 @@ __device__ __forceinline__ float row_max(uint32_t s_addr, int k0, int gi, int S,
     return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 }
 
-// p = 2^(c*s - m) for one row; P hi over the scores, P lo at plo_addr; returns the row sum
+// p = 2^(c*s - m) for one row, written over the scores it came from as full fp32: the tensor core reads
+// the tf32 part of a 32-bit container and ignores the 13 low mantissa bits, so this IS the hi operand.
+// Returns the row sum.
 template <bool MASK>
-__device__ __forceinline__ float row_exp(uint32_t s_addr, uint32_t plo_addr, float c_log2, float neg_m, int k0,
-                                         int gi, int S, int causal)
+__device__ __forceinline__ float row_exp(uint32_t s_addr, float c_log2, float neg_m, int k0, int gi, int S,
+                                         int causal)
 {
     float sum[4] = { 0.f, 0.f, 0.f, 0.f };
 #pragma unroll 1
     for (int c0 = 0; c0 < TKV; c0 += 32) {
-        uint32_t r[32], lo[32];
+        uint32_t r[32];
         tmem_ld_32x32(s_addr + c0, r);
         tmem_ld_wait();
 #pragma unroll
@@ -125,15 +133,28 @@ __device__ __forceinline__ float row_exp(uint32_t s_addr, uint32_t plo_addr, flo
                 if ((causal && gj > gi) || gj >= S) p = 0.f;
             }
             sum[c & 3] += p;
-            const float ph = tf32_rna(p);
-            r[c] = __float_as_uint(ph);
-            lo[c] = __float_as_uint(p - ph);
+            r[c] = __float_as_uint(p);
         }
         tmem_st_32x32(s_addr + c0, r);
-        tmem_st_32x32(plo_addr + c0, lo);
     }
     tmem_st_wait();
     return (sum[0] + sum[1]) + (sum[2] + sum[3]);
+}
+
+// P lo = p - (p cut to tf32), exact, for one row
+__device__ __forceinline__ void row_lo(uint32_t s_addr, uint32_t plo_addr)
+{
+#pragma unroll 1
+    for (int c0 = 0; c0 < TKV; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(s_addr + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+            r[c] = __float_as_uint(__uint_as_float(r[c]) - __uint_as_float(r[c] & 0xFFFFE000u));
+        tmem_st_32x32(plo_addr + c0, r);
+    }
+    tmem_st_wait();
 }
 
 template <int NSLAB>
@@ -163,10 +184,13 @@ __global__ void __launch_bounds__(ST_THREADS, 1) sdpa_tc_kernel(const __grid_con
     const int nb = (kv_end + TKV - 1) / TKV;
 
     if (threadIdx.x == 0) {
-        mbar_init(bar(B_Q_FULL), 1);
-        mbar_init(bar(B_K_FULL), 1);
+        mbar_init(bar(B_Q_RAW), 1);
+        mbar_init(bar(B_Q_FULL), 128);
+        mbar_init(bar(B_K_RAW), 1);
+        mbar_init(bar(B_K_FULL), 128);
         mbar_init(bar(B_K_EMPTY), 1);
-        mbar_init(bar(B_V_FULL), 1);
+        mbar_init(bar(B_V_RAW), 1);
+        mbar_init(bar(B_V_FULL), 128);
         mbar_init(bar(B_V_EMPTY), 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar(B_S_FULL + b), 1);
@@ -181,9 +205,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) sdpa_tc_kernel(const __grid_con
         tmem_relinquish();
     }
     if (warp == 4 && lane == 0) {
-        tma_prefetch_desc(&tm.q[0]); tma_prefetch_desc(&tm.q[1]);
-        tma_prefetch_desc(&tm.k[0]); tma_prefetch_desc(&tm.k[1]);
-        tma_prefetch_desc(&tm.v[0]); tma_prefetch_desc(&tm.v[1]);
+        tma_prefetch_desc(&tm.q);
+        tma_prefetch_desc(&tm.k);
+        tma_prefetch_desc(&tm.v);
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -193,22 +217,20 @@ __global__ void __launch_bounds__(ST_THREADS, 1) sdpa_tc_kernel(const __grid_con
     if (warp == 4) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
-            mbar_arrive_expect_tx(bar(B_Q_FULL), TILE);
+            mbar_arrive_expect_tx(bar(B_Q_RAW), PLANE);
 #pragma unroll
-            for (int pl = 0; pl < 2; ++pl)
-#pragma unroll
-                for (int s = 0; s < NSLAB; ++s)
-                    tma_load_3d(q_smem + pl * PLANE + s * SLAB, &tm.q[pl], bar(B_Q_FULL), 32 * s, q0, head);
+            for (int sl = 0; sl < NSLAB; ++sl) tma_load_3d(q_smem + sl * SLAB, &tm.q, bar(B_Q_RAW), 32 * sl, q0, head);
             // order K_0, K_1, V_0, K_2, V_1, ...: the K buffer frees early (its scores are computed one block
             // ahead), the V buffer only when the previous block's P.V has finished
             auto load_k = [&](int j) -> bool {
                 if (j >= 1 && !mbar_wait_bounded(bar(B_K_EMPTY), (j - 1) & 1)) return false;
-                mbar_arrive_expect_tx(bar(B_K_FULL), TILE);
+                mbar_arrive_expect_tx(bar(B_K_RAW), PLANE);
 #pragma unroll
-                for (int pl = 0; pl < 2; ++pl)
+                for (int sl = 0; sl < NSLAB; ++sl) tma_load_3d(k_smem + sl * SLAB, &tm.k, bar(B_K_RAW), 32 * sl, j * TKV, head);
+                if (j + 1 < nb) {   // the block after this one: into L2 now, so its load is short when its turn comes
 #pragma unroll
-                    for (int s = 0; s < NSLAB; ++s)
-                        tma_load_3d(k_smem + pl * PLANE + s * SLAB, &tm.k[pl], bar(B_K_FULL), 32 * s, j * TKV, head);
+                    for (int sl = 0; sl < NSLAB; ++sl) tma_prefetch_3d(&tm.k, 32 * sl, (j + 1) * TKV, head);
+                }
                 return true;
             };
             bool ok = load_k(0);
@@ -216,15 +238,58 @@ __global__ void __launch_bounds__(ST_THREADS, 1) sdpa_tc_kernel(const __grid_con
                 if (j + 1 < nb) ok = load_k(j + 1);
                 if (!ok) break;
                 if (j >= 1 && !mbar_wait_bounded(bar(B_V_EMPTY), (j - 1) & 1)) { ok = false; break; }
-                mbar_arrive_expect_tx(bar(B_V_FULL), TILE);
+                mbar_arrive_expect_tx(bar(B_V_RAW), PLANE);
 #pragma unroll
-                for (int pl = 0; pl < 2; ++pl)
+                for (int sl = 0; sl < NSLAB; ++sl) tma_load_3d(v_smem + sl * SLAB, &tm.v, bar(B_V_RAW), 32 * sl, j * TKV, head);
+                if (j + 1 < nb) {
 #pragma unroll
-                    for (int s = 0; s < NSLAB; ++s)
-                        tma_load_3d(v_smem + pl * PLANE + s * SLAB, &tm.v[pl], bar(B_V_FULL), 32 * s, j * TKV, head);
+                    for (int sl = 0; sl < NSLAB; ++sl) tma_prefetch_3d(&tm.v, 32 * sl, (j + 1) * TKV, head);
+                }
             }
             if (!ok) report_err(a.err, SERR_PRODUCER);
         }
+    } else if (warp >= 6) {
+        // ---------------------------------------------------------- converters
+        // lo = tf32(x - (x cut to tf32)) at the same offset of the lo plane.  x itself stays where TMA put it and
+        // serves as the hi operand: the tensor core ignores the 13 low mantissa bits of a tf32 container
+        // (results are bit-identical with the cut value written back, which costs a third of the traffic).
+        const int ct = threadIdx.x - 192;  // 0..127
+        auto split_tile = [&](uint32_t tile) {
+#pragma unroll 4
+            for (int i = ct; i < (int)(PLANE / 16); i += 128) {
+                const uint32_t addr = tile + (uint32_t)i * 16u;
+                uint32_t x0, x1, x2, x3;
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(addr));
+                const uint32_t h0 = x0 & 0xFFFFE000u, h1 = x1 & 0xFFFFE000u, h2 = x2 & 0xFFFFE000u, h3 = x3 & 0xFFFFE000u;
+                // remainder (exact), rounded to tf32 by adding half an ulp of its 13 dropped bits
+                const uint32_t l0 = (__float_as_uint(__uint_as_float(x0) - __uint_as_float(h0)) + 0x1000u) & 0xFFFFE000u;
+                const uint32_t l1 = (__float_as_uint(__uint_as_float(x1) - __uint_as_float(h1)) + 0x1000u) & 0xFFFFE000u;
+                const uint32_t l2 = (__float_as_uint(__uint_as_float(x2) - __uint_as_float(h2)) + 0x1000u) & 0xFFFFE000u;
+                const uint32_t l3 = (__float_as_uint(__uint_as_float(x3) - __uint_as_float(h3)) + 0x1000u) & 0xFFFFE000u;
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr + PLANE), "r"(l0), "r"(l1), "r"(l2), "r"(l3) : "memory");
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the MMA
+        };
+        bool ok = wait_warp(bar(B_Q_RAW), 0);
+        if (ok) {
+            split_tile(q_smem);
+            mbar_arrive(bar(B_Q_FULL));
+        }
+        auto do_k = [&](int j) -> bool {
+            if (!wait_warp(bar(B_K_RAW), j & 1)) return false;
+            split_tile(k_smem);
+            mbar_arrive(bar(B_K_FULL));
+            return true;
+        };
+        ok = ok && do_k(0);
+        for (int j = 0; ok && j < nb; ++j) {
+            if (j + 1 < nb) ok = do_k(j + 1);
+            if (!ok) break;
+            if (!wait_warp(bar(B_V_RAW), j & 1)) { ok = false; break; }
+            split_tile(v_smem);
+            mbar_arrive(bar(B_V_FULL));
+        }
+        if (!ok) report_err(a.err, SERR_CONVERT);
     } else if (warp == 5) {
         // ---------------------------------------------------------- MMA issuer
         if (lane == 0) {
@@ -346,18 +411,21 @@ __global__ void __launch_bounds__(ST_THREADS, 1) sdpa_tc_kernel(const __grid_con
             const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
             const float corr = ex2_approx(m - m_safe);  // 0 on the first block
             PROF_ADD(1)
-            // P lo is a single buffer: the previous block's P.V must have finished reading it
-            if (j > 0 && !wait_warp(bar(B_O_FULL + ((j - 1) & 1)), ((j - 1) >> 1) & 1)) { ok = false; break; }
+            const float sum = need_mask ? row_exp<true>(s_addr, a.c_log2, -m_safe, k0, gi, a.S, a.causal)
+                                        : row_exp<false>(s_addr, a.c_log2, -m_safe, k0, gi, a.S, a.causal);
             PROF_ADD(2)
-            const float sum = need_mask ? row_exp<true>(s_addr, lane_base + T_PLO, a.c_log2, -m_safe, k0, gi, a.S, a.causal)
-                                        : row_exp<false>(s_addr, lane_base + T_PLO, a.c_log2, -m_safe, k0, gi, a.S, a.causal);
+            // P lo is a single buffer: the previous block's P.V must have finished reading it.  Only this
+            // short pass sits between that P.V and the next one; the exponentials above overlap it.
+            if (j > 0 && !wait_warp(bar(B_O_FULL + ((j - 1) & 1)), ((j - 1) >> 1) & 1)) { ok = false; break; }
+            PROF_ADD(3)
+            row_lo(s_addr, lane_base + T_PLO);
             tc_fence_before_sync();
             mbar_arrive(bar(B_P_FULL + b));
             l = l * corr + sum;
             m = m_new;
-            PROF_ADD(3)
-            if (j > 0) fold(j - 1, corr);
             PROF_ADD(4)
+            if (j > 0) fold(j - 1, corr);
+            PROF_ADD(5)
         }
         if (ok && nb > 0) {
             if (wait_warp(bar(B_O_FULL + ((nb - 1) & 1)), ((nb - 1) >> 1) & 1)) fold(nb - 1, 1.0f);
@@ -392,38 +460,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) sdpa_tc_kernel(const __grid_con
     }
 }
 
-// Q, K, V [rows, dk] -> hi/lo tf32 planes [rows, pitch] (pitch = dk rounded up to 4; pad columns zero)
-__global__ void __launch_bounds__(256) sdpa_split_kernel(const float *__restrict__ q, const float *__restrict__ k,
-                                                         const float *__restrict__ v, float *planes,
-                                                         int64_t plane_floats, int64_t rows, int dk, int pitch)
-{
-    const int t = blockIdx.y;
-    const float *src = t == 0 ? q : (t == 1 ? k : v);
-    float *hi = planes + (int64_t)(2 * t) * plane_floats, *lo = hi + plane_floats;
-    const int p4 = pitch / 4;
-    const int64_t total = rows * p4;
-    const bool vec = (dk % 4 == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t r = i / p4;
-        const int c = (int)(i - r * p4) * 4;
-        float x[4];
-        if (vec) {
-            const float4 w = __ldg(reinterpret_cast<const float4 *>(src + r * dk + c));
-            x[0] = w.x; x[1] = w.y; x[2] = w.z; x[3] = w.w;
-        } else {
-#pragma unroll
-            for (int e = 0; e < 4; ++e) x[e] = (c + e < dk) ? __ldg(src + r * dk + c + e) : 0.f;
-        }
-        float4 h, d;
-        h.x = tf32_rna(x[0]); d.x = tf32_rna(x[0] - h.x);
-        h.y = tf32_rna(x[1]); d.y = tf32_rna(x[1] - h.y);
-        h.z = tf32_rna(x[2]); d.z = tf32_rna(x[2] - h.z);
-        h.w = tf32_rna(x[3]); d.w = tf32_rna(x[3] - h.w);
-        *reinterpret_cast<float4 *>(hi + r * pitch + c) = h;
-        *reinterpret_cast<float4 *>(lo + r * pitch + c) = d;
-    }
-}
-
 // ---------------------------------------------------------------------- host
 
 #ifdef AXB_SDPA_PROF
@@ -433,19 +469,15 @@ extern "C" __attribute__((visibility("default"))) int axb_debug_sdpa_prof(unsign
 }
 #endif
 
-bool sdpa_tc_applicable(int64_t BH, int64_t S, int64_t dk, float scale)
+bool sdpa_tc_applicable(const float *Q, const float *K, const float *V, int64_t BH, int64_t S, int64_t dk,
+                        float scale)
 {
-    // scale > 0: the row maximum is taken over the raw scores and scaled afterwards
-    return dk >= 1 && dk <= 64 && S >= 128 && BH >= 1 && BH <= 65535 && scale > 0.f && scale < INFINITY;
+    // TMA reads the caller's tensors: rows must be multiples of 16 bytes on 16-byte aligned bases.
+    // scale > 0: the row maximum is taken over the raw scores and scaled afterwards.
+    const uintptr_t align = reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(K) | reinterpret_cast<uintptr_t>(V);
+    return dk >= 4 && dk <= 64 && dk % 4 == 0 && (align & 15) == 0 && S >= 128 && BH >= 1 && BH <= 65535 &&
+           scale > 0.f && scale < INFINITY;
 }
-
-static inline size_t plane_bytes(int64_t BH, int64_t S, int64_t dk)
-{
-    const int64_t pitch = (dk + 3) / 4 * 4;
-    return ((size_t)BH * S * pitch * 4 + 1023) / 1024 * 1024;
-}
-
-size_t sdpa_tc_workspace_bytes(int64_t BH, int64_t S, int64_t dk) { return 6 * plane_bytes(BH, S, dk); }
 
 template <int NSLAB>
 static int launch_inst(const SdpaTmaps &tm, const SdpaTcArgs &a, dim3 grid, cudaStream_t st)
@@ -463,40 +495,21 @@ static int launch_inst(const SdpaTmaps &tm, const SdpaTcArgs &a, dim3 grid, cuda
     return (int)cudaGetLastError();
 }
 
-int launch_sdpa_tc_split(const float *Q, const float *K, const float *V, int64_t BH, int64_t S, int64_t dk,
-                         void *workspace, int sm_count, cudaStream_t st)
+int launch_sdpa_tc(const float *Q, const float *K, const float *V, float *O, float *L, int64_t BH, int64_t S,
+                   int64_t dk, float scale, int causal, int *err_word, cudaStream_t st)
 {
-    const int pitch = (int)((dk + 3) / 4 * 4);
-    const size_t pb = plane_bytes(BH, S, dk);
-    const int64_t rows = BH * S;
-    int64_t blocks = (rows * (pitch / 4) + 255) / 256;
-    const int64_t cap = (int64_t)sm_count * 8;
-    if (blocks > cap) blocks = cap;
-    sdpa_split_kernel<<<dim3((unsigned)blocks, 3), 256, 0, st>>>(Q, K, V, reinterpret_cast<float *>(workspace),
-                                                                 (int64_t)(pb / 4), rows, (int)dk, pitch);
-    return (int)cudaGetLastError();
-}
-
-int launch_sdpa_tc(const void *workspace, float *O, float *L, int64_t BH, int64_t S, int64_t dk, float scale,
-                   int causal, int *err_word, cudaStream_t st)
-{
-    const int pitch = (int)((dk + 3) / 4 * 4);
-    const size_t pb = plane_bytes(BH, S, dk);
     SdpaTmaps tm;
-    for (int t = 0; t < 3; ++t)
-        for (int pl = 0; pl < 2; ++pl) {
-            CUtensorMap *dst = t == 0 ? &tm.q[pl] : (t == 1 ? &tm.k[pl] : &tm.v[pl]);
-            int e = encode_f32_batched_tmap(dst, reinterpret_cast<const char *>(workspace) + (size_t)(2 * t + pl) * pb, BH, S,
-                                            dk, pitch, 128, t == 2);
-            if (e) return e;
-        }
+    int e = encode_f32_batched_tmap(&tm.q, Q, BH, S, dk, dk, 128, false);
+    if (!e) e = encode_f32_batched_tmap(&tm.k, K, BH, S, dk, dk, 128, false);
+    if (!e) e = encode_f32_batched_tmap(&tm.v, V, BH, S, dk, dk, 128, true);
+    if (e) return e;
     SdpaTcArgs a;
     a.O = O; a.L = L;
     a.S = (int)S; a.dk = (int)dk; a.causal = causal ? 1 : 0;
     a.c_log2 = scale * 1.4426950408889634f;
     a.ksteps_qk = (int)((dk + 7) / 8);
     a.n_pv = (int)((dk + 15) / 16 * 16);
-    a.vec_out = (dk % 4 == 0) && ((reinterpret_cast<uintptr_t>(O) & 15) == 0);
+    a.vec_out = (reinterpret_cast<uintptr_t>(O) & 15) == 0;
     a.err = err_word;
     dim3 grid((unsigned)((S + TQ - 1) / TQ), (unsigned)BH);
     return dk <= 32 ? launch_inst<1>(tm, a, grid, st) : launch_inst<2>(tm, a, grid, st);

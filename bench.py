@@ -429,7 +429,21 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
     O = torch.empty((BH, S, dk), device="cuda")
     L = torch.empty((BH, S), device="cuda")
     step_ms, core_ms, _ = core_time(lambda: eng.sdpa_fwd(Q, Kt, V, O, L, 0.125, True), 20, 3)
-    out.append({"workload": "causal SDPA fwd BH=128 S=1024 dk=64 (fp32)", "value": 4.0 * BH * S * S * dk / (step_ms * 1e-3) / 1e12,
+    # tensor work actually issued: 128-row query tiles x 128-key blocks at or below the diagonal, two contractions
+    tiles = S // 128
+    done = 2 * 2.0 * BH * (tiles * (tiles + 1) // 2) * 128 * 128 * dk
+    tf = done / (core_ms * 1e-3) / 1e12
+    out.append({"workload": "causal SDPA fwd BH=128 S=1024 dk=64 (fp32 in/out, 3xTF32 on the tensor cores)",
+                "value": 4.0 * BH * S * S * dk / (step_ms * 1e-3) / 1e12,
+                "unit": "TFLOP/s (4*BH*S^2*dk convention; causal does half)", "ms_per_step": step_ms, "kernel_ms": core_ms,
+                "roofline": {"bound": "tensor", "achieved": tf, "peak": bf16 / 6, "frac": tf / (bf16 / 6), "unit": "TFLOP/s",
+                             "peak_source": "measured bf16 burst / 2 (tf32 rate) / 3 (products)",
+                             "note": "achieved counts the useful FLOP of the key blocks the kernel visits (diagonal blocks whole)"}})
+    # the fp32-FMA kernel that serves head dims above 64, on its own largest case
+    Q2, K2, V2 = (torch.randn((64, 1024, 128), device="cuda") for _ in range(3))
+    O2 = torch.empty((64, 1024, 128), device="cuda")
+    step_ms, core_ms, _ = core_time(lambda: eng.sdpa_fwd(Q2, K2, V2, O2, None, 0.0884, True), 10, 3)
+    out.append({"workload": "causal SDPA fwd BH=64 S=1024 dk=128 (fp32 FMA kernel)", "value": 4.0 * 64 * S * S * 128 / (step_ms * 1e-3) / 1e12,
                 "unit": "TFLOP/s (4*BH*S^2*dk convention; causal does half)", "ms_per_step": step_ms, "kernel_ms": core_ms})
     return out
 

@@ -262,7 +262,8 @@ def test_sdpa_vs_golden(engine, oracle, golden, name, causal):
     np.testing.assert_array_equal(host(O2), host(O))
 
 
-@pytest.mark.parametrize("shape", [(4, 1024, 64), (2, 333, 64), (3, 200, 128), (2, 129, 40), (5, 64, 16)])
+@pytest.mark.parametrize("shape", [(4, 1024, 64), (2, 333, 64), (3, 200, 128), (2, 129, 40), (5, 64, 16),
+                                   (3, 300, 16), (2, 256, 32), (2, 200, 6), (2, 1000, 24), (1, 128, 4), (2, 640, 60), (1, 513, 72)])
 @pytest.mark.parametrize("causal", [0, 1])
 def test_sdpa_vs_oracle(engine, oracle, shape, causal):
     """BASELINE config 4 per-head shape (S=1024, dk=64, scale 1/8, causal) on a few heads, plus ragged ones."""
@@ -275,3 +276,31 @@ def test_sdpa_vs_oracle(engine, oracle, shape, causal):
     engine.sdpa_fwd(dev(Q), dev(K), dev(V), O, L, scale, causal)
     assert np.abs(host(O) - O64).max() < 1e-5
     assert np.abs(host(L) - L64).max() < 1e-5
+
+
+@pytest.mark.parametrize("scale", [-0.2, 0.05, 1.0])
+def test_sdpa_scale_sign_and_size(engine, oracle, scale):
+    """A negative scale takes the fp32-FMA kernel (the tensor-core kernel takes the row maximum before scaling);
+    both routes must agree with the oracle."""
+    BH, S, dk = 2, 384, 32
+    Q, K, V = oracle.normal((BH, S, dk), 41), oracle.normal((BH, S, dk), 43), oracle.normal((BH, S, dk), 47)
+    O64, L64 = oracle.sdpa_fwd_f64(Q, K, V, scale, 1)
+    O = torch.empty((BH, S, dk), device="cuda")
+    L = torch.empty((BH, S), device="cuda")
+    engine.sdpa_fwd(dev(Q), dev(K), dev(V), O, L, scale, 1)
+    assert np.abs(host(O) - O64).max() < 1e-5
+    assert np.abs(host(L) - L64).max() < 1e-5
+
+
+def test_sdpa_unaligned_base_takes_fma_kernel(engine, oracle):
+    """TMA needs 16-byte aligned tensors; a view that starts 4 bytes in is served by the plain-load kernel."""
+    BH, S, dk = 2, 256, 64
+    Q, K, V = oracle.normal((BH, S, dk), 41), oracle.normal((BH, S, dk), 43), oracle.normal((BH, S, dk), 47)
+    O64, _ = oracle.sdpa_fwd_f64(Q, K, V, 0.125, 0)
+    buf = torch.empty(BH * S * dk + 1, device="cuda")
+    Qu = buf[1:].view(BH, S, dk)
+    Qu.copy_(dev(Q))
+    O = torch.empty((BH, S, dk), device="cuda")
+    engine.sdpa_fwd(Qu, dev(K), dev(V), O, None, 0.125, 0)
+    assert np.abs(host(O) - O64).max() < 1e-5
+    assert engine.device_error() == 0
