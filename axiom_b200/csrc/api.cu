@@ -42,6 +42,11 @@ struct Engine {
     int sk_counter_cap = 0;
     int *err_word = nullptr;
     int64_t launches = 0;
+    // host-operand GEMM: device staging (grow-only), copy streams and the events that order them
+    void *hp_buf = nullptr;
+    size_t hp_bytes = 0;
+    cudaStream_t hp_in = nullptr, hp_out = nullptr;
+    cudaEvent_t hp_ev[9] = {};
     // optional timing of the last GEMM-family call: events around its pre-pass and its core kernel
     bool profiling = false;
     static constexpr int EV_RING = 256;
@@ -147,13 +152,9 @@ int run_split(const SplitOperand &s, const float *src, int64_t ld, bool transpos
     return e;
 }
 
-// the dense fp32 contraction on the tensor cores
-int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int64_t M, int64_t N, int64_t K,
-                int ta, int tb, float alpha, float beta, int act, float *const *extra = nullptr, int n_extra = 0,
-                int64_t a_chunk_k = 0, int64_t a_chunk_stride = 0)
+// operand split, MMA kind and product list of the current fp32 mode
+void fp32_mode_plan(int &split_mode, int &kind, TcProducts &prod)
 {
-    int split_mode, kind;
-    TcProducts prod;
     memset(&prod, 0, sizeof prod);
     switch (g.fp32_mode) {
     case AXB_FP32_BF16:
@@ -173,6 +174,16 @@ int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int
         prod.chunk_k = g.chunk_tf32;
         break;
     }
+}
+
+// the dense fp32 contraction on the tensor cores
+int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int64_t M, int64_t N, int64_t K,
+                int ta, int tb, float alpha, float beta, int act, float *const *extra = nullptr, int n_extra = 0,
+                int64_t a_chunk_k = 0, int64_t a_chunk_stride = 0)
+{
+    int split_mode, kind;
+    TcProducts prod;
+    fp32_mode_plan(split_mode, kind, prod);
     const SplitOperand sa = plan_split(split_mode, M, K), sb = plan_split(split_mode, N, K);
     int st = ensure_ws(sa.total() + sb.total());
     if (st) return st;
@@ -291,6 +302,11 @@ extern "C" void axb_shutdown(void)
     if (g.sk_partial) cudaFree(g.sk_partial);
     if (g.sk_counters) cudaFree(g.sk_counters);
     if (g.err_word) cudaFree(g.err_word);
+    if (g.hp_buf) cudaFree(g.hp_buf);
+    if (g.hp_in) cudaStreamDestroy(g.hp_in);
+    if (g.hp_out) cudaStreamDestroy(g.hp_out);
+    for (auto &e : g.hp_ev)
+        if (e) cudaEventDestroy(e);
     for (auto &slot : g.ev)
         for (auto &e : slot)
             if (e) cudaEventDestroy(e);
@@ -532,6 +548,124 @@ extern "C" int axb_gemm_relu(const float *A, const float *B, const float *bias, 
                              int64_t N, int64_t K)
 {
     return axb_gemm_bias_act(A, B, bias, C, M, N, K, 0, 0, 1.0f, 0.0f, AXB_ACT_RELU);
+}
+
+// C_host = A_host . B_host with the transfers pipelined against the tensor-core work: B goes up first and is
+// split once; A goes up in row chunks on a copy stream, each chunk is split and multiplied as soon as it has
+// landed, and its rows of C go back on a second copy stream while the next chunk is in flight.  Row chunks of
+// a GEMM are independent, so the result is bit-identical to one call over the whole matrix.
+extern "C" int axb_gemm_host(const float *A, const float *B, float *C, int64_t M, int64_t N, int64_t K,
+                             int64_t row_chunk)
+{
+    if (M == 0 || N == 0) return AXB_OK;
+    if (!A || !B || !C) return fail(AXB_ERR_NULL_ARG, "gemm_host: NULL");
+    if (M < 0 || N < 0 || K <= 0 || row_chunk < 0) return fail(AXB_ERR_INVALID_SHAPE, "gemm_host: bad shape");
+    if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "gemm_host: dimension exceeds 2^31-1");
+    int st = ensure_ready();
+    if (st) return st;
+    if (!g.hp_in) {
+        cudaError_t e = cudaStreamCreateWithFlags(&g.hp_in, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&g.hp_out, cudaStreamNonBlocking);
+        for (auto &ev : g.hp_ev)
+            if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
+        if (e != cudaSuccess) return cuda_fail("gemm_host: streams", e);
+    }
+    // the route follows the whole problem, as in axb_gemm (M <= 32 is the bandwidth-bound route), so that a
+    // short last chunk is computed exactly as its rows would be in one call over the whole matrix
+    const bool tensor_path = M > 32;
+    // default: about 16 chunks (a short tail after the last upload), whole 128-row tiles, 256..1024 rows
+    int64_t rc = row_chunk;
+    if (rc <= 0) {
+        rc = (M / 16 + 127) / 128 * 128;
+        if (rc < 256) rc = 256;
+        if (rc > 1024) rc = 1024;
+    }
+    if (rc > M) rc = M;
+    const int64_t chunks = (M + rc - 1) / rc;
+    // staging: B, two A chunks, two C chunks
+    const size_t b_bytes = round_up((size_t)K * N * 4, 1024), a_bytes = round_up((size_t)rc * K * 4, 1024),
+                 c_bytes = round_up((size_t)rc * N * 4, 1024);
+    const size_t need = b_bytes + 2 * a_bytes + 2 * c_bytes;
+    if (need > g.hp_bytes) {
+        cudaDeviceSynchronize();
+        if (g.hp_buf) cudaFree(g.hp_buf);
+        g.hp_buf = nullptr; g.hp_bytes = 0;
+        cudaError_t e = cudaMalloc(&g.hp_buf, need);
+        if (e != cudaSuccess) return fail(AXB_ERR_ALLOC, "gemm_host: staging of %zu bytes: %s", need, cudaGetErrorString(e));
+        g.hp_bytes = need;
+    }
+    char *base = (char *)g.hp_buf;
+    float *dB = (float *)base;
+    float *dA[2] = { (float *)(base + b_bytes), (float *)(base + b_bytes + a_bytes) };
+    float *dC[2] = { (float *)(base + b_bytes + 2 * a_bytes), (float *)(base + b_bytes + 2 * a_bytes + c_bytes) };
+    cudaEvent_t ev_b = g.hp_ev[0], *ev_a = &g.hp_ev[1], *ev_a_free = &g.hp_ev[3], *ev_c = &g.hp_ev[5], *ev_c_free = &g.hp_ev[7];
+
+    int split_mode, kind;
+    TcProducts prod;
+    fp32_mode_plan(split_mode, kind, prod);
+    SplitOperand sb = plan_split(split_mode, N, K), sa = plan_split(split_mode, rc, K);
+    TcOperand opb;
+    Carver carve{ nullptr };
+    if (tensor_path) {
+        st = ensure_ws(sa.total() + sb.total());
+        if (st) return st;
+        carve.p = (char *)g.ws;
+    }
+    // everything the engine's stream did before this call precedes the copies
+    cudaEventRecord(ev_b, g.stream);
+    cudaStreamWaitEvent(g.hp_in, ev_b, 0);
+    cudaStreamWaitEvent(g.hp_out, ev_b, 0);
+
+    cudaMemcpyAsync(dB, B, (size_t)K * N * 4, cudaMemcpyHostToDevice, g.hp_in);
+    cudaEventRecord(ev_b, g.hp_in);
+    cudaStreamWaitEvent(g.stream, ev_b, 0);
+    // on a failure half way: let the copies already queued finish before the caller may free its buffers
+    auto bail = [&](int status) {
+        cudaStreamSynchronize(g.hp_in);
+        cudaStreamSynchronize(g.hp_out);
+        return status;
+    };
+    int e = 0;
+    if (tensor_path) {
+        e = run_split(sb, dB, N, true, carve, opb);
+        if (e) return bail(cuda_fail("gemm_host: split B", e));
+    }
+    const size_t a_plane_off = carve.off;
+    for (int64_t i = 0; i < chunks; ++i) {
+        const int slot = (int)(i & 1);
+        const int64_t r0 = i * rc, rows = (M - r0 < rc) ? M - r0 : rc;
+        if (i >= 2) cudaStreamWaitEvent(g.hp_in, ev_a_free[slot], 0);
+        cudaMemcpyAsync(dA[slot], A + r0 * K, (size_t)rows * K * 4, cudaMemcpyHostToDevice, g.hp_in);
+        cudaEventRecord(ev_a[slot], g.hp_in);
+        cudaStreamWaitEvent(g.stream, ev_a[slot], 0);
+        if (i >= 2) cudaStreamWaitEvent(g.stream, ev_c_free[slot], 0);
+        if (tensor_path) {
+            carve.off = a_plane_off;
+            TcOperand opa;
+            SplitOperand sai = plan_split(split_mode, rows, K);
+            e = run_split(sai, dA[slot], K, false, carve, opa);
+            if (e) return bail(cuda_fail("gemm_host: split A", e));
+            cudaEventRecord(ev_a_free[slot], g.stream);
+            TcEpilogue ep;
+            ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = nullptr; ep.colscale = nullptr; ep.act = ACT_NONE;
+            ep.out_mode = OUT_F32; ep.C = dC[slot]; ep.acc_out = nullptr; ep.ldc = N; ep.n_extra = 0;
+            e = launch_gemm_tc(kind, opa, opb, prod, rows, N, K, ep, g.err_word, g.sm_count, g.stream);
+            g.launches++;
+            if (e) return bail(cuda_fail("gemm_host: tcgen05 gemm", e));
+        } else {
+            st = axb_gemm(dA[slot], dB, dC[slot], rows, N, K);   // M <= 32: the skinny route
+            if (st) return bail(st);
+            cudaEventRecord(ev_a_free[slot], g.stream);
+        }
+        cudaEventRecord(ev_c[slot], g.stream);
+        cudaStreamWaitEvent(g.hp_out, ev_c[slot], 0);
+        cudaMemcpyAsync(C + r0 * N, dC[slot], (size_t)rows * N * 4, cudaMemcpyDeviceToHost, g.hp_out);
+        cudaEventRecord(ev_c_free[slot], g.hp_out);
+    }
+    cudaError_t ce = cudaStreamSynchronize(g.hp_out);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(g.hp_in);
+    if (ce != cudaSuccess) return cuda_fail("gemm_host", ce);
+    return AXB_OK;
 }
 
 // ------------------------------------------------------------------ elementwise

@@ -22,7 +22,7 @@ EXPORTS = [
     "axb_storage_free", "axb_memcpy_h2d", "axb_memcpy_d2h", "axb_memcpy_d2d", "axb_set_stream",
     "axb_set_fp32_mode", "axb_get_fp32_mode", "axb_last_error", "axb_device_error", "axb_launch_count",
     "axb_set_profiling", "axb_timing_summary",
-    "axb_gemm", "axb_gemm_nt", "axb_gemm_tn", "axb_gemm_ex", "axb_gemm_relu", "axb_gemm_bias_act",
+    "axb_gemm", "axb_gemm_host", "axb_gemm_nt", "axb_gemm_tn", "axb_gemm_ex", "axb_gemm_relu", "axb_gemm_bias_act",
     "axb_skinny_gemm_static", "axb_gemm_bias_act_scatter", "axb_gemm_gathered_scatter", "axb_ipc_get_handle", "axb_ipc_open_handle",
     "axb_ipc_close_handle",
     "axb_bias_add", "axb_relu", "axb_gelu", "axb_qgemm_w8a32", "axb_qgemm_w8a8", "axb_quantize_rows",
@@ -110,6 +110,16 @@ class Engine:
         self._check(self.lib.axb_memcpy_d2h(C.c_void_p(dst_host_ptr), _ptr(src), nbytes))
 
     # ---- GEMM family (out is caller-allocated, as in the reference) -----
+    def gemm_host(self, A_host, B_host, C_host, row_chunk=0):
+        """C_host = A_host . B_host on host tensors (pinned for full speed); transfers overlap the GEMM."""
+        M, K = A_host.shape
+        N = B_host.shape[1]
+        assert not A_host.is_cuda and not B_host.is_cuda and not C_host.is_cuda
+        assert A_host.is_contiguous() and B_host.is_contiguous() and C_host.is_contiguous()
+        self._check(self.lib.axb_gemm_host(C.c_void_p(A_host.data_ptr()), C.c_void_p(B_host.data_ptr()),
+                                           C.c_void_p(C_host.data_ptr()), _i64(M), _i64(N), _i64(K), _i64(row_chunk)))
+        return C_host
+
     def gemm(self, A, B, out, variant="nn"):
         if variant == "nn":
             M, K = A.shape; N = B.shape[1]

@@ -88,6 +88,15 @@ AXB_API int axb_timing_summary(int *calls, float *prepass_ms_total, float *core_
 
 /* C[M,N] = A[M,K] . B[K,N]                        (ax_compute_gemm, dispatch.c:414) */
 AXB_API int axb_gemm(const float *A, const float *B, float *C, int64_t M, int64_t N, int64_t K);
+/* The same product on HOST operands (pinned memory for full transfer speed): C_host = A_host . B_host.
+   In the reference a host caller pays ax_tensor_to_cuda + gemm + ax_tensor_to_cpu one after the other
+   (src/core/tensor.c:1016-1090: three synchronous copies around the launch); this entry has no counterpart
+   there.  B is uploaded and split once; A goes up in chunks of row_chunk rows (0 = about M/16) that are multiplied
+   as they land while finished rows of C travel back, so the call costs about max(upload, compute, download)
+   instead of their sum.  Synchronous: C_host is complete on return.  Bit-identical to axb_gemm on device
+   copies of the same operands. */
+AXB_API int axb_gemm_host(const float *A_host, const float *B_host, float *C_host, int64_t M, int64_t N, int64_t K,
+                          int64_t row_chunk);
 /* C[M,N] = A[M,K] . B[N,K]^T                      (ax_compute_gemm_nt, dispatch.c:419) */
 AXB_API int axb_gemm_nt(const float *A, const float *B, float *C, int64_t M, int64_t N, int64_t K);
 /* C[M,N] = A[K,M]^T . B[K,N]                      (ax_compute_gemm_tn, dispatch.c:430) */

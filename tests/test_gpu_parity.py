@@ -304,3 +304,24 @@ def test_sdpa_unaligned_base_takes_fma_kernel(engine, oracle):
     engine.sdpa_fwd(Qu, dev(K), dev(V), O, None, 0.125, 0)
     assert np.abs(host(O) - O64).max() < 1e-5
     assert engine.device_error() == 0
+
+
+@pytest.mark.parametrize("shape,chunk", [((4096, 1024, 512), 1024), ((2500, 768, 640), 1024), ((2100, 512, 256), 0),
+                                          ((8, 512, 1024), 0), ((300, 200, 100), 128), ((1030, 256, 128), 512)])
+def test_gemm_host_pipelined_equals_device_gemm(engine, oracle, shape, chunk):
+    """Host-operand GEMM (chunked uploads overlapped with the tensor-core work) == one device call, bit for bit,
+    and both within the fp32 bound of the oracle."""
+    M, N, K = shape
+    A, B = oracle.uniform((M, K), 7), oracle.uniform((K, N), 13)
+    hA, hB = torch.from_numpy(A).pin_memory(), torch.from_numpy(B).pin_memory()
+    hC = torch.full((M, N), float("nan")).pin_memory()
+    engine.gemm_host(hA, hB, hC, row_chunk=chunk)
+    C = torch.empty((M, N), device="cuda")
+    engine.gemm(dev(A), dev(B), C)
+    np.testing.assert_array_equal(hC.numpy(), host(C))
+    assert nerr(hC.numpy(), oracle.gemm_f64(A, B)) <= 1e-5
+    # a second call reuses the staging and the streams
+    hC2 = torch.empty((M, N)).pin_memory()
+    engine.gemm_host(hA, hB, hC2, row_chunk=chunk)
+    np.testing.assert_array_equal(hC2.numpy(), hC.numpy())
+    assert engine.device_error() == 0
