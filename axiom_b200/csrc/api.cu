@@ -213,6 +213,22 @@ int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int
 int gemm_skinny(const float *X, const float *W, const float *bias, float *Y, int64_t M, int64_t N, int64_t K,
                 float alpha, float beta, int act)
 {
+    // above 8 rows the fp32 pipe, not memory, paces the FMA kernels: the tensor-core variant takes over
+    static const int tc_min = [] { const char *e = getenv("AX_B200_SKINNY_TC_MIN"); return e ? atoi(e) : 9; }();
+    if (M >= tc_min && skinny_tc_applicable(M, N, K, X, W)) {
+        SkinnyArgs a;
+        a.X = X; a.W = W; a.bias = bias; a.Y = Y; a.M = (int)M; a.N = N; a.K = K;
+        a.alpha = alpha; a.beta = beta; a.act = act;
+        a.ksplit = 0; a.kchunk = 0; a.stages = 0; a.cluster = 0; a.partial = nullptr; a.counters = nullptr;
+        a.err = g.err_word;
+        mark(0);
+        mark(1);
+        int e = launch_skinny_tc(a, g.sm_count, g.stream);
+        mark(2);
+        g.launches++;
+        if (e) return cuda_fail("skinny tensor-core gemm", e);
+        return AXB_OK;
+    }
     SkinnyPlan plan;
     skinny_plan(M, N, K, W, g.sm_count, &plan);
     if ((size_t)plan.partial_floats > g.sk_partial_floats) {

@@ -39,4 +39,9 @@ int skinny_tma_stage_rows(int mt, int cluster);
 size_t skinny_tma_smem_bytes(int mt, int kchunk, int stages);
 int launch_skinny_tma(const SkinnyArgs &args, const SkinnyPlan &plan, cudaStream_t st);
 
+// Tensor-core variant for 8 < M <= 32 (skinny_tc.cu): needs no scratch; X and W are read in place through TMA
+// (N % 4 == 0, K % 4 == 0, 16-byte aligned bases).
+bool skinny_tc_applicable(int64_t M, int64_t N, int64_t K, const float *X, const float *W);
+int launch_skinny_tc(const SkinnyArgs &args, int sm_count, cudaStream_t st);
+
 }  // namespace axb

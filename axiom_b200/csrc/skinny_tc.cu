@@ -1,0 +1,369 @@
+// skinny_tc.cu — Y[M,N] = act(alpha * X[M,K].W[K,N] + beta*Y + bias) for 8 < M <= 32 on the tensor cores.
+//
+// The fp32-FMA skinny kernels stream W at the HBM rate only while M is small: at M = 32 every weight float4
+// feeds 128 FMAs and the fp32 pipe, not memory, sets the pace (measured 16 % of the copy bandwidth).  Here the
+// product is computed transposed, Y^T[N,M] = W^T.X^T, so that the 128 rows of the MMA are output COLUMNS and the
+// few activation rows are its N: W is the A operand in MN-major form — the [k][n] tile exactly as TMA leaves it
+// (128-byte swizzle with 32-byte atoms) — and X the K-major B operand.  Three tf32 products (lo.hi, hi.lo,
+// hi.hi) keep fp32 accuracy; the hi operand is the fp32 tile itself (the tensor core ignores the 13 low mantissa
+// bits of a tf32 container) and converter warps write tf32(x - trunc(x)) next to it, so W crosses shared memory
+// once from TMA and once from the converters and never goes through registers for arithmetic.
+//
+// One CTA = 128 output columns x one K-slice; the K-slices of a column tile form a thread-block cluster and are
+// summed through distributed shared memory in slice order (deterministic).  Roles: warp 0 TMA producer (ring of
+// 8 raw stages of 32 k-rows — 128 KB of W in flight per SM), warp 1 MMA issuer, warps 2-5 converters (the lo tiles live in a ring of their own, two
+// deep, so the raw ring can be long), warps 6-9 drain the accumulator every 256 k (a fresh TMEM accumulator per
+// chunk: the tensor core truncates when it accumulates) and run the epilogue.
+#include "skinny.cuh"
+
+#include "gemm_tc.cuh"
+#include "ptx.cuh"
+
+#include <cuda.h>
+#include <math.h>
+
+namespace axb {
+
+static constexpr int KT_THREADS = 320;
+static constexpr int KT_STAGES = 8;      // raw ring (TMA destinations; the hi operands)
+static constexpr int KT_LO = 2;          // lo ring (converter output)
+static constexpr int KT_KB = 32;        // k rows per stage
+static constexpr int KT_BN = 128;       // output columns per CTA
+static constexpr int KT_CHUNK = 8;      // stages per accumulator chunk (256 k)
+static constexpr int KT_W_BYTES = KT_KB * KT_BN * 4;  // 16 KB: 4 slabs of [32 k][32 n]
+
+struct alignas(64) SkinnyTcMaps {
+    CUtensorMap w, x;
+};
+
+enum { KERR_PRODUCER = 21, KERR_CONVERT = 22, KERR_MMA = 23, KERR_DRAIN = 24 };
+
+enum { KB_RAW = 0, KB_EMPTY = KT_STAGES, KB_LO_FULL = 2 * KT_STAGES, KB_LO_EMPTY = 2 * KT_STAGES + KT_LO,
+       KB_CHUNK_FULL = 2 * KT_STAGES + 2 * KT_LO, KB_CHUNK_EMPTY = 2 * KT_STAGES + 2 * KT_LO + 2 };
+
+#ifdef AXB_SKTC_PROF
+__device__ unsigned long long g_sktc_prof[32];
+#define KP_DECL(n) long long prof_t[n] = {}; long long prof_c = clock64(); const long long prof_0 = prof_c; const bool prof_on = blockIdx.x == 0 && blockIdx.y == 0;
+#define KP_ADD(i) { const long long t_ = clock64(); prof_t[i] += t_ - prof_c; prof_c = t_; }
+#define KP_OUT(base, n) if (prof_on) { for (int i_ = 0; i_ < n; ++i_) g_sktc_prof[base + i_] = (unsigned long long)prof_t[i_]; g_sktc_prof[base + n] = (unsigned long long)(clock64() - prof_0); }
+extern "C" __attribute__((visibility("default"))) int axb_debug_sktc_prof(unsigned long long *out)
+{
+    return (int)cudaMemcpyFromSymbol(out, g_sktc_prof, sizeof(unsigned long long) * 32);
+}
+#else
+#define KP_DECL(n)
+#define KP_ADD(i)
+#define KP_OUT(base, n)
+#endif
+
+// one lane polls, the warp gets the outcome: 32 lanes spinning on a barrier cost shared-memory bandwidth that
+// the MMA operands need
+__device__ __forceinline__ bool kt_wait_warp(uint32_t bar, uint32_t parity)
+{
+    int ok = 1;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait_bounded(bar, parity) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+__device__ __forceinline__ void kt_report(int *err, int code)
+{
+    if (err) atomicCAS(err, 0, code);
+}
+
+__device__ __forceinline__ float kt_gelu(float v)
+{
+    const float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+    return 0.5f * v * (1.0f + tanhf(inner));
+}
+
+__device__ __forceinline__ float kt_epilogue(const SkinnyArgs &a, float v, int m, int64_t col)
+{
+    v *= a.alpha;
+    if (a.beta != 0.0f) v += a.beta * a.Y[(int64_t)m * a.N + col];
+    if (a.bias) v += __ldg(a.bias + col);
+    if (a.act == 1) v = fmaxf(v, 0.0f);
+    else if (a.act == 2) v = kt_gelu(v);
+    return v;
+}
+
+// lo = tf32(x - trunc_tf32(x)) for PER 16-byte groups per thread (group index first + 128*u) starting at `src`,
+// written `lo_off` bytes further on.  All loads are issued before the first use: four warps convert a stage, so
+// the loop must not serialise on shared-memory latency.
+template <int PER>
+__device__ __forceinline__ void kt_split(uint32_t src, uint32_t lo_off, int first)
+{
+    uint32_t x[PER][4];
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+        const uint32_t addr = src + (uint32_t)(first + 128 * u) * 16u;
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x[u][0]), "=r"(x[u][1]), "=r"(x[u][2]), "=r"(x[u][3]) : "r"(addr));
+    }
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+        const uint32_t addr = src + (uint32_t)(first + 128 * u) * 16u;
+        uint32_t l[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+            l[e] = (__float_as_uint(__uint_as_float(x[u][e]) - __uint_as_float(x[u][e] & 0xFFFFE000u)) + 0x1000u) & 0xFFFFE000u;
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr + lo_off), "r"(l[0]), "r"(l[1]), "r"(l[2]), "r"(l[3]) : "memory");
+    }
+}
+
+template <int MP>
+__global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_constant__ SkinnyTcMaps tm,
+                                                                   const SkinnyArgs a, int kb_total)
+{
+    constexpr uint32_t X_BYTES = MP * 128;                       // [MP rows][32 k] fp32
+    constexpr uint32_t STAGE = KT_W_BYTES + X_BYTES;             // W | X (raw ring and lo ring alike)
+#ifdef AXB_SKTC_PROF
+    const long long kernel_t0 = clock64();
+#endif
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *base_ptr = smem_raw + (base - raw);
+    volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + 512);
+    auto bar = [&](int i) -> uint32_t { return base + 8u * (uint32_t)i; };
+    auto stage_addr = [&](int s) -> uint32_t { return base + 1024u + (uint32_t)s * STAGE; };
+    auto lo_addr = [&](int s) -> uint32_t { return base + 1024u + (uint32_t)(KT_STAGES + s) * STAGE; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x, slice = blockIdx.y, nslices = gridDim.y;
+    const int64_t n0 = (int64_t)tile * KT_BN;
+    const int per = (kb_total + nslices - 1) / nslices;
+    const int kb0 = slice * per;
+    const int nkb = max(0, min(per, kb_total - kb0));
+    const int nchunks = (nkb + KT_CHUNK - 1) / KT_CHUNK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < KT_STAGES; ++s) {
+            mbar_init(bar(KB_RAW + s), 1);
+            mbar_init(bar(KB_EMPTY + s), 1);
+        }
+        for (int s = 0; s < KT_LO; ++s) {
+            mbar_init(bar(KB_LO_FULL + s), 128);
+            mbar_init(bar(KB_LO_EMPTY + s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar(KB_CHUNK_FULL + b), 1);
+            mbar_init(bar(KB_CHUNK_EMPTY + b), 128);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(base + 512, 64);
+        tmem_relinquish();
+    }
+    if (warp == 0 && lane == 0) {
+        tma_prefetch_desc(&tm.w);
+        tma_prefetch_desc(&tm.x);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = *tmem_slot;
+
+    float acc[MP];
+#pragma unroll
+    for (int m = 0; m < MP; ++m) acc[m] = 0.f;
+    const int t_row = 32 * (warp & 3) + lane;   // drain warps: TMEM lane = output column of the tile
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer
+        if (lane == 0) {
+            KP_DECL(2)
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % KT_STAGES, n = i / KT_STAGES;
+                KP_ADD(0)
+                if (n >= 1 && !mbar_wait_bounded(bar(KB_EMPTY + s), (n - 1) & 1)) { kt_report(a.err, KERR_PRODUCER); break; }
+                KP_ADD(1)
+                const uint32_t st = stage_addr(s);
+                const int k0 = (kb0 + i) * KT_KB;
+                mbar_arrive_expect_tx(bar(KB_RAW + s), KT_W_BYTES + X_BYTES);
+#pragma unroll
+                for (int sl = 0; sl < 4; ++sl)
+                    tma_load_3d(st + sl * 4096, &tm.w, bar(KB_RAW + s), (int32_t)(n0 + 32 * sl), k0, 0);
+                tma_load_3d(st + KT_W_BYTES, &tm.x, bar(KB_RAW + s), k0, 0, 0);
+            }
+            KP_ADD(0)
+            KP_OUT(0, 2)
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            const uint64_t desc_w = smem_desc_mnmajor_sw128_32b(0, 4096, 512);
+            const uint64_t desc_x = smem_desc_kmajor(0, 128);
+            const uint32_t idesc = make_idesc<KIND_TF32>(KT_BN, MP) | (1u << 15);   // A (the weights) is MN-major
+            bool ok = true;
+            KP_DECL(3)
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % KT_STAGES;
+                const int ci = i / KT_CHUNK, cb = ci & 1;
+                const bool first = (i % KT_CHUNK) == 0;
+                if (first && ci >= 2 && !mbar_wait_bounded(bar(KB_CHUNK_EMPTY + cb), ((ci >> 1) - 1) & 1)) { ok = false; break; }
+                KP_ADD(0)
+                const int ls = i % KT_LO;
+                if (!mbar_wait_bounded(bar(KB_LO_FULL + ls), (i / KT_LO) & 1)) { ok = false; break; }   // implies the raw stage
+                KP_ADD(1)
+                tc_fence_after_sync();
+                const uint32_t st = stage_addr(s), lo = lo_addr(ls);
+                const uint32_t d = tmem + cb * 32;
+                uint32_t accf = first ? 0u : 1u;
+#pragma unroll
+                for (int pr = 0; pr < 3; ++pr) {
+                    const uint32_t wa = pr == 0 ? lo : st;                                     // lo.hi, hi.lo, hi.hi
+                    const uint32_t xb = (pr == 1 ? lo : st) + KT_W_BYTES;
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        tc_mma<KIND_TF32>(d, desc_w | (uint64_t)(((wa + ks * 1024) & 0x3FFFFu) >> 4),
+                                          desc_x | (uint64_t)(((xb + ks * 32) & 0x3FFFFu) >> 4), idesc, accf);
+                        accf = 1u;
+                    }
+                }
+                tc_commit(bar(KB_LO_EMPTY + ls));
+                tc_commit(bar(KB_EMPTY + s));
+                if ((i % KT_CHUNK) == KT_CHUNK - 1 || i == nkb - 1) tc_commit(bar(KB_CHUNK_FULL + cb));
+                KP_ADD(2)
+            }
+            if (!ok) kt_report(a.err, KERR_MMA);
+            KP_OUT(4, 3)
+        }
+    } else if (warp < 6) {
+        // ---------------------------------------------------------- converters
+        const int ct = threadIdx.x - 64;  // 0..127
+        KP_DECL(3)
+        for (int i = 0; i < nkb; ++i) {
+            const int s = i % KT_STAGES, n = i / KT_STAGES;
+            if (!kt_wait_warp(bar(KB_RAW + s), n & 1)) { kt_report(a.err, KERR_CONVERT); break; }
+            KP_ADD(0)
+            const int ls = i % KT_LO;
+            if (i >= KT_LO && !kt_wait_warp(bar(KB_LO_EMPTY + ls), ((i / KT_LO) - 1) & 1)) {
+                kt_report(a.err, KERR_CONVERT);
+                break;
+            }
+            KP_ADD(1)
+            const uint32_t st = stage_addr(s), lo = lo_addr(ls);
+            kt_split<KT_W_BYTES / 16 / 128>(st, lo - st, ct);
+            kt_split<X_BYTES / 16 / 128>(st + KT_W_BYTES, lo - st, ct);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(bar(KB_LO_FULL + ls));
+            KP_ADD(2)
+        }
+        if (ct == 0) { KP_OUT(8, 3) }
+    } else {
+        // --------------------------------------------------------------- drain
+        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        for (int ci = 0; ci < nchunks; ++ci) {
+            const int cb = ci & 1;
+            if (!mbar_wait_warp_bounded(bar(KB_CHUNK_FULL + cb), (ci >> 1) & 1)) { kt_report(a.err, KERR_DRAIN); break; }
+            tc_fence_after_sync();
+            uint32_t r[32];
+            tmem_ld_32x32(lane_base + cb * 32, r);
+            tmem_ld_wait();
+            tc_fence_before_sync();
+            mbar_arrive(bar(KB_CHUNK_EMPTY + cb));
+#pragma unroll
+            for (int m = 0; m < MP; ++m) acc[m] += __uint_as_float(r[m]);
+        }
+    }
+
+    // ------------------------------------------------------------ reduce + epilogue
+    if (nslices == 1) {
+        if (warp >= 6 && n0 + t_row < a.N) {
+#pragma unroll
+            for (int m = 0; m < MP; ++m)
+                if (m < a.M) a.Y[(int64_t)m * a.N + n0 + t_row] = kt_epilogue(a, acc[m], m, n0 + t_row);
+        }
+    } else {
+        // the ring is idle: every MMA of this CTA has completed before the last chunk was drained
+        float *red = reinterpret_cast<float *>(base_ptr + 1024);   // [MP][128]
+        __syncthreads();
+        if (warp >= 6) {
+#pragma unroll
+            for (int m = 0; m < MP; ++m) red[m * KT_BN + t_row] = acc[m];
+        }
+        cluster_sync_all();
+        if (warp >= 6 && n0 + t_row < a.N) {
+            // slice r finishes rows r, r + nslices, ...: sums in slice order, straight out of the peers' shared memory
+            for (int m = slice; m < a.M; m += nslices) {
+                const uint32_t local = smem_u32(red + m * KT_BN + t_row);
+                float s = 0.f;
+                for (int q = 0; q < nslices; ++q) {
+                    float v;
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(map_to_cta(local, (uint32_t)q)));
+                    s += v;
+                }
+                a.Y[(int64_t)m * a.N + n0 + t_row] = kt_epilogue(a, s, m, n0 + t_row);
+            }
+        }
+        cluster_sync_all();   // the peers' shared memory must outlive the reads above
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+#ifdef AXB_SKTC_PROF
+    if (threadIdx.x == KT_THREADS - 1 && blockIdx.x == 0 && blockIdx.y == 0) g_sktc_prof[16] = (unsigned long long)(clock64() - kernel_t0);
+#endif
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem, 64);
+    }
+}
+
+// ---------------------------------------------------------------------- host
+
+bool skinny_tc_applicable(int64_t M, int64_t N, int64_t K, const float *X, const float *W)
+{
+    // TMA reads X and W in place: rows must be multiples of 16 bytes on 16-byte aligned bases
+    const uintptr_t align = reinterpret_cast<uintptr_t>(X) | reinterpret_cast<uintptr_t>(W);
+    return M >= 1 && M <= 32 && N % 4 == 0 && K % 4 == 0 && (align & 15) == 0 && N >= 128 && K >= 256 &&
+           N <= INT32_MAX && K <= INT32_MAX;
+}
+
+template <int MP>
+static int launch_inst(const SkinnyTcMaps &tm, const SkinnyArgs &a, int kb_total, dim3 grid, cudaStream_t st)
+{
+    const size_t smem = 1024 + (size_t)(KT_STAGES + KT_LO) * (KT_W_BYTES + MP * 128) + 1024;
+    auto kern = skinny_tc_kernel<MP>;
+    static bool attr_set[64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_set[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(KT_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 1;
+    at.val.clusterDim.y = grid.y;   // all K-slices of a column tile
+    at.val.clusterDim.z = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, kern, tm, a, kb_total);
+}
+
+int launch_skinny_tc(const SkinnyArgs &a, int sm_count, cudaStream_t st)
+{
+    const int mp = a.M <= 16 ? 16 : 32;
+    SkinnyTcMaps tm;
+    int e = encode_f32_batched_tmap(&tm.w, a.W, 1, a.K, a.N, a.N, KT_KB, true);
+    if (!e) e = encode_f32_batched_tmap(&tm.x, a.X, 1, a.M, a.K, a.K, mp, false);
+    if (e) return e;
+    const int tiles = (int)((a.N + KT_BN - 1) / KT_BN);
+    const int kb_total = (int)((a.K + KT_KB - 1) / KT_KB);
+    // K-slices: fill the GPU once, at most 8 per cluster, at least one accumulator chunk each
+    int slices = sm_count / tiles;
+    if (slices > 8) slices = 8;
+    if (slices > kb_total / KT_CHUNK) slices = kb_total / KT_CHUNK;
+    if (slices < 1) slices = 1;
+    dim3 grid((unsigned)tiles, (unsigned)slices);
+    return mp == 16 ? launch_inst<16>(tm, a, kb_total, grid, st) : launch_inst<32>(tm, a, kb_total, grid, st);
+}
+
+}  // namespace axb

@@ -135,10 +135,11 @@ def test_null_and_bad_arguments(engine):
     assert e.value.status == 5                      # AX_ERR_INVALID_AXIS
 
 
-@pytest.mark.parametrize("M", [1, 2, 5, 8, 32])
-@pytest.mark.parametrize("NK", [(4096, 4096), (1000, 777), (130, 257)])
+@pytest.mark.parametrize("M", [1, 2, 5, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("NK", [(4096, 4096), (1000, 777), (130, 257), (1000, 1028), (128, 256), (4100, 520), (512, 8192)])
 def test_skinny_route(engine, oracle, M, NK):
-    """BASELINE config 2 (x[M,4096].W[4096,4096] + bias -> GELU, M in {1,8,32}) and ragged shapes."""
+    """BASELINE config 2 (x[M,4096].W[4096,4096] + bias -> GELU, M in {1,8,32}) and ragged shapes.  M <= 8 runs the
+    fp32-FMA kernels, 9..32 the tensor-core kernel when N and K are multiples of 4 (else the FMA kernels again)."""
     N, K = NK
     x = oracle.normal((M, K), 31)
     W = oracle.normal((K, N), 13, sigma=1.0 / np.sqrt(K))
