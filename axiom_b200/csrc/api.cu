@@ -10,6 +10,7 @@
 #include "prepass.cuh"
 #include "ptx.cuh"
 #include "qgemv.cuh"
+#include "kv_attend.cuh"
 #include "sdpa.cuh"
 #include "skinny.cuh"
 
@@ -873,4 +874,42 @@ extern "C" int axb_sdpa_fwd(const float *Q, const float *K, const float *V, floa
     mark(2);
     g.launches++;
     return e ? cuda_fail("sdpa_fwd", e) : AXB_OK;
+}
+
+// ------------------------------------------------------------------ KV cache
+
+extern "C" int axb_kv_cache_append(float *K_cache, float *V_cache, const float *new_K, const float *new_V, int64_t BH,
+                                   int64_t cur_len, int64_t max_seq, int64_t dk)
+{
+    if (!K_cache || !V_cache || !new_K || !new_V) return fail(AXB_ERR_NULL_ARG, "kv_cache_append: NULL");
+    if (BH < 0 || dk <= 0 || max_seq <= 0 || cur_len < 0) return fail(AXB_ERR_INVALID_SHAPE, "kv_cache_append: bad shape");
+    if (cur_len >= max_seq) return fail(AXB_ERR_INVALID_SHAPE, "kv_cache_append: cache full (%lld of %lld)", (long long)cur_len, (long long)max_seq);
+    int st = ensure_ready();
+    if (st) return st;
+    if (BH == 0) return AXB_OK;
+    // row cur_len of every head: [BH] rows of dk floats, max_seq*dk apart in the cache
+    const size_t w = (size_t)dk * sizeof(float), pitch = (size_t)max_seq * w;
+    cudaError_t e = cudaMemcpy2DAsync(K_cache + cur_len * dk, pitch, new_K, w, w, (size_t)BH, cudaMemcpyDeviceToDevice, g.stream);
+    if (e == cudaSuccess)
+        e = cudaMemcpy2DAsync(V_cache + cur_len * dk, pitch, new_V, w, w, (size_t)BH, cudaMemcpyDeviceToDevice, g.stream);
+    return e == cudaSuccess ? AXB_OK : cuda_fail("kv_cache_append", e);
+}
+
+extern "C" int axb_kv_cache_attend(const float *K_cache, const float *V_cache, const float *Q_new, float *out, int64_t BH,
+                                   int64_t cur_len, int64_t max_seq, int64_t dk, float scale)
+{
+    if (!K_cache || !V_cache || !Q_new || !out) return fail(AXB_ERR_NULL_ARG, "kv_cache_attend: NULL");
+    if (BH < 0 || dk <= 0 || max_seq <= 0 || cur_len < 0 || cur_len > max_seq)
+        return fail(AXB_ERR_INVALID_SHAPE, "kv_cache_attend: bad shape");
+    if (dk > 128) return fail(AXB_ERR_NOT_IMPLEMENTED, "kv_cache_attend: head dim %lld > 128", (long long)dk);
+    if (cur_len > INT32_MAX || BH > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "kv_cache_attend: dimension exceeds 2^31-1");
+    int st = ensure_ready();
+    if (st) return st;
+    if (BH == 0) return AXB_OK;
+    mark(0);
+    mark(1);
+    int e = launch_kv_cache_attend(K_cache, V_cache, Q_new, out, BH, cur_len, max_seq, dk, scale, g.sm_count, g.stream);
+    mark(2);
+    g.launches++;
+    return e ? cuda_fail("kv_cache_attend", e) : AXB_OK;
 }

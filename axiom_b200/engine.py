@@ -26,7 +26,7 @@ EXPORTS = [
     "axb_skinny_gemm_static", "axb_gemm_bias_act_scatter", "axb_gemm_gathered_scatter", "axb_ipc_get_handle", "axb_ipc_open_handle",
     "axb_ipc_close_handle",
     "axb_bias_add", "axb_relu", "axb_gelu", "axb_qgemm_w8a32", "axb_qgemm_w8a8", "axb_quantize_rows",
-    "axb_sdpa_fwd",
+    "axb_sdpa_fwd", "axb_kv_cache_append", "axb_kv_cache_attend",
 ]
 
 
@@ -227,6 +227,18 @@ class Engine:
         self._check(self.lib.axb_sdpa_fwd(_ptr(Q), _ptr(K), _ptr(V), _ptr(out), _ptr(L), _i64(BH), _i64(S), _i64(dk),
                                           _f(scale), int(bool(causal)), None))
         return out, L
+
+    def kv_cache_append(self, K_cache, V_cache, new_K, new_V, cur_len):
+        BH, max_seq, dk = K_cache.shape
+        self._check(self.lib.axb_kv_cache_append(_ptr(K_cache), _ptr(V_cache), _ptr(new_K), _ptr(new_V), _i64(BH),
+                                                 _i64(cur_len), _i64(max_seq), _i64(dk)))
+        return cur_len + 1
+
+    def kv_cache_attend(self, K_cache, V_cache, Q_new, out, cur_len, scale):
+        BH, max_seq, dk = K_cache.shape
+        self._check(self.lib.axb_kv_cache_attend(_ptr(K_cache), _ptr(V_cache), _ptr(Q_new), _ptr(out), _i64(BH),
+                                                 _i64(cur_len), _i64(max_seq), _i64(dk), _f(scale)))
+        return out
 
 
 _engine = None

@@ -446,6 +446,22 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
                 "roofline": {"bound": "tensor", "achieved": tf, "peak": bf16 / 6, "frac": tf / (bf16 / 6), "unit": "TFLOP/s",
                              "peak_source": "measured bf16 burst / 2 (tf32 rate) / 3 (products)",
                              "note": "achieved counts the useful FLOP of the key blocks the kernel visits (diagonal blocks whole)"}})
+    # single-token decode against a KV cache: config-4 heads (BH=128, dk=64), 4096 cached tokens = 268 MB of K and V
+    try:
+        kc, vc = (torch.randn((BH, 4096, dk), device="cuda") for _ in range(2))
+        qn, on = torch.randn((BH, dk), device="cuda"), torch.empty((BH, dk), device="cuda")
+        kv = lambda: eng.kv_cache_attend(kc, vc, qn, on, 4096, 0.125)
+        step_ms, core_ms, _ = core_time(kv, 32, 4)
+        kern_ms = graph_time(eng, kv, calls=16) or core_ms
+        nb = 2.0 * BH * 4096 * dk * 4
+        out.append({"workload": "KV-cache attention, 1 new token, BH=128, 4096 cached tokens, dk=64 (K+V = 268 MB > L2)",
+                    "value": nb / (step_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": step_ms, "kernel_ms": kern_ms,
+                    "kernel_ms_eager_events": core_ms,
+                    "roofline": {"bound": "hbm", "achieved": nb / (kern_ms * 1e-3) / 1e9, "peak": hbm,
+                                 "frac": nb / (kern_ms * 1e-3) / 1e9 / hbm, "peak_source": f"{peaks['source']} HBM copy bandwidth"}})
+        del kc, vc
+    except Exception as exc:
+        out.append({"workload": "KV-cache attention", "error": repr(exc)})
     # the fp32-FMA kernel that serves head dims above 64, on its own largest case
     Q2, K2, V2 = (torch.randn((64, 1024, 128), device="cuda") for _ in range(3))
     O2 = torch.empty((64, 1024, 128), device="cuda")

@@ -209,6 +209,19 @@ AXB_API int axb_quantize_rows(const float *w, int64_t N, int64_t K, int8_t *q, f
 AXB_API int axb_sdpa_fwd(const float *Q, const float *K, const float *V, float *out, float *L,
                  int64_t BH, int64_t S, int64_t dk, float scale, int causal, float *P_save);
 
+/* ---- KV cache (autoregressive decode) ---------------------------------------
+   Device-pointer forms of ax_kv_cache_append / ax_kv_cache_attend (include/axiom/attention.h:341-381), whose
+   only implementation in the reference is the CPU one (src/compute/backends/cpu_opt.c:9586-9654,
+   ax_cpu_kv_cache_attend(K_cache, V_cache, Q_new, out, BH, cur_len, max_seq, dk, scale) — the same argument
+   list).  K_cache, V_cache: [BH, max_seq, dk]; new_K, new_V, Q_new, out: [BH, dk].  The caller owns cur_len.
+   append writes row cur_len of every head (cur_len < max_seq, else AX_ERR_INVALID_SHAPE where the reference
+   returns false); attend reads rows [0, cur_len) and, like the reference, leaves out = 0 for an empty cache.
+   dk <= 128. */
+AXB_API int axb_kv_cache_append(float *K_cache, float *V_cache, const float *new_K, const float *new_V, int64_t BH,
+                                int64_t cur_len, int64_t max_seq, int64_t dk);
+AXB_API int axb_kv_cache_attend(const float *K_cache, const float *V_cache, const float *Q_new, float *out,
+                                int64_t BH, int64_t cur_len, int64_t max_seq, int64_t dk, float scale);
+
 #ifdef __cplusplus
 }
 #endif

@@ -22,6 +22,7 @@
        src/core/quantize.c:36-56) and is pinned only by hand-checkable
        known-answer cases committed beside the tests. */
 
+#include <float.h>
 #include <math.h>
 #include <stdint.h>
 #include <stdlib.h>
@@ -380,6 +381,64 @@ ORC_API void orc_sdpa_fwd_f64(const float *Q, const float *K, const float *V,
             if (L) L[h * S + i] = mx + log(sum);
         }
         free(p);
+    }
+}
+
+/* Single-token attention against a KV cache (src/compute/backends/cpu_opt.c:9586-9654, reached from
+   ax_kv_cache_attend, include/axiom/attention.h:373-381): per head, scores[j] = dot(q, K[j]) * scale over the
+   cur_len cached rows, softmax with the maximum subtracted, out = sum_j p[j] * V[j].  The cache is laid out
+   [BH, max_seq, dk]; rows past cur_len are not read.  fp32 with sequential sums, as the reference's scalar tail. */
+ORC_API void orc_kv_cache_attend(const float *Kc, const float *Vc, const float *Qn, float *out,
+                                 int64_t BH, int64_t cur_len, int64_t max_seq, int64_t dk, float scale)
+{
+#pragma omp parallel for schedule(static)
+    for (int64_t h = 0; h < BH; h++) {
+        const float *K_h = Kc + h * max_seq * dk, *V_h = Vc + h * max_seq * dk, *q = Qn + h * dk;
+        float *o = out + h * dk;
+        float *scores = (float *)malloc((size_t)(cur_len > 0 ? cur_len : 1) * sizeof(float));
+        float mx = -FLT_MAX;
+        for (int64_t j = 0; j < cur_len; j++) {
+            float dot = 0.0f;
+            for (int64_t d = 0; d < dk; d++) dot += q[d] * K_h[j * dk + d];
+            scores[j] = dot * scale;
+            if (scores[j] > mx) mx = scores[j];
+        }
+        float sum = 0.0f;
+        for (int64_t j = 0; j < cur_len; j++) { scores[j] = expf(scores[j] - mx); sum += scores[j]; }
+        const float inv = 1.0f / sum;
+        for (int64_t d = 0; d < dk; d++) o[d] = 0.0f;
+        for (int64_t j = 0; j < cur_len; j++) {
+            const float w = scores[j] * inv;
+            for (int64_t d = 0; d < dk; d++) o[d] += w * V_h[j * dk + d];
+        }
+        free(scores);
+    }
+}
+
+/* The same in double (accuracy yardstick). */
+ORC_API void orc_kv_cache_attend_f64(const float *Kc, const float *Vc, const float *Qn, double *out,
+                                     int64_t BH, int64_t cur_len, int64_t max_seq, int64_t dk, float scale)
+{
+#pragma omp parallel for schedule(static)
+    for (int64_t h = 0; h < BH; h++) {
+        const float *K_h = Kc + h * max_seq * dk, *V_h = Vc + h * max_seq * dk, *q = Qn + h * dk;
+        double *o = out + h * dk;
+        double *scores = (double *)malloc((size_t)(cur_len > 0 ? cur_len : 1) * sizeof(double));
+        double mx = -INFINITY;
+        for (int64_t j = 0; j < cur_len; j++) {
+            double dot = 0.0;
+            for (int64_t d = 0; d < dk; d++) dot += (double)q[d] * (double)K_h[j * dk + d];
+            scores[j] = dot * (double)scale;
+            if (scores[j] > mx) mx = scores[j];
+        }
+        double sum = 0.0;
+        for (int64_t j = 0; j < cur_len; j++) { scores[j] = exp(scores[j] - mx); sum += scores[j]; }
+        for (int64_t d = 0; d < dk; d++) {
+            double acc = 0.0;
+            for (int64_t j = 0; j < cur_len; j++) acc += scores[j] * (double)V_h[j * dk + d];
+            o[d] = acc / sum;
+        }
+        free(scores);
     }
 }
 

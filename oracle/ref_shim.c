@@ -317,6 +317,20 @@ SHIM_API int ref_device_sdpa_fwd(const float *Q, const float *K, const float *V,
     return rc;
 }
 
+/* ax_kv_cache_create + cur_len x ax_kv_cache_append + ax_kv_cache_attend (include/axiom/attention.h:341-381).
+   Kseq, Vseq: [cur_len, BH, dk] (one appended row set per token); Q_new, out: [BH, dk]. */
+SHIM_API int ref_kv_cache_attend(const float *Kseq, const float *Vseq, const float *Q_new, float *out,
+                                 int64_t BH, int64_t cur_len, int64_t max_seq, int64_t dk, float scale)
+{
+    ax_kv_cache_t *c = ax_kv_cache_create(BH, max_seq, dk);
+    if (!c) return -1;
+    for (int64_t t = 0; t < cur_len; t++)
+        if (!ax_kv_cache_append(c, Kseq + t * BH * dk, Vseq + t * BH * dk)) { ax_kv_cache_destroy(c); return -2; }
+    ax_kv_cache_attend(c, Q_new, out, scale);
+    ax_kv_cache_destroy(c);
+    return 0;
+}
+
 /* ax_fused_attention_fwd / _causal on head-major [BH,S,dk] buffers. */
 SHIM_API int ref_sdpa_fwd(const float *Q, const float *K, const float *V, float *O, float *L,
                           int64_t BH, int64_t S, int64_t dk, float scale, int causal)

@@ -27,6 +27,8 @@ GEMM_CASES = [  # name, M, N, K
     ("g_96", 96, 96, 96), ("g_k1", 9, 11, 1), ("g_skinny1", 1, 192, 160), ("g_skinny8", 8, 130, 257),
 ]
 SDPA_CASES = [("s_test", 6, 24, 16, 0.25), ("s_c4like", 3, 80, 64, 0.125)]
+# (name, BH, max_seq, cur_len, dk): the reference test's shape, a ragged one, a longer cache at the config-4 head dim
+KV_CASES = [("kv_test", 2, 16, 5, 8), ("kv_ragged", 3, 50, 37, 20), ("kv_c4like", 4, 512, 300, 64)]
 
 
 def main():
@@ -77,6 +79,14 @@ def main():
             O, L = r.sdpa_fwd(Q, K_, V, scale, causal)
             out[f"{name}_c{causal}_O"] = O
             out[f"{name}_c{causal}_L"] = L
+
+    # KV-cache single-token attention (tests/test_attention.c:268-330 shape first, then longer caches)
+    for name, BH, max_seq, cur_len, dk in KV_CASES:
+        Kc, Vc = o.normal((BH, max_seq, dk), 43), o.normal((BH, max_seq, dk), 47)
+        Qn = o.normal((BH, dk), 41)
+        scale = np.float32(1.0 / np.sqrt(dk))
+        out[name + "_shape"] = np.array([BH, max_seq, cur_len, dk], np.int64)
+        out[name + "_out"] = r.kv_cache_attend(Kc, Vc, Qn, cur_len, scale)
 
     # -- W8A8 known answers (numpy, independent of the C oracle)
     rng = np.random.RandomState(1234)

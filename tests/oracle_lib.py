@@ -178,6 +178,20 @@ class Oracle:
                                   _i64(BH), _i64(S), _i64(dk), C.c_float(scale), int(causal))
         return O, L
 
+    def kv_cache_attend(self, Kc, Vc, Qn, cur_len, scale):
+        BH, max_seq, dk = Kc.shape
+        out = np.empty((BH, dk), np.float32)
+        self.lib.orc_kv_cache_attend(_p(Kc, _f32p), _p(Vc, _f32p), _p(Qn, _f32p), _p(out, _f32p),
+                                     _i64(BH), _i64(cur_len), _i64(max_seq), _i64(dk), C.c_float(scale))
+        return out
+
+    def kv_cache_attend_f64(self, Kc, Vc, Qn, cur_len, scale):
+        BH, max_seq, dk = Kc.shape
+        out = np.empty((BH, dk), np.float64)
+        self.lib.orc_kv_cache_attend_f64(_p(Kc, _f32p), _p(Vc, _f32p), _p(Qn, _f32p), _p(out, _f64p),
+                                         _i64(BH), _i64(cur_len), _i64(max_seq), _i64(dk), C.c_float(scale))
+        return out
+
     def num_threads(self):
         return int(self.lib.orc_num_threads())
 
@@ -282,6 +296,18 @@ class Reference:
         self.lib.ref_sdpa_fwd(_p(Q, _f32p), _p(K, _f32p), _p(V, _f32p), _p(O, _f32p), _p(L, _f32p),
                               _i64(BH), _i64(S), _i64(dk), C.c_float(scale), int(causal))
         return O, L
+
+
+    def kv_cache_attend(self, Kc, Vc, Qn, cur_len, scale):
+        """Kc, Vc: cache-layout [BH, max_seq, dk]; the rows are appended token by token through the reference API."""
+        BH, max_seq, dk = Kc.shape
+        Kseq = np.ascontiguousarray(Kc[:, :cur_len].transpose(1, 0, 2))
+        Vseq = np.ascontiguousarray(Vc[:, :cur_len].transpose(1, 0, 2))
+        out = np.zeros((BH, dk), np.float32)
+        st = self.lib.ref_kv_cache_attend(_p(Kseq, _f32p), _p(Vseq, _f32p), _p(Qn, _f32p), _p(out, _f32p),
+                                          _i64(BH), _i64(cur_len), _i64(max_seq), _i64(dk), C.c_float(scale))
+        assert st == 0, st
+        return out
 
 
 def nerr(x, ref):

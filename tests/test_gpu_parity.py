@@ -326,3 +326,63 @@ def test_gemm_host_pipelined_equals_device_gemm(engine, oracle, shape, chunk):
     engine.gemm_host(hA, hB, hC2, row_chunk=chunk)
     np.testing.assert_array_equal(hC2.numpy(), hC.numpy())
     assert engine.device_error() == 0
+
+
+@pytest.mark.parametrize("name", ["kv_test", "kv_ragged", "kv_c4like"])
+def test_kv_cache_attend_vs_golden(engine, oracle, golden, name):
+    """ax_kv_cache_append x cur_len + ax_kv_cache_attend through the reference (tests/test_attention.c:268-330)."""
+    BH, max_seq, cur_len, dk = (int(v) for v in golden[name + "_shape"])
+    Kc, Vc, Qn = oracle.normal((BH, max_seq, dk), 43), oracle.normal((BH, max_seq, dk), 47), oracle.normal((BH, dk), 41)
+    scale = float(np.float32(1.0 / np.sqrt(dk)))
+    # build the cache on the device token by token, as a decode loop does
+    Kd = torch.full((BH, max_seq, dk), float("nan"), device="cuda")
+    Vd = torch.full((BH, max_seq, dk), float("nan"), device="cuda")
+    n = 0
+    for t in range(cur_len):
+        n = engine.kv_cache_append(Kd, Vd, dev(np.ascontiguousarray(Kc[:, t])), dev(np.ascontiguousarray(Vc[:, t])), n)
+    assert n == cur_len
+    np.testing.assert_array_equal(host(Kd[:, :cur_len]), Kc[:, :cur_len])
+    out = torch.full((BH, dk), float("nan"), device="cuda")
+    engine.kv_cache_attend(Kd, Vd, dev(Qn), out, cur_len, scale)
+    assert np.abs(host(out) - golden[name + "_out"]).max() < 1e-5
+    assert np.abs(host(out) - oracle.kv_cache_attend_f64(Kc, Vc, Qn, cur_len, scale)).max() < 1e-5
+
+
+@pytest.mark.parametrize("shape", [(128, 1024, 1024, 64), (16, 4096, 4095, 64), (3, 9000, 8500, 128), (5, 300, 1, 40),
+                                   (2, 64, 64, 6), (7, 700, 513, 33), (4, 100, 0, 16)])
+def test_kv_cache_attend_vs_oracle(engine, oracle, shape):
+    """Config-4 heads at a full 1024-token cache, long caches (several segments, several chunks), odd head dims."""
+    BH, max_seq, cur_len, dk = shape
+    Kc, Vc, Qn = oracle.normal((BH, max_seq, dk), 43), oracle.normal((BH, max_seq, dk), 47), oracle.normal((BH, dk), 41)
+    scale = float(np.float32(1.0 / np.sqrt(dk)))
+    out = torch.full((BH, dk), float("nan"), device="cuda")
+    Kd, Vd, Qd = dev(Kc), dev(Vc), dev(Qn)
+    engine.kv_cache_attend(Kd, Vd, Qd, out, cur_len, scale)
+    if cur_len == 0:
+        assert np.all(host(out) == 0)
+        return
+    ref64 = oracle.kv_cache_attend_f64(Kc, Vc, Qn, cur_len, scale)
+    assert np.abs(host(out) - ref64).max() < 1e-5
+    assert np.abs(oracle.kv_cache_attend(Kc, Vc, Qn, cur_len, scale) - ref64).max() < 1e-5
+    out2 = torch.empty_like(out)
+    engine.kv_cache_attend(Kd, Vd, Qd, out2, cur_len, scale)       # deterministic merge of the segments
+    np.testing.assert_array_equal(host(out2), host(out))
+    # the last row of causal attention over the same keys is the same computation (tests/test_attention.c:300-327)
+    if dk <= 128 and cur_len >= 2:
+        S = min(cur_len, 256)
+        Q = np.zeros((BH, S, dk), np.float32); Q[:, -1] = Qn
+        O = torch.empty((BH, S, dk), device="cuda")
+        engine.sdpa_fwd(dev(Q), dev(np.ascontiguousarray(Kc[:, :S])), dev(np.ascontiguousarray(Vc[:, :S])), O, None, scale, 1)
+        o_s = torch.empty((BH, dk), device="cuda")
+        engine.kv_cache_attend(Kd, Vd, Qd, o_s, S, scale)
+        assert np.abs(host(O[:, -1]) - host(o_s)).max() < 1e-5
+
+
+def test_kv_cache_errors(engine):
+    from axiom_b200.engine import EngineError
+    Kd = torch.zeros((2, 4, 8), device="cuda")
+    q = torch.zeros((2, 8), device="cuda")
+    with pytest.raises(EngineError):
+        engine.kv_cache_append(Kd, Kd, q, q, 4)          # full
+    with pytest.raises(EngineError):
+        engine.kv_cache_attend(Kd, Kd, q, q, 5, 1.0)     # cur_len > max_seq
