@@ -43,6 +43,9 @@ struct Engine {
     int sk_counter_cap = 0;
     int *err_word = nullptr;
     int64_t launches = 0;
+    // grow-only buffer for intermediate results a fused route cannot avoid (the unfused qkv projection)
+    void *aux = nullptr;
+    size_t aux_bytes = 0;
     // host-operand GEMM: device staging (grow-only), copy streams and the events that order them
     void *hp_buf = nullptr;
     size_t hp_bytes = 0;
@@ -180,7 +183,8 @@ void fp32_mode_plan(int &split_mode, int &kind, TcProducts &prod)
 // the dense fp32 contraction on the tensor cores
 int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int64_t M, int64_t N, int64_t K,
                 int ta, int tb, float alpha, float beta, int act, float *const *extra = nullptr, int n_extra = 0,
-                int64_t a_chunk_k = 0, int64_t a_chunk_stride = 0)
+                int64_t a_chunk_k = 0, int64_t a_chunk_stride = 0, const int64_t *head_shape = nullptr,
+                float *const *head_out = nullptr)
 {
     int split_mode, kind;
     TcProducts prod;
@@ -203,6 +207,10 @@ int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int
     ep.out_mode = OUT_F32; ep.C = C; ep.acc_out = nullptr; ep.ldc = N;
     ep.n_extra = n_extra;
     for (int i = 0; i < n_extra && i < TC_MAX_EXTRA; ++i) ep.c_extra[i] = extra[i];
+    if (head_shape) {   // { S, H, dk }: the epilogue scatters into head_out[0..2] as [B*H, S, dk]
+        ep.hs_S = (int)head_shape[0]; ep.hs_H = (int)head_shape[1]; ep.hs_dk = (int)head_shape[2];
+        for (int i = 0; i < 3; ++i) ep.hs_out[i] = head_out[i];
+    }
     mark(1);
     e = launch_gemm_tc(kind, opa, opb, prod, M, N, K, ep, g.err_word, g.sm_count, g.stream);
     mark(2);
@@ -320,6 +328,7 @@ extern "C" void axb_shutdown(void)
     if (g.sk_counters) cudaFree(g.sk_counters);
     if (g.err_word) cudaFree(g.err_word);
     if (g.hp_buf) cudaFree(g.hp_buf);
+    if (g.aux) cudaFree(g.aux);
     if (g.hp_in) cudaStreamDestroy(g.hp_in);
     if (g.hp_out) cudaStreamDestroy(g.hp_out);
     for (auto &e : g.hp_ev)
@@ -912,4 +921,37 @@ extern "C" int axb_kv_cache_attend(const float *K_cache, const float *V_cache, c
     mark(2);
     g.launches++;
     return e ? cuda_fail("kv_cache_attend", e) : AXB_OK;
+}
+
+// ------------------------------------------------------- attention projections
+
+extern "C" int axb_qkv_head_gemm(const float *X, const float *Wqkv, const float *bqkv, int64_t B, int64_t S, int64_t H,
+                                 int64_t dk, float *Qh, float *Kh, float *Vh)
+{
+    if (!X || !Wqkv || !Qh || !Kh || !Vh) return fail(AXB_ERR_NULL_ARG, "qkv_head_gemm: NULL");
+    if (B < 0 || S < 0 || H <= 0 || dk <= 0) return fail(AXB_ERR_INVALID_SHAPE, "qkv_head_gemm: bad shape");
+    const int64_t rows = B * S, D = H * dk;
+    if (rows > INT32_MAX || 3 * D > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "qkv_head_gemm: dimension exceeds 2^31-1");
+    int st = ensure_ready();
+    if (st) return st;
+    if (rows == 0) return AXB_OK;
+    float *outs[3] = { Qh, Kh, Vh };
+    if (rows > 32 && dk % 32 == 0) {
+        // one launch: the tensor-core GEMM's epilogue adds the bias and stores head-major
+        const int64_t shape[3] = { S, H, dk };
+        return gemm_tc_f32(X, Wqkv, bqkv, nullptr, rows, 3 * D, D, 0, 0, 1.0f, 0.0f, AXB_ACT_NONE, nullptr, 0, 0, 0, shape, outs);
+    }
+    // other head dims and skinny inputs: the product (bias fused) into a scratch matrix, then the layout pass
+    const size_t need = (size_t)rows * 3 * D * sizeof(float);
+    if (need > g.aux_bytes) {
+        if (g.aux) { cudaStreamSynchronize(g.stream); cudaFree(g.aux); g.aux = nullptr; g.aux_bytes = 0; }
+        cudaError_t e = cudaMalloc(&g.aux, need);
+        if (e != cudaSuccess) return fail(AXB_ERR_ALLOC, "qkv_head_gemm: scratch of %zu bytes: %s", need, cudaGetErrorString(e));
+        g.aux_bytes = need;
+    }
+    st = axb_gemm_bias_act(X, Wqkv, bqkv, (float *)g.aux, rows, 3 * D, D, 0, 0, 1.0f, 0.0f, AXB_ACT_NONE);
+    if (st) return st;
+    int e = launch_head_split((const float *)g.aux, Qh, Kh, Vh, rows, S, H, dk, g.sm_count, g.stream);
+    g.launches++;
+    return e ? cuda_fail("qkv_head_gemm: head split", e) : AXB_OK;
 }

@@ -89,4 +89,33 @@ int launch_bias_add(const float *in, const float *bias, int axis, float *out, in
     return (int)cudaGetLastError();
 }
 
+// qkv [rows = B*S, 3*H*dk] -> Qh, Kh, Vh [B*H, S, dk] (ax_attn_head_interleave_qkv_split,
+// src/compute/backends/cuda/ops_attention.cu:74-137 in the reference): the layout pass for shapes the GEMM
+// epilogue does not scatter itself.
+__global__ void __launch_bounds__(256) head_split_kernel(const float *__restrict__ qkv, float *Qh, float *Kh, float *Vh,
+                                                         int64_t rows, int S, int H, int dk)
+{
+    const int64_t D = (int64_t)H * dk, total = rows * 3 * D;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = i / (3 * D), col = i - row * 3 * D;
+        const int which = (int)(col / D);
+        const int64_t rem = col - which * D;
+        const int h = (int)(rem / dk), d = (int)(rem - (int64_t)h * dk);
+        const int64_t b = row / S, s = row - b * S;
+        float *dst = which == 0 ? Qh : (which == 1 ? Kh : Vh);
+        dst[((b * H + h) * S + s) * dk + d] = qkv[i];
+    }
+}
+
+int launch_head_split(const float *qkv, float *Qh, float *Kh, float *Vh, int64_t rows, int64_t S, int64_t H, int64_t dk,
+                      int sm_count, cudaStream_t st)
+{
+    const int64_t total = rows * 3 * H * dk;
+    if (total <= 0) return 0;
+    int64_t blocks = (total + 255) / 256;
+    if (blocks > (int64_t)sm_count * 16) blocks = (int64_t)sm_count * 16;
+    head_split_kernel<<<(unsigned)blocks, 256, 0, st>>>(qkv, Qh, Kh, Vh, rows, (int)S, (int)H, (int)dk);
+    return (int)cudaGetLastError();
+}
+
 }  // namespace axb

@@ -283,7 +283,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                         const int col0 = col_base + c * 32;
                         if (col0 < p.N) {
                             const bool full = col0 + 32 <= p.N;
-                            float *dst = reinterpret_cast<float *>(p.C) + row * p.ldc + col0;
+                            float *dst = out_piece_ptr(p, row, col0);
                             const bool vec = full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
                             float v[32];
 #pragma unroll
@@ -560,6 +560,12 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
     ka.ldc = ep.ldc; ka.err = err_word;
     ka.n_extra = ep.n_extra < 0 ? 0 : (ep.n_extra > TC_MAX_EXTRA ? TC_MAX_EXTRA : ep.n_extra);
     for (int i = 0; i < ka.n_extra; ++i) ka.c_extra[i] = ep.c_extra[i];
+    if (ep.hs_dk > 0) {
+        ka.hs_dk = ep.hs_dk; ka.hs_S = ep.hs_S; ka.hs_H = ep.hs_H;
+        for (int i = 0; i < 3; ++i) ka.hs_out[i] = ep.hs_out[i];
+        ka.beta = 0.0f;
+        ka.n_extra = 0;
+    }
     const int64_t tiles = mt * nt;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);
     if (use_pair)

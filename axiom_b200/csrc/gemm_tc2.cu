@@ -275,7 +275,7 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                         const int col0 = col_base + c * 32;
                         if (col0 < p.N) {
                             const bool full = col0 + 32 <= p.N;
-                            float *dst = reinterpret_cast<float *>(p.C) + row * p.ldc + col0;
+                            float *dst = out_piece_ptr(p, row, col0);
                             const bool vec = full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
                             float v[32];
 #pragma unroll

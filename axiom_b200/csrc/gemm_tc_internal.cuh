@@ -37,6 +37,8 @@ struct KernelArgs {
     int *err;
     float *c_extra[TC_MAX_EXTRA];
     int n_extra;
+    int hs_dk, hs_S, hs_H;   // head-major scatter of the output (hs_dk > 0), see TcEpilogue
+    float *hs_out[3];
 };
 
 // error words written to *err (first writer wins)
@@ -56,6 +58,16 @@ __device__ __forceinline__ void tile_coords(int t, int m_tiles, int n_tiles, int
     const int r = t - g * per_group;
     mt = first_m + r % gm;
     nt = r / gm;
+}
+
+// where the 32 output columns starting at col0 of output row `row` go
+__device__ __forceinline__ float *out_piece_ptr(const KernelArgs &p, long long row, int col0)
+{
+    if (p.hs_dk == 0) return reinterpret_cast<float *>(p.C) + row * p.ldc + col0;
+    const int D = p.hs_H * p.hs_dk;
+    const int which = col0 / D, rem = col0 - which * D, h = rem / p.hs_dk, d0 = rem - h * p.hs_dk;
+    const long long b = row / p.hs_S, s = row - b * p.hs_S;
+    return p.hs_out[which] + ((b * p.hs_H + h) * p.hs_S + s) * p.hs_dk + d0;
 }
 
 __device__ __forceinline__ float gelu_tanh(float v)

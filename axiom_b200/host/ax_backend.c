@@ -137,6 +137,32 @@ static axb_status be_gemm_ex(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b,
     return gemm_common("gemm_ex", a, b, NULL, out, 0, 0, alpha, beta, AXB_ACT_NONE);
 }
 
+/* shape rules of the reference's CPU implementation (src/compute/backends/cpu_opt.c:6165-6189) */
+static axb_status be_qkv_head_gemm(const axb_ax_tensor_t *X, const axb_ax_tensor_t *Wqkv, const axb_ax_tensor_t *bqkv,
+                                   int64_t B, int64_t S, int64_t H, int64_t dk, axb_ax_tensor_t *Qh, axb_ax_tensor_t *Kh,
+                                   axb_ax_tensor_t *Vh)
+{
+    axb_status st;
+    if ((st = check_f32(X, "qkv_head_gemm", 2)) || (st = check_f32(Wqkv, "qkv_head_gemm", 2)) ||
+        (st = check_f32(Qh, "qkv_head_gemm", 3)) || (st = check_f32(Kh, "qkv_head_gemm", 3)) ||
+        (st = check_f32(Vh, "qkv_head_gemm", 3)))
+        return st;
+    const int64_t D = X->shape[1];
+    if (X->shape[0] != B * S || D != H * dk || Wqkv->shape[0] != D || Wqkv->shape[1] != 3 * D)
+        return report(ST_SHAPE, "qkv_head_gemm: X must be [B*S, H*dk] and Wqkv [H*dk, 3*H*dk]");
+    const axb_ax_tensor_t *outs[3] = { Qh, Kh, Vh };
+    for (int i = 0; i < 3; ++i)
+        if (outs[i]->shape[0] != B * H || outs[i]->shape[1] != S || outs[i]->shape[2] != dk)
+            return report(ST_SHAPE, "qkv_head_gemm: Qh, Kh, Vh must be [B*H, S, dk]");
+    const float *bias_p = NULL;
+    if (bqkv) {
+        if ((st = check_f32(bqkv, "qkv_head_gemm", 1))) return st;
+        if (bqkv->shape[0] != 3 * D) return report(ST_SHAPE, "qkv_head_gemm: bqkv must have 3*H*dk elements");
+        bias_p = fptr(bqkv);
+    }
+    return done(axb_qkv_head_gemm(fptr(X), fptr(Wqkv), bias_p, B, S, H, dk, fptr(Qh), fptr(Kh), fptr(Vh)));
+}
+
 static axb_status be_bias_add(const axb_ax_tensor_t *in, const axb_ax_tensor_t *bias, int axis, axb_ax_tensor_t *out)
 {
     axb_status st;
@@ -188,6 +214,7 @@ static const axb_ax_backend_ops_t ops_table = {
     .gemm = be_gemm,
     .gemm_nt = be_gemm_nt,
     .gemm_tn = be_gemm_tn,
+    .qkv_head_gemm = be_qkv_head_gemm,
     .gemm_relu = be_gemm_relu,
     .gemm_ex = be_gemm_ex,
     .bias_add = be_bias_add,

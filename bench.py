@@ -446,6 +446,20 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
                 "roofline": {"bound": "tensor", "achieved": tf, "peak": bf16 / 6, "frac": tf / (bf16 / 6), "unit": "TFLOP/s",
                              "peak_source": "measured bf16 burst / 2 (tf32 rate) / 3 (products)",
                              "note": "achieved counts the useful FLOP of the key blocks the kernel visits (diagonal blocks whole)"}})
+    # fused QKV projection into the head-major layout: B=8, S=1024, D=1024 (H=16, dk=64, the config-4 heads)
+    try:
+        Bq, Sq, Hq = 8, 1024, 16
+        Dq = Hq * dk
+        Xq, Wq, bq = uniform((Bq * Sq, Dq)), torch.randn((Dq, 3 * Dq), device="cuda") / 32, uniform((3 * Dq,))
+        heads = [torch.empty((Bq * Hq, Sq, dk), device="cuda") for _ in range(3)]
+        step_ms, core_ms, pre_ms = core_time(lambda: eng.qkv_head_gemm(Xq, Wq, bq, Bq, Sq, Hq, dk, *heads), 20, 3)
+        fl = 2.0 * Bq * Sq * Dq * 3 * Dq
+        out.append({"workload": "QKV projection + head-major split, X[8192x1024].Wqkv[1024x3072]+b -> Qh,Kh,Vh [128,1024,64] (one launch)",
+                    "value": fl / (step_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": step_ms, "kernel_ms": core_ms,
+                    "prepass_ms": pre_ms})
+    except Exception as exc:
+        out.append({"workload": "QKV projection + head-major split", "error": repr(exc)})
+
     # single-token decode against a KV cache: config-4 heads (BH=128, dk=64), 4096 cached tokens = 268 MB of K and V
     try:
         kc, vc = (torch.randn((BH, 4096, dk), device="cuda") for _ in range(2))

@@ -209,6 +209,17 @@ AXB_API int axb_quantize_rows(const float *w, int64_t N, int64_t K, int8_t *q, f
 AXB_API int axb_sdpa_fwd(const float *Q, const float *K, const float *V, float *out, float *L,
                  int64_t BH, int64_t S, int64_t dk, float scale, int causal, float *P_save);
 
+/* ---- attention projections --------------------------------------------------
+   Slot qkv_head_gemm of ax_backend_ops_t (include/axiom/internal/backend_ops.h:107-113; ax_compute_qkv_head_gemm,
+   include/axiom/compute.h:150-170; CPU implementation src/compute/backends/cpu_opt.c:6160).  The reference CUDA
+   backend leaves the slot NULL and runs gemm + k_head_interleave_qkv_split[_bias]
+   (src/compute/backends/cuda/ops_attention.cu:74-137).
+     qkv = X[B*S, D] . Wqkv[D, 3D] (+ bqkv[3D]),  D = H*dk
+     Qh, Kh, Vh [B*H, S, dk] = the three D-wide column blocks of qkv, head-major; all three are overwritten.
+   For dk % 32 == 0 the GEMM's epilogue stores head-major itself (one launch, no [B*S, 3D] intermediate). */
+AXB_API int axb_qkv_head_gemm(const float *X, const float *Wqkv, const float *bqkv, int64_t B, int64_t S, int64_t H,
+                              int64_t dk, float *Qh, float *Kh, float *Vh);
+
 /* ---- KV cache (autoregressive decode) ---------------------------------------
    Device-pointer forms of ax_kv_cache_append / ax_kv_cache_attend (include/axiom/attention.h:341-381), whose
    only implementation in the reference is the CPU one (src/compute/backends/cpu_opt.c:9586-9654,

@@ -63,7 +63,11 @@ typedef struct {
     axb_status (*gemm)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, axb_ax_tensor_t *out);
     axb_status (*gemm_nt)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, axb_ax_tensor_t *out);
     axb_status (*gemm_tn)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, axb_ax_tensor_t *out);
-    axb_opaque_fn dwqkv_split_acc, dwqkv_split_acc_hm, qkv_head_gemm, dattn_head_gemm_nt, mha_output_proj_fused;
+    axb_opaque_fn dwqkv_split_acc, dwqkv_split_acc_hm;
+    axb_status (*qkv_head_gemm)(const axb_ax_tensor_t *X, const axb_ax_tensor_t *Wqkv, const axb_ax_tensor_t *bqkv,
+                                int64_t B, int64_t S, int64_t H, int64_t dk, axb_ax_tensor_t *Qh, axb_ax_tensor_t *Kh,
+                                axb_ax_tensor_t *Vh);   /* backend_ops.h:107-113 */
+    axb_opaque_fn dattn_head_gemm_nt, mha_output_proj_fused;
     axb_status (*gemm_relu)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, const axb_ax_tensor_t *bias,
                             axb_ax_tensor_t *out);
     axb_status (*gemm_ex)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, float alpha, float beta,

@@ -384,6 +384,27 @@ ORC_API void orc_sdpa_fwd_f64(const float *Q, const float *K, const float *V,
     }
 }
 
+/* QKV projection straight into the head-major layout (src/compute/backends/cpu_opt.c:6160-6260,
+   ax_compute_qkv_head_gemm, include/axiom/compute.h:150-170): every output starts at its bias (or zero) and the
+   products are accumulated on top in k order; column which*D + h*dk + d of row b*S + s lands in
+   out[which][(b*H + h)*S + s][d]. */
+ORC_API void orc_qkv_head_gemm(const float *X, const float *Wqkv, const float *bqkv, int64_t B, int64_t S,
+                               int64_t H, int64_t dk, float *Qh, float *Kh, float *Vh)
+{
+    const int64_t D = H * dk, rows = B * S;
+    float *outs[3] = { Qh, Kh, Vh };
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; r++) {
+        const int64_t b = r / S, s = r - b * S;
+        for (int64_t c = 0; c < 3 * D; c++) {
+            const int64_t which = c / D, rem = c - which * D, h = rem / dk, d = rem - h * dk;
+            float acc = bqkv ? bqkv[c] : 0.0f;
+            for (int64_t k = 0; k < D; k++) acc += X[r * D + k] * Wqkv[k * 3 * D + c];
+            outs[which][((b * H + h) * S + s) * dk + d] = acc;
+        }
+    }
+}
+
 /* Single-token attention against a KV cache (src/compute/backends/cpu_opt.c:9586-9654, reached from
    ax_kv_cache_attend, include/axiom/attention.h:373-381): per head, scores[j] = dot(q, K[j]) * scale over the
    cur_len cached rows, softmax with the maximum subtracted, out = sum_j p[j] * V[j].  The cache is laid out

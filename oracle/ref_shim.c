@@ -317,6 +317,53 @@ SHIM_API int ref_device_sdpa_fwd(const float *Q, const float *K, const float *V,
     return rc;
 }
 
+/* ax_compute_qkv_head_gemm through the reference dispatcher with the registered device backend active: the
+   qkv_head_gemm slot of the drop-in table, on device tensors made by the reference. */
+SHIM_API int ref_device_qkv_head_gemm(const float *X, const float *Wqkv, const float *bqkv, int64_t B, int64_t S,
+                                      int64_t H, int64_t dk, float *Qh, float *Kh, float *Vh)
+{
+    const int64_t D = H * dk, n = B * H * S * dk;
+    use_cuda(1);
+    int64_t hshape[3] = { B * H, S, dk };
+    ax_tensor_t *x = to_dev(t2(X, B * S, D)), *w = to_dev(t2(Wqkv, D, 3 * D)), *b = bqkv ? to_dev(t1(bqkv, 3 * D)) : NULL;
+    ax_tensor_t *q = to_dev(ax_tensor_from_array(Qh, hshape, 3, AX_FLOAT32));
+    ax_tensor_t *k = to_dev(ax_tensor_from_array(Kh, hshape, 3, AX_FLOAT32));
+    ax_tensor_t *v = to_dev(ax_tensor_from_array(Vh, hshape, 3, AX_FLOAT32));
+    int rc = (!x || !w || (bqkv && !b) || !q || !k || !v) ? 100 : 0;
+    if (!rc) rc = ax_compute_has_qkv_head_gemm() ? (int)ax_compute_qkv_head_gemm(x, w, b, B, S, H, dk, q, k, v) : 200;
+    if (!rc) {
+        ax_device_synchronize(AX_DEVICE_CUDA);
+        rc = copy_back(q, Qh, n) || copy_back(k, Kh, n) || copy_back(v, Vh, n);
+    }
+    if (x) ax_tensor_destroy(x);
+    if (w) ax_tensor_destroy(w);
+    if (b) ax_tensor_destroy(b);
+    if (q) ax_tensor_destroy(q);
+    if (k) ax_tensor_destroy(k);
+    if (v) ax_tensor_destroy(v);
+    use_cuda(0);
+    return rc;
+}
+
+/* ax_compute_qkv_head_gemm (include/axiom/compute.h:150-170) on the active CPU backend: X[B*S, D],
+   Wqkv[D, 3D], bqkv[3D] or NULL -> Qh, Kh, Vh [B*H, S, dk]. */
+SHIM_API int ref_qkv_head_gemm(const float *X, const float *Wqkv, const float *bqkv, int64_t B, int64_t S,
+                               int64_t H, int64_t dk, float *Qh, float *Kh, float *Vh)
+{
+    const int64_t D = H * dk;
+    ax_compute_set_backend(AX_BACKEND_CPU_SIMD);
+    ax_tensor_t *x = t2(X, B * S, D), *w = t2(Wqkv, D, 3 * D), *b = bqkv ? t1(bqkv, 3 * D) : NULL;
+    int64_t hshape[3] = { B * H, S, dk };
+    ax_tensor_t *q = ax_tensor_zeros(hshape, 3, AX_FLOAT32), *k = ax_tensor_zeros(hshape, 3, AX_FLOAT32),
+                *v = ax_tensor_zeros(hshape, 3, AX_FLOAT32);
+    ax_status_t st = ax_compute_qkv_head_gemm(x, w, b, B, S, H, dk, q, k, v);
+    const size_t bytes = (size_t)(B * H * S * dk) * sizeof(float);
+    memcpy(Qh, tdata(q), bytes); memcpy(Kh, tdata(k), bytes); memcpy(Vh, tdata(v), bytes);
+    ax_tensor_destroy(x); ax_tensor_destroy(w); if (b) ax_tensor_destroy(b);
+    ax_tensor_destroy(q); ax_tensor_destroy(k); ax_tensor_destroy(v);
+    return (int)st;
+}
+
 /* ax_kv_cache_create + cur_len x ax_kv_cache_append + ax_kv_cache_attend (include/axiom/attention.h:341-381).
    Kseq, Vseq: [cur_len, BH, dk] (one appended row set per token); Q_new, out: [BH, dk]. */
 SHIM_API int ref_kv_cache_attend(const float *Kseq, const float *Vseq, const float *Q_new, float *out,

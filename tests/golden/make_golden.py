@@ -27,6 +27,8 @@ GEMM_CASES = [  # name, M, N, K
     ("g_96", 96, 96, 96), ("g_k1", 9, 11, 1), ("g_skinny1", 1, 192, 160), ("g_skinny8", 8, 130, 257),
 ]
 SDPA_CASES = [("s_test", 6, 24, 16, 0.25), ("s_c4like", 3, 80, 64, 0.125)]
+# (name, B, S, H, dk, bias): the fast-path shape class (dk = 64), a head dim off the fast path, no bias
+QKV_CASES = [("qkv_64", 2, 40, 2, 64, 1), ("qkv_24", 3, 10, 2, 24, 1), ("qkv_32_nobias", 1, 70, 3, 32, 0)]
 # (name, BH, max_seq, cur_len, dk): the reference test's shape, a ragged one, a longer cache at the config-4 head dim
 KV_CASES = [("kv_test", 2, 16, 5, 8), ("kv_ragged", 3, 50, 37, 20), ("kv_c4like", 4, 512, 300, 64)]
 
@@ -87,6 +89,15 @@ def main():
         scale = np.float32(1.0 / np.sqrt(dk))
         out[name + "_shape"] = np.array([BH, max_seq, cur_len, dk], np.int64)
         out[name + "_out"] = r.kv_cache_attend(Kc, Vc, Qn, cur_len, scale)
+
+    # fused QKV projection + head-major split (ax_compute_qkv_head_gemm)
+    for name, B, S, H, dk, with_bias in QKV_CASES:
+        D = H * dk
+        X, W = o.uniform((B * S, D), 7), o.normal((D, 3 * D), 13, sigma=1.0 / np.sqrt(D))
+        b = o.uniform((3 * D,), 29) if with_bias else None
+        out[name + "_shape"] = np.array([B, S, H, dk, int(with_bias)], np.int64)
+        q, k, v = r.qkv_head_gemm(X, W, b, B, S, H, dk)
+        out[name + "_q"], out[name + "_k"], out[name + "_v"] = q, k, v
 
     # -- W8A8 known answers (numpy, independent of the C oracle)
     rng = np.random.RandomState(1234)

@@ -178,6 +178,12 @@ class Oracle:
                                   _i64(BH), _i64(S), _i64(dk), C.c_float(scale), int(causal))
         return O, L
 
+    def qkv_head_gemm(self, X, W, b, B, S, H, dk):
+        outs = [np.empty((B * H, S, dk), np.float32) for _ in range(3)]
+        self.lib.orc_qkv_head_gemm(_p(X, _f32p), _p(W, _f32p), _p(b, _f32p) if b is not None else None, _i64(B), _i64(S),
+                                   _i64(H), _i64(dk), *[_p(t, _f32p) for t in outs])
+        return outs
+
     def kv_cache_attend(self, Kc, Vc, Qn, cur_len, scale):
         BH, max_seq, dk = Kc.shape
         out = np.empty((BH, dk), np.float32)
@@ -297,6 +303,13 @@ class Reference:
                               _i64(BH), _i64(S), _i64(dk), C.c_float(scale), int(causal))
         return O, L
 
+
+    def qkv_head_gemm(self, X, W, b, B, S, H, dk):
+        outs = [np.zeros((B * H, S, dk), np.float32) for _ in range(3)]
+        st = self.lib.ref_qkv_head_gemm(_p(X, _f32p), _p(W, _f32p), _p(b, _f32p) if b is not None else None, _i64(B),
+                                        _i64(S), _i64(H), _i64(dk), *[_p(t, _f32p) for t in outs])
+        assert st == 0, st
+        return outs
 
     def kv_cache_attend(self, Kc, Vc, Qn, cur_len, scale):
         """Kc, Vc: cache-layout [BH, max_seq, dk]; the rows are appended token by token through the reference API."""

@@ -4,7 +4,7 @@ The vtable of libaxiom_b200_backend.so is registered with the reference's own
 ax_compute_register_backend; operands reach the GPU through the reference's
 ax_tensor_to_cuda (our storage_alloc / memcpy_h2d hooks); ax_compute_gemm*,
 ax_compute_gemm_relu, ax_compute_gemm_ex, ax_compute_bias_add, ax_compute_relu,
-ax_matmul_bias_relu and the sdpa_fwd extension slot dispatch into our kernels.
+ax_matmul_bias_relu, ax_compute_qkv_head_gemm and the sdpa_fwd extension slot dispatch into our kernels.
 Results are compared with the same reference running its CPU backend.
 """
 import ctypes
@@ -95,6 +95,21 @@ def test_sdpa_extension_slot(dropin, reference, oracle, causal):
     assert rc == 0, dropin.ref_last_error()
     O_ref, L_ref = reference.sdpa_fwd(Q, K, V, 0.25, causal)
     assert np.abs(O - O_ref).max() < 1e-4 and np.abs(L - L_ref).max() < 1e-4
+
+
+@pytest.mark.parametrize("case", [(2, 40, 2, 64, True), (3, 10, 2, 24, True), (1, 70, 3, 32, False), (1, 8, 2, 64, True)])
+def test_qkv_head_gemm_slot(dropin, reference, oracle, case):
+    """ax_compute_qkv_head_gemm dispatches into the qkv_head_gemm slot (the stock CUDA backend leaves it NULL)."""
+    B, S, H, dk, with_bias = case
+    D = H * dk
+    X, W = oracle.uniform((B * S, D), 7), oracle.normal((D, 3 * D), 13, sigma=1.0 / np.sqrt(D))
+    b = oracle.uniform((3 * D,), 29) if with_bias else None
+    outs = [np.full((B * H, S, dk), np.nan, np.float32) for _ in range(3)]
+    rc = dropin.ref_device_qkv_head_gemm(p(X), p(W), p(b), i64(B), i64(S), i64(H), i64(dk), *[p(t) for t in outs])
+    assert rc == 0, (rc, dropin.ref_last_error())
+    for got, want in zip(outs, reference.qkv_head_gemm(X, W, b, B, S, H, dk)):
+        np.testing.assert_allclose(got, want, atol=1e-3, rtol=1e-4)
+        assert nerr(got, want) <= 1e-5
 
 
 def test_bias_add_axis0_is_per_row(dropin, oracle):

@@ -386,3 +386,37 @@ def test_kv_cache_errors(engine):
         engine.kv_cache_append(Kd, Kd, q, q, 4)          # full
     with pytest.raises(EngineError):
         engine.kv_cache_attend(Kd, Kd, q, q, 5, 1.0)     # cur_len > max_seq
+
+
+@pytest.mark.parametrize("name", ["qkv_64", "qkv_24", "qkv_32_nobias"])
+def test_qkv_head_gemm_vs_golden(engine, oracle, golden, name):
+    B, S, H, dk, with_bias = (int(v) for v in golden[name + "_shape"])
+    D = H * dk
+    X, W = oracle.uniform((B * S, D), 7), oracle.normal((D, 3 * D), 13, sigma=1.0 / np.sqrt(D))
+    b = oracle.uniform((3 * D,), 29) if with_bias else None
+    outs = [torch.full((B * H, S, dk), float("nan"), device="cuda") for _ in range(3)]
+    engine.qkv_head_gemm(dev(X), dev(W), dev(b) if with_bias else None, B, S, H, dk, *outs)
+    for got, key in zip(outs, "qkv"):
+        assert nerr(host(got), golden[f"{name}_{key}"]) <= TOL_SPLIT
+
+
+@pytest.mark.parametrize("case", [(8, 128, 16, 64, True), (2, 333, 4, 32, True), (1, 1000, 3, 96, False), (2, 50, 2, 40, True),
+                                  (1, 16, 4, 64, True), (4, 64, 8, 128, True), (1, 200, 5, 8, False)])
+def test_qkv_head_gemm_vs_oracle(engine, oracle, case):
+    """dk % 32 == 0 with more than 32 rows stores head-major from the GEMM epilogue; other shapes go through the
+    scratch matrix and the layout pass.  Both must match the oracle and leave no element unwritten."""
+    B, S, H, dk, with_bias = case
+    D = H * dk
+    X, W = oracle.uniform((B * S, D), 7), oracle.normal((D, 3 * D), 13, sigma=1.0 / np.sqrt(D))
+    b = oracle.uniform((3 * D,), 29) if with_bias else None
+    outs = [torch.full((B * H, S, dk), float("nan"), device="cuda") for _ in range(3)]
+    engine.qkv_head_gemm(dev(X), dev(W), dev(b) if with_bias else None, B, S, H, dk, *outs)
+    want = oracle.qkv_head_gemm(X, W, b, B, S, H, dk)
+    full = oracle.gemm_f64(X, W) + (b.astype(np.float64) if with_bias else 0.0)
+    for i, got in enumerate(outs):
+        g = host(got)
+        assert not np.isnan(g).any()
+        assert nerr(g, want[i]) <= TOL_SPLIT
+        blk = full[:, i * D:(i + 1) * D].reshape(B, S, H, dk).transpose(0, 2, 1, 3).reshape(B * H, S, dk)
+        assert nerr(g, blk) <= TOL_SPLIT
+    assert engine.device_error() == 0
