@@ -885,6 +885,28 @@ extern "C" int axb_sdpa_fwd(const float *Q, const float *K, const float *V, floa
     return e ? cuda_fail("sdpa_fwd", e) : AXB_OK;
 }
 
+extern "C" int axb_sdpa_bwd(const float *Q, const float *K, const float *V, const float *O, const float *dO,
+                            const float *L, float *dQ, float *dK, float *dV, int64_t BH, int64_t S, int64_t dk,
+                            float scale, int causal, const float *P_saved)
+{
+    if (!Q || !K || !V || !O || !dO || !L || !dQ || !dK || !dV) return fail(AXB_ERR_NULL_ARG, "sdpa_bwd: NULL");
+    (void)P_saved;   // scores are always recomputed from Q, K and L: a saved P would only add S*S traffic
+    if (BH < 0 || S < 0 || dk <= 0) return fail(AXB_ERR_INVALID_SHAPE, "sdpa_bwd: bad shape");
+    if (dk > 128) return fail(AXB_ERR_NOT_IMPLEMENTED, "sdpa_bwd: head dim %lld > 128", (long long)dk);
+    if (BH > 65535 || S > (1 << 24)) return fail(AXB_ERR_INVALID_SHAPE, "sdpa_bwd: BH > 65535 or S too large");
+    int st = ensure_ready();
+    if (st) return st;
+    if (BH == 0 || S == 0) return AXB_OK;
+    st = ensure_ws(sdpa_bwd_workspace_bytes(BH, S));
+    if (st) return st;
+    mark(0);
+    mark(1);
+    int e = launch_sdpa_bwd(Q, K, V, O, dO, L, dQ, dK, dV, BH, S, dk, scale, causal, (float *)g.ws, g.sm_count, g.stream);
+    mark(2);
+    g.launches += 3;
+    return e ? cuda_fail("sdpa_bwd", e) : AXB_OK;
+}
+
 // ------------------------------------------------------------------ KV cache
 
 extern "C" int axb_kv_cache_append(float *K_cache, float *V_cache, const float *new_K, const float *new_V, int64_t BH,

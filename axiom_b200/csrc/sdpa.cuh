@@ -8,6 +8,12 @@ namespace axb {
 int launch_sdpa_fwd(const float *Q, const float *K, const float *V, float *O, float *L, int64_t BH,
                     int64_t S, int64_t dk, float scale, int causal, cudaStream_t st);
 
+// Backward (sdpa_bwd.cu): dQ, dK, dV are overwritten; workspace holds BH*S floats (sdpa_bwd_workspace_bytes).
+size_t sdpa_bwd_workspace_bytes(int64_t BH, int64_t S);
+int launch_sdpa_bwd(const float *Q, const float *K, const float *V, const float *O, const float *dO, const float *L,
+                    float *dQ, float *dK, float *dV, int64_t BH, int64_t S, int64_t dk, float scale, int causal,
+                    float *workspace, int sm_count, cudaStream_t st);
+
 // Tensor-core route (sdpa_tc.cu): head dim <= 64 and a multiple of 4, 16-byte aligned tensors, scale > 0.
 // Reads the caller's tensors through TMA and splits them inside the kernel: no pre-pass, no scratch.  A bounded
 // wait that runs out inside the kernel is reported through *err_word.

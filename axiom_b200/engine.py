@@ -26,7 +26,7 @@ EXPORTS = [
     "axb_skinny_gemm_static", "axb_gemm_bias_act_scatter", "axb_gemm_gathered_scatter", "axb_ipc_get_handle", "axb_ipc_open_handle",
     "axb_ipc_close_handle",
     "axb_bias_add", "axb_relu", "axb_gelu", "axb_qgemm_w8a32", "axb_qgemm_w8a8", "axb_quantize_rows",
-    "axb_sdpa_fwd", "axb_kv_cache_append", "axb_kv_cache_attend", "axb_qkv_head_gemm",
+    "axb_sdpa_fwd", "axb_kv_cache_append", "axb_kv_cache_attend", "axb_qkv_head_gemm", "axb_sdpa_bwd",
 ]
 
 
@@ -227,6 +227,12 @@ class Engine:
         self._check(self.lib.axb_sdpa_fwd(_ptr(Q), _ptr(K), _ptr(V), _ptr(out), _ptr(L), _i64(BH), _i64(S), _i64(dk),
                                           _f(scale), int(bool(causal)), None))
         return out, L
+
+    def sdpa_bwd(self, Q, K, V, O, dO, L, dQ, dK, dV, scale, causal):
+        BH, S, dk = Q.shape
+        self._check(self.lib.axb_sdpa_bwd(_ptr(Q), _ptr(K), _ptr(V), _ptr(O), _ptr(dO), _ptr(L), _ptr(dQ), _ptr(dK), _ptr(dV),
+                                          _i64(BH), _i64(S), _i64(dk), _f(scale), int(bool(causal)), None))
+        return dQ, dK, dV
 
     def qkv_head_gemm(self, X, Wqkv, bqkv, B, S, H, dk, Qh, Kh, Vh):
         self._check(self.lib.axb_qkv_head_gemm(_ptr(X), _ptr(Wqkv), _ptr(bqkv), _i64(B), _i64(S), _i64(H), _i64(dk),

@@ -209,6 +209,13 @@ static axb_status ext_sdpa_fwd(const float *Q, const float *K, const float *V, f
     return done(axb_sdpa_fwd(Q, K, V, out, L, BH, S, dk, scale, causal ? 1 : 0, P_save));
 }
 
+static axb_status ext_sdpa_bwd(const float *Q, const float *K, const float *V, const float *O, const float *dO,
+                               const float *L, float *dQ, float *dK, float *dV, int64_t BH, int64_t S, int64_t dk,
+                               float scale, bool causal, const float *P_saved)
+{
+    return done(axb_sdpa_bwd(Q, K, V, O, dO, L, dQ, dK, dV, BH, S, dk, scale, causal ? 1 : 0, P_saved));
+}
+
 static const axb_ax_backend_ops_t ops_table = {
     .name = "b200_tcgen05",
     .gemm = be_gemm,
@@ -234,6 +241,7 @@ static const axb_ax_backend_ops_t ops_table = {
 
 static const axb_ax_cuda_extension_t extension_table = {
     .sdpa_fwd = ext_sdpa_fwd,
+    .sdpa_bwd = ext_sdpa_bwd,
 };
 
 const axb_ax_backend_ops_t *axb_backend_ops(void) { return &ops_table; }

@@ -446,6 +446,18 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
                 "roofline": {"bound": "tensor", "achieved": tf, "peak": bf16 / 6, "frac": tf / (bf16 / 6), "unit": "TFLOP/s",
                              "peak_source": "measured bf16 burst / 2 (tf32 rate) / 3 (products)",
                              "note": "achieved counts the useful FLOP of the key blocks the kernel visits (diagonal blocks whole)"}})
+    # attention backward at config 4 (fp32 FMA kernels; recomputes the scores, no S x S buffer)
+    try:
+        dOt = torch.randn((BH, S, dk), device="cuda")
+        gq, gk, gv = (torch.empty((BH, S, dk), device="cuda") for _ in range(3))
+        step_ms, core_ms, _ = core_time(lambda: eng.sdpa_bwd(Q, Kt, V, O, dOt, L, gq, gk, gv, 0.125, True), 10, 2)
+        out.append({"workload": "causal SDPA bwd BH=128 S=1024 dk=64 (fp32 FMA, dQ and dK/dV kernels)",
+                    "value": 2.5 * 4.0 * BH * S * S * dk / (step_ms * 1e-3) / 1e12,
+                    "unit": "TFLOP/s (2.5 x the forward's 4*BH*S^2*dk convention; causal does half)", "ms_per_step": step_ms,
+                    "kernel_ms": core_ms})
+    except Exception as exc:
+        out.append({"workload": "causal SDPA bwd", "error": repr(exc)})
+
     # fused QKV projection into the head-major layout: B=8, S=1024, D=1024 (H=16, dk=64, the config-4 heads)
     try:
         Bq, Sq, Hq = 8, 1024, 16

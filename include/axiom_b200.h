@@ -209,6 +209,15 @@ AXB_API int axb_quantize_rows(const float *w, int64_t N, int64_t K, int8_t *q, f
 AXB_API int axb_sdpa_fwd(const float *Q, const float *K, const float *V, float *out, float *L,
                  int64_t BH, int64_t S, int64_t dk, float scale, int causal, float *P_save);
 
+/* Slot sdpa_bwd of ax_cuda_extension_t (include/axiom/internal/cuda_extension.h:96-100; reference CUDA
+   implementation src/compute/backends/cuda/ops_attention.cu:443-590 with two BH*S*S scratch buffers, CPU
+   implementation src/compute/backends/cpu_opt.c:9112-9180).  O, dO: [BH, S, dk]; L: [BH, S] from the forward.
+   dQ, dK, dV are OVERWRITTEN (both reference implementations zero them first).  P_saved is accepted and
+   ignored: the scores are recomputed block by block and nothing of size S*S is read or written.  dk <= 128. */
+AXB_API int axb_sdpa_bwd(const float *Q, const float *K, const float *V, const float *O, const float *dO,
+                         const float *L, float *dQ, float *dK, float *dV, int64_t BH, int64_t S, int64_t dk,
+                         float scale, int causal, const float *P_saved);
+
 /* ---- attention projections --------------------------------------------------
    Slot qkv_head_gemm of ax_backend_ops_t (include/axiom/internal/backend_ops.h:107-113; ax_compute_qkv_head_gemm,
    include/axiom/compute.h:150-170; CPU implementation src/compute/backends/cpu_opt.c:6160).  The reference CUDA

@@ -94,14 +94,17 @@ typedef struct {
     axb_status (*memcpy_d2d)(void *dst, const void *src, size_t bytes);
 } axb_ax_backend_ops_t;
 
-/* ax_cuda_extension_t: only sdpa_fwd is provided. */
+/* ax_cuda_extension_t: sdpa_fwd and sdpa_bwd are provided. */
 typedef struct {
     axb_opaque_fn head_interleave_qkv_split, head_interleave_qkv_split_bias, head_interleave, head_deinterleave,
         head_deinterleave_qkv_merge;
     axb_opaque_fn qkv_cache_build, bias_cache_build;
     axb_status (*sdpa_fwd)(const float *Q, const float *K, const float *V, float *out, float *L, int64_t BH,
                            int64_t S, int64_t dk, float scale, bool causal, float *P_save);
-    axb_opaque_fn sdpa_bwd, conv_gemm_batched, conv_winograd_f23, winograd_f23_prefer;
+    axb_status (*sdpa_bwd)(const float *Q, const float *K, const float *V, const float *O, const float *dO,
+                           const float *L, float *dQ, float *dK, float *dV, int64_t BH, int64_t S, int64_t dk,
+                           float scale, bool causal, const float *P_saved);
+    axb_opaque_fn conv_gemm_batched, conv_winograd_f23, winograd_f23_prefer;
 } axb_ax_cuda_extension_t;
 
 #define AXB_BACKEND_API __attribute__((visibility("default")))

@@ -384,6 +384,47 @@ ORC_API void orc_sdpa_fwd_f64(const float *Q, const float *K, const float *V,
     }
 }
 
+/* Attention backward carried in double (src/compute/backends/cpu_opt.c:9112-9180 computes the same quantities
+   tile by tile in fp32): P = softmax(scale*Q.K^T [+causal mask]) recomputed from the inputs,
+   D_i = dO_i.O_i, dV = P^T.dO, dS = P o (dO.V^T - D) * scale, dQ = dS.K, dK = dS^T.Q.  O is the forward output
+   of the same inputs (the caller passes what the forward produced).  Outputs are overwritten. */
+ORC_API void orc_sdpa_bwd_f64(const float *Q, const float *K, const float *V, const float *O, const float *dO,
+                              double *dQ, double *dK, double *dV,
+                              int64_t BH, int64_t S, int64_t dk, float scale, int causal)
+{
+#pragma omp parallel for schedule(dynamic, 1)
+    for (int64_t h = 0; h < BH; h++) {
+        const float *q = Q + h * S * dk, *k = K + h * S * dk, *v = V + h * S * dk, *o = O + h * S * dk, *d_o = dO + h * S * dk;
+        double *dq = dQ + h * S * dk, *dkk = dK + h * S * dk, *dv = dV + h * S * dk;
+        for (int64_t i = 0; i < S * dk; i++) dq[i] = dkk[i] = dv[i] = 0.0;
+        double *p = (double *)malloc((size_t)S * sizeof(double));
+        for (int64_t i = 0; i < S; i++) {
+            const int64_t jend = causal ? i + 1 : S;
+            double mx = -INFINITY, sum = 0.0, Di = 0.0;
+            for (int64_t j = 0; j < jend; j++) {
+                double dot = 0.0;
+                for (int64_t d = 0; d < dk; d++) dot += (double)q[i * dk + d] * (double)k[j * dk + d];
+                p[j] = dot * (double)scale;
+                if (p[j] > mx) mx = p[j];
+            }
+            for (int64_t j = 0; j < jend; j++) { p[j] = exp(p[j] - mx); sum += p[j]; }
+            for (int64_t d = 0; d < dk; d++) Di += (double)d_o[i * dk + d] * (double)o[i * dk + d];
+            for (int64_t j = 0; j < jend; j++) {
+                const double pj = p[j] / sum;
+                double dp = 0.0;
+                for (int64_t d = 0; d < dk; d++) dp += (double)d_o[i * dk + d] * (double)v[j * dk + d];
+                const double ds = pj * (dp - Di) * (double)scale;
+                for (int64_t d = 0; d < dk; d++) {
+                    dv[j * dk + d] += pj * (double)d_o[i * dk + d];
+                    dq[i * dk + d] += ds * (double)k[j * dk + d];
+                    dkk[j * dk + d] += ds * (double)q[i * dk + d];
+                }
+            }
+        }
+        free(p);
+    }
+}
+
 /* QKV projection straight into the head-major layout (src/compute/backends/cpu_opt.c:6160-6260,
    ax_compute_qkv_head_gemm, include/axiom/compute.h:150-170): every output starts at its bias (or zero) and the
    products are accumulated on top in k order; column which*D + h*dk + d of row b*S + s lands in

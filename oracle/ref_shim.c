@@ -364,6 +364,45 @@ SHIM_API int ref_qkv_head_gemm(const float *X, const float *Wqkv, const float *b
     return (int)st;
 }
 
+/* ax_fused_attention_bwd / _causal (include/axiom/attention.h:282-293) on head-major buffers. */
+SHIM_API int ref_sdpa_bwd(const float *Q, const float *K, const float *V, const float *O, const float *dO,
+                          const float *L, float *dQ, float *dK, float *dV,
+                          int64_t BH, int64_t S, int64_t dk, float scale, int causal)
+{
+    if (causal) ax_fused_attention_bwd_causal(Q, K, V, O, dO, L, dQ, dK, dV, BH, S, dk, scale);
+    else        ax_fused_attention_bwd(Q, K, V, O, dO, L, dQ, dK, dV, BH, S, dk, scale);
+    return 0;
+}
+
+/* the sdpa_bwd slot of the registered extension table, on device buffers made by the reference */
+SHIM_API int ref_device_sdpa_bwd(const float *Q, const float *K, const float *V, const float *O, const float *dO,
+                                 const float *L, float *dQ, float *dK, float *dV,
+                                 int64_t BH, int64_t S, int64_t dk, float scale, int causal)
+{
+    const ax_cuda_extension_t *ext = ax_compute_get_cuda_extension();
+    if (!ext || !ext->sdpa_bwd) return 200;
+    use_cuda(1);
+    int64_t sh[3] = { BH, S, dk }, shl[2] = { BH, S };
+    const float *src[9] = { Q, K, V, O, dO, L, dQ, dK, dV };
+    ax_tensor_t *t[9];
+    int rc = 0;
+    for (int i = 0; i < 9; i++) {
+        t[i] = to_dev(i == 5 ? ax_tensor_from_array(src[i], shl, 2, AX_FLOAT32) : ax_tensor_from_array(src[i], sh, 3, AX_FLOAT32));
+        if (!t[i]) rc = 100;
+    }
+    if (!rc)
+        rc = (int)ext->sdpa_bwd(tdata(t[0]), tdata(t[1]), tdata(t[2]), tdata(t[3]), tdata(t[4]), tdata(t[5]),
+                                tdata(t[6]), tdata(t[7]), tdata(t[8]), BH, S, dk, scale, causal != 0, NULL);
+    if (!rc) {
+        ax_device_synchronize(AX_DEVICE_CUDA);
+        rc = copy_back(t[6], dQ, BH * S * dk) || copy_back(t[7], dK, BH * S * dk) || copy_back(t[8], dV, BH * S * dk);
+    }
+    for (int i = 0; i < 9; i++)
+        if (t[i]) ax_tensor_destroy(t[i]);
+    use_cuda(0);
+    return rc;
+}
+
 /* ax_kv_cache_create + cur_len x ax_kv_cache_append + ax_kv_cache_attend (include/axiom/attention.h:341-381).
    Kseq, Vseq: [cur_len, BH, dk] (one appended row set per token); Q_new, out: [BH, dk]. */
 SHIM_API int ref_kv_cache_attend(const float *Kseq, const float *Vseq, const float *Q_new, float *out,

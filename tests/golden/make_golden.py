@@ -81,6 +81,9 @@ def main():
             O, L = r.sdpa_fwd(Q, K_, V, scale, causal)
             out[f"{name}_c{causal}_O"] = O
             out[f"{name}_c{causal}_L"] = L
+            dO = o.normal((BH, S, dk), 53)
+            dq, dk_, dv = r.sdpa_bwd(Q, K_, V, O, dO, L, scale, causal)   # ax_fused_attention_bwd[_causal]
+            out[f"{name}_c{causal}_dQ"], out[f"{name}_c{causal}_dK"], out[f"{name}_c{causal}_dV"] = dq, dk_, dv
 
     # KV-cache single-token attention (tests/test_attention.c:268-330 shape first, then longer caches)
     for name, BH, max_seq, cur_len, dk in KV_CASES:

@@ -178,6 +178,13 @@ class Oracle:
                                   _i64(BH), _i64(S), _i64(dk), C.c_float(scale), int(causal))
         return O, L
 
+    def sdpa_bwd_f64(self, Q, K, V, O, dO, scale, causal):
+        BH, S, dk = Q.shape
+        outs = [np.empty(Q.shape, np.float64) for _ in range(3)]
+        self.lib.orc_sdpa_bwd_f64(_p(Q, _f32p), _p(K, _f32p), _p(V, _f32p), _p(O, _f32p), _p(dO, _f32p),
+                                  *[_p(t, _f64p) for t in outs], _i64(BH), _i64(S), _i64(dk), C.c_float(scale), int(causal))
+        return outs
+
     def qkv_head_gemm(self, X, W, b, B, S, H, dk):
         outs = [np.empty((B * H, S, dk), np.float32) for _ in range(3)]
         self.lib.orc_qkv_head_gemm(_p(X, _f32p), _p(W, _f32p), _p(b, _f32p) if b is not None else None, _i64(B), _i64(S),
@@ -303,6 +310,13 @@ class Reference:
                               _i64(BH), _i64(S), _i64(dk), C.c_float(scale), int(causal))
         return O, L
 
+
+    def sdpa_bwd(self, Q, K, V, O, dO, L, scale, causal):
+        BH, S, dk = Q.shape
+        outs = [np.zeros(Q.shape, np.float32) for _ in range(3)]
+        self.lib.ref_sdpa_bwd(_p(Q, _f32p), _p(K, _f32p), _p(V, _f32p), _p(O, _f32p), _p(dO, _f32p), _p(L, _f32p),
+                              *[_p(t, _f32p) for t in outs], _i64(BH), _i64(S), _i64(dk), C.c_float(scale), int(causal))
+        return outs
 
     def qkv_head_gemm(self, X, W, b, B, S, H, dk):
         outs = [np.zeros((B * H, S, dk), np.float32) for _ in range(3)]

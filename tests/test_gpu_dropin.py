@@ -112,6 +112,20 @@ def test_qkv_head_gemm_slot(dropin, reference, oracle, case):
         assert nerr(got, want) <= 1e-5
 
 
+@pytest.mark.parametrize("causal", [0, 1])
+def test_sdpa_bwd_extension_slot(dropin, reference, oracle, causal):
+    BH, S, dk = 6, 24, 16
+    Q, K, V = oracle.normal((BH, S, dk), 41), oracle.normal((BH, S, dk), 43), oracle.normal((BH, S, dk), 47)
+    dO = oracle.normal((BH, S, dk), 53)
+    O, L = reference.sdpa_fwd(Q, K, V, 0.25, causal)
+    grads = [np.full((BH, S, dk), np.nan, np.float32) for _ in range(3)]
+    rc = dropin.ref_device_sdpa_bwd(p(Q), p(K), p(V), p(O), p(dO), p(L), *[p(t) for t in grads], i64(BH), i64(S), i64(dk),
+                                    ctypes.c_float(0.25), causal)
+    assert rc == 0, dropin.ref_last_error()
+    for got, want in zip(grads, reference.sdpa_bwd(Q, K, V, O, dO, L, 0.25, causal)):
+        assert np.abs(got - want).max() < 1e-4
+
+
 def test_bias_add_axis0_is_per_row(dropin, oracle):
     """axis 0 broadcasts one value per ROW (the documented meaning of the slot), also for M != N."""
     M, N = 4, 6

@@ -420,3 +420,44 @@ def test_qkv_head_gemm_vs_oracle(engine, oracle, case):
         blk = full[:, i * D:(i + 1) * D].reshape(B, S, H, dk).transpose(0, 2, 1, 3).reshape(B * H, S, dk)
         assert nerr(g, blk) <= TOL_SPLIT
     assert engine.device_error() == 0
+
+
+@pytest.mark.parametrize("name", ["s_test", "s_c4like"])
+@pytest.mark.parametrize("causal", [0, 1])
+def test_sdpa_bwd_vs_golden(engine, oracle, golden, name, causal):
+    """ax_fused_attention_bwd[_causal] of the reference on the forward's own O and L."""
+    BH, S, dk = (int(v) for v in golden[name + "_shape"])
+    scale = float(golden[name + "_scale"][0])
+    Q, K, V = oracle.normal((BH, S, dk), 41), oracle.normal((BH, S, dk), 43), oracle.normal((BH, S, dk), 47)
+    dO = oracle.normal((BH, S, dk), 53)
+    Qd, Kd, Vd, dOd = dev(Q), dev(K), dev(V), dev(dO)
+    O = torch.empty((BH, S, dk), device="cuda")
+    L = torch.empty((BH, S), device="cuda")
+    engine.sdpa_fwd(Qd, Kd, Vd, O, L, scale, causal)
+    grads = [torch.full((BH, S, dk), float("nan"), device="cuda") for _ in range(3)]
+    engine.sdpa_bwd(Qd, Kd, Vd, O, dOd, L, *grads, scale, causal)
+    for got, key in zip(grads, ("dQ", "dK", "dV")):
+        assert np.abs(host(got) - golden[f"{name}_c{causal}_{key}"]).max() < 1e-4
+
+
+@pytest.mark.parametrize("shape", [(4, 1024, 64), (2, 333, 64), (3, 200, 128), (2, 129, 40), (5, 64, 16), (2, 70, 6), (1, 513, 72)])
+@pytest.mark.parametrize("causal", [0, 1])
+def test_sdpa_bwd_vs_oracle(engine, oracle, shape, causal):
+    BH, S, dk = shape
+    Q, K, V = oracle.normal((BH, S, dk), 41), oracle.normal((BH, S, dk), 43), oracle.normal((BH, S, dk), 47)
+    dO = oracle.normal((BH, S, dk), 53)
+    scale = 1.0 / np.sqrt(dk)
+    Qd, Kd, Vd, dOd = dev(Q), dev(K), dev(V), dev(dO)
+    O = torch.empty((BH, S, dk), device="cuda")
+    L = torch.empty((BH, S), device="cuda")
+    engine.sdpa_fwd(Qd, Kd, Vd, O, L, scale, causal)
+    grads = [torch.full((BH, S, dk), float("nan"), device="cuda") for _ in range(3)]   # outputs are overwritten
+    engine.sdpa_bwd(Qd, Kd, Vd, O, dOd, L, *grads, scale, causal)
+    want = oracle.sdpa_bwd_f64(Q, K, V, host(O), dO, scale, causal)
+    for got, ref in zip(grads, want):
+        assert nerr(host(got), ref) <= 1e-5
+    again = [torch.empty((BH, S, dk), device="cuda") for _ in range(3)]
+    engine.sdpa_bwd(Qd, Kd, Vd, O, dOd, L, *again, scale, causal)
+    for a, b in zip(again, grads):
+        np.testing.assert_array_equal(host(a), host(b))        # one writer per output, fixed order
+    assert engine.device_error() == 0
