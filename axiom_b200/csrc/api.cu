@@ -733,7 +733,14 @@ extern "C" int axb_gelu(const float *in, float *out, int64_t n)
 extern "C" int axb_qgemm_w8a32(const float *a, const int8_t *q, const float *scales, float *out, int64_t M,
                                int64_t N, int64_t K)
 {
+    return axb_qdense_w8a32(a, q, scales, nullptr, AXB_ACT_NONE, out, M, N, K);
+}
+
+extern "C" int axb_qdense_w8a32(const float *a, const int8_t *q, const float *scales, const float *bias, int act,
+                                float *out, int64_t M, int64_t N, int64_t K)
+{
     if (!a || !q || !scales || !out) return fail(AXB_ERR_NULL_ARG, "qgemm_w8a32: NULL");
+    if (act != AXB_ACT_NONE && act != AXB_ACT_RELU && act != AXB_ACT_GELU) return fail(AXB_ERR_INVALID_SHAPE, "qdense_w8a32: unknown activation %d", act);
     if (M < 0 || N <= 0 || K <= 0) return fail(AXB_ERR_INVALID_SHAPE, "qgemm_w8a32: bad shape");
     if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "qgemm_w8a32: dimension exceeds 2^31-1");
     int st = ensure_ready();
@@ -743,7 +750,7 @@ extern "C" int axb_qgemm_w8a32(const float *a, const int8_t *q, const float *sca
         // skinny activations: stream the int8 rows once, fp32 FMA (the reference's own arithmetic)
         mark(0);
         mark(1);
-        int e = launch_qgemv_w8a32(a, q, scales, out, M, N, K, g.sm_count, g.stream);
+        int e = launch_qgemv_w8a32(a, q, scales, bias, act, out, M, N, K, g.sm_count, g.stream);
         mark(2);
         g.launches++;
         return e ? cuda_fail("w8a32 gemv", e) : AXB_OK;
@@ -772,7 +779,7 @@ extern "C" int axb_qgemm_w8a32(const float *a, const int8_t *q, const float *sca
     prod.chunk_k = prod.n > 1 ? g.chunk_bf16 : 0;
     TcEpilogue ep;
     ep.n_extra = 0;
-    ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = nullptr; ep.colscale = scales; ep.act = ACT_NONE;
+    ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = bias; ep.colscale = scales; ep.act = act;
     ep.out_mode = OUT_F32; ep.C = out; ep.acc_out = nullptr; ep.ldc = N;
     mark(1);
     e = launch_gemm_tc(KIND_BF16, opa, opb, prod, M, N, K, ep, g.err_word, g.sm_count, g.stream);
@@ -905,6 +912,54 @@ extern "C" int axb_sdpa_bwd(const float *Q, const float *K, const float *V, cons
     mark(2);
     g.launches += 3;
     return e ? cuda_fail("sdpa_bwd", e) : AXB_OK;
+}
+
+// ---------------------------------------------------------------- convolution
+
+extern "C" int axb_conv_gemm(const float *weight, const float *input, int64_t C_out, int64_t C_in, int64_t H, int64_t W,
+                             int kh, int kw, int sh, int sw, int ph, int pw, int64_t out_h, int64_t out_w, float *out)
+{
+    if (!weight || !input || !out) return fail(AXB_ERR_NULL_ARG, "conv_gemm: NULL");
+    if (C_out <= 0 || C_in <= 0 || H <= 0 || W <= 0 || kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0 || ph < 0 || pw < 0 ||
+        out_h < 0 || out_w < 0)
+        return fail(AXB_ERR_INVALID_SHAPE, "conv_gemm: bad geometry");
+    const int64_t K = C_in * kh * kw, P = out_h * out_w;
+    if (C_out > INT32_MAX || K > INT32_MAX || P > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "conv_gemm: dimension exceeds 2^31-1");
+    int st = ensure_ready();
+    if (st) return st;
+    if (P == 0) return AXB_OK;
+    // out[C_out, P] = weight[C_out, K] . im2col(input)[K, P]: the weight rows are the A operand, the image patches
+    // are gathered straight into the planes of the B operand
+    int split_mode, kind;
+    TcProducts prod;
+    fp32_mode_plan(split_mode, kind, prod);
+    const SplitOperand sa = plan_split(split_mode, C_out, K), sb = plan_split(split_mode, P, K);
+    st = ensure_ws(sa.total() + sb.total());
+    if (st) return st;
+    Carver carve{ (char *)g.ws };
+    TcOperand opa, opb;
+    mark(0);
+    int e = run_split(sa, weight, K, false, carve, opa);
+    if (e) return cuda_fail("conv_gemm: split weight", e);
+    void *planes[3] = { nullptr, nullptr, nullptr };
+    opb.nplanes = split_num_planes(split_mode);
+    for (int i = 0; i < opb.nplanes; ++i) {
+        planes[i] = carve.take(sb.plane_bytes);
+        opb.plane[i] = planes[i];
+    }
+    opb.rows = P;
+    opb.pitch_elems = sb.pitch;
+    e = split_im2col(split_mode, input, C_in, H, W, kh, kw, sh, sw, ph, pw, out_h, out_w, planes, sb.pitch, g.sm_count, g.stream);
+    g.launches++;
+    if (e) return cuda_fail("conv_gemm: im2col split", e);
+    TcEpilogue ep;
+    ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = nullptr; ep.colscale = nullptr; ep.act = ACT_NONE;
+    ep.out_mode = OUT_F32; ep.C = out; ep.acc_out = nullptr; ep.ldc = P; ep.n_extra = 0;
+    mark(1);
+    e = launch_gemm_tc(kind, opa, opb, prod, C_out, P, K, ep, g.err_word, g.sm_count, g.stream);
+    mark(2);
+    g.launches++;
+    return e ? cuda_fail("conv_gemm", e) : AXB_OK;
 }
 
 // ------------------------------------------------------------------ KV cache

@@ -164,6 +164,27 @@ __global__ void __launch_bounds__(256) split_transpose_kernel(const float *__res
     }
 }
 
+// Implicit im2col: the B operand of a convolution-as-GEMM, written straight into K-major planes.  Row `pix` of
+// the operand is output pixel (oh, ow); its element k = (c, ky, kx) is input[c][oh*sh + ky - ph][ow*sw + kx - pw]
+// (zero outside the image) — the matrix k_im2col_sample materialises in the reference
+// (src/compute/backends/cuda/ops_conv.cu:120-200) never exists here; the planes are the only intermediate.
+template <int MODE>
+__global__ void __launch_bounds__(256) split_im2col_kernel(const float *__restrict__ in, int64_t C_in, int64_t H, int64_t W,
+                                                           int kh, int kw, int sh, int sw, int ph, int pw, int64_t out_h,
+                                                           int64_t out_w, PlanePtrs pl, int64_t pitch)
+{
+    const int64_t K = C_in * kh * kw, total = out_h * out_w * K;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t pix = i / K, k = i - pix * K;
+        const int64_t c = k / (kh * kw);
+        const int r = (int)(k - c * (kh * kw)), ky = r / kw, kx = r - ky * kw;
+        const int64_t oh = pix / out_w, ow = pix - oh * out_w;
+        const int64_t ih = oh * sh + ky - ph, iw = ow * sw + kx - pw;
+        const float x = (ih >= 0 && ih < H && iw >= 0 && iw < W) ? __ldg(in + (c * H + ih) * W + iw) : 0.0f;
+        store1<MODE>(pl.p, pix * pitch + k, x);
+    }
+}
+
 // int8 [rows, k] -> bf16 plane [rows, pitch] (every int8 is exact in bf16)
 __global__ void __launch_bounds__(256) widen_i8_bf16_kernel(const int8_t *__restrict__ in, int64_t rows,
                                                             int64_t k, __nv_bfloat16 *out, int64_t pitch)
@@ -260,6 +281,21 @@ int split_planes(int mode, const float *in, int64_t rows, int64_t k, int64_t ld,
         case SPLIT_BF16X2: split_transpose_kernel<SPLIT_BF16X2><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch); break;
         default: split_transpose_kernel<SPLIT_BF16X3><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch); break;
         }
+    }
+    return (int)cudaGetLastError();
+}
+
+int split_im2col(int mode, const float *in, int64_t C_in, int64_t H, int64_t W, int kh, int kw, int sh, int sw, int ph,
+                 int pw, int64_t out_h, int64_t out_w, void *const planes[3], int64_t pitch, int sm_count, cudaStream_t st)
+{
+    PlanePtrs pl;
+    for (int i = 0; i < 3; ++i) pl.p[i] = planes[i];
+    const int g = grid_for(out_h * out_w * C_in * kh * kw, 256, sm_count);
+    switch (mode) {
+    case SPLIT_TF32X2: split_im2col_kernel<SPLIT_TF32X2><<<g, 256, 0, st>>>(in, C_in, H, W, kh, kw, sh, sw, ph, pw, out_h, out_w, pl, pitch); break;
+    case SPLIT_BF16X1: split_im2col_kernel<SPLIT_BF16X1><<<g, 256, 0, st>>>(in, C_in, H, W, kh, kw, sh, sw, ph, pw, out_h, out_w, pl, pitch); break;
+    case SPLIT_BF16X2: split_im2col_kernel<SPLIT_BF16X2><<<g, 256, 0, st>>>(in, C_in, H, W, kh, kw, sh, sw, ph, pw, out_h, out_w, pl, pitch); break;
+    default: split_im2col_kernel<SPLIT_BF16X3><<<g, 256, 0, st>>>(in, C_in, H, W, kh, kw, sh, sw, ph, pw, out_h, out_w, pl, pitch); break;
     }
     return (int)cudaGetLastError();
 }

@@ -35,6 +35,7 @@ template <int MT>
 __global__ void __launch_bounds__(QV_THREADS) qgemv_w8a32_kernel(const float *__restrict__ a,
                                                                  const int8_t *__restrict__ q,
                                                                  const float *__restrict__ scales,
+                                                                 const float *__restrict__ bias, int act,
                                                                  float *__restrict__ out, int M, int64_t N, int K)
 {
     extern __shared__ __align__(16) float xs[];
@@ -126,12 +127,19 @@ __global__ void __launch_bounds__(QV_THREADS) qgemv_w8a32_kernel(const float *__
             }
         }
         const float sc = __ldg(scales + n);
+        const float bn = bias ? __ldg(bias + n) : 0.0f;
 #pragma unroll
         for (int m = 0; m < MT; ++m) {
             float v = acc[m];
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-            if (lane == 0 && m < M) out[(int64_t)m * N + n] = v * sc;
+            if (lane == 0 && m < M) {
+                v = v * sc;                       // the reference's result (quantize.c:100-177) ...
+                if (bias) v += bn;                // ... and the dense layer's bias and activation on top
+                if (act == 1) v = fmaxf(v, 0.0f);
+                else if (act == 2) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+                out[(int64_t)m * N + n] = v;
+            }
         }
     }
 }
@@ -145,8 +153,8 @@ bool qgemv_w8a32_applicable(int64_t M, int64_t N, int64_t K, const void *q)
 }
 
 template <int MT>
-static int launch_qv(const float *a, const int8_t *q, const float *scales, float *out, int M, int64_t N, int64_t K,
-                     int sm_count, cudaStream_t st)
+static int launch_qv(const float *a, const int8_t *q, const float *scales, const float *bias, int act, float *out, int M,
+                     int64_t N, int64_t K, int sm_count, cudaStream_t st)
 {
     auto k = qgemv_w8a32_kernel<MT>;
     const size_t smem = (size_t)MT * K * sizeof(float);
@@ -160,17 +168,17 @@ static int launch_qv(const float *a, const int8_t *q, const float *scales, float
     int64_t blocks = (N + QV_WARPS - 1) / QV_WARPS;
     const int64_t cap = (int64_t)sm_count * (smem > 48 * 1024 ? 2 : 4);
     if (blocks > cap) blocks = cap;
-    k<<<(unsigned)blocks, QV_THREADS, smem, st>>>(a, q, scales, out, M, N, (int)K);
+    k<<<(unsigned)blocks, QV_THREADS, smem, st>>>(a, q, scales, bias, act, out, M, N, (int)K);
     return (int)cudaGetLastError();
 }
 
-int launch_qgemv_w8a32(const float *a, const int8_t *q, const float *scales, float *out, int64_t M, int64_t N,
-                       int64_t K, int sm_count, cudaStream_t st)
+int launch_qgemv_w8a32(const float *a, const int8_t *q, const float *scales, const float *bias, int act, float *out,
+                       int64_t M, int64_t N, int64_t K, int sm_count, cudaStream_t st)
 {
-    if (M <= 1) return launch_qv<1>(a, q, scales, out, (int)M, N, K, sm_count, st);
-    if (M <= 2) return launch_qv<2>(a, q, scales, out, (int)M, N, K, sm_count, st);
-    if (M <= 4) return launch_qv<4>(a, q, scales, out, (int)M, N, K, sm_count, st);
-    return launch_qv<8>(a, q, scales, out, (int)M, N, K, sm_count, st);
+    if (M <= 1) return launch_qv<1>(a, q, scales, bias, act, out, (int)M, N, K, sm_count, st);
+    if (M <= 2) return launch_qv<2>(a, q, scales, bias, act, out, (int)M, N, K, sm_count, st);
+    if (M <= 4) return launch_qv<4>(a, q, scales, bias, act, out, (int)M, N, K, sm_count, st);
+    return launch_qv<8>(a, q, scales, bias, act, out, (int)M, N, K, sm_count, st);
 }
 
 }  // namespace axb

@@ -7,7 +7,8 @@ namespace axb {
 
 // M <= 8, K a multiple of 16 that fits shared memory, q 16-byte aligned
 bool qgemv_w8a32_applicable(int64_t M, int64_t N, int64_t K, const void *q);
-int launch_qgemv_w8a32(const float *a, const int8_t *q, const float *scales, float *out, int64_t M, int64_t N,
-                       int64_t K, int sm_count, cudaStream_t st);
+// out = act(scale[n] * sum_k a*q (+ bias[n])); bias may be null, act 0 none / 1 ReLU / 2 GELU (tanh form)
+int launch_qgemv_w8a32(const float *a, const int8_t *q, const float *scales, const float *bias, int act, float *out,
+                       int64_t M, int64_t N, int64_t K, int sm_count, cudaStream_t st);
 
 }  // namespace axb

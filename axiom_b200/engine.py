@@ -26,7 +26,7 @@ EXPORTS = [
     "axb_skinny_gemm_static", "axb_gemm_bias_act_scatter", "axb_gemm_gathered_scatter", "axb_ipc_get_handle", "axb_ipc_open_handle",
     "axb_ipc_close_handle",
     "axb_bias_add", "axb_relu", "axb_gelu", "axb_qgemm_w8a32", "axb_qgemm_w8a8", "axb_quantize_rows",
-    "axb_sdpa_fwd", "axb_kv_cache_append", "axb_kv_cache_attend", "axb_qkv_head_gemm", "axb_sdpa_bwd",
+    "axb_sdpa_fwd", "axb_kv_cache_append", "axb_kv_cache_attend", "axb_qkv_head_gemm", "axb_sdpa_bwd", "axb_conv_gemm", "axb_qdense_w8a32",
 ]
 
 
@@ -210,6 +210,12 @@ class Engine:
         self._check(self.lib.axb_qgemm_w8a32(_ptr(a), _ptr(q), _ptr(scales), _ptr(out), _i64(M), _i64(N), _i64(K)))
         return out
 
+    def qdense_w8a32(self, a, q, scales, bias, out, act="none"):
+        M, K = a.shape; N = q.shape[0]
+        self._check(self.lib.axb_qdense_w8a32(_ptr(a), _ptr(q), _ptr(scales), _ptr(bias), ACT[act], _ptr(out), _i64(M),
+                                              _i64(N), _i64(K)))
+        return out
+
     def qgemm_w8a8(self, a_q, a_scale, b_q, b_scales, out_scale, out_q=None, acc_out=None):
         M, K = a_q.shape; N = b_q.shape[0]
         self._check(self.lib.axb_qgemm_w8a8(_ptr(a_q), _f(a_scale), _ptr(b_q), _ptr(b_scales), _f(out_scale),
@@ -227,6 +233,16 @@ class Engine:
         self._check(self.lib.axb_sdpa_fwd(_ptr(Q), _ptr(K), _ptr(V), _ptr(out), _ptr(L), _i64(BH), _i64(S), _i64(dk),
                                           _f(scale), int(bool(causal)), None))
         return out, L
+
+    def conv_gemm(self, weight, inp, kh, kw, sh, sw, ph, pw, out):
+        """weight [C_out, C_in*kh*kw], inp [C_in, H, W], out [C_out, out_h*out_w] with the usual output size."""
+        C_in, H, W = inp.shape
+        C_out = weight.shape[0]
+        out_h, out_w = (H + 2 * ph - kh) // sh + 1, (W + 2 * pw - kw) // sw + 1
+        assert tuple(out.shape) == (C_out, out_h * out_w)
+        self._check(self.lib.axb_conv_gemm(_ptr(weight), _ptr(inp), _i64(C_out), _i64(C_in), _i64(H), _i64(W), kh, kw, sh, sw,
+                                           ph, pw, _i64(out_h), _i64(out_w), _ptr(out)))
+        return out
 
     def sdpa_bwd(self, Q, K, V, O, dO, L, dQ, dK, dV, scale, causal):
         BH, S, dk = Q.shape

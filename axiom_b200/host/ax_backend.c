@@ -163,6 +163,20 @@ static axb_status be_qkv_head_gemm(const axb_ax_tensor_t *X, const axb_ax_tensor
     return done(axb_qkv_head_gemm(fptr(X), fptr(Wqkv), bias_p, B, S, H, dk, fptr(Qh), fptr(Kh), fptr(Vh)));
 }
 
+/* shape rules of the reference's CUDA implementation (src/compute/backends/cuda/ops_conv.cu:113-142); params->input
+   is a raw pointer into the (device-resident) batched input, as the conv layer passes it */
+static axb_status be_conv_gemm(const axb_ax_tensor_t *weight, const axb_ax_conv_params_t *params, axb_ax_tensor_t *out)
+{
+    axb_status st;
+    if (!params || !params->input) return report(ST_NULL_ARG, "conv_gemm: NULL params");
+    if ((st = check_f32(weight, "conv_gemm", 2)) || (st = check_f32(out, "conv_gemm", 2))) return st;
+    const int64_t C_out = weight->shape[0], K = weight->shape[1], M = params->out_h * params->out_w;
+    if (K != params->C_in * params->kh * params->kw) return report(ST_SHAPE, "conv_gemm: weight columns must equal C_in*kh*kw");
+    if (out->shape[0] != C_out || out->shape[1] != M) return report(ST_SHAPE, "conv_gemm: out must be [C_out, out_h*out_w]");
+    return done(axb_conv_gemm(fptr(weight), params->input, C_out, params->C_in, params->H, params->W, params->kh, params->kw,
+                              params->sh, params->sw, params->ph, params->pw, params->out_h, params->out_w, fptr(out)));
+}
+
 static axb_status be_bias_add(const axb_ax_tensor_t *in, const axb_ax_tensor_t *bias, int axis, axb_ax_tensor_t *out)
 {
     axb_status st;
@@ -225,6 +239,7 @@ static const axb_ax_backend_ops_t ops_table = {
     .gemm_relu = be_gemm_relu,
     .gemm_ex = be_gemm_ex,
     .bias_add = be_bias_add,
+    .conv_gemm = be_conv_gemm,
     .relu = be_relu,
     .gelu_op = be_gelu,
     .device = AXB_AX_DEVICE_CUDA,

@@ -446,6 +446,17 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
                 "roofline": {"bound": "tensor", "achieved": tf, "peak": bf16 / 6, "frac": tf / (bf16 / 6), "unit": "TFLOP/s",
                              "peak_source": "measured bf16 burst / 2 (tf32 rate) / 3 (products)",
                              "note": "achieved counts the useful FLOP of the key blocks the kernel visits (diagonal blocks whole)"}})
+    # convolution as GEMM: a ResNet 3x3 layer on one sample (C_in = C_out = 256, 56x56, pad 1): weight [256 x 2304]
+    try:
+        wc, xc = torch.randn((256, 2304), device="cuda") / 48, uniform((256, 56, 56))
+        oc = torch.empty((256, 56 * 56), device="cuda")
+        step_ms, core_ms, pre_ms = core_time(lambda: eng.conv_gemm(wc, xc, 3, 3, 1, 1, 1, 1, oc), 20, 3)
+        out.append({"workload": "conv 3x3 pad 1 as GEMM, one sample [256,56,56] -> [256,56,56] (implicit im2col into the operand planes)",
+                    "value": 2.0 * 256 * 2304 * 3136 / (step_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": step_ms,
+                    "kernel_ms": core_ms, "prepass_ms": pre_ms})
+    except Exception as exc:
+        out.append({"workload": "conv 3x3 as GEMM", "error": repr(exc)})
+
     # attention backward at config 4 (fp32 FMA kernels; recomputes the scores, no S x S buffer)
     try:
         dOt = torch.randn((BH, S, dk), device="cuda")

@@ -186,6 +186,13 @@ AXB_API int axb_gelu(const float *in, float *out, int64_t n);
    src/core/quantize.c:100-177); q/scales/N/K are the fields of ax_qweight_t. */
 AXB_API int axb_qgemm_w8a32(const float *a, const int8_t *q, const float *scales, float *out,
                     int64_t M, int64_t N, int64_t K);
+
+/* The quantised dense layer the reference does not have ("raw kernel", docs/EMBEDDED.md:358: callers add bias and
+   activation themselves after ax_qgemm_w8a32): out[m,n] = act(scale[n] * sum_k a[m,k]*q[n,k] + bias[n]) in one
+   launch.  bias may be NULL; act is AXB_ACT_NONE / AXB_ACT_RELU / AXB_ACT_GELU.  axb_qgemm_w8a32 is this entry with
+   no bias and no activation. */
+AXB_API int axb_qdense_w8a32(const float *a, const int8_t *q, const float *scales, const float *bias, int act,
+                             float *out, int64_t M, int64_t N, int64_t K);
 /* W8A8: acc[m,n] = sum_k a_q[m,k] * b_q[n,k] in int32 (exact), then
      out_q[m,n] = clamp(rint(acc * ((a_scale * b_scales[n]) / out_scale)), -127, 127).
    acc_out (int32 [M,N]) and out_q (int8 [M,N]) may each be NULL.
@@ -228,6 +235,16 @@ AXB_API int axb_sdpa_bwd(const float *Q, const float *K, const float *V, const f
    For dk % 32 == 0 the GEMM's epilogue stores head-major itself (one launch, no [B*S, 3D] intermediate). */
 AXB_API int axb_qkv_head_gemm(const float *X, const float *Wqkv, const float *bqkv, int64_t B, int64_t S, int64_t H,
                               int64_t dk, float *Qh, float *Kh, float *Vh);
+
+/* ---- convolution as GEMM -----------------------------------------------------
+   Slot conv_gemm of ax_backend_ops_t (include/axiom/internal/backend_ops.h:199-202; ax_compute_conv_gemm,
+   src/compute/dispatch.c:723; reference CUDA implementation src/compute/backends/cuda/ops_conv.cu:113-215:
+   k_im2col_sample into a col buffer, then cuBLAS).  One [C_in, H, W] sample (ax_conv_params_t,
+   include/axiom/compute.h:36-43):
+     out[C_out, out_h*out_w] = weight[C_out, C_in*kh*kw] . im2col(input),  zero padding ph, pw; strides sh, sw.
+   The patches are gathered straight into the tensor-core operand planes: no col matrix is materialised. */
+AXB_API int axb_conv_gemm(const float *weight, const float *input, int64_t C_out, int64_t C_in, int64_t H, int64_t W,
+                          int kh, int kw, int sh, int sw, int ph, int pw, int64_t out_h, int64_t out_w, float *out);
 
 /* ---- KV cache (autoregressive decode) ---------------------------------------
    Device-pointer forms of ax_kv_cache_append / ax_kv_cache_attend (include/axiom/attention.h:341-381), whose

@@ -51,6 +51,16 @@ typedef struct axb_ax_tensor {
     int layout;                         /* ax_layout_t */
 } axb_ax_tensor_t;
 
+/* ax_conv_params_t (include/axiom/compute.h:36-43): one [C_in, H, W] sample plus the kernel geometry */
+typedef struct {
+    const float *input;
+    int64_t C_in, H, W;
+    int kh, kw;
+    int sh, sw;
+    int ph, pw;
+    int64_t out_h, out_w;
+} axb_ax_conv_params_t;
+
 typedef void (*axb_opaque_fn)(void);    /* a slot this engine leaves NULL */
 typedef int axb_status;                 /* ax_status_t */
 
@@ -74,7 +84,8 @@ typedef struct {
                           axb_ax_tensor_t *out);
     axb_opaque_fn add_relu, axpy, softmax_rowwise;
     axb_status (*bias_add)(const axb_ax_tensor_t *in, const axb_ax_tensor_t *bias, int axis, axb_ax_tensor_t *out);
-    axb_opaque_fn conv_gemm, conv_gemm_nt_dw;
+    axb_status (*conv_gemm)(const axb_ax_tensor_t *weight, const axb_ax_conv_params_t *params, axb_ax_tensor_t *out);
+    axb_opaque_fn conv_gemm_nt_dw;
     axb_opaque_fn sum, mean, max_op, min_op, argmax;
     axb_opaque_fn equal, greater;
     axb_opaque_fn fill, copy;

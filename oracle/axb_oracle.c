@@ -384,6 +384,31 @@ ORC_API void orc_sdpa_fwd_f64(const float *Q, const float *K, const float *V,
     }
 }
 
+/* Convolution of one sample as the reference's conv_gemm slot defines it (include/axiom/internal/backend_ops.h:193-202,
+   ax_conv_params_t in include/axiom/compute.h:36-43; CUDA path k_im2col_sample + GEMM,
+   src/compute/backends/cuda/ops_conv.cu:120-215): out[co, oh*out_w + ow] = sum over (c, ky, kx) of
+   weight[co, (c*kh + ky)*kw + kx] * input[c, oh*sh + ky - ph, ow*sw + kx - pw], zero outside the image.
+   fp32, terms added in k order. */
+ORC_API void orc_conv_gemm(const float *weight, const float *input, int64_t C_out, int64_t C_in, int64_t H, int64_t W,
+                           int kh, int kw, int sh, int sw, int ph, int pw, int64_t out_h, int64_t out_w, float *out)
+{
+    const int64_t K = C_in * kh * kw, P = out_h * out_w;
+#pragma omp parallel for schedule(static)
+    for (int64_t co = 0; co < C_out; co++)
+        for (int64_t pix = 0; pix < P; pix++) {
+            const int64_t oh = pix / out_w, ow = pix - oh * out_w;
+            float acc = 0.0f;
+            for (int64_t c = 0; c < C_in; c++)
+                for (int ky = 0; ky < kh; ky++)
+                    for (int kx = 0; kx < kw; kx++) {
+                        const int64_t ih = oh * sh + ky - ph, iw = ow * sw + kx - pw;
+                        if (ih >= 0 && ih < H && iw >= 0 && iw < W)
+                            acc += weight[co * K + (c * kh + ky) * kw + kx] * input[(c * H + ih) * W + iw];
+                    }
+            out[co * P + pix] = acc;
+        }
+}
+
 /* Attention backward carried in double (src/compute/backends/cpu_opt.c:9112-9180 computes the same quantities
    tile by tile in fp32): P = softmax(scale*Q.K^T [+causal mask]) recomputed from the inputs,
    D_i = dO_i.O_i, dV = P^T.dO, dS = P o (dO.V^T - D) * scale, dQ = dS.K, dK = dS^T.Q.  O is the forward output

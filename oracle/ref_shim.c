@@ -364,6 +364,38 @@ SHIM_API int ref_qkv_head_gemm(const float *X, const float *Wqkv, const float *b
     return (int)st;
 }
 
+/* ax_compute_conv_gemm (src/compute/dispatch.c:723) for one sample; device = 0 runs the reference's CPU backend
+   (which falls back to im2col + gemm when it has no conv_gemm slot: status 10 means not implemented), device = 1 the
+   registered device backend with weight, input and output moved by the reference. */
+SHIM_API int ref_conv_gemm(const float *weight, const float *input, int64_t C_out, int64_t C_in, int64_t H, int64_t W,
+                           int kh, int kw, int sh, int sw, int ph, int pw, int64_t out_h, int64_t out_w, float *out,
+                           int device)
+{
+    const int64_t K = C_in * kh * kw, P = out_h * out_w;
+    int64_t ishape[3] = { C_in, H, W };
+    int rc = 0;
+    if (device) use_cuda(1); else ax_compute_set_backend(AX_BACKEND_CPU_SIMD);
+    ax_tensor_t *w = t2(weight, C_out, K), *in = ax_tensor_from_array(input, ishape, 3, AX_FLOAT32), *o = t2(out, C_out, P);
+    if (device) { w = to_dev(w); in = to_dev(in); o = to_dev(o); }
+    if (!w || !in || !o) rc = 100;
+    if (!rc) {
+        ax_conv_params_t prm;
+        prm.input = tdata(in);
+        prm.C_in = C_in; prm.H = H; prm.W = W; prm.kh = kh; prm.kw = kw; prm.sh = sh; prm.sw = sw; prm.ph = ph; prm.pw = pw;
+        prm.out_h = out_h; prm.out_w = out_w;
+        rc = (int)ax_compute_conv_gemm(w, &prm, o);
+    }
+    if (!rc) {
+        if (device) { ax_device_synchronize(AX_DEVICE_CUDA); rc = copy_back(o, out, C_out * P); }
+        else memcpy(out, tdata(o), (size_t)(C_out * P) * sizeof(float));
+    }
+    if (w) ax_tensor_destroy(w);
+    if (in) ax_tensor_destroy(in);
+    if (o) ax_tensor_destroy(o);
+    if (device) use_cuda(0);
+    return rc;
+}
+
 /* ax_fused_attention_bwd / _causal (include/axiom/attention.h:282-293) on head-major buffers. */
 SHIM_API int ref_sdpa_bwd(const float *Q, const float *K, const float *V, const float *O, const float *dO,
                           const float *L, float *dQ, float *dK, float *dV,

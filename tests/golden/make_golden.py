@@ -27,6 +27,9 @@ GEMM_CASES = [  # name, M, N, K
     ("g_96", 96, 96, 96), ("g_k1", 9, 11, 1), ("g_skinny1", 1, 192, 160), ("g_skinny8", 8, 130, 257),
 ]
 SDPA_CASES = [("s_test", 6, 24, 16, 0.25), ("s_c4like", 3, 80, 64, 0.125)]
+# (name, C_out, C_in, H, W, kh, kw, sh, sw, ph, pw)
+CONV_CASES = [("conv_3x3_same", 8, 3, 12, 10, 3, 3, 1, 1, 1, 1), ("conv_3x3_s2", 16, 4, 9, 9, 3, 3, 2, 2, 0, 0),
+              ("conv_1x1", 5, 2, 7, 8, 1, 1, 1, 1, 0, 0), ("conv_5x3_mixed", 12, 6, 14, 14, 5, 3, 2, 1, 2, 1)]
 # (name, B, S, H, dk, bias): the fast-path shape class (dk = 64), a head dim off the fast path, no bias
 QKV_CASES = [("qkv_64", 2, 40, 2, 64, 1), ("qkv_24", 3, 10, 2, 24, 1), ("qkv_32_nobias", 1, 70, 3, 32, 0)]
 # (name, BH, max_seq, cur_len, dk): the reference test's shape, a ragged one, a longer cache at the config-4 head dim
@@ -101,6 +104,14 @@ def main():
         out[name + "_shape"] = np.array([B, S, H, dk, int(with_bias)], np.int64)
         q, k, v = r.qkv_head_gemm(X, W, b, B, S, H, dk)
         out[name + "_q"], out[name + "_k"], out[name + "_v"] = q, k, v
+
+    # implicit-im2col convolution GEMM of one sample (ax_compute_conv_gemm on the CPU backend)
+    for name, C_out, C_in, H, W, kh, kw, sh, sw, ph, pw in CONV_CASES:
+        w, x = o.uniform((C_out, C_in * kh * kw), 7), o.uniform((C_in, H, W), 13)
+        st, y = r.conv_gemm(w, x, kh, kw, sh, sw, ph, pw)
+        assert st == 0, st
+        out[name + "_geom"] = np.array([C_out, C_in, H, W, kh, kw, sh, sw, ph, pw], np.int64)
+        out[name + "_out"] = y
 
     # -- W8A8 known answers (numpy, independent of the C oracle)
     rng = np.random.RandomState(1234)

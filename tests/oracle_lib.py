@@ -178,6 +178,15 @@ class Oracle:
                                   _i64(BH), _i64(S), _i64(dk), C.c_float(scale), int(causal))
         return O, L
 
+    def conv_gemm(self, weight, inp, kh, kw, sh, sw, ph, pw):
+        C_in, H, W = inp.shape
+        C_out = weight.shape[0]
+        out_h, out_w = (H + 2 * ph - kh) // sh + 1, (W + 2 * pw - kw) // sw + 1
+        out = np.empty((C_out, out_h * out_w), np.float32)
+        self.lib.orc_conv_gemm(_p(weight, _f32p), _p(inp, _f32p), _i64(C_out), _i64(C_in), _i64(H), _i64(W), kh, kw, sh, sw,
+                               ph, pw, _i64(out_h), _i64(out_w), _p(out, _f32p))
+        return out
+
     def sdpa_bwd_f64(self, Q, K, V, O, dO, scale, causal):
         BH, S, dk = Q.shape
         outs = [np.empty(Q.shape, np.float64) for _ in range(3)]
@@ -310,6 +319,15 @@ class Reference:
                               _i64(BH), _i64(S), _i64(dk), C.c_float(scale), int(causal))
         return O, L
 
+
+    def conv_gemm(self, weight, inp, kh, kw, sh, sw, ph, pw, device=0):
+        C_in, H, W = inp.shape
+        C_out = weight.shape[0]
+        out_h, out_w = (H + 2 * ph - kh) // sh + 1, (W + 2 * pw - kw) // sw + 1
+        out = np.zeros((C_out, out_h * out_w), np.float32)
+        st = self.lib.ref_conv_gemm(_p(weight, _f32p), _p(inp, _f32p), _i64(C_out), _i64(C_in), _i64(H), _i64(W), kh, kw,
+                                    sh, sw, ph, pw, _i64(out_h), _i64(out_w), _p(out, _f32p), int(device))
+        return st, out
 
     def sdpa_bwd(self, Q, K, V, O, dO, L, scale, causal):
         BH, S, dk = Q.shape

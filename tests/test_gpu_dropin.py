@@ -112,6 +112,19 @@ def test_qkv_head_gemm_slot(dropin, reference, oracle, case):
         assert nerr(got, want) <= 1e-5
 
 
+@pytest.mark.parametrize("geom", [(8, 3, 12, 10, 3, 3, 1, 1, 1, 1), (16, 4, 9, 9, 3, 3, 2, 2, 0, 0), (12, 6, 14, 14, 5, 3, 2, 1, 2, 1)])
+def test_conv_gemm_slot(dropin, reference, oracle, geom):
+    """ax_compute_conv_gemm on device tensors made by the reference lands in the conv_gemm slot."""
+    C_out, C_in, H, W, kh, kw, sh, sw, ph, pw = geom
+    w, x = oracle.uniform((C_out, C_in * kh * kw), 7), oracle.uniform((C_in, H, W), 13)
+    st, got = reference.conv_gemm(w, x, kh, kw, sh, sw, ph, pw, device=1)
+    assert st == 0, (st, dropin.ref_last_error())
+    st, want = reference.conv_gemm(w, x, kh, kw, sh, sw, ph, pw, device=0)
+    assert st == 0
+    np.testing.assert_allclose(got, want, atol=1e-3, rtol=1e-4)
+    assert nerr(got, want) <= 1e-5
+
+
 @pytest.mark.parametrize("causal", [0, 1])
 def test_sdpa_bwd_extension_slot(dropin, reference, oracle, causal):
     BH, S, dk = 6, 24, 16

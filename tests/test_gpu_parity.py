@@ -461,3 +461,48 @@ def test_sdpa_bwd_vs_oracle(engine, oracle, shape, causal):
     for a, b in zip(again, grads):
         np.testing.assert_array_equal(host(a), host(b))        # one writer per output, fixed order
     assert engine.device_error() == 0
+
+
+@pytest.mark.parametrize("name", ["conv_3x3_same", "conv_3x3_s2", "conv_1x1", "conv_5x3_mixed"])
+def test_conv_gemm_vs_golden(engine, oracle, golden, name):
+    C_out, C_in, H, W, kh, kw, sh, sw, ph, pw = (int(v) for v in golden[name + "_geom"])
+    w, x = oracle.uniform((C_out, C_in * kh * kw), 7), oracle.uniform((C_in, H, W), 13)
+    want = golden[name + "_out"]
+    out = torch.full(want.shape, float("nan"), device="cuda")
+    engine.conv_gemm(dev(w), dev(x), kh, kw, sh, sw, ph, pw, out)
+    assert nerr(host(out), want) <= TOL_SPLIT
+    np.testing.assert_array_equal(oracle.conv_gemm(w, x, kh, kw, sh, sw, ph, pw).shape, want.shape)
+
+
+@pytest.mark.parametrize("geom", [(64, 3, 224, 224, 7, 7, 2, 2, 3, 3), (128, 64, 56, 56, 3, 3, 1, 1, 1, 1), (256, 128, 28, 28, 3, 3, 2, 2, 1, 1),
+                                  (10, 1, 28, 28, 5, 5, 1, 1, 0, 0), (33, 7, 17, 13, 3, 2, 2, 3, 1, 0), (512, 256, 14, 14, 1, 1, 1, 1, 0, 0)])
+def test_conv_gemm_vs_oracle(engine, oracle, geom):
+    """ResNet-style layers (7x7/2 stem, 3x3 same, 3x3/2, 1x1), an MNIST-size 5x5 and a ragged one."""
+    C_out, C_in, H, W, kh, kw, sh, sw, ph, pw = geom
+    w = oracle.normal((C_out, C_in * kh * kw), 7, sigma=1.0 / np.sqrt(C_in * kh * kw))
+    x = oracle.uniform((C_in, H, W), 13)
+    want = oracle.conv_gemm(w, x, kh, kw, sh, sw, ph, pw)
+    out = torch.full(want.shape, float("nan"), device="cuda")
+    engine.conv_gemm(dev(w), dev(x), kh, kw, sh, sw, ph, pw, out)
+    assert nerr(host(out), want) <= TOL_SPLIT
+    assert engine.device_error() == 0
+
+
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (8, 1000, 2048), (4, 16, 32), (32, 128, 512), (300, 512, 1024)])
+@pytest.mark.parametrize("act", ["none", "relu", "gelu"])
+def test_qdense_w8a32(engine, oracle, shape, act):
+    """Quantised dense layer = the reference's ax_qgemm_w8a32 plus the dense layer's bias and activation in one launch
+    (GEMV kernel for M <= 8, tensor-core kernel above)."""
+    M, N, K = shape
+    a, w = oracle.uniform((M, K), 7), oracle.uniform((N, K), 13)
+    bias = oracle.uniform((N,), 29)
+    q, s = oracle.quantize_rows(w)
+    pre = oracle.qgemm_w8a32_f64(a, q, s) + bias.astype(np.float64)
+    want = {"none": pre, "relu": np.maximum(pre, 0.0),
+            "gelu": 0.5 * pre * (1 + np.tanh(0.7978845608028654 * (pre + 0.044715 * pre ** 3)))}[act]
+    out = torch.full((M, N), float("nan"), device="cuda")
+    engine.qdense_w8a32(dev(a), torch.from_numpy(q).cuda(), dev(s), dev(bias), out, act=act)
+    assert nerr(host(out), want) <= TOL_SPLIT
+    plain = torch.empty((M, N), device="cuda")
+    engine.qgemm_w8a32(dev(a), torch.from_numpy(q).cuda(), dev(s), plain)          # the reference's entry: no bias, no act
+    assert nerr(host(plain), oracle.qgemm_w8a32_f64(a, q, s)) <= TOL_SPLIT
