@@ -30,7 +30,7 @@ static constexpr int PAIR_TILE_M = 256;
 
 template <int KIND, int SWB, int NPROD>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(NUM_THREADS, 1)
-gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
+gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ KernelArgs p)
 {
     constexpr int BN = PAIR_BN;
     constexpr int A_BYTES = BM * SWB;          // this CTA's 128 rows of an A plane
@@ -173,6 +173,7 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
         const int nchunks = (p.k_blocks + p.chunk_kb - 1) / p.chunk_kb;
         uint32_t vt = 0;
         bool alive = true;
+        const bool rows_aligned = KIND != KIND_I8 && epi_rows_aligned(p);
         for (int t = pair; t < total_tiles && alive; t += npairs) {
             int mt, nt;
             tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
@@ -269,48 +270,21 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const KernelArgs p)
                     }
                 }
                 if (!alive) break;
-                if (row_ok) {
+                {
+                    // sums -> this warp's staging tile (row = lane) -> fused epilogue and whole-line stores
+                    float4 *stg = reinterpret_cast<float4 *>(gen_base + HEADER_BYTES + (size_t)p.stages * stage_bytes) + (warp - 2) * 256;
+                    const long long row0 = row - lane;
 #pragma unroll
                     for (int c = 0; c < PIECES; ++c) {
                         const int col0 = col_base + c * 32;
                         if (col0 < p.N) {
-                            const bool full = col0 + 32 <= p.N;
-                            float *dst = out_piece_ptr(p, row, col0);
-                            const bool vec = full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0);
-                            float v[32];
+                            __syncwarp();                      // the previous piece has been read out
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const bool in = full || (col0 + j < p.N);
-                                float x = sum[c * 32 + j] * p.alpha;
-                                if (p.colscale) x *= in ? __ldg(p.colscale + col0 + j) : 0.0f;
-                                if (p.beta != 0.0f) x += p.beta * (in ? dst[j] : 0.0f);
-                                if (p.bias) x += in ? __ldg(p.bias + col0 + j) : 0.0f;
-                                if (p.act == ACT_RELU) x = fmaxf(x, 0.0f);
-                                else if (p.act == ACT_GELU) x = gelu_tanh(x);
-                                v[j] = x;
-                            }
-                            if (vec) {
-#pragma unroll
-                                for (int j = 0; j < 32; j += 4)
-                                    *reinterpret_cast<float4 *>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                    if (col0 + j < p.N) dst[j] = v[j];
-                            }
-                            // the same tile to every further destination (peer gather buffers)
-                            for (int x = 0; x < p.n_extra; ++x) {
-                                float *dx = p.c_extra[x] + row * p.ldc + col0;
-                                if (full && ((reinterpret_cast<uintptr_t>(dx) & 15) == 0)) {
-#pragma unroll
-                                    for (int j = 0; j < 32; j += 4)
-                                        *reinterpret_cast<float4 *>(dx + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                                } else {
-#pragma unroll
-                                    for (int j = 0; j < 32; ++j)
-                                        if (col0 + j < p.N) dx[j] = v[j];
-                                }
-                            }
+                            for (int j4 = 0; j4 < 8; ++j4)
+                                stg[lane * 8 + (j4 ^ (lane & 7))] = make_float4(sum[c * 32 + 4 * j4], sum[c * 32 + 4 * j4 + 1],
+                                                                                sum[c * 32 + 4 * j4 + 2], sum[c * 32 + 4 * j4 + 3]);
+                            __syncwarp();
+                            store_piece_f32(p, stg, row0, col0, lane, rows_aligned);
                         }
                     }
                 }
@@ -338,14 +312,15 @@ static int launch_pair_inst(const TmapPack &tm, KernelArgs &ka, int npa, int npb
                             char *err, size_t err_len)
 {
     const int stage_bytes = npa * BM * SWB + npb * (PAIR_BN / 2) * SWB;
-    int stages = (SMEM_BUDGET - HEADER_BYTES - 1024) / stage_bytes;
+    constexpr int STAGING = KIND == KIND_I8 ? 0 : EPI_STAGING_BYTES;
+    int stages = (SMEM_BUDGET - HEADER_BYTES - 1024 - STAGING) / stage_bytes;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) {
         snprintf(err, err_len, "pair kernel: stage of %d bytes leaves fewer than 2 pipeline stages", stage_bytes);
         return (int)cudaErrorInvalidConfiguration;
     }
     ka.stages = stages;
-    const int smem = HEADER_BYTES + 1024 + stages * stage_bytes;
+    const int smem = HEADER_BYTES + 1024 + stages * stage_bytes + STAGING;
     auto kern = gemm_tc_pair_kernel<KIND, SWB, NPROD>;
     static bool attr_set = false;
     if (!attr_set) {

@@ -15,6 +15,7 @@ static constexpr int B_PRODUCER_WARP = 10;
 static constexpr int HEADER_BYTES = 1024;
 static constexpr int MAX_STAGES = 8;
 static constexpr int SMEM_BUDGET = 227 * 1024;
+static constexpr int EPI_STAGING_BYTES = 8 * 4096;   // fp32 kinds: one 32 x 32 fp32 tile per epilogue warp, after the ring
 
 struct alignas(64) TmapPack {
     CUtensorMap a[TC_MAX_PLANES];
@@ -76,6 +77,78 @@ __device__ __forceinline__ float gelu_tanh(float v)
     return 0.5f * v * (1.0f + tanhf(inner));
 }
 
+
+// fp32 epilogue of one warp's 32 x 32 piece.  The sums arrive row-per-lane (that is how TMEM is read); they are
+// laid into a shared-memory tile (16-byte chunks XOR-swizzled, no bank conflicts either way) and read back so that
+// eight lanes cover the 128 bytes of a row: every global access is whole 128-byte lines, C is read the same way
+// when beta != 0, and the scale / bias / activation arithmetic sits in short ROLLED loops.  The first version kept
+// a row per lane and unrolled everything: 170 KB of straight-line code per kernel (128 inlined tanh), fetched again
+// for every tile through an L2 path the operand loads already saturate — 75 000 cycles per tile, longer than a
+// K = 1024 main loop.
+__device__ __forceinline__ float epi_act(float x, int act)
+{
+    if (act == ACT_RELU) return fmaxf(x, 0.0f);
+    if (act == ACT_GELU) return gelu_tanh(x);
+    return x;
+}
+
+static __device__ __noinline__ void store_piece_f32(const KernelArgs &p, const float4 *stg, long long row0, int col0, int lane,
+                                             bool aligned)
+{
+    if (aligned && col0 + 32 <= p.N) {
+        const int ch = lane & 7, colv = col0 + ch * 4;
+        float cs[4] = { 1.f, 1.f, 1.f, 1.f }, bs[4] = { 0.f, 0.f, 0.f, 0.f };
+        if (p.colscale) { cs[0] = __ldg(p.colscale + colv); cs[1] = __ldg(p.colscale + colv + 1); cs[2] = __ldg(p.colscale + colv + 2); cs[3] = __ldg(p.colscale + colv + 3); }
+        if (p.bias) { bs[0] = __ldg(p.bias + colv); bs[1] = __ldg(p.bias + colv + 1); bs[2] = __ldg(p.bias + colv + 2); bs[3] = __ldg(p.bias + colv + 3); }
+#pragma unroll 1
+        for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + (lane >> 3);
+            if (row0 + r >= p.M) continue;
+            const float4 v = stg[r * 8 + (ch ^ (r & 7))];
+            float *dst = out_piece_ptr(p, row0 + r, col0) + ch * 4;
+            float x[4] = { v.x * p.alpha * cs[0], v.y * p.alpha * cs[1], v.z * p.alpha * cs[2], v.w * p.alpha * cs[3] };
+            if (p.beta != 0.0f) {
+                const float4 c = *reinterpret_cast<const float4 *>(dst);
+                x[0] += p.beta * c.x; x[1] += p.beta * c.y; x[2] += p.beta * c.z; x[3] += p.beta * c.w;
+            }
+            const float4 o = make_float4(epi_act(x[0] + bs[0], p.act), epi_act(x[1] + bs[1], p.act),
+                                         epi_act(x[2] + bs[2], p.act), epi_act(x[3] + bs[3], p.act));
+            *reinterpret_cast<float4 *>(dst) = o;
+            for (int e = 0; e < p.n_extra; ++e)
+                *reinterpret_cast<float4 *>(p.c_extra[e] + (row0 + r) * p.ldc + colv) = o;
+        }
+    } else {
+        // ragged last piece or unaligned rows: lane = column, one 128-byte row per iteration
+        const int col = col0 + lane;
+        const bool ok = col < p.N;
+        const float cs = (p.colscale && ok) ? __ldg(p.colscale + col) : 1.0f;
+        const float bs = (p.bias && ok) ? __ldg(p.bias + col) : 0.0f;
+        const float *sf = reinterpret_cast<const float *>(stg);
+#pragma unroll 1
+        for (int r = 0; r < 32; ++r) {
+            if (!ok || row0 + r >= p.M) continue;
+            float *dst = out_piece_ptr(p, row0 + r, col0) + lane;
+            float x = sf[r * 32 + (((lane >> 2) ^ (r & 7)) << 2) + (lane & 3)] * p.alpha * cs;
+            if (p.beta != 0.0f) x += p.beta * *dst;
+            x = epi_act(x + bs, p.act);
+            *dst = x;
+            for (int e = 0; e < p.n_extra; ++e) p.c_extra[e][(row0 + r) * p.ldc + col] = x;
+        }
+    }
+}
+
+// every row start of every fp32 destination is 16-byte aligned: the 128-bit path of store_piece_f32 may be used
+__device__ __forceinline__ bool epi_rows_aligned(const KernelArgs &p)
+{
+    uintptr_t al;
+    if (p.hs_dk > 0) {
+        al = reinterpret_cast<uintptr_t>(p.hs_out[0]) | reinterpret_cast<uintptr_t>(p.hs_out[1]) | reinterpret_cast<uintptr_t>(p.hs_out[2]);
+    } else {
+        al = reinterpret_cast<uintptr_t>(p.C) | (uintptr_t)((p.ldc & 3) != 0 ? 4 : 0);
+        for (int e = 0; e < p.n_extra; ++e) al |= reinterpret_cast<uintptr_t>(p.c_extra[e]);
+    }
+    return (al & 15) == 0;
+}
 
 // All MMAs of one pipeline stage, fully unrolled.  tcgen05.mma holds the issuing thread while
 // the tensor pipe is busy and the pipe queues next to nothing, so every scalar instruction
