@@ -286,19 +286,23 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
                     for (int c = 0; c < PIECES; ++c) {
                         const int col0 = col_base + c * 32;
                         if (col0 < p.N) {
-                            __syncwarp();                      // the previous piece has been read out
+                            if (p.tma_store && lane == 0) tma_store_wait_read();   // the engine has read the previous piece
+                            __syncwarp();                      // ... and so has every lane
 #pragma unroll
                             for (int j4 = 0; j4 < 8; ++j4)
                                 stg[lane * 8 + (j4 ^ (lane & 7))] = make_float4(sum[c * 32 + 4 * j4], sum[c * 32 + 4 * j4 + 1],
                                                                                 sum[c * 32 + 4 * j4 + 2], sum[c * 32 + 4 * j4 + 3]);
                             __syncwarp();
-                            store_piece_f32(p, stg, row0, col0, lane, rows_aligned);
+                            if (p.tma_store) store_piece_f32_tma(p, &tm.c, stg, row0, col0, lane);
+                            else store_piece_f32(p, stg, row0, col0, lane, rows_aligned);
                         }
                     }
                 }
             }
         }
     }
+
+    if (p.tma_store && warp >= 2 && warp < B_PRODUCER_WARP && lane == 0) tma_store_wait_all();
 
     // ---------------------------------------------------------------- teardown
     // After a wait that ran out, give copies still in flight time to land in
@@ -416,6 +420,28 @@ int encode_f32_batched_tmap(void *tmap_out, const void *ptr, int64_t batch, int6
         snprintf(g_err, sizeof g_err,
                  "cuTensorMapEncodeTiled (batched planes) failed (%d): ptr=%p batch=%lld rows=%lld cols=%lld pitch=%lld",
                  (int)r, ptr, (long long)batch, (long long)rows, (long long)cols, (long long)pitch_elems);
+        return (int)cudaErrorInvalidValue;
+    }
+    return 0;
+}
+
+// fp32 matrix [rows, cols] with row pitch pitch_elems as the destination of 32 x 32 TMA stores, 128-byte swizzle
+static int encode_f32_store_tmap(CUtensorMap *out, float *ptr, int64_t rows, int64_t cols, int64_t pitch_elems)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled entry point not found");
+        return (int)cudaErrorSymbolNotFound;
+    }
+    cuuint64_t dims[2] = { (cuuint64_t)cols, (cuuint64_t)rows };
+    cuuint64_t strides[1] = { (cuuint64_t)pitch_elems * 4 };
+    cuuint32_t box[2] = { 32, 32 };
+    cuuint32_t estr[2] = { 1, 1 };
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled (output) failed (%d): ptr=%p rows=%lld cols=%lld pitch=%lld", (int)r,
+                 (void *)ptr, (long long)rows, (long long)cols, (long long)pitch_elems);
         return (int)cudaErrorInvalidValue;
     }
     return 0;
@@ -539,6 +565,16 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
         for (int i = 0; i < 3; ++i) ka.hs_out[i] = ep.hs_out[i];
         ka.beta = 0.0f;
         ka.n_extra = 0;
+    }
+    // plain aligned fp32 output that is not read back: the staging tiles leave through TMA stores
+    if (kind != KIND_I8 && ep.out_mode == OUT_F32 && ep.hs_dk == 0 && ka.n_extra == 0 && ep.beta == 0.0f && ep.C &&
+        (reinterpret_cast<uintptr_t>(ep.C) & 15) == 0 && ep.ldc % 4 == 0) {
+        static const bool off = getenv("AX_B200_NO_TMA_STORE") != nullptr;
+        if (!off) {
+            int e = encode_f32_store_tmap(&tm.c, reinterpret_cast<float *>(ep.C), M, N, ep.ldc);
+            if (e) return e;
+            ka.tma_store = 1;
+        }
     }
     const int64_t tiles = mt * nt;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);

@@ -25,6 +25,22 @@
 
 namespace axb {
 
+#ifdef AXB_GEMM_PROF
+__device__ unsigned long long g_gemm_prof[32];
+#define GP_DECL(n) long long prof_t[n] = {}; long long prof_c = clock64();
+#define GP_ADD(i) { const long long t_ = clock64(); prof_t[i] += t_ - prof_c; prof_c = t_; }
+#define GP_OUT(base, n) { for (int i_ = 0; i_ < n; ++i_) g_gemm_prof[base + i_] = (unsigned long long)prof_t[i_]; }
+extern "C" __attribute__((visibility("default"))) int axb_debug_gemm_prof(unsigned long long *out)
+{
+    return (int)cudaMemcpyFromSymbol(out, g_gemm_prof, sizeof(unsigned long long) * 32);
+}
+#else
+#define GP_DECL(n)
+#define GP_ADD(i)
+#define GP_OUT(base, n) {}
+#endif
+
+
 static constexpr int PAIR_BN = 256;
 static constexpr int PAIR_TILE_M = 256;
 
@@ -133,23 +149,28 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
             const uint32_t prod_a = p.prod_a, prod_b = p.prod_b;
             const uint64_t desc_hi = smem_desc_kmajor(0, SWB);
             const uint32_t npa_bytes = p.npa * A_BYTES, sbytes = (uint32_t)stage_bytes;
+            GP_DECL(3)
             for (int t = pair; t < total_tiles && ok; t += npairs) {
                 for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += chunk_kb, ++vt) {
                     const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
+                    GP_ADD(2)
                     if (!mbar_wait_bounded(bar_tempty + 8 * acc, aph ^ 1u)) {
                         report(p.err, ERR_MMA_WAIT_TMEM);
                         ok = false;
                         break;
                     }
+                    GP_ADD(0)
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + acc * BN;
                     const int kb1 = min(k_blocks, kb0 + chunk_kb);
                     for (int kb = kb0; kb < kb1; ++kb) {
+                        GP_ADD(2)
                         if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
                             report(p.err, ERR_MMA_WAIT_FULL);
                             ok = false;
                             break;
                         }
+                        GP_ADD(1)
                         tc_fence_after_sync();
                         const uint32_t sa = stage0 + s * sbytes;
                         issue_stage_mmas<KIND, SWB, NPROD, true, A_BYTES, B_BYTES>(
@@ -163,6 +184,8 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
                     if (ok) tc_commit_pair(bar_tfull + 8 * acc, 0x3);
                 }
             }
+            GP_ADD(2)
+            if (pair == 0) GP_OUT(0, 3)
         }
     } else if (warp < B_PRODUCER_WARP) {
         // ---------------------------------------------------------- epilogue
@@ -174,6 +197,7 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
         uint32_t vt = 0;
         bool alive = true;
         const bool rows_aligned = KIND != KIND_I8 && epi_rows_aligned(p);
+        GP_DECL(3)
         for (int t = pair; t < total_tiles && alive; t += npairs) {
             int mt, nt;
             tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
@@ -247,7 +271,9 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
                 for (int j = 0; j < HALF; ++j) sum[j] = 0.0f;
                 for (int ch = 0; ch < nchunks; ++ch, ++vt) {
                     const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
+                    GP_ADD(1)
                     const bool got = mbar_wait_warp_bounded(bar_tfull + 8 * acc, aph);
+                    GP_ADD(0)
                     if (!__all_sync(0xffffffffu, got)) {
                         report(p.err, ERR_EPI_WAIT);
                         alive = false;
@@ -270,6 +296,7 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
                     }
                 }
                 if (!alive) break;
+                GP_ADD(1)
                 {
                     // sums -> this warp's staging tile (row = lane) -> fused epilogue and whole-line stores
                     float4 *stg = reinterpret_cast<float4 *>(gen_base + HEADER_BYTES + (size_t)p.stages * stage_bytes) + (warp - 2) * 256;
@@ -278,19 +305,25 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
                     for (int c = 0; c < PIECES; ++c) {
                         const int col0 = col_base + c * 32;
                         if (col0 < p.N) {
-                            __syncwarp();                      // the previous piece has been read out
+                            if (p.tma_store && lane == 0) tma_store_wait_read();   // the engine has read the previous piece
+                            __syncwarp();                      // ... and so has every lane
 #pragma unroll
                             for (int j4 = 0; j4 < 8; ++j4)
                                 stg[lane * 8 + (j4 ^ (lane & 7))] = make_float4(sum[c * 32 + 4 * j4], sum[c * 32 + 4 * j4 + 1],
                                                                                 sum[c * 32 + 4 * j4 + 2], sum[c * 32 + 4 * j4 + 3]);
                             __syncwarp();
-                            store_piece_f32(p, stg, row0, col0, lane, rows_aligned);
+                            if (p.tma_store) store_piece_f32_tma(p, &tm.c, stg, row0, col0, lane);
+                            else store_piece_f32(p, stg, row0, col0, lane, rows_aligned);
                         }
                     }
                 }
+                GP_ADD(2)
             }
         }
+        if (pair == 0 && rank == 0 && warp == 2 && lane == 0) GP_OUT(8, 3)
     }
+
+    if (p.tma_store && warp >= 2 && warp < B_PRODUCER_WARP && lane == 0) tma_store_wait_all();
 
     // ---------------------------------------------------------------- teardown
     if (p.err && *reinterpret_cast<volatile int *>(p.err) != 0) {

@@ -20,6 +20,7 @@ static constexpr int EPI_STAGING_BYTES = 8 * 4096;   // fp32 kinds: one 32 x 32 
 struct alignas(64) TmapPack {
     CUtensorMap a[TC_MAX_PLANES];
     CUtensorMap b[TC_MAX_PLANES];
+    CUtensorMap c;   // fp32 output [M, N], box 32 x 32, 128-byte swizzle (valid when KernelArgs::tma_store)
 };
 
 struct KernelArgs {
@@ -39,6 +40,7 @@ struct KernelArgs {
     float *c_extra[TC_MAX_EXTRA];
     int n_extra;
     int hs_dk, hs_S, hs_H;   // head-major scatter of the output (hs_dk > 0), see TcEpilogue
+    int tma_store;           // fp32 output leaves through TMA stores of the staging tiles (plain C, beta == 0, aligned)
     float *hs_out[3];
 };
 
@@ -71,10 +73,15 @@ __device__ __forceinline__ float *out_piece_ptr(const KernelArgs &p, long long r
     return p.hs_out[which] + ((b * p.hs_H + h) * p.hs_S + s) * p.hs_dk + d0;
 }
 
+// GELU, tanh form (ax_gelu: src/core/activations.c:267-333).  tanh(u) = 1 - 2 / (exp(2u) + 1) on the fast
+// exponential and reciprocal: a dozen instructions instead of libm's tanhf, absolute error below 1e-6 * |v| — the
+// epilogue warps evaluate 128 of these per thread and tile while the next tile's accumulators wait for them.
 __device__ __forceinline__ float gelu_tanh(float v)
 {
-    const float inner = 0.7978845608028654f * (v + 0.044715f * v * v * v);
-    return 0.5f * v * (1.0f + tanhf(inner));
+    const float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
+    const float e = __expf(2.0f * u);                       // +inf for large u (tanh -> 1), 0 for very negative (-> -1)
+    const float t = 1.0f - __fdividef(2.0f, e + 1.0f);
+    return 0.5f * v * (1.0f + t);
 }
 
 
@@ -92,7 +99,7 @@ __device__ __forceinline__ float epi_act(float x, int act)
     return x;
 }
 
-static __device__ __noinline__ void store_piece_f32(const KernelArgs &p, const float4 *stg, long long row0, int col0, int lane,
+static __device__ __forceinline__ void store_piece_f32(const KernelArgs &p, const float4 *stg, long long row0, int col0, int lane,
                                              bool aligned)
 {
     if (aligned && col0 + 32 <= p.N) {
@@ -100,7 +107,7 @@ static __device__ __noinline__ void store_piece_f32(const KernelArgs &p, const f
         float cs[4] = { 1.f, 1.f, 1.f, 1.f }, bs[4] = { 0.f, 0.f, 0.f, 0.f };
         if (p.colscale) { cs[0] = __ldg(p.colscale + colv); cs[1] = __ldg(p.colscale + colv + 1); cs[2] = __ldg(p.colscale + colv + 2); cs[3] = __ldg(p.colscale + colv + 3); }
         if (p.bias) { bs[0] = __ldg(p.bias + colv); bs[1] = __ldg(p.bias + colv + 1); bs[2] = __ldg(p.bias + colv + 2); bs[3] = __ldg(p.bias + colv + 3); }
-#pragma unroll 1
+#pragma unroll 2
         for (int it = 0; it < 8; ++it) {
             const int r = it * 4 + (lane >> 3);
             if (row0 + r >= p.M) continue;
@@ -148,6 +155,37 @@ __device__ __forceinline__ bool epi_rows_aligned(const KernelArgs &p)
         for (int e = 0; e < p.n_extra; ++e) al |= reinterpret_cast<uintptr_t>(p.c_extra[e]);
     }
     return (al & 15) == 0;
+}
+
+// The same epilogue when C is a plain aligned matrix that is not read back: the arithmetic is done IN the staging
+// tile (rolled loop, shared memory only) and the tile leaves as one TMA store — the staging layout is the 128-byte
+// swizzle the tensor map names, rows and columns past M and N are clipped by the hardware, and the warp does not
+// wait for the global writes, only (before it reuses the tile) for the engine to have read it.
+static __device__ __forceinline__ void store_piece_f32_tma(const KernelArgs &p, const CUtensorMap *tmc, float4 *stg,
+                                                           long long row0, int col0, int lane)
+{
+    if (p.alpha != 1.0f || p.colscale || p.bias || p.act != ACT_NONE) {
+        const int ch = lane & 7, colv = col0 + ch * 4;
+        float cs[4] = { 1.f, 1.f, 1.f, 1.f }, bs[4] = { 0.f, 0.f, 0.f, 0.f };
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            if (p.colscale && colv + e < p.N) cs[e] = __ldg(p.colscale + colv + e);
+            if (p.bias && colv + e < p.N) bs[e] = __ldg(p.bias + colv + e);
+        }
+#pragma unroll 2
+        for (int it = 0; it < 8; ++it) {
+            const int r = it * 4 + (lane >> 3), idx = r * 8 + (ch ^ (r & 7));
+            const float4 v = stg[idx];
+            stg[idx] = make_float4(epi_act(v.x * p.alpha * cs[0] + bs[0], p.act), epi_act(v.y * p.alpha * cs[1] + bs[1], p.act),
+                                   epi_act(v.z * p.alpha * cs[2] + bs[2], p.act), epi_act(v.w * p.alpha * cs[3] + bs[3], p.act));
+        }
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+        tma_store_2d(tmc, smem_u32(stg), col0, (int32_t)row0);
+        tma_store_commit();
+    }
 }
 
 // All MMAs of one pipeline stage, fully unrolled.  tcgen05.mma holds the issuing thread while

@@ -244,6 +244,38 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tmap, uint
         : "memory");
 }
 
+// 2-D tiled store shared memory -> global (bulk async-group completion).  The part of the box outside the tensor
+// is clipped by the hardware; crd0 * element size must be a multiple of 16 bytes and no coordinate negative.
+__device__ __forceinline__ void tma_store_2d(const void *tmap, uint32_t src, int32_t crd0, int32_t crd1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap), "r"(src),
+                 "r"(crd0), "r"(crd1)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_store_commit()
+{
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
+// all committed bulk stores of this thread have finished READING shared memory (the source may be reused)
+__device__ __forceinline__ void tma_store_wait_read()
+{
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
+// ... have completed altogether (required before the CTA exits)
+__device__ __forceinline__ void tma_store_wait_all()
+{
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+
+// generic-proxy writes to shared memory become visible to the async proxy (TMA, tcgen05)
+__device__ __forceinline__ void fence_proxy_async_smem()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 // Ask for a tile to be brought into L2 (no shared-memory destination, no completion to wait for).
 __device__ __forceinline__ void tma_prefetch_3d(const void *tmap, int32_t crd0, int32_t crd1, int32_t crd2)
 {
