@@ -396,14 +396,6 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
                 "value": 2.0 * 512 * 4096 * 4096 / (step_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": step_ms,
                 "kernel_ms": core_ms, "prepass_ms": pre_ms})
 
-    # 3-layer MLP 8192 -> 16384 -> 16384 -> 8192 at batch 16384, bias + GELU fused (BASELINE config 5c):
-    # rows of the batch sharded over the ranks (no collective), and, with more than one rank, output
-    # columns sharded with one all-gather per layer.  Fixed total batch: strong scaling for this line.
-    try:
-        out.extend(mlp_extras(torch, dist, world, eng, K))
-    except Exception as exc:
-        out.append({"workload": "3-layer MLP batch 16384", "error": repr(exc)})
-
     # W8A32 at bs=1: the case the reference's quantised path exists for (int8 weights streamed once);
     # rotating weight buffers of 256 MiB in total (> L2) so every call streams from HBM
     for nq in (4096, 16384):
@@ -505,6 +497,16 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
     step_ms, core_ms, _ = core_time(lambda: eng.sdpa_fwd(Q2, K2, V2, O2, None, 0.0884, True), 10, 3)
     out.append({"workload": "causal SDPA fwd BH=64 S=1024 dk=128 (fp32 FMA kernel)", "value": 4.0 * 64 * S * S * 128 / (step_ms * 1e-3) / 1e12,
                 "unit": "TFLOP/s (4*BH*S^2*dk convention; causal does half)", "ms_per_step": step_ms, "kernel_ms": core_ms})
+    del Q, Kt, V, O, L, Q2, K2, V2, O2
+
+    # LAST, because it runs for seconds at the power cap and leaves the clocks low for whatever follows:
+    # 3-layer MLP 8192 -> 16384 -> 16384 -> 8192 at batch 16384, bias + GELU fused (BASELINE config 5c):
+    # rows of the batch sharded over the ranks (no collective), and, with more than one rank, output
+    # columns sharded with one all-gather per layer.  Fixed total batch: strong scaling for this line.
+    try:
+        out.extend(mlp_extras(torch, dist, world, eng, K))
+    except Exception as exc:
+        out.append({"workload": "3-layer MLP batch 16384", "error": repr(exc)})
     return out
 
 
