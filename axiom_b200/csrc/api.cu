@@ -197,10 +197,17 @@ int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int
     mark(0);
     // A is [M,K] (k contiguous) unless trans_a, where it is stored [K,M];
     // B is [K,N] (k outermost) unless trans_b, where it is stored [N,K].
-    int e = run_split(sa, A, ta ? M : K, ta != 0, carve, opa, a_chunk_k, a_chunk_stride);
-    if (e) return cuda_fail("split A", e);
-    e = run_split(sb, B, tb ? K : N, tb == 0, carve, opb);
-    if (e) return cuda_fail("split B", e);
+    // both operands in one pre-pass launch
+    void *pa[3] = { nullptr, nullptr, nullptr }, *pb[3] = { nullptr, nullptr, nullptr };
+    opa.nplanes = opb.nplanes = split_num_planes(split_mode);
+    for (int i = 0; i < opa.nplanes; ++i) opa.plane[i] = pa[i] = carve.take(sa.plane_bytes);
+    for (int i = 0; i < opb.nplanes; ++i) opb.plane[i] = pb[i] = carve.take(sb.plane_bytes);
+    opa.rows = sa.rows; opa.pitch_elems = sa.pitch;
+    opb.rows = sb.rows; opb.pitch_elems = sb.pitch;
+    int e = split_planes_pair(split_mode, A, M, ta ? M : K, ta != 0, pa, sa.pitch, a_chunk_k, a_chunk_stride, B, N,
+                              tb ? K : N, tb == 0, pb, sb.pitch, K, g.sm_count, g.stream);
+    g.launches++;
+    if (e) return cuda_fail("split operands", e);
     TcEpilogue ep;
     ep.n_extra = 0;
     ep.alpha = alpha; ep.beta = beta; ep.bias = bias; ep.colscale = nullptr; ep.act = act;

@@ -80,15 +80,14 @@ struct PlanePtrs {
 
 // in [rows, k] (k contiguous, row pitch ld) -> planes [rows, pitch]; 4 elements / thread
 template <int MODE>
-__global__ void __launch_bounds__(256) split_rows_kernel(const float *__restrict__ in, int64_t rows,
-                                                         int64_t k, int64_t ld, PlanePtrs pl, int64_t pitch,
-                                                         int64_t chunk_k, int64_t chunk_stride)
+__device__ __forceinline__ void split_rows_body(const float *__restrict__ in, int64_t rows, int64_t k, int64_t ld,
+                                                const PlanePtrs &pl, int64_t pitch, int64_t chunk_k,
+                                                int64_t chunk_stride, int vblock, int vgrid)
 {
     const int64_t k4 = (k + 3) / 4;
     const int64_t total = rows * k4;
     const bool vec = (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-         i += (int64_t)gridDim.x * blockDim.x) {
+    for (int64_t i = (int64_t)vblock * blockDim.x + threadIdx.x; i < total; i += (int64_t)vgrid * blockDim.x) {
         const int64_t r = i / k4, c = (i - r * k4) * 4;
         // chunk_k > 0: the k range is cut into chunks stored as separate [rows, chunk_k] blocks chunk_stride
         // apart (the layout an all-gather of column slabs leaves behind); chunk_k % 4 == 0
@@ -132,14 +131,13 @@ __global__ void __launch_bounds__(256) split_rows_kernel(const float *__restrict
 // in [k, rows] (rows contiguous, pitch ld) -> planes [rows, pitch] (k contiguous):
 // 64(k) x 32(rows) tiles through shared memory.
 template <int MODE>
-__global__ void __launch_bounds__(256) split_transpose_kernel(const float *__restrict__ in, int64_t rows,
-                                                              int64_t k, int64_t ld, PlanePtrs pl,
-                                                              int64_t pitch)
+__device__ __forceinline__ void split_transpose_body(const float *__restrict__ in, int64_t rows, int64_t k, int64_t ld,
+                                                     const PlanePtrs &pl, int64_t pitch, float (*tile)[33], int vblock,
+                                                     int vgrid)
 {
-    __shared__ float tile[64][33];
     const int64_t tiles_r = (rows + 31) / 32, tiles_k = (k + 63) / 64;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
-    for (int64_t t = blockIdx.x; t < tiles_r * tiles_k; t += gridDim.x) {
+    for (int64_t t = vblock; t < tiles_r * tiles_k; t += vgrid) {
         const int64_t tr = t % tiles_r, tk = t / tiles_r;
         const int64_t r0 = tr * 32, k0 = tk * 64;
 #pragma unroll
@@ -162,6 +160,42 @@ __global__ void __launch_bounds__(256) split_transpose_kernel(const float *__res
         }
         __syncthreads();
     }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(256) split_rows_kernel(const float *__restrict__ in, int64_t rows, int64_t k, int64_t ld,
+                                                         PlanePtrs pl, int64_t pitch, int64_t chunk_k, int64_t chunk_stride)
+{
+    split_rows_body<MODE>(in, rows, k, ld, pl, pitch, chunk_k, chunk_stride, blockIdx.x, gridDim.x);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(256) split_transpose_kernel(const float *__restrict__ in, int64_t rows, int64_t k,
+                                                              int64_t ld, PlanePtrs pl, int64_t pitch)
+{
+    __shared__ float tile[64][33];
+    split_transpose_body<MODE>(in, rows, k, ld, pl, pitch, tile, blockIdx.x, gridDim.x);
+}
+
+// Both operands of one GEMM in ONE launch: blocks [0, ga) split operand A, the rest operand B; each operand is either
+// row-major in k (rows body) or has k outermost (transpose body).  A 1024^3 GEMM is launch-bound: two pre-pass launches
+// were a third of its step.
+struct SplitTask {
+    const float *in;
+    int64_t rows, k, ld, pitch, chunk_k, chunk_stride;
+    PlanePtrs pl;
+    int transposed, blocks;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(256) split_pair_kernel(const SplitTask a, const SplitTask b)
+{
+    __shared__ float tile[64][33];
+    const bool first = (int)blockIdx.x < a.blocks;
+    const SplitTask &t = first ? a : b;
+    const int vblock = first ? (int)blockIdx.x : (int)blockIdx.x - a.blocks;
+    if (t.transposed) split_transpose_body<MODE>(t.in, t.rows, t.k, t.ld, t.pl, t.pitch, tile, vblock, t.blocks);
+    else split_rows_body<MODE>(t.in, t.rows, t.k, t.ld, t.pl, t.pitch, t.chunk_k, t.chunk_stride, vblock, t.blocks);
 }
 
 // Implicit im2col: the B operand of a convolution-as-GEMM, written straight into K-major planes.  Row `pix` of
@@ -281,6 +315,39 @@ int split_planes(int mode, const float *in, int64_t rows, int64_t k, int64_t ld,
         case SPLIT_BF16X2: split_transpose_kernel<SPLIT_BF16X2><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch); break;
         default: split_transpose_kernel<SPLIT_BF16X3><<<g, 256, 0, st>>>(in, rows, k, ld, pl, pitch); break;
         }
+    }
+    return (int)cudaGetLastError();
+}
+
+static SplitTask make_task(const float *in, int64_t rows, int64_t k, int64_t ld, bool transposed, void *const planes[3],
+                           int64_t pitch, int64_t chunk_k, int64_t chunk_stride, int sm_count)
+{
+    SplitTask t;
+    t.in = in; t.rows = rows; t.k = k; t.ld = ld; t.pitch = pitch; t.chunk_k = chunk_k; t.chunk_stride = chunk_stride;
+    for (int i = 0; i < 3; ++i) t.pl.p[i] = planes[i];
+    t.transposed = transposed ? 1 : 0;
+    if (!transposed) {
+        t.blocks = grid_for(rows * ((k + 3) / 4), 256, sm_count);
+    } else {
+        const int64_t tiles = ((rows + 31) / 32) * ((k + 63) / 64), cap = (int64_t)sm_count * 8;
+        t.blocks = (int)(tiles < cap ? (tiles > 0 ? tiles : 1) : cap);
+    }
+    return t;
+}
+
+int split_planes_pair(int mode, const float *a_in, int64_t a_rows, int64_t a_ld, bool a_transposed, void *const a_planes[3],
+                      int64_t a_pitch, int64_t a_chunk_k, int64_t a_chunk_stride, const float *b_in, int64_t b_rows,
+                      int64_t b_ld, bool b_transposed, void *const b_planes[3], int64_t b_pitch, int64_t k, int sm_count,
+                      cudaStream_t st)
+{
+    const SplitTask ta = make_task(a_in, a_rows, k, a_ld, a_transposed, a_planes, a_pitch, a_chunk_k, a_chunk_stride, sm_count);
+    const SplitTask tb = make_task(b_in, b_rows, k, b_ld, b_transposed, b_planes, b_pitch, 0, 0, sm_count);
+    const unsigned g = (unsigned)(ta.blocks + tb.blocks);
+    switch (mode) {
+    case SPLIT_TF32X2: split_pair_kernel<SPLIT_TF32X2><<<g, 256, 0, st>>>(ta, tb); break;
+    case SPLIT_BF16X1: split_pair_kernel<SPLIT_BF16X1><<<g, 256, 0, st>>>(ta, tb); break;
+    case SPLIT_BF16X2: split_pair_kernel<SPLIT_BF16X2><<<g, 256, 0, st>>>(ta, tb); break;
+    default: split_pair_kernel<SPLIT_BF16X3><<<g, 256, 0, st>>>(ta, tb); break;
     }
     return (int)cudaGetLastError();
 }

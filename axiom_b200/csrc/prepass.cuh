@@ -16,6 +16,11 @@ static inline int split_elem_bytes(int mode) { return mode == SPLIT_TF32X2 ? 4 :
 int split_planes(int mode, const float *in, int64_t rows, int64_t k, int64_t ld, bool in_is_k_major_outer,
                  void *const planes[3], int64_t pitch, int sm_count, cudaStream_t st, int64_t chunk_k = 0,
                  int64_t chunk_stride = 0);
+// Both operands of a GEMM (same mode, same k) in one launch; arguments as for two split_planes calls.
+int split_planes_pair(int mode, const float *a_in, int64_t a_rows, int64_t a_ld, bool a_transposed, void *const a_planes[3],
+                      int64_t a_pitch, int64_t a_chunk_k, int64_t a_chunk_stride, const float *b_in, int64_t b_rows,
+                      int64_t b_ld, bool b_transposed, void *const b_planes[3], int64_t b_pitch, int64_t k, int sm_count,
+                      cudaStream_t st);
 // planes [out_h*out_w, pitch] of the im2col matrix of one [C_in, H, W] sample (k = (c, ky, kx), zero padding)
 int split_im2col(int mode, const float *in, int64_t C_in, int64_t H, int64_t W, int kh, int kw, int sh, int sw, int ph,
                  int pw, int64_t out_h, int64_t out_w, void *const planes[3], int64_t pitch, int sm_count, cudaStream_t st);
