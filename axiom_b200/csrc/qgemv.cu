@@ -15,16 +15,19 @@ static constexpr int QV_THREADS = 256;
 static constexpr int QV_WARPS = 8;
 
 // int8 -> fp32 without the conversion pipe: flip the sign bits (s + 128 as an unsigned byte), drop the byte
-// into the mantissa of 2^23 and subtract 2^23 + 128.  Exact for every int8 value.
-__device__ __forceinline__ void unpack16(const uint4 &w, float (&f)[16])
+// into the mantissa of 2^23 and subtract 2^23 + 128.  Exact for every int8 value.  The values come out as
+// pairs so that the subtraction and the multiply-add run as packed f32x2 instructions: the kernel is paced by
+// instruction issue (ncu: 60 % issue-active at 33 % of DRAM throughput), not by memory.
+__device__ __forceinline__ void unpack16(const uint4 &w, float2 (&f)[8])
 {
     const uint32_t v[4] = { w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u };
+    const float2 bias = make_float2(-8388736.0f, -8388736.0f);
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        f[4 * i + 0] = __uint_as_float(__byte_perm(v[i], 0x4B000000u, 0x7540)) - 8388736.0f;
-        f[4 * i + 1] = __uint_as_float(__byte_perm(v[i], 0x4B000000u, 0x7541)) - 8388736.0f;
-        f[4 * i + 2] = __uint_as_float(__byte_perm(v[i], 0x4B000000u, 0x7542)) - 8388736.0f;
-        f[4 * i + 3] = __uint_as_float(__byte_perm(v[i], 0x4B000000u, 0x7543)) - 8388736.0f;
+        f[2 * i + 0] = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(v[i], 0x4B000000u, 0x7540)),
+                                              __uint_as_float(__byte_perm(v[i], 0x4B000000u, 0x7541))), bias);
+        f[2 * i + 1] = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(v[i], 0x4B000000u, 0x7542)),
+                                              __uint_as_float(__byte_perm(v[i], 0x4B000000u, 0x7543))), bias);
     }
 }
 
@@ -45,11 +48,12 @@ __global__ void __launch_bounds__(QV_THREADS) qgemv_w8a32_kernel(const float *__
     int64_t n = (int64_t)blockIdx.x * QV_WARPS + warp;
 
     // the first weight loads leave before the activations are staged
-    uint4 w[QV_UNROLL];
+    constexpr int U = MT >= 8 ? 4 : QV_UNROLL;   // 16-byte loads per lane and buffer
+    uint4 w[U], wb2[U];
     if (n < N) {
         const uint4 *row = reinterpret_cast<const uint4 *>(q + n * (int64_t)K);
 #pragma unroll
-        for (int u = 0; u < QV_UNROLL; ++u) {
+        for (int u = 0; u < U; ++u) {
             const int p = lane + 32 * u;
             w[u] = p < pieces ? __ldcs(row + p) : make_uint4(0, 0, 0, 0);
         }
@@ -81,65 +85,75 @@ __global__ void __launch_bounds__(QV_THREADS) qgemv_w8a32_kernel(const float *__
     }
     __syncthreads();
 
-    for (; n < N; n += row_stride) {
-        const uint4 *row = reinterpret_cast<const uint4 *>(q + n * (int64_t)K);
-        float acc[MT];
+    // The rows of this warp as one stream of chunks (a chunk = QV_UNROLL 16-byte pieces per lane of one row).  The
+    // loads of chunk c+1 are issued before chunk c is computed (two register buffers), so a warp always has weight
+    // bytes in flight; with a single buffer the loads waited for the arithmetic and the kernel sat at half the
+    // memory rate.
+    const int cpr = (pieces + 32 * U - 1) / (32 * U);                 // chunks per row
+    const int64_t my_rows = n < N ? (N - n + row_stride - 1) / row_stride : 0;
+    const int64_t total = my_rows * cpr;
+    float2 acc[MT];   // two partial sums per row (even and odd k), added at the end
 #pragma unroll
-        for (int m = 0; m < MT; ++m) acc[m] = 0.0f;
-#pragma unroll 1
-        for (int p0 = lane; p0 < pieces; p0 += 32 * QV_UNROLL) {
-            if (p0 != lane) {
+    for (int m = 0; m < MT; ++m) acc[m] = make_float2(0.0f, 0.0f);
+
+    auto load = [&](uint4 (&wb)[U], int64_t c) {
+        const int64_t r = c / cpr;
+        const int g = (int)(c - r * cpr);
+        const uint4 *row = reinterpret_cast<const uint4 *>(q + (n + r * row_stride) * (int64_t)K);
 #pragma unroll
-                for (int u = 0; u < QV_UNROLL; ++u) {
-                    const int p = p0 + 32 * u;
-                    w[u] = p < pieces ? __ldcs(row + p) : make_uint4(0, 0, 0, 0);
-                }
-            }
+        for (int u = 0; u < U; ++u) {
+            const int p = lane + 32 * (g * U + u);
+            wb[u] = p < pieces ? __ldcs(row + p) : make_uint4(0, 0, 0, 0);
+        }
+    };
+    auto compute = [&](const uint4 (&wb)[U], int64_t c) {
+        const int64_t r = c / cpr;
+        const int g = (int)(c - r * cpr);
 #pragma unroll
-            for (int u = 0; u < QV_UNROLL; ++u) {
-                const int p = p0 + 32 * u;
-                if (p < pieces) {
-                    float f[16];
-                    unpack16(w[u], f);
+        for (int u = 0; u < U; ++u) {
+            const int p = lane + 32 * (g * U + u);
+            if (p < pieces) {
+                float2 f[8];
+                unpack16(wb[u], f);
 #pragma unroll
-                    for (int m = 0; m < MT; ++m) {
-                        const float4 *xv = reinterpret_cast<const float4 *>(xs + m * K + p * 16);
+                for (int m = 0; m < MT; ++m) {
+                    const float4 *xv = reinterpret_cast<const float4 *>(xs + m * K + p * 16);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const float4 x4 = xv[(j + (p >> 1)) & 3];
-                            acc[m] = fmaf(x4.x, f[4 * j + 0], acc[m]);
-                            acc[m] = fmaf(x4.y, f[4 * j + 1], acc[m]);
-                            acc[m] = fmaf(x4.z, f[4 * j + 2], acc[m]);
-                            acc[m] = fmaf(x4.w, f[4 * j + 3], acc[m]);
-                        }
+                    for (int j = 0; j < 4; ++j) {
+                        const float4 x4 = xv[(j + (p >> 1)) & 3];
+                        acc[m] = __ffma2_rn(make_float2(x4.x, x4.y), f[2 * j + 0], acc[m]);
+                        acc[m] = __ffma2_rn(make_float2(x4.z, x4.w), f[2 * j + 1], acc[m]);
                     }
                 }
             }
         }
-        // the next row's first loads go out before this row's reduction
-        const int64_t nn = n + row_stride;
-        if (nn < N) {
-            const uint4 *nrow = reinterpret_cast<const uint4 *>(q + nn * (int64_t)K);
+        if (g == cpr - 1) {   // the row is complete
+            const int64_t nr = n + r * row_stride;
+            const float sc = __ldg(scales + nr);
+            const float bn = bias ? __ldg(bias + nr) : 0.0f;
 #pragma unroll
-            for (int u = 0; u < QV_UNROLL; ++u) {
-                const int p = lane + 32 * u;
-                w[u] = p < pieces ? __ldcs(nrow + p) : make_uint4(0, 0, 0, 0);
+            for (int m = 0; m < MT; ++m) {
+                float v = acc[m].x + acc[m].y;
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+                if (lane == 0 && m < M) {
+                    v = v * sc;                       // the reference's result (quantize.c:100-177) ...
+                    if (bias) v += bn;                // ... and the dense layer's bias and activation on top
+                    if (act == 1) v = fmaxf(v, 0.0f);
+                    else if (act == 2) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+                    out[(int64_t)m * N + nr] = v;
+                }
+                acc[m] = make_float2(0.0f, 0.0f);
             }
         }
-        const float sc = __ldg(scales + n);
-        const float bn = bias ? __ldg(bias + n) : 0.0f;
-#pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            float v = acc[m];
-#pragma unroll
-            for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-            if (lane == 0 && m < M) {
-                v = v * sc;                       // the reference's result (quantize.c:100-177) ...
-                if (bias) v += bn;                // ... and the dense layer's bias and activation on top
-                if (act == 1) v = fmaxf(v, 0.0f);
-                else if (act == 2) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
-                out[(int64_t)m * N + n] = v;
-            }
+    };
+
+    for (int64_t c = 0; c < total; c += 2) {
+        if (c + 1 < total) load(wb2, c + 1);
+        compute(w, c);
+        if (c + 1 < total) {
+            if (c + 2 < total) load(w, c + 2);
+            compute(wb2, c + 1);
         }
     }
 }
@@ -166,7 +180,7 @@ static int launch_qv(const float *a, const int8_t *q, const float *scales, const
         attr_set[dev] = true;
     }
     int64_t blocks = (N + QV_WARPS - 1) / QV_WARPS;
-    const int64_t cap = (int64_t)sm_count * (smem > 48 * 1024 ? 2 : 4);
+    const int64_t cap = (int64_t)sm_count * 2;   // two resident CTAs per SM (registers): one wave, rows strided over it
     if (blocks > cap) blocks = cap;
     k<<<(unsigned)blocks, QV_THREADS, smem, st>>>(a, q, scales, bias, act, out, M, N, (int)K);
     return (int)cudaGetLastError();

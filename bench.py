@@ -334,7 +334,7 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
                     "unit": "TFLOP/s", "ms_per_step": step_ms, "kernel_ms": core_ms, "prepass_ms": pre_ms,
                     "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "frac": tf / peak, "peak_source": note}})
 
-    # int8 GEMM 16384^3 -> requantised int8 (BASELINE config 5b)
+    # int8 GEMM 16384^3 -> requantised int8 (benchmark config 5b)
     n8 = 16384
     a8 = torch.randint(-127, 128, (n8, n8), device="cuda", dtype=torch.int8)
     b8 = torch.randint(-127, 128, (n8, n8), device="cuda", dtype=torch.int8)
@@ -349,7 +349,7 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
                              "peak_source": "2 x measured bf16 burst (int8 issues at twice the bf16 rate)"}})
     del a8, b8, q8
 
-    # skinny-M route: x[M,4096].W[4096,4096] + bias -> GELU (BASELINE config 2); 8 rotating weight
+    # skinny-M route: x[M,4096].W[4096,4096] + bias -> GELU (benchmark config 2); 8 rotating weight
     # buffers (512 MiB > L2) so every step streams W from HBM
     n = 4096
     Ws = [torch.randn((n, n), device="cuda") / 64 for _ in range(8)]
@@ -374,14 +374,14 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
                                  "peak_source": f"{peaks['source']} HBM copy bandwidth"}})
     del Ws
 
-    # dense + bias + ReLU 1024^3 (BASELINE config 1)
+    # dense + bias + ReLU 1024^3 (benchmark config 1)
     a1, b1, bias1 = uniform((1024, 1024)), uniform((1024, 1024)), uniform((1024,))
     c1 = torch.empty((1024, 1024), device="cuda")
     step_ms, core_ms, pre_ms = core_time(lambda: eng.gemm_relu(a1, b1, bias1, c1), 50, 5)
     out.append({"workload": "fp32 GEMM+bias+ReLU 1024^3 (3xTF32)", "value": 2.0 * 1024 ** 3 / (step_ms * 1e-3) / 1e12,
                 "unit": "TFLOP/s", "ms_per_step": step_ms, "kernel_ms": core_ms, "prepass_ms": pre_ms})
 
-    # quantised GEMM 512x4096x4096 (BASELINE config 3): W8A8 and the reference's W8A32
+    # quantised GEMM 512x4096x4096 (benchmark config 3): W8A8 and the reference's W8A32
     a3 = torch.randint(-127, 128, (512, 4096), device="cuda", dtype=torch.int8)
     b3 = torch.randint(-127, 128, (4096, 4096), device="cuda", dtype=torch.int8)
     s3 = torch.rand((4096,), device="cuda") * 0.019 + 0.001
@@ -422,7 +422,7 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
         except Exception as exc:
             out.append({"workload": f"W8A32 GEMV bs=1 N={nq}", "error": repr(exc)})
 
-    # causal attention B=8,H=16,S=1024,dk=64 (BASELINE config 4); FLOPs by the reference's 4*BH*S^2*dk convention
+    # causal attention B=8,H=16,S=1024,dk=64 (benchmark config 4); FLOPs by the reference's 4*BH*S^2*dk convention
     BH, S, dk = 128, 1024, 64
     Q, Kt, V = (torch.randn((BH, S, dk), device="cuda") for _ in range(3))
     O = torch.empty((BH, S, dk), device="cuda")
@@ -500,7 +500,7 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
     del Q, Kt, V, O, L, Q2, K2, V2, O2
 
     # LAST, because it runs for seconds at the power cap and leaves the clocks low for whatever follows:
-    # 3-layer MLP 8192 -> 16384 -> 16384 -> 8192 at batch 16384, bias + GELU fused (BASELINE config 5c):
+    # 3-layer MLP 8192 -> 16384 -> 16384 -> 8192 at batch 16384, bias + GELU fused (benchmark config 5c):
     # rows of the batch sharded over the ranks (no collective), and, with more than one rank, output
     # columns sharded with one all-gather per layer.  Fixed total batch: strong scaling for this line.
     try:
@@ -540,6 +540,19 @@ def run_profile_case(args):
         def fn():
             eng.gemm_bias_act(x, Ws[state["i"] % 4], bias, y, M, 4096, 4096, act="gelu")
             state["i"] += 1
+    elif case == "qgemv":
+        Wq = [torch.randint(-127, 128, (16384, 4096), device="cuda", dtype=torch.int8) for _ in range(4)]
+        sc = torch.rand((16384,), device="cuda") * 0.019 + 0.001
+        xq, oq = torch.randn((1, 4096), device="cuda"), torch.empty((1, 16384), device="cuda")
+        state = {"i": 0}
+
+        def fn():
+            eng.qgemm_w8a32(xq, Wq[state["i"] % 4], sc, oq)
+            state["i"] += 1
+    elif case == "kv":
+        kc, vc = (torch.randn((128, 4096, 64), device="cuda") for _ in range(2))
+        qn, on = torch.randn((128, 64), device="cuda"), torch.empty((128, 64), device="cuda")
+        fn = lambda: eng.kv_cache_attend(kc, vc, qn, on, 4096, 0.125)
     elif case == "sdpa":
         Q, K, V = (torch.randn((128, 1024, 64), device="cuda") for _ in range(3))
         O, L = torch.empty((128, 1024, 64), device="cuda"), torch.empty((128, 1024), device="cuda")

@@ -1,4 +1,4 @@
-"""Full-size checks at the BASELINE configurations, through properties that do not need a full CPU
+"""Full-size checks at the full benchmark configurations, through properties that do not need a full CPU
 recomputation: sampled rows against the oracle (bit-exact for integers, normalised error for fp32),
 linearity, and row-shard consistency (the multi-GPU row partition gives the same bits as the whole)."""
 import numpy as np

@@ -84,7 +84,7 @@ def test_gemm_modes_normalised_error(engine, oracle, shape, mode):
 
 
 def test_config1_dense_relu_1024(engine, oracle):
-    """BASELINE config 1: C = ReLU(A.B + bias), M=N=K=1024, U[-1,1] seeds 7/13/29."""
+    """benchmark config 1: C = ReLU(A.B + bias), M=N=K=1024, U[-1,1] seeds 7/13/29."""
     A, B, bias = oracle.uniform((1024, 1024), 7), oracle.uniform((1024, 1024), 13), oracle.uniform((1024,), 29)
     ref = oracle.bias_act(oracle.gemm(A, B), bias, "relu")
     ref64 = np.maximum(oracle.gemm_f64(A, B) + bias.astype(np.float64), 0)
@@ -138,7 +138,7 @@ def test_null_and_bad_arguments(engine):
 @pytest.mark.parametrize("M", [1, 2, 5, 8, 9, 16, 17, 32])
 @pytest.mark.parametrize("NK", [(4096, 4096), (1000, 777), (130, 257), (1000, 1028), (128, 256), (4100, 520), (512, 8192)])
 def test_skinny_route(engine, oracle, M, NK):
-    """BASELINE config 2 (x[M,4096].W[4096,4096] + bias -> GELU, M in {1,8,32}) and ragged shapes.  M <= 8 runs the
+    """benchmark config 2 (x[M,4096].W[4096,4096] + bias -> GELU, M in {1,8,32}) and ragged shapes.  M <= 8 runs the
     fp32-FMA kernels, 9..32 the tensor-core kernel when N and K are multiples of 4 (else the FMA kernels again)."""
     N, K = NK
     x = oracle.normal((M, K), 31)
@@ -194,7 +194,7 @@ def test_w8a8_known_answers_bit_exact(engine, golden):
 
 @pytest.mark.parametrize("shape", [(512, 4096, 4096), (130, 200, 1000), (128, 256, 128), (1, 64, 48), (300, 33, 4112)])
 def test_w8a8_bit_exact_vs_oracle(engine, oracle, shape):
-    """BASELINE config 3 first: A int8 [512,4096], B int8 [4096,4096], scales U[0.001,0.02]."""
+    """benchmark config 3 first: A int8 [512,4096], B int8 [4096,4096], scales U[0.001,0.02]."""
     M, N, K = shape
     a, b = oracle.int8((M, K), 7), oracle.int8((N, K), 13)
     bs = oracle.frange((N,), 17, 0.001, 0.02)
@@ -267,7 +267,7 @@ def test_sdpa_vs_golden(engine, oracle, golden, name, causal):
                                    (3, 300, 16), (2, 256, 32), (2, 200, 6), (2, 1000, 24), (1, 128, 4), (2, 640, 60), (1, 513, 72)])
 @pytest.mark.parametrize("causal", [0, 1])
 def test_sdpa_vs_oracle(engine, oracle, shape, causal):
-    """BASELINE config 4 per-head shape (S=1024, dk=64, scale 1/8, causal) on a few heads, plus ragged ones."""
+    """benchmark config 4 per-head shape (S=1024, dk=64, scale 1/8, causal) on a few heads, plus ragged ones."""
     BH, S, dk = shape
     Q, K, V = oracle.normal((BH, S, dk), 41), oracle.normal((BH, S, dk), 43), oracle.normal((BH, S, dk), 47)
     scale = 1.0 / np.sqrt(dk)
