@@ -196,17 +196,23 @@ template <int KIND, int SWB, int NPROD, bool PAIR, int A_BYTES, int B_BYTES>
 __device__ __forceinline__ void issue_stage_mmas(uint32_t d_tmem, uint32_t sa, uint32_t sb, uint32_t prod_a,
                                                  uint32_t prod_b, uint64_t desc_hi, uint32_t idesc, bool first)
 {
+    // Order: per 64 bytes of K (two MMA steps) all products, then the next 64 bytes.  A 128-byte stage therefore
+    // accumulates exactly like two 64-byte stages, so kernels with different stage widths (the tile heuristics pick
+    // them by shape) give bit-identical results — what makes a row-chunked GEMM equal to the whole one.
     constexpr int KSTEPS = SWB / 32;
 #pragma unroll
-    for (int pr = 0; pr < NPROD; ++pr) {
-        const uint32_t ia = (prod_a >> (4 * pr)) & 15u, ib = (prod_b >> (4 * pr)) & 15u;
-        const uint64_t da = desc_hi | (uint64_t)((sa + ia * A_BYTES) >> 4);
-        const uint64_t db = desc_hi | (uint64_t)((sb + ib * B_BYTES) >> 4);
+    for (int g = 0; g < KSTEPS / 2; ++g) {
 #pragma unroll
-        for (int ks = 0; ks < KSTEPS; ++ks) {
-            const uint32_t accumulate = (pr == 0 && ks == 0) ? (first ? 0u : 1u) : 1u;
-            if constexpr (PAIR) tc_mma_pair<KIND>(d_tmem, da + 2u * ks, db + 2u * ks, idesc, accumulate);
-            else tc_mma<KIND>(d_tmem, da + 2u * ks, db + 2u * ks, idesc, accumulate);
+        for (int pr = 0; pr < NPROD; ++pr) {
+            const uint32_t ia = (prod_a >> (4 * pr)) & 15u, ib = (prod_b >> (4 * pr)) & 15u;
+            const uint64_t da = desc_hi | (uint64_t)((sa + ia * A_BYTES) >> 4);
+            const uint64_t db = desc_hi | (uint64_t)((sb + ib * B_BYTES) >> 4);
+#pragma unroll
+            for (int ks = 2 * g; ks < 2 * g + 2; ++ks) {
+                const uint32_t accumulate = (g == 0 && pr == 0 && ks == 0) ? (first ? 0u : 1u) : 1u;
+                if constexpr (PAIR) tc_mma_pair<KIND>(d_tmem, da + 2u * ks, db + 2u * ks, idesc, accumulate);
+                else tc_mma<KIND>(d_tmem, da + 2u * ks, db + 2u * ks, idesc, accumulate);
+            }
         }
     }
 }
