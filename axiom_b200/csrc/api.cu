@@ -10,6 +10,7 @@
 #include "prepass.cuh"
 #include "ptx.cuh"
 #include "qgemv.cuh"
+#include "qskinny_tc.cuh"
 #include "kv_attend.cuh"
 #include "sdpa.cuh"
 #include "skinny.cuh"
@@ -753,6 +754,19 @@ extern "C" int axb_qdense_w8a32(const float *a, const int8_t *q, const float *sc
     int st = ensure_ready();
     if (st) return st;
     if (M == 0) return AXB_OK;
+    // AX_B200_QSKINNY_TC_MIN: smallest M that takes the integer tensor-core kernel (65 turns it off)
+    static const int qtc_min = [] { const char *e = getenv("AX_B200_QSKINNY_TC_MIN"); return e ? atoi(e) : 2; }();
+    if (M >= qtc_min && N * K >= (1 << 20) && qskinny_tc_applicable(M, N, K, a, q)) {
+        // skinny activations as four int8 digit planes, weights streamed once into kind::i8 MMAs
+        st = ensure_ws(qskinny_tc_workspace_bytes(M, K));
+        if (st) return st;
+        mark(0);
+        mark(1);
+        int e = launch_qskinny_tc(a, q, scales, bias, act, out, M, N, K, g.ws, g.err_word, g.sm_count, g.stream);
+        mark(2);
+        g.launches += 2;
+        return e ? cuda_fail("w8a32 skinny", e) : AXB_OK;
+    }
     if (qgemv_w8a32_applicable(M, N, K, q) && (reinterpret_cast<uintptr_t>(a) & 15) == 0) {
         // skinny activations: stream the int8 rows once, fp32 FMA (the reference's own arithmetic)
         mark(0);

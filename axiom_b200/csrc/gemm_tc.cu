@@ -425,6 +425,32 @@ int encode_f32_batched_tmap(void *tmap_out, const void *ptr, int64_t batch, int6
     return 0;
 }
 
+// int8 planes [batch][rows][pitch] with `cols` valid bytes per row, 128-byte swizzle, box = 128 x box_rows x box_batch.
+// Rows past `rows` and bytes past `cols` read as zero.
+int encode_i8_batched_tmap(void *tmap_out, const void *ptr, int64_t batch, int64_t rows, int64_t cols,
+                           int64_t pitch_bytes, int64_t batch_stride_bytes, int box_rows, int box_batch)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled entry point not found");
+        return (int)cudaErrorSymbolNotFound;
+    }
+    cuuint64_t dims[3] = { (cuuint64_t)cols, (cuuint64_t)rows, (cuuint64_t)batch };
+    cuuint64_t strides[2] = { (cuuint64_t)pitch_bytes, (cuuint64_t)batch_stride_bytes };
+    cuuint32_t box[3] = { 128, (cuuint32_t)box_rows, (cuuint32_t)box_batch };
+    cuuint32_t estr[3] = { 1, 1, 1 };
+    CUresult r = fn(reinterpret_cast<CUtensorMap *>(tmap_out), CU_TENSOR_MAP_DATA_TYPE_UINT8, 3,
+                    const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_err, sizeof g_err,
+                 "cuTensorMapEncodeTiled (int8 planes) failed (%d): ptr=%p batch=%lld rows=%lld cols=%lld pitch=%lld",
+                 (int)r, ptr, (long long)batch, (long long)rows, (long long)cols, (long long)pitch_bytes);
+        return (int)cudaErrorInvalidValue;
+    }
+    return 0;
+}
+
 // fp32 matrix [rows, cols] with row pitch pitch_elems as the destination of 32 x 32 TMA stores, 128-byte swizzle
 static int encode_f32_store_tmap(CUtensorMap *out, float *ptr, int64_t rows, int64_t cols, int64_t pitch_elems)
 {

@@ -68,5 +68,8 @@ int encode_f32_matrix_tmap(void *tmap_out, const float *ptr, int64_t rows, int64
 // the swizzle that moves 32-byte chunks (for MN-major tf32 MMA operands).
 int encode_f32_batched_tmap(void *tmap_out, const void *ptr, int64_t batch, int64_t rows, int64_t cols,
                             int64_t pitch_elems, int box_rows, bool atom32);
+// int8 planes [batch][rows][pitch_bytes], 128-byte swizzle, box = 128 bytes x box_rows x box_batch; out-of-range reads are zero
+int encode_i8_batched_tmap(void *tmap_out, const void *ptr, int64_t batch, int64_t rows, int64_t cols,
+                           int64_t pitch_bytes, int64_t batch_stride_bytes, int box_rows, int box_batch);
 
 }  // namespace axb

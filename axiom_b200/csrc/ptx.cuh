@@ -197,6 +197,15 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
         : "memory");
 }
 
+// The same for 8 consecutive columns.
+__device__ __forceinline__ void tmem_ld_32x32_x8(uint32_t taddr, uint32_t (&r)[8])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld_wait()
 {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
@@ -352,6 +361,19 @@ __device__ __forceinline__ float tf32_rna(float x)
 // The leader (cluster rank 0) issues the MMA; each CTA stages its own half of
 // both operands and owns the 128 accumulator rows in its own TMEM.
 namespace axb {
+
+// Programmatic dependent launch: a kernel launched with the programmatic-serialisation attribute may start while
+// the kernel before it on the stream still runs; grid_dep_wait() blocks until that kernel has finished and its
+// writes are visible, grid_dep_launch() (called by the earlier kernel) lets the dependent start early.
+__device__ __forceinline__ void grid_dep_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void grid_dep_launch()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 
 __device__ __forceinline__ uint32_t cluster_cta_rank()
 {

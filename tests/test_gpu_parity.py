@@ -488,11 +488,40 @@ def test_conv_gemm_vs_oracle(engine, oracle, geom):
     assert engine.device_error() == 0
 
 
-@pytest.mark.parametrize("shape", [(1, 4096, 4096), (8, 1000, 2048), (4, 16, 32), (32, 128, 512), (300, 512, 1024)])
+@pytest.mark.parametrize("shape", [(2, 1024, 1024), (8, 4096, 4096), (9, 1000, 2048), (16, 2048, 1040), (17, 8200, 1168),
+                                   (32, 16384, 512), (33, 1024, 1024), (64, 4096, 4096), (5, 128, 8192)])
+def test_w8a32_skinny_tensor_core_kernel(engine, oracle, shape):
+    """2 <= M <= 64 with at least 2^20 weights: activations as four int8 digit planes, kind::i8 MMAs.  Ragged N and K
+    (zero-filled tiles), one and several K-slices per tile, an outlier 1000x the other activations in one row, and a
+    row with an infinity (the reference's fp32 sum is NaN or infinite there; here the row is NaN)."""
+    M, N, K = shape
+    a, w = oracle.uniform((M, K), 7), oracle.uniform((N, K), 13)
+    a[0, 3] = 1000.0
+    q, s = oracle.quantize_rows(w)
+    out = torch.full((M, N), float("nan"), device="cuda")
+    engine.qgemm_w8a32(dev(a), torch.from_numpy(q).cuda(), dev(s), out)
+    got = host(out)
+    assert engine.device_error() == 0
+    assert nerr(got, oracle.qgemm_w8a32_f64(a, q, s)) <= 1e-6      # fixed point at 2^-30 of the row maximum
+    ref = oracle.qgemm_w8a32(a, q, s)
+    diff = np.abs(got - ref)
+    assert not np.any((diff > 1e-2) & (diff / (np.abs(ref) + 1e-5) > 1e-3))   # tests/test_quantize.c:109-113
+    again = torch.empty((M, N), device="cuda")
+    engine.qgemm_w8a32(dev(a), torch.from_numpy(q).cuda(), dev(s), again)
+    np.testing.assert_array_equal(host(again), got)
+    a[M - 1, 5] = np.inf
+    engine.qgemm_w8a32(dev(a), torch.from_numpy(q).cuda(), dev(s), out)
+    got2 = host(out)
+    assert np.all(np.isnan(got2[M - 1]))
+    if M > 1:
+        np.testing.assert_array_equal(got2[:M - 1], got[:M - 1])
+
+
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (8, 1000, 2048), (4, 16, 32), (32, 128, 512), (300, 512, 1024), (24, 2048, 1024)])
 @pytest.mark.parametrize("act", ["none", "relu", "gelu"])
 def test_qdense_w8a32(engine, oracle, shape, act):
     """Quantised dense layer = the reference's ax_qgemm_w8a32 plus the dense layer's bias and activation in one launch
-    (GEMV kernel for M <= 8, tensor-core kernel above)."""
+    (GEMV kernel for M = 1 and small layers, integer tensor-core kernel for 2 <= M <= 64, bf16 GEMM above)."""
     M, N, K = shape
     a, w = oracle.uniform((M, K), 7), oracle.uniform((N, K), 13)
     bias = oracle.uniform((N,), 29)
