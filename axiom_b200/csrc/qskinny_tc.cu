@@ -15,9 +15,10 @@
 // range of the CTA; the digits are recombined in 64-bit integers, so the result does not depend on how K is cut
 // into slices or in which order the slices are added.
 //
-// One CTA = 128 weight rows x one K-slice; the K-slices of a tile form a thread-block cluster and are added
-// through distributed shared memory.  Warp 0 is the TMA producer (a ring of 16 KB weight tiles plus the digit
-// tiles, ~190 KB in flight per SM), warp 1 issues the MMAs, warps 2-5 read the accumulator and run the epilogue.
+// One CTA = 128 weight rows x one K-slice; the K-slices of a tile form a thread-block cluster: every slice stores
+// its integer partial sums of row m into the shared memory of slice m mod nslices, one cluster barrier, and each
+// slice finishes the rows it owns.  Warp 0 is the TMA producer (a ring of 16 KB weight tiles plus the digit
+// tiles, ~190 KB in flight per SM), warp 1 issues the MMAs, warps 2-17 read the accumulator and run the epilogue.
 #include "qskinny_tc.cuh"
 
 #include "gemm_tc.cuh"
@@ -28,7 +29,7 @@
 
 namespace axb {
 
-static constexpr int QT_THREADS = 192;
+static constexpr int QT_THREADS = 576;
 static constexpr int QT_BN = 128;                    // weight rows per CTA
 static constexpr int QT_KB = 128;                    // k per stage: one 128-byte swizzled row
 static constexpr int QT_W_BYTES = QT_BN * QT_KB;     // 16 KB
@@ -48,37 +49,82 @@ struct QtArgs {
 
 enum { QERR_PRODUCER = 31, QERR_MMA = 32, QERR_DRAIN = 33 };
 
+#ifdef AXB_QTC_PROF
+// wall-clock stamps (ns) of CTA (0,0) of both kernels, for a profiling build only
+__device__ unsigned long long g_qtc_prof[16];
+#define QP_STAMP(i) { if (blockIdx.x == 0 && blockIdx.y == 0) g_qtc_prof[i] = global_timer_ns(); }
+extern "C" __attribute__((visibility("default"))) int axb_debug_qtc_prof(unsigned long long *out)
+{
+    return (int)cudaMemcpyFromSymbol(out, g_qtc_prof, sizeof(unsigned long long) * 16);
+}
+#else
+#define QP_STAMP(i) {}
+#endif
+
 __host__ __device__ constexpr int qt_stages(int mp)
 {
-    return mp <= 8 ? 10 : mp <= 16 ? 8 : mp <= 32 ? 6 : 4;   // (16 KB + 4*mp*128) * stages <= 200 KB
+    // (16 KB + 4*mp*128) * stages + (mp + 8) KB for the partial sums of the other K-slices <= 224 KB
+    return mp <= 8 ? 10 : mp <= 16 ? 8 : mp <= 32 ? 5 : 3;
 }
 
 // ------------------------------------------------------------------------------------------------ pre-pass
-// One CTA per activation row: largest magnitude, then the four digit planes digits[j][m][k] and 2^-s.
-__global__ void __launch_bounds__(256) qx_digits_kernel(const float *__restrict__ a, int K, int MP,
-                                                        int8_t *__restrict__ digits, float *__restrict__ inv_s)
+// One CTA per activation row: largest magnitude, then the four digit planes digits[j][m][k] and 2^-s.  The row
+// stays in registers between the two steps (up to 16384 elements; longer rows are read again), so the pre-pass
+// costs one trip to memory, a block reduction and the stores.
+static constexpr int QX_THREADS = 1024, QX_CACHE = 4;
+
+__device__ __forceinline__ void qx_emit(uint32_t *dst, size_t plane4, int i, const float4 &v, float s)
 {
-    __shared__ float wmax[8];
+    const float x[4] = { v.x, v.y, v.z, v.w };
+    uint32_t pk[4] = { 0u, 0u, 0u, 0u };
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        int t = __float2int_rn(x[e] * s);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int d = (int)(int8_t)(t & 0xFF);
+            t = (t - d) >> 8;
+            pk[j] |= (uint32_t)(d & 0xFF) << (8 * e);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[j * plane4 + i] = pk[j];
+}
+
+__device__ __forceinline__ float qx_absmax(const float4 &v, bool &bad)
+{
+    bad |= !(v.x - v.x == 0.0f) | !(v.y - v.y == 0.0f) | !(v.z - v.z == 0.0f) | !(v.w - v.w == 0.0f);
+    return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+}
+
+__global__ void __launch_bounds__(QX_THREADS) qx_digits_kernel(const float *__restrict__ a, int K, int MP,
+                                                               int8_t *__restrict__ digits, float *__restrict__ inv_s)
+{
+    __shared__ float wmax[32];
     const int m = blockIdx.x, tid = threadIdx.x;
+    if (tid == 0) QP_STAMP(0)
     grid_dep_launch();   // the tensor-core kernel may start streaming weights now; it waits before it reads the digits
     const float4 *row = reinterpret_cast<const float4 *>(a + (int64_t)m * K);
     const int k4n = K >> 2;
+    float4 v[QX_CACHE];
     float mx = 0.0f;
     bool bad = false;
-    for (int i = tid; i < k4n; i += 256) {
-        const float4 v = __ldg(row + i);
-        const float t = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-        bad |= !(v.x - v.x == 0.0f) | !(v.y - v.y == 0.0f) | !(v.z - v.z == 0.0f) | !(v.w - v.w == 0.0f);
-        mx = fmaxf(mx, t);
+#pragma unroll
+    for (int r = 0; r < QX_CACHE; ++r) {
+        const int i = tid + QX_THREADS * r;
+        v[r] = i < k4n ? __ldg(row + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+#pragma unroll
+    for (int r = 0; r < QX_CACHE; ++r) mx = fmaxf(mx, qx_absmax(v[r], bad));
+    for (int i = tid + QX_THREADS * QX_CACHE; i < k4n; i += QX_THREADS) mx = fmaxf(mx, qx_absmax(__ldg(row + i), bad));
     if (bad) mx = INFINITY;
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
     if ((tid & 31) == 0) wmax[tid >> 5] = mx;
     __syncthreads();
-    mx = wmax[0];
+    mx = wmax[tid & 31];
 #pragma unroll
-    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, wmax[w]);
+    for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
 
     const bool finite = mx < INFINITY;
     int sexp = 0;
@@ -90,25 +136,15 @@ __global__ void __launch_bounds__(256) qx_digits_kernel(const float *__restrict_
     // a row with an infinity or a NaN comes out as NaN
     if (tid == 0) inv_s[m] = finite ? __uint_as_float((uint32_t)(127 - sexp) << 23) : __int_as_float(0x7FC00000);
 
-    const size_t plane = (size_t)MP * K;
+    const size_t plane4 = ((size_t)MP * K) >> 2;
     uint32_t *dst = reinterpret_cast<uint32_t *>(digits + (size_t)m * K);
-    for (int i = tid; i < k4n; i += 256) {
-        const float4 v = __ldg(row + i);
-        const float x[4] = { v.x, v.y, v.z, v.w };
-        uint32_t pk[4] = { 0u, 0u, 0u, 0u };
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            int t = __float2int_rn(x[e] * s);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int d = (int)(int8_t)(t & 0xFF);
-                t = (t - d) >> 8;
-                pk[j] |= (uint32_t)(d & 0xFF) << (8 * e);
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) dst[(j * plane >> 2) + i] = pk[j];
+    for (int r = 0; r < QX_CACHE; ++r) {
+        const int i = tid + QX_THREADS * r;
+        if (i < k4n) qx_emit(dst, plane4, i, v[r], s);
     }
+    for (int i = tid + QX_THREADS * QX_CACHE; i < k4n; i += QX_THREADS) qx_emit(dst, plane4, i, __ldg(row + i), s);
+    if (tid == 0) QP_STAMP(1)
 }
 
 // ------------------------------------------------------------------------------------------------ main kernel
@@ -117,12 +153,16 @@ __device__ __forceinline__ void qt_report(int *err, int code)
     if (err) atomicCAS(err, 0, code);
 }
 
-__device__ __forceinline__ float qt_finish(const QtArgs &a, long long total, int m, int64_t col)
+// total * scale * 2^-s, then the dense layer's bias and activation.  The 64-bit total (|total| < 2^55) is cut
+// into a signed head and 24 low bits, which convert with 32-bit instructions: the epilogue is a handful of warps
+// running dependent chains, so its instruction count is what it costs.
+__device__ __forceinline__ float qt_finish(long long total, float inv_s, float scale, float bias, int act)
 {
-    float v = (float)((double)total * (double)__ldg(a.inv_s + m) * (double)__ldg(a.scales + col));
-    if (a.bias) v += __ldg(a.bias + col);
-    if (a.act == 1) v = fmaxf(v, 0.0f);
-    else if (a.act == 2) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    const float head = (float)(int)(total >> 24);
+    const float tail = (float)(int)((unsigned)total & 0xFFFFFFu);
+    float v = fmaf(head, 16777216.0f, tail) * scale * inv_s + bias;
+    if (act == 1) v = fmaxf(v, 0.0f);
+    else if (act == 2) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
     return v;
 }
 
@@ -146,11 +186,14 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
     auto stage_addr = [&](int s) -> uint32_t { return base + 1024u + (uint32_t)s * STAGE; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) QP_STAMP(2)
     const int tile = blockIdx.x, slice = blockIdx.y, nslices = gridDim.y;
     const int64_t n0 = (int64_t)tile * QT_BN;
     const int per = (kb_total + nslices - 1) / nslices;
     const int kb0 = slice * per;
     const int nkb = max(0, min(per, kb_total - kb0));
+    const int pre = min(nkb, STAGES);
+    auto kpos = [&](int i) -> int { return (kb0 + i) * QT_KB; };
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -159,41 +202,54 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
         }
         mbar_init(bar(B_ACC), 1);
         mbar_fence_init();
+        // The weights depend on nothing this call computes: the first ring of weight tiles is requested before
+        // anything else happens in this CTA — before tensor memory is allocated and long before the digits of the
+        // pre-pass (which may still be running: this kernel is its programmatic dependent) are needed.
+        tma_prefetch_desc(&tm.w);
+        for (int i = 0; i < pre; ++i) {
+            mbar_arrive_expect_tx(bar(B_FULL + i), STAGE);
+            tma_load_3d(stage_addr(i), &tm.w, bar(B_FULL + i), kpos(i), (int32_t)n0, 0);
+        }
+        tma_prefetch_desc(&tm.x);
+        QP_STAMP(3)
     }
     if (warp == 1) {
         tmem_alloc(base + 512, TCOLS);
         tmem_relinquish();
-    }
-    if (warp == 0 && lane == 0) {
-        tma_prefetch_desc(&tm.w);
-        tma_prefetch_desc(&tm.x);
     }
     tc_fence_before_sync();
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
 
-    const int t_row = 32 * (warp & 3) + lane;   // drain warps: TMEM lane = weight row of the tile
-    long long *red = reinterpret_cast<long long *>(base_ptr + 1024);   // [MP][128], over the idle ring
+    // drain warps 2..17: TMEM lane quadrant warp & 3 (four warps per quadrant, `quarter` tells them apart)
+    const int t_row = 32 * (warp & 3) + lane;   // TMEM lane = weight row of the tile
+    const int quarter = (warp - 2) >> 2;
+    const int64_t col = n0 + t_row;
+    const bool col_ok = col < a.N;
+    float col_scale = 0.0f, col_bias = 0.0f;    // inputs of the call, not of the pre-pass: loaded ahead of the K loop
+    if (warp >= 2 && col_ok) {
+        col_scale = __ldg(a.scales + col);
+        if (a.bias) col_bias = __ldg(a.bias + col);
+    }
+    float *s_inv = reinterpret_cast<float *>(base_ptr + 256);   // 2^-s per activation row
+    // Partial sums of the other K-slices arrive here, behind the ring (a peer may be done while this CTA still
+    // streams): recv[source slice][row owned by this CTA][weight row of the tile]
+    long long *recv = reinterpret_cast<long long *>(base_ptr + 1024 + STAGES * STAGE);
+    const int rows_owned = (a.M + nslices - 1) / nslices;
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
-            // The weights do not depend on the digit pre-pass: the first ring of weight tiles is requested before
-            // this kernel waits for it, so the pre-pass and the launch overlap the first HBM round trips.
-            const int pre = min(nkb, STAGES);
-            for (int i = 0; i < pre; ++i) {
-                mbar_arrive_expect_tx(bar(B_FULL + i), STAGE);
-                tma_load_3d(stage_addr(i), &tm.w, bar(B_FULL + i), (kb0 + i) * QT_KB, (int32_t)n0, 0);
-            }
-            grid_dep_wait();
+            grid_dep_wait();   // the digits
+            QP_STAMP(4)
             for (int i = 0; i < pre; ++i)
-                tma_load_3d(stage_addr(i) + QT_W_BYTES, &tm.x, bar(B_FULL + i), (kb0 + i) * QT_KB, 0, 0);
+                tma_load_3d(stage_addr(i) + QT_W_BYTES, &tm.x, bar(B_FULL + i), kpos(i), 0, 0);
             for (int i = pre; i < nkb; ++i) {
                 const int s = i % STAGES, n = i / STAGES;
                 if (!mbar_wait_bounded(bar(B_EMPTY + s), (n - 1) & 1)) { qt_report(a.err, QERR_PRODUCER); break; }
                 const uint32_t st = stage_addr(s);
-                const int k0 = (kb0 + i) * QT_KB;
+                const int k0 = kpos(i);
                 mbar_arrive_expect_tx(bar(B_FULL + s), STAGE);
                 tma_load_3d(st, &tm.w, bar(B_FULL + s), k0, (int32_t)n0, 0);
                 tma_load_3d(st + QT_W_BYTES, &tm.x, bar(B_FULL + s), k0, 0, 0);
@@ -209,6 +265,7 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
             for (int i = 0; i < nkb; ++i) {
                 const int s = i % STAGES;
                 if (!mbar_wait_bounded(bar(B_FULL + s), (i / STAGES) & 1)) { ok = false; break; }
+                if (i == 0) QP_STAMP(5)
                 tc_fence_after_sync();
                 const uint32_t st = stage_addr(s);
 #pragma unroll
@@ -220,67 +277,80 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
                 tc_commit(bar(B_EMPTY + s));
             }
             if (ok && nkb > 0) tc_commit(bar(B_ACC));
+            QP_STAMP(6)
             if (!ok) qt_report(a.err, QERR_MMA);
         }
     } else {
         // --------------------------------------------------------------- drain
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         grid_dep_wait();   // the row scales come from the pre-pass
+        const int dt = threadIdx.x - 64;
+        if (dt < MP) s_inv[dt] = dt < a.M ? __ldg(a.inv_s + dt) : 0.0f;
+        asm volatile("bar.sync 1, 512;" ::: "memory");   // the sixteen drain warps
         bool have = nkb > 0;
         if (have && !mbar_wait_warp_bounded(bar(B_ACC), 0)) {
             qt_report(a.err, QERR_DRAIN);
             have = false;
         }
         tc_fence_after_sync();
-        const bool col_ok = n0 + t_row < a.N;
+        if (threadIdx.x == 64) QP_STAMP(7)
 #pragma unroll 1
-        for (int g = 0; g < MP / 8; ++g) {
-            uint32_t d[4][8];
+        for (int g = quarter; g < MP / 4; g += 4) {
+            if (4 * g >= a.M) break;
+            uint32_t d[4][4];
             if (have) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) tmem_ld_32x32_x8(lane_base + (uint32_t)(j * MP + 8 * g), d[j]);
+                for (int j = 0; j < 4; ++j) tmem_ld_32x32_x4(lane_base + (uint32_t)(j * MP + 4 * g), d[j]);
                 tmem_ld_wait();
+                if (threadIdx.x == 64 && g == quarter) QP_STAMP(11)
             } else {
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) d[j][u] = 0u;
+                    for (int u = 0; u < 4; ++u) d[j][u] = 0u;
             }
 #pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                const int m = 8 * g + u;
+            for (int u = 0; u < 4; ++u) {
+                const int m = 4 * g + u;
                 const long long total = (long long)(int)d[0][u] + ((long long)(int)d[1][u] << 8) +
                                         ((long long)(int)d[2][u] << 16) + ((long long)(int)d[3][u] << 24);
-                if (nslices == 1) {
-                    if (m < a.M && col_ok) a.out[(int64_t)m * a.N + n0 + t_row] = qt_finish(a, total, m, n0 + t_row);
-                } else {
-                    red[m * QT_BN + t_row] = total;   // every MMA of this CTA has completed: the ring is idle
+                if (m < a.M) {
+                    if (nslices == 1) {
+                        if (col_ok) a.out[(int64_t)m * a.N + col] = qt_finish(total, s_inv[m], col_scale, col_bias, a.act);
+                    } else {
+                        // to the slice that finishes row m (m mod nslices): a store into its shared memory
+                        const int owner = m % nslices, r = m / nslices;
+                        const uint32_t dst = map_to_cta(smem_u32(recv + (slice * rows_owned + r) * QT_BN + t_row), (uint32_t)owner);
+                        asm volatile("st.shared::cluster.b64 [%0], %1;" ::"r"(dst), "l"(total) : "memory");
+                    }
                 }
             }
         }
         tc_fence_before_sync();
+        if (threadIdx.x == 64) QP_STAMP(8)
     }
 
     if (nslices > 1) {
-        cluster_sync_all();
-        if (warp >= 2 && n0 + t_row < a.N) {
-            // slice r finishes rows r, r + nslices, ...: integer sums straight out of the peers' shared memory
-            for (int m = slice; m < a.M; m += nslices) {
-                const uint32_t local = smem_u32(red + m * QT_BN + t_row);
-                long long s = 0;
-                for (int q = 0; q < nslices; ++q) {
-                    long long v;
-                    asm volatile("ld.shared::cluster.b64 %0, [%1];" : "=l"(v) : "r"(map_to_cta(local, (uint32_t)q)));
-                    s += v;
-                }
-                a.out[(int64_t)m * a.N + n0 + t_row] = qt_finish(a, s, m, n0 + t_row);
+        cluster_sync_all();   // release / acquire: every slice's partial sums have landed
+        if (threadIdx.x == 64) QP_STAMP(9)
+        if (warp >= 2 && col_ok) {
+            // integer sums of the rows this slice owns, out of its own shared memory: nobody reads a peer after the
+            // barrier, so a CTA may leave as soon as it is done
+            for (int r = quarter; r < rows_owned; r += 4) {
+                const int m = slice + r * nslices;
+                if (m >= a.M) break;
+                long long sum = 0;
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    if (q < nslices) sum += recv[(q * rows_owned + r) * QT_BN + t_row];
+                a.out[(int64_t)m * a.N + col] = qt_finish(sum, s_inv[m], col_scale, col_bias, a.act);
             }
         }
-        cluster_sync_all();   // the peers' shared memory must outlive the reads above
     }
 
     tc_fence_before_sync();
     __syncthreads();
+    if (threadIdx.x == 64) QP_STAMP(10)
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, TCOLS);
@@ -305,7 +375,7 @@ size_t qskinny_tc_workspace_bytes(int64_t M, int64_t K)
 template <int MP>
 static int launch_inst(const QtMaps &tm, const QtArgs &a, int kb_total, dim3 grid, cudaStream_t st)
 {
-    const size_t smem = 1024 + (size_t)qt_stages(MP) * (QT_W_BYTES + 4 * MP * 128) + 1024;
+    const size_t smem = 1024 + (size_t)qt_stages(MP) * (QT_W_BYTES + 4 * MP * 128) + (size_t)(MP + 8) * 1024 + 1024;
     auto kern = qskinny_tc_kernel<MP>;
     static bool attr_set[64] = {};
     int dev = 0;
@@ -338,7 +408,7 @@ int launch_qskinny_tc(const float *act_in, const int8_t *q, const float *scales,
     const int mp = M <= 8 ? 8 : M <= 16 ? 16 : M <= 32 ? 32 : 64;
     float *inv_s = reinterpret_cast<float *>(workspace);
     int8_t *digits = reinterpret_cast<int8_t *>(workspace) + 1024;
-    qx_digits_kernel<<<(unsigned)M, 256, 0, st>>>(act_in, (int)K, mp, digits, inv_s);
+    qx_digits_kernel<<<(unsigned)M, QX_THREADS, 0, st>>>(act_in, (int)K, mp, digits, inv_s);
     int e = (int)cudaGetLastError();
     if (e) return e;
 

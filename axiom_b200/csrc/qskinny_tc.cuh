@@ -11,8 +11,8 @@ bool qskinny_tc_applicable(int64_t M, int64_t N, int64_t K, const float *a, cons
 // bytes of device scratch one call needs (digit planes of the activations + one scale per row)
 size_t qskinny_tc_workspace_bytes(int64_t M, int64_t K);
 // out = act(scale[n] * sum_k a*q (+ bias[n])); bias may be null, act 0 none / 1 ReLU / 2 GELU (tanh form).
-// Two launches on `st`: the digit pre-pass and the tensor-core kernel.  `err` receives a code if a wait in the
-// kernel runs out.
+// Two launches on `st`: the digit pre-pass and the tensor-core kernel, which is launched as a programmatic dependent
+// and requests its first weight tiles while the pre-pass runs.  `err` receives a code if a wait in the kernel runs out.
 int launch_qskinny_tc(const float *a, const int8_t *q, const float *scales, const float *bias, int act, float *out,
                       int64_t M, int64_t N, int64_t K, void *workspace, int *err, int sm_count, cudaStream_t st);
 

@@ -398,12 +398,13 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
 
     # W8A32 at bs=1: the case the reference's quantised path exists for (int8 weights streamed once);
     # rotating weight buffers of 256 MiB in total (> L2) so every call streams from HBM
-    for nq in (4096, 16384):
+    # bs = 8 and 32 (batched decode) take the integer tensor-core kernel: activations as int8 digit planes
+    for nq, bs in ((4096, 1), (16384, 1), (16384, 8), (16384, 32)):
         try:
             nbuf = 256 * 2 ** 20 // (nq * 4096)
             w8 = [torch.randint(-127, 128, (nq, 4096), device="cuda", dtype=torch.int8) for _ in range(nbuf)]
             sq = torch.rand((nq,), device="cuda") * 0.019 + 0.001
-            x1, o1 = uniform((1, 4096)), torch.empty((1, nq), device="cuda")
+            x1, o1 = uniform((bs, 4096)), torch.empty((bs, nq), device="cuda")
             st8 = {"i": 0}
 
             def qv():
@@ -411,8 +412,8 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
                 st8["i"] += 1
             step_ms, core_ms, _ = core_time(qv, 64, 8)
             kern_ms = graph_time(eng, qv) or core_ms
-            nb = nq * 4096 + 4096 * 4 + 2 * nq * 4
-            out.append({"workload": f"W8A32 GEMV bs=1, int8 W[{nq}x4096] ({nbuf} rotating weight buffers)",
+            nb = nq * 4096 + bs * 4096 * 4 + (1 + bs) * nq * 4
+            out.append({"workload": f"W8A32 GEMV bs={bs}, int8 W[{nq}x4096] ({nbuf} rotating weight buffers)",
                         "value": nb / (step_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": step_ms, "kernel_ms": kern_ms,
                         "kernel_ms_eager_events": core_ms,
                         "timing": "kernel_ms: mean over a replayed CUDA graph of 64 calls; value/ms_per_step: eager calls from Python",
@@ -420,7 +421,7 @@ def extras(torch, dist, world, eng, peaks, uniform, A, B, Cout, K):
                                      "frac": nb / (kern_ms * 1e-3) / 1e9 / hbm, "peak_source": f"{peaks['source']} HBM copy bandwidth"}})
             del w8
         except Exception as exc:
-            out.append({"workload": f"W8A32 GEMV bs=1 N={nq}", "error": repr(exc)})
+            out.append({"workload": f"W8A32 GEMV bs={bs} N={nq}", "error": repr(exc)})
 
     # causal attention B=8,H=16,S=1024,dk=64 (benchmark config 4); FLOPs by the reference's 4*BH*S^2*dk convention
     BH, S, dk = 128, 1024, 64
@@ -544,6 +545,15 @@ def run_profile_case(args):
         Wq = [torch.randint(-127, 128, (16384, 4096), device="cuda", dtype=torch.int8) for _ in range(4)]
         sc = torch.rand((16384,), device="cuda") * 0.019 + 0.001
         xq, oq = torch.randn((1, 4096), device="cuda"), torch.empty((1, 16384), device="cuda")
+        state = {"i": 0}
+
+        def fn():
+            eng.qgemm_w8a32(xq, Wq[state["i"] % 4], sc, oq)
+            state["i"] += 1
+    elif case == "qskinny":
+        Wq = [torch.randint(-127, 128, (16384, 4096), device="cuda", dtype=torch.int8) for _ in range(4)]
+        sc = torch.rand((16384,), device="cuda") * 0.019 + 0.001
+        xq, oq = torch.randn((8, 4096), device="cuda"), torch.empty((8, 16384), device="cuda")
         state = {"i": 0}
 
         def fn():
