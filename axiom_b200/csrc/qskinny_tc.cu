@@ -302,7 +302,6 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
 #pragma unroll
                 for (int j = 0; j < 4; ++j) tmem_ld_32x32_x4(lane_base + (uint32_t)(j * MP + 4 * g), d[j]);
                 tmem_ld_wait();
-                if (threadIdx.x == 64 && g == quarter) QP_STAMP(11)
             } else {
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
