@@ -4,10 +4,13 @@
 // feeds 128 FMAs and the fp32 pipe, not memory, sets the pace (measured 16 % of the copy bandwidth).  Here the
 // product is computed transposed, Y^T[N,M] = W^T.X^T, so that the 128 rows of the MMA are output COLUMNS and the
 // few activation rows are its N: W is the A operand in MN-major form — the [k][n] tile exactly as TMA leaves it
-// (128-byte swizzle with 32-byte atoms) — and X the K-major B operand.  Three tf32 products (lo.hi, hi.lo,
-// hi.hi) keep fp32 accuracy; the hi operand is the fp32 tile itself (the tensor core ignores the 13 low mantissa
-// bits of a tf32 container) and converter warps write tf32(x - trunc(x)) next to it, so W crosses shared memory
-// once from TMA and once from the converters and never goes through registers for arithmetic.
+// (128-byte swizzle with 32-byte atoms) — and X the K-major B operand.  Three tf32 products (hi.hi, hi.lo,
+// lo.hi) keep fp32 accuracy; the hi operand is the fp32 tile itself (the tensor core ignores the 13 low mantissa
+// bits of a tf32 container) and converter warps write tf32(x - trunc(x)): W lo into a ring of its own, X lo right
+// behind X hi, so that both halves of X are one operand of 2*M rows and W hi is read once for two of the three
+// products (the kernel is bound by shared-memory bandwidth: every pass of the tensor core over a W tile counts).
+// W crosses shared memory once from TMA and once from the converters and never goes through registers for
+// arithmetic.
 //
 // One CTA = 128 output columns x one K-slice; the K-slices of a column tile form a thread-block cluster and are
 // summed through distributed shared memory in slice order (deterministic).  Roles: warp 0 TMA producer (ring of
@@ -114,7 +117,9 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
                                                                    const SkinnyArgs a, int kb_total)
 {
     constexpr uint32_t X_BYTES = MP * 128;                       // [MP rows][32 k] fp32
-    constexpr uint32_t STAGE = KT_W_BYTES + X_BYTES;             // W | X (raw ring and lo ring alike)
+    // raw stage: W | X hi | X lo.  The lo half of X is written by the converters right behind the hi half, so that
+    // both form ONE K-major operand of 2*MP rows: W hi then meets X hi and X lo in a single pass over W.
+    constexpr uint32_t STAGE = KT_W_BYTES + 2 * X_BYTES;
 #ifdef AXB_SKTC_PROF
     const long long kernel_t0 = clock64();
 #endif
@@ -125,7 +130,7 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + 512);
     auto bar = [&](int i) -> uint32_t { return base + 8u * (uint32_t)i; };
     auto stage_addr = [&](int s) -> uint32_t { return base + 1024u + (uint32_t)s * STAGE; };
-    auto lo_addr = [&](int s) -> uint32_t { return base + 1024u + (uint32_t)(KT_STAGES + s) * STAGE; };
+    auto lo_addr = [&](int s) -> uint32_t { return base + 1024u + (uint32_t)KT_STAGES * STAGE + (uint32_t)s * KT_W_BYTES; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x, slice = blockIdx.y, nslices = gridDim.y;
@@ -151,7 +156,7 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
         mbar_fence_init();
     }
     if (warp == 1) {
-        tmem_alloc(base + 512, 64);
+        tmem_alloc(base + 512, 128);
         tmem_relinquish();
     }
     if (warp == 0 && lane == 0) {
@@ -193,7 +198,9 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
         if (lane == 0) {
             const uint64_t desc_w = smem_desc_mnmajor_sw128_32b(0, 4096, 512);
             const uint64_t desc_x = smem_desc_kmajor(0, 128);
-            const uint32_t idesc = make_idesc<KIND_TF32>(KT_BN, MP) | (1u << 15);   // A (the weights) is MN-major
+            // A (the weights) is MN-major; N = 2*MP for the pass over W hi (X hi and X lo side by side), MP for W lo
+            const uint32_t idesc_hi = make_idesc<KIND_TF32>(KT_BN, 2 * MP) | (1u << 15);
+            const uint32_t idesc_lo = make_idesc<KIND_TF32>(KT_BN, MP) | (1u << 15);
             bool ok = true;
             KP_DECL(3)
             for (int i = 0; i < nkb; ++i) {
@@ -207,19 +214,18 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
                 KP_ADD(1)
                 tc_fence_after_sync();
                 const uint32_t st = stage_addr(s), lo = lo_addr(ls);
-                const uint32_t d = tmem + cb * 32;
-                uint32_t accf = first ? 0u : 1u;
+                const uint32_t d = tmem + cb * 64;
+                const uint32_t xb = st + KT_W_BYTES;
+                // columns [0, MP): hi.hi + lo.hi, columns [MP, 2*MP): hi.lo; the drain adds the two halves
 #pragma unroll
-                for (int pr = 0; pr < 3; ++pr) {
-                    const uint32_t wa = pr == 0 ? lo : st;                                     // lo.hi, hi.lo, hi.hi
-                    const uint32_t xb = (pr == 1 ? lo : st) + KT_W_BYTES;
+                for (int ks = 0; ks < 4; ++ks)
+                    tc_mma<KIND_TF32>(d, desc_w | (uint64_t)(((st + ks * 1024) & 0x3FFFFu) >> 4),
+                                      desc_x | (uint64_t)(((xb + ks * 32) & 0x3FFFFu) >> 4), idesc_hi,
+                                      (first && ks == 0) ? 0u : 1u);
 #pragma unroll
-                    for (int ks = 0; ks < 4; ++ks) {
-                        tc_mma<KIND_TF32>(d, desc_w | (uint64_t)(((wa + ks * 1024) & 0x3FFFFu) >> 4),
-                                          desc_x | (uint64_t)(((xb + ks * 32) & 0x3FFFFu) >> 4), idesc, accf);
-                        accf = 1u;
-                    }
-                }
+                for (int ks = 0; ks < 4; ++ks)
+                    tc_mma<KIND_TF32>(d, desc_w | (uint64_t)(((lo + ks * 1024) & 0x3FFFFu) >> 4),
+                                      desc_x | (uint64_t)(((xb + ks * 32) & 0x3FFFFu) >> 4), idesc_lo, 1u);
                 tc_commit(bar(KB_LO_EMPTY + ls));
                 tc_commit(bar(KB_EMPTY + s));
                 if ((i % KT_CHUNK) == KT_CHUNK - 1 || i == nkb - 1) tc_commit(bar(KB_CHUNK_FULL + cb));
@@ -244,7 +250,7 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
             KP_ADD(1)
             const uint32_t st = stage_addr(s), lo = lo_addr(ls);
             kt_split<KT_W_BYTES / 16 / 128>(st, lo - st, ct);
-            kt_split<X_BYTES / 16 / 128>(st + KT_W_BYTES, lo - st, ct);
+            kt_split<X_BYTES / 16 / 128>(st + KT_W_BYTES, X_BYTES, ct);
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(bar(KB_LO_FULL + ls));
             KP_ADD(2)
@@ -257,13 +263,15 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
             const int cb = ci & 1;
             if (!mbar_wait_warp_bounded(bar(KB_CHUNK_FULL + cb), (ci >> 1) & 1)) { kt_report(a.err, KERR_DRAIN); break; }
             tc_fence_after_sync();
-            uint32_t r[32];
-            tmem_ld_32x32(lane_base + cb * 32, r);
+            uint32_t r[32], r2[32];
+            tmem_ld_32x32(lane_base + cb * 64, r);
+            if (MP == 32) tmem_ld_32x32(lane_base + cb * 64 + 32, r2);
             tmem_ld_wait();
             tc_fence_before_sync();
             mbar_arrive(bar(KB_CHUNK_EMPTY + cb));
 #pragma unroll
-            for (int m = 0; m < MP; ++m) acc[m] += __uint_as_float(r[m]);
+            for (int m = 0; m < MP; ++m)
+                acc[m] += __uint_as_float(r[m]) + __uint_as_float(MP == 32 ? r2[m] : r[(MP + m) & 31]);
         }
     }
 
@@ -306,7 +314,7 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
 #endif
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem, 64);
+        tmem_dealloc(tmem, 128);
     }
 }
 
@@ -323,7 +331,7 @@ bool skinny_tc_applicable(int64_t M, int64_t N, int64_t K, const float *X, const
 template <int MP>
 static int launch_inst(const SkinnyTcMaps &tm, const SkinnyArgs &a, int kb_total, dim3 grid, cudaStream_t st)
 {
-    const size_t smem = 1024 + (size_t)(KT_STAGES + KT_LO) * (KT_W_BYTES + MP * 128) + 1024;
+    const size_t smem = 1024 + (size_t)KT_STAGES * (KT_W_BYTES + 2 * MP * 128) + (size_t)KT_LO * KT_W_BYTES + 1024;
     auto kern = skinny_tc_kernel<MP>;
     static bool attr_set[64] = {};
     int dev = 0;
