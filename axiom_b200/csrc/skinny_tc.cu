@@ -3,19 +3,22 @@
 // The fp32-FMA skinny kernels stream W at the HBM rate only while M is small: at M = 32 every weight float4
 // feeds 128 FMAs and the fp32 pipe, not memory, sets the pace (measured 16 % of the copy bandwidth).  Here the
 // product is computed transposed, Y^T[N,M] = W^T.X^T, so that the 128 rows of the MMA are output COLUMNS and the
-// few activation rows are its N: W is the A operand in MN-major form — the [k][n] tile exactly as TMA leaves it
-// (128-byte swizzle with 32-byte atoms) — and X the K-major B operand.  Three tf32 products (hi.hi, hi.lo,
-// lo.hi) keep fp32 accuracy; the hi operand is the fp32 tile itself (the tensor core ignores the 13 low mantissa
-// bits of a tf32 container) and converter warps write tf32(x - trunc(x)): W lo into a ring of its own, X lo right
-// behind X hi, so that both halves of X are one operand of 2*M rows and W hi is read once for two of the three
-// products (the kernel is bound by shared-memory bandwidth: every pass of the tensor core over a W tile counts).
-// W crosses shared memory once from TMA and once from the converters and never goes through registers for
-// arithmetic.
+// few activation rows are its N.  Three tf32 products (hi.hi, hi.lo, lo.hi) keep fp32 accuracy; hi is the fp32
+// value itself (the tensor core ignores the 13 low mantissa bits of a tf32 container), lo = tf32(x - trunc(x)).
+//
+// W is the A operand and is fed from TENSOR MEMORY: TMA lands the plain [32 k][128 n] tile in shared memory,
+// each converter thread reads one column of it (its 32 k values for one output column — a warp reads 128
+// contiguous bytes per k), computes the lo values in registers and stores hi and lo into tensor memory with
+// tcgen05.st, where lane = output column and column = k is exactly the layout of a TS-form MMA's A operand.  So W
+// crosses shared memory twice (TMA in, converter out) instead of six times (a version with W as a shared-memory
+// operand, lo tiles written back to shared memory and three passes of the tensor core over them, was bound by
+// shared-memory bandwidth at 35 % of the HBM rate).  X stays a K-major shared-memory B operand; its lo half is
+// written right behind its hi half, so both are ONE operand of 2*M rows and W hi meets them in one pass.
 //
 // One CTA = 128 output columns x one K-slice; the K-slices of a column tile form a thread-block cluster and are
 // summed through distributed shared memory in slice order (deterministic).  Roles: warp 0 TMA producer (ring of
-// 8 raw stages of 32 k-rows — 128 KB of W in flight per SM), warp 1 MMA issuer, warps 2-5 converters (the lo tiles live in a ring of their own, two
-// deep, so the raw ring can be long), warps 6-9 drain the accumulator every 256 k (a fresh TMEM accumulator per
+// 8 stages of 32 k-rows — 128 KB of W in flight per SM), warp 1 MMA issuer, warps 2-5 converters (a ring of four
+// hi/lo tile pairs in tensor memory), warps 6-9 drain the accumulator every 256 k (a fresh TMEM accumulator per
 // chunk: the tensor core truncates when it accumulates) and run the epilogue.
 #include "skinny.cuh"
 
@@ -28,12 +31,13 @@
 namespace axb {
 
 static constexpr int KT_THREADS = 320;
-static constexpr int KT_STAGES = 8;      // raw ring (TMA destinations; the hi operands)
-static constexpr int KT_LO = 2;          // lo ring (converter output)
+static constexpr int KT_STAGES = 8;      // shared-memory ring (TMA destinations)
+static constexpr int KT_T = 4;           // ring of W hi/lo tile pairs in tensor memory (64 columns each)
+static constexpr int KT_ACC_COL = KT_T * 64;   // the two accumulator buffers follow the ring
 static constexpr int KT_KB = 32;        // k rows per stage
 static constexpr int KT_BN = 128;       // output columns per CTA
 static constexpr int KT_CHUNK = 8;      // stages per accumulator chunk (256 k)
-static constexpr int KT_W_BYTES = KT_KB * KT_BN * 4;  // 16 KB: 4 slabs of [32 k][32 n]
+static constexpr int KT_W_BYTES = KT_KB * KT_BN * 4;  // 16 KB: [32 k][128 n], rows of 512 bytes
 
 struct alignas(64) SkinnyTcMaps {
     CUtensorMap w, x;
@@ -41,8 +45,8 @@ struct alignas(64) SkinnyTcMaps {
 
 enum { KERR_PRODUCER = 21, KERR_CONVERT = 22, KERR_MMA = 23, KERR_DRAIN = 24 };
 
-enum { KB_RAW = 0, KB_EMPTY = KT_STAGES, KB_LO_FULL = 2 * KT_STAGES, KB_LO_EMPTY = 2 * KT_STAGES + KT_LO,
-       KB_CHUNK_FULL = 2 * KT_STAGES + 2 * KT_LO, KB_CHUNK_EMPTY = 2 * KT_STAGES + 2 * KT_LO + 2 };
+enum { KB_RAW = 0, KB_EMPTY = KT_STAGES, KB_T_FULL = 2 * KT_STAGES, KB_T_EMPTY = 2 * KT_STAGES + KT_T,
+       KB_CHUNK_FULL = 2 * KT_STAGES + 2 * KT_T, KB_CHUNK_EMPTY = 2 * KT_STAGES + 2 * KT_T + 2 };
 
 #ifdef AXB_SKTC_PROF
 __device__ unsigned long long g_sktc_prof[32];
@@ -53,10 +57,12 @@ extern "C" __attribute__((visibility("default"))) int axb_debug_sktc_prof(unsign
 {
     return (int)cudaMemcpyFromSymbol(out, g_sktc_prof, sizeof(unsigned long long) * 32);
 }
+#define KP_STAMP(i) { if (blockIdx.x == 0 && blockIdx.y == 0) g_sktc_prof[i] = (unsigned long long)(clock64() - kernel_t0); }
 #else
 #define KP_DECL(n)
 #define KP_ADD(i)
 #define KP_OUT(base, n)
+#define KP_STAMP(i) {}
 #endif
 
 // one lane polls, the warp gets the outcome: 32 lanes spinning on a barrier cost shared-memory bandwidth that
@@ -117,8 +123,7 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
                                                                    const SkinnyArgs a, int kb_total)
 {
     constexpr uint32_t X_BYTES = MP * 128;                       // [MP rows][32 k] fp32
-    // raw stage: W | X hi | X lo.  The lo half of X is written by the converters right behind the hi half, so that
-    // both form ONE K-major operand of 2*MP rows: W hi then meets X hi and X lo in a single pass over W.
+    // stage: W | X hi | X lo (the lo half of X is written by the converters right behind the hi half)
     constexpr uint32_t STAGE = KT_W_BYTES + 2 * X_BYTES;
 #ifdef AXB_SKTC_PROF
     const long long kernel_t0 = clock64();
@@ -130,7 +135,6 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(base_ptr + 512);
     auto bar = [&](int i) -> uint32_t { return base + 8u * (uint32_t)i; };
     auto stage_addr = [&](int s) -> uint32_t { return base + 1024u + (uint32_t)s * STAGE; };
-    auto lo_addr = [&](int s) -> uint32_t { return base + 1024u + (uint32_t)KT_STAGES * STAGE + (uint32_t)s * KT_W_BYTES; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x, slice = blockIdx.y, nslices = gridDim.y;
@@ -145,9 +149,9 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
             mbar_init(bar(KB_RAW + s), 1);
             mbar_init(bar(KB_EMPTY + s), 1);
         }
-        for (int s = 0; s < KT_LO; ++s) {
-            mbar_init(bar(KB_LO_FULL + s), 128);
-            mbar_init(bar(KB_LO_EMPTY + s), 1);
+        for (int s = 0; s < KT_T; ++s) {
+            mbar_init(bar(KB_T_FULL + s), 128);
+            mbar_init(bar(KB_T_EMPTY + s), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar(KB_CHUNK_FULL + b), 1);
@@ -156,7 +160,7 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
         mbar_fence_init();
     }
     if (warp == 1) {
-        tmem_alloc(base + 512, 128);
+        tmem_alloc(base + 512, 512);
         tmem_relinquish();
     }
     if (warp == 0 && lane == 0) {
@@ -167,6 +171,7 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
+    if (threadIdx.x == 0) KP_STAMP(20)
 
     float acc[MP];
 #pragma unroll
@@ -185,9 +190,7 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
                 const uint32_t st = stage_addr(s);
                 const int k0 = (kb0 + i) * KT_KB;
                 mbar_arrive_expect_tx(bar(KB_RAW + s), KT_W_BYTES + X_BYTES);
-#pragma unroll
-                for (int sl = 0; sl < 4; ++sl)
-                    tma_load_3d(st + sl * 4096, &tm.w, bar(KB_RAW + s), (int32_t)(n0 + 32 * sl), k0, 0);
+                tma_load_2d(st, &tm.w, bar(KB_RAW + s), (int32_t)n0, k0);
                 tma_load_3d(st + KT_W_BYTES, &tm.x, bar(KB_RAW + s), k0, 0, 0);
             }
             KP_ADD(0)
@@ -196,11 +199,10 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
     } else if (warp == 1) {
         // ---------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            const uint64_t desc_w = smem_desc_mnmajor_sw128_32b(0, 4096, 512);
             const uint64_t desc_x = smem_desc_kmajor(0, 128);
-            // A (the weights) is MN-major; N = 2*MP for the pass over W hi (X hi and X lo side by side), MP for W lo
-            const uint32_t idesc_hi = make_idesc<KIND_TF32>(KT_BN, 2 * MP) | (1u << 15);
-            const uint32_t idesc_lo = make_idesc<KIND_TF32>(KT_BN, MP) | (1u << 15);
+            // N = 2*MP for the pass of W hi over X hi and X lo side by side, MP for W lo over X hi
+            const uint32_t idesc_hi = make_idesc<KIND_TF32>(KT_BN, 2 * MP);
+            const uint32_t idesc_lo = make_idesc<KIND_TF32>(KT_BN, MP);
             bool ok = true;
             KP_DECL(3)
             for (int i = 0; i < nkb; ++i) {
@@ -209,50 +211,65 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
                 const bool first = (i % KT_CHUNK) == 0;
                 if (first && ci >= 2 && !mbar_wait_bounded(bar(KB_CHUNK_EMPTY + cb), ((ci >> 1) - 1) & 1)) { ok = false; break; }
                 KP_ADD(0)
-                const int ls = i % KT_LO;
-                if (!mbar_wait_bounded(bar(KB_LO_FULL + ls), (i / KT_LO) & 1)) { ok = false; break; }   // implies the raw stage
+                const int ts = i % KT_T;
+                if (!mbar_wait_bounded(bar(KB_T_FULL + ts), (i / KT_T) & 1)) { ok = false; break; }   // implies the stage's X
                 KP_ADD(1)
+                if (i == 0) KP_STAMP(21)
                 tc_fence_after_sync();
-                const uint32_t st = stage_addr(s), lo = lo_addr(ls);
-                const uint32_t d = tmem + cb * 64;
-                const uint32_t xb = st + KT_W_BYTES;
-                // columns [0, MP): hi.hi + lo.hi, columns [MP, 2*MP): hi.lo; the drain adds the two halves
+                const uint32_t a_hi = tmem + ts * 64, a_lo = a_hi + 32;   // W^T: lane = output column, column = k
+                const uint32_t d = tmem + KT_ACC_COL + cb * 128;
+                const uint32_t xb = stage_addr(s) + KT_W_BYTES;
+                // columns [0, MP): hi.hi, [MP, 2*MP): hi.lo, [2*MP, 3*MP): lo.hi — the drain adds the three.  The two
+                // passes alternate and own separate columns: an MMA that accumulates waits for the one before it on
+                // the same columns, and two independent chains keep the pipe busy where one does not.
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                    tc_mma<KIND_TF32>(d, desc_w | (uint64_t)(((st + ks * 1024) & 0x3FFFFu) >> 4),
-                                      desc_x | (uint64_t)(((xb + ks * 32) & 0x3FFFFu) >> 4), idesc_hi,
-                                      (first && ks == 0) ? 0u : 1u);
-#pragma unroll
-                for (int ks = 0; ks < 4; ++ks)
-                    tc_mma<KIND_TF32>(d, desc_w | (uint64_t)(((lo + ks * 1024) & 0x3FFFFu) >> 4),
-                                      desc_x | (uint64_t)(((xb + ks * 32) & 0x3FFFFu) >> 4), idesc_lo, 1u);
-                tc_commit(bar(KB_LO_EMPTY + ls));
+                for (int ks = 0; ks < 4; ++ks) {
+                    const uint64_t bx = desc_x | (uint64_t)(((xb + ks * 32) & 0x3FFFFu) >> 4);
+                    const uint32_t accf = (first && ks == 0) ? 0u : 1u;
+                    tc_mma_ts_tf32(d, a_hi + ks * 8, bx, idesc_hi, accf);
+                    tc_mma_ts_tf32(d + 2 * MP, a_lo + ks * 8, bx, idesc_lo, accf);
+                }
+                tc_commit(bar(KB_T_EMPTY + ts));
                 tc_commit(bar(KB_EMPTY + s));
                 if ((i % KT_CHUNK) == KT_CHUNK - 1 || i == nkb - 1) tc_commit(bar(KB_CHUNK_FULL + cb));
                 KP_ADD(2)
             }
             if (!ok) kt_report(a.err, KERR_MMA);
+            KP_STAMP(22)
             KP_OUT(4, 3)
         }
     } else if (warp < 6) {
         // ---------------------------------------------------------- converters
         const int ct = threadIdx.x - 64;  // 0..127
+        const int t_n = 32 * (warp & 3) + lane;   // the output column this thread carries into its TMEM lane
+        const uint32_t st_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         KP_DECL(3)
         for (int i = 0; i < nkb; ++i) {
             const int s = i % KT_STAGES, n = i / KT_STAGES;
             if (!kt_wait_warp(bar(KB_RAW + s), n & 1)) { kt_report(a.err, KERR_CONVERT); break; }
             KP_ADD(0)
-            const int ls = i % KT_LO;
-            if (i >= KT_LO && !kt_wait_warp(bar(KB_LO_EMPTY + ls), ((i / KT_LO) - 1) & 1)) {
+            const int ts = i % KT_T;
+            if (i >= KT_T && !kt_wait_warp(bar(KB_T_EMPTY + ts), ((i / KT_T) - 1) & 1)) {
                 kt_report(a.err, KERR_CONVERT);
                 break;
             }
+            tc_fence_after_sync();
             KP_ADD(1)
-            const uint32_t st = stage_addr(s), lo = lo_addr(ls);
-            kt_split<KT_W_BYTES / 16 / 128>(st, lo - st, ct);
+            const uint32_t st = stage_addr(s);
+            uint32_t hi[32], lo[32];
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+                asm volatile("ld.shared.b32 %0, [%1];" : "=r"(hi[k]) : "r"(st + (uint32_t)k * 512u + (uint32_t)t_n * 4u));
             kt_split<X_BYTES / 16 / 128>(st + KT_W_BYTES, X_BYTES, ct);
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(bar(KB_LO_FULL + ls));
+#pragma unroll
+            for (int k = 0; k < 32; ++k)
+                lo[k] = (__float_as_uint(__uint_as_float(hi[k]) - __uint_as_float(hi[k] & 0xFFFFE000u)) + 0x1000u) & 0xFFFFE000u;
+            tmem_st_32x32(st_lane + ts * 64, hi);
+            tmem_st_32x32(st_lane + ts * 64 + 32, lo);
+            tmem_st_wait();
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // X lo, for the MMA's shared-memory reads
+            tc_fence_before_sync();
+            mbar_arrive(bar(KB_T_FULL + ts));
             KP_ADD(2)
         }
         if (ct == 0) { KP_OUT(8, 3) }
@@ -263,18 +280,33 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
             const int cb = ci & 1;
             if (!mbar_wait_warp_bounded(bar(KB_CHUNK_FULL + cb), (ci >> 1) & 1)) { kt_report(a.err, KERR_DRAIN); break; }
             tc_fence_after_sync();
-            uint32_t r[32], r2[32];
-            tmem_ld_32x32(lane_base + cb * 64, r);
-            if (MP == 32) tmem_ld_32x32(lane_base + cb * 64 + 32, r2);
-            tmem_ld_wait();
-            tc_fence_before_sync();
-            mbar_arrive(bar(KB_CHUNK_EMPTY + cb));
+            const uint32_t abuf = lane_base + KT_ACC_COL + cb * 128;
+            if (MP == 32) {
+                uint32_t r0[32], r1[32], r2[32];
+                tmem_ld_32x32(abuf, r0);
+                tmem_ld_32x32(abuf + 32, r1);
+                tmem_ld_32x32(abuf + 64, r2);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                mbar_arrive(bar(KB_CHUNK_EMPTY + cb));
 #pragma unroll
-            for (int m = 0; m < MP; ++m)
-                acc[m] += __uint_as_float(r[m]) + __uint_as_float(MP == 32 ? r2[m] : r[(MP + m) & 31]);
+                for (int m = 0; m < MP; ++m)
+                    acc[m] += (__uint_as_float(r1[m & 31]) + __uint_as_float(r2[m & 31])) + __uint_as_float(r0[m & 31]);
+            } else {
+                uint32_t r0[32], r1[32];
+                tmem_ld_32x32(abuf, r0);        // hi.hi | hi.lo
+                tmem_ld_32x32(abuf + 32, r1);   // lo.hi | unused
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                mbar_arrive(bar(KB_CHUNK_EMPTY + cb));
+#pragma unroll
+                for (int m = 0; m < MP; ++m)
+                    acc[m] += (__uint_as_float(r0[(MP + m) & 31]) + __uint_as_float(r1[m & 31])) + __uint_as_float(r0[m & 31]);
+            }
         }
     }
 
+    if (threadIdx.x == 192) KP_STAMP(23)
     // ------------------------------------------------------------ reduce + epilogue
     if (nslices == 1) {
         if (warp >= 6 && n0 + t_row < a.N) {
@@ -283,25 +315,44 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
                 if (m < a.M) a.Y[(int64_t)m * a.N + n0 + t_row] = kt_epilogue(a, acc[m], m, n0 + t_row);
         }
     } else {
-        // the ring is idle: every MMA of this CTA has completed before the last chunk was drained
-        float *red = reinterpret_cast<float *>(base_ptr + 1024);   // [MP][128]
+        // The ring is idle (every MMA of this CTA has completed before the last chunk was drained): it carries this
+        // slice's partial sums [MP][128].  Slice r finishes rows r, r + nslices, ...: its converter and drain warps
+        // take one (row, four columns) item each and fetch the four values of every slice with ONE 128-bit load per
+        // slice, all in flight together, and add them in slice order (bitwise deterministic).  One value per load,
+        // one load after the other — the first version — cost a round trip per term; pushing the sums with remote
+        // stores instead cost 2.8 us for 32 scalar stores per thread.
+        float *red = reinterpret_cast<float *>(base_ptr + 1024);
         __syncthreads();
         if (warp >= 6) {
 #pragma unroll
             for (int m = 0; m < MP; ++m) red[m * KT_BN + t_row] = acc[m];
         }
+        if (threadIdx.x == 192) KP_STAMP(24)
         cluster_sync_all();
-        if (warp >= 6 && n0 + t_row < a.N) {
-            // slice r finishes rows r, r + nslices, ...: sums in slice order, straight out of the peers' shared memory
-            for (int m = slice; m < a.M; m += nslices) {
-                const uint32_t local = smem_u32(red + m * KT_BN + t_row);
-                float s = 0.f;
-                for (int q = 0; q < nslices; ++q) {
-                    float v;
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(map_to_cta(local, (uint32_t)q)));
-                    s += v;
+        if (threadIdx.x == 192) KP_STAMP(25)
+        if (warp >= 2) {
+            const int rows_owned = (a.M - slice + nslices - 1) / nslices;
+            for (int it = threadIdx.x - 64; it < rows_owned * 32; it += 256) {
+                const int m = slice + (it >> 5) * nslices, c4 = (it & 31) * 4;
+                const uint32_t local = smem_u32(red + m * KT_BN + c4);
+                float4 v[8];
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                    v[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (q < nslices)
+                        asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                                     : "=f"(v[q].x), "=f"(v[q].y), "=f"(v[q].z), "=f"(v[q].w)
+                                     : "r"(map_to_cta(local, (uint32_t)q)));
                 }
-                a.Y[(int64_t)m * a.N + n0 + t_row] = kt_epilogue(a, s, m, n0 + t_row);
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    if (q < nslices) { sum.x += v[q].x; sum.y += v[q].y; sum.z += v[q].z; sum.w += v[q].w; }
+                const int64_t col = n0 + c4;
+                const float out4[4] = { sum.x, sum.y, sum.z, sum.w };
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    if (col + e < a.N) a.Y[(int64_t)m * a.N + col + e] = kt_epilogue(a, out4[e], m, col + e);
             }
         }
         cluster_sync_all();   // the peers' shared memory must outlive the reads above
@@ -314,7 +365,7 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
 #endif
     if (warp == 1) {
         tc_fence_after_sync();
-        tmem_dealloc(tmem, 128);
+        tmem_dealloc(tmem, 512);
     }
 }
 
@@ -331,7 +382,7 @@ bool skinny_tc_applicable(int64_t M, int64_t N, int64_t K, const float *X, const
 template <int MP>
 static int launch_inst(const SkinnyTcMaps &tm, const SkinnyArgs &a, int kb_total, dim3 grid, cudaStream_t st)
 {
-    const size_t smem = 1024 + (size_t)KT_STAGES * (KT_W_BYTES + 2 * MP * 128) + (size_t)KT_LO * KT_W_BYTES + 1024;
+    const size_t smem = 1024 + (size_t)KT_STAGES * (KT_W_BYTES + 2 * MP * 128) + 1024;
     auto kern = skinny_tc_kernel<MP>;
     static bool attr_set[64] = {};
     int dev = 0;
@@ -360,7 +411,7 @@ int launch_skinny_tc(const SkinnyArgs &a, int sm_count, cudaStream_t st)
 {
     const int mp = a.M <= 16 ? 16 : 32;
     SkinnyTcMaps tm;
-    int e = encode_f32_batched_tmap(&tm.w, a.W, 1, a.K, a.N, a.N, KT_KB, true);
+    int e = encode_f32_matrix_tmap(&tm.w, a.W, a.K, a.N, a.N, KT_BN, KT_KB);
     if (!e) e = encode_f32_batched_tmap(&tm.x, a.X, 1, a.M, a.K, a.K, mp, false);
     if (e) return e;
     const int tiles = (int)((a.N + KT_BN - 1) / KT_BN);
