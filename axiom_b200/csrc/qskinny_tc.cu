@@ -401,6 +401,71 @@ static int launch_inst(const QtMaps &tm, const QtArgs &a, int kb_total, dim3 gri
     return (int)cudaLaunchKernelEx(&cfg, kern, tm, a, kb_total);
 }
 
+// ------------------------------------------------------------------------- large M: the digits as a GEMM operand
+// For M > 64 the four digit planes [4][M][K] are the A operand of ONE int8 GEMM on the dense tcgen05 core
+// ([4M, K] x [N, K]^T -> s32 [4M, N]); this kernel recombines the four row blocks of that result:
+//     out[m,n] = act(scale[n] * 2^-s[m] * sum_j 256^j * acc[j*M + m, n] + bias[n]).
+__global__ void __launch_bounds__(256) qx_combine_kernel(const int32_t *__restrict__ acc, const float *__restrict__ inv_s,
+                                                         const float *__restrict__ scales, const float *__restrict__ bias,
+                                                         int act, float *__restrict__ out, int M, int64_t N)
+{
+    const int64_t n4 = (N + 3) >> 2;
+    const int64_t total = (int64_t)M * n4;
+    const bool vec = (N & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
+                     (reinterpret_cast<uintptr_t>(acc) & 15) == 0;
+    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
+        const int m = (int)(i / n4);
+        const int64_t n = (i - (int64_t)m * n4) << 2;
+        const float is = __ldg(inv_s + m);
+        int d[4][4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int32_t *src = acc + ((int64_t)j * M + m) * N + n;
+            if (vec) {
+                const int4 v = __ldcs(reinterpret_cast<const int4 *>(src));
+                d[j][0] = v.x; d[j][1] = v.y; d[j][2] = v.z; d[j][3] = v.w;
+            } else {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) d[j][e] = n + e < N ? src[e] : 0;
+            }
+        }
+        float y[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const long long t = (long long)d[0][e] + ((long long)d[1][e] << 8) + ((long long)d[2][e] << 16) +
+                                ((long long)d[3][e] << 24);
+            const int64_t c = n + e < N ? n + e : N - 1;
+            y[e] = qt_finish(t, is, __ldg(scales + c), bias ? __ldg(bias + c) : 0.0f, act);
+        }
+        float *dst = out + (int64_t)m * N + n;
+        if (vec) {
+            *reinterpret_cast<float4 *>(dst) = make_float4(y[0], y[1], y[2], y[3]);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)
+                if (n + e < N) dst[e] = y[e];
+        }
+    }
+}
+
+int launch_qx_digits(const float *act_in, int64_t M, int64_t K, int64_t plane_rows, int8_t *digits, float *inv_s,
+                     cudaStream_t st)
+{
+    qx_digits_kernel<<<(unsigned)M, QX_THREADS, 0, st>>>(act_in, (int)K, (int)plane_rows, digits, inv_s);
+    return (int)cudaGetLastError();
+}
+
+int launch_qx_combine(const int32_t *acc, const float *inv_s, const float *scales, const float *bias, int act, float *out,
+                      int64_t M, int64_t N, int sm_count, cudaStream_t st)
+{
+    const int64_t total = M * ((N + 3) >> 2);
+    int64_t blocks = (total + 255) / 256;
+    const int64_t cap = (int64_t)sm_count * 16;
+    if (blocks > cap) blocks = cap;
+    qx_combine_kernel<<<(unsigned)blocks, 256, 0, st>>>(acc, inv_s, scales, bias, act, out, (int)M, N);
+    return (int)cudaGetLastError();
+}
+
 int launch_qskinny_tc(const float *act_in, const int8_t *q, const float *scales, const float *bias, int act, float *out,
                       int64_t M, int64_t N, int64_t K, void *workspace, int *err, int sm_count, cudaStream_t st)
 {

@@ -16,4 +16,12 @@ size_t qskinny_tc_workspace_bytes(int64_t M, int64_t K);
 int launch_qskinny_tc(const float *a, const int8_t *q, const float *scales, const float *bias, int act, float *out,
                       int64_t M, int64_t N, int64_t K, void *workspace, int *err, int sm_count, cudaStream_t st);
 
+// M > 64: the same digit planes as the A operand of one int8 GEMM.  launch_qx_digits writes digits[4][plane_rows][K]
+// (row m of plane j at (j * plane_rows + m) * K) and 2^-s per row; launch_qx_combine turns the s32 result
+// [4 * M, N] of digits x weights^T into out[M, N] with the per-column scale, bias and activation.
+int launch_qx_digits(const float *a, int64_t M, int64_t K, int64_t plane_rows, int8_t *digits, float *inv_s,
+                     cudaStream_t st);
+int launch_qx_combine(const int32_t *acc, const float *inv_s, const float *scales, const float *bias, int act, float *out,
+                      int64_t M, int64_t N, int sm_count, cudaStream_t st);
+
 }  // namespace axb

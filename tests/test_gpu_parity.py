@@ -517,11 +517,35 @@ def test_w8a32_skinny_tensor_core_kernel(engine, oracle, shape):
         np.testing.assert_array_equal(got2[:M - 1], got[:M - 1])
 
 
+@pytest.mark.parametrize("shape", [(65, 1024, 1024), (129, 1000, 1168), (70, 1001, 1024), (512, 2048, 512)])
+def test_w8a32_digit_planes_as_gemm_operand(engine, oracle, shape):
+    """M > 64: the four int8 digit planes of the activations are the A operand of one int8 GEMM on the dense core; its
+    s32 result [4M, N] is recombined in 64-bit integers.  Ragged M, N (also not a multiple of 4: scalar path of the
+    combine kernel) and K, an outlier, and a row with an infinity."""
+    M, N, K = shape
+    a, w = oracle.uniform((M, K), 7), oracle.uniform((N, K), 13)
+    a[1, 3] = 1000.0
+    q, s = oracle.quantize_rows(w)
+    bias = oracle.uniform((N,), 29)
+    out = torch.full((M, N), float("nan"), device="cuda")
+    engine.qdense_w8a32(dev(a), torch.from_numpy(q).cuda(), dev(s), dev(bias), out, act="relu")
+    got = host(out)
+    assert engine.device_error() == 0
+    want = np.maximum(oracle.qgemm_w8a32_f64(a, q, s) + bias.astype(np.float64), 0.0)
+    assert nerr(got, want) <= 1e-6
+    a[M - 1, 5] = -np.inf
+    engine.qdense_w8a32(dev(a), torch.from_numpy(q).cuda(), dev(s), dev(bias), out, act="none")
+    got2 = host(out)
+    assert np.all(np.isnan(got2[M - 1]))
+    assert np.all(np.isfinite(got2[:M - 1]))
+
+
 @pytest.mark.parametrize("shape", [(1, 4096, 4096), (8, 1000, 2048), (4, 16, 32), (32, 128, 512), (300, 512, 1024), (24, 2048, 1024)])
 @pytest.mark.parametrize("act", ["none", "relu", "gelu"])
 def test_qdense_w8a32(engine, oracle, shape, act):
     """Quantised dense layer = the reference's ax_qgemm_w8a32 plus the dense layer's bias and activation in one launch
-    (GEMV kernel for M = 1 and small layers, integer tensor-core kernel for 2 <= M <= 64, bf16 GEMM above)."""
+    (GEMV kernel for M = 1 and small layers, integer tensor-core kernel for 2 <= M <= 64, digit planes through the
+    int8 GEMM core above)."""
     M, N, K = shape
     a, w = oracle.uniform((M, K), 7), oracle.uniform((N, K), 13)
     bias = oracle.uniform((N,), 29)
