@@ -158,14 +158,21 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
             mbar_init(bar(KB_CHUNK_EMPTY + b), 128);
         }
         mbar_fence_init();
+        // the first ring of tiles is requested before anything else happens in this CTA (tensor-memory allocation,
+        // the block-wide barrier): the first HBM round trip is the longest wait of the kernel
+        tma_prefetch_desc(&tm.w);
+        tma_prefetch_desc(&tm.x);
+        for (int i = 0; i < nkb && i < KT_STAGES; ++i) {
+            const uint32_t st = stage_addr(i);
+            const int k0 = (kb0 + i) * KT_KB;
+            mbar_arrive_expect_tx(bar(KB_RAW + i), KT_W_BYTES + X_BYTES);
+            tma_load_2d(st, &tm.w, bar(KB_RAW + i), (int32_t)n0, k0);
+            tma_load_3d(st + KT_W_BYTES, &tm.x, bar(KB_RAW + i), k0, 0, 0);
+        }
     }
     if (warp == 1) {
         tmem_alloc(base + 512, 512);
         tmem_relinquish();
-    }
-    if (warp == 0 && lane == 0) {
-        tma_prefetch_desc(&tm.w);
-        tma_prefetch_desc(&tm.x);
     }
     tc_fence_before_sync();
     __syncthreads();
@@ -182,10 +189,10 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
         // ------------------------------------------------------------ producer
         if (lane == 0) {
             KP_DECL(2)
-            for (int i = 0; i < nkb; ++i) {
+            for (int i = KT_STAGES; i < nkb; ++i) {
                 const int s = i % KT_STAGES, n = i / KT_STAGES;
                 KP_ADD(0)
-                if (n >= 1 && !mbar_wait_bounded(bar(KB_EMPTY + s), (n - 1) & 1)) { kt_report(a.err, KERR_PRODUCER); break; }
+                if (!mbar_wait_bounded(bar(KB_EMPTY + s), (n - 1) & 1)) { kt_report(a.err, KERR_PRODUCER); break; }
                 KP_ADD(1)
                 const uint32_t st = stage_addr(s);
                 const int k0 = (kb0 + i) * KT_KB;
