@@ -71,7 +71,9 @@ __host__ __device__ constexpr int qt_stages(int mp)
 // One CTA per activation row: largest magnitude, then the four digit planes digits[j][m][k] and 2^-s.  The row
 // stays in registers between the two steps (up to 16384 elements; longer rows are read again), so the pre-pass
 // costs one trip to memory, a block reduction and the stores.
-static constexpr int QX_THREADS = 1024, QX_CACHE = 4;
+// QX_THREADS x QX_CACHE float4 = 16384 elements stay in registers.  1024 threads: lowest latency for the few rows of
+// the skinny kernel; 256 threads (eight CTAs per SM): one wave for the hundreds of rows of the GEMM route.
+static constexpr int QX_CACHED_F4 = 4096;
 
 __device__ __forceinline__ void qx_emit(uint32_t *dst, size_t plane4, int i, const float4 &v, float s)
 {
@@ -97,9 +99,11 @@ __device__ __forceinline__ float qx_absmax(const float4 &v, bool &bad)
     return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
 }
 
+template <int QX_THREADS>
 __global__ void __launch_bounds__(QX_THREADS) qx_digits_kernel(const float *__restrict__ a, int K, int MP,
                                                                int8_t *__restrict__ digits, float *__restrict__ inv_s)
 {
+    constexpr int QX_CACHE = QX_CACHED_F4 / QX_THREADS;
     __shared__ float wmax[32];
     const int m = blockIdx.x, tid = threadIdx.x;
     if (tid == 0) QP_STAMP(0)
@@ -122,7 +126,7 @@ __global__ void __launch_bounds__(QX_THREADS) qx_digits_kernel(const float *__re
     for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
     if ((tid & 31) == 0) wmax[tid >> 5] = mx;
     __syncthreads();
-    mx = wmax[tid & 31];
+    mx = (tid & 31) < QX_THREADS / 32 ? wmax[tid & 31] : 0.0f;
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
 
@@ -451,7 +455,8 @@ __global__ void __launch_bounds__(256) qx_combine_kernel(const int32_t *__restri
 int launch_qx_digits(const float *act_in, int64_t M, int64_t K, int64_t plane_rows, int8_t *digits, float *inv_s,
                      cudaStream_t st)
 {
-    qx_digits_kernel<<<(unsigned)M, QX_THREADS, 0, st>>>(act_in, (int)K, (int)plane_rows, digits, inv_s);
+    if (M <= 64) qx_digits_kernel<1024><<<(unsigned)M, 1024, 0, st>>>(act_in, (int)K, (int)plane_rows, digits, inv_s);
+    else qx_digits_kernel<256><<<(unsigned)M, 256, 0, st>>>(act_in, (int)K, (int)plane_rows, digits, inv_s);
     return (int)cudaGetLastError();
 }
 
@@ -472,7 +477,7 @@ int launch_qskinny_tc(const float *act_in, const int8_t *q, const float *scales,
     const int mp = M <= 8 ? 8 : M <= 16 ? 16 : M <= 32 ? 32 : 64;
     float *inv_s = reinterpret_cast<float *>(workspace);
     int8_t *digits = reinterpret_cast<int8_t *>(workspace) + 1024;
-    qx_digits_kernel<<<(unsigned)M, QX_THREADS, 0, st>>>(act_in, (int)K, mp, digits, inv_s);
+    qx_digits_kernel<1024><<<(unsigned)M, 1024, 0, st>>>(act_in, (int)K, mp, digits, inv_s);
     int e = (int)cudaGetLastError();
     if (e) return e;
 
