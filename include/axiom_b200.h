@@ -183,13 +183,17 @@ AXB_API int axb_gelu(const float *in, float *out, int64_t n);
 /* ---- quantised GEMM -------------------------------------------------------- */
 /* W8A32: out[M,N] = scales[n] * sum_k a[m,k] * q[n,k], q int8 [N,K], fp32 result.
    Device-pointer form of ax_qgemm_w8a32 (include/axiom/quantize.h:75-79,
-   src/core/quantize.c:100-177); q/scales/N/K are the fields of ax_qweight_t. */
+   src/core/quantize.c:100-177); q/scales/N/K are the fields of ax_qweight_t.
+   M = 1 runs the reference's fp32 multiply-adds in a fixed order.  For M >= 2 (K a multiple of 16 up to 65536,
+   16-byte aligned operands) each activation row is first rounded to a fixed-point grid of 2^-30 of its largest
+   magnitude and the products are exact integer arithmetic on the tensor cores: the result is within 1e-7 of the
+   exact sum and does not depend on summation order; a row that holds an infinity or a NaN comes out as NaN. */
 AXB_API int axb_qgemm_w8a32(const float *a, const int8_t *q, const float *scales, float *out,
                     int64_t M, int64_t N, int64_t K);
 
 /* The quantised dense layer the reference does not have ("raw kernel", docs/EMBEDDED.md:358: callers add bias and
-   activation themselves after ax_qgemm_w8a32): out[m,n] = act(scale[n] * sum_k a[m,k]*q[n,k] + bias[n]) in one
-   launch.  bias may be NULL; act is AXB_ACT_NONE / AXB_ACT_RELU / AXB_ACT_GELU.  axb_qgemm_w8a32 is this entry with
+   activation themselves after ax_qgemm_w8a32): out[m,n] = act(scale[n] * sum_k a[m,k]*q[n,k] + bias[n]), scale,
+   bias and activation applied where the sums are finished (no pass over the output).  bias may be NULL; act is AXB_ACT_NONE / AXB_ACT_RELU / AXB_ACT_GELU.  axb_qgemm_w8a32 is this entry with
    no bias and no activation. */
 AXB_API int axb_qdense_w8a32(const float *a, const int8_t *q, const float *scales, const float *bias, int act,
                              float *out, int64_t M, int64_t N, int64_t K);
