@@ -756,7 +756,10 @@ extern "C" int axb_qdense_w8a32(const float *a, const int8_t *q, const float *sc
     if (M == 0) return AXB_OK;
     // AX_B200_QSKINNY_TC_MIN: smallest M that takes the integer tensor-core kernel (65 turns it off)
     static const int qtc_min = [] { const char *e = getenv("AX_B200_QSKINNY_TC_MIN"); return e ? atoi(e) : 2; }();
-    if (M >= qtc_min && N * K >= (1 << 20) && qskinny_tc_applicable(M, N, K, a, q)) {
+    // a single activation row too once the layer is large: the fp32-FMA GEMV tops out at 3.7 TB/s (instruction issue),
+    // the tensor-core kernel at the memory system's 5.1 TB/s, and from 2^26 weights on that outweighs its second launch
+    const bool tc_route = M >= qtc_min ? N * K >= (1 << 20) : (qtc_min <= 64 && N * K >= (1 << 26));
+    if (tc_route && qskinny_tc_applicable(M, N, K, a, q)) {
         // skinny activations as four int8 digit planes, weights streamed once into kind::i8 MMAs
         st = ensure_ws(qskinny_tc_workspace_bytes(M, K));
         if (st) return st;

@@ -542,6 +542,8 @@ def run_profile_case(args):
             eng.gemm_bias_act(x, Ws[state["i"] % 4], bias, y, M, 4096, 4096, act="gelu")
             state["i"] += 1
     elif case == "qgemv":
+        # the fp32-FMA GEMV itself: at this size a single row would otherwise take the integer tensor-core kernel
+        os.environ["AX_B200_QSKINNY_TC_MIN"] = "65"
         Wq = [torch.randint(-127, 128, (16384, 4096), device="cuda", dtype=torch.int8) for _ in range(4)]
         sc = torch.rand((16384,), device="cuda") * 0.019 + 0.001
         xq, oq = torch.randn((1, 4096), device="cuda"), torch.empty((1, 16384), device="cuda")
