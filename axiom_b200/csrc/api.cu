@@ -231,8 +231,7 @@ int gemm_skinny(const float *X, const float *W, const float *bias, float *Y, int
                 float alpha, float beta, int act)
 {
     // above 8 rows the fp32 pipe, not memory, paces the FMA kernels: the tensor-core variant takes over
-    static const int tc_min = [] { const char *e = getenv("AX_B200_SKINNY_TC_MIN"); return e ? atoi(e) : 9; }();
-    if (M >= tc_min && skinny_tc_applicable(M, N, K, X, W)) {
+    if (M >= 9 && skinny_tc_applicable(M, N, K, X, W)) {
         SkinnyArgs a;
         a.X = X; a.W = W; a.bias = bias; a.Y = Y; a.M = (int)M; a.N = N; a.K = K;
         a.alpha = alpha; a.beta = beta; a.act = act;
@@ -318,8 +317,6 @@ extern "C" int axb_init(int device)
         else if (!strcmp(mode, "bf16x3")) g.fp32_mode = AXB_FP32_BF16X3;
         else if (!strcmp(mode, "3xtf32")) g.fp32_mode = AXB_FP32_3XTF32;
     }
-    if (const char *c = getenv("AX_B200_CHUNK_TF32")) g.chunk_tf32 = atoi(c);
-    if (const char *c = getenv("AX_B200_CHUNK_BF16")) g.chunk_bf16 = atoi(c);
     g.ready = true;
     if (getenv("AX_B200_VERBOSE"))
         fprintf(stderr, "axiom: b200 engine on device %d (%s, %d SMs), fp32 mode %d\n", device, prop.name,
@@ -454,6 +451,26 @@ extern "C" int axb_timing_summary(int *calls, float *prepass_ms_total, float *co
     if (prepass_ms_total) *prepass_ms_total = pre;
     if (core_ms_total) *core_ms_total = core;
     g.ev_count = 0;
+    return AXB_OK;
+}
+
+extern "C" int axb_timing_samples(float *prepass_ms, float *core_ms, int cap, int *n_out)
+{
+    if (!g.profiling) return fail(AXB_ERR_BACKEND, "timing_samples: profiling is off");
+    if (!n_out || cap < 0) return fail(AXB_ERR_NULL_ARG, "timing_samples: NULL");
+    int n = g.ev_count < Engine::EV_RING ? g.ev_count : Engine::EV_RING;
+    if (n > cap) n = cap;
+    for (int i = 0; i < n; ++i) {   // oldest of the kept calls first
+        cudaEvent_t *slot = g.ev[(g.ev_count - n + i) % Engine::EV_RING];
+        cudaError_t e = cudaEventSynchronize(slot[2]);
+        if (e != cudaSuccess) return cuda_fail("timing_samples", e);
+        float a = 0.f, b = 0.f;
+        cudaEventElapsedTime(&a, slot[0], slot[1]);
+        cudaEventElapsedTime(&b, slot[1], slot[2]);
+        if (prepass_ms) prepass_ms[i] = a;
+        if (core_ms) core_ms[i] = b;
+    }
+    *n_out = n;
     return AXB_OK;
 }
 
@@ -716,6 +733,21 @@ extern "C" int axb_bias_add(const float *in, const float *bias, int axis, float 
     return e ? cuda_fail("bias_add", e) : AXB_OK;
 }
 
+extern "C" int axb_bias_add_nd(const float *in, const float *bias, float *out, int64_t outer, int64_t axis_len,
+                               int64_t inner)
+{
+    if (!in || !bias || !out) return fail(AXB_ERR_NULL_ARG, "bias_add: NULL");
+    if (outer < 0 || axis_len < 0 || inner < 0) return fail(AXB_ERR_INVALID_SHAPE, "bias_add: negative dimension");
+    int st = ensure_ready();
+    if (st) return st;
+    // the broadcast axis last: a [outer, axis_len] matrix with one value per column; otherwise
+    // [outer*axis_len, inner] with one value per row, repeating every axis_len rows
+    int e = inner == 1 ? launch_bias_add(in, bias, 1, out, outer, axis_len, g.sm_count, g.stream)
+                       : launch_bias_add(in, bias, 0, out, outer * axis_len, inner, g.sm_count, g.stream, axis_len);
+    g.launches++;
+    return e ? cuda_fail("bias_add", e) : AXB_OK;
+}
+
 extern "C" int axb_relu(const float *in, float *out, int64_t n)
 {
     if (!in || !out) return fail(AXB_ERR_NULL_ARG, "relu: NULL");
@@ -744,6 +776,12 @@ extern "C" int axb_qgemm_w8a32(const float *a, const int8_t *q, const float *sca
     return axb_qdense_w8a32(a, q, scales, nullptr, AXB_ACT_NONE, out, M, N, K);
 }
 
+extern "C" int axb_qgemm_w8a32_qw(const float *a, const axb_qweight_t *qw, float *out, int64_t M)
+{
+    if (!a || !qw || !out || !qw->data || !qw->scales) return fail(AXB_ERR_NULL_ARG, "qgemm_w8a32: NULL");
+    return axb_qdense_w8a32(a, qw->data, qw->scales, nullptr, AXB_ACT_NONE, out, M, qw->N, qw->K);
+}
+
 extern "C" int axb_qdense_w8a32(const float *a, const int8_t *q, const float *scales, const float *bias, int act,
                                 float *out, int64_t M, int64_t N, int64_t K)
 {
@@ -754,11 +792,9 @@ extern "C" int axb_qdense_w8a32(const float *a, const int8_t *q, const float *sc
     int st = ensure_ready();
     if (st) return st;
     if (M == 0) return AXB_OK;
-    // AX_B200_QSKINNY_TC_MIN: smallest M that takes the integer tensor-core kernel (65 turns it off)
-    static const int qtc_min = [] { const char *e = getenv("AX_B200_QSKINNY_TC_MIN"); return e ? atoi(e) : 2; }();
     // a single activation row too once the layer is large: the fp32-FMA GEMV tops out at 3.7 TB/s (instruction issue),
     // the tensor-core kernel at the memory system's 5.1 TB/s, and from 2^26 weights on that outweighs its second launch
-    const bool tc_route = M >= qtc_min ? N * K >= (1 << 20) : (qtc_min <= 64 && N * K >= (1 << 26));
+    const bool tc_route = M >= 2 ? N * K >= (1 << 20) : N * K >= (1 << 26);
     if (tc_route && qskinny_tc_applicable(M, N, K, a, q)) {
         // skinny activations as four int8 digit planes, weights streamed once into kind::i8 MMAs
         st = ensure_ws(qskinny_tc_workspace_bytes(M, K));
@@ -779,9 +815,7 @@ extern "C" int axb_qdense_w8a32(const float *a, const int8_t *q, const float *sc
         g.launches++;
         return e ? cuda_fail("w8a32 gemv", e) : AXB_OK;
     }
-    // AX_B200_QDIGIT_GEMM=0 sends large M through the bf16 route below
-    static const bool digit_gemm = [] { const char *e = getenv("AX_B200_QDIGIT_GEMM"); return !e || atoi(e) != 0; }();
-    if (digit_gemm && K % 16 == 0 && K <= 65536 && 4 * M <= INT32_MAX &&
+    if (K % 16 == 0 && K <= 65536 && 4 * M <= INT32_MAX &&
         ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(q)) & 15) == 0) {
         // activations as four int8 digit planes [4][M][K] = the A operand of one int8 GEMM against the weights as they
         // are; the s32 result [4M, N] is recombined with 64-bit integers (exact), then scale, bias, activation
@@ -929,28 +963,33 @@ extern "C" int axb_sdpa_fwd(const float *Q, const float *K, const float *V, floa
                             int64_t S, int64_t dk, float scale, int causal, float *P_save)
 {
     if (!Q || !K || !V || !out) return fail(AXB_ERR_NULL_ARG, "sdpa_fwd: NULL");
-    if (P_save) return fail(AXB_ERR_NOT_IMPLEMENTED, "sdpa_fwd: P_save is not produced by the fused kernel");
     if (BH < 0 || S < 0 || dk <= 0) return fail(AXB_ERR_INVALID_SHAPE, "sdpa_fwd: bad shape");
     if (dk > 128) return fail(AXB_ERR_NOT_IMPLEMENTED, "sdpa_fwd: head dim %lld > 128", (long long)dk);
     if (BH > 65535 || S > (1 << 24)) return fail(AXB_ERR_INVALID_SHAPE, "sdpa_fwd: BH > 65535 or S too large");
     int st = ensure_ready();
     if (st) return st;
     if (BH == 0 || S == 0) return AXB_OK;
-    static const int route_env = [] { const char *e = getenv("AX_B200_SDPA"); return e ? (strcmp(e, "fma") == 0 ? 1 : 2) : 0; }();
-    if (route_env != 1 && sdpa_tc_applicable(Q, K, V, BH, S, dk, scale)) {
-        mark(0);
-        mark(1);
-        int e = launch_sdpa_tc(Q, K, V, out, L, BH, S, dk, scale, causal, g.err_word, g.stream);
-        mark(2);
-        g.launches++;
-        return e ? cuda_fail("sdpa_fwd", e) : AXB_OK;
+    // the probabilities a caller wants kept are written after the fused pass from its log-sum-exp: O and L never
+    // depend on them, and a caller that ignores the status (src/core/attention.c:335-342) still gets its output
+    if (P_save && !L) {
+        st = ensure_ws((size_t)BH * S * sizeof(float));
+        if (st) return st;
+        L = (float *)g.ws;
     }
     mark(0);
     mark(1);
-    int e = launch_sdpa_fwd(Q, K, V, out, L, BH, S, dk, scale, causal, g.stream);
+    int e;
+    if (sdpa_tc_applicable(Q, K, V, BH, S, dk, scale)) e = launch_sdpa_tc(Q, K, V, out, L, BH, S, dk, scale, causal, g.err_word, g.stream);
+    else e = launch_sdpa_fwd(Q, K, V, out, L, BH, S, dk, scale, causal, g.stream);
     mark(2);
     g.launches++;
-    return e ? cuda_fail("sdpa_fwd", e) : AXB_OK;
+    if (e) return cuda_fail("sdpa_fwd", e);
+    if (P_save) {
+        e = launch_sdpa_probs(Q, K, L, P_save, BH, S, dk, scale, causal, g.stream);
+        g.launches++;
+        if (e) return cuda_fail("sdpa_fwd: saved probabilities", e);
+    }
+    return AXB_OK;
 }
 
 extern "C" int axb_sdpa_bwd(const float *Q, const float *K, const float *V, const float *O, const float *dO,
@@ -1089,7 +1128,88 @@ extern "C" int axb_qkv_head_gemm(const float *X, const float *Wqkv, const float 
     }
     st = axb_gemm_bias_act(X, Wqkv, bqkv, (float *)g.aux, rows, 3 * D, D, 0, 0, 1.0f, 0.0f, AXB_ACT_NONE);
     if (st) return st;
-    int e = launch_head_split((const float *)g.aux, Qh, Kh, Vh, rows, S, H, dk, g.sm_count, g.stream);
+    int e = launch_head_layout(true, (float *)g.aux, outs, nullptr, 3, B, S, H, dk, g.sm_count, g.stream);
     g.launches++;
     return e ? cuda_fail("qkv_head_gemm: head split", e) : AXB_OK;
+}
+
+// ------------------------------------------------------- attention layout passes
+
+static int head_layout_call(const char *what, bool to_head, const float *flat, float *const head[3], const float *bias,
+                            int nslot, int64_t B, int64_t S, int64_t H, int64_t dk)
+{
+    if (!flat) return fail(AXB_ERR_NULL_ARG, "%s: NULL", what);
+    for (int i = 0; i < nslot; ++i)
+        if (!head[i]) return fail(AXB_ERR_NULL_ARG, "%s: NULL", what);
+    if (B < 0 || S < 0 || H <= 0 || dk <= 0) return fail(AXB_ERR_INVALID_SHAPE, "%s: bad shape", what);
+    if (S > INT32_MAX || H > INT32_MAX || dk > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "%s: dimension exceeds 2^31-1", what);
+    int st = ensure_ready();
+    if (st) return st;
+    int e = launch_head_layout(to_head, const_cast<float *>(flat), head, bias, nslot, B, S, H, dk, g.sm_count, g.stream);
+    g.launches++;
+    return e ? cuda_fail(what, e) : AXB_OK;
+}
+
+extern "C" int axb_head_interleave_qkv_split(const float *qkv, const float *bqkv, float *Qh, float *Kh, float *Vh,
+                                             int64_t B, int64_t S, int64_t H, int64_t dk)
+{
+    float *head[3] = { Qh, Kh, Vh };
+    return head_layout_call("head_interleave_qkv_split", true, qkv, head, bqkv, 3, B, S, H, dk);
+}
+
+extern "C" int axb_head_interleave(const float *src, float *dst, int64_t B, int64_t S, int64_t H, int64_t dk)
+{
+    float *head[3] = { dst, nullptr, nullptr };
+    return head_layout_call("head_interleave", true, src, head, nullptr, 1, B, S, H, dk);
+}
+
+extern "C" int axb_head_deinterleave(const float *src, float *dst, int64_t B, int64_t S, int64_t H, int64_t dk)
+{
+    float *head[3] = { const_cast<float *>(src), nullptr, nullptr };
+    return head_layout_call("head_deinterleave", false, dst, head, nullptr, 1, B, S, H, dk);
+}
+
+extern "C" int axb_head_deinterleave_qkv_merge(const float *dQ, const float *dK, const float *dV, float *dst, int64_t B,
+                                               int64_t S, int64_t H, int64_t dk)
+{
+    float *head[3] = { const_cast<float *>(dQ), const_cast<float *>(dK), const_cast<float *>(dV) };
+    return head_layout_call("head_deinterleave_qkv_merge", false, dst, head, nullptr, 3, B, S, H, dk);
+}
+
+// dst[rows, 3*cols] = [a | b | c] row by row (rows = cols = D for the weights; rows = 1 for the biases)
+static int concat3(const char *what, float *dst, const float *a, const float *b, const float *c, int64_t rows, int64_t cols)
+{
+    if (!dst || !a || !b || !c) return fail(AXB_ERR_NULL_ARG, "%s: NULL", what);
+    if (rows < 0 || cols < 0) return fail(AXB_ERR_INVALID_SHAPE, "%s: bad shape", what);
+    int st = ensure_ready();
+    if (st) return st;
+    if (rows == 0 || cols == 0) return AXB_OK;
+    const size_t w = (size_t)cols * sizeof(float);
+    const float *src[3] = { a, b, c };
+    for (int i = 0; i < 3; ++i) {
+        cudaError_t e = cudaMemcpy2DAsync(dst + i * cols, 3 * w, src[i], w, w, (size_t)rows, cudaMemcpyDeviceToDevice, g.stream);
+        if (e != cudaSuccess) return cuda_fail(what, e);
+    }
+    return AXB_OK;
+}
+
+extern "C" int axb_qkv_cache_build(float *dst, const float *wq, const float *wk, const float *wv, int64_t D)
+{
+    return concat3("qkv_cache_build", dst, wq, wk, wv, D, D);
+}
+
+extern "C" int axb_bias_cache_build(float *dst, const float *bq, const float *bk, const float *bv, int64_t D)
+{
+    return concat3("bias_cache_build", dst, bq, bk, bv, 1, D);
+}
+
+extern "C" int axb_pointer_on_device(const void *p)
+{
+    if (!p) return 0;
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return (at.type == cudaMemoryTypeDevice || at.type == cudaMemoryTypeManaged) ? 1 : 0;
 }

@@ -31,9 +31,11 @@ __global__ void __launch_bounds__(256) unary_kernel(const float *__restrict__ in
     }
 }
 
-// out[i,j] = in[i,j] + bias[axis == 0 ? i : j]; in-place safe (each element read then written by one thread)
+// out[i,j] = in[i,j] + bias[axis == 0 ? i % period : j]; in-place safe (each element read then written by one
+// thread).  period < M serves a broadcast axis in the middle of an n-d tensor viewed as [outer*axis_len, inner].
 __global__ void __launch_bounds__(256) bias_add_kernel(const float *in, const float *__restrict__ bias,
-                                                       int axis, float *out, int64_t M, int64_t N, bool vec)
+                                                       int axis, float *out, int64_t M, int64_t N, int64_t period,
+                                                       bool vec)
 {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -43,7 +45,7 @@ __global__ void __launch_bounds__(256) bias_add_kernel(const float *in, const fl
             const int64_t r = i / n4, c = (i - r * n4) * 4;
             float4 v = reinterpret_cast<const float4 *>(in)[i];
             if (axis == 0) {
-                const float b = __ldg(bias + r);
+                const float b = __ldg(bias + r % period);
                 v.x += b; v.y += b; v.z += b; v.w += b;
             } else {
                 const float4 b = __ldg(reinterpret_cast<const float4 *>(bias + c));
@@ -54,7 +56,7 @@ __global__ void __launch_bounds__(256) bias_add_kernel(const float *in, const fl
     } else {
         for (int64_t i = t; i < M * N; i += stride) {
             const int64_t r = i / N, c = i - r * N;
-            out[i] = in[i] + __ldg(bias + (axis == 0 ? r : c));
+            out[i] = in[i] + __ldg(bias + (axis == 0 ? r % period : c));
         }
     }
 }
@@ -80,41 +82,13 @@ int launch_unary(int op, const float *in, float *out, int64_t n, int sm_count, c
 }
 
 int launch_bias_add(const float *in, const float *bias, int axis, float *out, int64_t M, int64_t N,
-                    int sm_count, cudaStream_t st)
+                    int sm_count, cudaStream_t st, int64_t period)
 {
     if (M <= 0 || N <= 0) return 0;
+    if (period <= 0) period = M;
     const bool vec = (N % 4 == 0) && aligned16(in) && aligned16(out) && aligned16(bias);
     const int g = ew_grid(vec ? M * N / 4 : M * N, sm_count);
-    bias_add_kernel<<<g, 256, 0, st>>>(in, bias, axis, out, M, N, vec);
-    return (int)cudaGetLastError();
-}
-
-// qkv [rows = B*S, 3*H*dk] -> Qh, Kh, Vh [B*H, S, dk] (ax_attn_head_interleave_qkv_split,
-// src/compute/backends/cuda/ops_attention.cu:74-137 in the reference): the layout pass for shapes the GEMM
-// epilogue does not scatter itself.
-__global__ void __launch_bounds__(256) head_split_kernel(const float *__restrict__ qkv, float *Qh, float *Kh, float *Vh,
-                                                         int64_t rows, int S, int H, int dk)
-{
-    const int64_t D = (int64_t)H * dk, total = rows * 3 * D;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t row = i / (3 * D), col = i - row * 3 * D;
-        const int which = (int)(col / D);
-        const int64_t rem = col - which * D;
-        const int h = (int)(rem / dk), d = (int)(rem - (int64_t)h * dk);
-        const int64_t b = row / S, s = row - b * S;
-        float *dst = which == 0 ? Qh : (which == 1 ? Kh : Vh);
-        dst[((b * H + h) * S + s) * dk + d] = qkv[i];
-    }
-}
-
-int launch_head_split(const float *qkv, float *Qh, float *Kh, float *Vh, int64_t rows, int64_t S, int64_t H, int64_t dk,
-                      int sm_count, cudaStream_t st)
-{
-    const int64_t total = rows * 3 * H * dk;
-    if (total <= 0) return 0;
-    int64_t blocks = (total + 255) / 256;
-    if (blocks > (int64_t)sm_count * 16) blocks = (int64_t)sm_count * 16;
-    head_split_kernel<<<(unsigned)blocks, 256, 0, st>>>(qkv, Qh, Kh, Vh, rows, (int)S, (int)H, (int)dk);
+    bias_add_kernel<<<g, 256, 0, st>>>(in, bias, axis, out, M, N, period, vec);
     return (int)cudaGetLastError();
 }
 

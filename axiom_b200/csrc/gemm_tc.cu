@@ -29,6 +29,7 @@
 
 #include <cuda.h>
 #include <stdio.h>
+#include "errors.cuh"
 #include <stdlib.h>
 #include <string.h>
 
@@ -479,8 +480,6 @@ static int launch_inst(const TmapPack &tm, KernelArgs &ka, int stage_bytes, int 
     constexpr int STAGING = KIND == KIND_I8 ? 0 : EPI_STAGING_BYTES;
     int stages = (SMEM_BUDGET - HEADER_BYTES - 1024 - STAGING) / stage_bytes;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
-    static const int stages_env = [] { const char *e = getenv("AX_B200_STAGES"); return e ? atoi(e) : 0; }();
-    if (stages_env >= 2 && stages_env < stages) stages = stages_env;
     if (stages < 2) {
         snprintf(g_err, sizeof g_err, "stage of %d bytes leaves fewer than 2 pipeline stages", stage_bytes);
         return (int)cudaErrorInvalidConfiguration;
@@ -488,14 +487,13 @@ static int launch_inst(const TmapPack &tm, KernelArgs &ka, int stage_bytes, int 
     ka.stages = stages;
     const int smem = HEADER_BYTES + 1024 + stages * stage_bytes + STAGING;
     auto kern = gemm_tc_kernel<KIND, BN, SWB, NPROD>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce once;
+    if (once.first()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET);
         if (e != cudaSuccess) {
             snprintf(g_err, sizeof g_err, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
             return (int)e;
         }
-        attr_set = true;
     }
     kern<<<grid, NUM_THREADS, smem, stream>>>(tm, ka);
     cudaError_t e = cudaGetLastError();
@@ -534,25 +532,18 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
     if (bn == 128 && mt * ((N + 127) / 128) * 2 < sm_count) bn = 64;
     if (N <= 64) bn = 64;
     else if (N <= 128 && bn > 128) bn = 128;
-    static const int bn_env = [] { const char *e = getenv("AX_B200_BN"); return e ? atoi(e) : 0; }();
-    if (bn_env == 64 || bn_env == 128 || bn_env == 256) bn = bn_env;
     // CTA pairs (256 x 256 tiles, gemm_tc2.cu) when there are enough such tiles to fill the machine
-    static const int pair_env = [] { const char *e = getenv("AX_B200_PAIR"); return e ? atoi(e) : -1; }();
-    bool use_pair = ((M + 255) / 256) * ((N + 255) / 256) >= sm_count / 2 && N >= 256 && M >= 256;
-    if (pair_env == 0) use_pair = false;
-    if (pair_env == 1 && N >= 256 && M >= 256) use_pair = true;
+    const bool use_pair = ((M + 255) / 256) * ((N + 255) / 256) >= sm_count / 2 && N >= 256 && M >= 256;
     if (use_pair) {
         bn = 256;
         mt = (M + 255) / 256;
     }
     const int64_t nt = (N + bn - 1) / bn;
     const int planes = A.nplanes + B.nplanes;
-    static const int swb_env = [] { const char *e = getenv("AX_B200_SWB"); return e ? atoi(e) : 0; }();
     // 128-byte rows everywhere (fewer, larger stages: half the TMA and barrier traffic per unit of K) except
     // for the split-precision modes on single-CTA 128 x 256 tiles, where four operand planes of 128-byte rows
     // would leave a two-stage ring: those take 64-byte rows and keep four stages.
-    int swb = (kind != KIND_I8 && prod.n > 1 && !use_pair && bn == 256) ? 64 : 128;
-    if (swb_env == 128 || (swb_env == 64 && kind != KIND_I8 && prod.n > 1)) swb = swb_env;
+    const int swb = (kind != KIND_I8 && prod.n > 1 && !use_pair && bn == 256) ? 64 : 128;
     (void)planes;
     const int es = kind == KIND_TF32 ? 4 : (kind == KIND_BF16 ? 2 : 1);
     const int bke = swb / es;
@@ -597,12 +588,9 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
     // plain aligned fp32 output that is not read back: the staging tiles leave through TMA stores
     if (kind != KIND_I8 && ep.out_mode == OUT_F32 && ep.hs_dk == 0 && ka.n_extra == 0 && ep.beta == 0.0f && ep.C &&
         (reinterpret_cast<uintptr_t>(ep.C) & 15) == 0 && ep.ldc % 4 == 0) {
-        static const bool off = getenv("AX_B200_NO_TMA_STORE") != nullptr;
-        if (!off) {
-            int e = encode_f32_store_tmap(&tm.c, reinterpret_cast<float *>(ep.C), M, N, ep.ldc);
-            if (e) return e;
-            ka.tma_store = 1;
-        }
+        int e = encode_f32_store_tmap(&tm.c, reinterpret_cast<float *>(ep.C), M, N, ep.ldc);
+        if (e) return e;
+        ka.tma_store = 1;
     }
     const int64_t tiles = mt * nt;
     const int grid = (int)(tiles < sm_count ? tiles : sm_count);

@@ -18,6 +18,7 @@
 // No multicast copies are used: every CTA fetches its own operand tiles.
 #include "gemm_tc.cuh"
 #include "gemm_tc_internal.cuh"
+#include "errors.cuh"
 #include "ptx.cuh"
 
 #include <cuda.h>
@@ -25,20 +26,9 @@
 
 namespace axb {
 
-#ifdef AXB_GEMM_PROF
-__device__ unsigned long long g_gemm_prof[32];
-#define GP_DECL(n) long long prof_t[n] = {}; long long prof_c = clock64();
-#define GP_ADD(i) { const long long t_ = clock64(); prof_t[i] += t_ - prof_c; prof_c = t_; }
-#define GP_OUT(base, n) { for (int i_ = 0; i_ < n; ++i_) g_gemm_prof[base + i_] = (unsigned long long)prof_t[i_]; }
-extern "C" __attribute__((visibility("default"))) int axb_debug_gemm_prof(unsigned long long *out)
-{
-    return (int)cudaMemcpyFromSymbol(out, g_gemm_prof, sizeof(unsigned long long) * 32);
-}
-#else
 #define GP_DECL(n)
 #define GP_ADD(i)
 #define GP_OUT(base, n) {}
-#endif
 
 
 static constexpr int PAIR_BN = 256;
@@ -355,18 +345,18 @@ static int launch_pair_inst(const TmapPack &tm, KernelArgs &ka, int npa, int npb
     ka.stages = stages;
     const int smem = HEADER_BYTES + 1024 + stages * stage_bytes + STAGING;
     auto kern = gemm_tc_pair_kernel<KIND, SWB, NPROD>;
-    static bool attr_set = false;
-    if (!attr_set) {
+    static PerDeviceOnce once;
+    static int resident_pairs_dev[64] = {};
+    if (once.first()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET);
         if (e != cudaSuccess) {
             snprintf(err, err_len, "pair kernel: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
             return (int)e;
         }
-        attr_set = true;
     }
+    int &resident_pairs = resident_pairs_dev[once.device()];
     // how many CTA pairs the device can hold at once (an SM without a free partner in its
     // cluster-scheduling group cannot host half a pair): persistent grid = that many pairs
-    static int resident_pairs = 0;
     if (resident_pairs == 0) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)(sm_count / 2 * 2));

@@ -49,17 +49,7 @@ struct QtArgs {
 
 enum { QERR_PRODUCER = 31, QERR_MMA = 32, QERR_DRAIN = 33 };
 
-#ifdef AXB_QTC_PROF
-// wall-clock stamps (ns) of CTA (0,0) of both kernels, for a profiling build only
-__device__ unsigned long long g_qtc_prof[16];
-#define QP_STAMP(i) { if (blockIdx.x == 0 && blockIdx.y == 0) g_qtc_prof[i] = global_timer_ns(); }
-extern "C" __attribute__((visibility("default"))) int axb_debug_qtc_prof(unsigned long long *out)
-{
-    return (int)cudaMemcpyFromSymbol(out, g_qtc_prof, sizeof(unsigned long long) * 16);
-}
-#else
 #define QP_STAMP(i) {}
-#endif
 
 __host__ __device__ constexpr int qt_stages(int mp)
 {

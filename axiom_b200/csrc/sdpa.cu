@@ -9,6 +9,7 @@
 // restatement to ~1e-6, which the bf16 tensor-core route cannot do without
 // operand splitting.
 #include "sdpa.cuh"
+#include "errors.cuh"
 
 #include <math.h>
 #include <stdint.h>
@@ -224,21 +225,77 @@ int launch_sdpa_fwd(const float *Q, const float *K, const float *V, float *O, fl
     dim3 grid((unsigned)((S + BQ - 1) / BQ), (unsigned)BH);
     if (dk <= 64) {
         const size_t smem = (size_t)(BQ * 64 + 64 * BKV + BKV * 64 + BQ * PS_PITCH) * 4;
-        static bool attr64 = false;
-        if (!attr64) {
-            cudaFuncSetAttribute(sdpa_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            attr64 = true;
-        }
+        static PerDeviceOnce once64;
+        if (once64.first()) cudaFuncSetAttribute(sdpa_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         sdpa_fwd_kernel<64><<<grid, SD_THREADS, smem, st>>>(Q, K, V, O, L, (int)S, (int)dk, scale, causal);
     } else {
         const size_t smem = (size_t)(BQ * 128 + 128 * BKV + BKV * 128 + BQ * PS_PITCH) * 4;
-        static bool attr128 = false;
-        if (!attr128) {
-            cudaFuncSetAttribute(sdpa_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            attr128 = true;
-        }
+        static PerDeviceOnce once128;
+        if (once128.first()) cudaFuncSetAttribute(sdpa_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         sdpa_fwd_kernel<128><<<grid, SD_THREADS, smem, st>>>(Q, K, V, O, L, (int)S, (int)dk, scale, causal);
     }
+    return (int)cudaGetLastError();
+}
+
+// P[bh,i,j] = exp(scale * q_i.k_j - L[bh,i]) (0 above the diagonal when causal): the soft-max probabilities the
+// stock backend copies into P_save out of its score buffer (src/compute/backends/cuda/ops_attention.cu:366-370).
+// The fused forward never forms them, so a caller that passes P_save gets them from this pass, after L is known.
+// One CTA per 64x64 tile, fp32 FMA over dk in chunks of 32; tiles wholly above the diagonal are only cleared.
+__global__ void __launch_bounds__(256) sdpa_probs_kernel(const float *__restrict__ Q, const float *__restrict__ K,
+                                                         const float *__restrict__ L, float *__restrict__ P, int S,
+                                                         int dk, float scale, int causal)
+{
+    __shared__ float Qs[64][33], Ks[64][33];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    const int j0 = blockIdx.x * 64, i0 = blockIdx.y * 64;
+    const int64_t head = blockIdx.z;
+    const float *Qh = Q + head * (int64_t)S * dk, *Kh = K + head * (int64_t)S * dk;
+    float *Ph = P + head * (int64_t)S * S;
+    float acc[4][4] = {};
+    const bool dead = causal && j0 > i0 + 63;
+    if (!dead) {
+        for (int k0 = 0; k0 < dk; k0 += 32) {
+            for (int e = tid; e < 64 * 32; e += 256) {
+                const int r = e >> 5, c = e & 31;
+                Qs[r][c] = (i0 + r < S && k0 + c < dk) ? __ldg(Qh + (int64_t)(i0 + r) * dk + k0 + c) : 0.0f;
+                Ks[r][c] = (j0 + r < S && k0 + c < dk) ? __ldg(Kh + (int64_t)(j0 + r) * dk + k0 + c) : 0.0f;
+            }
+            __syncthreads();
+#pragma unroll 8
+            for (int k = 0; k < 32; ++k) {
+                float q[4], kk[4];
+#pragma unroll
+                for (int a = 0; a < 4; ++a) q[a] = Qs[ty * 4 + a][k];
+#pragma unroll
+                for (int b = 0; b < 4; ++b) kk[b] = Ks[tx + 16 * b][k];
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(q[a], kk[b], acc[a][b]);
+            }
+            __syncthreads();
+        }
+    }
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int i = i0 + ty * 4 + a;
+        if (i >= S) continue;
+        const float l = dead ? 0.0f : __ldg(L + head * (int64_t)S + i);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+            const int j = j0 + tx + 16 * b;
+            if (j >= S) continue;
+            Ph[(int64_t)i * S + j] = (dead || (causal && j > i)) ? 0.0f : expf(acc[a][b] * scale - l);
+        }
+    }
+}
+
+int launch_sdpa_probs(const float *Q, const float *K, const float *L, float *P, int64_t BH, int64_t S, int64_t dk,
+                      float scale, int causal, cudaStream_t st)
+{
+    if (BH <= 0 || S <= 0) return 0;
+    const unsigned t = (unsigned)((S + 63) / 64);
+    sdpa_probs_kernel<<<dim3(t, t, (unsigned)BH), 256, 0, st>>>(Q, K, L, P, (int)S, (int)dk, scale, causal);
     return (int)cudaGetLastError();
 }
 

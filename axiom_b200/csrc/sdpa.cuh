@@ -8,6 +8,10 @@ namespace axb {
 int launch_sdpa_fwd(const float *Q, const float *K, const float *V, float *O, float *L, int64_t BH,
                     int64_t S, int64_t dk, float scale, int causal, cudaStream_t st);
 
+// P[BH,S,S] = exp(scale*Q.K^T - L), 0 above the diagonal when causal (the probabilities a caller may ask to keep).
+int launch_sdpa_probs(const float *Q, const float *K, const float *L, float *P, int64_t BH, int64_t S, int64_t dk,
+                      float scale, int causal, cudaStream_t st);
+
 // Backward (sdpa_bwd.cu): dQ, dK, dV are overwritten; workspace holds BH*S floats (sdpa_bwd_workspace_bytes).
 size_t sdpa_bwd_workspace_bytes(int64_t BH, int64_t S);
 int launch_sdpa_bwd(const float *Q, const float *K, const float *V, const float *O, const float *dO, const float *L,

@@ -73,16 +73,6 @@ enum {
 // TMEM columns: two score buffers (P hi is written over the scores), P lo, two output buffers
 enum { T_S = 0, T_PLO = 256, T_O = 384, T_COLS = 512 };
 
-#ifdef AXB_SDPA_PROF
-__device__ unsigned long long g_sdpa_prof[32];
-#define PROF_DECL(n) long long prof_t[n] = {}; long long prof_c = clock64(); const bool prof_on = blockIdx.x == 0 && blockIdx.y == 0;
-#define PROF_ADD(i) { const long long t_ = clock64(); prof_t[i] += t_ - prof_c; prof_c = t_; }
-#define PROF_OUT(base, n) if (prof_on) { for (int i_ = 0; i_ < n; ++i_) g_sdpa_prof[base + i_] = (unsigned long long)prof_t[i_]; }
-#else
-#define PROF_DECL(n)
-#define PROF_ADD(i)
-#define PROF_OUT(base, n)
-#endif
 
 __device__ __forceinline__ bool wait_warp(uint32_t bar, uint32_t parity)
 {
@@ -337,40 +327,29 @@ __global__ void __launch_bounds__(ST_THREADS, 1) sdpa_tc_kernel(const __grid_con
                 tc_commit(bar(B_O_FULL + b));
                 tc_commit(bar(B_V_EMPTY));
             };
-
-            PROF_DECL(8)
             bool ok = mbar_wait_bounded(bar(B_Q_FULL), 0) && mbar_wait_bounded(bar(B_K_FULL), 0);
-            PROF_ADD(0)
             if (ok) {
                 tc_fence_after_sync();
                 issue_qk(0);
             }
-            PROF_ADD(1)
             for (int j = 0; ok && j < nb; ++j) {
                 if (j + 1 < nb) {
                     // the score buffer of block j+1 held P hi of block j-1: its P.V was issued before this
                     // point and MMAs execute in order, so nothing else has to be waited for
                     ok = mbar_wait_bounded(bar(B_K_FULL), (j + 1) & 1);
-                    PROF_ADD(2)
                     if (!ok) break;
                     tc_fence_after_sync();
                     issue_qk(j + 1);
-                    PROF_ADD(1)
                 }
                 const int b = j & 1, n = j >> 1;
                 ok = mbar_wait_bounded(bar(B_P_FULL + b), n & 1);
-                PROF_ADD(4)
                 ok = ok && mbar_wait_bounded(bar(B_V_FULL), j & 1);
-                PROF_ADD(5)
                 ok = ok && (j < 2 || mbar_wait_bounded(bar(B_O_EMPTY + b), (n - 1) & 1));
-                PROF_ADD(6)
                 if (!ok) break;
                 tc_fence_after_sync();
                 issue_pv(j);
-                PROF_ADD(7)
             }
             if (!ok) report_err(a.err, SERR_MMA);
-            PROF_OUT(0, 8)
         }
     } else {
         // ------------------------------------------------------- softmax warps
@@ -395,12 +374,9 @@ __global__ void __launch_bounds__(ST_THREADS, 1) sdpa_tc_kernel(const __grid_con
 #pragma unroll
             for (int c = 0; c < OW; ++c) o[c] = (o[c] + __uint_as_float(r[c >> 5][c & 31])) * corr;
         };
-
-        PROF_DECL(8)
         for (int j = 0; j < nb; ++j) {
             const int b = j & 1, n = j >> 1;
             if (!wait_warp(bar(B_S_FULL + b), n & 1)) { ok = false; break; }
-            PROF_ADD(0)
             tc_fence_after_sync();
             const uint32_t s_addr = lane_base + T_S + b * TKV;
             const int k0 = j * TKV;
@@ -410,29 +386,23 @@ __global__ void __launch_bounds__(ST_THREADS, 1) sdpa_tc_kernel(const __grid_con
             const float m_new = fmaxf(m, mx * a.c_log2);
             const float m_safe = (m_new == -INFINITY) ? 0.f : m_new;
             const float corr = ex2_approx(m - m_safe);  // 0 on the first block
-            PROF_ADD(1)
             const float sum = need_mask ? row_exp<true>(s_addr, a.c_log2, -m_safe, k0, gi, a.S, a.causal)
                                         : row_exp<false>(s_addr, a.c_log2, -m_safe, k0, gi, a.S, a.causal);
-            PROF_ADD(2)
             // P lo is a single buffer: the previous block's P.V must have finished reading it.  Only this
             // short pass sits between that P.V and the next one; the exponentials above overlap it.
             if (j > 0 && !wait_warp(bar(B_O_FULL + ((j - 1) & 1)), ((j - 1) >> 1) & 1)) { ok = false; break; }
-            PROF_ADD(3)
             row_lo(s_addr, lane_base + T_PLO);
             tc_fence_before_sync();
             mbar_arrive(bar(B_P_FULL + b));
             l = l * corr + sum;
             m = m_new;
-            PROF_ADD(4)
             if (j > 0) fold(j - 1, corr);
-            PROF_ADD(5)
         }
         if (ok && nb > 0) {
             if (wait_warp(bar(B_O_FULL + ((nb - 1) & 1)), ((nb - 1) >> 1) & 1)) fold(nb - 1, 1.0f);
             else ok = false;
         }
         if (!ok) report_err(a.err, SERR_SOFTMAX);
-        if (threadIdx.x == 0) { PROF_OUT(8, 8) }
 
         if (ok && gi < a.S) {
             const float inv = l > 0.f ? 1.0f / l : 0.f;
@@ -462,12 +432,6 @@ __global__ void __launch_bounds__(ST_THREADS, 1) sdpa_tc_kernel(const __grid_con
 
 // ---------------------------------------------------------------------- host
 
-#ifdef AXB_SDPA_PROF
-extern "C" __attribute__((visibility("default"))) int axb_debug_sdpa_prof(unsigned long long *out)
-{
-    return (int)cudaMemcpyFromSymbol(out, g_sdpa_prof, sizeof(unsigned long long) * 32);
-}
-#endif
 
 bool sdpa_tc_applicable(const float *Q, const float *K, const float *V, int64_t BH, int64_t S, int64_t dk,
                         float scale)

@@ -176,10 +176,7 @@ static int mt_for(int64_t M) { return M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : M <
 static void skinny_plan_tma(int64_t M, int64_t N, int64_t K, int sm_count, SkinnyPlan *plan)
 {
     const int mt = mt_for(M);
-    static const int env_ctas = [] { const char *e = getenv("AX_B200_SK_CTAS_PER_SM"); return e ? atoi(e) : 0; }();
-    static const int env_stages = [] { const char *e = getenv("AX_B200_SK_STAGES"); return e ? atoi(e) : 0; }();
-    static const int env_cluster = [] { const char *e = getenv("AX_B200_SK_CLUSTER"); return e ? atoi(e) : -1; }();
-    const int stages = env_stages >= 2 && env_stages <= 8 ? env_stages : 4;
+    const int stages = 4;
     plan->use_tma = 1;
     plan->mt = mt;
     plan->stages = stages;
@@ -194,7 +191,7 @@ static void skinny_plan_tma(int64_t M, int64_t N, int64_t K, int sm_count, Skinn
         const bool fits = kchunk * mt * 4 <= 64 * 1024 && kchunk >= 128;
         const bool fills = (int64_t)strips * ksplit >= sm_count;
         // (M > 8 holds one CTA per SM for its registers: a 256-CTA cluster grid would run in two waves)
-        if (env_cluster != 0 && mt <= 8 && ksplit >= 2 && ksplit <= 8 && fits && (fills || env_cluster == 1)) {
+        if (mt <= 8 && ksplit >= 2 && ksplit <= 8 && fits && fills) {
             plan->cluster = 1;
             plan->strips = strips;
             plan->ksplit = (int)ksplit;
@@ -207,7 +204,7 @@ static void skinny_plan_tma(int64_t M, int64_t N, int64_t K, int sm_count, Skinn
     plan->cluster = 0;
     const int cols = skinny_tma_strip_cols(mt, 0), rows = skinny_tma_stage_rows(mt, 0);
     const int strips = (int)((N + cols - 1) / cols);
-    const int ctas_per_sm = env_ctas > 0 ? env_ctas : 2;
+    const int ctas_per_sm = 2;
     int64_t ksplit = (ctas_per_sm * (int64_t)sm_count) / strips;
     if (ksplit < 1) ksplit = 1;
     const int64_t max_split = (K + 4 * rows - 1) / (4 * rows);  // at least one trip round the ring
@@ -280,12 +277,13 @@ int launch_skinny(const SkinnyArgs &args, const SkinnyPlan &plan, cudaStream_t s
 namespace {
 
 constexpr int64_t kStaticPartialFloats = (int64_t)1 << 20;   // 4 MiB of split-K partial sums
-constexpr int kStaticCounters = 1024;                        // one arrival counter per 128-column strip
+constexpr int kStaticCounters = 1023;                        // one arrival counter per 128-column strip
+constexpr int kStaticWords = kStaticCounters + 1;            // ... and, after them, the word a timed-out wait reports in
 constexpr int kMaxDevices = 64;
 
 // In host code this name is only a handle for cudaGetSymbolAddress; the device
 // address it stands for differs per GPU and is looked up once per device below.
-static __device__ __align__(256) float g_static_scratch[kStaticPartialFloats + kStaticCounters];
+static __device__ __align__(256) float g_static_scratch[kStaticPartialFloats + kStaticWords];
 
 static float *s_scratch_addr[kMaxDevices];   // device address of g_static_scratch, per device ordinal
 static int s_sm_count[kMaxDevices];
@@ -317,8 +315,28 @@ extern "C" int axb_skinny_gemm_static(const float *X, const float *W, const floa
         e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
         if (e != cudaSuccess || sms <= 0)
             return set_error(AXB_ERR_BACKEND, "skinny_gemm_static: cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
+        // the word a timed-out wait reports in starts at zero (the image initialises the array to zero; a previous
+        // process cannot have touched this context's copy, so this is belt and braces)
+        e = cudaMemset(static_cast<float *>(addr) + kStaticPartialFloats + kStaticCounters, 0, sizeof(int));
+        if (e != cudaSuccess) return set_error(AXB_ERR_BACKEND, "skinny_gemm_static: cudaMemset: %s", cudaGetErrorString(e));
         s_sm_count[dev] = sms;
         s_scratch_addr[dev] = static_cast<float *>(addr);
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+    float *scratch = s_scratch_addr[dev];
+    int *counters = reinterpret_cast<int *>(scratch + kStaticPartialFloats);
+    int *err_word = counters + kStaticCounters;
+    SkinnyArgs a;
+    a.X = X; a.W = W; a.bias = bias; a.Y = Y; a.M = (int)M; a.N = N; a.K = K;
+    a.alpha = alpha; a.beta = beta; a.act = act;
+    a.err = err_word;
+    // the same choice of kernel as the skinny route of axb_gemm_bias_act: above 8 rows the tensor-core kernel,
+    // which reduces inside its clusters and needs no scratch at all
+    if (M >= 9 && skinny_tc_applicable(M, N, K, X, W)) {
+        a.ksplit = 0; a.kchunk = 0; a.stages = 0; a.cluster = 0; a.partial = nullptr; a.counters = nullptr;
+        int le = launch_skinny_tc(a, s_sm_count[dev], st);
+        if (le) return set_error(AXB_ERR_BACKEND, "skinny_gemm_static: launch: %s", cudaGetErrorString((cudaError_t)le));
+        return AXB_OK;
     }
     SkinnyPlan plan;
     skinny_plan(M, N, K, W, s_sm_count[dev], &plan);
@@ -328,21 +346,28 @@ extern "C" int axb_skinny_gemm_static(const float *X, const float *W, const floa
                          "scratch holds %lld and %d (use axb_gemm_bias_act, which allocates)",
                          (long long)M, (long long)N, (long long)K, (long long)plan.partial_floats, plan.strips,
                          (long long)kStaticPartialFloats, kStaticCounters);
-    cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
-    float *scratch = s_scratch_addr[dev];
-    int *counters = reinterpret_cast<int *>(scratch + kStaticPartialFloats);
     // the array keeps whatever the previous call left: the arrival counters must start at zero
     e = cudaMemsetAsync(counters, 0, (size_t)plan.strips * sizeof(int), st);
     if (e != cudaSuccess) return set_error(AXB_ERR_BACKEND, "skinny_gemm_static: cudaMemsetAsync: %s", cudaGetErrorString(e));
-    SkinnyArgs a;
-    a.X = X; a.W = W; a.bias = bias; a.Y = Y; a.M = (int)M; a.N = N; a.K = K;
-    a.alpha = alpha; a.beta = beta; a.act = act;
     a.ksplit = plan.ksplit; a.kchunk = plan.kchunk; a.stages = plan.stages; a.cluster = plan.cluster;
     a.partial = (plan.ksplit > 1 && !plan.cluster) ? scratch : nullptr;
     a.counters = counters;
-    a.err = nullptr;
     int le = launch_skinny(a, plan, st);
     if (le) return set_error(AXB_ERR_BACKEND, "skinny_gemm_static: launch: %s", cudaGetErrorString((cudaError_t)le));
     return AXB_OK;
 }
 
+extern "C" int axb_skinny_gemm_static_error(void)
+{
+    using namespace axb;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices || !s_scratch_addr[dev]) return 0;
+    int *err_word = reinterpret_cast<int *>(s_scratch_addr[dev] + kStaticPartialFloats) + kStaticCounters;
+    int v = 0;
+    if (cudaMemcpy(&v, err_word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (v) {
+        cudaMemset(err_word, 0, sizeof(int));
+        set_error(AXB_ERR_BACKEND, "skinny_gemm_static: a kernel gave up on a bounded wait (code %d)", v);
+    }
+    return v;
+}

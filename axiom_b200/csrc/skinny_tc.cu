@@ -48,22 +48,10 @@ enum { KERR_PRODUCER = 21, KERR_CONVERT = 22, KERR_MMA = 23, KERR_DRAIN = 24 };
 enum { KB_RAW = 0, KB_EMPTY = KT_STAGES, KB_T_FULL = 2 * KT_STAGES, KB_T_EMPTY = 2 * KT_STAGES + KT_T,
        KB_CHUNK_FULL = 2 * KT_STAGES + 2 * KT_T, KB_CHUNK_EMPTY = 2 * KT_STAGES + 2 * KT_T + 2 };
 
-#ifdef AXB_SKTC_PROF
-__device__ unsigned long long g_sktc_prof[32];
-#define KP_DECL(n) long long prof_t[n] = {}; long long prof_c = clock64(); const long long prof_0 = prof_c; const bool prof_on = blockIdx.x == 0 && blockIdx.y == 0;
-#define KP_ADD(i) { const long long t_ = clock64(); prof_t[i] += t_ - prof_c; prof_c = t_; }
-#define KP_OUT(base, n) if (prof_on) { for (int i_ = 0; i_ < n; ++i_) g_sktc_prof[base + i_] = (unsigned long long)prof_t[i_]; g_sktc_prof[base + n] = (unsigned long long)(clock64() - prof_0); }
-extern "C" __attribute__((visibility("default"))) int axb_debug_sktc_prof(unsigned long long *out)
-{
-    return (int)cudaMemcpyFromSymbol(out, g_sktc_prof, sizeof(unsigned long long) * 32);
-}
-#define KP_STAMP(i) { if (blockIdx.x == 0 && blockIdx.y == 0) g_sktc_prof[i] = (unsigned long long)(clock64() - kernel_t0); }
-#else
 #define KP_DECL(n)
 #define KP_ADD(i)
 #define KP_OUT(base, n)
 #define KP_STAMP(i) {}
-#endif
 
 // one lane polls, the warp gets the outcome: 32 lanes spinning on a barrier cost shared-memory bandwidth that
 // the MMA operands need
@@ -125,9 +113,6 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
     constexpr uint32_t X_BYTES = MP * 128;                       // [MP rows][32 k] fp32
     // stage: W | X hi | X lo (the lo half of X is written by the converters right behind the hi half)
     constexpr uint32_t STAGE = KT_W_BYTES + 2 * X_BYTES;
-#ifdef AXB_SKTC_PROF
-    const long long kernel_t0 = clock64();
-#endif
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -367,9 +352,6 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
 
     tc_fence_before_sync();
     __syncthreads();
-#ifdef AXB_SKTC_PROF
-    if (threadIdx.x == KT_THREADS - 1 && blockIdx.x == 0 && blockIdx.y == 0) g_sktc_prof[16] = (unsigned long long)(clock64() - kernel_t0);
-#endif
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, 512);

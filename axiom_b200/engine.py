@@ -8,6 +8,7 @@ There is no fallback: if the shared library is missing, loading raises.
 from __future__ import annotations
 
 import ctypes as C
+import math
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
@@ -21,13 +22,20 @@ EXPORTS = [
     "axb_init", "axb_shutdown", "axb_device_count", "axb_synchronize", "axb_storage_alloc",
     "axb_storage_free", "axb_memcpy_h2d", "axb_memcpy_d2h", "axb_memcpy_d2d", "axb_set_stream",
     "axb_set_fp32_mode", "axb_get_fp32_mode", "axb_last_error", "axb_device_error", "axb_launch_count",
-    "axb_set_profiling", "axb_timing_summary",
+    "axb_set_profiling", "axb_timing_summary", "axb_timing_samples",
     "axb_gemm", "axb_gemm_host", "axb_gemm_nt", "axb_gemm_tn", "axb_gemm_ex", "axb_gemm_relu", "axb_gemm_bias_act",
-    "axb_skinny_gemm_static", "axb_gemm_bias_act_scatter", "axb_gemm_gathered_scatter", "axb_ipc_get_handle", "axb_ipc_open_handle",
+    "axb_skinny_gemm_static", "axb_skinny_gemm_static_error", "axb_gemm_bias_act_scatter", "axb_gemm_gathered_scatter", "axb_ipc_get_handle", "axb_ipc_open_handle",
     "axb_ipc_close_handle",
     "axb_bias_add", "axb_relu", "axb_gelu", "axb_qgemm_w8a32", "axb_qgemm_w8a8", "axb_quantize_rows",
     "axb_sdpa_fwd", "axb_kv_cache_append", "axb_kv_cache_attend", "axb_qkv_head_gemm", "axb_sdpa_bwd", "axb_conv_gemm", "axb_qdense_w8a32",
+    "axb_qgemm_w8a32_qw", "axb_bias_add_nd", "axb_head_interleave_qkv_split", "axb_head_interleave", "axb_head_deinterleave",
+    "axb_head_deinterleave_qkv_merge", "axb_qkv_cache_build", "axb_bias_cache_build", "axb_pointer_on_device",
 ]
+
+
+class QWeight(C.Structure):
+    """Host struct with axiom's ax_qweight_t layout (include/axiom/quantize.h:50-55); data and scales are device pointers."""
+    _fields_ = [("data", C.c_void_p), ("scales", C.c_void_p), ("N", C.c_int64), ("K", C.c_int64)]
 
 
 class EngineError(RuntimeError):
@@ -56,6 +64,7 @@ class Engine:
             raise FileNotFoundError(
                 f"{so_path} is missing: build it with `python -m axiom_b200.build` (no CPU fallback exists)")
         self.lib = C.CDLL(so_path)
+        self.stream_ptr = 0          # the stream the engine enqueues on (0 = legacy default stream)
         L = self.lib
         L.axb_last_error.restype = C.c_char_p
         L.axb_storage_alloc.restype = C.c_void_p
@@ -94,11 +103,18 @@ class Engine:
         self._check(self.lib.axb_timing_summary(C.byref(n), C.byref(a), C.byref(b)))
         return n.value, a.value, b.value
 
+    def timing_samples(self, cap=256):
+        """Per-call (prepass_ms, core_ms) lists of the current profiling window, oldest first."""
+        pre, core, n = (C.c_float * cap)(), (C.c_float * cap)(), C.c_int(0)
+        self._check(self.lib.axb_timing_samples(pre, core, cap, C.byref(n)))
+        return list(pre[:n.value]), list(core[:n.value])
+
     def set_fp32_mode(self, mode):
         self._check(self.lib.axb_set_fp32_mode(FP32_MODES[mode] if isinstance(mode, str) else int(mode)))
 
     def set_stream(self, stream_ptr):
         self.lib.axb_set_stream(C.c_void_p(stream_ptr))
+        self.stream_ptr = int(stream_ptr or 0)
 
     def last_error(self):
         return self.lib.axb_last_error().decode()
@@ -190,10 +206,21 @@ class Engine:
                                                     _f(alpha), _f(beta), ACT[act], C.c_void_p(stream_ptr)))
         return out
 
+    def skinny_gemm_static_error(self):
+        return int(self.lib.axb_skinny_gemm_static_error())
+
     # ---- elementwise ---------------------------------------------------
     def bias_add(self, X, bias, axis, out):
         M, N = X.shape
         self._check(self.lib.axb_bias_add(_ptr(X), _ptr(bias), int(axis), _ptr(out), _i64(M), _i64(N)))
+        return out
+
+    def bias_add_nd(self, X, bias, axis, out):
+        """out = X + bias broadcast along `axis` of a tensor of any rank."""
+        shape = list(X.shape)
+        outer = math.prod(shape[:axis])
+        inner = math.prod(shape[axis + 1:])
+        self._check(self.lib.axb_bias_add_nd(_ptr(X), _ptr(bias), _ptr(out), _i64(outer), _i64(shape[axis]), _i64(inner)))
         return out
 
     def relu(self, X, out):
@@ -208,6 +235,13 @@ class Engine:
     def qgemm_w8a32(self, a, q, scales, out):
         M, K = a.shape; N = q.shape[0]
         self._check(self.lib.axb_qgemm_w8a32(_ptr(a), _ptr(q), _ptr(scales), _ptr(out), _i64(M), _i64(N), _i64(K)))
+        return out
+
+    def qgemm_w8a32_qw(self, a, q, scales, out):
+        """axiom's own argument list: a host ax_qweight_t-layout struct whose members are device pointers."""
+        M, K = a.shape; N = q.shape[0]
+        qw = QWeight(q.data_ptr(), scales.data_ptr(), N, K)
+        self._check(self.lib.axb_qgemm_w8a32_qw(_ptr(a), C.byref(qw), _ptr(out), _i64(M)))
         return out
 
     def qdense_w8a32(self, a, q, scales, bias, out, act="none"):
@@ -228,11 +262,35 @@ class Engine:
         return q, scales
 
     # ---- attention -----------------------------------------------------
-    def sdpa_fwd(self, Q, K, V, out, L, scale, causal):
+    def sdpa_fwd(self, Q, K, V, out, L, scale, causal, P_save=None):
         BH, S, dk = Q.shape
         self._check(self.lib.axb_sdpa_fwd(_ptr(Q), _ptr(K), _ptr(V), _ptr(out), _ptr(L), _i64(BH), _i64(S), _i64(dk),
-                                          _f(scale), int(bool(causal)), None))
+                                          _f(scale), int(bool(causal)), _ptr(P_save)))
         return out, L
+
+    # ---- attention layout passes (flat = [B*S, H*dk], head-major = [B*H, S, dk]) ----
+    def head_interleave_qkv_split(self, qkv, bqkv, Qh, Kh, Vh, B, S, H, dk):
+        self._check(self.lib.axb_head_interleave_qkv_split(_ptr(qkv), _ptr(bqkv), _ptr(Qh), _ptr(Kh), _ptr(Vh), _i64(B), _i64(S),
+                                                           _i64(H), _i64(dk)))
+
+    def head_interleave(self, src, dst, B, S, H, dk):
+        self._check(self.lib.axb_head_interleave(_ptr(src), _ptr(dst), _i64(B), _i64(S), _i64(H), _i64(dk)))
+
+    def head_deinterleave(self, src, dst, B, S, H, dk):
+        self._check(self.lib.axb_head_deinterleave(_ptr(src), _ptr(dst), _i64(B), _i64(S), _i64(H), _i64(dk)))
+
+    def head_deinterleave_qkv_merge(self, dQ, dK, dV, dst, B, S, H, dk):
+        self._check(self.lib.axb_head_deinterleave_qkv_merge(_ptr(dQ), _ptr(dK), _ptr(dV), _ptr(dst), _i64(B), _i64(S), _i64(H),
+                                                             _i64(dk)))
+
+    def qkv_cache_build(self, dst, wq, wk, wv, D):
+        self._check(self.lib.axb_qkv_cache_build(_ptr(dst), _ptr(wq), _ptr(wk), _ptr(wv), _i64(D)))
+
+    def bias_cache_build(self, dst, bq, bk, bv, D):
+        self._check(self.lib.axb_bias_cache_build(_ptr(dst), _ptr(bq), _ptr(bk), _ptr(bv), _i64(D)))
+
+    def pointer_on_device(self, ptr):
+        return bool(self.lib.axb_pointer_on_device(C.c_void_p(ptr)))
 
     def conv_gemm(self, weight, inp, kh, kw, sh, sw, ph, pw, out):
         """weight [C_out, C_in*kh*kw], inp [C_in, H, W], out [C_out, out_h*out_w] with the usual output size."""

@@ -72,7 +72,11 @@ static axb_status check_f32(const axb_ax_tensor_t *t, const char *what, int want
         snprintf(msg, sizeof msg, "%s: tensor must be contiguous", what);
         return report(ST_INVALID_SHAPE, msg);
     }
-    if (t->storage->device != AXB_AX_DEVICE_CUDA) {
+    /* axiom's attention layer wraps device buffers in stack views whose storage says CPU
+       (mha_make_stack_view, src/core/attention.c:71-89), and the stock CUDA backend never looks at the field
+       (src/compute/backends/cuda/ops_gemm.cu:15-27): trust the pointer, not the label, but never hand host
+       memory to a kernel */
+    if (t->storage->device != AXB_AX_DEVICE_CUDA && !axb_pointer_on_device(t->storage->data)) {
         snprintf(msg, sizeof msg, "%s: tensor is not on the CUDA device", what);
         return report(ST_BACKEND, msg);
     }
@@ -177,17 +181,24 @@ static axb_status be_conv_gemm(const axb_ax_tensor_t *weight, const axb_ax_conv_
                               params->sh, params->sw, params->ph, params->pw, params->out_h, params->out_w, fptr(out)));
 }
 
+/* shape rules of the reference's CUDA implementation (src/compute/backends/cuda/ops_fused.cu:268-292): any rank,
+   bias 1-d of length in->shape[axis], broadcast along that axis */
 static axb_status be_bias_add(const axb_ax_tensor_t *in, const axb_ax_tensor_t *bias, int axis, axb_ax_tensor_t *out)
 {
     axb_status st;
-    if ((st = check_f32(in, "bias_add", 2)) || (st = check_f32(out, "bias_add", 2)) ||
+    if ((st = check_f32(in, "bias_add", 0)) || (st = check_f32(out, "bias_add", 0)) ||
         (st = check_f32(bias, "bias_add", 1)))
         return st;
-    if (axis < 0) axis += 2;
-    if (axis != 0 && axis != 1) return report(ST_AXIS, "bias_add: axis out of range for a 2-d tensor");
-    if (out->shape[0] != in->shape[0] || out->shape[1] != in->shape[1] || bias->shape[0] != in->shape[axis])
-        return report(ST_SHAPE, "bias_add: bias length must equal in->shape[axis] and out must match in");
-    return done(axb_bias_add(fptr(in), fptr(bias), axis, fptr(out), in->shape[0], in->shape[1]));
+    if (axis < 0) axis += in->ndim;
+    if (axis < 0 || axis >= in->ndim) return report(ST_AXIS, "bias_add: axis out of range");
+    if (out->ndim != in->ndim) return report(ST_SHAPE, "bias_add: out must have the shape of in");
+    for (int d = 0; d < in->ndim; ++d)
+        if (out->shape[d] != in->shape[d]) return report(ST_SHAPE, "bias_add: out must have the shape of in");
+    if (bias->shape[0] != in->shape[axis]) return report(ST_SHAPE, "bias_add: bias length must equal in->shape[axis]");
+    int64_t outer = 1, inner = 1;
+    for (int d = 0; d < axis; ++d) outer *= in->shape[d];
+    for (int d = axis + 1; d < in->ndim; ++d) inner *= in->shape[d];
+    return done(axb_bias_add_nd(fptr(in), fptr(bias), fptr(out), outer, in->shape[axis], inner));
 }
 
 static axb_status unary(const char *what, const axb_ax_tensor_t *in, axb_ax_tensor_t *out, int gelu)
@@ -230,6 +241,58 @@ static axb_status ext_sdpa_bwd(const float *Q, const float *K, const float *V, c
     return done(axb_sdpa_bwd(Q, K, V, O, dO, L, dQ, dK, dV, BH, S, dk, scale, causal ? 1 : 0, P_saved));
 }
 
+/* ---- attention layout slots (include/axiom/internal/cuda_extension.h:41-88).  The five layout slots return
+   void in axiom; a failure reaches the caller through the error hook only, as with the stock kernels' launch
+   errors.  D is redundant (D = H*dk at every call site, src/core/attention.c:236-261,700-716). ---- */
+
+static int d_matches(const char *what, int64_t H, int64_t dk, int64_t D)
+{
+    if (D == H * dk) return 1;
+    char msg[120];
+    snprintf(msg, sizeof msg, "%s: D must equal H*dk", what);
+    report(ST_SHAPE, msg);
+    return 0;
+}
+
+static void ext_qkv_split(const float *src, float *q, float *k, float *v, int64_t B, int64_t S, int64_t H, int64_t dk,
+                          int64_t D)
+{
+    if (d_matches("head_interleave_qkv_split", H, dk, D)) done(axb_head_interleave_qkv_split(src, NULL, q, k, v, B, S, H, dk));
+}
+
+static void ext_qkv_split_bias(const float *src, const float *bqkv, float *q, float *k, float *v, int64_t B, int64_t S,
+                               int64_t H, int64_t dk, int64_t D)
+{
+    if (!bqkv) { report(ST_NULL_ARG, "head_interleave_qkv_split_bias: NULL bias"); return; }
+    if (d_matches("head_interleave_qkv_split_bias", H, dk, D)) done(axb_head_interleave_qkv_split(src, bqkv, q, k, v, B, S, H, dk));
+}
+
+static void ext_head_interleave(const float *src, float *dst, int64_t B, int64_t S, int64_t H, int64_t dk)
+{
+    done(axb_head_interleave(src, dst, B, S, H, dk));
+}
+
+static void ext_head_deinterleave(const float *src, float *dst, int64_t B, int64_t S, int64_t H, int64_t dk)
+{
+    done(axb_head_deinterleave(src, dst, B, S, H, dk));
+}
+
+static void ext_qkv_merge(const float *dQ, const float *dK, const float *dV, float *dst, int64_t B, int64_t S, int64_t H,
+                          int64_t dk, int64_t D)
+{
+    if (d_matches("head_deinterleave_qkv_merge", H, dk, D)) done(axb_head_deinterleave_qkv_merge(dQ, dK, dV, dst, B, S, H, dk));
+}
+
+static axb_status ext_qkv_cache_build(float *dst, const float *wq, const float *wk, const float *wv, int64_t D)
+{
+    return done(axb_qkv_cache_build(dst, wq, wk, wv, D));
+}
+
+static axb_status ext_bias_cache_build(float *dst, const float *bq, const float *bk, const float *bv, int64_t D)
+{
+    return done(axb_bias_cache_build(dst, bq, bk, bv, D));
+}
+
 static const axb_ax_backend_ops_t ops_table = {
     .name = "b200_tcgen05",
     .gemm = be_gemm,
@@ -255,6 +318,13 @@ static const axb_ax_backend_ops_t ops_table = {
 };
 
 static const axb_ax_cuda_extension_t extension_table = {
+    .head_interleave_qkv_split = ext_qkv_split,
+    .head_interleave_qkv_split_bias = ext_qkv_split_bias,
+    .head_interleave = ext_head_interleave,
+    .head_deinterleave = ext_head_deinterleave,
+    .head_deinterleave_qkv_merge = ext_qkv_merge,
+    .qkv_cache_build = ext_qkv_cache_build,
+    .bias_cache_build = ext_bias_cache_build,
     .sdpa_fwd = ext_sdpa_fwd,
     .sdpa_bwd = ext_sdpa_bwd,
 };

@@ -95,7 +95,9 @@ class PeerScatterColumnMLP:
 
     Gather buffers are plain device allocations (``axb_storage_alloc``) shared through CUDA IPC handles that
     the ranks exchange once with ``all_gather_object``; they are reused every step (a rank can only start
-    the next step after the last layer's synchronisation, by which time every rank has finished reading)."""
+    the next step after the last layer's synchronisation, by which time every rank has finished reading the
+    buffers of all layers but the last; with a single layer the caller must not start the next step before
+    its peers have consumed the output, e.g. by a barrier of its own)."""
 
     def __init__(self, engine, weight_slabs, bias_slabs, world, rank, batch, dist, act="gelu"):
         import torch
@@ -135,9 +137,23 @@ class PeerScatterColumnMLP:
                 self.engine.gemm_bias_act_scatter(x_full, W, b, slab, dests, M, n, x_full.shape[1], act=self.act)
             else:
                 self.engine.gemm_gathered_scatter(self.local[l - 1], g, prev_n, W, b, slab, dests, M, n, act=self.act)
-            self.dist.all_reduce(self._token)           # everybody's stores are done before anybody reads
+            self._exchange_token()                      # everybody's stores are done before anybody reads
             prev_n = n
         return self.local[-1], n
+
+    def _exchange_token(self):
+        """The all-reduce runs on torch's current stream, the GEMMs on the engine's: order the collective after this
+        rank's stores and the next layer's reads after the collective, whichever streams those are."""
+        import torch
+        cur = torch.cuda.current_stream()
+        sp = getattr(self.engine, "stream_ptr", 0)
+        eng_stream = torch.cuda.ExternalStream(sp) if sp else torch.cuda.default_stream()
+        same = eng_stream.cuda_stream == cur.cuda_stream
+        if not same:
+            cur.wait_stream(eng_stream)
+        self.dist.all_reduce(self._token)
+        if not same:
+            eng_stream.wait_stream(cur)
 
     def close(self):
         self.dist.barrier()

@@ -12,7 +12,9 @@
    reference): 0 = AX_OK, 1 = NULL_ARG, 2 = ALLOC, 3 = SHAPE_MISMATCH,
    7 = INVALID_DTYPE, 9 = BACKEND, 10 = NOT_IMPLEMENTED ...  The engine never
    aborts and never falls back to host arithmetic; axb_last_error() returns
-   the message of the most recent failure on the calling thread's engine.
+   the message of the most recent failure.  The engine is one per process
+   (one process per GPU) and is not thread-safe: one host thread drives it,
+   as with the reference backend (src/compute/backends/cuda/internal.h:70-74).
 
    Each declaration cites the reference interface it replaces as
    file:line within the axiom source tree. */
@@ -79,6 +81,9 @@ AXB_API int64_t axb_launch_count(int reset);
    milliseconds, and starts a new window.  axb_set_profiling also starts one. */
 AXB_API void axb_set_profiling(int on);
 AXB_API int axb_timing_summary(int *calls, float *prepass_ms_total, float *core_ms_total);
+/* The same window call by call (oldest first, at most cap entries, newest 256 kept): per-call pre-pass and
+   main-kernel milliseconds, for medians and minima.  Does not start a new window. */
+AXB_API int axb_timing_samples(float *prepass_ms, float *core_ms, int cap, int *n_out);
 
 /* ---- dense fp32 GEMM family ----------------------------------------------
    Slots gemm / gemm_nt / gemm_tn / gemm_ex / gemm_relu of ax_backend_ops_t
@@ -145,36 +150,48 @@ AXB_API int axb_ipc_close_handle(void *dev_ptr);
 
 /* Skinny-M GEMM that never allocates (no counterpart in the reference).
      Y[M,N] = act(alpha * X[M,K] . W[K,N] + beta * Y + bias[n]),  1 <= M <= 32
-   Same kernel and bit-identical results as the skinny route of axb_gemm_bias_act,
-   but the split-K scratch is a fixed 4 MiB + 4 KiB array inside the library image
-   (AXB_STATIC_SCRATCH_BYTES, resident on every GPU that loads the library) instead
-   of memory obtained from cudaMalloc.  It is meant for callers that must not
-   allocate once they are running: a host framework that handed the whole device
-   to its own arena at start-up, a serving loop that cannot afford the device-wide
-   stall an allocation may cause, or a process held to a fixed memory budget.
-   The call uses neither the engine's state nor axb_init, and issues no cudaMalloc,
-   cudaFree or other allocating call.
+   Takes the same kernel as the skinny route of axb_gemm_bias_act for the same arguments — the TMA-ringed FMA
+   kernel up to 8 rows, the tensor-core kernel from 9 rows on (which needs no scratch), the plain-load kernel for
+   operands a tensor map cannot describe — and gives bit-identical results, but the split-K scratch is a fixed
+   4 MiB + 4 KiB array inside the library image (AXB_STATIC_SCRATCH_BYTES, resident on every GPU that loads the
+   library) instead of memory obtained from cudaMalloc.  It is meant for callers that must not allocate once they
+   are running: a host framework that handed the whole device to its own arena at start-up, a serving loop that
+   cannot afford the device-wide stall an allocation may cause, or a process held to a fixed memory budget.
+   The call uses neither the engine's state nor axb_init, and issues no cudaMalloc, cudaFree or other allocating
+   call.
    - The device used is the calling thread's current CUDA device; work goes to
      cuda_stream (NULL = legacy default stream).
    - The first call on each device looks up the array's address on that device;
      make that first call during start-up, outside any stream capture.
+   - The CUDA runtime loads a kernel's code onto the device the first time that kernel is launched, and each
+     row bucket (1, 2, 4, 8, 16, 32 rows) and route is a kernel of its own.  A caller that may not see the
+     driver touch device memory at all after start-up makes one call per row bucket and route it will use
+     while starting up; later calls then change nothing on the device but Y and the array.
    - Most shapes reduce their K-slices inside a thread-block cluster and need no scratch at all.  Shapes
      that do need it (K too long for a cluster of 8 slices, i.e. roughly K * M > 131072, or N < 2400)
      and whose split-K partial sums exceed the array (slices * M * N > 2^20 floats), or with more than
-     1024 column strips, are refused with AXB_ERR_INVALID_SHAPE and a message; nothing is launched.
+     1023 column strips, are refused with AXB_ERR_INVALID_SHAPE and a message; nothing is launched.
    - All calls on a device share the one array and it keeps the previous call's
      contents (the counters are cleared on the stream before each launch).  Two
      calls that overlap on the GPU — different streams without ordering, or
-     different threads — race on it; serialise them. */
+     different threads — race on it; serialise them.
+   - Every wait inside the kernels is bounded.  If one runs out (it should not), the kernel writes a code into
+     the last word of the array and returns; Y is then incomplete.  axb_skinny_gemm_static_error() reads that
+     word for the current device (a blocking 4-byte copy, no allocation), returns it and clears it; 0 = none. */
 #define AXB_STATIC_SCRATCH_BYTES ((1u << 22) + 4096u)
 AXB_API int axb_skinny_gemm_static(const float *X, const float *W, const float *bias, float *Y,
                                    int64_t M, int64_t N, int64_t K, float alpha, float beta, int act,
                                    void *cuda_stream);
+AXB_API int axb_skinny_gemm_static_error(void);
 
 /* ---- elementwise slots that remain as separate calls ---------------------- */
 /* out = in + bias broadcast along axis (0: bias[M], 1: bias[N]); out may alias in.
    (bias_add slot, backend_ops.h:190; src/compute/backends/cuda/ops_fused.cu:260-292) */
 AXB_API int axb_bias_add(const float *in, const float *bias, int axis, float *out, int64_t M, int64_t N);
+/* The same slot for a tensor of any rank seen as [outer, axis_len, inner] (the products of the dimensions before
+   and after the broadcast axis, ops_fused.cu:281-285): out[o,a,i] = in[o,a,i] + bias[a]. */
+AXB_API int axb_bias_add_nd(const float *in, const float *bias, float *out, int64_t outer, int64_t axis_len,
+                            int64_t inner);
 /* (relu slot, backend_ops.h:235) */
 AXB_API int axb_relu(const float *in, float *out, int64_t n);
 /* (gelu_op slot, backend_ops.h:244; src/compute/backends/cuda/ops_activations.cu:12-24) */
@@ -190,6 +207,16 @@ AXB_API int axb_gelu(const float *in, float *out, int64_t n);
    exact sum and does not depend on summation order; a row that holds an infinity or a NaN comes out as NaN. */
 AXB_API int axb_qgemm_w8a32(const float *a, const int8_t *q, const float *scales, float *out,
                     int64_t M, int64_t N, int64_t K);
+/* The same call with axiom's own argument list, ax_qgemm_w8a32(a, qw, out, M) (include/axiom/quantize.h:75-79):
+   qw points to a HOST struct laid out as ax_qweight_t (quantize.h:50-55) whose data and scales members are DEVICE
+   pointers.  Status codes follow the reference (src/core/quantize.c:100-112): NULL_ARG for a NULL argument or
+   member, INVALID_SHAPE for non-positive N or K. */
+typedef struct {
+    int8_t *data;   /* [N, K] int8 rows, device memory */
+    float *scales;  /* [N] per-row scale, device memory */
+    int64_t N, K;
+} axb_qweight_t;
+AXB_API int axb_qgemm_w8a32_qw(const float *a, const axb_qweight_t *qw, float *out, int64_t M);
 
 /* The quantised dense layer the reference does not have ("raw kernel", docs/EMBEDDED.md:358: callers add bias and
    activation themselves after ax_qgemm_w8a32): out[m,n] = act(scale[n] * sum_k a[m,k]*q[n,k] + bias[n]), scale,
@@ -212,8 +239,14 @@ AXB_API int axb_quantize_rows(const float *w, int64_t N, int64_t K, int8_t *q, f
 
 /* ---- attention ------------------------------------------------------------- */
 /* O = softmax(scale * Q.K^T [+ causal mask]) . V per head on head-major
-   [BH,S,dk] buffers; L[BH,S] = log-sum-exp per row or NULL.  P_save must be NULL
-   (returns NOT_IMPLEMENTED otherwise, which the caller treats as "no saved P").
+   [BH,S,dk] buffers; L[BH,S] = log-sum-exp per row or NULL.  P_save is NULL or a
+   [BH,S,S] buffer that receives the soft-max probabilities (exactly 0 above the
+   diagonal when causal), as the stock backend's copy of its score buffer does
+   (ops_attention.cu:366-370).  O and L are always computed first by the fused
+   kernel, which forms no S x S matrix; a non-NULL P_save costs one more pass
+   that writes it from L.  axiom's caller ignores the returned status
+   (src/core/attention.c:335-342), so no argument combination may skip O.
+   axb_sdpa_bwd never reads the saved probabilities.
    (sdpa_fwd slot of ax_cuda_extension_t, include/axiom/internal/cuda_extension.h:89-92;
    src/compute/backends/cuda/ops_attention.cu:299-392; public CPU form
    ax_fused_attention_fwd[_causal], include/axiom/attention.h:273-280) */
@@ -239,6 +272,30 @@ AXB_API int axb_sdpa_bwd(const float *Q, const float *K, const float *V, const f
    For dk % 32 == 0 the GEMM's epilogue stores head-major itself (one launch, no [B*S, 3D] intermediate). */
 AXB_API int axb_qkv_head_gemm(const float *X, const float *Wqkv, const float *bqkv, int64_t B, int64_t S, int64_t H,
                               int64_t dk, float *Qh, float *Kh, float *Vh);
+
+/* ---- attention layout passes and fused-parameter builders ---------------------
+   The remaining attention slots of ax_cuda_extension_t (include/axiom/internal/cuda_extension.h:41-88; stock
+   kernels src/compute/backends/cuda/ops_attention.cu:18-211), which axiom's multi-head attention layer calls
+   between its GEMMs when its tensors live on a device (src/core/attention.c:234-261,368-375,665-716;
+   src/core/attention/cache.c:43-80).  "flat" is the [B*S, H*dk] layout of a projection GEMM, "head-major" is
+   [B*H, S, dk].  Each is one pass that reads and writes every element once. */
+/* qkv [B*S, 3*H*dk] (+ bqkv[3*H*dk], may be NULL) -> Qh, Kh, Vh head-major   (head_interleave_qkv_split[_bias]) */
+AXB_API int axb_head_interleave_qkv_split(const float *qkv, const float *bqkv, float *Qh, float *Kh, float *Vh,
+                                          int64_t B, int64_t S, int64_t H, int64_t dk);
+/* flat -> head-major                                                          (head_interleave) */
+AXB_API int axb_head_interleave(const float *src, float *dst, int64_t B, int64_t S, int64_t H, int64_t dk);
+/* head-major -> flat                                                          (head_deinterleave) */
+AXB_API int axb_head_deinterleave(const float *src, float *dst, int64_t B, int64_t S, int64_t H, int64_t dk);
+/* dQ, dK, dV head-major -> dst [B*S, 3*H*dk]                                  (head_deinterleave_qkv_merge) */
+AXB_API int axb_head_deinterleave_qkv_merge(const float *dQ, const float *dK, const float *dV, float *dst, int64_t B,
+                                            int64_t S, int64_t H, int64_t dk);
+/* dst [D, 3D] = [wq | wk | wv] row by row, each [D, D]                        (qkv_cache_build) */
+AXB_API int axb_qkv_cache_build(float *dst, const float *wq, const float *wk, const float *wv, int64_t D);
+/* dst [3D] = bq | bk | bv                                                     (bias_cache_build) */
+AXB_API int axb_bias_cache_build(float *dst, const float *bq, const float *bk, const float *bv, int64_t D);
+/* 1 when p points into device (or managed) memory, else 0.  axiom labels some device buffers as CPU storage
+   (the stack views of src/core/attention.c:71-89); the host layer asks the driver instead of trusting the label. */
+AXB_API int axb_pointer_on_device(const void *p);
 
 /* ---- convolution as GEMM -----------------------------------------------------
    Slot conv_gemm of ax_backend_ops_t (include/axiom/internal/backend_ops.h:199-202; ax_compute_conv_gemm,

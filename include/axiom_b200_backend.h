@@ -105,11 +105,20 @@ typedef struct {
     axb_status (*memcpy_d2d)(void *dst, const void *src, size_t bytes);
 } axb_ax_backend_ops_t;
 
-/* ax_cuda_extension_t: sdpa_fwd and sdpa_bwd are provided. */
+/* ax_cuda_extension_t (include/axiom/internal/cuda_extension.h:41-130): everything the attention layer calls on a
+   device — the five head-layout passes, the two fused-parameter builders, sdpa_fwd and sdpa_bwd — is provided; the
+   batched-convolution slots stay NULL. */
 typedef struct {
-    axb_opaque_fn head_interleave_qkv_split, head_interleave_qkv_split_bias, head_interleave, head_deinterleave,
-        head_deinterleave_qkv_merge;
-    axb_opaque_fn qkv_cache_build, bias_cache_build;
+    void (*head_interleave_qkv_split)(const float *src, float *q, float *k, float *v, int64_t B, int64_t S, int64_t H,
+                                      int64_t dk, int64_t D);
+    void (*head_interleave_qkv_split_bias)(const float *src, const float *bqkv, float *q, float *k, float *v, int64_t B,
+                                           int64_t S, int64_t H, int64_t dk, int64_t D);
+    void (*head_interleave)(const float *src, float *dst, int64_t B, int64_t S, int64_t H, int64_t dk);
+    void (*head_deinterleave)(const float *src, float *dst, int64_t B, int64_t S, int64_t H, int64_t dk);
+    void (*head_deinterleave_qkv_merge)(const float *dQ, const float *dK, const float *dV, float *dst, int64_t B,
+                                        int64_t S, int64_t H, int64_t dk, int64_t D);
+    axb_status (*qkv_cache_build)(float *dst, const float *wq, const float *wk, const float *wv, int64_t D);
+    axb_status (*bias_cache_build)(float *dst, const float *bq, const float *bk, const float *bv, int64_t D);
     axb_status (*sdpa_fwd)(const float *Q, const float *K, const float *V, float *out, float *L, int64_t BH,
                            int64_t S, int64_t dk, float scale, bool causal, float *P_save);
     axb_status (*sdpa_bwd)(const float *Q, const float *K, const float *V, const float *O, const float *dO,

@@ -457,3 +457,327 @@ SHIM_API int ref_sdpa_fwd(const float *Q, const float *K, const float *V, float 
     else        ax_fused_attention_fwd(Q, K, V, O, L, BH, S, dk, scale);
     return 0;
 }
+
+/* ---- the multi-head attention layer ---------------------------------------------------------------
+   ref_mha_layer runs the reference's own layer (ax_mha_create + ax_layer_forward, and ax_backward of
+   sum(out * dOut) when dOut is given) on its CPU backend with caller-supplied parameters.
+   W: [4][D][D] = Wq, Wk, Wv, Wo; b: [4][D] = bq, bk, bv, bo or NULL.  Outputs that are NULL are skipped. */
+#include "axiom/layer.h"
+#include "axiom/autograd.h"
+#include <math.h>
+
+static void grad_out(const ax_tensor_t *p, float *dst, int64_t n)
+{
+    if (!dst) return;
+    if (p && p->grad) memcpy(dst, tdata(p->grad), (size_t)n * sizeof(float));
+    else memset(dst, 0, (size_t)n * sizeof(float));
+}
+
+SHIM_API int ref_mha_layer(const float *x, const float *W, const float *b, int64_t B, int64_t S, int64_t D, int H,
+                           int causal, const float *dOut, float *out, float *dX, float *dW, float *db)
+{
+    ax_compute_set_backend(AX_BACKEND_CPU_SIMD);
+    ax_set_default_device(AX_DEVICE_CPU);
+    ax_layer_t *layer = ax_mha_create(D, H, b != NULL, causal != 0);
+    if (!layer) return 100;
+    ax_mha_t *m = (ax_mha_t *)layer;
+    ax_tensor_t *w[4] = { m->Wq, m->Wk, m->Wv, m->Wo }, *bs[4] = { m->bq, m->bk, m->bv, m->bo };
+    for (int i = 0; i < 4; i++) {
+        memcpy(tdata(w[i]), W + (size_t)i * D * D, (size_t)(D * D) * sizeof(float));
+        ax_storage_touch(w[i]->storage);
+        if (b) memcpy(tdata(bs[i]), b + (size_t)i * D, (size_t)D * sizeof(float));
+    }
+    int64_t xs[3] = { B, S, D };
+    ax_tensor_t *xt = ax_tensor_from_array(x, xs, 3, AX_FLOAT32);
+    int rc = 0;
+    ax_tensor_t *o = NULL;
+    if (dOut) {
+        layer->training = true;
+        ax_enable_grad();
+        xt->requires_grad = true;
+        o = ax_layer_forward(layer, xt);
+        if (!o) rc = 101;
+        else {
+            memcpy(out, tdata(o), (size_t)(B * S * D) * sizeof(float));
+            ax_tensor_t *g = ax_tensor_from_array(dOut, xs, 3, AX_FLOAT32);
+            ax_tensor_t *prod = ax_mul(o, g);
+            ax_tensor_t *loss = prod ? ax_sum(prod, -1) : NULL;
+            if (!loss) rc = 102;
+            else rc = (int)ax_backward(loss);
+            if (!rc) {
+                grad_out(xt, dX, B * S * D);
+                for (int i = 0; i < 4; i++) {
+                    grad_out(w[i], dW ? dW + (size_t)i * D * D : NULL, D * D);
+                    if (b) grad_out(bs[i], db ? db + (size_t)i * D : NULL, D);
+                }
+            }
+            if (loss) { ax_graph_cleanup(loss); ax_tensor_destroy(loss); }
+            ax_tensor_destroy(g);
+            o = NULL;   /* an interior node of the graph: released by the cleanup above */
+        }
+    } else {
+        layer->training = false;
+        o = ax_layer_forward(layer, xt);
+        if (!o) rc = 101;
+        else memcpy(out, tdata(o), (size_t)(B * S * D) * sizeof(float));
+    }
+    if (o) ax_tensor_destroy(o);
+    ax_tensor_destroy(xt);
+    ax_layer_destroy(layer);
+    return rc;
+}
+
+/* The same layer on the DEVICE, call by call as mha_forward / mha_backward make them when their tensors live on a
+   device (src/core/attention.c:213-261,335-342,368-375,392-431 and :640-716,741-800,880-900; parameter caches
+   src/core/attention/cache.c:43-80): every step is the reference's own dispatcher wrapper or a slot of the
+   registered extension table, on device tensors the reference allocates through the backend's hooks.  The layer
+   object itself cannot be driven this way in v0.10.0: mha_forward wraps its input in a stack view whose storage
+   is labelled CPU (mha_make_stack_view, attention.c:71-89) and derives `on_cuda` from that label (:213), so the
+   device branch is never taken and host loops would run over device pointers.  x_flat below is such a view, so
+   the backend's handling of the mislabelled operand is exercised too.  The reductions the reference does in
+   host loops with no device slot (bias gradients = column sums, attention.c:653-658,820-845) are done here on
+   host copies.  save_p: pass a P_save buffer to sdpa_fwd and hand it to sdpa_bwd, as the layer does when P fits. */
+static void colsum(const float *M, float *out, int64_t rows, int64_t cols)
+{
+    for (int64_t c = 0; c < cols; c++) out[c] = 0.0f;
+    for (int64_t r = 0; r < rows; r++)
+        for (int64_t c = 0; c < cols; c++) out[c] += M[r * cols + c];
+}
+
+SHIM_API int ref_device_mha_sequence(const float *x, const float *W, const float *b, int64_t B, int64_t S, int64_t D,
+                                     int H, int causal, int save_p, const float *dOut, float *out, float *dX, float *dW,
+                                     float *db, float *P_out)
+{
+    const ax_cuda_extension_t *cu = ax_compute_get_cuda_extension();
+    if (!cu || !cu->head_interleave_qkv_split || !cu->head_interleave_qkv_split_bias || !cu->head_interleave ||
+        !cu->head_deinterleave || !cu->head_deinterleave_qkv_merge || !cu->qkv_cache_build || !cu->bias_cache_build ||
+        !cu->sdpa_fwd || !cu->sdpa_bwd)
+        return 200;
+    const int64_t rows = B * S, dk = D / H, BH = B * H;
+    const float scale = 1.0f / sqrtf((float)dk);
+    int rc = 0;
+    use_cuda(1);
+    ax_tensor_t *w[4], *bs[4] = { NULL, NULL, NULL, NULL };
+    for (int i = 0; i < 4; i++) {
+        w[i] = to_dev(t2(W + (size_t)i * D * D, D, D));
+        if (b) bs[i] = to_dev(t1(b + (size_t)i * D, D));
+    }
+    ax_tensor_t *xd = to_dev(t2(x, rows, D));
+    /* the layer's view of its input: device memory behind a storage labelled CPU */
+    ax_tensor_t x_view;
+    ax_storage_t x_view_st;
+    memset(&x_view, 0, sizeof x_view);
+    memset(&x_view_st, 0, sizeof x_view_st);
+    x_view_st.data = xd->storage->data;
+    x_view_st.size_bytes = (size_t)(rows * D) * sizeof(float);
+    x_view_st.device = AX_DEVICE_CPU;
+    x_view_st.is_arena_temp = true;
+    x_view_st.generation = 1;
+    x_view.storage = &x_view_st;
+    x_view.ndim = 2; x_view.dtype = AX_FLOAT32;
+    x_view.shape[0] = rows; x_view.shape[1] = D; x_view.strides[0] = D; x_view.strides[1] = 1;
+
+    int64_t sh_w3[2] = { D, 3 * D }, sh_b3[1] = { 3 * D }, sh_qkv[2] = { rows, 3 * D }, sh_head[3] = { BH, S, dk },
+            sh_L[2] = { BH, S }, sh_P[3] = { BH, S, S }, sh_flat[2] = { rows, D };
+    ax_tensor_t *Wqkv = ax_tensor_create(sh_w3, 2, AX_FLOAT32), *bqkv = b ? ax_tensor_create(sh_b3, 1, AX_FLOAT32) : NULL;
+    ax_tensor_t *qkv = ax_tensor_create(sh_qkv, 2, AX_FLOAT32);
+    ax_tensor_t *Qh = ax_tensor_create(sh_head, 3, AX_FLOAT32), *Kh = ax_tensor_create(sh_head, 3, AX_FLOAT32),
+                *Vh = ax_tensor_create(sh_head, 3, AX_FLOAT32), *Oh = ax_tensor_create(sh_head, 3, AX_FLOAT32);
+    ax_tensor_t *Lt = dOut ? ax_tensor_create(sh_L, 2, AX_FLOAT32) : NULL;
+    ax_tensor_t *Pt = save_p ? ax_tensor_create(sh_P, 3, AX_FLOAT32) : NULL;
+    ax_tensor_t *attn = ax_tensor_create(sh_flat, 2, AX_FLOAT32), *of = ax_tensor_create(sh_flat, 2, AX_FLOAT32);
+    if (!Wqkv || (b && !bqkv) || !qkv || !Qh || !Kh || !Vh || !Oh || (dOut && !Lt) || (save_p && !Pt) || !attn || !of) rc = 100;
+
+    /* ---- forward ---- */
+    if (!rc) rc = (int)cu->qkv_cache_build(tdata(Wqkv), tdata(w[0]), tdata(w[1]), tdata(w[2]), D);
+    if (!rc && b) rc = (int)cu->bias_cache_build(tdata(bqkv), tdata(bs[0]), tdata(bs[1]), tdata(bs[2]), D);
+    if (!rc) rc = (int)ax_compute_gemm(&x_view, Wqkv, qkv);
+    if (!rc) {
+        if (b) cu->head_interleave_qkv_split_bias(tdata(qkv), tdata(bqkv), tdata(Qh), tdata(Kh), tdata(Vh), B, S, H, dk, D);
+        else cu->head_interleave_qkv_split(tdata(qkv), tdata(Qh), tdata(Kh), tdata(Vh), B, S, H, dk, D);
+        /* status ignored, as the layer does */
+        cu->sdpa_fwd(tdata(Qh), tdata(Kh), tdata(Vh), tdata(Oh), Lt ? tdata(Lt) : NULL, BH, S, dk, scale, causal != 0,
+                     Pt ? tdata(Pt) : NULL);
+        cu->head_deinterleave(tdata(Oh), tdata(attn), B, S, H, dk);
+        rc = (int)ax_compute_gemm(attn, w[3], of);
+        if (!rc && b) rc = (int)ax_compute_bias_add(of, bs[3], 1, of);
+    }
+    if (!rc) { ax_device_synchronize(AX_DEVICE_CUDA); rc = copy_back(of, out, rows * D); }
+    if (!rc && Pt && P_out) rc = copy_back(Pt, P_out, BH * S * S);
+
+    /* ---- backward ---- */
+    if (!rc && dOut) {
+        int64_t sh_dw[2] = { D, D };
+        ax_tensor_t *g = to_dev(t2(dOut, rows, D));
+        ax_tensor_t *dWo = ax_tensor_create(sh_dw, 2, AX_FLOAT32);       /* device storage is zero-filled */
+        ax_tensor_t *dattn = ax_tensor_create(sh_flat, 2, AX_FLOAT32), *dOh = ax_tensor_create(sh_head, 3, AX_FLOAT32);
+        ax_tensor_t *dQh = ax_tensor_create(sh_head, 3, AX_FLOAT32), *dKh = ax_tensor_create(sh_head, 3, AX_FLOAT32),
+                    *dVh = ax_tensor_create(sh_head, 3, AX_FLOAT32);
+        ax_tensor_t *dQKV = ax_tensor_create(sh_qkv, 2, AX_FLOAT32), *dWqkv = ax_tensor_create(sh_w3, 2, AX_FLOAT32),
+                    *dXt = ax_tensor_create(sh_flat, 2, AX_FLOAT32);
+        if (!g || !dWo || !dattn || !dOh || !dQh || !dKh || !dVh || !dQKV || !dWqkv || !dXt) rc = 110;
+        if (!rc) {
+            ax_gemm_set_skip_init(true);                                  /* grad_Wo += attn^T . dOut */
+            rc = (int)ax_compute_gemm_tn(attn, g, dWo);
+            ax_gemm_set_skip_init(false);
+        }
+        if (!rc) rc = (int)ax_compute_gemm_nt(g, w[3], dattn);
+        if (!rc) {
+            cu->head_interleave(tdata(dattn), tdata(dOh), B, S, H, dk);
+            cu->sdpa_bwd(tdata(Qh), tdata(Kh), tdata(Vh), tdata(Oh), tdata(dOh), tdata(Lt), tdata(dQh), tdata(dKh),
+                         tdata(dVh), BH, S, dk, scale, causal != 0, Pt ? tdata(Pt) : NULL);
+            cu->head_deinterleave_qkv_merge(tdata(dQh), tdata(dKh), tdata(dVh), tdata(dQKV), B, S, H, dk, D);
+            rc = (int)ax_compute_gemm_tn(&x_view, dQKV, dWqkv);
+        }
+        if (!rc) rc = (int)ax_compute_gemm_nt(dQKV, Wqkv, dXt);
+        if (!rc) {
+            ax_device_synchronize(AX_DEVICE_CUDA);
+            float *h_dwqkv = (float *)malloc((size_t)(D * 3 * D) * sizeof(float));
+            float *h_dqkv = (float *)malloc((size_t)(rows * 3 * D) * sizeof(float));
+            rc = copy_back(dXt, dX, rows * D) || copy_back(dWo, dW + (size_t)3 * D * D, D * D) ||
+                 copy_back(dWqkv, h_dwqkv, D * 3 * D) || copy_back(dQKV, h_dqkv, rows * 3 * D);
+            if (!rc) {
+                for (int64_t i = 0; i < D; i++)
+                    for (int s = 0; s < 3; s++)
+                        memcpy(dW + (size_t)s * D * D + i * D, h_dwqkv + i * 3 * D + s * D, (size_t)D * sizeof(float));
+                if (b && db) {
+                    float *tmp = (float *)malloc((size_t)(3 * D) * sizeof(float));
+                    colsum(h_dqkv, tmp, rows, 3 * D);
+                    memcpy(db, tmp, (size_t)(3 * D) * sizeof(float));
+                    colsum(dOut, db + 3 * D, rows, D);
+                    free(tmp);
+                }
+            }
+            free(h_dwqkv); free(h_dqkv);
+        }
+        ax_tensor_t *tmp[] = { g, dWo, dattn, dOh, dQh, dKh, dVh, dQKV, dWqkv, dXt };
+        for (unsigned i = 0; i < sizeof tmp / sizeof tmp[0]; i++)
+            if (tmp[i]) ax_tensor_destroy(tmp[i]);
+    }
+    ax_tensor_t *all[] = { w[0], w[1], w[2], w[3], bs[0], bs[1], bs[2], bs[3], xd, Wqkv, bqkv, qkv, Qh, Kh, Vh, Oh, Lt, Pt, attn, of };
+    for (unsigned i = 0; i < sizeof all / sizeof all[0]; i++)
+        if (all[i]) ax_tensor_destroy(all[i]);
+    use_cuda(0);
+    return rc;
+}
+
+/* the head-layout helpers of the reference's CPU attention layer (src/core/attention/internal.h): the CPU
+   counterparts of the five layout slots.  op: 0 qkv_split (bias nullable), 1 interleave, 2 deinterleave, 3 qkv_merge. */
+#include "core/attention/internal.h"
+SHIM_API int ref_head_layout(int op, const float *a, const float *bias, float *h0, float *h1, float *h2, float *flat,
+                             int64_t B, int64_t S, int64_t H, int64_t dk)
+{
+    const int64_t D = H * dk;
+    if (op == 0 && bias) ax_attn_head_interleave_qkv_split_bias(a, bias, h0, h1, h2, B, S, H, dk, D);
+    else if (op == 0) ax_attn_head_interleave_qkv_split(a, h0, h1, h2, B, S, H, dk, D);
+    else if (op == 1) ax_attn_head_interleave(a, h0, B, S, H, dk);
+    else if (op == 2) ax_attn_head_deinterleave(a, flat, B, S, H, dk);
+    else ax_attn_head_deinterleave_qkv_merge(h0, h1, h2, flat, B, S, H, dk, D);
+    return 0;
+}
+
+/* ---- timing doors: the bench's CPU baselines ----------------------------------------------------------
+   Each builds its operands ONCE with the reference's constructors, then calls one reference entry point
+   warmup + iters times and writes the wall time of each of the last `iters` calls (CLOCK_MONOTONIC, as the
+   reference's own benchmarks do, benchmarks/bench_common.h:45-50) into secs[].  Nothing but the entry point is
+   inside a timed interval; the result of the last call is copied out afterwards so the caller can check it. */
+#include <time.h>
+
+static double now_s(void)
+{
+    struct timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return (double)ts.tv_sec + 1e-9 * (double)ts.tv_nsec;
+}
+
+/* ax_compute_gemm on the active CPU backend (cpu_opt) */
+SHIM_API int ref_time_gemm(const float *A, const float *B, float *C, int64_t M, int64_t N, int64_t K, int warmup,
+                           int iters, double *secs)
+{
+    ax_compute_set_backend(AX_BACKEND_CPU_SIMD);
+    ax_tensor_t *a = t2(A, M, K), *b = t2(B, K, N);
+    int64_t oshape[2] = { M, N };
+    ax_tensor_t *o = ax_tensor_zeros(oshape, 2, AX_FLOAT32);
+    if (!a || !b || !o) return 100;
+    int rc = 0;
+    for (int i = 0; i < warmup + iters && !rc; i++) {
+        const double t0 = now_s();
+        rc = (int)ax_compute_gemm(a, b, o);
+        if (i >= warmup) secs[i - warmup] = now_s() - t0;
+    }
+    if (!rc && C) memcpy(C, tdata(o), (size_t)(M * N) * sizeof(float));
+    ax_tensor_destroy(a); ax_tensor_destroy(b); ax_tensor_destroy(o);
+    return rc;
+}
+
+/* the dense-layer op ax_matmul_bias_relu (allocates its output, which is part of the op; freed outside the interval) */
+SHIM_API int ref_time_matmul_bias_relu(const float *A, const float *B, const float *bias, float *C, int64_t M, int64_t N,
+                                       int64_t K, int warmup, int iters, double *secs)
+{
+    ax_compute_set_backend(AX_BACKEND_CPU_SIMD);
+    ax_tensor_t *a = t2(A, M, K), *b = t2(B, K, N), *bs = t1(bias, N);
+    if (!a || !b || !bs) return 100;
+    int rc = 0;
+    for (int i = 0; i < warmup + iters && !rc; i++) {
+        const double t0 = now_s();
+        ax_tensor_t *o = ax_matmul_bias_relu(a, b, bs);
+        if (i >= warmup) secs[i - warmup] = now_s() - t0;
+        if (!o) { rc = 101; break; }
+        if (i == warmup + iters - 1 && C) memcpy(C, tdata(o), (size_t)(M * N) * sizeof(float));
+        ax_tensor_destroy(o);
+    }
+    ax_tensor_destroy(a); ax_tensor_destroy(b); ax_tensor_destroy(bs);
+    return rc;
+}
+
+/* dense + bias + GELU as the reference composes it (ax_compute_gemm, the column-bias loop of src/core/ops.c:359-364,
+   ax_gelu): all three steps are inside the interval */
+SHIM_API int ref_time_dense_gelu(const float *X, const float *W, const float *bias, float *Y, int64_t M, int64_t N,
+                                 int64_t K, int warmup, int iters, double *secs)
+{
+    ax_compute_set_backend(AX_BACKEND_CPU_SIMD);
+    ax_tensor_t *a = t2(X, M, K), *b = t2(W, K, N);
+    int64_t oshape[2] = { M, N };
+    ax_tensor_t *o = ax_tensor_zeros(oshape, 2, AX_FLOAT32);
+    if (!a || !b || !o) return 100;
+    int rc = 0;
+    for (int i = 0; i < warmup + iters && !rc; i++) {
+        const double t0 = now_s();
+        rc = (int)ax_compute_gemm(a, b, o);
+        float *od = tdata(o);
+        for (int64_t r = 0; r < M; r++)
+            for (int64_t j = 0; j < N; j++) od[r * N + j] += bias[j];
+        ax_tensor_t *y = ax_gelu(o);
+        if (i >= warmup) secs[i - warmup] = now_s() - t0;
+        if (!y) { rc = 101; break; }
+        if (i == warmup + iters - 1 && Y) memcpy(Y, tdata(y), (size_t)(M * N) * sizeof(float));
+        ax_tensor_destroy(y);
+    }
+    ax_tensor_destroy(a); ax_tensor_destroy(b); ax_tensor_destroy(o);
+    return rc;
+}
+
+SHIM_API int ref_time_qgemm_w8a32(const float *a, const int8_t *q, const float *scales, float *out, int64_t M, int64_t N,
+                                  int64_t K, int warmup, int iters, double *secs)
+{
+    ax_qweight_t qw;
+    qw.data = (int8_t *)q; qw.scales = (float *)scales; qw.N = N; qw.K = K;
+    int rc = 0;
+    for (int i = 0; i < warmup + iters && !rc; i++) {
+        const double t0 = now_s();
+        rc = (int)ax_qgemm_w8a32(a, &qw, out, M);
+        if (i >= warmup) secs[i - warmup] = now_s() - t0;
+    }
+    return rc;
+}
+
+SHIM_API int ref_time_sdpa_causal(const float *Q, const float *K, const float *V, float *O, float *L, int64_t BH,
+                                  int64_t S, int64_t dk, float scale, int warmup, int iters, double *secs)
+{
+    for (int i = 0; i < warmup + iters; i++) {
+        const double t0 = now_s();
+        ax_fused_attention_fwd_causal(Q, K, V, O, L, BH, S, dk, scale);
+        if (i >= warmup) secs[i - warmup] = now_s() - t0;
+    }
+    return 0;
+}

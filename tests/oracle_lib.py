@@ -34,9 +34,19 @@ def _p(a, typ):
     return a.ctypes.data_as(typ)
 
 
+def axiom_source_tree():
+    """Root of the axiom source tree the compiled reference is built from: $AXIOM_SRC, else a checkout named
+    `reference` beside this repository; None when neither exists (the prebuilt oracle/_ref is then used as it is)."""
+    for cand in (os.environ.get("AXIOM_SRC"), os.path.join(os.path.dirname(ROOT), "reference")):
+        if cand and os.path.exists(os.path.join(cand, "src", "compute", "dispatch.c")):
+            return cand
+    return None
+
+
 def build_oracle():
     """Compile oracle/liboracle.so (and oracle/_ref when the axiom tree exists)."""
-    subprocess.run(["make", "-C", ORACLE_DIR, "-j8", "all"], check=True,
+    src = axiom_source_tree()
+    subprocess.run(["make", "-C", ORACLE_DIR, "-j8", "all"] + ([f"AXIOM_SRC={src}"] if src else []), check=True,
                    stdout=subprocess.DEVNULL)
 
 
@@ -234,6 +244,43 @@ class Reference:
     def num_threads(self):
         return int(self.lib.ref_num_threads())
 
+    # ---- timing doors (bench CPU baselines): operands built once, only the entry point is timed -------------
+    def _timed(self, fn, args, warmup, iters):
+        secs = (C.c_double * iters)()
+        st = fn(*args, int(warmup), int(iters), secs)
+        assert st == 0, st
+        return list(secs)
+
+    def time_gemm(self, A, B, out, warmup, iters):
+        M, K = A.shape
+        N = B.shape[1]
+        return self._timed(self.lib.ref_time_gemm, [_p(A, _f32p), _p(B, _f32p), _p(out, _f32p), _i64(M), _i64(N), _i64(K)],
+                           warmup, iters)
+
+    def time_matmul_bias_relu(self, A, B, bias, out, warmup, iters):
+        M, K = A.shape
+        N = B.shape[1]
+        return self._timed(self.lib.ref_time_matmul_bias_relu,
+                           [_p(A, _f32p), _p(B, _f32p), _p(bias, _f32p), _p(out, _f32p), _i64(M), _i64(N), _i64(K)], warmup, iters)
+
+    def time_dense_gelu(self, X, W, bias, out, warmup, iters):
+        M, K = X.shape
+        N = W.shape[1]
+        return self._timed(self.lib.ref_time_dense_gelu,
+                           [_p(X, _f32p), _p(W, _f32p), _p(bias, _f32p), _p(out, _f32p), _i64(M), _i64(N), _i64(K)], warmup, iters)
+
+    def time_qgemm_w8a32(self, a, q, s, out, warmup, iters):
+        M, K = a.shape
+        N = q.shape[0]
+        return self._timed(self.lib.ref_time_qgemm_w8a32,
+                           [_p(a, _f32p), _p(q, _i8p), _p(s, _f32p), _p(out, _f32p), _i64(M), _i64(N), _i64(K)], warmup, iters)
+
+    def time_sdpa_causal(self, Q, K, V, O, L, scale, warmup, iters):
+        BH, S, dk = Q.shape
+        return self._timed(self.lib.ref_time_sdpa_causal,
+                           [_p(Q, _f32p), _p(K, _f32p), _p(V, _f32p), _p(O, _f32p), _p(L, _f32p), _i64(BH), _i64(S), _i64(dk),
+                            C.c_float(scale)], warmup, iters)
+
     def gemm(self, A, B, variant="nn", backend="opt"):
         v = {"nn": 0, "nt": 1, "tn": 2}[variant]
         M = A.shape[1] if v == 2 else A.shape[0]
@@ -343,6 +390,42 @@ class Reference:
         assert st == 0, st
         return outs
 
+    def mha_layer(self, x, W, b, H, causal, dOut=None, device=False, save_p=False):
+        """The reference's multi-head attention layer: x [B,S,D], W [4,D,D] = Wq,Wk,Wv,Wo, b [4,D] or None.
+        device=False: ax_mha_create + ax_layer_forward (+ ax_backward of sum(out*dOut)) on the CPU backend.
+        device=True: the layer's device call sequence through the dispatcher and the registered extension table.
+        Returns dict(out, dX, dW, db, P) with the gradients only when dOut is given."""
+        B, S, D = x.shape
+        out = np.zeros((B, S, D), np.float32)
+        dX = np.zeros((B, S, D), np.float32) if dOut is not None else None
+        dW = np.zeros((4, D, D), np.float32) if dOut is not None else None
+        db = np.zeros((4, D), np.float32) if dOut is not None and b is not None else None
+        P = np.zeros((B * H, S, S), np.float32) if device and save_p else None
+        args = [_p(x, _f32p), _p(W, _f32p), _p(b, _f32p), _i64(B), _i64(S), _i64(D), int(H), int(causal)]
+        if device:
+            st = self.lib.ref_device_mha_sequence(*args, int(save_p), _p(dOut, _f32p), _p(out, _f32p), _p(dX, _f32p),
+                                                  _p(dW, _f32p), _p(db, _f32p), _p(P, _f32p))
+        else:
+            st = self.lib.ref_mha_layer(*args, _p(dOut, _f32p), _p(out, _f32p), _p(dX, _f32p), _p(dW, _f32p), _p(db, _f32p))
+        return st, dict(out=out, dX=dX, dW=dW, db=db, P=P)
+
+    def head_layout(self, op, B, S, H, dk, flat=None, heads=None, bias=None):
+        """CPU layout helpers of the reference's attention layer. op: 'split' (flat [B*S,3D] -> 3 heads), 'interleave'
+        (flat [B*S,D] -> head), 'deinterleave' (head -> flat), 'merge' (3 heads -> flat [B*S,3D])."""
+        D = H * dk
+        hs = [np.zeros((B * H, S, dk), np.float32) for _ in range(3)]
+        code = {"split": 0, "interleave": 1, "deinterleave": 2, "merge": 3}[op]
+        if op in ("split", "interleave"):
+            self.lib.ref_head_layout(code, _p(flat, _f32p), _p(bias, _f32p), *[_p(h, _f32p) for h in hs], None,
+                                     _i64(B), _i64(S), _i64(H), _i64(dk))
+            return hs if op == "split" else hs[0]
+        out = np.zeros((B * S, D if op == "deinterleave" else 3 * D), np.float32)
+        if op == "deinterleave":
+            self.lib.ref_head_layout(code, _p(heads, _f32p), None, None, None, None, _p(out, _f32p), _i64(B), _i64(S), _i64(H), _i64(dk))
+        else:
+            self.lib.ref_head_layout(code, None, None, *[_p(h, _f32p) for h in heads], _p(out, _f32p), _i64(B), _i64(S), _i64(H), _i64(dk))
+        return out
+
     def kv_cache_attend(self, Kc, Vc, Qn, cur_len, scale):
         """Kc, Vc: cache-layout [BH, max_seq, dk]; the rows are appended token by token through the reference API."""
         BH, max_seq, dk = Kc.shape
@@ -353,6 +436,39 @@ class Reference:
                                           _i64(BH), _i64(cur_len), _i64(max_seq), _i64(dk), C.c_float(scale))
         assert st == 0, st
         return out
+
+
+def mha_f64(x, W, b, H, causal, dOut=None):
+    """Double-precision restatement of axiom's multi-head attention layer, forward and backward
+    (src/core/attention.c:121-464 and :560-900): x [B,S,D]; W [4,D,D] = Wq,Wk,Wv,Wo; b [4,D] or None.
+    Returns dict(out, dX, dW [4,D,D], db [4,D]); the gradients are those of sum(out * dOut)."""
+    B, S, D = x.shape
+    dk = D // H
+    X = x.reshape(B * S, D).astype(np.float64)
+    W = W.astype(np.float64)
+    bb = b.astype(np.float64) if b is not None else np.zeros((4, D))
+    heads = lambda t: t.reshape(B, S, H, dk).transpose(0, 2, 1, 3)
+    flat = lambda t: t.transpose(0, 2, 1, 3).reshape(B * S, D)
+    qh, kh, vh = (heads(X @ W[i] + bb[i]) for i in range(3))
+    s = qh @ kh.transpose(0, 1, 3, 2) / np.sqrt(dk)
+    if causal:
+        s = np.where(np.triu(np.ones((S, S), bool), 1), -np.inf, s)
+    p = np.exp(s - s.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    attn = flat(p @ vh)
+    res = dict(out=(attn @ W[3] + bb[3]).reshape(B, S, D), dX=None, dW=None, db=None, P=p.reshape(B * H, S, S))
+    if dOut is None:
+        return res
+    G = dOut.reshape(B * S, D).astype(np.float64)
+    doh = heads(G @ W[3].T)
+    dv = p.transpose(0, 1, 3, 2) @ doh
+    dp = doh @ vh.transpose(0, 1, 3, 2)
+    ds = p * (dp - (dp * p).sum(-1, keepdims=True)) / np.sqrt(dk)
+    dq, dkk, dv = flat(ds @ kh), flat(ds.transpose(0, 1, 3, 2) @ qh), flat(dv)
+    res["dX"] = (dq @ W[0].T + dkk @ W[1].T + dv @ W[2].T).reshape(B, S, D)
+    res["dW"] = np.stack([X.T @ dq, X.T @ dkk, X.T @ dv, attn.T @ G])
+    res["db"] = np.stack([dq.sum(0), dkk.sum(0), dv.sum(0), G.sum(0)])
+    return res
 
 
 def nerr(x, ref):

@@ -8,7 +8,9 @@ import textwrap
 import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-AXIOM_INCLUDE = os.environ.get("AXIOM_SRC", "/root/reference") + "/include"
+from oracle_lib import axiom_source_tree
+
+AXIOM_INCLUDE = os.path.join(axiom_source_tree() or "", "include")
 
 LAYOUT_CHECK = r"""
 #include <stddef.h>
@@ -34,6 +36,20 @@ SLOT(leaky_relu); SLOT(gelu_op); SLOT(swish_op); SLOT(adam_update); SLOT(sgd_upd
 SLOT(shutdown); SLOT(synchronize); SLOT(device_count); SLOT(storage_alloc); SLOT(storage_free); SLOT(memcpy_h2d);
 SLOT(memcpy_d2h); SLOT(memcpy_d2d);
 _Static_assert(sizeof(ax_cuda_extension_t) == sizeof(axb_ax_cuda_extension_t), "extension size");
+#define EXT(f) SAME(ax_cuda_extension_t, axb_ax_cuda_extension_t, f)
+EXT(head_interleave_qkv_split); EXT(head_interleave_qkv_split_bias); EXT(head_interleave); EXT(head_deinterleave);
+EXT(head_deinterleave_qkv_merge); EXT(qkv_cache_build); EXT(bias_cache_build); EXT(conv_gemm_batched);
+/* the slots are called through the reference's own prototypes: they must be assignable both ways */
+static void same_signatures(ax_cuda_extension_t *r, const axb_ax_cuda_extension_t *m)
+{
+    r->head_interleave_qkv_split = m->head_interleave_qkv_split;
+    r->head_interleave_qkv_split_bias = m->head_interleave_qkv_split_bias;
+    r->head_interleave = m->head_interleave;
+    r->head_deinterleave = m->head_deinterleave;
+    r->head_deinterleave_qkv_merge = m->head_deinterleave_qkv_merge;
+    r->qkv_cache_build = (ax_status_t (*)(float *, const float *, const float *, const float *, int64_t))m->qkv_cache_build;
+    r->bias_cache_build = (ax_status_t (*)(float *, const float *, const float *, const float *, int64_t))m->bias_cache_build;
+}
 SAME(ax_cuda_extension_t, axb_ax_cuda_extension_t, sdpa_fwd); SAME(ax_cuda_extension_t, axb_ax_cuda_extension_t, sdpa_bwd);
 SAME(ax_cuda_extension_t, axb_ax_cuda_extension_t, winograd_f23_prefer);
 _Static_assert(AX_FLOAT32 == AXB_AX_FLOAT32 && AX_DEVICE_CUDA == AXB_AX_DEVICE_CUDA && AX_BACKEND_CUDA == AXB_AX_BACKEND_CUDA, "enums");
@@ -53,7 +69,7 @@ def test_table_layout_matches_reference_headers(tmp_path):
         pytest.skip("axiom headers not present on this machine")
     src = tmp_path / "layout.c"
     src.write_text(LAYOUT_CHECK)
-    subprocess.run(["gcc", "-std=c11", "-I", AXIOM_INCLUDE, "-I", os.path.join(ROOT, "include"), "-c", str(src),
+    subprocess.run(["gcc", "-std=c11", "-Werror=incompatible-pointer-types", "-I", AXIOM_INCLUDE, "-I", os.path.join(ROOT, "include"), "-c", str(src),
                     "-o", str(tmp_path / "layout.o")], check=True)
 
 

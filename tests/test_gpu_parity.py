@@ -174,6 +174,14 @@ def test_elementwise_slots(engine, oracle, golden):
     engine.bias_add(xd, dev(bias_n), 1, xd)          # out may alias in
     np.testing.assert_array_equal(host(xd), oracle.bias_add_axis(X, bias_n, 1))
     np.testing.assert_array_equal(host(engine.relu(dev(X), out)), oracle.relu(X))
+    # any rank, any axis (the stock backend's rule, src/compute/backends/cuda/ops_fused.cu:268-292)
+    X3 = oracle.uniform((5, 7, 12), 8)
+    for axis in (0, 1, 2):
+        b = oracle.uniform((X3.shape[axis],), 9 + axis)
+        o3 = torch.empty(X3.shape, device="cuda")
+        shape = [1, 1, 1]
+        shape[axis] = -1
+        np.testing.assert_array_equal(host(engine.bias_add_nd(dev(X3), dev(b), axis, o3)), X3 + b.reshape(shape))
     gx = golden["gelu_x"]
     g = torch.empty(gx.shape, device="cuda")
     np.testing.assert_allclose(host(engine.gelu(dev(gx), g)), golden["gelu_y"], atol=2e-6)
@@ -231,7 +239,7 @@ def test_quantize_rows_bit_exact(engine, oracle, shape):
 
 
 @pytest.mark.parametrize("shape", [(1, 8, 8), (4, 16, 32), (8, 64, 128), (32, 128, 512), (16, 256, 1024), (512, 1024, 1024),
-                                   (1, 4096, 4096), (3, 1000, 2048), (8, 4096, 4096)])
+                                   (1, 4096, 4096), (3, 1000, 2048), (8, 4096, 4096), (512, 4096, 4096)])
 def test_w8a32_vs_oracle_and_golden(engine, oracle, golden, shape):
     M, N, K = shape
     a, w = oracle.uniform((M, K), 7), oracle.uniform((N, K), 13)
@@ -239,6 +247,10 @@ def test_w8a32_vs_oracle_and_golden(engine, oracle, golden, shape):
     out = torch.empty((M, N), device="cuda")
     engine.qgemm_w8a32(dev(a), dev(q), dev(s), out)
     got = host(out)
+    # axiom's own argument list (a, qw, out, M) with a host ax_qweight_t-layout struct: the same call
+    out_qw = torch.full((M, N), float("nan"), device="cuda")
+    engine.qgemm_w8a32_qw(dev(a), dev(q), dev(s), out_qw)
+    np.testing.assert_array_equal(host(out_qw), got)
     assert nerr(got, oracle.qgemm_w8a32_f64(a, q, s)) <= TOL_SPLIT
     tag = f"q_{M}_{N}_{K}_out"
     ref = golden[tag] if tag in golden.files else oracle.qgemm_w8a32(a, q, s)

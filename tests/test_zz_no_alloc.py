@@ -22,7 +22,8 @@ def dev(x):
     return torch.from_numpy(np.ascontiguousarray(x)).cuda()
 
 
-@pytest.mark.parametrize("shape", [(1, 4096, 4096), (8, 4096, 4096), (5, 1000, 777), (2, 512, 8192)])
+@pytest.mark.parametrize("shape", [(1, 4096, 4096), (8, 4096, 4096), (5, 1000, 777), (2, 512, 8192), (16, 4096, 4096),
+                                   (32, 4096, 4096), (9, 1000, 1028), (20, 1001, 777)])
 def test_static_scratch_matches_regular_entry_point(engine, oracle, shape):
     M, N, K = shape
     W = dev(oracle.normal((K, N), 13, sigma=1.0 / np.sqrt(K)))
@@ -33,8 +34,14 @@ def test_static_scratch_matches_regular_entry_point(engine, oracle, shape):
         want = torch.empty((M, N), device="cuda")
         engine.gemm_bias_act(x, W, bias, want, M, N, K, act="gelu")
         got = torch.full((M, N), float("nan"), device="cuda")
+        if call == 1:
+            torch.cuda.synchronize()
+            free_before = torch.cuda.mem_get_info()[0]
         engine.skinny_gemm_static(x, W, bias, got, M, N, K, act="gelu")
         torch.cuda.synchronize()
+        if call == 1:   # the kernel variant was loaded by the first call: the second changes nothing on the device
+            assert torch.cuda.mem_get_info()[0] == free_before
+        assert engine.skinny_gemm_static_error() == 0
         g, w = got.cpu().numpy(), want.cpu().numpy()
         assert nerr(g, w) <= 1e-5, (call, nerr(g, w))
         np.testing.assert_array_equal(g, w)
@@ -44,7 +51,7 @@ def test_static_scratch_matches_regular_entry_point(engine, oracle, shape):
 
 def test_static_scratch_refuses_oversized_shapes(engine):
     from axiom_b200.engine import EngineError
-    M, N, K = 32, 8192, 16384                                   # needs split-K scratch, and more than the 4 MiB array holds
+    M, N, K = 32, 8192, 16386                # K % 4 != 0 keeps it off the tensor-core kernel: split-K scratch beyond the 4 MiB array
     x = torch.zeros((M, K), device="cuda")
     W = torch.zeros((K, N), device="cuda")
     y = torch.zeros((M, N), device="cuda")
