@@ -43,6 +43,7 @@ struct Engine {
     int *sk_counters = nullptr;
     int sk_counter_cap = 0;
     int *err_word = nullptr;
+    int *gemm_counters = nullptr;   // split-K arrival counters of the tensor-core GEMM (zero between launches)
     int64_t launches = 0;
     // grow-only buffer for intermediate results a fused route cannot avoid (the unfused qkv projection)
     void *aux = nullptr;
@@ -61,6 +62,10 @@ struct Engine {
 };
 
 Engine g;
+
+// split-K scratch of the tensor-core GEMM: room for one partial tile per SM (148 x 128 x 256 fp32 < 20 MiB)
+constexpr size_t kSplitScratch = (size_t)20 << 20;
+constexpr int kSplitCounters = 1024;
 
 int fail(int status, const char *fmt, ...)
 {
@@ -120,6 +125,17 @@ struct Carver {
         return r;
     }
 };
+
+// the split-K scratch, carved behind a call's operand planes
+TcSplitK take_splitk(Carver &c)
+{
+    TcSplitK sk;
+    sk.scratch = c.take(kSplitScratch);
+    sk.scratch_bytes = kSplitScratch;
+    sk.counters = g.gemm_counters;
+    sk.n_counters = kSplitCounters;
+    return sk;
+}
 
 // planes of one fp32 operand, written by the split pre-pass
 struct SplitOperand {
@@ -191,9 +207,10 @@ int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int
     TcProducts prod;
     fp32_mode_plan(split_mode, kind, prod);
     const SplitOperand sa = plan_split(split_mode, M, K), sb = plan_split(split_mode, N, K);
-    int st = ensure_ws(sa.total() + sb.total());
+    int st = ensure_ws(sa.total() + sb.total() + kSplitScratch);
     if (st) return st;
     Carver carve{ (char *)g.ws };
+    const TcSplitK sk = take_splitk(carve);
     TcOperand opa, opb;
     mark(0);
     // A is [M,K] (k contiguous) unless trans_a, where it is stored [K,M];
@@ -220,7 +237,7 @@ int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int
         for (int i = 0; i < 3; ++i) ep.hs_out[i] = head_out[i];
     }
     mark(1);
-    e = launch_gemm_tc(kind, opa, opb, prod, M, N, K, ep, g.err_word, g.sm_count, g.stream);
+    e = launch_gemm_tc(kind, opa, opb, prod, M, N, K, ep, g.err_word, g.sm_count, g.stream, &sk);
     mark(2);
     g.launches++;
     if (e) return cuda_fail("tcgen05 gemm", e);
@@ -311,6 +328,8 @@ extern "C" int axb_init(int device)
     g.sm_count = prop.multiProcessorCount;
     if ((e = cudaMalloc(&g.err_word, sizeof(int))) != cudaSuccess) return cuda_fail("cudaMalloc", e);
     cudaMemset(g.err_word, 0, sizeof(int));
+    if ((e = cudaMalloc(&g.gemm_counters, kSplitCounters * sizeof(int))) != cudaSuccess) return cuda_fail("cudaMalloc", e);
+    cudaMemset(g.gemm_counters, 0, kSplitCounters * sizeof(int));
     const char *mode = getenv("AX_B200_FP32_MODE");
     if (mode) {
         if (!strcmp(mode, "bf16")) g.fp32_mode = AXB_FP32_BF16;
@@ -332,6 +351,7 @@ extern "C" void axb_shutdown(void)
     if (g.sk_partial) cudaFree(g.sk_partial);
     if (g.sk_counters) cudaFree(g.sk_counters);
     if (g.err_word) cudaFree(g.err_word);
+    if (g.gemm_counters) cudaFree(g.gemm_counters);
     if (g.hp_buf) cudaFree(g.hp_buf);
     if (g.aux) cudaFree(g.aux);
     if (g.hp_in) cudaStreamDestroy(g.hp_in);
@@ -624,6 +644,32 @@ extern "C" int axb_gemm_host(const float *A, const float *B, float *C, int64_t M
     // the route follows the whole problem, as in axb_gemm (M <= 32 is the bandwidth-bound route), so that a
     // short last chunk is computed exactly as its rows would be in one call over the whole matrix
     const bool tensor_path = M > 32;
+    {
+        // a problem small enough for axb_gemm to split K over several CTAs is not worth a pipeline, and its row
+        // blocks would add their partial sums in another order: upload, one axb_gemm, download
+        int sm, kd;
+        TcProducts pr;
+        fp32_mode_plan(sm, kd, pr);
+        if (tensor_path && gemm_tc_splits_k(kd, pr, M, N, K, g.sm_count)) {
+            const size_t ab = round_up((size_t)M * K * 4, 1024), bb = round_up((size_t)K * N * 4, 1024), cb = (size_t)M * N * 4;
+            if (ab + bb + cb > g.hp_bytes) {
+                cudaDeviceSynchronize();
+                if (g.hp_buf) cudaFree(g.hp_buf);
+                g.hp_buf = nullptr; g.hp_bytes = 0;
+                cudaError_t e = cudaMalloc(&g.hp_buf, ab + bb + cb);
+                if (e != cudaSuccess) return fail(AXB_ERR_ALLOC, "gemm_host: staging of %zu bytes: %s", ab + bb + cb, cudaGetErrorString(e));
+                g.hp_bytes = ab + bb + cb;
+            }
+            float *dA = (float *)g.hp_buf, *dB = (float *)((char *)g.hp_buf + ab), *dC = (float *)((char *)g.hp_buf + ab + bb);
+            cudaMemcpyAsync(dA, A, (size_t)M * K * 4, cudaMemcpyHostToDevice, g.stream);
+            cudaMemcpyAsync(dB, B, (size_t)K * N * 4, cudaMemcpyHostToDevice, g.stream);
+            st = axb_gemm(dA, dB, dC, M, N, K);
+            if (st) { cudaStreamSynchronize(g.stream); return st; }
+            cudaMemcpyAsync(C, dC, cb, cudaMemcpyDeviceToHost, g.stream);
+            cudaError_t ce = cudaStreamSynchronize(g.stream);
+            return ce == cudaSuccess ? AXB_OK : cuda_fail("gemm_host", ce);
+        }
+    }
     // default: about 16 chunks (a short tail after the last upload), whole 128-row tiles, 256..1024 rows
     int64_t rc = row_chunk;
     if (rc <= 0) {
@@ -820,9 +866,10 @@ extern "C" int axb_qdense_w8a32(const float *a, const int8_t *q, const float *sc
         // activations as four int8 digit planes [4][M][K] = the A operand of one int8 GEMM against the weights as they
         // are; the s32 result [4M, N] is recombined with 64-bit integers (exact), then scale, bias, activation
         const size_t dig_bytes = (size_t)4 * M * K, acc_bytes = (size_t)4 * M * N * sizeof(int32_t);
-        st = ensure_ws(round_up((size_t)M * sizeof(float), 1024) + round_up(dig_bytes, 1024) + round_up(acc_bytes, 1024));
+        st = ensure_ws(round_up((size_t)M * sizeof(float), 1024) + round_up(dig_bytes, 1024) + round_up(acc_bytes, 1024) + kSplitScratch);
         if (st) return st;
         Carver carve{ (char *)g.ws };
+        const TcSplitK sk = take_splitk(carve);
         float *inv_s = (float *)carve.take((size_t)M * sizeof(float));
         int8_t *digits = (int8_t *)carve.take(dig_bytes);
         int32_t *acc = (int32_t *)carve.take(acc_bytes);
@@ -842,7 +889,7 @@ extern "C" int axb_qdense_w8a32(const float *a, const int8_t *q, const float *sc
         ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = nullptr; ep.colscale = nullptr; ep.act = ACT_NONE;
         ep.out_mode = OUT_S32_ONLY; ep.C = nullptr; ep.acc_out = acc; ep.ldc = N;
         mark(1);
-        e = launch_gemm_tc(KIND_I8, opa, opb, prod, 4 * M, N, K, ep, g.err_word, g.sm_count, g.stream);
+        e = launch_gemm_tc(KIND_I8, opa, opb, prod, 4 * M, N, K, ep, g.err_word, g.sm_count, g.stream, &sk);
         g.launches++;
         if (e) return cuda_fail("w8a32 digit gemm", e);
         e = launch_qx_combine(acc, inv_s, scales, bias, act, out, M, N, g.sm_count, g.stream);
@@ -899,20 +946,15 @@ extern "C" int axb_qgemm_w8a8(const int8_t *a_q, float a_scale, const int8_t *b_
     const bool a_direct = (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(a_q) & 15) == 0);
     const bool b_direct = (K % 16 == 0) && ((reinterpret_cast<uintptr_t>(b_q) & 15) == 0);
     const int64_t pitch = (int64_t)round_up((size_t)K, 16);
-    size_t need = round_up((size_t)N * sizeof(float), 1024);
+    size_t need = kSplitScratch;
     if (!a_direct) need += round_up((size_t)M * pitch, 1024);
     if (!b_direct) need += round_up((size_t)N * pitch, 1024);
     st = ensure_ws(need);
     if (st) return st;
     Carver carve{ (char *)g.ws };
-    float *mult = (float *)carve.take((size_t)N * sizeof(float));
+    const TcSplitK sk = take_splitk(carve);
     int e;
     mark(0);
-    if (out_q) {
-        e = requant_mult(a_scale, b_scales, out_scale, N, mult, g.stream);
-        g.launches++;
-        if (e) return cuda_fail("requant multiplier", e);
-    }
     TcOperand opa, opb;
     opa.nplanes = opb.nplanes = 1;
     opa.rows = M; opb.rows = N;
@@ -937,10 +979,12 @@ extern "C" int axb_qgemm_w8a8(const int8_t *a_q, float a_scale, const int8_t *b_
     prod.n = 1;
     TcEpilogue ep;
     ep.n_extra = 0;
-    ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = nullptr; ep.colscale = mult; ep.act = ACT_NONE;
+    // the requantisation multiplier (a_scale * b_scales[n]) / out_scale is formed in the epilogue, rounding for rounding
+    ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = nullptr; ep.colscale = b_scales; ep.act = ACT_NONE;
+    ep.rq_a_scale = a_scale; ep.rq_out_scale = out_scale;
     ep.out_mode = out_q ? OUT_I8_REQUANT : OUT_S32_ONLY; ep.C = out_q; ep.acc_out = acc_out; ep.ldc = N;
     mark(1);
-    e = launch_gemm_tc(KIND_I8, opa, opb, prod, M, N, K, ep, g.err_word, g.sm_count, g.stream);
+    e = launch_gemm_tc(KIND_I8, opa, opb, prod, M, N, K, ep, g.err_word, g.sm_count, g.stream, &sk);
     mark(2);
     g.launches++;
     return e ? cuda_fail("w8a8 gemm", e) : AXB_OK;
@@ -1034,9 +1078,10 @@ extern "C" int axb_conv_gemm(const float *weight, const float *input, int64_t C_
     TcProducts prod;
     fp32_mode_plan(split_mode, kind, prod);
     const SplitOperand sa = plan_split(split_mode, C_out, K), sb = plan_split(split_mode, P, K);
-    st = ensure_ws(sa.total() + sb.total());
+    st = ensure_ws(sa.total() + sb.total() + kSplitScratch);
     if (st) return st;
     Carver carve{ (char *)g.ws };
+    const TcSplitK sk = take_splitk(carve);
     TcOperand opa, opb;
     mark(0);
     int e = run_split(sa, weight, K, false, carve, opa);
@@ -1056,7 +1101,7 @@ extern "C" int axb_conv_gemm(const float *weight, const float *input, int64_t C_
     ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = nullptr; ep.colscale = nullptr; ep.act = ACT_NONE;
     ep.out_mode = OUT_F32; ep.C = out; ep.acc_out = nullptr; ep.ldc = P; ep.n_extra = 0;
     mark(1);
-    e = launch_gemm_tc(kind, opa, opb, prod, C_out, P, K, ep, g.err_word, g.sm_count, g.stream);
+    e = launch_gemm_tc(kind, opa, opb, prod, C_out, P, K, ep, g.err_word, g.sm_count, g.stream, &sk);
     mark(2);
     g.launches++;
     return e ? cuda_fail("conv_gemm", e) : AXB_OK;

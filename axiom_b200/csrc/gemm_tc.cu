@@ -35,7 +35,10 @@
 
 namespace axb {
 
-template <int KIND, int BN, int SWB, int NPROD>
+
+// SPLITK: compiled with the split-K hand-over (KernelArgs::ksplit > 1 allowed); the plain variant keeps the
+// epilogue's registers for itself.
+template <int KIND, int BN, int SWB, int NPROD, bool SPLITK>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ KernelArgs p)
 {
@@ -61,6 +64,8 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int total_tiles = p.m_tiles * p.n_tiles;
+    const int ksplit_all = SPLITK ? p.ksplit : 1;
+    const int items = total_tiles * ksplit_all;   // work item = (tile, K-slice); one slice per tile unless K is split
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
@@ -72,6 +77,8 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
             mbar_init(bar_tempty + 8 * a, 8);
         }
         mbar_fence_init();
+        *reinterpret_cast<volatile int *>(gen_base + HDR_SK_DEAD) = 0;
+        *reinterpret_cast<volatile int *>(gen_base + HDR_SK_LAST) = 0;
         for (int i = 0; i < p.npa; ++i) tma_prefetch_desc(&tm.a[i]);
         for (int i = 0; i < p.npb; ++i) tma_prefetch_desc(&tm.b[i]);
     }
@@ -94,13 +101,15 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
             // has to turn a stage around faster than the tensor pipe drains one
             uint32_t s = 0, ph = 0;
             bool ok = true;
-            const int k_blocks = p.k_blocks, stages = p.stages, npa = p.npa, npb = p.npb;
+            const int k_blocks = p.k_blocks, stages = p.stages, npa = p.npa, npb = p.npb, ksplit = ksplit_all;
             const uint32_t sbytes = (uint32_t)stage_bytes;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            grid_dep_wait();   // the operand planes come from the kernel before this one
+            for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+                const int t = w / ksplit, kb_lo = (w - t * ksplit) * p.kb_per_slice, kb_hi = min(k_blocks, kb_lo + p.kb_per_slice);
                 int mt, nt;
                 tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
                 const int row_a = mt * BM, row_b = nt * BN;
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                for (int kb = kb_lo; kb < kb_hi; ++kb) {
                     if (!mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1u)) {
                         report(p.err, ERR_PRODUCER_WAIT);
                         ok = false;
@@ -138,12 +147,13 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
             uint32_t s = 0, ph = 0, vt = 0;
             bool ok = true;
             // everything the issue loop needs lives in registers
-            const int k_blocks = p.k_blocks, chunk_kb = p.chunk_kb, stages = p.stages;
+            const int k_blocks = p.k_blocks, chunk_kb = p.chunk_kb, stages = p.stages, ksplit = ksplit_all;
             const uint32_t prod_a = p.prod_a, prod_b = p.prod_b;
             const uint64_t desc_hi = smem_desc_kmajor(0, SWB);
             const uint32_t npa_bytes = p.npa * A_BYTES, sbytes = (uint32_t)stage_bytes;
-            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += chunk_kb, ++vt) {
+            for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+                const int kb_lo = (w % ksplit) * p.kb_per_slice, kb_hi = min(k_blocks, kb_lo + p.kb_per_slice);
+                for (int kb0 = kb_lo; kb0 < kb_hi && ok; kb0 += chunk_kb, ++vt) {
                     const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
                     if (!mbar_wait_bounded(bar_tempty + 8 * acc, aph ^ 1u)) {
                         report(p.err, ERR_MMA_WAIT_TMEM);
@@ -152,7 +162,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
                     }
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + acc * BN;
-                    const int kb1 = min(k_blocks, kb0 + chunk_kb);
+                    const int kb1 = min(kb_hi, kb0 + chunk_kb);
                     for (int kb = kb0; kb < kb1; ++kb) {
                         if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
                             report(p.err, ERR_MMA_WAIT_FULL);
@@ -181,11 +191,14 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
         constexpr int PIECES = HALF / 32;
         const int q = warp & 3;
         const int half = (warp - 2) >> 2;
-        const int nchunks = (p.k_blocks + p.chunk_kb - 1) / p.chunk_kb;
         uint32_t vt = 0;
         bool alive = true;
         const bool rows_aligned = KIND != KIND_I8 && epi_rows_aligned(p);
-        for (int t = blockIdx.x; t < total_tiles && alive; t += gridDim.x) {
+        const int ksplit = ksplit_all;
+        for (int w = blockIdx.x; w < items && alive; w += gridDim.x) {
+            const int t = w / ksplit, slice = w - t * ksplit;
+            const int kb_lo = slice * p.kb_per_slice, kb_hi = min(p.k_blocks, kb_lo + p.kb_per_slice);
+            const int nchunks = (kb_hi - kb_lo + p.chunk_kb - 1) / p.chunk_kb;
             int mt, nt;
             tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
             const long long row = (long long)mt * BM + q * 32 + lane;
@@ -194,75 +207,71 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
             const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16) + half * HALF;
 
             if constexpr (KIND == KIND_I8) {
-                // one chunk, exact integers: stream 32 columns at a time
+                // one chunk, exact integers
                 const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
                 ++vt;
-                const bool got = mbar_wait_warp_bounded(bar_tfull + 8 * acc, aph);
-                if (!__all_sync(0xffffffffu, got)) {
-                    report(p.err, ERR_EPI_WAIT);
-                    alive = false;
-                    break;
-                }
+                const bool got = __all_sync(0xffffffffu, mbar_wait_warp_bounded(bar_tfull + 8 * acc, aph));
+                if (!got) report(p.err, ERR_EPI_WAIT);
                 tc_fence_after_sync();
+                if (!SPLITK || ksplit == 1) {
+                    if (!got) {
+                        alive = false;
+                        break;
+                    }
+                    // stream 32 columns at a time
 #pragma unroll 1
-                for (int c = 0; c < PIECES; ++c) {
-                    const int col0 = col_base + c * 32;
-                    if (col0 >= p.N) break;  // warp-uniform
-                    uint32_t r[32];
-                    __syncwarp();  // the TMEM load is warp-collective: reconverge after masked stores
-                    tmem_ld_32x32(lane_addr + acc * BN + c * 32, r);
-                    tmem_ld_wait();
-                    const bool full = col0 + 32 <= p.N;
-                    if (row_ok) {
-                        if (p.acc_out) {
-                            int32_t *dst = p.acc_out + row * p.ldc + col0;
-                            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+                    for (int c = 0; c < PIECES; ++c) {
+                        const int col0 = col_base + c * 32;
+                        if (col0 >= p.N) break;  // warp-uniform
+                        uint32_t r[32];
+                        __syncwarp();  // the TMEM load is warp-collective: reconverge after masked stores
+                        tmem_ld_32x32(lane_addr + acc * BN + c * 32, r);
+                        tmem_ld_wait();
+                        store_piece_i8(p, reinterpret_cast<const int *>(r), row, row_ok, col0);
+                    }
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+                } else if constexpr (SPLITK) {
+                    // K is split: the whole partial row goes through the hand-over, the last slice stores
+                    int v[HALF];
+                    if (got) {
 #pragma unroll
-                                for (int j = 0; j < 32; j += 4)
-                                    *reinterpret_cast<int4 *>(dst + j) =
-                                        make_int4((int)r[j], (int)r[j + 1], (int)r[j + 2], (int)r[j + 3]);
-                            } else {
-                                for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = (int32_t)r[j];
-                            }
+                        for (int c = 0; c < PIECES; ++c) {
+                            uint32_t r[32];
+                            tmem_ld_32x32(lane_addr + acc * BN + c * 32, r);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) v[c * 32 + j] = (int)r[j];
                         }
-                        if (p.out_mode == OUT_I8_REQUANT) {
-                            int8_t *dst = reinterpret_cast<int8_t *>(p.C) + row * p.ldc + col0;
-                            uint32_t packed[8];
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
+                    }
+                    const int st = splitk_exchange<int, HALF>(p, v, t, slice, warp, lane, gen_base, got);
+                    if (st == SK_DEAD) {
+                        alive = false;
+                        break;
+                    }
+                    if (st == SK_LAST) {
 #pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const float mult = (col0 + j < p.N) ? __ldg(p.colscale + col0 + j) : 0.0f;
-                                const float y = __fmul_rn(__int2float_rn((int32_t)r[j]), mult);
-                                int v = __float2int_rn(y);
-                                v = max(-127, min(127, v));
-                                if ((j & 3) == 0) packed[j >> 2] = 0;
-                                packed[j >> 2] |= (uint32_t)(v & 0xff) << (8 * (j & 3));
-                            }
-                            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-                                *reinterpret_cast<uint4 *>(dst) =
-                                    make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                                *reinterpret_cast<uint4 *>(dst + 16) =
-                                    make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                            } else {
-                                for (int j = 0; j < 32 && col0 + j < p.N; ++j)
-                                    dst[j] = (int8_t)((packed[j >> 2] >> (8 * (j & 3))) & 0xff);
-                            }
+                        for (int c = 0; c < PIECES; ++c) {
+                            const int col0 = col_base + c * 32;
+                            if (col0 < p.N) store_piece_i8(p, &v[c * 32], row, row_ok, col0);
                         }
                     }
                 }
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
             } else {
                 // fp32 kinds: add the chunks up in registers, then the fused epilogue
                 float sum[HALF];
 #pragma unroll
                 for (int j = 0; j < HALF; ++j) sum[j] = 0.0f;
+                bool got = true;
                 for (int ch = 0; ch < nchunks; ++ch, ++vt) {
                     const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
-                    const bool got = mbar_wait_warp_bounded(bar_tfull + 8 * acc, aph);
-                    if (!__all_sync(0xffffffffu, got)) {
+                    if (!__all_sync(0xffffffffu, mbar_wait_warp_bounded(bar_tfull + 8 * acc, aph))) {
                         report(p.err, ERR_EPI_WAIT);
-                        alive = false;
+                        got = false;
                         break;
                     }
                     tc_fence_after_sync();
@@ -278,7 +287,19 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
                 }
-                if (!alive) break;
+                if (SPLITK && ksplit > 1) {
+                    if constexpr (SPLITK) {
+                        const int st = splitk_exchange<float, HALF>(p, sum, t, slice, warp, lane, gen_base, got);
+                        if (st == SK_DEAD) {
+                            alive = false;
+                            break;
+                        }
+                        if (st == SK_NOT_LAST) continue;
+                    }
+                } else if (!got) {
+                    alive = false;
+                    break;
+                }
                 {
                     // sums -> this warp's staging tile (row = lane) -> fused epilogue and whole-line stores
                     float4 *stg = reinterpret_cast<float4 *>(gen_base + HEADER_BYTES + (size_t)p.stages * stage_bytes) + (warp - 2) * 256;
@@ -303,7 +324,9 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
         }
     }
 
-    if (p.tma_store && warp >= 2 && warp < B_PRODUCER_WARP && lane == 0) tma_store_wait_all();
+    // the staging tiles must have been read before the shared memory goes away; the global writes themselves are
+    // complete when the kernel is
+    if (p.tma_store && warp >= 2 && warp < B_PRODUCER_WARP && lane == 0) tma_store_wait_read();
 
     // ---------------------------------------------------------------- teardown
     // After a wait that ran out, give copies still in flight time to land in
@@ -474,7 +497,7 @@ static int encode_f32_store_tmap(CUtensorMap *out, float *ptr, int64_t rows, int
     return 0;
 }
 
-template <int KIND, int BN, int SWB, int NPROD>
+template <int KIND, int BN, int SWB, int NPROD, bool SPLITK>
 static int launch_inst(const TmapPack &tm, KernelArgs &ka, int stage_bytes, int grid, cudaStream_t stream)
 {
     constexpr int STAGING = KIND == KIND_I8 ? 0 : EPI_STAGING_BYTES;
@@ -486,7 +509,7 @@ static int launch_inst(const TmapPack &tm, KernelArgs &ka, int stage_bytes, int 
     }
     ka.stages = stages;
     const int smem = HEADER_BYTES + 1024 + stages * stage_bytes + STAGING;
-    auto kern = gemm_tc_kernel<KIND, BN, SWB, NPROD>;
+    auto kern = gemm_tc_kernel<KIND, BN, SWB, NPROD, SPLITK>;
     static PerDeviceOnce once;
     if (once.first()) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BUDGET);
@@ -495,8 +518,20 @@ static int launch_inst(const TmapPack &tm, KernelArgs &ka, int stage_bytes, int 
             return (int)e;
         }
     }
-    kern<<<grid, NUM_THREADS, smem, stream>>>(tm, ka);
-    cudaError_t e = cudaGetLastError();
+    // programmatic dependent launch: when the kernel before this one in the stream is the operand pre-pass (which
+    // releases its dependents as it starts), the barrier set-up and the TMEM allocation run under the pre-pass's
+    // tail; the TMA producers wait for the pre-pass to have finished before the first load
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tm, ka);
     if (e != cudaSuccess) snprintf(g_err, sizeof g_err, "gemm_tc launch: %s", cudaGetErrorString(e));
     return (int)e;
 }
@@ -505,16 +540,101 @@ template <int KIND, int SWB, int NPROD>
 static int launch_bn(int bn, const TmapPack &tm, KernelArgs &ka, int npa, int npb, int grid, cudaStream_t st)
 {
     const int sb = npa * BM * SWB + npb * bn * SWB;
+    // K is split only on 128- and 64-column tiles (a problem that takes 256-column tiles has enough of them)
+    const bool split = ka.ksplit > 1;
     switch (bn) {
-    case 256: return launch_inst<KIND, 256, SWB, NPROD>(tm, ka, sb, grid, st);
-    case 128: return launch_inst<KIND, 128, SWB, NPROD>(tm, ka, sb, grid, st);
-    default: return launch_inst<KIND, 64, SWB, NPROD>(tm, ka, sb, grid, st);
+    case 256: return launch_inst<KIND, 256, SWB, NPROD, false>(tm, ka, sb, grid, st);
+    case 128: return split ? launch_inst<KIND, 128, SWB, NPROD, true>(tm, ka, sb, grid, st)
+                           : launch_inst<KIND, 128, SWB, NPROD, false>(tm, ka, sb, grid, st);
+    default: return split ? launch_inst<KIND, 64, SWB, NPROD, true>(tm, ka, sb, grid, st)
+                          : launch_inst<KIND, 64, SWB, NPROD, false>(tm, ka, sb, grid, st);
     }
+}
+
+// How a problem is cut into work: tile shape, stage width, accumulator chunks and K-slices.
+struct TcPlan {
+    int bn;            // tile columns (256 for CTA pairs)
+    bool pair;         // CTA pairs on 256 x 256 tiles (gemm_tc2.cu)
+    int64_t mt, nt;    // tiles along M (of 256 rows for pairs) and along N
+    int swb;           // bytes of K per stage row
+    int k_blocks, chunk_kb;
+    int ksplit, kb_per_slice;
+};
+
+
+static TcPlan make_plan(int kind, const TcProducts &prod, int64_t M, int64_t N, int64_t K, int sm_count, const TcSplitK *splitk)
+{
+    TcPlan pl;
+    const bool can_split = splitk && splitk->scratch && splitk->counters;
+    // Tile shape.  CTA pairs when there are enough 256 x 256 tiles to fill the machine.  Otherwise one CTA per
+    // 128 x bn tile; with split-K available the tile stays 128 columns wide and K is cut instead (every halving of
+    // the width adds operand traffic — the A panel is loaded once per column tile — and an N = 64 MMA runs the
+    // tensor pipe at two thirds of its rate); without it a width is given up only when it would leave more than half
+    // of the SMs without a tile.
+    int64_t mt = (M + BM - 1) / BM;
+    int bn = 256;
+    if (mt * ((N + 255) / 256) * 2 < sm_count) bn = 128;
+    if (!can_split && bn == 128 && mt * ((N + 127) / 128) * 2 < sm_count) bn = 64;
+    if (N <= 64) bn = 64;
+    else if (N <= 128 && bn > 128) bn = 128;
+    bool use_pair = ((M + 255) / 256) * ((N + 255) / 256) >= sm_count / 2 && N >= 256 && M >= 256;
+    if (use_pair) {
+        bn = 256;
+        mt = (M + 255) / 256;
+    }
+    pl.bn = bn;
+    pl.pair = use_pair;
+    pl.mt = mt;
+    pl.nt = (N + bn - 1) / bn;
+    // 128-byte rows everywhere (fewer, larger stages: half the TMA and barrier traffic per unit of K) except
+    // for the split-precision modes on single-CTA 128 x 256 tiles, where four operand planes of 128-byte rows
+    // would leave a two-stage ring: those take 64-byte rows and keep four stages.
+    pl.swb = (kind != KIND_I8 && prod.n > 1 && !use_pair && bn == 256) ? 64 : 128;
+    const int es = kind == KIND_TF32 ? 4 : (kind == KIND_BF16 ? 2 : 1);
+    const int bke = pl.swb / es;
+    pl.k_blocks = (int)((K + bke - 1) / bke);
+    pl.chunk_kb = pl.k_blocks;
+    if (kind != KIND_I8 && prod.chunk_k > 0) {
+        pl.chunk_kb = prod.chunk_k / bke;
+        if (pl.chunk_kb < 1) pl.chunk_kb = 1;
+        if (pl.chunk_kb > pl.k_blocks) pl.chunk_kb = pl.k_blocks;
+    }
+    // split-K: when the tiles would leave at least half of the SMs idle, K is cut into slices of whole accumulator
+    // chunks (so the arithmetic of a slice is that of the same k range in an unsplit run) and tile x slice items fill
+    // the machine; the partial tiles meet in scratch (splitk_exchange)
+    pl.ksplit = 1;
+    pl.kb_per_slice = pl.k_blocks;
+    const int64_t tiles = pl.mt * pl.nt;
+    const int64_t slots = sm_count;   // CTAs that run at once
+    // (CTA pairs never split: measured, a problem with that few 256 x 256 tiles is faster on single-CTA tiles)
+    if (can_split && !use_pair && bn <= 128 && tiles * 2 <= slots) {
+        const int unit = (kind != KIND_I8 && pl.chunk_kb < pl.k_blocks) ? pl.chunk_kb : 4;   // k-blocks a slice is made of
+        const int64_t units = (pl.k_blocks + unit - 1) / unit;
+        const size_t slice_bytes = (size_t)BM * bn * 4;
+        int64_t want = slots / tiles;
+        if (want > units) want = units;
+        if (want > 8) want = 8;
+        const int64_t fit = (int64_t)(splitk->scratch_bytes / (slice_bytes * (size_t)tiles));
+        if (want > fit) want = fit;
+        if (tiles > splitk->n_counters) want = 1;
+        if (want >= 2) {
+            pl.kb_per_slice = (int)((units + want - 1) / want) * unit;
+            pl.ksplit = (pl.k_blocks + pl.kb_per_slice - 1) / pl.kb_per_slice;
+        }
+    }
+    return pl;
+}
+
+bool gemm_tc_splits_k(int kind, const TcProducts &prod, int64_t M, int64_t N, int64_t K, int sm_count)
+{
+    static int dummy_counter;
+    const TcSplitK any = { &dummy_counter, (size_t)1 << 40, &dummy_counter, 1 << 30 };
+    return make_plan(kind, prod, M, N, K, sm_count, &any).ksplit > 1;
 }
 
 int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcProducts &prod,
                    int64_t M, int64_t N, int64_t K, const TcEpilogue &ep, int *err_word,
-                   int sm_count, cudaStream_t stream)
+                   int sm_count, cudaStream_t stream, const TcSplitK *splitk)
 {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || A.nplanes < 1 || B.nplanes < 1 || A.nplanes > TC_MAX_PLANES || B.nplanes > TC_MAX_PLANES ||
@@ -522,31 +642,10 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
         snprintf(g_err, sizeof g_err, "launch_gemm_tc: bad operand description");
         return (int)cudaErrorInvalidValue;
     }
-    // Column-tile width: narrower tiles let more SMs take part in a small problem, but every halving of the width
-    // adds operand traffic (the A panel is loaded once per column tile) and the small problems are bound by what one
-    // SM can pull from L2: a width is given up only when it would leave more than half of the SMs without a tile
-    // (int8 512 x 4096 x 4096: 20.7 us at 128 columns, 28.2 at 64, 24.8 at 256).
-    int64_t mt = (M + BM - 1) / BM;
-    int bn = 256;
-    if (mt * ((N + 255) / 256) * 2 < sm_count) bn = 128;
-    if (bn == 128 && mt * ((N + 127) / 128) * 2 < sm_count) bn = 64;
-    if (N <= 64) bn = 64;
-    else if (N <= 128 && bn > 128) bn = 128;
-    // CTA pairs (256 x 256 tiles, gemm_tc2.cu) when there are enough such tiles to fill the machine
-    const bool use_pair = ((M + 255) / 256) * ((N + 255) / 256) >= sm_count / 2 && N >= 256 && M >= 256;
-    if (use_pair) {
-        bn = 256;
-        mt = (M + 255) / 256;
-    }
-    const int64_t nt = (N + bn - 1) / bn;
-    const int planes = A.nplanes + B.nplanes;
-    // 128-byte rows everywhere (fewer, larger stages: half the TMA and barrier traffic per unit of K) except
-    // for the split-precision modes on single-CTA 128 x 256 tiles, where four operand planes of 128-byte rows
-    // would leave a two-stage ring: those take 64-byte rows and keep four stages.
-    const int swb = (kind != KIND_I8 && prod.n > 1 && !use_pair && bn == 256) ? 64 : 128;
-    (void)planes;
-    const int es = kind == KIND_TF32 ? 4 : (kind == KIND_BF16 ? 2 : 1);
-    const int bke = swb / es;
+    const TcPlan pl = make_plan(kind, prod, M, N, K, sm_count, splitk);
+    const int bn = pl.bn, swb = pl.swb;
+    const bool use_pair = pl.pair;
+    const int64_t mt = pl.mt, nt = pl.nt;
 
     TmapPack tm;
     memset(&tm, 0, sizeof tm);
@@ -567,14 +666,16 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
         ka.prod_b |= (uint32_t)(prod.b[i] & 15) << (4 * i);
     }
     ka.m_tiles = (int)mt; ka.n_tiles = (int)nt;
-    ka.k_blocks = (int)((K + bke - 1) / bke);
-    ka.chunk_kb = ka.k_blocks;
-    if (kind != KIND_I8 && prod.chunk_k > 0) {
-        ka.chunk_kb = prod.chunk_k / bke;
-        if (ka.chunk_kb < 1) ka.chunk_kb = 1;
-        if (ka.chunk_kb > ka.k_blocks) ka.chunk_kb = ka.k_blocks;
+    ka.k_blocks = pl.k_blocks;
+    ka.chunk_kb = pl.chunk_kb;
+    ka.ksplit = pl.ksplit;
+    ka.kb_per_slice = pl.kb_per_slice;
+    if (pl.ksplit > 1) {
+        ka.sk_scratch = splitk->scratch;
+        ka.sk_counters = splitk->counters;
     }
     ka.alpha = ep.alpha; ka.beta = ep.beta; ka.bias = ep.bias; ka.colscale = ep.colscale;
+    ka.rq_a_scale = ep.rq_a_scale; ka.rq_out_scale = ep.rq_out_scale;
     ka.act = ep.act; ka.out_mode = ep.out_mode; ka.C = ep.C; ka.acc_out = ep.acc_out;
     ka.ldc = ep.ldc; ka.err = err_word;
     ka.n_extra = ep.n_extra < 0 ? 0 : (ep.n_extra > TC_MAX_EXTRA ? TC_MAX_EXTRA : ep.n_extra);
@@ -592,8 +693,8 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
         if (e) return e;
         ka.tma_store = 1;
     }
-    const int64_t tiles = mt * nt;
-    const int grid = (int)(tiles < sm_count ? tiles : sm_count);
+    const int64_t work = mt * nt * ka.ksplit;
+    const int grid = (int)(work < sm_count ? work : sm_count);
     if (use_pair)
         return launch_gemm_tc_pair(kind, swb, prod.n, tm, ka, A.nplanes, B.nplanes, sm_count, stream, g_err, sizeof g_err);
 

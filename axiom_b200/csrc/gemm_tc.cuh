@@ -22,7 +22,8 @@ struct TcOperand {
 struct TcEpilogue {
     float alpha, beta;      // f32 kinds: v = alpha * acc (* colscale[n]) (+ beta * C) (+ bias[n]) -> act
     const float *bias;      // [N] or null
-    const float *colscale;  // [N] or null; int8 requant: the per-column multiplier
+    const float *colscale;  // [N] or null; int8 requant: the per-column weight scales b_scales[n]
+    float rq_a_scale = 1.0f, rq_out_scale = 1.0f;   // int8 requant: out = clamp(rint(acc * ((rq_a_scale * colscale[n]) / rq_out_scale)))
     int act;                // ACT_*
     int out_mode;           // OUT_*
     void *C;                // float* (OUT_F32) / int8_t* (OUT_I8_REQUANT) / unused
@@ -48,11 +49,24 @@ struct TcProducts {
     int chunk_k;
 };
 
+// Scratch the core may use to split K over several CTAs of one output tile (problems with too few tiles to fill
+// the GPU).  counters must be zero on entry and are left zero.  A null pointer switches splitting off.
+struct TcSplitK {
+    void *scratch;
+    size_t scratch_bytes;
+    int *counters;
+    int n_counters;
+};
+
 // kind: MmaKind (0 tf32, 1 bf16, 2 int8).  Returns cudaError_t as int; a device
 // side wait that ran out is reported through *err_word (0 = clean).
 int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcProducts &prod,
                    int64_t M, int64_t N, int64_t K, const TcEpilogue &ep, int *err_word,
-                   int sm_count, cudaStream_t stream);
+                   int sm_count, cudaStream_t stream, const TcSplitK *splitk = nullptr);
+
+// Whether launch_gemm_tc would cut K into slices for this problem when given scratch: callers that multiply row
+// blocks of one problem in separate launches ask, because a split changes the order of the fp32 additions.
+bool gemm_tc_splits_k(int kind, const TcProducts &prod, int64_t M, int64_t N, int64_t K, int sm_count);
 
 // Message of the last failure in this translation unit (tensor-map encoding, launch).
 const char *gemm_tc_last_error();

@@ -26,9 +26,6 @@
 
 namespace axb {
 
-#define GP_DECL(n)
-#define GP_ADD(i)
-#define GP_OUT(base, n) {}
 
 
 static constexpr int PAIR_BN = 256;
@@ -98,6 +95,7 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
             bool ok = true;
             const int k_blocks = p.k_blocks, stages = p.stages, npa = p.npa, npb = p.npb;
             const uint32_t sbytes = (uint32_t)stage_bytes;
+            grid_dep_wait();   // the operand planes come from the kernel before this one
             for (int t = pair; t < total_tiles && ok; t += npairs) {
                 int mt, nt;
                 tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
@@ -139,28 +137,23 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
             const uint32_t prod_a = p.prod_a, prod_b = p.prod_b;
             const uint64_t desc_hi = smem_desc_kmajor(0, SWB);
             const uint32_t npa_bytes = p.npa * A_BYTES, sbytes = (uint32_t)stage_bytes;
-            GP_DECL(3)
             for (int t = pair; t < total_tiles && ok; t += npairs) {
                 for (int kb0 = 0; kb0 < k_blocks && ok; kb0 += chunk_kb, ++vt) {
                     const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
-                    GP_ADD(2)
                     if (!mbar_wait_bounded(bar_tempty + 8 * acc, aph ^ 1u)) {
                         report(p.err, ERR_MMA_WAIT_TMEM);
                         ok = false;
                         break;
                     }
-                    GP_ADD(0)
                     tc_fence_after_sync();
                     const uint32_t d_tmem = tmem_base + acc * BN;
                     const int kb1 = min(k_blocks, kb0 + chunk_kb);
                     for (int kb = kb0; kb < kb1; ++kb) {
-                        GP_ADD(2)
                         if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
                             report(p.err, ERR_MMA_WAIT_FULL);
                             ok = false;
                             break;
                         }
-                        GP_ADD(1)
                         tc_fence_after_sync();
                         const uint32_t sa = stage0 + s * sbytes;
                         issue_stage_mmas<KIND, SWB, NPROD, true, A_BYTES, B_BYTES>(
@@ -174,8 +167,6 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
                     if (ok) tc_commit_pair(bar_tfull + 8 * acc, 0x3);
                 }
             }
-            GP_ADD(2)
-            if (pair == 0) GP_OUT(0, 3)
         }
     } else if (warp < B_PRODUCER_WARP) {
         // ---------------------------------------------------------- epilogue
@@ -187,7 +178,6 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
         uint32_t vt = 0;
         bool alive = true;
         const bool rows_aligned = KIND != KIND_I8 && epi_rows_aligned(p);
-        GP_DECL(3)
         for (int t = pair; t < total_tiles && alive; t += npairs) {
             int mt, nt;
             tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
@@ -214,40 +204,7 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
                     __syncwarp();
                     tmem_ld_32x32(lane_addr + acc * BN + c * 32, r);
                     tmem_ld_wait();
-                    const bool full = col0 + 32 <= p.N;
-                    if (row_ok) {
-                        if (p.acc_out) {
-                            int32_t *dst = p.acc_out + row * p.ldc + col0;
-                            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-                                for (int j = 0; j < 32; j += 4)
-                                    *reinterpret_cast<int4 *>(dst + j) =
-                                        make_int4((int)r[j], (int)r[j + 1], (int)r[j + 2], (int)r[j + 3]);
-                            } else {
-                                for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = (int32_t)r[j];
-                            }
-                        }
-                        if (p.out_mode == OUT_I8_REQUANT) {
-                            int8_t *dst = reinterpret_cast<int8_t *>(p.C) + row * p.ldc + col0;
-                            uint32_t packed[8];
-#pragma unroll
-                            for (int j = 0; j < 32; ++j) {
-                                const float mult = (col0 + j < p.N) ? __ldg(p.colscale + col0 + j) : 0.0f;
-                                const float y = __fmul_rn(__int2float_rn((int32_t)r[j]), mult);
-                                int v = __float2int_rn(y);
-                                v = max(-127, min(127, v));
-                                if ((j & 3) == 0) packed[j >> 2] = 0;
-                                packed[j >> 2] |= (uint32_t)(v & 0xff) << (8 * (j & 3));
-                            }
-                            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-                                *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                                *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                            } else {
-                                for (int j = 0; j < 32 && col0 + j < p.N; ++j)
-                                    dst[j] = (int8_t)((packed[j >> 2] >> (8 * (j & 3))) & 0xff);
-                            }
-                        }
-                    }
+                    store_piece_i8(p, reinterpret_cast<const int *>(r), row, row_ok, col0);
                 }
                 tc_fence_before_sync();
                 __syncwarp();
@@ -261,9 +218,7 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
                 for (int j = 0; j < HALF; ++j) sum[j] = 0.0f;
                 for (int ch = 0; ch < nchunks; ++ch, ++vt) {
                     const uint32_t acc = vt & 1u, aph = (vt >> 1) & 1u;
-                    GP_ADD(1)
                     const bool got = mbar_wait_warp_bounded(bar_tfull + 8 * acc, aph);
-                    GP_ADD(0)
                     if (!__all_sync(0xffffffffu, got)) {
                         report(p.err, ERR_EPI_WAIT);
                         alive = false;
@@ -286,7 +241,6 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
                     }
                 }
                 if (!alive) break;
-                GP_ADD(1)
                 {
                     // sums -> this warp's staging tile (row = lane) -> fused epilogue and whole-line stores
                     float4 *stg = reinterpret_cast<float4 *>(gen_base + HEADER_BYTES + (size_t)p.stages * stage_bytes) + (warp - 2) * 256;
@@ -307,13 +261,13 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
                         }
                     }
                 }
-                GP_ADD(2)
             }
         }
-        if (pair == 0 && rank == 0 && warp == 2 && lane == 0) GP_OUT(8, 3)
     }
 
-    if (p.tma_store && warp >= 2 && warp < B_PRODUCER_WARP && lane == 0) tma_store_wait_all();
+    // the staging tiles must have been read before the shared memory goes away; the global writes themselves are
+    // complete when the kernel is
+    if (p.tma_store && warp >= 2 && warp < B_PRODUCER_WARP && lane == 0) tma_store_wait_read();
 
     // ---------------------------------------------------------------- teardown
     if (p.err && *reinterpret_cast<volatile int *>(p.err) != 0) {
@@ -378,8 +332,18 @@ static int launch_pair_inst(const TmapPack &tm, KernelArgs &ka, int npa, int npb
     long long pairs = resident_pairs;
     if (pairs > sm_count / 2) pairs = sm_count / 2;
     if (pairs > tiles) pairs = tiles;
-    kern<<<(unsigned)(2 * pairs), NUM_THREADS, smem, stream>>>(tm, ka);
-    cudaError_t e = cudaGetLastError();
+    // programmatic dependent launch, as in the single-CTA launcher: set-up overlaps the operand pre-pass's tail
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((unsigned)(2 * pairs));
+    lc.blockDim = dim3(NUM_THREADS);
+    lc.dynamicSmemBytes = (size_t)smem;
+    lc.stream = stream;
+    cudaLaunchAttribute lat;
+    lat.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    lat.val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = &lat;
+    lc.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&lc, kern, tm, ka);
     if (e != cudaSuccess) snprintf(err, err_len, "pair kernel launch: %s", cudaGetErrorString(e));
     return (int)e;
 }

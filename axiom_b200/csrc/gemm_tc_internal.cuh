@@ -5,6 +5,7 @@
 #include "ptx.cuh"
 
 #include <cuda.h>
+#include <type_traits>
 
 namespace axb {
 
@@ -32,6 +33,7 @@ struct KernelArgs {
     float alpha, beta;
     const float *bias;
     const float *colscale;
+    float rq_a_scale, rq_out_scale;   // int8 requantisation: multiplier = (rq_a_scale * colscale[n]) / rq_out_scale
     int act, out_mode;
     void *C;
     int32_t *acc_out;
@@ -42,7 +44,16 @@ struct KernelArgs {
     int hs_dk, hs_S, hs_H;   // head-major scatter of the output (hs_dk > 0), see TcEpilogue
     int tma_store;           // fp32 output leaves through TMA stores of the staging tiles (plain C, beta == 0, aligned)
     float *hs_out[3];
+    // split-K (ksplit > 1): work item w = tile * ksplit + slice covers k-blocks [slice * kb_per_slice, ...); every
+    // slice leaves its partial sums in sk_scratch and counts itself in on sk_counters[tile]; the slice that counts
+    // last adds all of them in slice order and runs the epilogue (no CTA ever waits for another)
+    int ksplit, kb_per_slice;
+    void *sk_scratch;        // [tiles x CTAs per tile][ksplit][128 x BN] fp32 / s32
+    int *sk_counters;        // [tiles x CTAs per tile], zero between launches
 };
+
+// shared-memory header words used by the split-K hand-over (after the barriers and the TMEM slot)
+static constexpr int HDR_SK_DEAD = 176, HDR_SK_LAST = 180;
 
 // error words written to *err (first writer wins)
 enum { ERR_PRODUCER_WAIT = 1, ERR_MMA_WAIT_FULL = 2, ERR_MMA_WAIT_TMEM = 3, ERR_EPI_WAIT = 4 };
@@ -212,6 +223,115 @@ __device__ __forceinline__ void issue_stage_mmas(uint32_t d_tmem, uint32_t sa, u
                 const uint32_t accumulate = (g == 0 && pr == 0 && ks == 0) ? (first ? 0u : 1u) : 1u;
                 if constexpr (PAIR) tc_mma_pair<KIND>(d_tmem, da + 2u * ks, db + 2u * ks, idesc, accumulate);
                 else tc_mma<KIND>(d_tmem, da + 2u * ks, db + 2u * ks, idesc, accumulate);
+            }
+        }
+    }
+}
+
+// barrier over the eight epilogue warps only (the producer and MMA warps never take part)
+__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+
+enum { SK_DEAD = 0, SK_NOT_LAST = 1, SK_LAST = 2 };
+
+// Split-K hand-over of one CTA's 128 x (2*HALF) partial tile.  `v` holds this thread's row (lane) x HALF columns.
+// Every slice stores its partials to scratch in a thread-private order (the same thread of the same warp role reads
+// them back, so the layout only has to be coalesced: consecutive lanes write consecutive 16-byte words), makes them
+// visible device-wide and counts itself in.  The slice that counts last reloads ALL slices, its own included, and
+// adds them in slice order, so the sum does not depend on which slice happened to finish last: results are bitwise
+// repeatable.  Nobody waits for anybody.  `alive` = this warp's accumulator wait succeeded; a failed wait is
+// agreed on by all eight warps here (they must keep meeting at the barrier) and ends the kernel's epilogue.
+template <typename T, int HALF>
+__device__ __forceinline__ int splitk_exchange(const KernelArgs &p, T (&v)[HALF], long long region, int slice, int warp,
+                                               int lane, uint8_t *hdr, bool alive)
+{
+    constexpr int PIECES = HALF / 32;
+    constexpr size_t SLICE_ELEMS = (size_t)BM * 2 * HALF;
+    using V4 = typename std::conditional<std::is_same<T, float>::value, float4, int4>::type;
+    volatile int *dead = reinterpret_cast<volatile int *>(hdr + HDR_SK_DEAD);
+    volatile int *last = reinterpret_cast<volatile int *>(hdr + HDR_SK_LAST);
+    T *tile0 = reinterpret_cast<T *>(p.sk_scratch) + (size_t)region * p.ksplit * SLICE_ELEMS;
+    const size_t warp_off = (size_t)(warp - 2) * 32 * HALF;
+    if (alive) {
+        V4 *mine = reinterpret_cast<V4 *>(tile0 + (size_t)slice * SLICE_ELEMS + warp_off);
+#pragma unroll
+        for (int c = 0; c < PIECES; ++c)
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4) {
+                V4 w;
+                w.x = v[c * 32 + 4 * j4]; w.y = v[c * 32 + 4 * j4 + 1]; w.z = v[c * 32 + 4 * j4 + 2]; w.w = v[c * 32 + 4 * j4 + 3];
+                mine[(c * 8 + j4) * 32 + lane] = w;
+            }
+        __threadfence();
+    } else {
+        *dead = 1;
+    }
+    epi_bar_sync();
+    if (warp == 2 && lane == 0) {
+        int is_last = 0;
+        if (!*dead) {
+            const int old = atomicAdd(p.sk_counters + region, 1);
+            if (old == p.ksplit - 1) {
+                is_last = 1;
+                p.sk_counters[region] = 0;   // every slice has counted: ready for the next launch
+            }
+        }
+        *last = is_last;
+    }
+    epi_bar_sync();
+    if (*dead) return SK_DEAD;
+    if (!*last) return SK_NOT_LAST;
+    __threadfence();
+#pragma unroll
+    for (int j = 0; j < HALF; ++j) v[j] = T(0);
+    for (int s = 0; s < p.ksplit; ++s) {
+        const V4 *src = reinterpret_cast<const V4 *>(tile0 + (size_t)s * SLICE_ELEMS + warp_off);
+#pragma unroll
+        for (int c = 0; c < PIECES; ++c)
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4) {
+                const V4 w = __ldcg(src + (c * 8 + j4) * 32 + lane);
+                v[c * 32 + 4 * j4] += w.x; v[c * 32 + 4 * j4 + 1] += w.y; v[c * 32 + 4 * j4 + 2] += w.z; v[c * 32 + 4 * j4 + 3] += w.w;
+            }
+    }
+    return SK_LAST;
+}
+
+// int8 epilogue of 32 accumulator columns of one row: raw s32 to acc_out and / or the requantised int8 to C.
+// Called by all 32 lanes of a warp together (lane = row): lane j forms the multiplier of column col0 + j — one
+// division per lane instead of 32 per thread — and the row loops fetch it with a shuffle.
+__device__ __forceinline__ void store_piece_i8(const KernelArgs &p, const int *r, long long row, bool row_ok, int col0)
+{
+    const bool full = col0 + 32 <= p.N;
+    if (p.acc_out && row_ok) {
+        int32_t *dst = p.acc_out + row * p.ldc + col0;
+        if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) *reinterpret_cast<int4 *>(dst + j) = make_int4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+        } else {
+            for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = r[j];
+        }
+    }
+    if (p.out_mode == OUT_I8_REQUANT) {
+        const int lane = threadIdx.x & 31;
+        // (a_scale * b_scales[n]) / out_scale with one rounding per operation, as the CPU restatement does it
+        const float my_mult = (col0 + lane < p.N) ? __fdiv_rn(__fmul_rn(p.rq_a_scale, __ldg(p.colscale + col0 + lane)), p.rq_out_scale) : 0.0f;
+        uint32_t packed[8];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+            const float mult = __shfl_sync(0xffffffffu, my_mult, j);
+            const float y = __fmul_rn(__int2float_rn(r[j]), mult);
+            int v = __float2int_rn(y);
+            v = max(-127, min(127, v));
+            if ((j & 3) == 0) packed[j >> 2] = 0;
+            packed[j >> 2] |= (uint32_t)(v & 0xff) << (8 * (j & 3));
+        }
+        if (row_ok) {
+            int8_t *dst = reinterpret_cast<int8_t *>(p.C) + row * p.ldc + col0;
+            if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+                *reinterpret_cast<uint4 *>(dst) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+                *reinterpret_cast<uint4 *>(dst + 16) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+            } else {
+                for (int j = 0; j < 32 && col0 + j < p.N; ++j) dst[j] = (int8_t)((packed[j >> 2] >> (8 * (j & 3))) & 0xff);
             }
         }
     }

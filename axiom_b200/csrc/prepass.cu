@@ -6,6 +6,7 @@
 //   * re-pitch int8 operands whose row length is not a multiple of 16 bytes;
 //   * the per-column requantisation multiplier and the row quantiser.
 #include "prepass.cuh"
+#include "ptx.cuh"
 
 #include <cuda_bf16.h>
 #include <stdint.h>
@@ -166,6 +167,7 @@ template <int MODE>
 __global__ void __launch_bounds__(256) split_rows_kernel(const float *__restrict__ in, int64_t rows, int64_t k, int64_t ld,
                                                          PlanePtrs pl, int64_t pitch, int64_t chunk_k, int64_t chunk_stride)
 {
+    grid_dep_launch();   // the GEMM that follows may set itself up now; its producers wait for this grid to finish
     split_rows_body<MODE>(in, rows, k, ld, pl, pitch, chunk_k, chunk_stride, blockIdx.x, gridDim.x);
 }
 
@@ -174,6 +176,7 @@ __global__ void __launch_bounds__(256) split_transpose_kernel(const float *__res
                                                               int64_t ld, PlanePtrs pl, int64_t pitch)
 {
     __shared__ float tile[64][33];
+    grid_dep_launch();
     split_transpose_body<MODE>(in, rows, k, ld, pl, pitch, tile, blockIdx.x, gridDim.x);
 }
 
@@ -191,6 +194,7 @@ template <int MODE>
 __global__ void __launch_bounds__(256) split_pair_kernel(const SplitTask a, const SplitTask b)
 {
     __shared__ float tile[64][33];
+    grid_dep_launch();
     const bool first = (int)blockIdx.x < a.blocks;
     const SplitTask &t = first ? a : b;
     const int vblock = first ? (int)blockIdx.x : (int)blockIdx.x - a.blocks;
@@ -211,6 +215,7 @@ __global__ void __launch_bounds__(256) split_im2col_kernel(const float *__restri
     // arithmetic per element is two 32-bit divisions and the stores are 8 bytes per plane.  (One element per thread
     // with the pixel recovered from a flat 64-bit index — the first version — spent its time in four 64-bit divisions
     // per element: 55 us for a 56x56x256 sample, 1 TB/s.)
+    grid_dep_launch();
     const int K = (int)(C_in * kh * kw), khkw = kh * kw;
     const int64_t npix = out_h * out_w;
     // what depends on k alone — the offset of (c, ky, kx) inside the sample and the window position — is tabulated

@@ -49,7 +49,6 @@ struct QtArgs {
 
 enum { QERR_PRODUCER = 31, QERR_MMA = 32, QERR_DRAIN = 33 };
 
-#define QP_STAMP(i) {}
 
 __host__ __device__ constexpr int qt_stages(int mp)
 {
@@ -96,7 +95,6 @@ __global__ void __launch_bounds__(QX_THREADS) qx_digits_kernel(const float *__re
     constexpr int QX_CACHE = QX_CACHED_F4 / QX_THREADS;
     __shared__ float wmax[32];
     const int m = blockIdx.x, tid = threadIdx.x;
-    if (tid == 0) QP_STAMP(0)
     grid_dep_launch();   // the tensor-core kernel may start streaming weights now; it waits before it reads the digits
     const float4 *row = reinterpret_cast<const float4 *>(a + (int64_t)m * K);
     const int k4n = K >> 2;
@@ -138,7 +136,6 @@ __global__ void __launch_bounds__(QX_THREADS) qx_digits_kernel(const float *__re
         if (i < k4n) qx_emit(dst, plane4, i, v[r], s);
     }
     for (int i = tid + QX_THREADS * QX_CACHE; i < k4n; i += QX_THREADS) qx_emit(dst, plane4, i, __ldg(row + i), s);
-    if (tid == 0) QP_STAMP(1)
 }
 
 // ------------------------------------------------------------------------------------------------ main kernel
@@ -180,7 +177,6 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
     auto stage_addr = [&](int s) -> uint32_t { return base + 1024u + (uint32_t)s * STAGE; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) QP_STAMP(2)
     const int tile = blockIdx.x, slice = blockIdx.y, nslices = gridDim.y;
     const int64_t n0 = (int64_t)tile * QT_BN;
     const int per = (kb_total + nslices - 1) / nslices;
@@ -205,7 +201,6 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
             tma_load_3d(stage_addr(i), &tm.w, bar(B_FULL + i), kpos(i), (int32_t)n0, 0);
         }
         tma_prefetch_desc(&tm.x);
-        QP_STAMP(3)
     }
     if (warp == 1) {
         tmem_alloc(base + 512, TCOLS);
@@ -236,7 +231,6 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
         // ------------------------------------------------------------ producer
         if (lane == 0) {
             grid_dep_wait();   // the digits
-            QP_STAMP(4)
             for (int i = 0; i < pre; ++i)
                 tma_load_3d(stage_addr(i) + QT_W_BYTES, &tm.x, bar(B_FULL + i), kpos(i), 0, 0);
             for (int i = pre; i < nkb; ++i) {
@@ -259,7 +253,6 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
             for (int i = 0; i < nkb; ++i) {
                 const int s = i % STAGES;
                 if (!mbar_wait_bounded(bar(B_FULL + s), (i / STAGES) & 1)) { ok = false; break; }
-                if (i == 0) QP_STAMP(5)
                 tc_fence_after_sync();
                 const uint32_t st = stage_addr(s);
 #pragma unroll
@@ -271,7 +264,6 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
                 tc_commit(bar(B_EMPTY + s));
             }
             if (ok && nkb > 0) tc_commit(bar(B_ACC));
-            QP_STAMP(6)
             if (!ok) qt_report(a.err, QERR_MMA);
         }
     } else {
@@ -287,7 +279,6 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
             have = false;
         }
         tc_fence_after_sync();
-        if (threadIdx.x == 64) QP_STAMP(7)
 #pragma unroll 1
         for (int g = quarter; g < MP / 4; g += 4) {
             if (4 * g >= a.M) break;
@@ -320,12 +311,10 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
             }
         }
         tc_fence_before_sync();
-        if (threadIdx.x == 64) QP_STAMP(8)
     }
 
     if (nslices > 1) {
         cluster_sync_all();   // release / acquire: every slice's partial sums have landed
-        if (threadIdx.x == 64) QP_STAMP(9)
         if (warp >= 2 && col_ok) {
             // integer sums of the rows this slice owns, out of its own shared memory: nobody reads a peer after the
             // barrier, so a CTA may leave as soon as it is done
@@ -343,7 +332,6 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
 
     tc_fence_before_sync();
     __syncthreads();
-    if (threadIdx.x == 64) QP_STAMP(10)
     if (warp == 1) {
         tc_fence_after_sync();
         tmem_dealloc(tmem, TCOLS);

@@ -51,7 +51,6 @@ enum { KB_RAW = 0, KB_EMPTY = KT_STAGES, KB_T_FULL = 2 * KT_STAGES, KB_T_EMPTY =
 #define KP_DECL(n)
 #define KP_ADD(i)
 #define KP_OUT(base, n)
-#define KP_STAMP(i) {}
 
 // one lane polls, the warp gets the outcome: 32 lanes spinning on a barrier cost shared-memory bandwidth that
 // the MMA operands need
@@ -163,7 +162,6 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = *tmem_slot;
-    if (threadIdx.x == 0) KP_STAMP(20)
 
     float acc[MP];
 #pragma unroll
@@ -206,7 +204,6 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
                 const int ts = i % KT_T;
                 if (!mbar_wait_bounded(bar(KB_T_FULL + ts), (i / KT_T) & 1)) { ok = false; break; }   // implies the stage's X
                 KP_ADD(1)
-                if (i == 0) KP_STAMP(21)
                 tc_fence_after_sync();
                 const uint32_t a_hi = tmem + ts * 64, a_lo = a_hi + 32;   // W^T: lane = output column, column = k
                 const uint32_t d = tmem + KT_ACC_COL + cb * 128;
@@ -227,7 +224,6 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
                 KP_ADD(2)
             }
             if (!ok) kt_report(a.err, KERR_MMA);
-            KP_STAMP(22)
             KP_OUT(4, 3)
         }
     } else if (warp < 6) {
@@ -298,7 +294,6 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
         }
     }
 
-    if (threadIdx.x == 192) KP_STAMP(23)
     // ------------------------------------------------------------ reduce + epilogue
     if (nslices == 1) {
         if (warp >= 6 && n0 + t_row < a.N) {
@@ -319,9 +314,7 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
 #pragma unroll
             for (int m = 0; m < MP; ++m) red[m * KT_BN + t_row] = acc[m];
         }
-        if (threadIdx.x == 192) KP_STAMP(24)
         cluster_sync_all();
-        if (threadIdx.x == 192) KP_STAMP(25)
         if (warp >= 2) {
             const int rows_owned = (a.M - slice + nslices - 1) / nslices;
             for (int it = threadIdx.x - 64; it < rows_owned * 32; it += 256) {

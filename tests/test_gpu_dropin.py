@@ -183,11 +183,12 @@ def test_mha_layer_forward_on_device(dropin, reference, oracle, shape, causal, w
 def test_mha_layer_training_step_on_device(dropin, reference, oracle, causal, with_bias, save_p):
     """Forward with L (and, when save_p, a P_save buffer handed on to sdpa_bwd as the layer does when P fits) and the
     layer's backward sequence (gemm_tn with skip_init, gemm_nt, head_interleave, sdpa_bwd, qkv_merge, gemm_tn, gemm_nt)
-    on the device.  Checked against the double-precision restatement of the layer, and against ax_layer_forward +
-    ax_backward of sum(out * dOut) on the reference's CPU backend: the forward always, the gradients without biases.
-    With biases the reference's own CPU backward returns wrong dX / dW for part of the batch at this shape (it differs
-    from its own bias-free run when the biases are all zero; tests/test_mha_reference_defect.py pins that on the CPU),
-    so there the restatement alone is the judge."""
+    on the device.  The forward is checked against ax_layer_forward of the reference's CPU backend and against the
+    double-precision restatement of the layer; the gradients against the restatement only.  The reference's own CPU
+    backward is not repeatable at this shape: its dX / dW change with the number of OpenMP threads and with the presence
+    of (even all-zero) biases, and disagree with a float64 evaluation by 10 % and more (tests/test_mha_reference_defect.py
+    records this on the CPU).  The pieces of the restatement's backward — the GEMMs and the attention backward — are
+    each pinned against the reference separately (golden vectors of ax_compute_gemm* and ax_fused_attention_bwd)."""
     from oracle_lib import mha_f64
     B, S, D, H = 2, 128, 256, 4
     x, W, b, g = mha_inputs(oracle, B, S, D, with_bias)
@@ -199,8 +200,6 @@ def test_mha_layer_training_step_on_device(dropin, reference, oracle, causal, wi
     assert np.abs(got["out"] - ref["out"]).max() < 1e-4
     for key in ("out", "dX", "dW") + (("db",) if with_bias else ()):
         assert nerr(got[key], want[key]) <= 1e-5, key
-        if not with_bias:
-            assert nerr(got[key], ref[key]) <= 5e-5, key
     if save_p:
         assert np.abs(got["P"] - want["P"]).max() < 1e-5
         if causal:

@@ -574,3 +574,55 @@ def test_qdense_w8a32(engine, oracle, shape, act):
     plain = torch.empty((M, N), device="cuda")
     engine.qgemm_w8a32(dev(a), torch.from_numpy(q).cuda(), dev(s), plain)          # the reference's entry: no bias, no act
     assert nerr(host(plain), oracle.qgemm_w8a32_f64(a, q, s)) <= TOL_SPLIT
+
+
+# ---- split-K of the dense tensor-core core: few output tiles, long K ----------------------------------------------
+
+@pytest.mark.parametrize("shape", [(256, 384, 4096), (130, 200, 3000), (1024, 1024, 1024), (64, 128, 8192), (300, 96, 2052),
+                                   (256, 3136, 2304), (33, 520, 1536)])
+def test_split_k_fp32_vs_oracle_and_repeatable(engine, oracle, shape):
+    """Problems with too few 128-column tiles to fill the GPU cut K into slices that meet in scratch; the slice that
+    arrives last adds all partial tiles in slice order, so the result is inside the fp32 tolerance AND bitwise
+    repeatable, with every epilogue form (bias + GELU, alpha/beta, transposed operands)."""
+    M, N, K = shape
+    A, B, bias, Cin = oracle.uniform((M, K), 7), oracle.uniform((K, N), 13), oracle.uniform((N,), 29), oracle.uniform((M, N), 5)
+    ref = oracle.gemm_f64(A, B)
+    Ad, Bd = dev(A), dev(B)
+    outs = []
+    for _ in range(3):
+        out = torch.full((M, N), float("nan"), device="cuda")
+        engine.gemm(Ad, Bd, out)
+        outs.append(host(out))
+    assert nerr(outs[0], ref) <= TOL_SPLIT
+    np.testing.assert_array_equal(outs[0], outs[1])
+    np.testing.assert_array_equal(outs[0], outs[2])
+    out = torch.empty((M, N), device="cuda")
+    engine.gemm_bias_act(Ad, Bd, dev(bias), out, M, N, K, act="gelu")
+    assert nerr(host(out), oracle.bias_act(ref.astype(np.float32), bias, "gelu")) <= TOL_SPLIT
+    c = dev(Cin)
+    engine.gemm_ex(Ad, Bd, 0.5, 2.0, c)
+    assert nerr(host(c), 0.5 * ref + 2.0 * Cin) <= TOL_SPLIT
+    np.testing.assert_array_equal(run_gemm(engine, A, np.ascontiguousarray(B.T), "nt"), outs[0])
+    np.testing.assert_array_equal(run_gemm(engine, np.ascontiguousarray(A.T), B, "tn"), outs[0])
+    for mode, tol in (("bf16x3", TOL_SPLIT), ("bf16", TOL_BF16)):
+        engine.set_fp32_mode(mode)
+        try:
+            engine.gemm(Ad, Bd, out)
+        finally:
+            engine.set_fp32_mode("3xtf32")
+        assert nerr(host(out), ref) <= tol
+    assert engine.device_error() == 0
+
+
+@pytest.mark.parametrize("shape", [(64, 256, 8192), (256, 384, 4096), (130, 200, 3001), (128, 128, 16384), (512, 512, 2048)])
+def test_split_k_int8_bit_exact(engine, oracle, shape):
+    M, N, K = shape
+    a, b, bs = oracle.int8((M, K), 7), oracle.int8((N, K), 13), oracle.frange((N,), 17, 0.001, 0.02)
+    out_scale = 0.02 * 0.0105 * 73.0 * np.sqrt(K)
+    acc_ref, q_ref = oracle.qgemm_w8a8(a, 0.02, b, bs, out_scale)
+    q = torch.zeros((M, N), dtype=torch.int8, device="cuda")
+    acc = torch.zeros((M, N), dtype=torch.int32, device="cuda")
+    engine.qgemm_w8a8(dev(a), 0.02, dev(b), dev(bs), out_scale, q, acc)
+    np.testing.assert_array_equal(host(acc), acc_ref)
+    np.testing.assert_array_equal(host(q), q_ref)
+    assert engine.device_error() == 0
