@@ -44,6 +44,9 @@ struct Engine {
     int sk_counter_cap = 0;
     int *err_word = nullptr;
     int *gemm_counters = nullptr;   // split-K arrival counters of the tensor-core GEMM (zero between launches)
+    // output range of the last skinny kernel, which lets the next one start under it: a skinny call whose WEIGHTS lie
+    // in that range must not prefetch them early
+    const char *chain_lo = nullptr, *chain_hi = nullptr;
     int64_t launches = 0;
     // grow-only buffer for intermediate results a fused route cannot avoid (the unfused qkv projection)
     void *aux = nullptr;
@@ -247,6 +250,12 @@ int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int
 int gemm_skinny(const float *X, const float *W, const float *bias, float *Y, int64_t M, int64_t N, int64_t K,
                 float alpha, float beta, int act)
 {
+    // back-to-back skinny calls (a decode step walks a chain of them) overlap: this call may request its first weight
+    // tiles while the previous one drains, unless those weights are what the previous call wrote
+    const char *w_lo = reinterpret_cast<const char *>(W), *w_hi = w_lo + (size_t)K * N * sizeof(float);
+    const int pdl = !(g.chain_lo && w_lo < g.chain_hi && g.chain_lo < w_hi);
+    g.chain_lo = reinterpret_cast<const char *>(Y);
+    g.chain_hi = g.chain_lo + (size_t)M * N * sizeof(float);
     // above 8 rows the fp32 pipe, not memory, paces the FMA kernels: the tensor-core variant takes over
     if (M >= 9 && skinny_tc_applicable(M, N, K, X, W)) {
         SkinnyArgs a;
@@ -254,6 +263,7 @@ int gemm_skinny(const float *X, const float *W, const float *bias, float *Y, int
         a.alpha = alpha; a.beta = beta; a.act = act;
         a.ksplit = 0; a.kchunk = 0; a.stages = 0; a.cluster = 0; a.partial = nullptr; a.counters = nullptr;
         a.err = g.err_word;
+        a.pdl = pdl;
         mark(0);
         mark(1);
         int e = launch_skinny_tc(a, g.sm_count, g.stream);
@@ -286,6 +296,7 @@ int gemm_skinny(const float *X, const float *W, const float *bias, float *Y, int
     a.partial = (plan.ksplit > 1 && !plan.cluster) ? g.sk_partial : nullptr;
     a.counters = g.sk_counters;
     a.err = g.err_word;
+    a.pdl = pdl;
     mark(0);
     mark(1);
     int e = launch_skinny(a, plan, g.stream);
@@ -422,7 +433,11 @@ extern "C" int axb_memcpy_d2d(void *dst, const void *src, size_t bytes)
     return e == cudaSuccess ? AXB_OK : cuda_fail("memcpy_d2d", e);
 }
 
-extern "C" void axb_set_stream(void *cuda_stream) { g.stream = (cudaStream_t)cuda_stream; }
+extern "C" void axb_set_stream(void *cuda_stream)
+{
+    g.stream = (cudaStream_t)cuda_stream;
+    g.chain_lo = g.chain_hi = nullptr;
+}
 
 extern "C" int axb_set_fp32_mode(int mode)
 {

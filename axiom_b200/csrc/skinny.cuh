@@ -21,6 +21,10 @@ struct SkinnyArgs {
     float *partial;     // [ksplit][M][N] scratch when ksplit > 1
     int *counters;      // [strips] zero between calls
     int *err;           // device word that receives a code when a bounded wait runs out, or null
+    // 1: launch as a programmatic dependent of the kernel before it in the stream.  The TMA-staged kernels request
+    // their first ring of WEIGHT tiles before they wait for that kernel to finish (X, bias and Y are only touched
+    // afterwards), so the caller sets this only when W cannot be that kernel's output.
+    int pdl = 0;
 };
 
 struct SkinnyPlan {

@@ -48,9 +48,6 @@ enum { KERR_PRODUCER = 21, KERR_CONVERT = 22, KERR_MMA = 23, KERR_DRAIN = 24 };
 enum { KB_RAW = 0, KB_EMPTY = KT_STAGES, KB_T_FULL = 2 * KT_STAGES, KB_T_EMPTY = 2 * KT_STAGES + KT_T,
        KB_CHUNK_FULL = 2 * KT_STAGES + 2 * KT_T, KB_CHUNK_EMPTY = 2 * KT_STAGES + 2 * KT_T + 2 };
 
-#define KP_DECL(n)
-#define KP_ADD(i)
-#define KP_OUT(base, n)
 
 // one lane polls, the warp gets the outcome: 32 lanes spinning on a barrier cost shared-memory bandwidth that
 // the MMA operands need
@@ -146,13 +143,16 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
         // the block-wide barrier): the first HBM round trip is the longest wait of the kernel
         tma_prefetch_desc(&tm.w);
         tma_prefetch_desc(&tm.x);
+        grid_dep_launch();   // a skinny call queued behind this one may start streaming ITS weights now
         for (int i = 0; i < nkb && i < KT_STAGES; ++i) {
-            const uint32_t st = stage_addr(i);
-            const int k0 = (kb0 + i) * KT_KB;
             mbar_arrive_expect_tx(bar(KB_RAW + i), KT_W_BYTES + X_BYTES);
-            tma_load_2d(st, &tm.w, bar(KB_RAW + i), (int32_t)n0, k0);
-            tma_load_3d(st + KT_W_BYTES, &tm.x, bar(KB_RAW + i), k0, 0, 0);
+            tma_load_2d(stage_addr(i), &tm.w, bar(KB_RAW + i), (int32_t)n0, (kb0 + i) * KT_KB);
         }
+        // the weights were requested while the kernel before this one may still be running (programmatic dependent
+        // launch); the activations may be its output, so they are fetched only once it has finished
+        grid_dep_wait();
+        for (int i = 0; i < nkb && i < KT_STAGES; ++i)
+            tma_load_3d(stage_addr(i) + KT_W_BYTES, &tm.x, bar(KB_RAW + i), (kb0 + i) * KT_KB, 0, 0);
     }
     if (warp == 1) {
         tmem_alloc(base + 512, 512);
@@ -171,20 +171,15 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
-            KP_DECL(2)
             for (int i = KT_STAGES; i < nkb; ++i) {
                 const int s = i % KT_STAGES, n = i / KT_STAGES;
-                KP_ADD(0)
                 if (!mbar_wait_bounded(bar(KB_EMPTY + s), (n - 1) & 1)) { kt_report(a.err, KERR_PRODUCER); break; }
-                KP_ADD(1)
                 const uint32_t st = stage_addr(s);
                 const int k0 = (kb0 + i) * KT_KB;
                 mbar_arrive_expect_tx(bar(KB_RAW + s), KT_W_BYTES + X_BYTES);
                 tma_load_2d(st, &tm.w, bar(KB_RAW + s), (int32_t)n0, k0);
                 tma_load_3d(st + KT_W_BYTES, &tm.x, bar(KB_RAW + s), k0, 0, 0);
             }
-            KP_ADD(0)
-            KP_OUT(0, 2)
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------- MMA issuer
@@ -194,16 +189,13 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
             const uint32_t idesc_hi = make_idesc<KIND_TF32>(KT_BN, 2 * MP);
             const uint32_t idesc_lo = make_idesc<KIND_TF32>(KT_BN, MP);
             bool ok = true;
-            KP_DECL(3)
             for (int i = 0; i < nkb; ++i) {
                 const int s = i % KT_STAGES;
                 const int ci = i / KT_CHUNK, cb = ci & 1;
                 const bool first = (i % KT_CHUNK) == 0;
                 if (first && ci >= 2 && !mbar_wait_bounded(bar(KB_CHUNK_EMPTY + cb), ((ci >> 1) - 1) & 1)) { ok = false; break; }
-                KP_ADD(0)
                 const int ts = i % KT_T;
                 if (!mbar_wait_bounded(bar(KB_T_FULL + ts), (i / KT_T) & 1)) { ok = false; break; }   // implies the stage's X
-                KP_ADD(1)
                 tc_fence_after_sync();
                 const uint32_t a_hi = tmem + ts * 64, a_lo = a_hi + 32;   // W^T: lane = output column, column = k
                 const uint32_t d = tmem + KT_ACC_COL + cb * 128;
@@ -221,28 +213,23 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
                 tc_commit(bar(KB_T_EMPTY + ts));
                 tc_commit(bar(KB_EMPTY + s));
                 if ((i % KT_CHUNK) == KT_CHUNK - 1 || i == nkb - 1) tc_commit(bar(KB_CHUNK_FULL + cb));
-                KP_ADD(2)
             }
             if (!ok) kt_report(a.err, KERR_MMA);
-            KP_OUT(4, 3)
         }
     } else if (warp < 6) {
         // ---------------------------------------------------------- converters
         const int ct = threadIdx.x - 64;  // 0..127
         const int t_n = 32 * (warp & 3) + lane;   // the output column this thread carries into its TMEM lane
         const uint32_t st_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        KP_DECL(3)
         for (int i = 0; i < nkb; ++i) {
             const int s = i % KT_STAGES, n = i / KT_STAGES;
             if (!kt_wait_warp(bar(KB_RAW + s), n & 1)) { kt_report(a.err, KERR_CONVERT); break; }
-            KP_ADD(0)
             const int ts = i % KT_T;
             if (i >= KT_T && !kt_wait_warp(bar(KB_T_EMPTY + ts), ((i / KT_T) - 1) & 1)) {
                 kt_report(a.err, KERR_CONVERT);
                 break;
             }
             tc_fence_after_sync();
-            KP_ADD(1)
             const uint32_t st = stage_addr(s);
             uint32_t hi[32], lo[32];
 #pragma unroll
@@ -258,9 +245,7 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // X lo, for the MMA's shared-memory reads
             tc_fence_before_sync();
             mbar_arrive(bar(KB_T_FULL + ts));
-            KP_ADD(2)
         }
-        if (ct == 0) { KP_OUT(8, 3) }
     } else {
         // --------------------------------------------------------------- drain
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
@@ -295,6 +280,7 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
     }
 
     // ------------------------------------------------------------ reduce + epilogue
+    grid_dep_wait();   // Y and the bias are touched only after the kernel before this one has finished
     if (nslices == 1) {
         if (warp >= 6 && n0 + t_row < a.N) {
 #pragma unroll
@@ -379,13 +365,15 @@ static int launch_inst(const SkinnyTcMaps &tm, const SkinnyArgs &a, int kb_total
     cfg.blockDim = dim3(KT_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute at;
-    at.id = cudaLaunchAttributeClusterDimension;
-    at.val.clusterDim.x = 1;
-    at.val.clusterDim.y = grid.y;   // all K-slices of a column tile
-    at.val.clusterDim.z = 1;
-    cfg.attrs = &at;
-    cfg.numAttrs = 1;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeClusterDimension;
+    at[0].val.clusterDim.x = 1;
+    at[0].val.clusterDim.y = grid.y;   // all K-slices of a column tile
+    at[0].val.clusterDim.z = 1;
+    at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // may start under the skinny call before it
+    at[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = a.pdl ? 2 : 1;
     return (int)cudaLaunchKernelEx(&cfg, kern, tm, a, kb_total);
 }
 

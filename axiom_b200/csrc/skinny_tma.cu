@@ -47,6 +47,13 @@ __device__ __forceinline__ float st_epilogue(const SkinnyArgs &a, float v, int m
     return v;
 }
 
+// floats of the region that holds the X slice [kchunk][mt] and later the CTA's strip sums [min(mt, 8)][<= 256]
+__host__ __device__ inline int skinny_tma_x_floats(int mt, int kchunk)
+{
+    const int x = kchunk * mt, sums = (mt < 8 ? mt : 8) * 256;
+    return ((x > sums ? x : sums) + 3) & ~3;
+}
+
 template <int MT, int CPL>
 __global__ void __launch_bounds__(ST_THREADS) skinny_tma_kernel(const __grid_constant__ CUtensorMap tmW,
                                                                 const SkinnyArgs a)
@@ -79,6 +86,7 @@ __global__ void __launch_bounds__(ST_THREADS) skinny_tma_kernel(const __grid_con
         tma_prefetch_desc(&tmW);
     }
     __syncthreads();
+    grid_dep_launch();   // a skinny call queued behind this one may start streaming ITS weights now
 
     // the producer puts the first stages in flight before anyone touches X
     if (warp == ST_CONSUMERS && lane == 0) {
@@ -87,15 +95,56 @@ __global__ void __launch_bounds__(ST_THREADS) skinny_tma_kernel(const __grid_con
             tma_load_2d(ring + st * ST_STAGE_BYTES, &tmW, bar_full + 8 * st, strip * COLS, (int)(k_begin + st * R));
         }
     }
+    // the weights were requested while the kernel before this one may still be running (programmatic dependent
+    // launch); X may be its output and Y its input, so everything else waits until it has finished
+    grid_dep_wait();
     // X slice -> shared as [k][MT]; for MT >= 8 the float4 groups of a row are XOR-permuted with k so
-    // the transposing stores spread over the banks (a lane stores one k, lanes differ in k)
-    for (int kk = tid; kk < kc; kk += ST_THREADS) {
-        const int swz = MT >= 4 ? ((kk & 7) & (MT / 4 - 1)) : 0;
-#pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            const float v = (m < a.M) ? __ldg(a.X + (int64_t)m * a.K + k_begin + kk) : 0.0f;
+    // the transposing stores spread over the banks (a lane stores one k, lanes differ in k).  Four consecutive k of
+    // one row per 128-bit load when the rows allow it: the loads of a thread are independent and in flight together,
+    // where one scalar load per (k, m) made the slice the longest wait before the first multiply (2.5 us at M = 8).
+    {
+        auto put = [&](int kk, int m, float v) {
+            const int swz = MT >= 4 ? ((kk & 7) & (MT / 4 - 1)) : 0;
             const int pm = MT >= 4 ? ((((m >> 2) ^ swz) << 2) | (m & 3)) : m;
             xs[kk * MT + pm] = v;
+        };
+        const bool xvec = ((a.K | k_begin) & 3) == 0 && (reinterpret_cast<uintptr_t>(a.X) & 15) == 0;
+        if (xvec) {
+            const int kq = (kc + 3) >> 2;   // groups of four k
+            constexpr int XB = 4;           // loads of a thread issued together, before any of them is stored
+            for (int it0 = 0; it0 < kq * MT; it0 += XB * ST_THREADS) {
+                float4 v[XB];
+#pragma unroll
+                for (int j = 0; j < XB; ++j) {
+                    const int it = it0 + j * ST_THREADS + tid;
+                    const int g = it / MT, m = it - g * MT, kk = g << 2;   // lanes run over the rows first
+                    v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (it < kq * MT && m < a.M) {
+                        const float *src = a.X + (int64_t)m * a.K + k_begin + kk;
+                        if (kk + 4 <= kc) v[j] = __ldg(reinterpret_cast<const float4 *>(src));
+                        else {
+                            v[j].x = __ldg(src);
+                            if (kk + 1 < kc) v[j].y = __ldg(src + 1);
+                            if (kk + 2 < kc) v[j].z = __ldg(src + 2);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < XB; ++j) {
+                    const int it = it0 + j * ST_THREADS + tid;
+                    if (it >= kq * MT) continue;
+                    const int g = it / MT, m = it - g * MT, kk = g << 2;
+                    put(kk, m, v[j].x);
+                    if (kk + 1 < kc) put(kk + 1, m, v[j].y);
+                    if (kk + 2 < kc) put(kk + 2, m, v[j].z);
+                    if (kk + 3 < kc) put(kk + 3, m, v[j].w);
+                }
+            }
+        } else {
+            for (int kk = tid; kk < kc; kk += ST_THREADS) {
+#pragma unroll
+                for (int m = 0; m < MT; ++m) put(kk, m, (m < a.M) ? __ldg(a.X + (int64_t)m * a.K + k_begin + kk) : 0.0f);
+            }
         }
     }
     __syncthreads();
@@ -222,33 +271,35 @@ __global__ void __launch_bounds__(ST_THREADS) skinny_tma_kernel(const __grid_con
     }
 
     if (a.ksplit > 1 && a.cluster) {
-        // The K-slices of this strip are the CTAs of one cluster: the outputs of the strip are dealt out to all of
-        // them, and each adds the slices' sums straight out of their shared memory, in slice order, so no scratch in
-        // global memory is touched.  All remote loads of an output are in flight together: one after the other
-        // (and all outputs on one CTA) they cost a round trip each, ~6 us at M = 8.
+        // The K-slices of this strip are the CTAs of one cluster and the strip's outputs are dealt out to them in
+        // contiguous shares: slice r finishes outputs [r * per_owner, (r + 1) * per_owner).  Every slice PUSHES its sums into the owners' shared memory (remote
+        // stores, fire and forget: slot [sender][o % per_owner] of a region behind X, which nobody reads any more), one
+        // cluster barrier makes them visible, and each owner adds the slices in slice order out of its OWN memory — no
+        // scratch in global memory, bitwise repeatable, and nobody reads a peer, so no second barrier keeps the
+        // CTAs alive.  (Pulling the sums with remote loads needed that second barrier and a round trip: 2.9 us.)
+        const int ncols = (int)min((int64_t)COLS, a.N - (int64_t)strip * COLS);
+        const int total = a.M * ncols;
+        const int per_owner = (total + a.ksplit - 1) / a.ksplit;
+        // [ksplit][per_owner], behind the X slice: a peer that finishes early pushes while this CTA still reads X
+        float *inbox = xs + skinny_tma_x_floats(MT, a.kchunk);
+        const uint32_t me = cluster_cta_rank();
+        for (int o = tid; o < total; o += ST_THREADS) {
+            const int m = o / ncols, c = o - m * ncols;
+            const int owner = o / per_owner, idx = o - owner * per_owner;
+            const uint32_t dst = map_to_cta(smem_u32(inbox + (int)me * per_owner + idx), (uint32_t)owner);
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(dst), "f"(xs[m * COLS + c]) : "memory");
+        }
         cluster_sync_all();
-        {
-            const int ncols = (int)min((int64_t)COLS, a.N - (int64_t)strip * COLS);
-            const int total = a.M * ncols;
-            for (int o = (int)cluster_cta_rank() * ST_THREADS + tid; o < total; o += a.ksplit * ST_THREADS) {
+        for (int idx = tid; idx < per_owner; idx += ST_THREADS) {
+            const int o = (int)me * per_owner + idx;
+            if (o < total) {
+                float sum = 0.0f;
+                for (int q = 0; q < a.ksplit; ++q) sum += inbox[q * per_owner + idx];
                 const int m = o / ncols, c = o - m * ncols;
-                const uint32_t local = smem_u32(xs + m * COLS + c);
-                float v[8];
-#pragma unroll
-                for (int q = 0; q < 8; ++q) {
-                    v[q] = 0.0f;
-                    if (q < a.ksplit)
-                        asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v[q]) : "r"(map_to_cta(local, (uint32_t)q)));
-                }
-                float s = 0.0f;
-#pragma unroll
-                for (int q = 0; q < 8; ++q)
-                    if (q < a.ksplit) s += v[q];
                 const int64_t gc = (int64_t)strip * COLS + c;
-                a.Y[(int64_t)m * a.N + gc] = st_epilogue(a, s, m, gc);
+                a.Y[(int64_t)m * a.N + gc] = st_epilogue(a, sum, m, gc);
             }
         }
-        cluster_sync_all();   // the other CTAs' shared memory must outlive the reads above
     } else if (a.ksplit > 1) {
         __threadfence();
         __syncthreads();
@@ -294,19 +345,33 @@ static int launch_tma_inst(const CUtensorMap &tm, const SkinnyArgs &a, dim3 grid
         at.val.clusterDim.x = 1;
         at.val.clusterDim.y = grid.y;   // all K-slices of a strip
         at.val.clusterDim.z = 1;
-        cfg.attrs = &at;
-        cfg.numAttrs = 1;
+        cudaLaunchAttribute ats[2] = { at, {} };
+        ats[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        ats[1].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = ats;
+        cfg.numAttrs = a.pdl ? 2 : 1;
         return (int)cudaLaunchKernelEx(&cfg, k, tm, a);
     }
-    k<<<grid, ST_THREADS, smem, st>>>(tm, a);
-    return (int)cudaGetLastError();
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(ST_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = a.pdl ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, k, tm, a);
 }
 
 int skinny_tma_strip_cols(int mt, int cluster) { return (mt <= 8 && !cluster) ? 256 : 128; }
 int skinny_tma_stage_rows(int mt, int cluster) { return ST_STAGE_BYTES / (skinny_tma_strip_cols(mt, cluster) * 4); }
 size_t skinny_tma_smem_bytes(int mt, int kchunk, int stages)
 {
-    return (size_t)ST_HEADER + 128 + (size_t)stages * ST_STAGE_BYTES + (size_t)kchunk * mt * 4;
+    // header, ring, the X slice [kchunk][mt] (which later carries this CTA's strip sums, at most [8][256]) and, behind
+    // it, the inbox of the cluster reduction: [ksplit][ceil(M * 128 / ksplit)] <= 8 * 128 + 8 floats
+    return (size_t)ST_HEADER + 128 + (size_t)stages * ST_STAGE_BYTES + ((size_t)skinny_tma_x_floats(mt, kchunk) + 1024 + 8) * 4;
 }
 
 int launch_skinny_tma(const SkinnyArgs &a, const SkinnyPlan &plan, cudaStream_t st)
