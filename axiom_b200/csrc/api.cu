@@ -64,7 +64,19 @@ struct Engine {
     char msg[320] = "";
 };
 
-Engine g;
+// One engine per device.  A host thread drives the device it selected with axb_init (a thread that never did uses
+// the first device any thread initialised): one process per GPU sees exactly one engine, a host that walks several
+// devices from one thread (the multi-GPU entry points, mgpu.cu) switches with axb_init(device).
+constexpr int kMaxDevices = 16;
+Engine g_engines[kMaxDevices];
+thread_local int tl_device = -1;
+int g_default_device = -1;
+
+inline Engine &cur()
+{
+    const int d = tl_device >= 0 ? tl_device : (g_default_device >= 0 ? g_default_device : 0);
+    return g_engines[d];
+}
 
 // split-K scratch of the tensor-core GEMM: room for one partial tile per SM (148 x 128 x 256 fp32 < 20 MiB)
 constexpr size_t kSplitScratch = (size_t)20 << 20;
@@ -74,7 +86,7 @@ int fail(int status, const char *fmt, ...)
 {
     va_list ap;
     va_start(ap, fmt);
-    vsnprintf(g.msg, sizeof g.msg, fmt, ap);
+    vsnprintf(cur().msg, sizeof cur().msg, fmt, ap);
     va_end(ap);
     return status;
 }
@@ -89,32 +101,32 @@ inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 inline void mark(int i)
 {
-    if (!g.profiling) return;
-    cudaEvent_t *slot = g.ev[g.ev_count % Engine::EV_RING];
+    if (!cur().profiling) return;
+    cudaEvent_t *slot = cur().ev[cur().ev_count % Engine::EV_RING];
     if (!slot[i]) cudaEventCreate(&slot[i]);
-    cudaEventRecord(slot[i], g.stream);
-    if (i == 2) g.ev_count++;
+    cudaEventRecord(slot[i], cur().stream);
+    if (i == 2) cur().ev_count++;
 }
 
 int ensure_ready()
 {
-    if (g.ready) return AXB_OK;
+    if (cur().ready) return AXB_OK;
     return axb_init(-1);
 }
 
 int ensure_ws(size_t bytes)
 {
-    if (bytes <= g.ws_bytes) return AXB_OK;
-    if (g.ws) {
-        cudaStreamSynchronize(g.stream);
-        cudaFree(g.ws);
-        g.ws = nullptr;
-        g.ws_bytes = 0;
+    if (bytes <= cur().ws_bytes) return AXB_OK;
+    if (cur().ws) {
+        cudaStreamSynchronize(cur().stream);
+        cudaFree(cur().ws);
+        cur().ws = nullptr;
+        cur().ws_bytes = 0;
     }
     const size_t want = round_up(bytes + bytes / 8, (size_t)1 << 20);
-    cudaError_t e = cudaMalloc(&g.ws, want);
+    cudaError_t e = cudaMalloc(&cur().ws, want);
     if (e != cudaSuccess) return fail(AXB_ERR_ALLOC, "scratch allocation of %zu bytes failed: %s", want, cudaGetErrorString(e));
-    g.ws_bytes = want;
+    cur().ws_bytes = want;
     return AXB_OK;
 }
 
@@ -135,7 +147,7 @@ TcSplitK take_splitk(Carver &c)
     TcSplitK sk;
     sk.scratch = c.take(kSplitScratch);
     sk.scratch_bytes = kSplitScratch;
-    sk.counters = g.gemm_counters;
+    sk.counters = cur().gemm_counters;
     sk.n_counters = kSplitCounters;
     return sk;
 }
@@ -170,9 +182,9 @@ int run_split(const SplitOperand &s, const float *src, int64_t ld, bool transpos
     }
     op.rows = s.rows;
     op.pitch_elems = s.pitch;
-    int e = split_planes(s.mode, src, s.rows, s.k, ld, transposed, planes, s.pitch, g.sm_count, g.stream, chunk_k,
+    int e = split_planes(s.mode, src, s.rows, s.k, ld, transposed, planes, s.pitch, cur().sm_count, cur().stream, chunk_k,
                          chunk_stride);
-    g.launches++;
+    cur().launches++;
     return e;
 }
 
@@ -180,7 +192,7 @@ int run_split(const SplitOperand &s, const float *src, int64_t ld, bool transpos
 void fp32_mode_plan(int &split_mode, int &kind, TcProducts &prod)
 {
     memset(&prod, 0, sizeof prod);
-    switch (g.fp32_mode) {
+    switch (cur().fp32_mode) {
     case AXB_FP32_BF16:
         split_mode = SPLIT_BF16X1; kind = KIND_BF16;
         prod.n = 1; prod.a[0] = 0; prod.b[0] = 0;
@@ -189,13 +201,13 @@ void fp32_mode_plan(int &split_mode, int &kind, TcProducts &prod)
     case AXB_FP32_BF16X3:
         split_mode = SPLIT_BF16X2; kind = KIND_BF16;
         prod.n = 3; prod.a[0] = 1; prod.b[0] = 0; prod.a[1] = 0; prod.b[1] = 1; prod.a[2] = 0; prod.b[2] = 0;
-        prod.chunk_k = g.chunk_bf16;
+        prod.chunk_k = cur().chunk_bf16;
         break;
     default:
         split_mode = SPLIT_TF32X2; kind = KIND_TF32;
         // small cross terms first, the hi.hi product last
         prod.n = 3; prod.a[0] = 1; prod.b[0] = 0; prod.a[1] = 0; prod.b[1] = 1; prod.a[2] = 0; prod.b[2] = 0;
-        prod.chunk_k = g.chunk_tf32;
+        prod.chunk_k = cur().chunk_tf32;
         break;
     }
 }
@@ -212,7 +224,7 @@ int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int
     const SplitOperand sa = plan_split(split_mode, M, K), sb = plan_split(split_mode, N, K);
     int st = ensure_ws(sa.total() + sb.total() + kSplitScratch);
     if (st) return st;
-    Carver carve{ (char *)g.ws };
+    Carver carve{ (char *)cur().ws };
     const TcSplitK sk = take_splitk(carve);
     TcOperand opa, opb;
     mark(0);
@@ -226,8 +238,8 @@ int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int
     opa.rows = sa.rows; opa.pitch_elems = sa.pitch;
     opb.rows = sb.rows; opb.pitch_elems = sb.pitch;
     int e = split_planes_pair(split_mode, A, M, ta ? M : K, ta != 0, pa, sa.pitch, a_chunk_k, a_chunk_stride, B, N,
-                              tb ? K : N, tb == 0, pb, sb.pitch, K, g.sm_count, g.stream);
-    g.launches++;
+                              tb ? K : N, tb == 0, pb, sb.pitch, K, cur().sm_count, cur().stream);
+    cur().launches++;
     if (e) return cuda_fail("split operands", e);
     TcEpilogue ep;
     ep.n_extra = 0;
@@ -240,9 +252,9 @@ int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int
         for (int i = 0; i < 3; ++i) ep.hs_out[i] = head_out[i];
     }
     mark(1);
-    e = launch_gemm_tc(kind, opa, opb, prod, M, N, K, ep, g.err_word, g.sm_count, g.stream, &sk);
+    e = launch_gemm_tc(kind, opa, opb, prod, M, N, K, ep, cur().err_word, cur().sm_count, cur().stream, &sk);
     mark(2);
-    g.launches++;
+    cur().launches++;
     if (e) return cuda_fail("tcgen05 gemm", e);
     return AXB_OK;
 }
@@ -253,66 +265,69 @@ int gemm_skinny(const float *X, const float *W, const float *bias, float *Y, int
     // back-to-back skinny calls (a decode step walks a chain of them) overlap: this call may request its first weight
     // tiles while the previous one drains, unless those weights are what the previous call wrote
     const char *w_lo = reinterpret_cast<const char *>(W), *w_hi = w_lo + (size_t)K * N * sizeof(float);
-    const int pdl = !(g.chain_lo && w_lo < g.chain_hi && g.chain_lo < w_hi);
-    g.chain_lo = reinterpret_cast<const char *>(Y);
-    g.chain_hi = g.chain_lo + (size_t)M * N * sizeof(float);
+    const int pdl = !(cur().chain_lo && w_lo < cur().chain_hi && cur().chain_lo < w_hi);
+    cur().chain_lo = reinterpret_cast<const char *>(Y);
+    cur().chain_hi = cur().chain_lo + (size_t)M * N * sizeof(float);
     // above 8 rows the fp32 pipe, not memory, paces the FMA kernels: the tensor-core variant takes over
     if (M >= 9 && skinny_tc_applicable(M, N, K, X, W)) {
         SkinnyArgs a;
         a.X = X; a.W = W; a.bias = bias; a.Y = Y; a.M = (int)M; a.N = N; a.K = K;
         a.alpha = alpha; a.beta = beta; a.act = act;
         a.ksplit = 0; a.kchunk = 0; a.stages = 0; a.cluster = 0; a.partial = nullptr; a.counters = nullptr;
-        a.err = g.err_word;
+        a.err = cur().err_word;
         a.pdl = pdl;
         mark(0);
         mark(1);
-        int e = launch_skinny_tc(a, g.sm_count, g.stream);
+        int e = launch_skinny_tc(a, cur().sm_count, cur().stream);
         mark(2);
-        g.launches++;
+        cur().launches++;
         if (e) return cuda_fail("skinny tensor-core gemm", e);
         return AXB_OK;
     }
     SkinnyPlan plan;
-    skinny_plan(M, N, K, W, g.sm_count, &plan);
-    if ((size_t)plan.partial_floats > g.sk_partial_floats) {
-        if (g.sk_partial) { cudaStreamSynchronize(g.stream); cudaFree(g.sk_partial); g.sk_partial = nullptr; }
+    skinny_plan(M, N, K, W, cur().sm_count, &plan);
+    if ((size_t)plan.partial_floats > cur().sk_partial_floats) {
+        if (cur().sk_partial) { cudaStreamSynchronize(cur().stream); cudaFree(cur().sk_partial); cur().sk_partial = nullptr; }
         const size_t want = (size_t)plan.partial_floats + (size_t)plan.partial_floats / 4;
-        cudaError_t e = cudaMalloc(&g.sk_partial, want * sizeof(float));
-        if (e != cudaSuccess) { g.sk_partial_floats = 0; return fail(AXB_ERR_ALLOC, "skinny scratch: %s", cudaGetErrorString(e)); }
-        g.sk_partial_floats = want;
+        cudaError_t e = cudaMalloc(&cur().sk_partial, want * sizeof(float));
+        if (e != cudaSuccess) { cur().sk_partial_floats = 0; return fail(AXB_ERR_ALLOC, "skinny scratch: %s", cudaGetErrorString(e)); }
+        cur().sk_partial_floats = want;
     }
-    if (plan.strips > g.sk_counter_cap) {
-        if (g.sk_counters) { cudaStreamSynchronize(g.stream); cudaFree(g.sk_counters); g.sk_counters = nullptr; }
+    if (plan.strips > cur().sk_counter_cap) {
+        if (cur().sk_counters) { cudaStreamSynchronize(cur().stream); cudaFree(cur().sk_counters); cur().sk_counters = nullptr; }
         const int want = plan.strips * 2 + 64;
-        cudaError_t e = cudaMalloc(&g.sk_counters, (size_t)want * sizeof(int));
-        if (e != cudaSuccess) { g.sk_counter_cap = 0; return fail(AXB_ERR_ALLOC, "skinny counters: %s", cudaGetErrorString(e)); }
-        cudaMemsetAsync(g.sk_counters, 0, (size_t)want * sizeof(int), g.stream);
-        g.sk_counter_cap = want;
+        cudaError_t e = cudaMalloc(&cur().sk_counters, (size_t)want * sizeof(int));
+        if (e != cudaSuccess) { cur().sk_counter_cap = 0; return fail(AXB_ERR_ALLOC, "skinny counters: %s", cudaGetErrorString(e)); }
+        cudaMemsetAsync(cur().sk_counters, 0, (size_t)want * sizeof(int), cur().stream);
+        cur().sk_counter_cap = want;
     }
     SkinnyArgs a;
     a.X = X; a.W = W; a.bias = bias; a.Y = Y; a.M = (int)M; a.N = N; a.K = K;
     a.alpha = alpha; a.beta = beta; a.act = act;
     a.ksplit = plan.ksplit; a.kchunk = plan.kchunk; a.stages = plan.stages; a.cluster = plan.cluster;
-    a.partial = (plan.ksplit > 1 && !plan.cluster) ? g.sk_partial : nullptr;
-    a.counters = g.sk_counters;
-    a.err = g.err_word;
+    a.partial = (plan.ksplit > 1 && !plan.cluster) ? cur().sk_partial : nullptr;
+    a.counters = cur().sk_counters;
+    a.err = cur().err_word;
     a.pdl = pdl;
     mark(0);
     mark(1);
-    int e = launch_skinny(a, plan, g.stream);
+    int e = launch_skinny(a, plan, cur().stream);
     mark(2);
-    g.launches++;
+    cur().launches++;
     if (e) return cuda_fail("skinny gemm", e);
     return AXB_OK;
 }
 
 }  // namespace
 
+cudaStream_t axb::engine_stream() { return cur().stream; }
+int axb::engine_device() { return tl_device >= 0 ? tl_device : g_default_device; }
+
 int axb::set_error(int status, const char *fmt, ...)
 {
     va_list ap;
     va_start(ap, fmt);
-    vsnprintf(g.msg, sizeof g.msg, fmt, ap);
+    vsnprintf(cur().msg, sizeof cur().msg, fmt, ap);
     va_end(ap);
     return status;
 }
@@ -321,58 +336,70 @@ int axb::set_error(int status, const char *fmt, ...)
 
 extern "C" int axb_init(int device)
 {
-    if (g.ready) return AXB_OK;
     int count = 0;
     cudaError_t e = cudaGetDeviceCount(&count);
     if (e != cudaSuccess || count == 0)
         return fail(AXB_ERR_BACKEND, "no CUDA device: %s", e == cudaSuccess ? "device count is 0" : cudaGetErrorString(e));
     if (device < 0) {
-        if (cudaGetDevice(&device) != cudaSuccess) device = 0;
+        if (tl_device >= 0) device = tl_device;
+        else if (g_default_device >= 0) device = g_default_device;
+        else if (cudaGetDevice(&device) != cudaSuccess) device = 0;
     }
-    if (device >= count) return fail(AXB_ERR_BACKEND, "device %d out of range (%d devices)", device, count);
+    if (device >= count || device >= kMaxDevices)
+        return fail(AXB_ERR_BACKEND, "device %d out of range (%d devices, at most %d engines)", device, count, kMaxDevices);
     if ((e = cudaSetDevice(device)) != cudaSuccess) return cuda_fail("cudaSetDevice", e);
+    tl_device = device;
+    if (g_default_device < 0) g_default_device = device;
+    Engine &en = g_engines[device];
+    if (en.ready) return AXB_OK;
     cudaDeviceProp prop;
     if ((e = cudaGetDeviceProperties(&prop, device)) != cudaSuccess) return cuda_fail("cudaGetDeviceProperties", e);
     if (prop.major != 10)
         return fail(AXB_ERR_BACKEND, "device %d is sm_%d%d; this engine holds sm_100a code only", device, prop.major, prop.minor);
-    g.device = device;
-    g.sm_count = prop.multiProcessorCount;
-    if ((e = cudaMalloc(&g.err_word, sizeof(int))) != cudaSuccess) return cuda_fail("cudaMalloc", e);
-    cudaMemset(g.err_word, 0, sizeof(int));
-    if ((e = cudaMalloc(&g.gemm_counters, kSplitCounters * sizeof(int))) != cudaSuccess) return cuda_fail("cudaMalloc", e);
-    cudaMemset(g.gemm_counters, 0, kSplitCounters * sizeof(int));
+    en.device = device;
+    en.sm_count = prop.multiProcessorCount;
+    if ((e = cudaMalloc(&en.err_word, sizeof(int))) != cudaSuccess) return cuda_fail("cudaMalloc", e);
+    cudaMemset(en.err_word, 0, sizeof(int));
+    if ((e = cudaMalloc(&en.gemm_counters, kSplitCounters * sizeof(int))) != cudaSuccess) return cuda_fail("cudaMalloc", e);
+    cudaMemset(en.gemm_counters, 0, kSplitCounters * sizeof(int));
     const char *mode = getenv("AX_B200_FP32_MODE");
     if (mode) {
-        if (!strcmp(mode, "bf16")) g.fp32_mode = AXB_FP32_BF16;
-        else if (!strcmp(mode, "bf16x3")) g.fp32_mode = AXB_FP32_BF16X3;
-        else if (!strcmp(mode, "3xtf32")) g.fp32_mode = AXB_FP32_3XTF32;
+        if (!strcmp(mode, "bf16")) en.fp32_mode = AXB_FP32_BF16;
+        else if (!strcmp(mode, "bf16x3")) en.fp32_mode = AXB_FP32_BF16X3;
+        else if (!strcmp(mode, "3xtf32")) en.fp32_mode = AXB_FP32_3XTF32;
     }
-    g.ready = true;
+    en.ready = true;
     if (getenv("AX_B200_VERBOSE"))
         fprintf(stderr, "axiom: b200 engine on device %d (%s, %d SMs), fp32 mode %d\n", device, prop.name,
-                g.sm_count, g.fp32_mode);
+                en.sm_count, en.fp32_mode);
     return AXB_OK;
 }
 
 extern "C" void axb_shutdown(void)
 {
-    if (!g.ready) return;
-    cudaDeviceSynchronize();
-    if (g.ws) cudaFree(g.ws);
-    if (g.sk_partial) cudaFree(g.sk_partial);
-    if (g.sk_counters) cudaFree(g.sk_counters);
-    if (g.err_word) cudaFree(g.err_word);
-    if (g.gemm_counters) cudaFree(g.gemm_counters);
-    if (g.hp_buf) cudaFree(g.hp_buf);
-    if (g.aux) cudaFree(g.aux);
-    if (g.hp_in) cudaStreamDestroy(g.hp_in);
-    if (g.hp_out) cudaStreamDestroy(g.hp_out);
-    for (auto &e : g.hp_ev)
-        if (e) cudaEventDestroy(e);
-    for (auto &slot : g.ev)
-        for (auto &e : slot)
-            if (e) cudaEventDestroy(e);
-    g = Engine();
+    for (int d = 0; d < kMaxDevices; ++d) {
+        Engine &en = g_engines[d];
+        if (!en.ready) continue;
+        cudaSetDevice(d);
+        cudaDeviceSynchronize();
+        if (en.ws) cudaFree(en.ws);
+        if (en.sk_partial) cudaFree(en.sk_partial);
+        if (en.sk_counters) cudaFree(en.sk_counters);
+        if (en.err_word) cudaFree(en.err_word);
+        if (en.gemm_counters) cudaFree(en.gemm_counters);
+        if (en.hp_buf) cudaFree(en.hp_buf);
+        if (en.aux) cudaFree(en.aux);
+        if (en.hp_in) cudaStreamDestroy(en.hp_in);
+        if (en.hp_out) cudaStreamDestroy(en.hp_out);
+        for (auto &ev : en.hp_ev)
+            if (ev) cudaEventDestroy(ev);
+        for (auto &slot : en.ev)
+            for (auto &ev : slot)
+                if (ev) cudaEventDestroy(ev);
+        en = Engine();
+    }
+    tl_device = -1;
+    g_default_device = -1;
 }
 
 extern "C" int axb_device_count(void)
@@ -384,7 +411,7 @@ extern "C" int axb_device_count(void)
 
 extern "C" void axb_synchronize(void)
 {
-    if (!g.ready) return;
+    if (!cur().ready) return;
     cudaError_t e = cudaDeviceSynchronize();
     if (e != cudaSuccess) cuda_fail("synchronize", e);
 }
@@ -398,7 +425,7 @@ extern "C" void *axb_storage_alloc(size_t bytes)
         fail(AXB_ERR_ALLOC, "storage_alloc(%zu): %s", bytes, cudaGetErrorString(e));
         return nullptr;
     }
-    if (bytes) cudaMemsetAsync(p, 0, bytes, g.stream);
+    if (bytes) cudaMemsetAsync(p, 0, bytes, cur().stream);
     return p;
 }
 
@@ -411,8 +438,8 @@ extern "C" int axb_memcpy_h2d(void *dst, const void *src_host, size_t bytes)
 {
     if (!dst || !src_host) return fail(AXB_ERR_NULL_ARG, "memcpy_h2d: NULL");
     if (ensure_ready()) return AXB_ERR_BACKEND;
-    cudaError_t e = cudaMemcpyAsync(dst, src_host, bytes, cudaMemcpyHostToDevice, g.stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(g.stream);
+    cudaError_t e = cudaMemcpyAsync(dst, src_host, bytes, cudaMemcpyHostToDevice, cur().stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(cur().stream);
     return e == cudaSuccess ? AXB_OK : cuda_fail("memcpy_h2d", e);
 }
 
@@ -420,8 +447,8 @@ extern "C" int axb_memcpy_d2h(void *dst_host, const void *src, size_t bytes)
 {
     if (!dst_host || !src) return fail(AXB_ERR_NULL_ARG, "memcpy_d2h: NULL");
     if (ensure_ready()) return AXB_ERR_BACKEND;
-    cudaError_t e = cudaMemcpyAsync(dst_host, src, bytes, cudaMemcpyDeviceToHost, g.stream);
-    if (e == cudaSuccess) e = cudaStreamSynchronize(g.stream);
+    cudaError_t e = cudaMemcpyAsync(dst_host, src, bytes, cudaMemcpyDeviceToHost, cur().stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(cur().stream);
     return e == cudaSuccess ? AXB_OK : cuda_fail("memcpy_d2h", e);
 }
 
@@ -429,33 +456,33 @@ extern "C" int axb_memcpy_d2d(void *dst, const void *src, size_t bytes)
 {
     if (!dst || !src) return fail(AXB_ERR_NULL_ARG, "memcpy_d2d: NULL");
     if (ensure_ready()) return AXB_ERR_BACKEND;
-    cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, g.stream);
+    cudaError_t e = cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, cur().stream);
     return e == cudaSuccess ? AXB_OK : cuda_fail("memcpy_d2d", e);
 }
 
 extern "C" void axb_set_stream(void *cuda_stream)
 {
-    g.stream = (cudaStream_t)cuda_stream;
-    g.chain_lo = g.chain_hi = nullptr;
+    cur().stream = (cudaStream_t)cuda_stream;
+    cur().chain_lo = cur().chain_hi = nullptr;
 }
 
 extern "C" int axb_set_fp32_mode(int mode)
 {
     if (mode < AXB_FP32_3XTF32 || mode > AXB_FP32_BF16) return fail(AXB_ERR_INVALID_SHAPE, "unknown fp32 mode %d", mode);
-    g.fp32_mode = mode;
+    cur().fp32_mode = mode;
     return AXB_OK;
 }
 
-extern "C" int axb_get_fp32_mode(void) { return g.fp32_mode; }
-extern "C" const char *axb_last_error(void) { return g.msg; }
+extern "C" int axb_get_fp32_mode(void) { return cur().fp32_mode; }
+extern "C" const char *axb_last_error(void) { return cur().msg; }
 
 extern "C" int axb_device_error(void)
 {
-    if (!g.ready || !g.err_word) return 0;
+    if (!cur().ready || !cur().err_word) return 0;
     int v = 0;
-    if (cudaMemcpy(&v, g.err_word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
+    if (cudaMemcpy(&v, cur().err_word, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return -1;
     if (v) {
-        cudaMemset(g.err_word, 0, sizeof(int));
+        cudaMemset(cur().err_word, 0, sizeof(int));
         fail(AXB_ERR_BACKEND, "a kernel gave up on a bounded wait (code %d)", v);
     }
     return v;
@@ -463,17 +490,17 @@ extern "C" int axb_device_error(void)
 
 extern "C" void axb_set_profiling(int on)
 {
-    g.profiling = on != 0;
-    g.ev_count = 0;
+    cur().profiling = on != 0;
+    cur().ev_count = 0;
 }
 
 extern "C" int axb_timing_summary(int *calls, float *prepass_ms_total, float *core_ms_total)
 {
-    if (!g.profiling) return fail(AXB_ERR_BACKEND, "timing_summary: profiling is off");
-    const int n = g.ev_count < Engine::EV_RING ? g.ev_count : Engine::EV_RING;
+    if (!cur().profiling) return fail(AXB_ERR_BACKEND, "timing_summary: profiling is off");
+    const int n = cur().ev_count < Engine::EV_RING ? cur().ev_count : Engine::EV_RING;
     float pre = 0.f, core = 0.f;
     for (int i = 0; i < n; ++i) {
-        cudaEvent_t *slot = g.ev[(g.ev_count - 1 - i) % Engine::EV_RING];
+        cudaEvent_t *slot = cur().ev[(cur().ev_count - 1 - i) % Engine::EV_RING];
         cudaError_t e = cudaEventSynchronize(slot[2]);
         if (e != cudaSuccess) return cuda_fail("timing_summary", e);
         float a = 0.f, b = 0.f;
@@ -485,18 +512,18 @@ extern "C" int axb_timing_summary(int *calls, float *prepass_ms_total, float *co
     if (calls) *calls = n;
     if (prepass_ms_total) *prepass_ms_total = pre;
     if (core_ms_total) *core_ms_total = core;
-    g.ev_count = 0;
+    cur().ev_count = 0;
     return AXB_OK;
 }
 
 extern "C" int axb_timing_samples(float *prepass_ms, float *core_ms, int cap, int *n_out)
 {
-    if (!g.profiling) return fail(AXB_ERR_BACKEND, "timing_samples: profiling is off");
+    if (!cur().profiling) return fail(AXB_ERR_BACKEND, "timing_samples: profiling is off");
     if (!n_out || cap < 0) return fail(AXB_ERR_NULL_ARG, "timing_samples: NULL");
-    int n = g.ev_count < Engine::EV_RING ? g.ev_count : Engine::EV_RING;
+    int n = cur().ev_count < Engine::EV_RING ? cur().ev_count : Engine::EV_RING;
     if (n > cap) n = cap;
     for (int i = 0; i < n; ++i) {   // oldest of the kept calls first
-        cudaEvent_t *slot = g.ev[(g.ev_count - n + i) % Engine::EV_RING];
+        cudaEvent_t *slot = cur().ev[(cur().ev_count - n + i) % Engine::EV_RING];
         cudaError_t e = cudaEventSynchronize(slot[2]);
         if (e != cudaSuccess) return cuda_fail("timing_samples", e);
         float a = 0.f, b = 0.f;
@@ -511,8 +538,8 @@ extern "C" int axb_timing_samples(float *prepass_ms, float *core_ms, int cap, in
 
 extern "C" int64_t axb_launch_count(int reset)
 {
-    const int64_t v = g.launches;
-    if (reset) g.launches = 0;
+    const int64_t v = cur().launches;
+    if (reset) cur().launches = 0;
     return v;
 }
 
@@ -532,10 +559,10 @@ extern "C" int axb_gemm_bias_act(const float *A, const float *B, const float *bi
     if (K == 0) {
         // empty contraction: C = act(beta*C + bias) via the skinny kernel's epilogue is not
         // reachable (no rows to stream); express it as the bias/activation passes
-        if (beta == 0.0f) cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(float), g.stream);
+        if (beta == 0.0f) cudaMemsetAsync(C, 0, (size_t)M * N * sizeof(float), cur().stream);
         else if (beta != 1.0f) return fail(AXB_ERR_NOT_IMPLEMENTED, "gemm: K == 0 with beta not in {0,1}");
-        if (bias) { int e = launch_bias_add(C, bias, 1, C, M, N, g.sm_count, g.stream); g.launches++; if (e) return cuda_fail("bias_add", e); }
-        if (act) { int e = launch_unary(act == AXB_ACT_RELU ? 0 : 1, C, C, M * N, g.sm_count, g.stream); g.launches++; if (e) return cuda_fail("activation", e); }
+        if (bias) { int e = launch_bias_add(C, bias, 1, C, M, N, cur().sm_count, cur().stream); cur().launches++; if (e) return cuda_fail("bias_add", e); }
+        if (act) { int e = launch_unary(act == AXB_ACT_RELU ? 0 : 1, C, C, M * N, cur().sm_count, cur().stream); cur().launches++; if (e) return cuda_fail("activation", e); }
         return AXB_OK;
     }
     if (M <= 32 && !trans_a && !trans_b) return gemm_skinny(A, B, bias, C, M, N, K, alpha, beta, act);
@@ -649,10 +676,10 @@ extern "C" int axb_gemm_host(const float *A, const float *B, float *C, int64_t M
     if (M > INT32_MAX || N > INT32_MAX || K > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "gemm_host: dimension exceeds 2^31-1");
     int st = ensure_ready();
     if (st) return st;
-    if (!g.hp_in) {
-        cudaError_t e = cudaStreamCreateWithFlags(&g.hp_in, cudaStreamNonBlocking);
-        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&g.hp_out, cudaStreamNonBlocking);
-        for (auto &ev : g.hp_ev)
+    if (!cur().hp_in) {
+        cudaError_t e = cudaStreamCreateWithFlags(&cur().hp_in, cudaStreamNonBlocking);
+        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&cur().hp_out, cudaStreamNonBlocking);
+        for (auto &ev : cur().hp_ev)
             if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ev, cudaEventDisableTiming);
         if (e != cudaSuccess) return cuda_fail("gemm_host: streams", e);
     }
@@ -665,23 +692,23 @@ extern "C" int axb_gemm_host(const float *A, const float *B, float *C, int64_t M
         int sm, kd;
         TcProducts pr;
         fp32_mode_plan(sm, kd, pr);
-        if (tensor_path && gemm_tc_splits_k(kd, pr, M, N, K, g.sm_count)) {
+        if (tensor_path && gemm_tc_splits_k(kd, pr, M, N, K, cur().sm_count)) {
             const size_t ab = round_up((size_t)M * K * 4, 1024), bb = round_up((size_t)K * N * 4, 1024), cb = (size_t)M * N * 4;
-            if (ab + bb + cb > g.hp_bytes) {
+            if (ab + bb + cb > cur().hp_bytes) {
                 cudaDeviceSynchronize();
-                if (g.hp_buf) cudaFree(g.hp_buf);
-                g.hp_buf = nullptr; g.hp_bytes = 0;
-                cudaError_t e = cudaMalloc(&g.hp_buf, ab + bb + cb);
+                if (cur().hp_buf) cudaFree(cur().hp_buf);
+                cur().hp_buf = nullptr; cur().hp_bytes = 0;
+                cudaError_t e = cudaMalloc(&cur().hp_buf, ab + bb + cb);
                 if (e != cudaSuccess) return fail(AXB_ERR_ALLOC, "gemm_host: staging of %zu bytes: %s", ab + bb + cb, cudaGetErrorString(e));
-                g.hp_bytes = ab + bb + cb;
+                cur().hp_bytes = ab + bb + cb;
             }
-            float *dA = (float *)g.hp_buf, *dB = (float *)((char *)g.hp_buf + ab), *dC = (float *)((char *)g.hp_buf + ab + bb);
-            cudaMemcpyAsync(dA, A, (size_t)M * K * 4, cudaMemcpyHostToDevice, g.stream);
-            cudaMemcpyAsync(dB, B, (size_t)K * N * 4, cudaMemcpyHostToDevice, g.stream);
+            float *dA = (float *)cur().hp_buf, *dB = (float *)((char *)cur().hp_buf + ab), *dC = (float *)((char *)cur().hp_buf + ab + bb);
+            cudaMemcpyAsync(dA, A, (size_t)M * K * 4, cudaMemcpyHostToDevice, cur().stream);
+            cudaMemcpyAsync(dB, B, (size_t)K * N * 4, cudaMemcpyHostToDevice, cur().stream);
             st = axb_gemm(dA, dB, dC, M, N, K);
-            if (st) { cudaStreamSynchronize(g.stream); return st; }
-            cudaMemcpyAsync(C, dC, cb, cudaMemcpyDeviceToHost, g.stream);
-            cudaError_t ce = cudaStreamSynchronize(g.stream);
+            if (st) { cudaStreamSynchronize(cur().stream); return st; }
+            cudaMemcpyAsync(C, dC, cb, cudaMemcpyDeviceToHost, cur().stream);
+            cudaError_t ce = cudaStreamSynchronize(cur().stream);
             return ce == cudaSuccess ? AXB_OK : cuda_fail("gemm_host", ce);
         }
     }
@@ -698,19 +725,19 @@ extern "C" int axb_gemm_host(const float *A, const float *B, float *C, int64_t M
     const size_t b_bytes = round_up((size_t)K * N * 4, 1024), a_bytes = round_up((size_t)rc * K * 4, 1024),
                  c_bytes = round_up((size_t)rc * N * 4, 1024);
     const size_t need = b_bytes + 2 * a_bytes + 2 * c_bytes;
-    if (need > g.hp_bytes) {
+    if (need > cur().hp_bytes) {
         cudaDeviceSynchronize();
-        if (g.hp_buf) cudaFree(g.hp_buf);
-        g.hp_buf = nullptr; g.hp_bytes = 0;
-        cudaError_t e = cudaMalloc(&g.hp_buf, need);
+        if (cur().hp_buf) cudaFree(cur().hp_buf);
+        cur().hp_buf = nullptr; cur().hp_bytes = 0;
+        cudaError_t e = cudaMalloc(&cur().hp_buf, need);
         if (e != cudaSuccess) return fail(AXB_ERR_ALLOC, "gemm_host: staging of %zu bytes: %s", need, cudaGetErrorString(e));
-        g.hp_bytes = need;
+        cur().hp_bytes = need;
     }
-    char *base = (char *)g.hp_buf;
+    char *base = (char *)cur().hp_buf;
     float *dB = (float *)base;
     float *dA[2] = { (float *)(base + b_bytes), (float *)(base + b_bytes + a_bytes) };
     float *dC[2] = { (float *)(base + b_bytes + 2 * a_bytes), (float *)(base + b_bytes + 2 * a_bytes + c_bytes) };
-    cudaEvent_t ev_b = g.hp_ev[0], *ev_a = &g.hp_ev[1], *ev_a_free = &g.hp_ev[3], *ev_c = &g.hp_ev[5], *ev_c_free = &g.hp_ev[7];
+    cudaEvent_t ev_b = cur().hp_ev[0], *ev_a = &cur().hp_ev[1], *ev_a_free = &cur().hp_ev[3], *ev_c = &cur().hp_ev[5], *ev_c_free = &cur().hp_ev[7];
 
     int split_mode, kind;
     TcProducts prod;
@@ -721,20 +748,20 @@ extern "C" int axb_gemm_host(const float *A, const float *B, float *C, int64_t M
     if (tensor_path) {
         st = ensure_ws(sa.total() + sb.total());
         if (st) return st;
-        carve.p = (char *)g.ws;
+        carve.p = (char *)cur().ws;
     }
     // everything the engine's stream did before this call precedes the copies
-    cudaEventRecord(ev_b, g.stream);
-    cudaStreamWaitEvent(g.hp_in, ev_b, 0);
-    cudaStreamWaitEvent(g.hp_out, ev_b, 0);
+    cudaEventRecord(ev_b, cur().stream);
+    cudaStreamWaitEvent(cur().hp_in, ev_b, 0);
+    cudaStreamWaitEvent(cur().hp_out, ev_b, 0);
 
-    cudaMemcpyAsync(dB, B, (size_t)K * N * 4, cudaMemcpyHostToDevice, g.hp_in);
-    cudaEventRecord(ev_b, g.hp_in);
-    cudaStreamWaitEvent(g.stream, ev_b, 0);
+    cudaMemcpyAsync(dB, B, (size_t)K * N * 4, cudaMemcpyHostToDevice, cur().hp_in);
+    cudaEventRecord(ev_b, cur().hp_in);
+    cudaStreamWaitEvent(cur().stream, ev_b, 0);
     // on a failure half way: let the copies already queued finish before the caller may free its buffers
     auto bail = [&](int status) {
-        cudaStreamSynchronize(g.hp_in);
-        cudaStreamSynchronize(g.hp_out);
+        cudaStreamSynchronize(cur().hp_in);
+        cudaStreamSynchronize(cur().hp_out);
         return status;
     };
     int e = 0;
@@ -746,36 +773,36 @@ extern "C" int axb_gemm_host(const float *A, const float *B, float *C, int64_t M
     for (int64_t i = 0; i < chunks; ++i) {
         const int slot = (int)(i & 1);
         const int64_t r0 = i * rc, rows = (M - r0 < rc) ? M - r0 : rc;
-        if (i >= 2) cudaStreamWaitEvent(g.hp_in, ev_a_free[slot], 0);
-        cudaMemcpyAsync(dA[slot], A + r0 * K, (size_t)rows * K * 4, cudaMemcpyHostToDevice, g.hp_in);
-        cudaEventRecord(ev_a[slot], g.hp_in);
-        cudaStreamWaitEvent(g.stream, ev_a[slot], 0);
-        if (i >= 2) cudaStreamWaitEvent(g.stream, ev_c_free[slot], 0);
+        if (i >= 2) cudaStreamWaitEvent(cur().hp_in, ev_a_free[slot], 0);
+        cudaMemcpyAsync(dA[slot], A + r0 * K, (size_t)rows * K * 4, cudaMemcpyHostToDevice, cur().hp_in);
+        cudaEventRecord(ev_a[slot], cur().hp_in);
+        cudaStreamWaitEvent(cur().stream, ev_a[slot], 0);
+        if (i >= 2) cudaStreamWaitEvent(cur().stream, ev_c_free[slot], 0);
         if (tensor_path) {
             carve.off = a_plane_off;
             TcOperand opa;
             SplitOperand sai = plan_split(split_mode, rows, K);
             e = run_split(sai, dA[slot], K, false, carve, opa);
             if (e) return bail(cuda_fail("gemm_host: split A", e));
-            cudaEventRecord(ev_a_free[slot], g.stream);
+            cudaEventRecord(ev_a_free[slot], cur().stream);
             TcEpilogue ep;
             ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = nullptr; ep.colscale = nullptr; ep.act = ACT_NONE;
             ep.out_mode = OUT_F32; ep.C = dC[slot]; ep.acc_out = nullptr; ep.ldc = N; ep.n_extra = 0;
-            e = launch_gemm_tc(kind, opa, opb, prod, rows, N, K, ep, g.err_word, g.sm_count, g.stream);
-            g.launches++;
+            e = launch_gemm_tc(kind, opa, opb, prod, rows, N, K, ep, cur().err_word, cur().sm_count, cur().stream);
+            cur().launches++;
             if (e) return bail(cuda_fail("gemm_host: tcgen05 gemm", e));
         } else {
             st = axb_gemm(dA[slot], dB, dC[slot], rows, N, K);   // M <= 32: the skinny route
             if (st) return bail(st);
-            cudaEventRecord(ev_a_free[slot], g.stream);
+            cudaEventRecord(ev_a_free[slot], cur().stream);
         }
-        cudaEventRecord(ev_c[slot], g.stream);
-        cudaStreamWaitEvent(g.hp_out, ev_c[slot], 0);
-        cudaMemcpyAsync(C + r0 * N, dC[slot], (size_t)rows * N * 4, cudaMemcpyDeviceToHost, g.hp_out);
-        cudaEventRecord(ev_c_free[slot], g.hp_out);
+        cudaEventRecord(ev_c[slot], cur().stream);
+        cudaStreamWaitEvent(cur().hp_out, ev_c[slot], 0);
+        cudaMemcpyAsync(C + r0 * N, dC[slot], (size_t)rows * N * 4, cudaMemcpyDeviceToHost, cur().hp_out);
+        cudaEventRecord(ev_c_free[slot], cur().hp_out);
     }
-    cudaError_t ce = cudaStreamSynchronize(g.hp_out);
-    if (ce == cudaSuccess) ce = cudaStreamSynchronize(g.hp_in);
+    cudaError_t ce = cudaStreamSynchronize(cur().hp_out);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(cur().hp_in);
     if (ce != cudaSuccess) return cuda_fail("gemm_host", ce);
     return AXB_OK;
 }
@@ -789,8 +816,8 @@ extern "C" int axb_bias_add(const float *in, const float *bias, int axis, float 
     if (M < 0 || N < 0) return fail(AXB_ERR_INVALID_SHAPE, "bias_add: negative dimension");
     int st = ensure_ready();
     if (st) return st;
-    int e = launch_bias_add(in, bias, axis, out, M, N, g.sm_count, g.stream);
-    g.launches++;
+    int e = launch_bias_add(in, bias, axis, out, M, N, cur().sm_count, cur().stream);
+    cur().launches++;
     return e ? cuda_fail("bias_add", e) : AXB_OK;
 }
 
@@ -803,9 +830,9 @@ extern "C" int axb_bias_add_nd(const float *in, const float *bias, float *out, i
     if (st) return st;
     // the broadcast axis last: a [outer, axis_len] matrix with one value per column; otherwise
     // [outer*axis_len, inner] with one value per row, repeating every axis_len rows
-    int e = inner == 1 ? launch_bias_add(in, bias, 1, out, outer, axis_len, g.sm_count, g.stream)
-                       : launch_bias_add(in, bias, 0, out, outer * axis_len, inner, g.sm_count, g.stream, axis_len);
-    g.launches++;
+    int e = inner == 1 ? launch_bias_add(in, bias, 1, out, outer, axis_len, cur().sm_count, cur().stream)
+                       : launch_bias_add(in, bias, 0, out, outer * axis_len, inner, cur().sm_count, cur().stream, axis_len);
+    cur().launches++;
     return e ? cuda_fail("bias_add", e) : AXB_OK;
 }
 
@@ -814,8 +841,8 @@ extern "C" int axb_relu(const float *in, float *out, int64_t n)
     if (!in || !out) return fail(AXB_ERR_NULL_ARG, "relu: NULL");
     int st = ensure_ready();
     if (st) return st;
-    int e = launch_unary(0, in, out, n, g.sm_count, g.stream);
-    g.launches++;
+    int e = launch_unary(0, in, out, n, cur().sm_count, cur().stream);
+    cur().launches++;
     return e ? cuda_fail("relu", e) : AXB_OK;
 }
 
@@ -824,8 +851,8 @@ extern "C" int axb_gelu(const float *in, float *out, int64_t n)
     if (!in || !out) return fail(AXB_ERR_NULL_ARG, "gelu: NULL");
     int st = ensure_ready();
     if (st) return st;
-    int e = launch_unary(1, in, out, n, g.sm_count, g.stream);
-    g.launches++;
+    int e = launch_unary(1, in, out, n, cur().sm_count, cur().stream);
+    cur().launches++;
     return e ? cuda_fail("gelu", e) : AXB_OK;
 }
 
@@ -862,18 +889,18 @@ extern "C" int axb_qdense_w8a32(const float *a, const int8_t *q, const float *sc
         if (st) return st;
         mark(0);
         mark(1);
-        int e = launch_qskinny_tc(a, q, scales, bias, act, out, M, N, K, g.ws, g.err_word, g.sm_count, g.stream);
+        int e = launch_qskinny_tc(a, q, scales, bias, act, out, M, N, K, cur().ws, cur().err_word, cur().sm_count, cur().stream);
         mark(2);
-        g.launches += 2;
+        cur().launches += 2;
         return e ? cuda_fail("w8a32 skinny", e) : AXB_OK;
     }
     if (qgemv_w8a32_applicable(M, N, K, q) && (reinterpret_cast<uintptr_t>(a) & 15) == 0) {
         // skinny activations: stream the int8 rows once, fp32 FMA (the reference's own arithmetic)
         mark(0);
         mark(1);
-        int e = launch_qgemv_w8a32(a, q, scales, bias, act, out, M, N, K, g.sm_count, g.stream);
+        int e = launch_qgemv_w8a32(a, q, scales, bias, act, out, M, N, K, cur().sm_count, cur().stream);
         mark(2);
-        g.launches++;
+        cur().launches++;
         return e ? cuda_fail("w8a32 gemv", e) : AXB_OK;
     }
     if (K % 16 == 0 && K <= 65536 && 4 * M <= INT32_MAX &&
@@ -883,14 +910,14 @@ extern "C" int axb_qdense_w8a32(const float *a, const int8_t *q, const float *sc
         const size_t dig_bytes = (size_t)4 * M * K, acc_bytes = (size_t)4 * M * N * sizeof(int32_t);
         st = ensure_ws(round_up((size_t)M * sizeof(float), 1024) + round_up(dig_bytes, 1024) + round_up(acc_bytes, 1024) + kSplitScratch);
         if (st) return st;
-        Carver carve{ (char *)g.ws };
+        Carver carve{ (char *)cur().ws };
         const TcSplitK sk = take_splitk(carve);
         float *inv_s = (float *)carve.take((size_t)M * sizeof(float));
         int8_t *digits = (int8_t *)carve.take(dig_bytes);
         int32_t *acc = (int32_t *)carve.take(acc_bytes);
         mark(0);
-        int e = launch_qx_digits(a, M, K, M, digits, inv_s, g.stream);
-        g.launches++;
+        int e = launch_qx_digits(a, M, K, M, digits, inv_s, cur().stream);
+        cur().launches++;
         if (e) return cuda_fail("w8a32 digits", e);
         TcOperand opa, opb;
         opa.nplanes = opb.nplanes = 1;
@@ -904,44 +931,44 @@ extern "C" int axb_qdense_w8a32(const float *a, const int8_t *q, const float *sc
         ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = nullptr; ep.colscale = nullptr; ep.act = ACT_NONE;
         ep.out_mode = OUT_S32_ONLY; ep.C = nullptr; ep.acc_out = acc; ep.ldc = N;
         mark(1);
-        e = launch_gemm_tc(KIND_I8, opa, opb, prod, 4 * M, N, K, ep, g.err_word, g.sm_count, g.stream, &sk);
-        g.launches++;
+        e = launch_gemm_tc(KIND_I8, opa, opb, prod, 4 * M, N, K, ep, cur().err_word, cur().sm_count, cur().stream, &sk);
+        cur().launches++;
         if (e) return cuda_fail("w8a32 digit gemm", e);
-        e = launch_qx_combine(acc, inv_s, scales, bias, act, out, M, N, g.sm_count, g.stream);
+        e = launch_qx_combine(acc, inv_s, scales, bias, act, out, M, N, cur().sm_count, cur().stream);
         mark(2);
-        g.launches++;
+        cur().launches++;
         return e ? cuda_fail("w8a32 combine", e) : AXB_OK;
     }
     // activations: bf16 hi/mid/lo (exact to 24 bits); weights: int8 widened to bf16 (exact)
-    const int amode = g.fp32_mode == AXB_FP32_BF16 ? SPLIT_BF16X1 : SPLIT_BF16X3;
+    const int amode = cur().fp32_mode == AXB_FP32_BF16 ? SPLIT_BF16X1 : SPLIT_BF16X3;
     const SplitOperand sa = plan_split(amode, M, K);
     const int64_t wpitch = (int64_t)round_up((size_t)K, 16);
     const size_t wbytes = (size_t)N * wpitch * 2;
     st = ensure_ws(sa.total() + round_up(wbytes, 1024));
     if (st) return st;
-    Carver carve{ (char *)g.ws };
+    Carver carve{ (char *)cur().ws };
     TcOperand opa, opb;
     mark(0);
     int e = run_split(sa, a, K, false, carve, opa);
     if (e) return cuda_fail("split activations", e);
     void *wplane = carve.take(wbytes);
-    e = widen_i8_to_bf16(q, N, K, wplane, wpitch, g.sm_count, g.stream);
-    g.launches++;
+    e = widen_i8_to_bf16(q, N, K, wplane, wpitch, cur().sm_count, cur().stream);
+    cur().launches++;
     if (e) return cuda_fail("widen weights", e);
     opb.nplanes = 1; opb.plane[0] = wplane; opb.rows = N; opb.pitch_elems = wpitch;
     TcProducts prod;
     memset(&prod, 0, sizeof prod);
     prod.n = opa.nplanes;
     for (int i = 0; i < prod.n; ++i) { prod.a[i] = (int8_t)(prod.n - 1 - i); prod.b[i] = 0; }  // smallest plane first
-    prod.chunk_k = prod.n > 1 ? g.chunk_bf16 : 0;
+    prod.chunk_k = prod.n > 1 ? cur().chunk_bf16 : 0;
     TcEpilogue ep;
     ep.n_extra = 0;
     ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = bias; ep.colscale = scales; ep.act = act;
     ep.out_mode = OUT_F32; ep.C = out; ep.acc_out = nullptr; ep.ldc = N;
     mark(1);
-    e = launch_gemm_tc(KIND_BF16, opa, opb, prod, M, N, K, ep, g.err_word, g.sm_count, g.stream);
+    e = launch_gemm_tc(KIND_BF16, opa, opb, prod, M, N, K, ep, cur().err_word, cur().sm_count, cur().stream);
     mark(2);
-    g.launches++;
+    cur().launches++;
     return e ? cuda_fail("w8a32 gemm", e) : AXB_OK;
 }
 
@@ -966,7 +993,7 @@ extern "C" int axb_qgemm_w8a8(const int8_t *a_q, float a_scale, const int8_t *b_
     if (!b_direct) need += round_up((size_t)N * pitch, 1024);
     st = ensure_ws(need);
     if (st) return st;
-    Carver carve{ (char *)g.ws };
+    Carver carve{ (char *)cur().ws };
     const TcSplitK sk = take_splitk(carve);
     int e;
     mark(0);
@@ -976,16 +1003,16 @@ extern "C" int axb_qgemm_w8a8(const int8_t *a_q, float a_scale, const int8_t *b_
     if (a_direct) { opa.plane[0] = a_q; opa.pitch_elems = K; }
     else {
         int8_t *p = (int8_t *)carve.take((size_t)M * pitch);
-        e = repitch_i8(a_q, M, K, p, pitch, g.sm_count, g.stream);
-        g.launches++;
+        e = repitch_i8(a_q, M, K, p, pitch, cur().sm_count, cur().stream);
+        cur().launches++;
         if (e) return cuda_fail("repitch A", e);
         opa.plane[0] = p; opa.pitch_elems = pitch;
     }
     if (b_direct) { opb.plane[0] = b_q; opb.pitch_elems = K; }
     else {
         int8_t *p = (int8_t *)carve.take((size_t)N * pitch);
-        e = repitch_i8(b_q, N, K, p, pitch, g.sm_count, g.stream);
-        g.launches++;
+        e = repitch_i8(b_q, N, K, p, pitch, cur().sm_count, cur().stream);
+        cur().launches++;
         if (e) return cuda_fail("repitch B", e);
         opb.plane[0] = p; opb.pitch_elems = pitch;
     }
@@ -999,9 +1026,9 @@ extern "C" int axb_qgemm_w8a8(const int8_t *a_q, float a_scale, const int8_t *b_
     ep.rq_a_scale = a_scale; ep.rq_out_scale = out_scale;
     ep.out_mode = out_q ? OUT_I8_REQUANT : OUT_S32_ONLY; ep.C = out_q; ep.acc_out = acc_out; ep.ldc = N;
     mark(1);
-    e = launch_gemm_tc(KIND_I8, opa, opb, prod, M, N, K, ep, g.err_word, g.sm_count, g.stream, &sk);
+    e = launch_gemm_tc(KIND_I8, opa, opb, prod, M, N, K, ep, cur().err_word, cur().sm_count, cur().stream, &sk);
     mark(2);
-    g.launches++;
+    cur().launches++;
     return e ? cuda_fail("w8a8 gemm", e) : AXB_OK;
 }
 
@@ -1011,8 +1038,8 @@ extern "C" int axb_quantize_rows(const float *w, int64_t N, int64_t K, int8_t *q
     if (N <= 0 || K <= 0) return fail(AXB_ERR_INVALID_SHAPE, "quantize_rows: bad shape");
     int st = ensure_ready();
     if (st) return st;
-    int e = quantize_rows(w, N, K, q, scales, g.stream);
-    g.launches++;
+    int e = quantize_rows(w, N, K, q, scales, cur().stream);
+    cur().launches++;
     return e ? cuda_fail("quantize_rows", e) : AXB_OK;
 }
 
@@ -1033,19 +1060,19 @@ extern "C" int axb_sdpa_fwd(const float *Q, const float *K, const float *V, floa
     if (P_save && !L) {
         st = ensure_ws((size_t)BH * S * sizeof(float));
         if (st) return st;
-        L = (float *)g.ws;
+        L = (float *)cur().ws;
     }
     mark(0);
     mark(1);
     int e;
-    if (sdpa_tc_applicable(Q, K, V, BH, S, dk, scale)) e = launch_sdpa_tc(Q, K, V, out, L, BH, S, dk, scale, causal, g.err_word, g.stream);
-    else e = launch_sdpa_fwd(Q, K, V, out, L, BH, S, dk, scale, causal, g.stream);
+    if (sdpa_tc_applicable(Q, K, V, BH, S, dk, scale)) e = launch_sdpa_tc(Q, K, V, out, L, BH, S, dk, scale, causal, cur().err_word, cur().stream);
+    else e = launch_sdpa_fwd(Q, K, V, out, L, BH, S, dk, scale, causal, cur().stream);
     mark(2);
-    g.launches++;
+    cur().launches++;
     if (e) return cuda_fail("sdpa_fwd", e);
     if (P_save) {
-        e = launch_sdpa_probs(Q, K, L, P_save, BH, S, dk, scale, causal, g.stream);
-        g.launches++;
+        e = launch_sdpa_probs(Q, K, L, P_save, BH, S, dk, scale, causal, cur().stream);
+        cur().launches++;
         if (e) return cuda_fail("sdpa_fwd: saved probabilities", e);
     }
     return AXB_OK;
@@ -1067,9 +1094,9 @@ extern "C" int axb_sdpa_bwd(const float *Q, const float *K, const float *V, cons
     if (st) return st;
     mark(0);
     mark(1);
-    int e = launch_sdpa_bwd(Q, K, V, O, dO, L, dQ, dK, dV, BH, S, dk, scale, causal, (float *)g.ws, g.sm_count, g.stream);
+    int e = launch_sdpa_bwd(Q, K, V, O, dO, L, dQ, dK, dV, BH, S, dk, scale, causal, (float *)cur().ws, cur().sm_count, cur().stream);
     mark(2);
-    g.launches += 3;
+    cur().launches += 3;
     return e ? cuda_fail("sdpa_bwd", e) : AXB_OK;
 }
 
@@ -1095,7 +1122,7 @@ extern "C" int axb_conv_gemm(const float *weight, const float *input, int64_t C_
     const SplitOperand sa = plan_split(split_mode, C_out, K), sb = plan_split(split_mode, P, K);
     st = ensure_ws(sa.total() + sb.total() + kSplitScratch);
     if (st) return st;
-    Carver carve{ (char *)g.ws };
+    Carver carve{ (char *)cur().ws };
     const TcSplitK sk = take_splitk(carve);
     TcOperand opa, opb;
     mark(0);
@@ -1109,16 +1136,16 @@ extern "C" int axb_conv_gemm(const float *weight, const float *input, int64_t C_
     }
     opb.rows = P;
     opb.pitch_elems = sb.pitch;
-    e = split_im2col(split_mode, input, C_in, H, W, kh, kw, sh, sw, ph, pw, out_h, out_w, planes, sb.pitch, g.sm_count, g.stream);
-    g.launches++;
+    e = split_im2col(split_mode, input, C_in, H, W, kh, kw, sh, sw, ph, pw, out_h, out_w, planes, sb.pitch, cur().sm_count, cur().stream);
+    cur().launches++;
     if (e) return cuda_fail("conv_gemm: im2col split", e);
     TcEpilogue ep;
     ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = nullptr; ep.colscale = nullptr; ep.act = ACT_NONE;
     ep.out_mode = OUT_F32; ep.C = out; ep.acc_out = nullptr; ep.ldc = P; ep.n_extra = 0;
     mark(1);
-    e = launch_gemm_tc(kind, opa, opb, prod, C_out, P, K, ep, g.err_word, g.sm_count, g.stream, &sk);
+    e = launch_gemm_tc(kind, opa, opb, prod, C_out, P, K, ep, cur().err_word, cur().sm_count, cur().stream, &sk);
     mark(2);
-    g.launches++;
+    cur().launches++;
     return e ? cuda_fail("conv_gemm", e) : AXB_OK;
 }
 
@@ -1135,9 +1162,9 @@ extern "C" int axb_kv_cache_append(float *K_cache, float *V_cache, const float *
     if (BH == 0) return AXB_OK;
     // row cur_len of every head: [BH] rows of dk floats, max_seq*dk apart in the cache
     const size_t w = (size_t)dk * sizeof(float), pitch = (size_t)max_seq * w;
-    cudaError_t e = cudaMemcpy2DAsync(K_cache + cur_len * dk, pitch, new_K, w, w, (size_t)BH, cudaMemcpyDeviceToDevice, g.stream);
+    cudaError_t e = cudaMemcpy2DAsync(K_cache + cur_len * dk, pitch, new_K, w, w, (size_t)BH, cudaMemcpyDeviceToDevice, cur().stream);
     if (e == cudaSuccess)
-        e = cudaMemcpy2DAsync(V_cache + cur_len * dk, pitch, new_V, w, w, (size_t)BH, cudaMemcpyDeviceToDevice, g.stream);
+        e = cudaMemcpy2DAsync(V_cache + cur_len * dk, pitch, new_V, w, w, (size_t)BH, cudaMemcpyDeviceToDevice, cur().stream);
     return e == cudaSuccess ? AXB_OK : cuda_fail("kv_cache_append", e);
 }
 
@@ -1154,9 +1181,9 @@ extern "C" int axb_kv_cache_attend(const float *K_cache, const float *V_cache, c
     if (BH == 0) return AXB_OK;
     mark(0);
     mark(1);
-    int e = launch_kv_cache_attend(K_cache, V_cache, Q_new, out, BH, cur_len, max_seq, dk, scale, g.sm_count, g.stream);
+    int e = launch_kv_cache_attend(K_cache, V_cache, Q_new, out, BH, cur_len, max_seq, dk, scale, cur().sm_count, cur().stream);
     mark(2);
-    g.launches++;
+    cur().launches++;
     return e ? cuda_fail("kv_cache_attend", e) : AXB_OK;
 }
 
@@ -1180,16 +1207,16 @@ extern "C" int axb_qkv_head_gemm(const float *X, const float *Wqkv, const float 
     }
     // other head dims and skinny inputs: the product (bias fused) into a scratch matrix, then the layout pass
     const size_t need = (size_t)rows * 3 * D * sizeof(float);
-    if (need > g.aux_bytes) {
-        if (g.aux) { cudaStreamSynchronize(g.stream); cudaFree(g.aux); g.aux = nullptr; g.aux_bytes = 0; }
-        cudaError_t e = cudaMalloc(&g.aux, need);
+    if (need > cur().aux_bytes) {
+        if (cur().aux) { cudaStreamSynchronize(cur().stream); cudaFree(cur().aux); cur().aux = nullptr; cur().aux_bytes = 0; }
+        cudaError_t e = cudaMalloc(&cur().aux, need);
         if (e != cudaSuccess) return fail(AXB_ERR_ALLOC, "qkv_head_gemm: scratch of %zu bytes: %s", need, cudaGetErrorString(e));
-        g.aux_bytes = need;
+        cur().aux_bytes = need;
     }
-    st = axb_gemm_bias_act(X, Wqkv, bqkv, (float *)g.aux, rows, 3 * D, D, 0, 0, 1.0f, 0.0f, AXB_ACT_NONE);
+    st = axb_gemm_bias_act(X, Wqkv, bqkv, (float *)cur().aux, rows, 3 * D, D, 0, 0, 1.0f, 0.0f, AXB_ACT_NONE);
     if (st) return st;
-    int e = launch_head_layout(true, (float *)g.aux, outs, nullptr, 3, B, S, H, dk, g.sm_count, g.stream);
-    g.launches++;
+    int e = launch_head_layout(true, (float *)cur().aux, outs, nullptr, 3, B, S, H, dk, cur().sm_count, cur().stream);
+    cur().launches++;
     return e ? cuda_fail("qkv_head_gemm: head split", e) : AXB_OK;
 }
 
@@ -1205,8 +1232,8 @@ static int head_layout_call(const char *what, bool to_head, const float *flat, f
     if (S > INT32_MAX || H > INT32_MAX || dk > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "%s: dimension exceeds 2^31-1", what);
     int st = ensure_ready();
     if (st) return st;
-    int e = launch_head_layout(to_head, const_cast<float *>(flat), head, bias, nslot, B, S, H, dk, g.sm_count, g.stream);
-    g.launches++;
+    int e = launch_head_layout(to_head, const_cast<float *>(flat), head, bias, nslot, B, S, H, dk, cur().sm_count, cur().stream);
+    cur().launches++;
     return e ? cuda_fail(what, e) : AXB_OK;
 }
 
@@ -1247,7 +1274,7 @@ static int concat3(const char *what, float *dst, const float *a, const float *b,
     const size_t w = (size_t)cols * sizeof(float);
     const float *src[3] = { a, b, c };
     for (int i = 0; i < 3; ++i) {
-        cudaError_t e = cudaMemcpy2DAsync(dst + i * cols, 3 * w, src[i], w, w, (size_t)rows, cudaMemcpyDeviceToDevice, g.stream);
+        cudaError_t e = cudaMemcpy2DAsync(dst + i * cols, 3 * w, src[i], w, w, (size_t)rows, cudaMemcpyDeviceToDevice, cur().stream);
         if (e != cudaSuccess) return cuda_fail(what, e);
     }
     return AXB_OK;

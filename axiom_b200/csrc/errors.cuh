@@ -8,6 +8,10 @@ namespace axb {
 // printf-style; returns `status` so call sites can `return set_error(...)`.
 int set_error(int status, const char *fmt, ...);
 
+// the stream and the device of the engine the calling thread drives (-1: none selected yet)
+cudaStream_t engine_stream();
+int engine_device();
+
 // Function attributes (the dynamic shared-memory opt-in) belong to a device's context: a launcher keeps one of
 // these per kernel instantiation and sets the attribute the first time it runs on each device.
 struct PerDeviceOnce {

@@ -30,6 +30,8 @@ EXPORTS = [
     "axb_sdpa_fwd", "axb_kv_cache_append", "axb_kv_cache_attend", "axb_qkv_head_gemm", "axb_sdpa_bwd", "axb_conv_gemm", "axb_qdense_w8a32",
     "axb_qgemm_w8a32_qw", "axb_bias_add_nd", "axb_head_interleave_qkv_split", "axb_head_interleave", "axb_head_deinterleave",
     "axb_head_deinterleave_qkv_merge", "axb_qkv_cache_build", "axb_bias_cache_build", "axb_pointer_on_device",
+    "axb_mgpu_create", "axb_mgpu_destroy", "axb_mgpu_size", "axb_mgpu_device", "axb_mgpu_alloc", "axb_mgpu_free", "axb_mgpu_h2d",
+    "axb_mgpu_d2h", "axb_mgpu_synchronize", "axb_mgpu_gemm_rows", "axb_mgpu_qgemm_w8a8_rows", "axb_mgpu_gemm_cols_allgather",
 ]
 
 
@@ -324,6 +326,77 @@ class Engine:
         self._check(self.lib.axb_kv_cache_attend(_ptr(K_cache), _ptr(V_cache), _ptr(Q_new), _ptr(out), _i64(BH),
                                                  _i64(cur_len), _i64(max_seq), _i64(dk), _f(scale)))
         return out
+
+
+class MultiGpu:
+    """The C multi-GPU entry points (axb_mgpu_*): one host thread, n devices.  Buffers are raw device pointers owned by
+    this object (allocated through the library, no torch involved)."""
+
+    def __init__(self, engine: Engine, n_devices: int, devices=None):
+        self.eng, self.lib = engine, engine.lib
+        L = self.lib
+        L.axb_mgpu_alloc.restype = C.c_void_p
+        L.axb_mgpu_alloc.argtypes = [C.c_void_p, C.c_int, C.c_size_t]
+        L.axb_mgpu_free.argtypes = [C.c_void_p, C.c_int, C.c_void_p]
+        L.axb_mgpu_h2d.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_size_t]
+        L.axb_mgpu_d2h.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_size_t]
+        L.axb_mgpu_destroy.argtypes = [C.c_void_p]
+        L.axb_mgpu_synchronize.argtypes = [C.c_void_p]
+        h = C.c_void_p(0)
+        devs = (C.c_int * n_devices)(*devices) if devices is not None else None
+        engine._check(L.axb_mgpu_create(int(n_devices), devs, C.byref(h)))
+        self.h, self.n = h, n_devices
+        self._owned = []
+
+    def alloc(self, rank, nbytes):
+        p = self.lib.axb_mgpu_alloc(self.h, rank, nbytes)
+        if not p:
+            raise EngineError(2, self.eng.last_error())
+        self._owned.append((rank, p))
+        return int(p)
+
+    def upload(self, rank, array):
+        """numpy array -> a new device buffer on `rank`; returns the device pointer."""
+        import numpy as np
+        a = np.ascontiguousarray(array)
+        p = self.alloc(rank, max(a.nbytes, 4))
+        self.eng._check(self.lib.axb_mgpu_h2d(self.h, rank, C.c_void_p(p), a.ctypes.data_as(C.c_void_p), a.nbytes))
+        return p
+
+    def download(self, rank, ptr, shape, dtype):
+        import numpy as np
+        out = np.empty(shape, dtype)
+        self.eng._check(self.lib.axb_mgpu_d2h(self.h, rank, out.ctypes.data_as(C.c_void_p), C.c_void_p(ptr), out.nbytes))
+        return out
+
+    def _ptrs(self, ptrs):
+        return (C.c_void_p * self.n)(*[None if p is None else C.c_void_p(p) for p in ptrs]) if ptrs is not None else None
+
+    def gemm_rows(self, A, B, bias, Cout, rows, N, K, act="none"):
+        r = (C.c_int64 * self.n)(*rows)
+        self.eng._check(self.lib.axb_mgpu_gemm_rows(self.h, self._ptrs(A), self._ptrs(B), self._ptrs(bias), self._ptrs(Cout), r,
+                                                    _i64(N), _i64(K), ACT[act]))
+
+    def qgemm_w8a8_rows(self, a_q, a_scale, b_q, b_scales, out_scale, out_q, rows, N, K):
+        r = (C.c_int64 * self.n)(*rows)
+        self.eng._check(self.lib.axb_mgpu_qgemm_w8a8_rows(self.h, self._ptrs(a_q), _f(a_scale), self._ptrs(b_q), self._ptrs(b_scales),
+                                                          _f(out_scale), self._ptrs(out_q), r, _i64(N), _i64(K)))
+
+    def gemm_cols_allgather(self, X, x_chunks, W, bias, slab, gathered, M, n, K, act="none"):
+        self.eng._check(self.lib.axb_mgpu_gemm_cols_allgather(self.h, self._ptrs(X), int(x_chunks), self._ptrs(W), self._ptrs(bias),
+                                                              self._ptrs(slab), self._ptrs(gathered), _i64(M), _i64(n), _i64(K),
+                                                              ACT[act]))
+
+    def synchronize(self):
+        self.eng._check(self.lib.axb_mgpu_synchronize(self.h))
+
+    def close(self):
+        if self.h:
+            for rank, p in self._owned:
+                self.lib.axb_mgpu_free(self.h, rank, C.c_void_p(p))
+            self._owned = []
+            self.lib.axb_mgpu_destroy(self.h)
+            self.h = None
 
 
 _engine = None

@@ -12,9 +12,9 @@
    reference): 0 = AX_OK, 1 = NULL_ARG, 2 = ALLOC, 3 = SHAPE_MISMATCH,
    7 = INVALID_DTYPE, 9 = BACKEND, 10 = NOT_IMPLEMENTED ...  The engine never
    aborts and never falls back to host arithmetic; axb_last_error() returns
-   the message of the most recent failure.  The engine is one per process
-   (one process per GPU) and is not thread-safe: one host thread drives it,
-   as with the reference backend (src/compute/backends/cuda/internal.h:70-74).
+   the message of the most recent failure.  There is one engine per device;
+   an engine is not thread-safe: one host thread drives it at a time, as with
+   the reference backend (src/compute/backends/cuda/internal.h:70-74).
 
    Each declaration cites the reference interface it replaces as
    file:line within the axiom source tree. */
@@ -56,8 +56,9 @@ extern "C" {
    storage + memcpy hooks (src/compute/backends/cuda/memory.cu:80-140), i.e. the
    device-owner slots of ax_backend_ops_t
    (include/axiom/internal/backend_ops.h:262-296). */
-AXB_API int axb_init(int device);      /* idempotent; also reads AX_B200_FP32_MODE = 3xtf32|bf16x3|bf16 */
-AXB_API void axb_shutdown(void);
+AXB_API int axb_init(int device);      /* idempotent per device; selects the device (and its engine) for the calling thread;
+                                          -1 = the thread's current choice; reads AX_B200_FP32_MODE = 3xtf32|bf16x3|bf16 */
+AXB_API void axb_shutdown(void);       /* every device's engine */
 AXB_API int axb_device_count(void);
 AXB_API void axb_synchronize(void);    /* blocks; afterwards axb_device_error() is current */
 AXB_API void *axb_storage_alloc(size_t bytes);   /* zero-filled, like the reference's pool allocator */
@@ -147,6 +148,42 @@ AXB_API int axb_gemm_gathered_scatter(const float *A_gathered, int chunks, int64
 AXB_API int axb_ipc_get_handle(const void *dev_ptr, void *handle_64_bytes);
 AXB_API int axb_ipc_open_handle(const void *handle_64_bytes, void **dev_ptr_out);
 AXB_API int axb_ipc_close_handle(void *dev_ptr);
+
+/* ---- one host thread, several GPUs (no counterpart in the reference) -----------------------------------
+   Every device has its own engine; axb_init(device) initialises it on first use and makes it the one the
+   calling thread's subsequent axb_* calls drive (it also makes that device the thread's current CUDA device).
+   The entry points below walk the devices of a handle from the calling thread — every launch is asynchronous,
+   so the devices work side by side — and put the caller's device back before they return.  Arrays are indexed
+   by rank (0 .. n-1); rank r's pointers are device pointers on device axb_mgpu_device(h, r).
+   NCCL (libnccl.so.2) is loaded when a handle with more than one device is created. */
+typedef struct axb_mgpu axb_mgpu_t;
+AXB_API int axb_mgpu_create(int n_devices, const int *devices /* NULL = 0 .. n-1 */, axb_mgpu_t **out);
+AXB_API void axb_mgpu_destroy(axb_mgpu_t *h);
+AXB_API int axb_mgpu_size(const axb_mgpu_t *h);
+AXB_API int axb_mgpu_device(const axb_mgpu_t *h, int rank);
+AXB_API void *axb_mgpu_alloc(axb_mgpu_t *h, int rank, size_t bytes);   /* zero-filled, on rank's device */
+AXB_API void axb_mgpu_free(axb_mgpu_t *h, int rank, void *ptr);
+AXB_API int axb_mgpu_h2d(axb_mgpu_t *h, int rank, void *dst, const void *src_host, size_t bytes);
+AXB_API int axb_mgpu_d2h(axb_mgpu_t *h, int rank, void *dst_host, const void *src, size_t bytes);
+AXB_API int axb_mgpu_synchronize(axb_mgpu_t *h);   /* all devices; AX_ERR_BACKEND if a kernel gave up on a bounded wait */
+/* Rows (M) partitioned, weights replicated, no communication:
+     rank r:  C[r][rows[r], N] = act(A[r][rows[r], K] . B[r][K, N] + bias[r][N])      (bias may be NULL)
+   Each rank's result is bit-identical to the same rows of one axb_gemm_bias_act over the whole matrix whenever
+   both take the same K-slicing (always for problems that fill a GPU). */
+AXB_API int axb_mgpu_gemm_rows(axb_mgpu_t *h, const float *const *A, const float *const *B, const float *const *bias,
+                               float *const *C, const int64_t *rows, int64_t N, int64_t K, int act);
+/* The same partition for axb_qgemm_w8a8 (requantised int8 output). */
+AXB_API int axb_mgpu_qgemm_w8a8_rows(axb_mgpu_t *h, const int8_t *const *a_q, float a_scale, const int8_t *const *b_q,
+                                     const float *const *b_scales, float out_scale, int8_t *const *out_q,
+                                     const int64_t *rows, int64_t N, int64_t K);
+/* Output columns (N) partitioned, one NCCL all-gather: rank r holds W[r][K, n] and bias[r][n] (its n = N/g columns),
+     slab[r][M, n] = act(X[r] . W[r] + bias[r]);   gathered[r][q][M][n] = slab[q] for every rank q
+   so every rank ends up with the full activation as [g][M][n].  X[r] is the full input on rank r: a plain [M, K]
+   matrix (x_chunks = 1) or the [x_chunks][M][K / x_chunks] buffer a previous call gathered, read in place.
+   Chaining calls gives the column-sharded MLP with one all-gather per layer. */
+AXB_API int axb_mgpu_gemm_cols_allgather(axb_mgpu_t *h, const float *const *X, int x_chunks, const float *const *W,
+                                         const float *const *bias, float *const *slab, float *const *gathered,
+                                         int64_t M, int64_t n, int64_t K, int act);
 
 /* Skinny-M GEMM that never allocates (no counterpart in the reference).
      Y[M,N] = act(alpha * X[M,K] . W[K,N] + beta * Y + bias[n]),  1 <= M <= 32
