@@ -1094,9 +1094,11 @@ extern "C" int axb_sdpa_bwd(const float *Q, const float *K, const float *V, cons
     if (st) return st;
     mark(0);
     mark(1);
-    int e = launch_sdpa_bwd(Q, K, V, O, dO, L, dQ, dK, dV, BH, S, dk, scale, causal, (float *)cur().ws, cur().sm_count, cur().stream);
+    int n_launched = 0;
+    int e = launch_sdpa_bwd(Q, K, V, O, dO, L, dQ, dK, dV, BH, S, dk, scale, causal, (float *)cur().ws, cur().sm_count,
+                            cur().err_word, cur().stream, &n_launched);
     mark(2);
-    cur().launches += 3;
+    cur().launches += n_launched;
     return e ? cuda_fail("sdpa_bwd", e) : AXB_OK;
 }
 

@@ -14,9 +14,17 @@ int launch_sdpa_probs(const float *Q, const float *K, const float *L, float *P, 
 
 // Backward (sdpa_bwd.cu): dQ, dK, dV are overwritten; workspace holds BH*S floats (sdpa_bwd_workspace_bytes).
 size_t sdpa_bwd_workspace_bytes(int64_t BH, int64_t S);
+// Head dims <= 64 (multiples of 4, 16-byte aligned tensors, S >= 128, scale > 0) run on the tensor cores
+// (sdpa_bwd_tc.cu), the rest on the fp32 FMA kernels.  *launches receives the number of kernels enqueued.
 int launch_sdpa_bwd(const float *Q, const float *K, const float *V, const float *O, const float *dO, const float *L,
                     float *dQ, float *dK, float *dV, int64_t BH, int64_t S, int64_t dk, float scale, int causal,
-                    float *workspace, int sm_count, cudaStream_t st);
+                    float *workspace, int sm_count, int *err_word, cudaStream_t st, int *launches);
+bool sdpa_bwd_tc_applicable(const float *Q, const float *K, const float *V, const float *dO, int64_t BH, int64_t S, int64_t dk,
+                            float scale);
+// D = rowsum(dO o O) [BH][S] must have been computed; one kernel in three roles (dQ, dK, dV)
+int launch_sdpa_bwd_tc(const float *Q, const float *K, const float *V, const float *dO, const float *L, const float *D,
+                       float *dQ, float *dK, float *dV, int64_t BH, int64_t S, int64_t dk, float scale, int causal,
+                       int *err_word, cudaStream_t st);
 
 // Tensor-core route (sdpa_tc.cu): head dim <= 64 and a multiple of 4, 16-byte aligned tensors, scale > 0.
 // Reads the caller's tensors through TMA and splits them inside the kernel: no pre-pass, no scratch.  A bounded

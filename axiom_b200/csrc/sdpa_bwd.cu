@@ -315,8 +315,9 @@ static int launch_bwd(const float *Q, const float *K, const float *V, const floa
 
 int launch_sdpa_bwd(const float *Q, const float *K, const float *V, const float *O, const float *dO, const float *L,
                     float *dQ, float *dK, float *dV, int64_t BH, int64_t S, int64_t dk, float scale, int causal,
-                    float *workspace, int sm_count, cudaStream_t st)
+                    float *workspace, int sm_count, int *err_word, cudaStream_t st, int *launches)
 {
+    if (launches) *launches = 0;
     if (BH <= 0 || S <= 0) return 0;
     const int64_t rows = BH * S;
     int64_t blocks = (rows + 7) / 8;
@@ -324,6 +325,11 @@ int launch_sdpa_bwd(const float *Q, const float *K, const float *V, const float 
     sdpa_bwd_rowdot_kernel<<<(unsigned)blocks, 256, 0, st>>>(O, dO, workspace, rows, (int)dk);
     int e = (int)cudaGetLastError();
     if (e) return e;
+    if (sdpa_bwd_tc_applicable(Q, K, V, dO, BH, S, dk, scale)) {
+        if (launches) *launches = 4;
+        return launch_sdpa_bwd_tc(Q, K, V, dO, L, workspace, dQ, dK, dV, BH, S, dk, scale, causal, err_word, st);
+    }
+    if (launches) *launches = 3;
     const uintptr_t align = reinterpret_cast<uintptr_t>(Q) | reinterpret_cast<uintptr_t>(K) | reinterpret_cast<uintptr_t>(V) |
                             reinterpret_cast<uintptr_t>(dO) | reinterpret_cast<uintptr_t>(dQ) | reinterpret_cast<uintptr_t>(dK) |
                             reinterpret_cast<uintptr_t>(dV);
