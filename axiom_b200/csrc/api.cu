@@ -216,13 +216,13 @@ void fp32_mode_plan(int &split_mode, int &kind, TcProducts &prod)
 int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int64_t M, int64_t N, int64_t K,
                 int ta, int tb, float alpha, float beta, int act, float *const *extra = nullptr, int n_extra = 0,
                 int64_t a_chunk_k = 0, int64_t a_chunk_stride = 0, const int64_t *head_shape = nullptr,
-                float *const *head_out = nullptr)
+                float *const *head_out = nullptr, const TcOperand *prepared_b = nullptr)
 {
     int split_mode, kind;
     TcProducts prod;
     fp32_mode_plan(split_mode, kind, prod);
     const SplitOperand sa = plan_split(split_mode, M, K), sb = plan_split(split_mode, N, K);
-    int st = ensure_ws(sa.total() + sb.total() + kSplitScratch);
+    int st = ensure_ws(sa.total() + (prepared_b ? 0 : sb.total()) + kSplitScratch);
     if (st) return st;
     Carver carve{ (char *)cur().ws };
     const TcSplitK sk = take_splitk(carve);
@@ -230,15 +230,24 @@ int gemm_tc_f32(const float *A, const float *B, const float *bias, float *C, int
     mark(0);
     // A is [M,K] (k contiguous) unless trans_a, where it is stored [K,M];
     // B is [K,N] (k outermost) unless trans_b, where it is stored [N,K].
-    // both operands in one pre-pass launch
     void *pa[3] = { nullptr, nullptr, nullptr }, *pb[3] = { nullptr, nullptr, nullptr };
-    opa.nplanes = opb.nplanes = split_num_planes(split_mode);
+    opa.nplanes = split_num_planes(split_mode);
     for (int i = 0; i < opa.nplanes; ++i) opa.plane[i] = pa[i] = carve.take(sa.plane_bytes);
-    for (int i = 0; i < opb.nplanes; ++i) opb.plane[i] = pb[i] = carve.take(sb.plane_bytes);
     opa.rows = sa.rows; opa.pitch_elems = sa.pitch;
-    opb.rows = sb.rows; opb.pitch_elems = sb.pitch;
-    int e = split_planes_pair(split_mode, A, M, ta ? M : K, ta != 0, pa, sa.pitch, a_chunk_k, a_chunk_stride, B, N,
+    int e;
+    if (prepared_b) {
+        // the weight's planes exist already: only the left operand is split
+        opb = *prepared_b;
+        e = split_planes(split_mode, A, M, K, ta ? M : K, ta != 0, pa, sa.pitch, cur().sm_count, cur().stream, a_chunk_k,
+                         a_chunk_stride);
+    } else {
+        // both operands in one pre-pass launch
+        opb.nplanes = opa.nplanes;
+        for (int i = 0; i < opb.nplanes; ++i) opb.plane[i] = pb[i] = carve.take(sb.plane_bytes);
+        opb.rows = sb.rows; opb.pitch_elems = sb.pitch;
+        e = split_planes_pair(split_mode, A, M, ta ? M : K, ta != 0, pa, sa.pitch, a_chunk_k, a_chunk_stride, B, N,
                               tb ? K : N, tb == 0, pb, sb.pitch, K, cur().sm_count, cur().stream);
+    }
     cur().launches++;
     if (e) return cuda_fail("split operands", e);
     TcEpilogue ep;
@@ -661,6 +670,82 @@ extern "C" int axb_gemm_relu(const float *A, const float *B, const float *bias, 
                              int64_t N, int64_t K)
 {
     return axb_gemm_bias_act(A, B, bias, C, M, N, K, 0, 0, 1.0f, 0.0f, AXB_ACT_RELU);
+}
+
+// ---------------------------------------------------------------- prepared weights
+//
+// A dense layer multiplies by the same weight matrix call after call; its tensor-core operand planes (hi/lo tf32 or
+// bf16, K-major) are the same every time.  A prepared weight holds them, so a product against it splits the left
+// operand only.  The reference's CPU backend does the same thing behind the scenes: cpu_opt keeps packed B panels
+// in a cache keyed on the storage pointer and its generation counter (src/compute/backends/cpu_opt.c, pack_b cache).
+struct axb_weight {
+    const float *src;     // the caller's matrix (borrowed: the skinny route streams it as it is)
+    int64_t K, N;
+    int trans;            // src is [N,K] instead of [K,N]
+    int mode;             // fp32 mode the planes were made for
+    int device;
+    void *planes;         // owned
+    TcOperand op;
+};
+
+extern "C" int axb_weight_prepare(const float *B, int64_t K, int64_t N, int trans_b, axb_weight **out)
+{
+    if (!out) return fail(AXB_ERR_NULL_ARG, "weight_prepare: NULL");
+    *out = nullptr;
+    if (!B) return fail(AXB_ERR_NULL_ARG, "weight_prepare: NULL");
+    if (K <= 0 || N <= 0 || K > INT32_MAX || N > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "weight_prepare: bad shape");
+    int st = ensure_ready();
+    if (st) return st;
+    int split_mode, kind;
+    TcProducts prod;
+    fp32_mode_plan(split_mode, kind, prod);
+    const SplitOperand sb = plan_split(split_mode, N, K);
+    axb_weight *w = new axb_weight();
+    w->src = B; w->K = K; w->N = N; w->trans = trans_b != 0; w->mode = cur().fp32_mode; w->device = cur().device;
+    cudaError_t ce = cudaMalloc(&w->planes, sb.total());
+    if (ce != cudaSuccess) {
+        delete w;
+        return fail(AXB_ERR_ALLOC, "weight_prepare: %zu bytes of operand planes: %s", sb.total(), cudaGetErrorString(ce));
+    }
+    Carver carve{ (char *)w->planes };
+    int e = run_split(sb, B, trans_b ? K : N, trans_b == 0, carve, w->op);
+    if (e) {
+        cudaFree(w->planes);
+        delete w;
+        return cuda_fail("weight_prepare: split", e);
+    }
+    *out = w;
+    return AXB_OK;
+}
+
+extern "C" void axb_weight_release(axb_weight *w)
+{
+    if (!w) return;
+    if (w->planes) {
+        cudaStreamSynchronize(cur().stream);
+        cudaFree(w->planes);
+    }
+    delete w;
+}
+
+extern "C" int axb_gemm_prepared(const float *A, const axb_weight *W, const float *bias, float *C, int64_t M, int trans_a,
+                                 float alpha, float beta, int act)
+{
+    if (!W) return fail(AXB_ERR_NULL_ARG, "gemm_prepared: NULL weight");
+    if (M < 0) return fail(AXB_ERR_INVALID_SHAPE, "gemm_prepared: negative dimension");
+    if (M == 0) return AXB_OK;
+    if (!A || !C) return fail(AXB_ERR_NULL_ARG, "gemm_prepared: NULL operand");
+    if (act < AXB_ACT_NONE || act > AXB_ACT_GELU) return fail(AXB_ERR_INVALID_SHAPE, "gemm_prepared: unknown activation %d", act);
+    if (M > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "gemm_prepared: dimension exceeds 2^31-1");
+    int st = ensure_ready();
+    if (st) return st;
+    if (W->device != cur().device) return fail(AXB_ERR_BACKEND, "gemm_prepared: the weight was prepared on device %d", W->device);
+    if (W->mode != cur().fp32_mode)
+        return fail(AXB_ERR_BACKEND, "gemm_prepared: the weight was prepared in fp32 mode %d, the engine is in mode %d", W->mode, cur().fp32_mode);
+    // the same routes as axb_gemm_bias_act, so the results are the same bits
+    if (M <= 32 && !trans_a && !W->trans) return gemm_skinny(A, W->src, bias, C, M, W->N, W->K, alpha, beta, act);
+    return gemm_tc_f32(A, W->src, bias, C, M, W->N, W->K, trans_a, W->trans, alpha, beta, act, nullptr, 0, 0, 0, nullptr, nullptr,
+                       &W->op);
 }
 
 // C_host = A_host . B_host with the transfers pipelined against the tensor-core work: B goes up first and is

@@ -30,6 +30,7 @@ EXPORTS = [
     "axb_sdpa_fwd", "axb_kv_cache_append", "axb_kv_cache_attend", "axb_qkv_head_gemm", "axb_sdpa_bwd", "axb_conv_gemm", "axb_qdense_w8a32",
     "axb_qgemm_w8a32_qw", "axb_bias_add_nd", "axb_head_interleave_qkv_split", "axb_head_interleave", "axb_head_deinterleave",
     "axb_head_deinterleave_qkv_merge", "axb_qkv_cache_build", "axb_bias_cache_build", "axb_pointer_on_device",
+    "axb_weight_prepare", "axb_weight_release", "axb_gemm_prepared",
     "axb_mgpu_create", "axb_mgpu_destroy", "axb_mgpu_size", "axb_mgpu_device", "axb_mgpu_alloc", "axb_mgpu_free", "axb_mgpu_h2d",
     "axb_mgpu_d2h", "axb_mgpu_synchronize", "axb_mgpu_gemm_rows", "axb_mgpu_qgemm_w8a8_rows", "axb_mgpu_gemm_cols_allgather",
 ]
@@ -74,6 +75,8 @@ class Engine:
         L.axb_storage_free.argtypes = [C.c_void_p]
         L.axb_launch_count.restype = C.c_int64
         L.axb_set_stream.argtypes = [C.c_void_p]
+        L.axb_weight_release.argtypes = [C.c_void_p]
+        L.axb_gemm_prepared.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int, C.c_float, C.c_float, C.c_int]
         for name in ("axb_memcpy_h2d", "axb_memcpy_d2h", "axb_memcpy_d2d"):
             getattr(L, name).argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
         if device is not None:
@@ -163,6 +166,21 @@ class Engine:
     def gemm_bias_act(self, A, B, bias, out, M, N, K, trans_a=False, trans_b=False, alpha=1.0, beta=0.0, act="none"):
         self._check(self.lib.axb_gemm_bias_act(_ptr(A), _ptr(B), _ptr(bias), _ptr(out), _i64(M), _i64(N), _i64(K),
                                                int(trans_a), int(trans_b), _f(alpha), _f(beta), ACT[act]))
+        return out
+
+    def weight_prepare(self, B, trans_b=False):
+        """Operand planes of a weight matrix, made once (axb_weight_prepare); B must outlive the handle."""
+        K, N = (B.shape[1], B.shape[0]) if trans_b else (B.shape[0], B.shape[1])
+        h = C.c_void_p(0)
+        self._check(self.lib.axb_weight_prepare(_ptr(B), _i64(K), _i64(N), int(trans_b), C.byref(h)))
+        return h
+
+    def weight_release(self, h):
+        self.lib.axb_weight_release(h)
+
+    def gemm_prepared(self, A, W, bias, out, M, trans_a=False, alpha=1.0, beta=0.0, act="none"):
+        self._check(self.lib.axb_gemm_prepared(_ptr(A), W, _ptr(bias), _ptr(out), _i64(M), int(trans_a), _f(alpha), _f(beta),
+                                               ACT[act]))
         return out
 
     def gemm_bias_act_scatter(self, A, B, bias, out, more, M, N, K, trans_a=False, trans_b=False, alpha=1.0, beta=0.0,

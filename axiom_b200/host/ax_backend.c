@@ -85,6 +85,102 @@ static axb_status check_f32(const axb_ax_tensor_t *t, const char *what, int want
 
 static float *fptr(const axb_ax_tensor_t *t) { return (float *)t->storage->data + t->offset; }
 
+/* ---- prepared-weight cache ------------------------------------------------------------------------------
+   A dense layer hands the same weight tensor to `gemm` call after call.  The engine can keep a weight's
+   tensor-core operand planes (axb_weight_prepare), so the second time a right-hand operand is seen with the
+   same storage, generation counter and shape it is prepared, and from then on only the left operand is split.
+   This is what axiom's own cpu_opt backend does with its packed-B cache, under the same contract: every
+   in-place write to a tensor bumps its storage's generation (ax_storage_touch; the dispatcher does it for every
+   op's output, src/compute/dispatch.c:347-350).  Writes that reach the device through this backend's own copy
+   hooks and frees through its free hook drop the entries they touch.  Results are bit-identical with and
+   without the cache. */
+enum { WCACHE_SLOTS = 8 };
+static const size_t WCACHE_MAX_BYTES = (size_t)2 << 30;   /* operand planes kept at most */
+static const int64_t WCACHE_MIN_ELEMS = 1 << 16;          /* smaller weights are not worth a handle */
+
+typedef struct {
+    const void *data;     /* storage->data (+ offset folded into ptr below) */
+    const float *ptr;
+    uint64_t generation;
+    int64_t K, N;
+    axb_weight_t *w;      /* NULL: seen once, not prepared yet */
+    size_t bytes;
+    uint64_t stamp;
+} wcache_entry;
+
+static wcache_entry wcache[WCACHE_SLOTS];
+static uint64_t wcache_clock;
+static size_t wcache_bytes;
+
+static void wcache_drop(wcache_entry *e)
+{
+    if (e->w) {
+        axb_weight_release(e->w);
+        wcache_bytes -= e->bytes;
+    }
+    e->data = NULL; e->ptr = NULL; e->w = NULL; e->bytes = 0; e->stamp = 0;
+}
+
+/* drops what lies in [lo, lo + bytes) or belongs to the storage whose base is lo */
+static void wcache_drop_range(const void *lo, size_t bytes)
+{
+    const char *a = (const char *)lo, *b = a + (bytes ? bytes : 1);
+    for (int i = 0; i < WCACHE_SLOTS; ++i) {
+        wcache_entry *e = &wcache[i];
+        if (!e->ptr) continue;
+        const char *p = (const char *)e->ptr, *q = p + (size_t)(e->K * e->N) * sizeof(float);
+        if (e->data == lo || (p < b && a < q)) wcache_drop(e);
+    }
+}
+
+static void wcache_clear(void)
+{
+    for (int i = 0; i < WCACHE_SLOTS; ++i)
+        if (wcache[i].ptr) wcache_drop(&wcache[i]);
+}
+
+/* the prepared form of right-hand operand b [K,N], or NULL (not seen before, too small, no room) */
+static const axb_weight_t *wcache_lookup(const axb_ax_tensor_t *b, int64_t K, int64_t N)
+{
+    if (K * N < WCACHE_MIN_ELEMS) return NULL;
+    const float *ptr = fptr(b);
+    wcache_entry *hit = NULL, *victim = NULL;
+    for (int i = 0; i < WCACHE_SLOTS; ++i) {
+        wcache_entry *e = &wcache[i];
+        if (e->ptr == ptr && e->K == K && e->N == N) hit = e;
+        /* the slot a newcomer takes: an empty one, else the least recently used */
+        if (!victim || (victim->ptr && (!e->ptr || e->stamp < victim->stamp))) victim = e;
+    }
+    if (hit && hit->generation != b->storage->generation) {   /* written since: start over */
+        wcache_drop(hit);
+        hit = NULL;
+    }
+    if (!hit) {                                                /* first sighting: remember it, prepare next time */
+        if (victim->ptr) wcache_drop(victim);
+        victim->data = b->storage->data; victim->ptr = ptr; victim->generation = b->storage->generation;
+        victim->K = K; victim->N = N; victim->w = NULL; victim->bytes = 0; victim->stamp = ++wcache_clock;
+        return NULL;
+    }
+    hit->stamp = ++wcache_clock;
+    if (!hit->w) {
+        const size_t bytes = (size_t)(K * N) * 8;              /* upper bound: two fp32-sized planes */
+        while (wcache_bytes + bytes > WCACHE_MAX_BYTES) {
+            wcache_entry *old = NULL;
+            for (int i = 0; i < WCACHE_SLOTS; ++i)
+                if (wcache[i].w && &wcache[i] != hit && (!old || wcache[i].stamp < old->stamp)) old = &wcache[i];
+            if (!old) return NULL;
+            wcache_drop(old);
+        }
+        if (axb_weight_prepare(ptr, K, N, 0, &hit->w) != AXB_OK) {
+            hit->w = NULL;
+            return NULL;
+        }
+        hit->bytes = bytes;
+        wcache_bytes += bytes;
+    }
+    return hit->w;
+}
+
 /* shared body of gemm / gemm_nt / gemm_tn / gemm_relu / gemm_ex */
 static axb_status gemm_common(const char *what, const axb_ax_tensor_t *a, const axb_ax_tensor_t *b,
                               const axb_ax_tensor_t *bias, axb_ax_tensor_t *out, int ta, int tb, float alpha,
@@ -108,6 +204,10 @@ static axb_status gemm_common(const char *what, const axb_ax_tensor_t *a, const 
         if ((st = check_f32(bias, what, 1))) return st;
         if (bias->shape[0] != N) return report(ST_SHAPE, "gemm bias length must equal the output columns");
         bias_p = fptr(bias);
+    }
+    if (!ta && !tb && M > 32) {
+        const axb_weight_t *w = wcache_lookup(b, K, N);
+        if (w) return done(axb_gemm_prepared(fptr(a), w, bias_p, fptr(out), M, 0, alpha, beta, act));
     }
     return done(axb_gemm_bias_act(fptr(a), fptr(b), bias_p, fptr(out), M, N, K, ta, tb, alpha, beta, act));
 }
@@ -215,7 +315,11 @@ static axb_status be_gelu(const axb_ax_tensor_t *in, axb_ax_tensor_t *out) { ret
 /* ---- device-owner hooks (src/compute/backends/cuda/backend.cu:56-116, memory.cu:80-140) ---- */
 
 static axb_status be_init(void) { return done(axb_init(-1)); }
-static void be_shutdown(void) { axb_shutdown(); }
+static void be_shutdown(void)
+{
+    wcache_clear();
+    axb_shutdown();
+}
 static void be_synchronize(void)
 {
     axb_synchronize();
@@ -223,10 +327,22 @@ static void be_synchronize(void)
 }
 static int be_device_count(void) { return axb_device_count(); }
 static void *be_alloc(size_t bytes) { return axb_storage_alloc(bytes); }
-static void be_free(void *p) { axb_storage_free(p); }
-static axb_status be_h2d(void *dst, const void *src, size_t bytes) { return done(axb_memcpy_h2d(dst, src, bytes)); }
+static void be_free(void *p)
+{
+    if (p) wcache_drop_range(p, 1);   /* entries are keyed on pointers into live storage */
+    axb_storage_free(p);
+}
+static axb_status be_h2d(void *dst, const void *src, size_t bytes)
+{
+    wcache_drop_range(dst, bytes);
+    return done(axb_memcpy_h2d(dst, src, bytes));
+}
 static axb_status be_d2h(void *dst, const void *src, size_t bytes) { return done(axb_memcpy_d2h(dst, src, bytes)); }
-static axb_status be_d2d(void *dst, const void *src, size_t bytes) { return done(axb_memcpy_d2d(dst, src, bytes)); }
+static axb_status be_d2d(void *dst, const void *src, size_t bytes)
+{
+    wcache_drop_range(dst, bytes);
+    return done(axb_memcpy_d2d(dst, src, bytes));
+}
 
 static axb_status ext_sdpa_fwd(const float *Q, const float *K, const float *V, float *out, float *L, int64_t BH,
                                int64_t S, int64_t dk, float scale, bool causal, float *P_save)

@@ -30,19 +30,30 @@ def shard_bounds(n: int, world: int, rank: int) -> tuple[int, int]:
 class RowShardedMLP:
     """y = act(...act(x W1 + b1)... Wn + bn) on this rank's rows of x; weights replicated, no communication."""
 
-    def __init__(self, engine, weights, biases, act="gelu"):
+    def __init__(self, engine, weights, biases, act="gelu", prepare=False):
+        """prepare: keep every weight's tensor-core operand planes (axb_weight_prepare) so a forward pass splits
+        activations only; the weights must then stay unchanged until close()."""
         assert len(weights) == len(biases)
         self.engine, self.weights, self.biases, self.act = engine, list(weights), list(biases), act
+        self.prepared = [engine.weight_prepare(W) for W in self.weights] if prepare else None
 
     def forward(self, x_rows, new_empty):
         h = x_rows
-        for W, b in zip(self.weights, self.biases):
+        for l, (W, b) in enumerate(zip(self.weights, self.biases)):
             M, K = h.shape
             N = W.shape[1]
             out = new_empty((M, N))
-            self.engine.gemm_bias_act(h, W, b, out, M, N, K, act=self.act)
+            if self.prepared is not None:
+                self.engine.gemm_prepared(h, self.prepared[l], b, out, M, act=self.act)
+            else:
+                self.engine.gemm_bias_act(h, W, b, out, M, N, K, act=self.act)
             h = out
         return h
+
+    def close(self):
+        for w in self.prepared or []:
+            self.engine.weight_release(w)
+        self.prepared = None
 
 
 class ColumnShardedMLP:

@@ -534,10 +534,24 @@ def w_c1(ctx, shared):
     fl = 2.0 * 1024 ** 3
     peak = ctx.peaks["bf16_tflops"] / 6
     step = g_ms or t["ms_per_step"]
-    return [dict(t, name="c1_1024", workload="fp32 GEMM+bias+ReLU 1024^3 (3xTF32)", value=fl / (t["ms_per_step"] * 1e-3) / 1e12,
-                 unit="TFLOP/s", graph_ms_per_call=g_ms,
-                 roofline=tensor_roof(fl / (step * 1e-3) / 1e12, peak, "measured bf16 burst / 2 / 3; whole call (pre-pass included) from a replayed graph"),
-                 parity_checked=bool(e <= 1e-5), parity_nerr=e)]
+    out = [dict(t, name="c1_1024", workload="fp32 GEMM+bias+ReLU 1024^3 (3xTF32)", value=fl / (t["ms_per_step"] * 1e-3) / 1e12,
+                unit="TFLOP/s", graph_ms_per_call=g_ms,
+                roofline=tensor_roof(fl / (step * 1e-3) / 1e12, peak, "measured bf16 burst / 2 / 3; whole call (pre-pass included) from a replayed graph"),
+                parity_checked=bool(e <= 1e-5), parity_nerr=e)]
+    # the same layer with its weight prepared once, as a dense layer would hold it
+    w = eng.weight_prepare(b1)
+    try:
+        fn2 = lambda: eng.gemm_prepared(a1, w, bias1, c1, 1024, act="relu")
+        t2 = ctx.core_time(fn2, 50, 5)
+        g2 = ctx.graph_time(fn2, calls=32)
+        e2 = nerr(host(c1[rows]), want)
+        out.append(dict(t2, name="c1_1024_prepared", workload="fp32 GEMM+bias+ReLU 1024^3, weight prepared once (axb_weight_prepare)",
+                        value=fl / (t2["ms_per_step"] * 1e-3) / 1e12, unit="TFLOP/s", graph_ms_per_call=g2,
+                        roofline=tensor_roof(fl / ((g2 or t2["ms_per_step"]) * 1e-3) / 1e12, peak, "measured bf16 burst / 2 / 3; whole call from a replayed graph"),
+                        parity_checked=bool(e2 <= 1e-5), parity_nerr=e2))
+    finally:
+        eng.weight_release(w)
+    return out
 
 
 def w_c3(ctx, shared):
@@ -723,25 +737,31 @@ def w_mlp(ctx, shared):
         return bool(t.item() > 0.5)
 
     res = []
-    rows = RowShardedMLP(eng, Ws, bs, act="gelu")
     xr = x[r0:r1].contiguous()
-    ms, per = ctx.timed(lambda: rows.forward(xr, new_empty), steps, 1)
-    ms /= steps
-    y = rows.forward(xr, new_empty)
     mine = [i for i, r in enumerate(probe) if r0 <= r < r1]
-    e = nerr(host(y[[probe[i] - r0 for i in mine]]), want[mine])
-    res.append({"name": "mlp_rows", "workload": f"3-layer MLP 8192-16384-16384-8192, batch 16384, rows sharded x{world} (no collective)",
-                "value": flop / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "ms_median": statistics.median(per),
-                "ms_min": min(per), "scaling": "strong", "parity_checked": all_ranks(e <= 1e-5), "parity_nerr": e,
-                "parity": "sampled rows on every rank vs a float64 forward"})
-    del y
+    for prepared in (True, False):
+        rows = RowShardedMLP(eng, Ws, bs, act="gelu", prepare=prepared)
+        ms, per = ctx.timed(lambda: rows.forward(xr, new_empty), steps, 1)
+        ms /= steps
+        y = rows.forward(xr, new_empty)
+        e = nerr(host(y[[probe[i] - r0 for i in mine]]), want[mine])
+        how = ("weights prepared once (axb_weight_prepare: only activations are split per step)" if prepared
+               else "plain axb_gemm_bias_act (weights split every step)")
+        res.append({"name": "mlp_rows" if prepared else "mlp_rows_unprepared",
+                    "workload": f"3-layer MLP 8192-16384-16384-8192, batch 16384, rows sharded x{world} (no collective), {how}",
+                    "value": flop / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "ms_median": statistics.median(per),
+                    "ms_min": min(per), "scaling": "strong", "parity_checked": all_ranks(e <= 1e-5), "parity_nerr": e,
+                    "parity": "sampled rows on every rank vs a float64 forward"})
+        rows.close()
+        del y, rows
+        torch.cuda.empty_cache()
     if world > 1:
         slabs, bias_slabs = [], []
         for Wl, b in zip(Ws, bs):
             c0, c1 = shard_bounds(Wl.shape[1], world, rank)
             slabs.append(Wl[:, c0:c1].contiguous())
             bias_slabs.append(b[c0:c1].contiguous())
-        del Ws, rows
+        del Ws
         torch.cuda.empty_cache()
         ag = lambda dst, src: dist.all_gather_into_tensor(dst.view(-1, dst.shape[-1]), src)
         cols = ColumnShardedMLP(eng, slabs, bias_slabs, world, rank, ag, act="gelu")

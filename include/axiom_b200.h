@@ -125,6 +125,22 @@ AXB_API int axb_gemm_bias_act(const float *A, const float *B, const float *bias,
                       int64_t M, int64_t N, int64_t K, int trans_a, int trans_b,
                       float alpha, float beta, int act);
 
+/* ---- prepared weights --------------------------------------------------------
+   A dense layer multiplies by the same weight matrix call after call.  axb_weight_prepare makes the tensor-core
+   operand planes of B once (device memory owned by the handle: 8 bytes per element in the 3xTF32 mode, 4 in bf16x3,
+   2 in bf16); axb_gemm_prepared then splits only the left operand:
+     C[M,N] = act(alpha * op(A) . op(B) + beta * C + bias[n])
+   with the same routes and bit-identical results as axb_gemm_bias_act on the same operands.  B must stay allocated
+   and unchanged until axb_weight_release (M <= 32 streams it directly); a weight belongs to the device and the fp32
+   mode it was prepared under.  The reference's CPU backend keeps packed B panels across calls in the same spirit
+   (pack_b cache keyed on storage pointer and generation, src/compute/backends/cpu_opt.c); its CUDA backend has no
+   counterpart (cuBLAS repacks nothing). */
+typedef struct axb_weight axb_weight_t;
+AXB_API int axb_weight_prepare(const float *B, int64_t K, int64_t N, int trans_b, axb_weight_t **out);
+AXB_API void axb_weight_release(axb_weight_t *w);
+AXB_API int axb_gemm_prepared(const float *A, const axb_weight_t *W, const float *bias, float *C, int64_t M, int trans_a,
+                              float alpha, float beta, int act);
+
 /* ---- multi-GPU building blocks (no counterpart in the reference, which is single-device) ----
    axb_gemm_bias_act_scatter is axb_gemm_bias_act on the tensor cores whose epilogue stores each finished tile to C
    AND to n_more further buffers of the same shape and pitch (at most 8).  With C_more pointing into peers' gather

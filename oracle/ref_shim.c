@@ -781,3 +781,40 @@ SHIM_API int ref_time_sdpa_causal(const float *Q, const float *K, const float *V
     }
     return 0;
 }
+
+/* A dense layer's life on the device: the SAME weight tensor b multiplies `reps` different inputs through
+   ax_compute_gemm_relu (bias nullable), is then overwritten in place with B2 (the backend's memcpy_h2d hook +
+   ax_storage_touch, as an optimizer step or a checkpoint load would) and multiplies the last input once more.
+   As: [reps][M,K]; C: [reps + 1][M,N].  Exercises whatever a backend caches per weight tensor. */
+SHIM_API int ref_device_dense_repeat(const float *As, const float *B, const float *B2, const float *bias, float *C,
+                                     int64_t M, int64_t N, int64_t K, int reps)
+{
+    use_cuda(1);
+    int rc = 0;
+    ax_tensor_t *b = to_dev(t2(B, K, N));
+    ax_tensor_t *bs = bias ? to_dev(t1(bias, N)) : NULL;
+    if (!b || (bias && !bs)) rc = 100;
+    const ax_backend_ops_t *ops = ax_compute_get_ops();
+    for (int r = 0; r <= reps && !rc; r++) {
+        const int ai = r < reps ? r : reps - 1;
+        if (r == reps) {
+            rc = (int)ops->memcpy_h2d(b->storage->data, B2, (size_t)(K * N) * sizeof(float));
+            ax_storage_touch(b->storage);
+        }
+        ax_tensor_t *a = to_dev(t2(As + (size_t)ai * M * K, M, K));
+        int64_t osh[2] = { M, N };
+        ax_tensor_t *o = ax_tensor_create(osh, 2, AX_FLOAT32);
+        if (!a || !o) rc = 101;
+        if (!rc) rc = (int)ax_compute_gemm_relu(a, b, bs, o);
+        if (!rc) {
+            ax_device_synchronize(AX_DEVICE_CUDA);
+            rc = copy_back(o, C + (size_t)r * M * N, M * N);
+        }
+        if (a) ax_tensor_destroy(a);
+        if (o) ax_tensor_destroy(o);
+    }
+    if (b) ax_tensor_destroy(b);
+    if (bs) ax_tensor_destroy(bs);
+    use_cuda(0);
+    return rc;
+}

@@ -271,3 +271,22 @@ def test_device_label_is_checked_against_the_pointer(engine):
     d = torch.zeros(16, device="cuda")
     assert engine.pointer_on_device(d.data_ptr()) and not engine.pointer_on_device(h.ctypes.data)
     assert not engine.pointer_on_device(0)
+
+
+@pytest.mark.parametrize("shape", [(200, 384, 512), (64, 1024, 256), (1024, 1024, 1024)])
+def test_dense_layer_weight_reuse_and_in_place_update(dropin, reference, oracle, shape):
+    """The same device-resident weight tensor through the dispatcher again and again (the host layer keeps its operand
+    planes from the second call on), then overwritten in place: every product must match the reference's CPU backend,
+    the ones after the update with the NEW weights."""
+    M, N, K = shape
+    reps = 4
+    As = np.stack([oracle.uniform((M, K), 7 + r) for r in range(reps)])
+    B, B2, bias = oracle.uniform((K, N), 13), oracle.uniform((K, N), 113), oracle.uniform((N,), 29)
+    out = np.full((reps + 1, M, N), np.nan, np.float32)
+    rc = dropin.ref_device_dense_repeat(p(As), p(B), p(B2), p(bias), p(out), i64(M), i64(N), i64(K), reps)
+    assert rc == 0, (rc, dropin.ref_last_error())
+    for r in range(reps + 1):
+        a = As[min(r, reps - 1)]
+        w = B if r < reps else B2
+        np.testing.assert_allclose(out[r], reference.gemm_relu(a, w, bias), atol=1e-3, rtol=1e-4)
+        assert nerr(out[r], np.maximum(oracle.gemm_f64(a, w) + bias, 0)) <= 1e-5, r

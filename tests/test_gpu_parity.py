@@ -626,3 +626,32 @@ def test_split_k_int8_bit_exact(engine, oracle, shape):
     np.testing.assert_array_equal(host(acc), acc_ref)
     np.testing.assert_array_equal(host(q), q_ref)
     assert engine.device_error() == 0
+
+
+@pytest.mark.parametrize("shape", [(1024, 1024, 1024), (300, 520, 1000), (8, 4096, 4096), (20, 1000, 1028), (2560, 2560, 512),
+                                   (256, 384, 4096)])
+@pytest.mark.parametrize("trans_b", [False, True])
+def test_prepared_weight_is_bit_identical(engine, oracle, shape, trans_b):
+    """axb_gemm_prepared (operand planes of the weight made once) against axb_gemm_bias_act on the same operands: the
+    same routes, so the same bits — tensor-core tiles, CTA pairs, split-K and the skinny route."""
+    M, N, K = shape
+    A, B, bias = oracle.uniform((M, K), 7), oracle.uniform((K, N), 13), oracle.uniform((N,), 29)
+    Bd = dev(np.ascontiguousarray(B.T) if trans_b else B)
+    Ad, bd = dev(A), dev(bias)
+    want = torch.empty((M, N), device="cuda")
+    engine.gemm_bias_act(Ad, Bd, bd, want, M, N, K, trans_b=trans_b, act="gelu")
+    w = engine.weight_prepare(Bd, trans_b=trans_b)
+    try:
+        for _ in range(2):
+            got = torch.full((M, N), float("nan"), device="cuda")
+            engine.gemm_prepared(Ad, w, bd, got, M, act="gelu")
+            np.testing.assert_array_equal(host(got), host(want))
+        assert nerr(host(got), oracle.bias_act(oracle.gemm_f64(A, B).astype(np.float32), bias, "gelu")) <= TOL_SPLIT
+        engine.set_fp32_mode("bf16")
+        try:
+            with pytest.raises(Exception):
+                engine.gemm_prepared(Ad, w, bd, got, M)       # prepared under another arithmetic
+        finally:
+            engine.set_fp32_mode("3xtf32")
+    finally:
+        engine.weight_release(w)
