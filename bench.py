@@ -385,7 +385,7 @@ def headline(ctx, args):
                 "frac": achieved / tf32_split_peak,
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload, from the
                 # ncu capture summarised for this kernel; algorithmic bytes: 4 operand planes + C
-                "traffic": 5.64e9, "algorithmic_bytes": 1.34e9,
+                "traffic": 6.65e9, "algorithmic_bytes": 1.34e9,
                 "kernel": "gemm_tc_pair_kernel<tf32, 3 products> (CTA pairs, 256x256 tiles)", "kernel_ms": core_avg_ms,
                 "kernel_ms_median": k_med, "kernel_ms_min": k_min, "prepass_ms": sum(pre) / max(len(pre), 1),
                 "peak_source": f"{peaks['source']} bf16 burst {peaks['bf16_tflops']} TFLOP/s / 2 (tf32 rate) / 3 (products)"}
