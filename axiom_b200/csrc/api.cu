@@ -1206,6 +1206,43 @@ extern "C" int axb_conv_gemm(const float *weight, const float *input, int64_t C_
     int split_mode, kind;
     TcProducts prod;
     fp32_mode_plan(split_mode, kind, prod);
+    TcConv cv;
+    cv.C = C_in; cv.H = H; cv.W = W; cv.kh = kh; cv.kw = kw; cv.pad_h = ph; cv.pad_w = pw; cv.out_h = out_h; cv.out_w = out_w;
+    if (gemm_tc_conv_applicable(cv, sh, sw, out) && H * W <= INT32_MAX) {
+        // Stride 1: implicit GEMM.  The image is transposed once into channel-innermost planes (the same pre-pass
+        // that transposes a [K, N] operand), the filter into [C_out][tap][channel] planes, and the GEMM's producer
+        // reads shifted windows of the image planes — the patch matrix, kh * kw times the image, never exists.
+        const int cpad = gemm_tc_conv_channel_pad(kind);
+        const int64_t c_pad = (C_in + cpad - 1) / cpad * cpad, taps = (int64_t)kh * kw;
+        const SplitOperand si = plan_split(split_mode, H * W, C_in), sw_ = plan_split(split_mode, C_out, taps * c_pad);
+        st = ensure_ws(si.total() + sw_.total() + kSplitScratch);
+        if (st) return st;
+        Carver carve{ (char *)cur().ws };
+        const TcSplitK sk = take_splitk(carve);
+        TcOperand opw, opi;
+        mark(0);
+        int e = run_split(si, input, H * W, true, carve, opi);
+        if (e) return cuda_fail("conv_gemm: image planes", e);
+        void *planes[3] = { nullptr, nullptr, nullptr };
+        opw.nplanes = split_num_planes(split_mode);
+        for (int i = 0; i < opw.nplanes; ++i) {
+            planes[i] = carve.take(sw_.plane_bytes);
+            opw.plane[i] = planes[i];
+        }
+        opw.rows = C_out;
+        opw.pitch_elems = sw_.pitch;
+        e = split_conv_weight(split_mode, weight, C_out, C_in, (int)taps, (int)c_pad, planes, sw_.pitch, cur().sm_count, cur().stream);
+        cur().launches++;
+        if (e) return cuda_fail("conv_gemm: filter planes", e);
+        TcEpilogue ep;
+        ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = nullptr; ep.colscale = nullptr; ep.act = ACT_NONE;
+        ep.out_mode = OUT_F32; ep.C = out; ep.acc_out = nullptr; ep.ldc = P; ep.n_extra = 0;
+        mark(1);
+        e = launch_gemm_tc_conv(kind, opw, opi, prod, C_out, cv, ep, cur().err_word, cur().sm_count, cur().stream, &sk);
+        mark(2);
+        cur().launches++;
+        return e ? cuda_fail("conv_gemm", e) : AXB_OK;
+    }
     const SplitOperand sa = plan_split(split_mode, C_out, K), sb = plan_split(split_mode, P, K);
     st = ensure_ws(sa.total() + sb.total() + kSplitScratch);
     if (st) return st;

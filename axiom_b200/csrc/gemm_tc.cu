@@ -104,6 +104,50 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
             const int k_blocks = p.k_blocks, stages = p.stages, npa = p.npa, npb = p.npb, ksplit = ksplit_all;
             const uint32_t sbytes = (uint32_t)stage_bytes;
             grid_dep_wait();   // the operand planes come from the kernel before this one
+            if (!do_a && p.cv_taps > 0) {
+                // implicit convolution: a stage of B is, per plane, one box per 64-pixel patch of the tile, taken
+                // from the image at the window offset of the stage's tap (out-of-range coordinates read as zero)
+                constexpr int NPATCH = BN / 64, PATCH_BYTES = 64 * SWB;
+                const int cblocks = p.cv_cblocks, kw = p.cv_kw, pw = p.cv_pw, phh = 64 / p.cv_pw;
+                for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
+                    const int t = w / ksplit, kb_lo = (w - t * ksplit) * p.kb_per_slice, kb_hi = min(k_blocks, kb_lo + p.kb_per_slice);
+                    int mt, nt;
+                    tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
+                    int x0[NPATCH], y0[NPATCH];
+#pragma unroll
+                    for (int q = 0; q < NPATCH; ++q) {
+                        const int patch = nt * NPATCH + q, py = patch / p.cv_px;
+                        x0[q] = (patch - py * p.cv_px) * pw - p.cv_pad_w;
+                        y0[q] = py * phh - p.cv_pad_h;
+                    }
+                    int tap = kb_lo / cblocks, cb = kb_lo - tap * cblocks;
+                    int ky = tap / kw, kx = tap - ky * kw;
+                    for (int kb = kb_lo; kb < kb_hi; ++kb) {
+                        if (!mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1u)) {
+                            report(p.err, ERR_PRODUCER_WAIT);
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t fb = bar_full + 8 * s;
+                        uint32_t dst = stage0 + s * sbytes + npa * A_BYTES;
+                        for (int i = 0; i < npb; ++i)
+#pragma unroll
+                            for (int q = 0; q < NPATCH; ++q, dst += PATCH_BYTES)
+                                tma_load_3d(dst, &tm.b[i], fb, cb * BKE, x0[q] + kx, y0[q] + ky);
+                        if (++cb == cblocks) {
+                            cb = 0;
+                            if (++kx == kw) {
+                                kx = 0;
+                                ++ky;
+                            }
+                        }
+                        if (++s == (uint32_t)stages) {
+                            s = 0;
+                            ph ^= 1u;
+                        }
+                    }
+                }
+            } else
             for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
                 const int t = w / ksplit, kb_lo = (w - t * ksplit) * p.kb_per_slice, kb_hi = min(k_blocks, kb_lo + p.kb_per_slice);
                 int mt, nt;
@@ -316,6 +360,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
                                                                                 sum[c * 32 + 4 * j4 + 2], sum[c * 32 + 4 * j4 + 3]);
                             __syncwarp();
                             if (p.tma_store) store_piece_f32_tma(p, &tm.c, stg, row0, col0, lane);
+                            else if (p.cv_taps > 0) store_piece_f32_conv(p, stg, row0, col0, lane);
                             else store_piece_f32(p, stg, row0, col0, lane, rows_aligned);
                         }
                     }
@@ -497,6 +542,35 @@ static int encode_f32_store_tmap(CUtensorMap *out, float *ptr, int64_t rows, int
     return 0;
 }
 
+// Image planes [H][W][pitch] (C valid channels per pixel) as the B operand of an implicit convolution:
+// box = swb bytes of channels x patch_w x patch_h pixels, swizzled like a K-major tile of patch_w * patch_h rows.
+static int encode_conv_image_tmap(CUtensorMap *out, int kind, const void *ptr, int64_t C, int64_t H, int64_t W,
+                                  int64_t pitch_elems, int swb, int patch_w, int patch_h)
+{
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) {
+        snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled entry point not found");
+        return (int)cudaErrorSymbolNotFound;
+    }
+    const int es = kind == KIND_TF32 ? 4 : (kind == KIND_BF16 ? 2 : 1);
+    const CUtensorMapDataType dt = kind == KIND_TF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : kind == KIND_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                     : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    cuuint64_t dims[3] = { (cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H };
+    cuuint64_t strides[2] = { (cuuint64_t)pitch_elems * es, (cuuint64_t)W * (cuuint64_t)pitch_elems * es };
+    cuuint32_t box[3] = { (cuuint32_t)(swb / es), (cuuint32_t)patch_w, (cuuint32_t)patch_h };
+    cuuint32_t estr[3] = { 1, 1, 1 };
+    CUresult r = fn(out, dt, 3, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swb == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled (image planes) failed (%d): ptr=%p C=%lld H=%lld W=%lld pitch=%lld box=%ux%ux%u",
+                 (int)r, ptr, (long long)C, (long long)H, (long long)W, (long long)pitch_elems, box[0], box[1], box[2]);
+        return (int)cudaErrorInvalidValue;
+    }
+    return 0;
+}
+
 template <int KIND, int BN, int SWB, int NPROD, bool SPLITK>
 static int launch_inst(const TmapPack &tm, KernelArgs &ka, int stage_bytes, int grid, cudaStream_t stream)
 {
@@ -562,7 +636,8 @@ struct TcPlan {
 };
 
 
-static TcPlan make_plan(int kind, const TcProducts &prod, int64_t M, int64_t N, int64_t K, int sm_count, const TcSplitK *splitk)
+static TcPlan make_plan(int kind, const TcProducts &prod, int64_t M, int64_t N, int64_t K, int sm_count, const TcSplitK *splitk,
+                        bool allow_pair = true)
 {
     TcPlan pl;
     const bool can_split = splitk && splitk->scratch && splitk->counters;
@@ -577,7 +652,7 @@ static TcPlan make_plan(int kind, const TcProducts &prod, int64_t M, int64_t N, 
     if (!can_split && bn == 128 && mt * ((N + 127) / 128) * 2 < sm_count) bn = 64;
     if (N <= 64) bn = 64;
     else if (N <= 128 && bn > 128) bn = 128;
-    bool use_pair = ((M + 255) / 256) * ((N + 255) / 256) >= sm_count / 2 && N >= 256 && M >= 256;
+    bool use_pair = allow_pair && ((M + 255) / 256) * ((N + 255) / 256) >= sm_count / 2 && N >= 256 && M >= 256;
     if (use_pair) {
         bn = 256;
         mt = (M + 255) / 256;
@@ -632,9 +707,63 @@ bool gemm_tc_splits_k(int kind, const TcProducts &prod, int64_t M, int64_t N, in
     return make_plan(kind, prod, M, N, K, sm_count, &any).ksplit > 1;
 }
 
+// The 64-pixel patch of an implicit convolution: patch_w x 64/patch_w output pixels, the shape that wastes the
+// fewest pixels past the image's right and bottom edges.
+static int conv_patch_w(int64_t out_h, int64_t out_w)
+{
+    int best = 8;
+    int64_t best_area = -1;
+    for (int pw = 8; pw <= 32; pw *= 2) {
+        const int ph = 64 / pw;
+        const int64_t area = ((out_w + pw - 1) / pw) * ((out_h + ph - 1) / ph);
+        if (best_area < 0 || area < best_area) {
+            best = pw;
+            best_area = area;
+        }
+    }
+    return best;
+}
+
+int gemm_tc_conv_channel_pad(int kind) { return kind == KIND_TF32 ? 32 : (kind == KIND_BF16 ? 64 : 128); }
+
+bool gemm_tc_conv_applicable(const TcConv &cv, int sh, int sw, const void *out)
+{
+    return sh == 1 && sw == 1 && cv.out_w % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && cv.out_h > 0 &&
+           cv.out_w > 0 && cv.H < (1 << 30) && cv.W < (1 << 30) && cv.out_h < (1 << 30) && cv.out_w < (1 << 30) &&
+           cv.kh * cv.kw < (1 << 20);
+}
+
+static int launch_common(int kind, const TcOperand &A, const TcOperand &B, const TcProducts &prod, int64_t M, int64_t N,
+                         int64_t K, const TcEpilogue &ep, int *err_word, int sm_count, cudaStream_t stream,
+                         const TcSplitK *splitk, const TcConv *cv);
+
 int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcProducts &prod,
                    int64_t M, int64_t N, int64_t K, const TcEpilogue &ep, int *err_word,
                    int sm_count, cudaStream_t stream, const TcSplitK *splitk)
+{
+    return launch_common(kind, A, B, prod, M, N, K, ep, err_word, sm_count, stream, splitk, nullptr);
+}
+
+int launch_gemm_tc_conv(int kind, const TcOperand &A, const TcOperand &B_image, const TcProducts &prod, int64_t M,
+                        const TcConv &cv, const TcEpilogue &ep, int *err_word, int sm_count, cudaStream_t stream,
+                        const TcSplitK *splitk)
+{
+    if (!gemm_tc_conv_applicable(cv, 1, 1, ep.C) || ep.out_mode != OUT_F32 || ep.beta != 0.0f || ep.n_extra != 0 ||
+        ep.hs_dk != 0 || ep.bias || ep.colscale || kind == KIND_I8) {
+        snprintf(g_err, sizeof g_err, "launch_gemm_tc_conv: geometry or epilogue outside the implicit path");
+        return (int)cudaErrorInvalidValue;
+    }
+    const int pw = conv_patch_w(cv.out_h, cv.out_w), ph = 64 / pw;
+    const int64_t npatch = ((cv.out_w + pw - 1) / pw) * ((cv.out_h + ph - 1) / ph);
+    const int cpad = gemm_tc_conv_channel_pad(kind);
+    const int64_t c_pad = (cv.C + cpad - 1) / cpad * cpad;
+    return launch_common(kind, A, B_image, prod, M, npatch * 64, (int64_t)cv.kh * cv.kw * c_pad, ep, err_word, sm_count,
+                         stream, splitk, &cv);
+}
+
+static int launch_common(int kind, const TcOperand &A, const TcOperand &B, const TcProducts &prod, int64_t M, int64_t N,
+                         int64_t K, const TcEpilogue &ep, int *err_word, int sm_count, cudaStream_t stream,
+                         const TcSplitK *splitk, const TcConv *cv)
 {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || A.nplanes < 1 || B.nplanes < 1 || A.nplanes > TC_MAX_PLANES || B.nplanes > TC_MAX_PLANES ||
@@ -642,7 +771,7 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
         snprintf(g_err, sizeof g_err, "launch_gemm_tc: bad operand description");
         return (int)cudaErrorInvalidValue;
     }
-    const TcPlan pl = make_plan(kind, prod, M, N, K, sm_count, splitk);
+    const TcPlan pl = make_plan(kind, prod, M, N, K, sm_count, splitk, cv == nullptr);
     const int bn = pl.bn, swb = pl.swb;
     const bool use_pair = pl.pair;
     const int64_t mt = pl.mt, nt = pl.nt;
@@ -653,8 +782,10 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
         int e = encode_plane(&tm.a[i], kind, A.plane[i], M, K, A.pitch_elems, BM, swb);
         if (e) return e;
     }
+    const int cv_pw = cv ? conv_patch_w(cv->out_h, cv->out_w) : 0;
     for (int i = 0; i < B.nplanes; ++i) {
-        int e = encode_plane(&tm.b[i], kind, B.plane[i], N, K, B.pitch_elems, use_pair ? bn / 2 : bn, swb);
+        int e = cv ? encode_conv_image_tmap(&tm.b[i], kind, B.plane[i], cv->C, cv->H, cv->W, B.pitch_elems, swb, cv_pw, 64 / cv_pw)
+                   : encode_plane(&tm.b[i], kind, B.plane[i], N, K, B.pitch_elems, use_pair ? bn / 2 : bn, swb);
         if (e) return e;
     }
     KernelArgs ka;
@@ -686,6 +817,21 @@ int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcPro
         ka.beta = 0.0f;
         ka.n_extra = 0;
     }
+    if (cv) {
+        const int es = kind == KIND_TF32 ? 4 : 2;
+        const int cpad = gemm_tc_conv_channel_pad(kind);
+        ka.cv_taps = cv->kh * cv->kw;
+        ka.cv_kw = cv->kw;
+        ka.cv_cblocks = (int)((cv->C + cpad - 1) / cpad * cpad / (swb / es));
+        ka.cv_pw = cv_pw;
+        ka.cv_px = (int)((cv->out_w + cv_pw - 1) / cv_pw);
+        ka.cv_npatch = (int)(N / 64);
+        ka.cv_pad_w = cv->pad_w;
+        ka.cv_pad_h = cv->pad_h;
+        // the output leaves through store_piece_f32_conv
+        ka.ldc = cv->out_h * cv->out_w;
+        ka.cv_out_w = (int)cv->out_w;
+    } else
     // plain aligned fp32 output that is not read back: the staging tiles leave through TMA stores
     if (kind != KIND_I8 && ep.out_mode == OUT_F32 && ep.hs_dk == 0 && ka.n_extra == 0 && ep.beta == 0.0f && ep.C &&
         (reinterpret_cast<uintptr_t>(ep.C) & 15) == 0 && ep.ldc % 4 == 0) {

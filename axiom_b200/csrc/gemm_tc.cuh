@@ -58,6 +58,26 @@ struct TcSplitK {
     int n_counters;
 };
 
+// Convolution as an implicit GEMM (stride 1): the B operand is not a matrix in memory but the channel-innermost
+// image planes [H][W][pitch] read through shifted windows.  Output pixel (oh, ow) is row `pixel` of B; its element
+// k = tap * c_pad + c (tap = ky * kw + kx) is image[oh + ky - pad_h][ow + kx - pad_w][c], zero outside the image
+// and for c >= C — each pipeline stage is one TMA box per 64-pixel patch at window-shifted coordinates, and the
+// zero fill of out-of-range coordinates IS the padding.  The A operand (the filter) is laid out to match:
+// [M][taps * c_pad] with c_pad = C rounded up to gemm_tc_conv_channel_pad(kind).  The output [M][out_h][out_w] is
+// written in 16-byte groups that must not straddle pixel rows, so out_w % 4 == 0 and a 16-byte aligned base are
+// required (gemm_tc_conv_applicable).
+struct TcConv {
+    int64_t C, H, W;       // image planes: C valid channels per pixel (B.pitch_elems apart)
+    int kh, kw, pad_h, pad_w;
+    int64_t out_h, out_w;
+};
+int gemm_tc_conv_channel_pad(int kind);
+bool gemm_tc_conv_applicable(const TcConv &cv, int sh, int sw, const void *out);
+// ep.C = out [M][out_h][out_w] fp32; alpha and act are applied, beta must be 0, no bias, no extra destinations
+int launch_gemm_tc_conv(int kind, const TcOperand &A, const TcOperand &B_image, const TcProducts &prod, int64_t M,
+                        const TcConv &cv, const TcEpilogue &ep, int *err_word, int sm_count, cudaStream_t stream,
+                        const TcSplitK *splitk = nullptr);
+
 // kind: MmaKind (0 tf32, 1 bf16, 2 int8).  Returns cudaError_t as int; a device
 // side wait that ran out is reported through *err_word (0 = clean).
 int launch_gemm_tc(int kind, const TcOperand &A, const TcOperand &B, const TcProducts &prod,

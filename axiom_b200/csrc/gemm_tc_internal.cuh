@@ -50,6 +50,10 @@ struct KernelArgs {
     int ksplit, kb_per_slice;
     void *sk_scratch;        // [tiles x CTAs per tile][ksplit][128 x BN] fp32 / s32
     int *sk_counters;        // [tiles x CTAs per tile], zero between launches
+    // implicit convolution (cv_taps > 0, see TcConv): the B maps are 3-D over the image planes with one box per
+    // 64-pixel patch (cv_pw x 64/cv_pw pixels); output column j of the GEMM is pixel j % 64 of patch j / 64, stored
+    // by store_piece_f32_conv (ldc = out_h * out_w)
+    int cv_taps, cv_kw, cv_cblocks, cv_pw, cv_px, cv_npatch, cv_pad_w, cv_pad_h, cv_out_w;
 };
 
 // shared-memory header words used by the split-K hand-over (after the barriers and the TMEM slot)
@@ -196,6 +200,29 @@ static __device__ __forceinline__ void store_piece_f32_tma(const KernelArgs &p, 
     if (lane == 0) {
         tma_store_2d(tmc, smem_u32(stg), col0, (int32_t)row0);
         tma_store_commit();
+    }
+}
+
+// The fp32 epilogue of an implicit convolution (alpha and activation only): the piece's 32 columns are 32 / cv_pw
+// pixel rows of cv_pw pixels of one patch, so each 16-byte group of the staging tile goes to its own place in
+// out[row][oh][ow] (ldc = out_h * out_w; out_w % 4 == 0 keeps every group inside one pixel row and
+// 16-byte aligned).  Pixels past the right and bottom edges of the image are dropped.
+static __device__ __forceinline__ void store_piece_f32_conv(const KernelArgs &p, const float4 *stg, long long row0, int col0, int lane)
+{
+    const int patch = col0 >> 6, py = patch / p.cv_px, px = patch - py * p.cv_px;
+    if (patch >= p.cv_npatch) return;
+    const int ch = lane & 7, j = (col0 & 63) + ch * 4;            // pixel index inside the patch of this lane's group
+    const int out_w = p.cv_out_w, oh = py * (64 / p.cv_pw) + j / p.cv_pw, ow = px * p.cv_pw + j % p.cv_pw;
+    if (ow >= out_w || (long long)oh * out_w >= p.ldc) return;
+    float *dst0 = reinterpret_cast<float *>(p.C) + (long long)oh * out_w + ow;
+#pragma unroll 2
+    for (int it = 0; it < 8; ++it) {
+        const int r = it * 4 + (lane >> 3);
+        if (row0 + r >= p.M) continue;
+        const float4 v = stg[r * 8 + (ch ^ (r & 7))];
+        *reinterpret_cast<float4 *>(dst0 + (row0 + r) * p.ldc) =
+            make_float4(epi_act(v.x * p.alpha, p.act), epi_act(v.y * p.alpha, p.act), epi_act(v.z * p.alpha, p.act),
+                        epi_act(v.w * p.alpha, p.act));
     }
 }
 

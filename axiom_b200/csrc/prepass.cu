@@ -262,6 +262,26 @@ __global__ void __launch_bounds__(256) split_im2col_kernel(const float *__restri
     }
 }
 
+// Filter of an implicit convolution: weight [C_out][C_in][taps] (taps = kh * kw) -> planes [C_out][taps][c_pad],
+// channel innermost and zero for c >= C_in, so that a k-block of the GEMM lies inside one window tap.
+template <int MODE>
+__global__ void __launch_bounds__(256) split_conv_weight_kernel(const float *__restrict__ w, int64_t C_out, int C_in, int taps,
+                                                                int c_pad, PlanePtrs pl, int64_t pitch)
+{
+    grid_dep_launch();
+    const int half = c_pad / 2;
+    const int64_t total = C_out * taps * half;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int c = 2 * (int)(i % half);
+        const int64_t rest = i / half;
+        const int tap = (int)(rest % taps);
+        const int64_t co = rest / taps;
+        const float *src = w + (co * C_in + c) * taps + tap;
+        const float v0 = c < C_in ? __ldg(src) : 0.0f, v1 = c + 1 < C_in ? __ldg(src + taps) : 0.0f;
+        store2<MODE>(pl.p, co * pitch + (int64_t)tap * c_pad + c, v0, v1);
+    }
+}
+
 // int8 [rows, k] -> bf16 plane [rows, pitch] (every int8 is exact in bf16)
 __global__ void __launch_bounds__(256) widen_i8_bf16_kernel(const int8_t *__restrict__ in, int64_t rows,
                                                             int64_t k, __nv_bfloat16 *out, int64_t pitch)
@@ -411,6 +431,21 @@ int split_im2col(int mode, const float *in, int64_t C_in, int64_t H, int64_t W, 
     case SPLIT_BF16X1: split_im2col_kernel<SPLIT_BF16X1><<<g, 256, sm, st>>>(in, C_in, H, W, kh, kw, sh, sw, ph, pw, out_h, out_w, pl, pitch, table); break;
     case SPLIT_BF16X2: split_im2col_kernel<SPLIT_BF16X2><<<g, 256, sm, st>>>(in, C_in, H, W, kh, kw, sh, sw, ph, pw, out_h, out_w, pl, pitch, table); break;
     default: split_im2col_kernel<SPLIT_BF16X3><<<g, 256, sm, st>>>(in, C_in, H, W, kh, kw, sh, sw, ph, pw, out_h, out_w, pl, pitch, table); break;
+    }
+    return (int)cudaGetLastError();
+}
+
+int split_conv_weight(int mode, const float *w, int64_t C_out, int64_t C_in, int taps, int c_pad, void *const planes[3],
+                      int64_t pitch, int sm_count, cudaStream_t st)
+{
+    PlanePtrs pl;
+    for (int i = 0; i < 3; ++i) pl.p[i] = planes[i];
+    const int g = grid_for(C_out * taps * (c_pad / 2), 256, sm_count);
+    switch (mode) {
+    case SPLIT_TF32X2: split_conv_weight_kernel<SPLIT_TF32X2><<<g, 256, 0, st>>>(w, C_out, (int)C_in, taps, c_pad, pl, pitch); break;
+    case SPLIT_BF16X1: split_conv_weight_kernel<SPLIT_BF16X1><<<g, 256, 0, st>>>(w, C_out, (int)C_in, taps, c_pad, pl, pitch); break;
+    case SPLIT_BF16X2: split_conv_weight_kernel<SPLIT_BF16X2><<<g, 256, 0, st>>>(w, C_out, (int)C_in, taps, c_pad, pl, pitch); break;
+    default: split_conv_weight_kernel<SPLIT_BF16X3><<<g, 256, 0, st>>>(w, C_out, (int)C_in, taps, c_pad, pl, pitch); break;
     }
     return (int)cudaGetLastError();
 }

@@ -698,7 +698,7 @@ def w_conv(ctx, shared):
     t = ctx.core_time(lambda: eng.conv_gemm(wc, xc, 3, 3, 1, 1, 1, 1, oc), 20, 3)
     want = ctx.oracle.conv_gemm(host(wc), host(xc), 3, 3, 1, 1, 1, 1)
     e = nerr(host(oc), want)
-    return [dict(t, name="conv3x3", workload="conv 3x3 pad 1 as GEMM, one sample [256,56,56] -> [256,56,56] (im2col gathered into the operand planes)",
+    return [dict(t, name="conv3x3", workload="conv 3x3 pad 1 as an implicit GEMM, one sample [256,56,56] -> [256,56,56] (shifted TMA windows of the channel-innermost image; no patch matrix)",
                  value=2.0 * 256 * 2304 * 3136 / (t["ms_per_step"] * 1e-3) / 1e12, unit="TFLOP/s",
                  parity_checked=bool(e <= 2e-5), parity_nerr=e, parity="whole output vs the fp32 oracle (tolerance of two fp32 summation orders)")]
 

@@ -500,6 +500,39 @@ def test_conv_gemm_vs_oracle(engine, oracle, geom):
     assert engine.device_error() == 0
 
 
+@pytest.mark.parametrize("geom", [(256, 256, 56, 56, 3, 3, 1, 1, 1, 1),    # the benchmark layer: two 8 x 8 patches per tile, K split
+                                  (96, 20, 30, 36, 5, 5, 1, 1, 2, 2),      # channels padded 20 -> 32, ragged patches on both edges
+                                  (40, 33, 5, 64, 3, 3, 1, 1, 1, 1),       # flat image: 32 x 2 patches
+                                  (300, 40, 20, 16, 1, 3, 1, 1, 0, 1),     # three row tiles, 1 x 3 window
+                                  (64, 16, 33, 21, 2, 2, 1, 1, 0, 0),      # even window, no padding
+                                  (16, 8, 6, 8, 3, 3, 1, 1, 3, 3),         # padding as wide as the window: all-zero windows
+                                  (512, 32, 112, 112, 3, 3, 1, 1, 1, 1)])  # enough tiles for 128 x 256 tiles (four patches each)
+@pytest.mark.parametrize("mode", ["3xtf32", "bf16x3", "bf16"])
+def test_conv_implicit_gemm(engine, oracle, geom, mode):
+    """Stride-1 layers whose output width is a multiple of 4 take the implicit-GEMM route (shifted TMA windows of the
+    channel-innermost image, no patch matrix): every patch shape, channel padding, edge clipping, in all fp32 modes."""
+    C_out, C_in, H, W, kh, kw, sh, sw, ph, pw = geom
+    if mode != "3xtf32" and C_out * C_in * H * W > 1 << 28:
+        pytest.skip("largest layer in the default mode only")
+    w = oracle.normal((C_out, C_in * kh * kw), 7, sigma=1.0 / np.sqrt(C_in * kh * kw))
+    x = oracle.uniform((C_in, H, W), 13)
+    want = oracle.conv_gemm(w, x, kh, kw, sh, sw, ph, pw)
+    assert ((W + 2 * pw - kw) // sw + 1) % 4 == 0 and sh == 1 and sw == 1     # the route's own conditions
+    out = torch.full(want.shape, float("nan"), device="cuda")
+    engine.set_fp32_mode(mode)
+    try:
+        engine.conv_gemm(dev(w), dev(x), kh, kw, sh, sw, ph, pw, out)
+        again = torch.full(want.shape, float("nan"), device="cuda")
+        engine.conv_gemm(dev(w), dev(x), kh, kw, sh, sw, ph, pw, again)
+    finally:
+        engine.set_fp32_mode("3xtf32")
+    got = host(out)
+    assert np.isfinite(got).all()
+    assert nerr(got, want) <= (TOL_BF16 if mode == "bf16" else TOL_SPLIT), (mode, nerr(got, want))
+    np.testing.assert_array_equal(host(again), got)      # split-K sums in slice order: repeatable
+    assert engine.device_error() == 0
+
+
 @pytest.mark.parametrize("shape", [(2, 1024, 1024), (8, 4096, 4096), (9, 1000, 2048), (16, 2048, 1040), (17, 8200, 1168),
                                    (32, 16384, 512), (33, 1024, 1024), (64, 4096, 4096), (5, 128, 8192),
                                    (2, 8192, 128), (64, 130, 8192), (7, 64, 16384), (48, 2048, 65536 // 64),
