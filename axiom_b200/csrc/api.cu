@@ -1221,19 +1221,18 @@ extern "C" int axb_conv_gemm(const float *weight, const float *input, int64_t C_
         const TcSplitK sk = take_splitk(carve);
         TcOperand opw, opi;
         mark(0);
-        int e = run_split(si, input, H * W, true, carve, opi);
-        if (e) return cuda_fail("conv_gemm: image planes", e);
-        void *planes[3] = { nullptr, nullptr, nullptr };
-        opw.nplanes = split_num_planes(split_mode);
-        for (int i = 0; i < opw.nplanes; ++i) {
-            planes[i] = carve.take(sw_.plane_bytes);
-            opw.plane[i] = planes[i];
-        }
+        void *ip[3] = { nullptr, nullptr, nullptr }, *wp[3] = { nullptr, nullptr, nullptr };
+        opi.nplanes = opw.nplanes = split_num_planes(split_mode);
+        for (int i = 0; i < opi.nplanes; ++i) opi.plane[i] = ip[i] = carve.take(si.plane_bytes);
+        for (int i = 0; i < opw.nplanes; ++i) opw.plane[i] = wp[i] = carve.take(sw_.plane_bytes);
+        opi.rows = H * W;
+        opi.pitch_elems = si.pitch;
         opw.rows = C_out;
         opw.pitch_elems = sw_.pitch;
-        e = split_conv_weight(split_mode, weight, C_out, C_in, (int)taps, (int)c_pad, planes, sw_.pitch, cur().sm_count, cur().stream);
+        int e = split_conv_operands(split_mode, input, C_in, H * W, ip, si.pitch, weight, C_out, (int)taps, (int)c_pad, wp, sw_.pitch,
+                                    cur().sm_count, cur().stream);
         cur().launches++;
-        if (e) return cuda_fail("conv_gemm: filter planes", e);
+        if (e) return cuda_fail("conv_gemm: operand planes", e);
         TcEpilogue ep;
         ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = nullptr; ep.colscale = nullptr; ep.act = ACT_NONE;
         ep.out_mode = OUT_F32; ep.C = out; ep.acc_out = nullptr; ep.ldc = P; ep.n_extra = 0;

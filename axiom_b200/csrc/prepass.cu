@@ -180,6 +180,25 @@ __global__ void __launch_bounds__(256) split_transpose_kernel(const float *__res
     split_transpose_body<MODE>(in, rows, k, ld, pl, pitch, tile, blockIdx.x, gridDim.x);
 }
 
+// Filter of an implicit convolution: weight [C_out][C_in][taps] (taps = kh * kw) -> planes [C_out][taps][c_pad],
+// channel innermost and zero for c >= C_in, so that a k-block of the GEMM lies inside one window tap.
+template <int MODE>
+__device__ __forceinline__ void split_conv_weight_body(const float *__restrict__ w, int64_t C_out, int C_in, int taps, int c_pad,
+                                                       const PlanePtrs &pl, int64_t pitch, int vblock, int vgrid)
+{
+    const int half = c_pad / 2;
+    const int64_t total = C_out * taps * half;
+    for (int64_t i = (int64_t)vblock * blockDim.x + threadIdx.x; i < total; i += (int64_t)vgrid * blockDim.x) {
+        const int c = 2 * (int)(i % half);
+        const int64_t rest = i / half;
+        const int tap = (int)(rest % taps);
+        const int64_t co = rest / taps;
+        const float *src = w + (co * C_in + c) * taps + tap;
+        const float v0 = c < C_in ? __ldg(src) : 0.0f, v1 = c + 1 < C_in ? __ldg(src + taps) : 0.0f;
+        store2<MODE>(pl.p, co * pitch + (int64_t)tap * c_pad + c, v0, v1);
+    }
+}
+
 // Both operands of one GEMM in ONE launch: blocks [0, ga) split operand A, the rest operand B; each operand is either
 // row-major in k (rows body) or has k outermost (transpose body).  A 1024^3 GEMM is launch-bound: two pre-pass launches
 // were a third of its step.
@@ -188,6 +207,7 @@ struct SplitTask {
     int64_t rows, k, ld, pitch, chunk_k, chunk_stride;
     PlanePtrs pl;
     int transposed, blocks;
+    int conv_taps, conv_cin, conv_cpad;   // conv_taps > 0: `in` is a filter [rows][conv_cin][conv_taps] (split_conv_weight_body)
 };
 
 template <int MODE>
@@ -198,7 +218,8 @@ __global__ void __launch_bounds__(256) split_pair_kernel(const SplitTask a, cons
     const bool first = (int)blockIdx.x < a.blocks;
     const SplitTask &t = first ? a : b;
     const int vblock = first ? (int)blockIdx.x : (int)blockIdx.x - a.blocks;
-    if (t.transposed) split_transpose_body<MODE>(t.in, t.rows, t.k, t.ld, t.pl, t.pitch, tile, vblock, t.blocks);
+    if (t.conv_taps > 0) split_conv_weight_body<MODE>(t.in, t.rows, t.conv_cin, t.conv_taps, t.conv_cpad, t.pl, t.pitch, vblock, t.blocks);
+    else if (t.transposed) split_transpose_body<MODE>(t.in, t.rows, t.k, t.ld, t.pl, t.pitch, tile, vblock, t.blocks);
     else split_rows_body<MODE>(t.in, t.rows, t.k, t.ld, t.pl, t.pitch, t.chunk_k, t.chunk_stride, vblock, t.blocks);
 }
 
@@ -259,26 +280,6 @@ __global__ void __launch_bounds__(256) split_im2col_kernel(const float *__restri
                 if (k + 1 < K) store1<MODE>(pl.p, row + k + 1, v[1]);
             }
         }
-    }
-}
-
-// Filter of an implicit convolution: weight [C_out][C_in][taps] (taps = kh * kw) -> planes [C_out][taps][c_pad],
-// channel innermost and zero for c >= C_in, so that a k-block of the GEMM lies inside one window tap.
-template <int MODE>
-__global__ void __launch_bounds__(256) split_conv_weight_kernel(const float *__restrict__ w, int64_t C_out, int C_in, int taps,
-                                                                int c_pad, PlanePtrs pl, int64_t pitch)
-{
-    grid_dep_launch();
-    const int half = c_pad / 2;
-    const int64_t total = C_out * taps * half;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int c = 2 * (int)(i % half);
-        const int64_t rest = i / half;
-        const int tap = (int)(rest % taps);
-        const int64_t co = rest / taps;
-        const float *src = w + (co * C_in + c) * taps + tap;
-        const float v0 = c < C_in ? __ldg(src) : 0.0f, v1 = c + 1 < C_in ? __ldg(src + taps) : 0.0f;
-        store2<MODE>(pl.p, co * pitch + (int64_t)tap * c_pad + c, v0, v1);
     }
 }
 
@@ -389,6 +390,7 @@ static SplitTask make_task(const float *in, int64_t rows, int64_t k, int64_t ld,
     t.in = in; t.rows = rows; t.k = k; t.ld = ld; t.pitch = pitch; t.chunk_k = chunk_k; t.chunk_stride = chunk_stride;
     for (int i = 0; i < 3; ++i) t.pl.p[i] = planes[i];
     t.transposed = transposed ? 1 : 0;
+    t.conv_taps = t.conv_cin = t.conv_cpad = 0;
     if (!transposed) {
         t.blocks = grid_for(rows * ((k + 3) / 4), 256, sm_count);
     } else {
@@ -435,17 +437,21 @@ int split_im2col(int mode, const float *in, int64_t C_in, int64_t H, int64_t W, 
     return (int)cudaGetLastError();
 }
 
-int split_conv_weight(int mode, const float *w, int64_t C_out, int64_t C_in, int taps, int c_pad, void *const planes[3],
-                      int64_t pitch, int sm_count, cudaStream_t st)
+int split_conv_operands(int mode, const float *image, int64_t C_in, int64_t HW, void *const image_planes[3], int64_t image_pitch,
+                        const float *w, int64_t C_out, int taps, int c_pad, void *const w_planes[3], int64_t w_pitch,
+                        int sm_count, cudaStream_t st)
 {
-    PlanePtrs pl;
-    for (int i = 0; i < 3; ++i) pl.p[i] = planes[i];
-    const int g = grid_for(C_out * taps * (c_pad / 2), 256, sm_count);
+    // the image [C_in][HW] is a k-outermost operand: the transposing body writes it channel-innermost
+    const SplitTask ta = make_task(image, HW, C_in, HW, true, image_planes, image_pitch, 0, 0, sm_count);
+    SplitTask tb = make_task(w, C_out, (int64_t)taps * c_pad, 0, false, w_planes, w_pitch, 0, 0, sm_count);
+    tb.conv_taps = taps; tb.conv_cin = (int)C_in; tb.conv_cpad = c_pad;
+    tb.blocks = grid_for(C_out * taps * (c_pad / 2), 256, sm_count);
+    const int g = ta.blocks + tb.blocks;
     switch (mode) {
-    case SPLIT_TF32X2: split_conv_weight_kernel<SPLIT_TF32X2><<<g, 256, 0, st>>>(w, C_out, (int)C_in, taps, c_pad, pl, pitch); break;
-    case SPLIT_BF16X1: split_conv_weight_kernel<SPLIT_BF16X1><<<g, 256, 0, st>>>(w, C_out, (int)C_in, taps, c_pad, pl, pitch); break;
-    case SPLIT_BF16X2: split_conv_weight_kernel<SPLIT_BF16X2><<<g, 256, 0, st>>>(w, C_out, (int)C_in, taps, c_pad, pl, pitch); break;
-    default: split_conv_weight_kernel<SPLIT_BF16X3><<<g, 256, 0, st>>>(w, C_out, (int)C_in, taps, c_pad, pl, pitch); break;
+    case SPLIT_TF32X2: split_pair_kernel<SPLIT_TF32X2><<<g, 256, 0, st>>>(ta, tb); break;
+    case SPLIT_BF16X1: split_pair_kernel<SPLIT_BF16X1><<<g, 256, 0, st>>>(ta, tb); break;
+    case SPLIT_BF16X2: split_pair_kernel<SPLIT_BF16X2><<<g, 256, 0, st>>>(ta, tb); break;
+    default: split_pair_kernel<SPLIT_BF16X3><<<g, 256, 0, st>>>(ta, tb); break;
     }
     return (int)cudaGetLastError();
 }

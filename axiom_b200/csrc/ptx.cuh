@@ -57,6 +57,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return done != 0;
 }
 
+// Non-blocking test (try_wait may suspend the thread for a while; a thread that polls several barriers in turn
+// must not).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t done;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
 // Wait with a wall-clock limit.  Every spin in these kernels goes through
 // here: when the limit passes the caller records an error word and unwinds
 // instead of spinning for ever on a barrier nobody will complete.

@@ -23,12 +23,19 @@
 // layout an MN-major tf32 operand may have): nothing is transposed.  Every block's product lands in a fresh
 // accumulator and is added to the row's fp32 registers by its thread, so the tensor core's truncating accumulation
 // never spans more than one block.
-//   warp 4    TMA producer (the fixed tiles once; per block T1/T2 as soon as their MMAs have retired, T3 after its own)
-//   warps 6-9 converters: lo = tf32(x - trunc(x)) of every tile, in place behind the hi plane
+//   warp 4    TMA producer: one thread runs two independent chains — T1/T2 of block b+2 as soon as the score MMAs of
+//             block b have retired (two buffers), T3 of block b+1 as soon as the output product of block b has
+//   warps 6-9 converters: lo = tf32(x - trunc(x)).  Stream tiles: in place behind the hi plane.  Fixed tiles: into
+//             TENSOR MEMORY (thread = row), where the lo.hi product reads them as its A operand (TS form) — that
+//             frees the 64 KB of shared memory the second T1/T2 buffer needs
 //   warp 5    one thread issues the MMAs: scores of block b+1 go ahead of the output product of block b (two score
 //             buffers), so the pipe works on the next block while the row threads turn this one into dS
 //   warps 0-3 thread t owns row t of the fixed side
-// The 64-row stream (not 128) is what fits: five operand tiles with their lo planes are 224 KB at head dim 64.
+// In-kernel time stamps of the single-buffered first version showed one serial cycle per block — load T1/T2, split,
+// issue the scores, issue the output product, only then the next load — of 7.8 k cycles against 4.2 k of MMA issue;
+// with the loads a block ahead the cycle is the MMA issue.
+// The 64-row stream (not 128) is what fits: 64 KB fixed, 2 x 64 KB of T1/T2 and 32 KB of T3 are 224 KB at head dim 64;
+// all 512 tensor-memory columns are in use (one CTA per SM, by shared memory).
 #include "sdpa.cuh"
 
 #include "errors.cuh"
@@ -68,12 +75,13 @@ struct BwdTcArgs {
 enum { BERR_PRODUCER = 21, BERR_MMA = 22, BERR_ROWS = 23, BERR_CONVERT = 24 };
 
 enum {
-    B_F_RAW = 0, B_F_FULL, B_T12_RAW, B_T12_FULL, B_T12_EMPTY, B_T3_RAW, B_T3_FULL, B_T3_EMPTY,
-    B_S_FULL = 8, B_DS_FULL = 10, B_ACC_FULL = 12, B_ACC_EMPTY = 14, B_COUNT = 16
+    B_F_RAW = 0, B_F_FULL = 1, B_T12_RAW = 2, B_T12_FULL = 4, B_T12_EMPTY = 6, B_T3_RAW = 8, B_T3_FULL = 9, B_T3_EMPTY = 10,
+    B_S_FULL = 12, B_DS_FULL = 14, B_ACC_FULL = 16, B_ACC_EMPTY = 18, B_COUNT = 20
 };
 
-// tensor-memory columns: two score buffers of 128 (S at +0 -> dS hi, dP at +64 -> dS lo), two output accumulators
-enum { T_SC = 0, T_ACC = 256, T_COLS = 512 };
+// tensor-memory columns: two score buffers of 128 (S at +0 -> dS hi, dP at +64 -> dS lo), two output accumulators,
+// and the lo planes of the two fixed tiles (row = lane, k = column)
+enum { T_SC = 0, T_ACC = 256, T_FLO = 384, T_COLS = 512 };
 
 __device__ __forceinline__ void bt_report(int *err, int code)
 {
@@ -92,8 +100,9 @@ __global__ void __launch_bounds__(BT_THREADS, 1) sdpa_bwd_tc_kernel(const __grid
 {
     constexpr bool HAS2 = ROLE != ROLE_DV;                 // the second score product (dP) and its operands exist
     constexpr int NF = HAS2 ? 2 : 1;                       // fixed tiles
-    constexpr uint32_t PLANE_F = NSLAB * SLAB_F, TILE_F = 2 * PLANE_F;
+    constexpr uint32_t PLANE_F = NSLAB * SLAB_F;                     // fixed tiles: the hi plane only (lo in tensor memory)
     constexpr uint32_t PLANE_T = NSLAB * SLAB_T, TILE_T = 2 * PLANE_T;
+    constexpr uint32_t T12_BYTES = (HAS2 ? 2 : 1) * TILE_T;           // one buffer of the T1 (and T2) tiles
     constexpr int OW = 32 * NSLAB;                         // accumulator columns in use
 
     extern __shared__ uint8_t smem_raw[];
@@ -104,10 +113,9 @@ __global__ void __launch_bounds__(BT_THREADS, 1) sdpa_bwd_tc_kernel(const __grid
     float *col_L = reinterpret_cast<float *>(base_ptr + 512);    // [2][64]: the stream rows' L (in the base-2 domain)
     float *col_D = col_L + 128;                                  // [2][64]: ... and D
     const uint32_t f1_smem = base + BT_HEADER;
-    const uint32_t f2_smem = f1_smem + TILE_F;
-    const uint32_t t1_smem = f1_smem + NF * TILE_F;
-    const uint32_t t2_smem = t1_smem + TILE_T;
-    const uint32_t t3_smem = t1_smem + (HAS2 ? 2 : 1) * TILE_T;
+    const uint32_t f2_smem = f1_smem + PLANE_F;
+    const uint32_t t12_smem = f1_smem + NF * PLANE_F;               // [2 buffers][T1, T2]
+    const uint32_t t3_smem = t12_smem + 2 * T12_BYTES;
     auto bar = [&](int i) -> uint32_t { return base + 8u * (uint32_t)i; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -128,11 +136,13 @@ __global__ void __launch_bounds__(BT_THREADS, 1) sdpa_bwd_tc_kernel(const __grid
     if (threadIdx.x == 0) {
         mbar_init(bar(B_F_RAW), 1);
         mbar_init(bar(B_F_FULL), 128);
-        mbar_init(bar(B_T12_RAW), 1);
-        mbar_init(bar(B_T12_FULL), 128);
-        mbar_init(bar(B_T12_EMPTY), 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar(B_T12_RAW + b), 1);
+            mbar_init(bar(B_T12_FULL + b), 64);
+            mbar_init(bar(B_T12_EMPTY + b), 1);
+        }
         mbar_init(bar(B_T3_RAW), 1);
-        mbar_init(bar(B_T3_FULL), 128);
+        mbar_init(bar(B_T3_FULL), 64);
         mbar_init(bar(B_T3_EMPTY), 1);
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar(B_S_FULL + b), 1);
@@ -167,28 +177,41 @@ __global__ void __launch_bounds__(BT_THREADS, 1) sdpa_bwd_tc_kernel(const __grid
                 tma_load_3d(f1_smem + sl * SLAB_F, &tm.f1, bar(B_F_RAW), 32 * sl, f0, head);
                 if (HAS2) tma_load_3d(f2_smem + sl * SLAB_F, &tm.f2, bar(B_F_RAW), 32 * sl, f0, head);
             }
+            // Two chains, polled in turn so that neither waits behind the other: T1/T2 of block n12 go into buffer
+            // n12 % 2 once the scores of block n12 - 2 have retired; T3 of block n3 once the output product of block
+            // n3 - 1 has.  A chain completes every phase of its barrier before the next can begin, so the parities
+            // cannot alias.
             bool ok = true;
-            for (int bi = 0; bi < nb; ++bi) {
-                const int r0 = (b_lo + bi) * BT_T;
-                if (bi >= 1 && !mbar_wait_bounded(bar(B_T12_EMPTY), (bi - 1) & 1)) { ok = false; break; }
-                mbar_arrive_expect_tx(bar(B_T12_RAW), (HAS2 ? 2 : 1) * PLANE_T);
-#pragma unroll
-                for (int sl = 0; sl < NSLAB; ++sl) {
-                    tma_load_3d(t1_smem + sl * SLAB_T, &tm.t1, bar(B_T12_RAW), 32 * sl, r0, head);
-                    if (HAS2) tma_load_3d(t2_smem + sl * SLAB_T, &tm.t2, bar(B_T12_RAW), 32 * sl, r0, head);
-                }
-                if (bi >= 1 && !mbar_wait_bounded(bar(B_T3_EMPTY), (bi - 1) & 1)) { ok = false; break; }
-                mbar_arrive_expect_tx(bar(B_T3_RAW), PLANE_T);
-#pragma unroll
-                for (int sl = 0; sl < NSLAB; ++sl) tma_load_3d(t3_smem + sl * SLAB_T, &tm.t3, bar(B_T3_RAW), 32 * sl, r0, head);
-                if (bi + 1 < nb) {   // the next block: into L2 now, so its loads are short when their turn comes
+            int n12 = 0, n3 = 0;
+            uint64_t t_idle = global_timer_ns();
+            while (ok && (n12 < nb || n3 < nb)) {
+                bool moved = false;
+                if (n12 < nb && (n12 < 2 || mbar_test_wait(bar(B_T12_EMPTY + (n12 & 1)), ((n12 >> 1) - 1) & 1))) {
+                    const int r0 = (b_lo + n12) * BT_T, b = n12 & 1;
+                    const uint32_t t1 = t12_smem + b * T12_BYTES, t2 = t1 + TILE_T;
+                    mbar_arrive_expect_tx(bar(B_T12_RAW + b), (HAS2 ? 2 : 1) * PLANE_T);
 #pragma unroll
                     for (int sl = 0; sl < NSLAB; ++sl) {
-                        tma_prefetch_3d(&tm.t1, 32 * sl, r0 + BT_T, head);
-                        if (HAS2) tma_prefetch_3d(&tm.t2, 32 * sl, r0 + BT_T, head);
-                        if (ROLE == ROLE_DV) tma_prefetch_3d(&tm.t3, 32 * sl, r0 + BT_T, head);   // (DQ/DK: T3 is T1's data)
+                        tma_load_3d(t1 + sl * SLAB_T, &tm.t1, bar(B_T12_RAW + b), 32 * sl, r0, head);
+                        if (HAS2) tma_load_3d(t2 + sl * SLAB_T, &tm.t2, bar(B_T12_RAW + b), 32 * sl, r0, head);
                     }
+                    ++n12;
+                    moved = true;
                 }
+                if (n3 < nb && (n3 < 1 || mbar_test_wait(bar(B_T3_EMPTY), (n3 - 1) & 1))) {
+                    const int r0 = (b_lo + n3) * BT_T;
+                    mbar_arrive_expect_tx(bar(B_T3_RAW), PLANE_T);
+#pragma unroll
+                    for (int sl = 0; sl < NSLAB; ++sl) tma_load_3d(t3_smem + sl * SLAB_T, &tm.t3, bar(B_T3_RAW), 32 * sl, r0, head);
+                    if (ROLE == ROLE_DV && n3 + 1 < nb) {   // the next block into L2 now (DQ / DK: T3 is T1's data, loaded a block ahead)
+#pragma unroll
+                        for (int sl = 0; sl < NSLAB; ++sl) tma_prefetch_3d(&tm.t3, 32 * sl, r0 + BT_T, head);
+                    }
+                    ++n3;
+                    moved = true;
+                }
+                if (moved) t_idle = global_timer_ns();
+                else if (global_timer_ns() - t_idle > AXB_WAIT_LIMIT_NS) ok = false;
             }
             if (!ok) bt_report(a.err, BERR_PRODUCER);
         }
@@ -196,10 +219,14 @@ __global__ void __launch_bounds__(BT_THREADS, 1) sdpa_bwd_tc_kernel(const __grid
         // ---------------------------------------------------------- converters
         // lo = tf32(x - (x cut to tf32)) at the same offset of the lo plane; x itself stays where TMA put it and is
         // the hi operand
-        const int ct = threadIdx.x - 192;  // 0..127
+        // After the fixed tiles the four warps part: warps 6-7 split every T1/T2 buffer as it lands, warps 8-9 every T3
+        // — T3 of a block arrives a block later than T1/T2 of the next one, and one group walking both in order
+        // would hold the early tile behind the late one.
+        const int grp = (warp - 6) >> 1;
+        const int ct = threadIdx.x - 192 - grp * 64;  // 0..63 inside the group
         auto split_tile = [&](uint32_t tile, uint32_t plane) {
 #pragma unroll 4
-            for (int i = ct; i < (int)(plane / 16); i += 128) {
+            for (int i = ct; i < (int)(plane / 16); i += 64) {
                 const uint32_t addr = tile + (uint32_t)i * 16u;
                 uint32_t x0, x1, x2, x3;
                 asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(addr));
@@ -211,20 +238,54 @@ __global__ void __launch_bounds__(BT_THREADS, 1) sdpa_bwd_tc_kernel(const __grid
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> visible to the MMA
         };
+        // a fixed tile's lo plane goes to tensor memory: this thread's row (the lane quarter a warp may address is
+        // warp % 4), 32 columns per slab, read through the 128-byte swizzle TMA wrote the tile with
+        // (hi_cols >= 0: the raw values go to tensor memory as well — the role with one fixed tile has the columns to
+        // spare, and then none of its score products reads the fixed tile from shared memory)
+        auto split_fixed = [&](uint32_t tile, uint32_t t_cols, int hi_cols) {
+            const int r = (warp & 3) * 32 + lane;
+            const uint32_t taddr = tmem + ((uint32_t)((warp & 3) * 32) << 16) + t_cols;
+#pragma unroll
+            for (int sl = 0; sl < NSLAB; ++sl) {
+                uint32_t v[32], h[32];
+#pragma unroll
+                for (int c4 = 0; c4 < 8; ++c4) {
+                    const uint32_t addr = tile + sl * SLAB_F + (uint32_t)r * 128u + (uint32_t)((c4 ^ (r & 7)) << 4);
+                    uint32_t x0, x1, x2, x3;
+                    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(x0), "=r"(x1), "=r"(x2), "=r"(x3) : "r"(addr));
+                    h[4 * c4 + 0] = x0; h[4 * c4 + 1] = x1; h[4 * c4 + 2] = x2; h[4 * c4 + 3] = x3;
+                    v[4 * c4 + 0] = (__float_as_uint(__uint_as_float(x0) - __uint_as_float(x0 & 0xFFFFE000u)) + 0x1000u) & 0xFFFFE000u;
+                    v[4 * c4 + 1] = (__float_as_uint(__uint_as_float(x1) - __uint_as_float(x1 & 0xFFFFE000u)) + 0x1000u) & 0xFFFFE000u;
+                    v[4 * c4 + 2] = (__float_as_uint(__uint_as_float(x2) - __uint_as_float(x2 & 0xFFFFE000u)) + 0x1000u) & 0xFFFFE000u;
+                    v[4 * c4 + 3] = (__float_as_uint(__uint_as_float(x3) - __uint_as_float(x3 & 0xFFFFE000u)) + 0x1000u) & 0xFFFFE000u;
+                }
+                tmem_st_32x32(taddr + 32 * sl, v);
+                if (hi_cols >= 0) tmem_st_32x32(taddr - t_cols + (uint32_t)hi_cols + 32 * sl, h);
+            }
+        };
         bool ok = nb > 0 && bt_wait_warp(bar(B_F_RAW), 0);
         if (ok) {
-            split_tile(f1_smem, PLANE_F);
-            if (HAS2) split_tile(f2_smem, PLANE_F);
+            split_fixed(f1_smem, T_FLO, HAS2 ? -1 : T_FLO + 64);
+            if (HAS2) split_fixed(f2_smem, T_FLO + 64, -1);
+            tmem_st_wait();
+            tc_fence_before_sync();
             mbar_arrive(bar(B_F_FULL));
         }
-        for (int bi = 0; ok && bi < nb; ++bi) {
-            if (!bt_wait_warp(bar(B_T12_RAW), bi & 1)) { ok = false; break; }
-            split_tile(t1_smem, PLANE_T);
-            if (HAS2) split_tile(t2_smem, PLANE_T);
-            mbar_arrive(bar(B_T12_FULL));
-            if (!bt_wait_warp(bar(B_T3_RAW), bi & 1)) { ok = false; break; }
-            split_tile(t3_smem, PLANE_T);
-            mbar_arrive(bar(B_T3_FULL));
+        if (grp == 0) {
+            for (int bi = 0; ok && bi < nb; ++bi) {
+                const int b = bi & 1;
+                const uint32_t t1 = t12_smem + b * T12_BYTES;
+                if (!bt_wait_warp(bar(B_T12_RAW + b), (bi >> 1) & 1)) { ok = false; break; }
+                split_tile(t1, PLANE_T);
+                if (HAS2) split_tile(t1 + TILE_T, PLANE_T);
+                mbar_arrive(bar(B_T12_FULL + b));
+            }
+        } else {
+            for (int bi = 0; ok && bi < nb; ++bi) {
+                if (!bt_wait_warp(bar(B_T3_RAW), bi & 1)) { ok = false; break; }
+                split_tile(t3_smem, PLANE_T);
+                mbar_arrive(bar(B_T3_FULL));
+            }
         }
         if (!ok && nb > 0) bt_report(a.err, BERR_CONVERT);
     } else if (warp == 5) {
@@ -236,18 +297,28 @@ __global__ void __launch_bounds__(BT_THREADS, 1) sdpa_bwd_tc_kernel(const __grid
             const uint32_t idesc_out = make_idesc<KIND_TF32>(BT_F, a.n_out) | (1u << 16);  // B is MN-major
             const int ksteps = a.ksteps;
 
-            // D[128 x 64] = F . T^T, both K-major in shared memory, three products
-            auto issue_scores = [&](uint32_t d, uint32_t f_smem, uint32_t t_smem) {
+            // D[128 x 64] = F . T^T, three products: lo.hi with F's lo plane from tensor memory (TS form), then hi.lo
+            // and hi.hi with both operands K-major in shared memory
+            // (!HAS2: the hi plane of the fixed tile is in tensor memory too, at f_lo + 64)
+            auto issue_scores = [&](uint32_t d, uint32_t f_smem, uint32_t f_lo, uint32_t t_smem) {
                 uint32_t acc = 0;
 #pragma unroll
-                for (int pr = 0; pr < 3; ++pr) {
-                    const uint32_t fa = f_smem + (pr == 0 ? PLANE_F : 0);   // lo.hi, hi.lo, hi.hi
+                for (int ks = 0; ks < 4 * NSLAB; ++ks) {
+                    if (ks < ksteps) {
+                        tc_mma_ts_tf32(d, f_lo + ks * 8,
+                                       desc_k | (uint64_t)(((t_smem + (ks >> 2) * SLAB_T + (ks & 3) * 32) & 0x3FFFFu) >> 4), idesc_sc, acc);
+                        acc = 1;
+                    }
+                }
+#pragma unroll
+                for (int pr = 1; pr < 3; ++pr) {
                     const uint32_t tb = t_smem + (pr == 1 ? PLANE_T : 0);
 #pragma unroll
                     for (int ks = 0; ks < 4 * NSLAB; ++ks) {
                         if (ks < ksteps) {
-                            tc_mma<KIND_TF32>(d, desc_k | (uint64_t)(((fa + (ks >> 2) * SLAB_F + (ks & 3) * 32) & 0x3FFFFu) >> 4),
-                                              desc_k | (uint64_t)(((tb + (ks >> 2) * SLAB_T + (ks & 3) * 32) & 0x3FFFFu) >> 4), idesc_sc, acc);
+                            const uint64_t db = desc_k | (uint64_t)(((tb + (ks >> 2) * SLAB_T + (ks & 3) * 32) & 0x3FFFFu) >> 4);
+                            if (HAS2) tc_mma<KIND_TF32>(d, desc_k | (uint64_t)(((f_smem + (ks >> 2) * SLAB_F + (ks & 3) * 32) & 0x3FFFFu) >> 4), db, idesc_sc, acc);
+                            else tc_mma_ts_tf32(d, f_lo + 64 + ks * 8, db, idesc_sc, acc);
                             acc = 1;
                         }
                     }
@@ -256,10 +327,11 @@ __global__ void __launch_bounds__(BT_THREADS, 1) sdpa_bwd_tc_kernel(const __grid
             auto issue_block_scores = [&](int bi) {
                 const int b = bi & 1;
                 const uint32_t d = tmem + T_SC + b * 128;
-                issue_scores(d, f1_smem, t1_smem);
-                if (HAS2) issue_scores(d + 64, f2_smem, t2_smem);
+                const uint32_t t1 = t12_smem + b * T12_BYTES;
+                issue_scores(d, f1_smem, tmem + T_FLO, t1);
+                if (HAS2) issue_scores(d + 64, f2_smem, tmem + T_FLO + 64, t1 + TILE_T);
                 tc_commit(bar(B_S_FULL + b));
-                tc_commit(bar(B_T12_EMPTY));
+                tc_commit(bar(B_T12_EMPTY + b));
             };
             auto issue_out = [&](int bi) {
                 const int b = bi & 1;
@@ -279,7 +351,7 @@ __global__ void __launch_bounds__(BT_THREADS, 1) sdpa_bwd_tc_kernel(const __grid
                 tc_commit(bar(B_ACC_FULL + b));
                 tc_commit(bar(B_T3_EMPTY));
             };
-            bool ok = mbar_wait_bounded(bar(B_F_FULL), 0) && mbar_wait_bounded(bar(B_T12_FULL), 0);
+            bool ok = mbar_wait_bounded(bar(B_F_FULL), 0) && mbar_wait_bounded(bar(B_T12_FULL + 0), 0);
             if (ok) {
                 tc_fence_after_sync();
                 issue_block_scores(0);
@@ -288,7 +360,7 @@ __global__ void __launch_bounds__(BT_THREADS, 1) sdpa_bwd_tc_kernel(const __grid
                 if (bi + 1 < nb) {
                     // the score buffer of block bi+1 held dS of block bi-1: its output product was issued before this
                     // point and MMAs execute in order, so nothing else has to be waited for
-                    ok = mbar_wait_bounded(bar(B_T12_FULL), (bi + 1) & 1);
+                    ok = mbar_wait_bounded(bar(B_T12_FULL + ((bi + 1) & 1)), ((bi + 1) >> 1) & 1);
                     if (!ok) break;
                     tc_fence_after_sync();
                     issue_block_scores(bi + 1);
@@ -434,8 +506,8 @@ bool sdpa_bwd_tc_applicable(const float *Q, const float *K, const float *V, cons
 template <int ROLE, int NSLAB>
 static int launch_role(const BwdTmaps &tm, const BwdTcArgs &a, dim3 grid, cudaStream_t st)
 {
-    constexpr int NF = ROLE != ROLE_DV ? 2 : 1, NT = ROLE != ROLE_DV ? 3 : 2;
-    const size_t smem = BT_HEADER + (size_t)NF * 2 * NSLAB * SLAB_F + (size_t)NT * 2 * NSLAB * SLAB_T + 1024;   // 227 KB at most
+    constexpr int NF = ROLE != ROLE_DV ? 2 : 1, NT = ROLE != ROLE_DV ? 5 : 3;   // hi planes of the fixed tiles; T1(,T2) twice and T3
+    const size_t smem = BT_HEADER + (size_t)NF * NSLAB * SLAB_F + (size_t)NT * 2 * NSLAB * SLAB_T + 1024;   // 227 KB at most
     auto kern = sdpa_bwd_tc_kernel<ROLE, NSLAB>;
     static PerDeviceOnce once;
     if (once.first()) {
