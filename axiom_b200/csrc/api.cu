@@ -1189,11 +1189,13 @@ extern "C" int axb_sdpa_bwd(const float *Q, const float *K, const float *V, cons
 
 // ---------------------------------------------------------------- convolution
 
-extern "C" int axb_conv_gemm(const float *weight, const float *input, int64_t C_out, int64_t C_in, int64_t H, int64_t W,
-                             int kh, int kw, int sh, int sw, int ph, int pw, int64_t out_h, int64_t out_w, float *out)
+// `batch` samples [C_in, H, W] back to back -> out [batch][C_out][out_h * out_w]
+static int conv_gemm_any(const float *weight, const float *input, int64_t batch, int64_t C_out, int64_t C_in, int64_t H, int64_t W,
+                         int kh, int kw, int sh, int sw, int ph, int pw, int64_t out_h, int64_t out_w, float *out)
 {
+    if (batch == 0) return AXB_OK;   // nothing to read or write (the pointers of an empty batch may be NULL)
     if (!weight || !input || !out) return fail(AXB_ERR_NULL_ARG, "conv_gemm: NULL");
-    if (C_out <= 0 || C_in <= 0 || H <= 0 || W <= 0 || kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0 || ph < 0 || pw < 0 ||
+    if (batch < 0 || C_out <= 0 || C_in <= 0 || H <= 0 || W <= 0 || kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0 || ph < 0 || pw < 0 ||
         out_h < 0 || out_w < 0)
         return fail(AXB_ERR_INVALID_SHAPE, "conv_gemm: bad geometry");
     const int64_t K = C_in * kh * kw, P = out_h * out_w;
@@ -1208,13 +1210,14 @@ extern "C" int axb_conv_gemm(const float *weight, const float *input, int64_t C_
     fp32_mode_plan(split_mode, kind, prod);
     TcConv cv;
     cv.C = C_in; cv.H = H; cv.W = W; cv.kh = kh; cv.kw = kw; cv.pad_h = ph; cv.pad_w = pw; cv.out_h = out_h; cv.out_w = out_w;
-    if (gemm_tc_conv_applicable(cv, sh, sw, out) && H * W <= INT32_MAX) {
+    cv.batch = batch;
+    if (gemm_tc_conv_applicable(cv, sh, sw, out) && batch * H * W <= INT32_MAX) {
         // Stride 1: implicit GEMM.  The image is transposed once into channel-innermost planes (the same pre-pass
         // that transposes a [K, N] operand), the filter into [C_out][tap][channel] planes, and the GEMM's producer
         // reads shifted windows of the image planes — the patch matrix, kh * kw times the image, never exists.
         const int cpad = gemm_tc_conv_channel_pad(kind);
         const int64_t c_pad = (C_in + cpad - 1) / cpad * cpad, taps = (int64_t)kh * kw;
-        const SplitOperand si = plan_split(split_mode, H * W, C_in), sw_ = plan_split(split_mode, C_out, taps * c_pad);
+        const SplitOperand si = plan_split(split_mode, batch * H * W, C_in), sw_ = plan_split(split_mode, C_out, taps * c_pad);
         st = ensure_ws(si.total() + sw_.total() + kSplitScratch);
         if (st) return st;
         Carver carve{ (char *)cur().ws };
@@ -1225,11 +1228,11 @@ extern "C" int axb_conv_gemm(const float *weight, const float *input, int64_t C_
         opi.nplanes = opw.nplanes = split_num_planes(split_mode);
         for (int i = 0; i < opi.nplanes; ++i) opi.plane[i] = ip[i] = carve.take(si.plane_bytes);
         for (int i = 0; i < opw.nplanes; ++i) opw.plane[i] = wp[i] = carve.take(sw_.plane_bytes);
-        opi.rows = H * W;
+        opi.rows = batch * H * W;
         opi.pitch_elems = si.pitch;
         opw.rows = C_out;
         opw.pitch_elems = sw_.pitch;
-        int e = split_conv_operands(split_mode, input, C_in, H * W, ip, si.pitch, weight, C_out, (int)taps, (int)c_pad, wp, sw_.pitch,
+        int e = split_conv_operands(split_mode, input, batch, C_in, H * W, ip, si.pitch, weight, C_out, (int)taps, (int)c_pad, wp, sw_.pitch,
                                     cur().sm_count, cur().stream);
         cur().launches++;
         if (e) return cuda_fail("conv_gemm: operand planes", e);
@@ -1241,6 +1244,15 @@ extern "C" int axb_conv_gemm(const float *weight, const float *input, int64_t C_
         mark(2);
         cur().launches++;
         return e ? cuda_fail("conv_gemm", e) : AXB_OK;
+    }
+    if (batch > 1) {
+        // the gathered form (strided layers, output widths that are not a multiple of 4) takes the samples one by one
+        for (int64_t n = 0; n < batch; ++n) {
+            st = conv_gemm_any(weight, input + n * C_in * H * W, 1, C_out, C_in, H, W, kh, kw, sh, sw, ph, pw, out_h, out_w,
+                               out + n * C_out * P);
+            if (st) return st;
+        }
+        return AXB_OK;
     }
     const SplitOperand sa = plan_split(split_mode, C_out, K), sb = plan_split(split_mode, P, K);
     st = ensure_ws(sa.total() + sb.total() + kSplitScratch);
@@ -1270,6 +1282,19 @@ extern "C" int axb_conv_gemm(const float *weight, const float *input, int64_t C_
     mark(2);
     cur().launches++;
     return e ? cuda_fail("conv_gemm", e) : AXB_OK;
+}
+
+extern "C" int axb_conv_gemm(const float *weight, const float *input, int64_t C_out, int64_t C_in, int64_t H, int64_t W,
+                             int kh, int kw, int sh, int sw, int ph, int pw, int64_t out_h, int64_t out_w, float *out)
+{
+    return conv_gemm_any(weight, input, 1, C_out, C_in, H, W, kh, kw, sh, sw, ph, pw, out_h, out_w, out);
+}
+
+extern "C" int axb_conv_gemm_batched(const float *weight, const float *input, int64_t batch, int64_t C_out, int64_t C_in, int64_t H,
+                                     int64_t W, int kh, int kw, int sh, int sw, int ph, int pw, int64_t out_h, int64_t out_w,
+                                     float *out)
+{
+    return conv_gemm_any(weight, input, batch, C_out, C_in, H, W, kh, kw, sh, sw, ph, pw, out_h, out_w, out);
 }
 
 // ------------------------------------------------------------------ KV cache

@@ -113,11 +113,13 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
                     const int t = w / ksplit, kb_lo = (w - t * ksplit) * p.kb_per_slice, kb_hi = min(k_blocks, kb_lo + p.kb_per_slice);
                     int mt, nt;
                     tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
-                    int x0[NPATCH], y0[NPATCH];
+                    int x0[NPATCH], y0[NPATCH], n0[NPATCH];
 #pragma unroll
                     for (int q = 0; q < NPATCH; ++q) {
-                        const int patch = nt * NPATCH + q, py = patch / p.cv_px;
-                        x0[q] = (patch - py * p.cv_px) * pw - p.cv_pad_w;
+                        // (a patch past the last one reads sample `batch`: outside the tensor, all zeros)
+                        const int patch = nt * NPATCH + q, n = patch / p.cv_npatch_s, rem = patch - n * p.cv_npatch_s, py = rem / p.cv_px;
+                        n0[q] = n;
+                        x0[q] = (rem - py * p.cv_px) * pw - p.cv_pad_w;
                         y0[q] = py * phh - p.cv_pad_h;
                     }
                     int tap = kb_lo / cblocks, cb = kb_lo - tap * cblocks;
@@ -133,7 +135,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
                         for (int i = 0; i < npb; ++i)
 #pragma unroll
                             for (int q = 0; q < NPATCH; ++q, dst += PATCH_BYTES)
-                                tma_load_3d(dst, &tm.b[i], fb, cb * BKE, x0[q] + kx, y0[q] + ky);
+                                tma_load_4d(dst, &tm.b[i], fb, cb * BKE, x0[q] + kx, y0[q] + ky, n0[q]);
                         if (++cb == cblocks) {
                             cb = 0;
                             if (++kx == kw) {
@@ -542,9 +544,10 @@ static int encode_f32_store_tmap(CUtensorMap *out, float *ptr, int64_t rows, int
     return 0;
 }
 
-// Image planes [H][W][pitch] (C valid channels per pixel) as the B operand of an implicit convolution:
-// box = swb bytes of channels x patch_w x patch_h pixels, swizzled like a K-major tile of patch_w * patch_h rows.
-static int encode_conv_image_tmap(CUtensorMap *out, int kind, const void *ptr, int64_t C, int64_t H, int64_t W,
+// Image planes [batch][H][W][pitch] (C valid channels per pixel) as the B operand of an implicit convolution:
+// box = swb bytes of channels x patch_w x patch_h pixels of one sample, swizzled like a K-major tile of
+// patch_w * patch_h rows.
+static int encode_conv_image_tmap(CUtensorMap *out, int kind, const void *ptr, int64_t batch, int64_t C, int64_t H, int64_t W,
                                   int64_t pitch_elems, int swb, int patch_w, int patch_h)
 {
     EncodeTiledFn fn = encode_fn();
@@ -556,16 +559,17 @@ static int encode_conv_image_tmap(CUtensorMap *out, int kind, const void *ptr, i
     const CUtensorMapDataType dt = kind == KIND_TF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                  : kind == KIND_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
                                                      : CU_TENSOR_MAP_DATA_TYPE_UINT8;
-    cuuint64_t dims[3] = { (cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H };
-    cuuint64_t strides[2] = { (cuuint64_t)pitch_elems * es, (cuuint64_t)W * (cuuint64_t)pitch_elems * es };
-    cuuint32_t box[3] = { (cuuint32_t)(swb / es), (cuuint32_t)patch_w, (cuuint32_t)patch_h };
-    cuuint32_t estr[3] = { 1, 1, 1 };
-    CUresult r = fn(out, dt, 3, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    cuuint64_t dims[4] = { (cuuint64_t)C, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)batch };
+    cuuint64_t strides[3] = { (cuuint64_t)pitch_elems * es, (cuuint64_t)W * (cuuint64_t)pitch_elems * es,
+                              (cuuint64_t)H * (cuuint64_t)W * (cuuint64_t)pitch_elems * es };
+    cuuint32_t box[4] = { (cuuint32_t)(swb / es), (cuuint32_t)patch_w, (cuuint32_t)patch_h, 1 };
+    cuuint32_t estr[4] = { 1, 1, 1, 1 };
+    CUresult r = fn(out, dt, 4, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     swb == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
-        snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled (image planes) failed (%d): ptr=%p C=%lld H=%lld W=%lld pitch=%lld box=%ux%ux%u",
-                 (int)r, ptr, (long long)C, (long long)H, (long long)W, (long long)pitch_elems, box[0], box[1], box[2]);
+        snprintf(g_err, sizeof g_err, "cuTensorMapEncodeTiled (image planes) failed (%d): ptr=%p batch=%lld C=%lld H=%lld W=%lld pitch=%lld box=%ux%ux%u",
+                 (int)r, ptr, (long long)batch, (long long)C, (long long)H, (long long)W, (long long)pitch_elems, box[0], box[1], box[2]);
         return (int)cudaErrorInvalidValue;
     }
     return 0;
@@ -728,9 +732,13 @@ int gemm_tc_conv_channel_pad(int kind) { return kind == KIND_TF32 ? 32 : (kind =
 
 bool gemm_tc_conv_applicable(const TcConv &cv, int sh, int sw, const void *out)
 {
-    return sh == 1 && sw == 1 && cv.out_w % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && cv.out_h > 0 &&
-           cv.out_w > 0 && cv.H < (1 << 30) && cv.W < (1 << 30) && cv.out_h < (1 << 30) && cv.out_w < (1 << 30) &&
-           cv.kh * cv.kw < (1 << 20);
+    if (!(sh == 1 && sw == 1 && cv.out_w % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && cv.out_h > 0 &&
+          cv.out_w > 0 && cv.batch >= 1 && cv.H < (1 << 30) && cv.W < (1 << 30) && cv.out_h < (1 << 30) &&
+          cv.out_w < (1 << 30) && cv.kh * cv.kw < (1 << 20)))
+        return false;
+    // the GEMM's column count (64 per patch, samples back to back) must stay inside 31 bits
+    const int64_t patches = ((cv.out_w + 7) / 8) * ((cv.out_h + 1) / 2) * cv.batch;   // the most any patch shape needs
+    return patches < (1 << 24);
 }
 
 static int launch_common(int kind, const TcOperand &A, const TcOperand &B, const TcProducts &prod, int64_t M, int64_t N,
@@ -754,7 +762,7 @@ int launch_gemm_tc_conv(int kind, const TcOperand &A, const TcOperand &B_image, 
         return (int)cudaErrorInvalidValue;
     }
     const int pw = conv_patch_w(cv.out_h, cv.out_w), ph = 64 / pw;
-    const int64_t npatch = ((cv.out_w + pw - 1) / pw) * ((cv.out_h + ph - 1) / ph);
+    const int64_t npatch = ((cv.out_w + pw - 1) / pw) * ((cv.out_h + ph - 1) / ph) * cv.batch;
     const int cpad = gemm_tc_conv_channel_pad(kind);
     const int64_t c_pad = (cv.C + cpad - 1) / cpad * cpad;
     return launch_common(kind, A, B_image, prod, M, npatch * 64, (int64_t)cv.kh * cv.kw * c_pad, ep, err_word, sm_count,
@@ -784,7 +792,7 @@ static int launch_common(int kind, const TcOperand &A, const TcOperand &B, const
     }
     const int cv_pw = cv ? conv_patch_w(cv->out_h, cv->out_w) : 0;
     for (int i = 0; i < B.nplanes; ++i) {
-        int e = cv ? encode_conv_image_tmap(&tm.b[i], kind, B.plane[i], cv->C, cv->H, cv->W, B.pitch_elems, swb, cv_pw, 64 / cv_pw)
+        int e = cv ? encode_conv_image_tmap(&tm.b[i], kind, B.plane[i], cv->batch, cv->C, cv->H, cv->W, B.pitch_elems, swb, cv_pw, 64 / cv_pw)
                    : encode_plane(&tm.b[i], kind, B.plane[i], N, K, B.pitch_elems, use_pair ? bn / 2 : bn, swb);
         if (e) return e;
     }
@@ -826,6 +834,7 @@ static int launch_common(int kind, const TcOperand &A, const TcOperand &B, const
         ka.cv_pw = cv_pw;
         ka.cv_px = (int)((cv->out_w + cv_pw - 1) / cv_pw);
         ka.cv_npatch = (int)(N / 64);
+        ka.cv_npatch_s = (int)(N / 64 / cv->batch);
         ka.cv_pad_w = cv->pad_w;
         ka.cv_pad_h = cv->pad_h;
         // the output leaves through store_piece_f32_conv

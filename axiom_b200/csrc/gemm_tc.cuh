@@ -63,13 +63,14 @@ struct TcSplitK {
 // k = tap * c_pad + c (tap = ky * kw + kx) is image[oh + ky - pad_h][ow + kx - pad_w][c], zero outside the image
 // and for c >= C — each pipeline stage is one TMA box per 64-pixel patch at window-shifted coordinates, and the
 // zero fill of out-of-range coordinates IS the padding.  The A operand (the filter) is laid out to match:
-// [M][taps * c_pad] with c_pad = C rounded up to gemm_tc_conv_channel_pad(kind).  The output [M][out_h][out_w] is
+// [M][taps * c_pad] with c_pad = C rounded up to gemm_tc_conv_channel_pad(kind).  The output [batch][M][out_h][out_w] is
 // written in 16-byte groups that must not straddle pixel rows, so out_w % 4 == 0 and a 16-byte aligned base are
 // required (gemm_tc_conv_applicable).
 struct TcConv {
     int64_t C, H, W;       // image planes: C valid channels per pixel (B.pitch_elems apart)
     int kh, kw, pad_h, pad_w;
     int64_t out_h, out_w;
+    int64_t batch = 1;     // samples: image planes [batch][H][W][pitch], output [batch][M][out_h][out_w]
 };
 int gemm_tc_conv_channel_pad(int kind);
 bool gemm_tc_conv_applicable(const TcConv &cv, int sh, int sw, const void *out);

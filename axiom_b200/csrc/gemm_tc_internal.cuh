@@ -50,10 +50,11 @@ struct KernelArgs {
     int ksplit, kb_per_slice;
     void *sk_scratch;        // [tiles x CTAs per tile][ksplit][128 x BN] fp32 / s32
     int *sk_counters;        // [tiles x CTAs per tile], zero between launches
-    // implicit convolution (cv_taps > 0, see TcConv): the B maps are 3-D over the image planes with one box per
-    // 64-pixel patch (cv_pw x 64/cv_pw pixels); output column j of the GEMM is pixel j % 64 of patch j / 64, stored
-    // by store_piece_f32_conv (ldc = out_h * out_w)
-    int cv_taps, cv_kw, cv_cblocks, cv_pw, cv_px, cv_npatch, cv_pad_w, cv_pad_h, cv_out_w;
+    // implicit convolution (cv_taps > 0, see TcConv): the B maps are 4-D over the image planes [batch][H][W][C] with
+    // one box per 64-pixel patch (cv_pw x 64/cv_pw pixels of one sample); output column j of the GEMM is pixel j % 64
+    // of patch j / 64, patches numbered sample-major (cv_npatch_s per sample, cv_px per patch row), stored by
+    // store_piece_f32_conv (ldc = out_h * out_w, samples M * ldc apart)
+    int cv_taps, cv_kw, cv_cblocks, cv_pw, cv_px, cv_npatch, cv_npatch_s, cv_pad_w, cv_pad_h, cv_out_w;
 };
 
 // shared-memory header words used by the split-K hand-over (after the barriers and the TMEM slot)
@@ -205,16 +206,17 @@ static __device__ __forceinline__ void store_piece_f32_tma(const KernelArgs &p, 
 
 // The fp32 epilogue of an implicit convolution (alpha and activation only): the piece's 32 columns are 32 / cv_pw
 // pixel rows of cv_pw pixels of one patch, so each 16-byte group of the staging tile goes to its own place in
-// out[row][oh][ow] (ldc = out_h * out_w; out_w % 4 == 0 keeps every group inside one pixel row and
+// out[sample][row][oh][ow] (ldc = out_h * out_w; out_w % 4 == 0 keeps every group inside one pixel row and
 // 16-byte aligned).  Pixels past the right and bottom edges of the image are dropped.
 static __device__ __forceinline__ void store_piece_f32_conv(const KernelArgs &p, const float4 *stg, long long row0, int col0, int lane)
 {
-    const int patch = col0 >> 6, py = patch / p.cv_px, px = patch - py * p.cv_px;
+    const int patch = col0 >> 6;
     if (patch >= p.cv_npatch) return;
+    const int n = patch / p.cv_npatch_s, rem = patch - n * p.cv_npatch_s, py = rem / p.cv_px, px = rem - py * p.cv_px;
     const int ch = lane & 7, j = (col0 & 63) + ch * 4;            // pixel index inside the patch of this lane's group
     const int out_w = p.cv_out_w, oh = py * (64 / p.cv_pw) + j / p.cv_pw, ow = px * p.cv_pw + j % p.cv_pw;
     if (ow >= out_w || (long long)oh * out_w >= p.ldc) return;
-    float *dst0 = reinterpret_cast<float *>(p.C) + (long long)oh * out_w + ow;
+    float *dst0 = reinterpret_cast<float *>(p.C) + (long long)n * p.M * p.ldc + (long long)oh * out_w + ow;
 #pragma unroll 2
     for (int it = 0; it < 8; ++it) {
         const int r = it * 4 + (lane >> 3);

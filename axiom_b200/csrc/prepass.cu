@@ -132,13 +132,16 @@ __device__ __forceinline__ void split_rows_body(const float *__restrict__ in, in
 // in [k, rows] (rows contiguous, pitch ld) -> planes [rows, pitch] (k contiguous):
 // 64(k) x 32(rows) tiles through shared memory.
 template <int MODE>
-__device__ __forceinline__ void split_transpose_body(const float *__restrict__ in, int64_t rows, int64_t k, int64_t ld,
+__device__ __forceinline__ void split_transpose_body(const float *__restrict__ in0, int64_t rows, int64_t k, int64_t ld,
                                                      const PlanePtrs &pl, int64_t pitch, float (*tile)[33], int vblock,
-                                                     int vgrid)
+                                                     int vgrid, int64_t batch = 1)
 {
-    const int64_t tiles_r = (rows + 31) / 32, tiles_k = (k + 63) / 64;
+    // batch > 1: `batch` matrices [k, rows] k * ld apart; matrix b fills plane rows [b * rows, (b + 1) * rows)
+    const int64_t tiles_r = (rows + 31) / 32, tiles_k = (k + 63) / 64, per = tiles_r * tiles_k;
     const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
-    for (int64_t t = vblock; t < tiles_r * tiles_k; t += vgrid) {
+    for (int64_t tt = vblock; tt < per * batch; tt += vgrid) {
+        const int64_t b = tt / per, t = tt - b * per;
+        const float *in = in0 + b * k * ld;
         const int64_t tr = t % tiles_r, tk = t / tiles_r;
         const int64_t r0 = tr * 32, k0 = tk * 64;
 #pragma unroll
@@ -155,8 +158,9 @@ __device__ __forceinline__ void split_transpose_body(const float *__restrict__ i
             const int64_t gr = r0 + rr;
             if (gr < rows) {
                 const int kk = 2 * tx;
-                if (k0 + kk + 1 < k) store2<MODE>(pl.p, gr * pitch + k0 + kk, tile[kk][rr], tile[kk + 1][rr]);
-                else if (k0 + kk < k) store1<MODE>(pl.p, gr * pitch + k0 + kk, tile[kk][rr]);
+                const int64_t o = (b * rows + gr) * pitch + k0 + kk;
+                if (k0 + kk + 1 < k) store2<MODE>(pl.p, o, tile[kk][rr], tile[kk + 1][rr]);
+                else if (k0 + kk < k) store1<MODE>(pl.p, o, tile[kk][rr]);
             }
         }
         __syncthreads();
@@ -208,6 +212,7 @@ struct SplitTask {
     PlanePtrs pl;
     int transposed, blocks;
     int conv_taps, conv_cin, conv_cpad;   // conv_taps > 0: `in` is a filter [rows][conv_cin][conv_taps] (split_conv_weight_body)
+    int64_t batch;                        // transposed tasks: matrices [k, rows] back to back (1 unless set)
 };
 
 template <int MODE>
@@ -219,7 +224,7 @@ __global__ void __launch_bounds__(256) split_pair_kernel(const SplitTask a, cons
     const SplitTask &t = first ? a : b;
     const int vblock = first ? (int)blockIdx.x : (int)blockIdx.x - a.blocks;
     if (t.conv_taps > 0) split_conv_weight_body<MODE>(t.in, t.rows, t.conv_cin, t.conv_taps, t.conv_cpad, t.pl, t.pitch, vblock, t.blocks);
-    else if (t.transposed) split_transpose_body<MODE>(t.in, t.rows, t.k, t.ld, t.pl, t.pitch, tile, vblock, t.blocks);
+    else if (t.transposed) split_transpose_body<MODE>(t.in, t.rows, t.k, t.ld, t.pl, t.pitch, tile, vblock, t.blocks, t.batch);
     else split_rows_body<MODE>(t.in, t.rows, t.k, t.ld, t.pl, t.pitch, t.chunk_k, t.chunk_stride, vblock, t.blocks);
 }
 
@@ -391,6 +396,7 @@ static SplitTask make_task(const float *in, int64_t rows, int64_t k, int64_t ld,
     for (int i = 0; i < 3; ++i) t.pl.p[i] = planes[i];
     t.transposed = transposed ? 1 : 0;
     t.conv_taps = t.conv_cin = t.conv_cpad = 0;
+    t.batch = 1;
     if (!transposed) {
         t.blocks = grid_for(rows * ((k + 3) / 4), 256, sm_count);
     } else {
@@ -437,12 +443,17 @@ int split_im2col(int mode, const float *in, int64_t C_in, int64_t H, int64_t W, 
     return (int)cudaGetLastError();
 }
 
-int split_conv_operands(int mode, const float *image, int64_t C_in, int64_t HW, void *const image_planes[3], int64_t image_pitch,
-                        const float *w, int64_t C_out, int taps, int c_pad, void *const w_planes[3], int64_t w_pitch,
-                        int sm_count, cudaStream_t st)
+int split_conv_operands(int mode, const float *image, int64_t batch, int64_t C_in, int64_t HW, void *const image_planes[3],
+                        int64_t image_pitch, const float *w, int64_t C_out, int taps, int c_pad, void *const w_planes[3],
+                        int64_t w_pitch, int sm_count, cudaStream_t st)
 {
-    // the image [C_in][HW] is a k-outermost operand: the transposing body writes it channel-innermost
-    const SplitTask ta = make_task(image, HW, C_in, HW, true, image_planes, image_pitch, 0, 0, sm_count);
+    // a sample [C_in][HW] is a k-outermost operand: the transposing body writes it channel-innermost
+    SplitTask ta = make_task(image, HW, C_in, HW, true, image_planes, image_pitch, 0, 0, sm_count);
+    ta.batch = batch;
+    {
+        const int64_t tiles = ((HW + 31) / 32) * ((C_in + 63) / 64) * batch, cap = (int64_t)sm_count * 8;
+        ta.blocks = (int)(tiles < cap ? (tiles > 0 ? tiles : 1) : cap);
+    }
     SplitTask tb = make_task(w, C_out, (int64_t)taps * c_pad, 0, false, w_planes, w_pitch, 0, 0, sm_count);
     tb.conv_taps = taps; tb.conv_cin = (int)C_in; tb.conv_cpad = c_pad;
     tb.blocks = grid_for(C_out * taps * (c_pad / 2), 256, sm_count);

@@ -24,12 +24,12 @@ int split_planes_pair(int mode, const float *a_in, int64_t a_rows, int64_t a_ld,
 // planes [out_h*out_w, pitch] of the im2col matrix of one [C_in, H, W] sample (k = (c, ky, kx), zero padding)
 int split_im2col(int mode, const float *in, int64_t C_in, int64_t H, int64_t W, int kh, int kw, int sh, int sw, int ph,
                  int pw, int64_t out_h, int64_t out_w, void *const planes[3], int64_t pitch, int sm_count, cudaStream_t st);
-// The two operands of an implicit convolution in one launch: the image [C_in][HW] -> channel-innermost planes
-// [HW][image_pitch], and the filter [C_out][C_in][taps] -> planes [C_out][w_pitch] with element tap * c_pad + c
-// (zero for c >= C_in; c_pad even).
-int split_conv_operands(int mode, const float *image, int64_t C_in, int64_t HW, void *const image_planes[3], int64_t image_pitch,
-                        const float *w, int64_t C_out, int taps, int c_pad, void *const w_planes[3], int64_t w_pitch,
-                        int sm_count, cudaStream_t st);
+// The two operands of an implicit convolution in one launch: the images [batch][C_in][HW] -> channel-innermost planes
+// [batch * HW][image_pitch], and the filter [C_out][C_in][taps] -> planes [C_out][w_pitch] with element
+// tap * c_pad + c (zero for c >= C_in; c_pad even).
+int split_conv_operands(int mode, const float *image, int64_t batch, int64_t C_in, int64_t HW, void *const image_planes[3],
+                        int64_t image_pitch, const float *w, int64_t C_out, int taps, int c_pad, void *const w_planes[3],
+                        int64_t w_pitch, int sm_count, cudaStream_t st);
 int widen_i8_to_bf16(const int8_t *in, int64_t rows, int64_t k, void *out, int64_t pitch, int sm_count,
                      cudaStream_t st);
 int repitch_i8(const int8_t *in, int64_t rows, int64_t k, int8_t *out, int64_t pitch, int sm_count,

@@ -279,6 +279,18 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void *tmap, uint
         : "memory");
 }
 
+// 4-D tiled load (innermost coordinate first); same alignment rule as the 2-D form.
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void *tmap, uint32_t bar, int32_t crd0,
+                                            int32_t crd1, int32_t crd2, int32_t crd3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        :
+        : "r"(dst), "l"(tmap), "r"(bar), "r"(crd0), "r"(crd1), "r"(crd2), "r"(crd3)
+        : "memory");
+}
+
 // 2-D tiled store shared memory -> global (bulk async-group completion).  The part of the box outside the tensor
 // is clipped by the hardware; crd0 * element size must be a multiple of 16 bytes and no coordinate negative.
 __device__ __forceinline__ void tma_store_2d(const void *tmap, uint32_t src, int32_t crd0, int32_t crd1)

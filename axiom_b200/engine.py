@@ -27,7 +27,7 @@ EXPORTS = [
     "axb_skinny_gemm_static", "axb_skinny_gemm_static_error", "axb_gemm_bias_act_scatter", "axb_gemm_gathered_scatter", "axb_ipc_get_handle", "axb_ipc_open_handle",
     "axb_ipc_close_handle",
     "axb_bias_add", "axb_relu", "axb_gelu", "axb_qgemm_w8a32", "axb_qgemm_w8a8", "axb_quantize_rows",
-    "axb_sdpa_fwd", "axb_kv_cache_append", "axb_kv_cache_attend", "axb_qkv_head_gemm", "axb_sdpa_bwd", "axb_conv_gemm", "axb_qdense_w8a32",
+    "axb_sdpa_fwd", "axb_kv_cache_append", "axb_kv_cache_attend", "axb_qkv_head_gemm", "axb_sdpa_bwd", "axb_conv_gemm", "axb_conv_gemm_batched", "axb_qdense_w8a32",
     "axb_qgemm_w8a32_qw", "axb_bias_add_nd", "axb_head_interleave_qkv_split", "axb_head_interleave", "axb_head_deinterleave",
     "axb_head_deinterleave_qkv_merge", "axb_qkv_cache_build", "axb_bias_cache_build", "axb_pointer_on_device",
     "axb_weight_prepare", "axb_weight_release", "axb_gemm_prepared",
@@ -320,6 +320,16 @@ class Engine:
         assert tuple(out.shape) == (C_out, out_h * out_w)
         self._check(self.lib.axb_conv_gemm(_ptr(weight), _ptr(inp), _i64(C_out), _i64(C_in), _i64(H), _i64(W), kh, kw, sh, sw,
                                            ph, pw, _i64(out_h), _i64(out_w), _ptr(out)))
+        return out
+
+    def conv_gemm_batched(self, weight, inp, kh, kw, sh, sw, ph, pw, out):
+        """weight [C_out, C_in*kh*kw], inp [N, C_in, H, W], out [N, C_out, out_h*out_w]."""
+        N, C_in, H, W = inp.shape
+        C_out = weight.shape[0]
+        out_h, out_w = (H + 2 * ph - kh) // sh + 1, (W + 2 * pw - kw) // sw + 1
+        assert tuple(out.shape) == (N, C_out, out_h * out_w)
+        self._check(self.lib.axb_conv_gemm_batched(_ptr(weight), _ptr(inp), _i64(N), _i64(C_out), _i64(C_in), _i64(H), _i64(W), kh, kw,
+                                                   sh, sw, ph, pw, _i64(out_h), _i64(out_w), _ptr(out)))
         return out
 
     def sdpa_bwd(self, Q, K, V, O, dO, L, dQ, dK, dV, scale, causal):

@@ -433,6 +433,22 @@ static const axb_ax_backend_ops_t ops_table = {
     .memcpy_d2d = be_d2d,
 };
 
+/* shape rules of the reference's implementation (src/compute/backends/cuda/ops_conv.cu:213-232): weight [C_out, K],
+   out [N, C_out, out_h*out_w] contiguous, in_dev all N samples back to back */
+static axb_status ext_conv_gemm_batched(const axb_ax_tensor_t *weight, const float *in_dev, int64_t N,
+                                        const axb_ax_conv_params_t *single, axb_ax_tensor_t *out)
+{
+    axb_status st;
+    if (!single || !in_dev) return report(ST_NULL_ARG, "conv_gemm_batched: NULL params");
+    if ((st = check_f32(weight, "conv_gemm_batched", 2)) || (st = check_f32(out, "conv_gemm_batched", 3))) return st;
+    const int64_t C_out = weight->shape[0], K = weight->shape[1], M = single->out_h * single->out_w;
+    if (K != single->C_in * single->kh * single->kw) return report(ST_SHAPE, "conv_gemm_batched: weight columns must equal C_in*kh*kw");
+    if (out->shape[0] != N || out->shape[1] != C_out || out->shape[2] != M)
+        return report(ST_SHAPE, "conv_gemm_batched: out must be [N, C_out, out_h*out_w]");
+    return done(axb_conv_gemm_batched(fptr(weight), in_dev, N, C_out, single->C_in, single->H, single->W, single->kh, single->kw,
+                                      single->sh, single->sw, single->ph, single->pw, single->out_h, single->out_w, fptr(out)));
+}
+
 static const axb_ax_cuda_extension_t extension_table = {
     .head_interleave_qkv_split = ext_qkv_split,
     .head_interleave_qkv_split_bias = ext_qkv_split_bias,
@@ -443,6 +459,7 @@ static const axb_ax_cuda_extension_t extension_table = {
     .bias_cache_build = ext_bias_cache_build,
     .sdpa_fwd = ext_sdpa_fwd,
     .sdpa_bwd = ext_sdpa_bwd,
+    .conv_gemm_batched = ext_conv_gemm_batched,
 };
 
 const axb_ax_backend_ops_t *axb_backend_ops(void) { return &ops_table; }

@@ -698,9 +698,25 @@ def w_conv(ctx, shared):
     t = ctx.core_time(lambda: eng.conv_gemm(wc, xc, 3, 3, 1, 1, 1, 1, oc), 20, 3)
     want = ctx.oracle.conv_gemm(host(wc), host(xc), 3, 3, 1, 1, 1, 1)
     e = nerr(host(oc), want)
-    return [dict(t, name="conv3x3", workload="conv 3x3 pad 1 as an implicit GEMM, one sample [256,56,56] -> [256,56,56] (shifted TMA windows of the channel-innermost image; no patch matrix)",
-                 value=2.0 * 256 * 2304 * 3136 / (t["ms_per_step"] * 1e-3) / 1e12, unit="TFLOP/s",
-                 parity_checked=bool(e <= 2e-5), parity_nerr=e, parity="whole output vs the fp32 oracle (tolerance of two fp32 summation orders)")]
+    res = [dict(t, name="conv3x3", workload="conv 3x3 pad 1 as an implicit GEMM, one sample [256,56,56] -> [256,56,56] (shifted TMA windows of the channel-innermost image; no patch matrix)",
+                value=2.0 * 256 * 2304 * 3136 / (t["ms_per_step"] * 1e-3) / 1e12, unit="TFLOP/s",
+                parity_checked=bool(e <= 2e-5), parity_nerr=e, parity="whole output vs the fp32 oracle (tolerance of two fp32 summation orders)")]
+    # the same layer over a batch of 16 samples: one implicit GEMM whose columns are the pixels of all samples
+    nb = 16
+    xb = ctx.uniform((nb, 256, 56, 56))
+    ob = torch.empty((nb, 256, 56 * 56), device="cuda")
+    tb = ctx.core_time(lambda: eng.conv_gemm_batched(wc, xb, 3, 3, 1, 1, 1, 1, ob), 20, 3)
+    probe = [0, nb - 1]
+    eb = max(nerr(host(ob[i]), ctx.oracle.conv_gemm(host(wc), host(xb[i]), 3, 3, 1, 1, 1, 1)) for i in probe)
+    peak = ctx.peaks["bf16_tflops"] / 6.0
+    val = 2.0 * nb * 256 * 2304 * 3136 / (tb["ms_per_step"] * 1e-3) / 1e12
+    kern = 2.0 * nb * 256 * 2304 * 3136 / (tb["kernel_ms"] * 1e-3) / 1e12 if tb.get("kernel_ms") else None
+    res.append(dict(tb, name="conv3x3_batch16", workload="the same layer on 16 samples through axb_conv_gemm_batched (one implicit GEMM, [256 x 2304] . [2304 x 50176])",
+                    value=val, unit="TFLOP/s",
+                    roofline={"bound": "tensor", "achieved": kern, "peak": peak, "frac": (kern / peak) if kern else None, "unit": "TFLOP/s",
+                              "peak_source": "measured bf16 burst / 2 / 3"},
+                    parity_checked=bool(eb <= 2e-5), parity_nerr=eb, parity="first and last sample vs the fp32 oracle"))
+    return res
 
 
 def w_mlp(ctx, shared):

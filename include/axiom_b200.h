@@ -356,9 +356,20 @@ AXB_API int axb_pointer_on_device(const void *p);
    k_im2col_sample into a col buffer, then cuBLAS).  One [C_in, H, W] sample (ax_conv_params_t,
    include/axiom/compute.h:36-43):
      out[C_out, out_h*out_w] = weight[C_out, C_in*kh*kw] . im2col(input),  zero padding ph, pw; strides sh, sw.
-   The patches are gathered straight into the tensor-core operand planes: no col matrix is materialised. */
+   Stride-1 layers whose output width is a multiple of 4 run as an implicit GEMM (the producer of the tensor-core
+   kernel reads shifted windows of the channel-innermost image; the padding is TMA's zero fill); for the rest the
+   patches are gathered straight into the tensor-core operand planes.  No col matrix is materialised either way. */
 AXB_API int axb_conv_gemm(const float *weight, const float *input, int64_t C_out, int64_t C_in, int64_t H, int64_t W,
                           int kh, int kw, int sh, int sw, int ph, int pw, int64_t out_h, int64_t out_w, float *out);
+/* Slot conv_gemm_batched of ax_cuda_extension_t (include/axiom/internal/cuda_extension.h:102-108; caller
+   src/core/conv/forward.c:529-560; reference implementation src/compute/backends/cuda/ops_conv.cu:213-290: one im2col
+   launch per sample into an N*K*M col buffer, then one strided-batched cuBLAS GEMM).  `batch` samples [C_in, H, W]
+   back to back in `input`, the filter shared: out[batch][C_out][out_h*out_w].  Stride-1 layers whose output width is
+   a multiple of 4 run as ONE implicit GEMM over all samples (the pixels of all samples are its columns); other
+   geometries take the samples one by one through axb_conv_gemm.  batch == 0 is a no-op. */
+AXB_API int axb_conv_gemm_batched(const float *weight, const float *input, int64_t batch, int64_t C_out, int64_t C_in,
+                                  int64_t H, int64_t W, int kh, int kw, int sh, int sw, int ph, int pw, int64_t out_h,
+                                  int64_t out_w, float *out);
 
 /* ---- KV cache (autoregressive decode) ---------------------------------------
    Device-pointer forms of ax_kv_cache_append / ax_kv_cache_attend (include/axiom/attention.h:341-381), whose

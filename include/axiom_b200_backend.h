@@ -106,8 +106,8 @@ typedef struct {
 } axb_ax_backend_ops_t;
 
 /* ax_cuda_extension_t (include/axiom/internal/cuda_extension.h:41-130): everything the attention layer calls on a
-   device — the five head-layout passes, the two fused-parameter builders, sdpa_fwd and sdpa_bwd — is provided; the
-   batched-convolution slots stay NULL. */
+   device — the five head-layout passes, the two fused-parameter builders, sdpa_fwd and sdpa_bwd — is provided, and the
+   batched convolution; the Winograd slots stay NULL (callers test them). */
 typedef struct {
     void (*head_interleave_qkv_split)(const float *src, float *q, float *k, float *v, int64_t B, int64_t S, int64_t H,
                                       int64_t dk, int64_t D);
@@ -124,7 +124,9 @@ typedef struct {
     axb_status (*sdpa_bwd)(const float *Q, const float *K, const float *V, const float *O, const float *dO,
                            const float *L, float *dQ, float *dK, float *dV, int64_t BH, int64_t S, int64_t dk,
                            float scale, bool causal, const float *P_saved);
-    axb_opaque_fn conv_gemm_batched, conv_winograd_f23, winograd_f23_prefer;
+    axb_status (*conv_gemm_batched)(const axb_ax_tensor_t *weight, const float *in_dev, int64_t N,
+                                    const axb_ax_conv_params_t *single, axb_ax_tensor_t *out);
+    axb_opaque_fn conv_winograd_f23, winograd_f23_prefer;
 } axb_ax_cuda_extension_t;
 
 #define AXB_BACKEND_API __attribute__((visibility("default")))

@@ -396,6 +396,40 @@ SHIM_API int ref_conv_gemm(const float *weight, const float *input, int64_t C_ou
     return rc;
 }
 
+/* the conv_gemm_batched slot of the registered extension table (include/axiom/internal/cuda_extension.h:102-108) on
+   device tensors made by the reference, called the way the conv layer calls it (src/core/conv/forward.c:527-560):
+   input [N, C_in, H, W] -> out [N, C_out, out_h*out_w] */
+SHIM_API int ref_device_conv_gemm_batched(const float *weight, const float *input, int64_t N, int64_t C_out, int64_t C_in,
+                                          int64_t H, int64_t W, int kh, int kw, int sh, int sw, int ph, int pw,
+                                          int64_t out_h, int64_t out_w, float *out)
+{
+    const ax_cuda_extension_t *ext = ax_compute_get_cuda_extension();
+    if (!ext || !ext->conv_gemm_batched) return 200;
+    const int64_t K = C_in * kh * kw, P = out_h * out_w;
+    int64_t ishape[4] = { N, C_in, H, W }, oshape[3] = { N, C_out, P };
+    int rc = 0;
+    use_cuda(1);
+    ax_tensor_t *w = to_dev(t2(weight, C_out, K)), *in = to_dev(ax_tensor_from_array(input, ishape, 4, AX_FLOAT32)),
+                *o = to_dev(ax_tensor_from_array(out, oshape, 3, AX_FLOAT32));
+    if (!w || !in || !o) rc = 100;
+    if (!rc) {
+        ax_conv_params_t prm;
+        prm.input = tdata(in);
+        prm.C_in = C_in; prm.H = H; prm.W = W; prm.kh = kh; prm.kw = kw; prm.sh = sh; prm.sw = sw; prm.ph = ph; prm.pw = pw;
+        prm.out_h = out_h; prm.out_w = out_w;
+        rc = (int)ext->conv_gemm_batched(w, tdata(in), N, &prm, o);
+    }
+    if (!rc) {
+        ax_device_synchronize(AX_DEVICE_CUDA);
+        rc = copy_back(o, out, N * C_out * P);
+    }
+    if (w) ax_tensor_destroy(w);
+    if (in) ax_tensor_destroy(in);
+    if (o) ax_tensor_destroy(o);
+    use_cuda(0);
+    return rc;
+}
+
 /* ax_fused_attention_bwd / _causal (include/axiom/attention.h:282-293) on head-major buffers. */
 SHIM_API int ref_sdpa_bwd(const float *Q, const float *K, const float *V, const float *O, const float *dO,
                           const float *L, float *dQ, float *dK, float *dV,

@@ -84,7 +84,7 @@ def test_tables_are_filled(backend):
     assert all(slots[i] for i in (13, 14, 15))
     assert not any(slots[i] for i in range(1, 13))
     ext = (ctypes.c_void_p * 12).from_address(backend.axb_cuda_extension())
-    assert ext[7] and ext[8] and not ext[9]   # sdpa_fwd and sdpa_bwd set, conv_gemm_batched left NULL
+    assert ext[7] and ext[8] and ext[9] and not ext[10] and not ext[11]   # sdpa_fwd, sdpa_bwd, conv_gemm_batched set; Winograd NULL
     assert slots[18]                          # qkv_head_gemm (after dwqkv_split_acc, dwqkv_split_acc_hm)
 
 

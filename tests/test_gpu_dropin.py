@@ -125,6 +125,24 @@ def test_conv_gemm_slot(dropin, reference, oracle, geom):
     assert nerr(got, want) <= 1e-5
 
 
+@pytest.mark.parametrize("geom", [(3, 8, 4, 12, 12, 3, 3, 1, 1, 1, 1), (2, 16, 4, 9, 9, 3, 3, 2, 2, 0, 0), (4, 12, 6, 10, 16, 1, 1, 1, 1, 0, 0)])
+def test_conv_gemm_batched_extension_slot(dropin, reference, oracle, geom):
+    """The conv_gemm_batched slot, called as the reference's conv layer calls it on a device (N samples back to back,
+    out [N, C_out, out_h*out_w]): every sample must match the reference's own CPU conv_gemm on that sample."""
+    N, C_out, C_in, H, W, kh, kw, sh, sw, ph, pw = geom
+    out_h, out_w = (H + 2 * ph - kh) // sh + 1, (W + 2 * pw - kw) // sw + 1
+    w, x = oracle.uniform((C_out, C_in * kh * kw), 7), oracle.uniform((N, C_in, H, W), 13)
+    got = np.full((N, C_out, out_h * out_w), np.nan, np.float32)
+    rc = dropin.ref_device_conv_gemm_batched(p(w), p(x), i64(N), i64(C_out), i64(C_in), i64(H), i64(W), kh, kw, sh, sw, ph, pw,
+                                             i64(out_h), i64(out_w), p(got))
+    assert rc == 0, (rc, dropin.ref_last_error())
+    for n in range(N):
+        st, want = reference.conv_gemm(w, np.ascontiguousarray(x[n]), kh, kw, sh, sw, ph, pw, device=0)
+        assert st == 0
+        np.testing.assert_allclose(got[n], want, atol=1e-3, rtol=1e-4)
+        assert nerr(got[n], want) <= 1e-5
+
+
 @pytest.mark.parametrize("causal", [0, 1])
 def test_sdpa_bwd_extension_slot(dropin, reference, oracle, causal):
     BH, S, dk = 6, 24, 16

@@ -533,6 +533,29 @@ def test_conv_implicit_gemm(engine, oracle, geom, mode):
     assert engine.device_error() == 0
 
 
+@pytest.mark.parametrize("geom", [(8, 256, 256, 56, 56, 3, 3, 1, 1, 1, 1),   # a ResNet stage at batch 8: one implicit GEMM, 128 x 256 tiles
+                                  (3, 40, 20, 12, 20, 5, 5, 1, 1, 2, 2),      # patches of the last tile run into the next sample and past the end
+                                  (5, 16, 3, 6, 8, 3, 3, 1, 1, 1, 1),         # samples smaller than one patch row
+                                  (2, 24, 8, 15, 15, 3, 3, 2, 2, 1, 1),       # strided: samples one by one through the gathered form
+                                  (1, 8, 4, 8, 8, 3, 3, 1, 1, 1, 1)])
+def test_conv_gemm_batched(engine, oracle, geom):
+    """axb_conv_gemm_batched: every sample equals the single-sample oracle; batch 0 is a no-op."""
+    N, C_out, C_in, H, W, kh, kw, sh, sw, ph, pw = geom
+    w = oracle.normal((C_out, C_in * kh * kw), 7, sigma=1.0 / np.sqrt(C_in * kh * kw))
+    x = oracle.uniform((N, C_in, H, W), 13)
+    out_h, out_w = (H + 2 * ph - kh) // sh + 1, (W + 2 * pw - kw) // sw + 1
+    out = torch.full((N, C_out, out_h * out_w), float("nan"), device="cuda")
+    engine.conv_gemm_batched(dev(w), dev(x), kh, kw, sh, sw, ph, pw, out)
+    got = host(out)
+    assert np.isfinite(got).all()
+    for n in range(N):
+        want = oracle.conv_gemm(w, np.ascontiguousarray(x[n]), kh, kw, sh, sw, ph, pw)
+        assert nerr(got[n], want) <= TOL_SPLIT, (n, nerr(got[n], want))
+    empty = torch.empty((0, C_out, out_h * out_w), device="cuda")
+    engine.conv_gemm_batched(dev(w), torch.empty((0, C_in, H, W), device="cuda"), kh, kw, sh, sw, ph, pw, empty)
+    assert engine.device_error() == 0
+
+
 @pytest.mark.parametrize("shape", [(2, 1024, 1024), (8, 4096, 4096), (9, 1000, 2048), (16, 2048, 1040), (17, 8200, 1168),
                                    (32, 16384, 512), (33, 1024, 1024), (64, 4096, 4096), (5, 128, 8192),
                                    (2, 8192, 128), (64, 130, 8192), (7, 64, 16384), (48, 2048, 65536 // 64),
