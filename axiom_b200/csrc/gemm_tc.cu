@@ -63,6 +63,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    bool passed_cluster_barrier = false;   // split-K through the cluster: see the end of the kernel
     const int total_tiles = p.m_tiles * p.n_tiles;
     const int ksplit_all = SPLITK ? p.ksplit : 1;
     const int items = total_tiles * ksplit_all;   // work item = (tile, K-slice); one slice per tile unless K is split
@@ -333,7 +334,45 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_tempty + 8 * acc);
                 }
-                if (SPLITK && ksplit > 1) {
+                if (SPLITK && ksplit > 1 && p.sk_cluster) {
+                    if constexpr (SPLITK) {
+                        // The partner CTA holds the other K-slice of this tile.  This warp's 32 rows x HALF columns
+                        // belong to column half `half`; the CTA of cluster rank `half` finishes them.  The staging
+                        // area (untouched until the finishing pass) is the inbox: slot q, thread-private order.
+                        const uint32_t rank = cluster_cta_rank();
+                        uint8_t *stg0 = gen_base + HEADER_BYTES + (size_t)p.stages * stage_bytes;
+                        volatile int *dead = reinterpret_cast<volatile int *>(gen_base + HDR_SK_DEAD);
+                        if (!got) *dead = 1;
+                        if (got && (uint32_t)half != rank) {
+                            const uint32_t dst = map_to_cta(smem_u32(stg0) + (uint32_t)q * 8192u + (uint32_t)lane * 16u, (uint32_t)half);
+#pragma unroll
+                            for (int i = 0; i < HALF / 4; ++i)
+                                asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst + (uint32_t)i * 512u),
+                                             "f"(sum[4 * i]), "f"(sum[4 * i + 1]), "f"(sum[4 * i + 2]), "f"(sum[4 * i + 3])
+                                             : "memory");
+                        }
+                        __syncwarp();
+                        cluster_sync_all();          // every thread of both CTAs passes here exactly once
+                        passed_cluster_barrier = true;
+                        if ((uint32_t)half != rank) break;          // (one work item per CTA: the loop is over)
+                        {
+                            const float4 *in4 = reinterpret_cast<const float4 *>(stg0 + (size_t)q * 8192) + lane;
+#pragma unroll
+                            for (int i = 0; i < HALF / 4; ++i) {
+                                const float4 o4 = in4[i * 32];
+                                // slice order: rank 0's partial first
+                                if (rank == 0) { sum[4 * i] += o4.x; sum[4 * i + 1] += o4.y; sum[4 * i + 2] += o4.z; sum[4 * i + 3] += o4.w; }
+                                else { sum[4 * i] = o4.x + sum[4 * i]; sum[4 * i + 1] = o4.y + sum[4 * i + 1]; sum[4 * i + 2] = o4.z + sum[4 * i + 2]; sum[4 * i + 3] = o4.w + sum[4 * i + 3]; }
+                            }
+                        }
+                        // the four finishing warps reuse the inbox as their staging tiles: all must have read it
+                        asm volatile("bar.sync 2, 128;" ::: "memory");
+                        if (*dead) {
+                            alive = false;
+                            break;
+                        }
+                    }
+                } else if (SPLITK && ksplit > 1) {
                     if constexpr (SPLITK) {
                         const int st = splitk_exchange<float, HALF>(p, sum, t, slice, warp, lane, gen_base, got);
                         if (st == SK_DEAD) {
@@ -368,6 +407,16 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
                     }
                 }
             }
+        }
+    }
+
+    // split-K through the cluster: the warps that do not take part in the hand-over (producers, MMA issuer) meet the
+    // epilogue warps at the cluster barrier, which counts every thread of both CTAs — each thread exactly once,
+    // whatever happened before (a partner waiting there has no time limit)
+    if constexpr (SPLITK) {
+        if (p.sk_cluster && !passed_cluster_barrier) {
+            __syncwarp();
+            cluster_sync_all();
         }
     }
 
@@ -604,11 +653,18 @@ static int launch_inst(const TmapPack &tm, KernelArgs &ka, int stage_bytes, int 
     cfg.blockDim = dim3(NUM_THREADS);
     cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = stream;
-    cudaLaunchAttribute at;
-    at.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at.val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = &at;
+    cudaLaunchAttribute at[2];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
     cfg.numAttrs = 1;
+    if (SPLITK && ka.sk_cluster) {   // the two K-slices of a tile are consecutive CTAs: one cluster
+        at[1].id = cudaLaunchAttributeClusterDimension;
+        at[1].val.clusterDim.x = 2;
+        at[1].val.clusterDim.y = 1;
+        at[1].val.clusterDim.z = 1;
+        cfg.numAttrs = 2;
+    }
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, tm, ka);
     if (e != cudaSuccess) snprintf(g_err, sizeof g_err, "gemm_tc launch: %s", cudaGetErrorString(e));
     return (int)e;
@@ -812,6 +868,8 @@ static int launch_common(int kind, const TcOperand &A, const TcOperand &B, const
     if (pl.ksplit > 1) {
         ka.sk_scratch = splitk->scratch;
         ka.sk_counters = splitk->counters;
+        // two slices of an fp32 tile meet in shared memory (one work item per CTA: mt * nt * 2 <= sm_count by the plan)
+        ka.sk_cluster = (pl.ksplit == 2 && kind != KIND_I8 && mt * nt * 2 <= sm_count) ? 1 : 0;
     }
     ka.alpha = ep.alpha; ka.beta = ep.beta; ka.bias = ep.bias; ka.colscale = ep.colscale;
     ka.rq_a_scale = ep.rq_a_scale; ka.rq_out_scale = ep.rq_out_scale;

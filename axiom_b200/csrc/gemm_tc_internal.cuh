@@ -50,6 +50,10 @@ struct KernelArgs {
     int ksplit, kb_per_slice;
     void *sk_scratch;        // [tiles x CTAs per tile][ksplit][128 x BN] fp32 / s32
     int *sk_counters;        // [tiles x CTAs per tile], zero between launches
+    // sk_cluster (fp32 kinds, ksplit == 2, one work item per CTA): the two slices of a tile are one thread-block
+    // cluster and meet in shared memory instead of scratch — each CTA pushes the column half it does not finish into
+    // its partner's epilogue staging area, one cluster barrier, and each finishes and stores its own half
+    int sk_cluster;
     // implicit convolution (cv_taps > 0, see TcConv): the B maps are 4-D over the image planes [batch][H][W][C] with
     // one box per 64-pixel patch (cv_pw x 64/cv_pw pixels of one sample); output column j of the GEMM is pixel j % 64
     // of patch j / 64, patches numbered sample-major (cv_npatch_s per sample, cv_px per patch row), stored by

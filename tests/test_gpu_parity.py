@@ -635,10 +635,14 @@ def test_qdense_w8a32(engine, oracle, shape, act):
 # ---- split-K of the dense tensor-core core: few output tiles, long K ----------------------------------------------
 
 @pytest.mark.parametrize("shape", [(256, 384, 4096), (130, 200, 3000), (1024, 1024, 1024), (64, 128, 8192), (300, 96, 2052),
-                                   (256, 3136, 2304), (33, 520, 1536)])
+                                   (256, 3136, 2304), (33, 520, 1536),
+                                   # two slices per tile (the pair of CTAs meets in shared memory): ragged edges,
+                                   # slices of unequal length, K shorter than two chunks, 64-column tiles
+                                   (1000, 900, 1100), (640, 1408, 520), (896, 1024, 300), (7000, 64, 2048)])
 def test_split_k_fp32_vs_oracle_and_repeatable(engine, oracle, shape):
-    """Problems with too few 128-column tiles to fill the GPU cut K into slices that meet in scratch; the slice that
-    arrives last adds all partial tiles in slice order, so the result is inside the fp32 tolerance AND bitwise
+    """Problems with too few 128-column tiles to fill the GPU cut K into slices.  Two slices are a thread-block cluster
+    and meet in shared memory (each CTA finishes one column half); more meet in scratch, where the slice that arrives
+    last adds all partial tiles in slice order.  Either way the result is inside the fp32 tolerance AND bitwise
     repeatable, with every epilogue form (bias + GELU, alpha/beta, transposed operands)."""
     M, N, K = shape
     A, B, bias, Cin = oracle.uniform((M, K), 7), oracle.uniform((K, N), 13), oracle.uniform((N,), 29), oracle.uniform((M, N), 5)
