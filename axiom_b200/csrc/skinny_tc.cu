@@ -17,9 +17,10 @@
 //
 // One CTA = 128 output columns x one K-slice; the K-slices of a column tile form a thread-block cluster and are
 // summed through distributed shared memory in slice order (deterministic).  Roles: warp 0 TMA producer (ring of
-// 8 stages of 32 k-rows — 128 KB of W in flight per SM), warp 1 MMA issuer, warps 2-5 converters (a ring of four
-// hi/lo tile pairs in tensor memory), warps 6-9 drain the accumulator every 256 k (a fresh TMEM accumulator per
-// chunk: the tensor core truncates when it accumulates) and run the epilogue.
+// 8 stages of 32 k-rows — 128 KB of W in flight per SM), warps 1 and 10 MMA issuers for the even and the odd k-blocks
+// (each into its own accumulator set), warps 2-5 and 6-9 two converter groups that take alternate k-blocks (a ring of
+// four hi/lo tile pairs in tensor memory); warps 6-9 also drain the accumulators every 256 k (fresh TMEM
+// accumulators per chunk: the tensor core truncates when it accumulates) and run the epilogue.
 #include "skinny.cuh"
 
 #include "gemm_tc.cuh"
@@ -30,10 +31,10 @@
 
 namespace axb {
 
-static constexpr int KT_THREADS = 320;
+static constexpr int KT_THREADS = 352;   // producer, MMA issuer, 4 + 4 converter warps, second MMA issuer
 static constexpr int KT_STAGES = 8;      // shared-memory ring (TMA destinations)
 static constexpr int KT_T = 4;           // ring of W hi/lo tile pairs in tensor memory (64 columns each)
-static constexpr int KT_ACC_COL = KT_T * 64;   // the two accumulator buffers follow the ring
+static constexpr int KT_ACC_COL = KT_T * 64;   // two accumulator buffers of two sets of 2*MP columns follow the ring
 static constexpr int KT_KB = 32;        // k rows per stage
 static constexpr int KT_BN = 128;       // output columns per CTA
 static constexpr int KT_CHUNK = 8;      // stages per accumulator chunk (256 k)
@@ -45,8 +46,10 @@ struct alignas(64) SkinnyTcMaps {
 
 enum { KERR_PRODUCER = 21, KERR_CONVERT = 22, KERR_MMA = 23, KERR_DRAIN = 24 };
 
-enum { KB_RAW = 0, KB_EMPTY = KT_STAGES, KB_T_FULL = 2 * KT_STAGES, KB_T_EMPTY = 2 * KT_STAGES + KT_T,
-       KB_CHUNK_FULL = 2 * KT_STAGES + 2 * KT_T, KB_CHUNK_EMPTY = 2 * KT_STAGES + 2 * KT_T + 2 };
+// KB_EMPTY + s completes when the MMAs of the block in stage s have retired: it frees the stage for the producer and,
+// four blocks on, that block's tensor-memory slot for the converters
+enum { KB_RAW = 0, KB_EMPTY = KT_STAGES, KB_T_FULL = 2 * KT_STAGES, KB_CHUNK_FULL = 2 * KT_STAGES + KT_T,
+       KB_CHUNK_EMPTY = 2 * KT_STAGES + KT_T + 2 };
 
 
 // one lane polls, the warp gets the outcome: 32 lanes spinning on a barrier cost shared-memory bandwidth that
@@ -130,12 +133,9 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
             mbar_init(bar(KB_RAW + s), 1);
             mbar_init(bar(KB_EMPTY + s), 1);
         }
-        for (int s = 0; s < KT_T; ++s) {
-            mbar_init(bar(KB_T_FULL + s), 128);
-            mbar_init(bar(KB_T_EMPTY + s), 1);
-        }
+        for (int s = 0; s < KT_T; ++s) mbar_init(bar(KB_T_FULL + s), 128);
         for (int b = 0; b < 2; ++b) {
-            mbar_init(bar(KB_CHUNK_FULL + b), 1);
+            mbar_init(bar(KB_CHUNK_FULL + b), 2);      // one arrival per MMA issuer
             mbar_init(bar(KB_CHUNK_EMPTY + b), 128);
         }
         mbar_fence_init();
@@ -181,52 +181,116 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
                 tma_load_3d(st + KT_W_BYTES, &tm.x, bar(KB_RAW + s), k0, 0, 0);
             }
         }
-    } else if (warp == 1) {
-        // ---------------------------------------------------------- MMA issuer
+    } else if (warp == 1 || warp == 10) {
+        // --------------------------------------------------------- MMA issuers
+        // TWO issuing threads: warp 1 takes the even k-blocks, warp 10 the odd ones, each into its own accumulator
+        // set.  These MMAs are short (M128 x N<=64 x K8) and the tensor pipe is mostly idle; what a block costs is
+        // the issuing thread's own time — about 70 cycles per tcgen05.mma and 120 per tcgen05.commit, 1.2 k cycles
+        // per block of 8 + 2, measured with in-kernel time stamps — so a second thread doubles the rate.
         if (lane == 0) {
+            const int par = warp == 1 ? 0 : 1;
             const uint64_t desc_x = smem_desc_kmajor(0, 128);
             // N = 2*MP for the pass of W hi over X hi and X lo side by side, MP for W lo over X hi
             const uint32_t idesc_hi = make_idesc<KIND_TF32>(KT_BN, 2 * MP);
             const uint32_t idesc_lo = make_idesc<KIND_TF32>(KT_BN, MP);
             bool ok = true;
-            for (int i = 0; i < nkb; ++i) {
-                const int s = i % KT_STAGES;
-                const int ci = i / KT_CHUNK, cb = ci & 1;
-                const bool first = (i % KT_CHUNK) == 0;
-                if (first && ci >= 2 && !mbar_wait_bounded(bar(KB_CHUNK_EMPTY + cb), ((ci >> 1) - 1) & 1)) { ok = false; break; }
-                const int ts = i % KT_T;
-                if (!mbar_wait_bounded(bar(KB_T_FULL + ts), (i / KT_T) & 1)) { ok = false; break; }   // implies the stage's X
-                tc_fence_after_sync();
-                const uint32_t a_hi = tmem + ts * 64, a_lo = a_hi + 32;   // W^T: lane = output column, column = k
-                const uint32_t d = tmem + KT_ACC_COL + cb * 128;
-                const uint32_t xb = stage_addr(s) + KT_W_BYTES;
-                // columns [0, MP): hi.hi, [MP, 2*MP): hi.lo, [2*MP, 3*MP): lo.hi — the drain adds the three.  The two
-                // passes alternate and own separate columns: an MMA that accumulates waits for the one before it on
-                // the same columns, and two independent chains keep the pipe busy where one does not.
+            for (int ci = 0; ci < nchunks && ok; ++ci) {
+                const int cb = ci & 1;
+                if (ci >= 2 && !mbar_wait_bounded(bar(KB_CHUNK_EMPTY + cb), ((ci >> 1) - 1) & 1)) { ok = false; break; }
+                // a SET = columns [0, MP): hi.hi, [MP, 2*MP): hi.lo + lo.hi (the second pass accumulates into the
+                // columns of the first pass's second half: both are corrections of the same size)
+                const uint32_t d = tmem + KT_ACC_COL + cb * (4 * MP) + par * (2 * MP);
+                const int i_end = min(nkb, (ci + 1) * KT_CHUNK);
+                bool issued = false;
+                for (int i = ci * KT_CHUNK + par; i < i_end; i += 2) {
+                    const int s = i % KT_STAGES, ts = i % KT_T;
+                    if (!mbar_wait_bounded(bar(KB_T_FULL + ts), (i / KT_T) & 1)) { ok = false; break; }   // implies the stage's X
+                    tc_fence_after_sync();
+                    const uint32_t a_hi = tmem + ts * 64, a_lo = a_hi + 32;   // W^T: lane = output column, column = k
+                    const uint32_t xb = stage_addr(s) + KT_W_BYTES;
 #pragma unroll
-                for (int ks = 0; ks < 4; ++ks) {
-                    const uint64_t bx = desc_x | (uint64_t)(((xb + ks * 32) & 0x3FFFFu) >> 4);
-                    const uint32_t accf = (first && ks == 0) ? 0u : 1u;
-                    tc_mma_ts_tf32(d, a_hi + ks * 8, bx, idesc_hi, accf);
-                    tc_mma_ts_tf32(d + 2 * MP, a_lo + ks * 8, bx, idesc_lo, accf);
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint64_t bx = desc_x | (uint64_t)(((xb + ks * 32) & 0x3FFFFu) >> 4);
+                        tc_mma_ts_tf32(d, a_hi + ks * 8, bx, idesc_hi, (!issued && ks == 0) ? 0u : 1u);
+                    }
+#pragma unroll
+                    for (int ks = 0; ks < 4; ++ks) {
+                        const uint64_t bx = desc_x | (uint64_t)(((xb + ks * 32) & 0x3FFFFu) >> 4);
+                        tc_mma_ts_tf32(d + MP, a_lo + ks * 8, bx, idesc_lo, 1u);
+                    }
+                    issued = true;
+                    // one barrier per block serves both rings: the converters wait on it for the tensor-memory slot of
+                    // block i + 4, the producer for the shared-memory stage of block i + 8
+                    tc_commit(bar(KB_EMPTY + s));
                 }
-                tc_commit(bar(KB_T_EMPTY + ts));
-                tc_commit(bar(KB_EMPTY + s));
-                if ((i % KT_CHUNK) == KT_CHUNK - 1 || i == nkb - 1) tc_commit(bar(KB_CHUNK_FULL + cb));
+                if (!ok) break;
+                // every issuer arrives once per chunk — through the tensor pipe when it has MMAs in flight for it
+                if (issued) tc_commit(bar(KB_CHUNK_FULL + cb));
+                else mbar_arrive(bar(KB_CHUNK_FULL + cb));
             }
             if (!ok) kt_report(a.err, KERR_MMA);
         }
-    } else if (warp < 6) {
-        // ---------------------------------------------------------- converters
-        const int ct = threadIdx.x - 64;  // 0..127
-        const int t_n = 32 * (warp & 3) + lane;   // the output column this thread carries into its TMEM lane
+    } else {
+        // ----------------------------------------------------- converters + drain
+        // Two groups of four warps (each covers the four lane quarters of tensor memory): warps 2-5 convert the even
+        // k-blocks, warps 6-9 the odd ones and, between two of theirs, drain the accumulator chunks.  In-kernel time
+        // stamps of the version with ONE converter group (and four drain warps that idled seven blocks out of
+        // eight) showed the conversion as the whole critical path: 1.4 k cycles per k-block, serial in its waits —
+        // barrier, 32 shared-memory loads, the tensor-memory stores and their completion — against 0.5 k of MMA
+        // issue, with the weight tiles in shared memory eight blocks ahead.
+        const int grp = warp >= 6 ? 1 : 0;
+        const int ct = threadIdx.x - 64 - grp * 128;  // 0..127 inside the group
+        const int t_n = 32 * (warp & 3) + lane;       // the output column this thread carries into its TMEM lane
         const uint32_t st_lane = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        for (int i = 0; i < nkb; ++i) {
+        bool ok = true;
+        auto drain = [&](int ci) -> bool {
+            const int cb = ci & 1;
+            if (!mbar_wait_warp_bounded(bar(KB_CHUNK_FULL + cb), (ci >> 1) & 1)) { kt_report(a.err, KERR_DRAIN); return false; }
+            tc_fence_after_sync();
+            const uint32_t abuf = st_lane + KT_ACC_COL + cb * (4 * MP);
+            // a chunk of a single k-block (the tail of a slice) leaves the second set untouched: stale columns
+            const bool two = min(nkb, (ci + 1) * KT_CHUNK) - ci * KT_CHUNK >= 2;
+            if (MP == 32) {
+                uint32_t r0[32], r1[32], r2[32], r3[32];   // set 0: hi.hi, corrections; set 1: the same
+                tmem_ld_32x32(abuf, r0);
+                tmem_ld_32x32(abuf + 32, r1);
+                tmem_ld_32x32(abuf + 64, r2);
+                tmem_ld_32x32(abuf + 96, r3);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                mbar_arrive(bar(KB_CHUNK_EMPTY + cb));
+#pragma unroll
+                for (int m = 0; m < MP; ++m)
+                    acc[m] += two ? (__uint_as_float(r1[m & 31]) + __uint_as_float(r3[m & 31])) + (__uint_as_float(r0[m & 31]) + __uint_as_float(r2[m & 31]))
+                                  : __uint_as_float(r1[m & 31]) + __uint_as_float(r0[m & 31]);
+            } else {
+                uint32_t r0[32], r1[32];   // MP = 16: a set is 32 columns
+                tmem_ld_32x32(abuf, r0);
+                tmem_ld_32x32(abuf + 32, r1);
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                mbar_arrive(bar(KB_CHUNK_EMPTY + cb));
+#pragma unroll
+                for (int m = 0; m < MP; ++m)
+                    acc[m] += two ? (__uint_as_float(r0[(MP + m) & 31]) + __uint_as_float(r1[(MP + m) & 31])) +
+                                        (__uint_as_float(r0[m & 31]) + __uint_as_float(r1[m & 31]))
+                                  : __uint_as_float(r0[(MP + m) & 31]) + __uint_as_float(r0[m & 31]);
+            }
+            return true;
+        };
+        int drained = 0;
+        for (int i = grp; i < nkb && ok; i += 2) {
+            // a chunk whose last block lies two blocks back has been through the tensor pipe (or is about to): it is
+            // drained here, a whole chunk before the MMA issuer needs its buffer again
+            while (grp == 1 && ok && drained < nchunks && (drained + 1) * KT_CHUNK + 1 <= i) ok = drain(drained++);
+            if (!ok) break;
             const int s = i % KT_STAGES, n = i / KT_STAGES;
-            if (!kt_wait_warp(bar(KB_RAW + s), n & 1)) { kt_report(a.err, KERR_CONVERT); break; }
+            if (!kt_wait_warp(bar(KB_RAW + s), n & 1)) { kt_report(a.err, KERR_CONVERT); ok = false; break; }
             const int ts = i % KT_T;
-            if (i >= KT_T && !kt_wait_warp(bar(KB_T_EMPTY + ts), ((i / KT_T) - 1) & 1)) {
+            // the tensor-memory slot is free when the MMAs of block i - 4 have retired (barrier of that block's stage)
+            if (i >= KT_T && !kt_wait_warp(bar(KB_EMPTY + (i - KT_T) % KT_STAGES), ((i - KT_T) / KT_STAGES) & 1)) {
                 kt_report(a.err, KERR_CONVERT);
+                ok = false;
                 break;
             }
             tc_fence_after_sync();
@@ -246,43 +310,13 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
             tc_fence_before_sync();
             mbar_arrive(bar(KB_T_FULL + ts));
         }
-    } else {
-        // --------------------------------------------------------------- drain
-        const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        for (int ci = 0; ci < nchunks; ++ci) {
-            const int cb = ci & 1;
-            if (!mbar_wait_warp_bounded(bar(KB_CHUNK_FULL + cb), (ci >> 1) & 1)) { kt_report(a.err, KERR_DRAIN); break; }
-            tc_fence_after_sync();
-            const uint32_t abuf = lane_base + KT_ACC_COL + cb * 128;
-            if (MP == 32) {
-                uint32_t r0[32], r1[32], r2[32];
-                tmem_ld_32x32(abuf, r0);
-                tmem_ld_32x32(abuf + 32, r1);
-                tmem_ld_32x32(abuf + 64, r2);
-                tmem_ld_wait();
-                tc_fence_before_sync();
-                mbar_arrive(bar(KB_CHUNK_EMPTY + cb));
-#pragma unroll
-                for (int m = 0; m < MP; ++m)
-                    acc[m] += (__uint_as_float(r1[m & 31]) + __uint_as_float(r2[m & 31])) + __uint_as_float(r0[m & 31]);
-            } else {
-                uint32_t r0[32], r1[32];
-                tmem_ld_32x32(abuf, r0);        // hi.hi | hi.lo
-                tmem_ld_32x32(abuf + 32, r1);   // lo.hi | unused
-                tmem_ld_wait();
-                tc_fence_before_sync();
-                mbar_arrive(bar(KB_CHUNK_EMPTY + cb));
-#pragma unroll
-                for (int m = 0; m < MP; ++m)
-                    acc[m] += (__uint_as_float(r0[(MP + m) & 31]) + __uint_as_float(r1[m & 31])) + __uint_as_float(r0[m & 31]);
-            }
-        }
+        while (grp == 1 && ok && drained < nchunks) ok = drain(drained++);
     }
 
     // ------------------------------------------------------------ reduce + epilogue
     grid_dep_wait();   // Y and the bias are touched only after the kernel before this one has finished
     if (nslices == 1) {
-        if (warp >= 6 && n0 + t_row < a.N) {
+        if (warp >= 6 && warp < 10 && n0 + t_row < a.N) {
 #pragma unroll
             for (int m = 0; m < MP; ++m)
                 if (m < a.M) a.Y[(int64_t)m * a.N + n0 + t_row] = kt_epilogue(a, acc[m], m, n0 + t_row);
@@ -296,12 +330,12 @@ __global__ void __launch_bounds__(KT_THREADS, 1) skinny_tc_kernel(const __grid_c
         // stores instead cost 2.8 us for 32 scalar stores per thread.
         float *red = reinterpret_cast<float *>(base_ptr + 1024);
         __syncthreads();
-        if (warp >= 6) {
+        if (warp >= 6 && warp < 10) {
 #pragma unroll
             for (int m = 0; m < MP; ++m) red[m * KT_BN + t_row] = acc[m];
         }
         cluster_sync_all();
-        if (warp >= 2) {
+        if (warp >= 2 && warp < 10) {
             const int rows_owned = (a.M - slice + nslices - 1) / nslices;
             for (int it = threadIdx.x - 64; it < rows_owned * 32; it += 256) {
                 const int m = slice + (it >> 5) * nslices, c4 = (it & 31) * 4;
