@@ -28,8 +28,8 @@
 //   warps 6-9 converters: lo = tf32(x - trunc(x)).  Stream tiles: in place behind the hi plane.  Fixed tiles: into
 //             TENSOR MEMORY (thread = row), where the lo.hi product reads them as its A operand (TS form) — that
 //             frees the 64 KB of shared memory the second T1/T2 buffer needs
-//   warp 5    one thread issues the MMAs: scores of block b+1 go ahead of the output product of block b (two score
-//             buffers), so the pipe works on the next block while the row threads turn this one into dS
+//   warp 5    one thread issues the score MMAs, up to two blocks ahead of the row threads (two score buffers);
+//   warp 10   one thread issues the output products (dS from tensor memory) as the row threads finish a block
 //   warps 0-3 thread t owns row t of the fixed side
 // In-kernel time stamps of the single-buffered first version showed one serial cycle per block — load T1/T2, split,
 // issue the scores, issue the output product, only then the next load — of 7.8 k cycles against 4.2 k of MMA issue;
@@ -49,7 +49,7 @@ namespace axb {
 
 namespace {
 
-constexpr int BT_F = 128, BT_T = 64, BT_THREADS = 320;
+constexpr int BT_F = 128, BT_T = 64, BT_THREADS = 352;
 constexpr int BT_HEADER = 2048;   // barriers, the TMEM slot, and the stream rows' L and D [2][64] each
 constexpr uint32_t SLAB_F = 128 * 128;   // bytes of one 32-column slab of a 128-row tile
 constexpr uint32_t SLAB_T = 64 * 128;    // ... of a 64-row tile
@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(BT_THREADS, 1) sdpa_bwd_tc_kernel(const __grid
             }
             if (!ok) bt_report(a.err, BERR_PRODUCER);
         }
-    } else if (warp >= 6) {
+    } else if (warp >= 6 && warp < 10) {
         // ---------------------------------------------------------- converters
         // lo = tf32(x - (x cut to tf32)) at the same offset of the lo plane; x itself stays where TMA put it and is
         // the hi operand
@@ -288,8 +288,12 @@ __global__ void __launch_bounds__(BT_THREADS, 1) sdpa_bwd_tc_kernel(const __grid
             }
         }
         if (!ok && nb > 0) bt_report(a.err, BERR_CONVERT);
-    } else if (warp == 5) {
-        // ---------------------------------------------------------- MMA issuer
+    } else if (warp == 5 || warp == 10) {
+        // --------------------------------------------------------- MMA issuers
+        // Two issuing threads: warp 5 the score products, warp 10 the output products.  A tcgen05.mma of this size costs
+        // the issuing thread more time (70 - 90 cycles) than it costs the tensor pipe, so one thread issuing both kinds
+        // in turn was the loop's critical path with the pipe a quarter busy.  (A third thread, for the dP products, was
+        // measured: the row threads slowed down beside it and the backward took 0.90 ms instead of 0.83.)
         if (lane == 0 && nb > 0) {
             const uint64_t desc_k = smem_desc_kmajor(0, 128);
             const uint64_t desc_mn = smem_desc_mnmajor_sw128_32b(0, SLAB_T, 512);
@@ -351,27 +355,28 @@ __global__ void __launch_bounds__(BT_THREADS, 1) sdpa_bwd_tc_kernel(const __grid
                 tc_commit(bar(B_ACC_FULL + b));
                 tc_commit(bar(B_T3_EMPTY));
             };
-            bool ok = mbar_wait_bounded(bar(B_F_FULL), 0) && mbar_wait_bounded(bar(B_T12_FULL + 0), 0);
-            if (ok) {
-                tc_fence_after_sync();
-                issue_block_scores(0);
-            }
-            for (int bi = 0; ok && bi < nb; ++bi) {
-                if (bi + 1 < nb) {
-                    // the score buffer of block bi+1 held dS of block bi-1: its output product was issued before this
-                    // point and MMAs execute in order, so nothing else has to be waited for
-                    ok = mbar_wait_bounded(bar(B_T12_FULL + ((bi + 1) & 1)), ((bi + 1) >> 1) & 1);
+            bool ok = true;
+            if (warp == 5) {
+                ok = mbar_wait_bounded(bar(B_F_FULL), 0);
+                for (int bi = 0; ok && bi < nb; ++bi) {
+                    // score buffer bi % 2 held dS of block bi - 2, the A operand of that block's output product, which
+                    // the other thread issues: wait until it has retired
+                    if (bi >= 2) ok = mbar_wait_bounded(bar(B_ACC_FULL + (bi & 1)), ((bi - 2) >> 1) & 1);
+                    ok = ok && mbar_wait_bounded(bar(B_T12_FULL + (bi & 1)), (bi >> 1) & 1);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    issue_block_scores(bi + 1);
+                    issue_block_scores(bi);
                 }
-                const int b = bi & 1, n = bi >> 1;
-                ok = mbar_wait_bounded(bar(B_DS_FULL + b), n & 1);
-                ok = ok && mbar_wait_bounded(bar(B_T3_FULL), bi & 1);
-                ok = ok && (bi < 2 || mbar_wait_bounded(bar(B_ACC_EMPTY + b), (n - 1) & 1));
-                if (!ok) break;
-                tc_fence_after_sync();
-                issue_out(bi);
+            } else {
+                for (int bi = 0; ok && bi < nb; ++bi) {
+                    const int b = bi & 1, n = bi >> 1;
+                    ok = mbar_wait_bounded(bar(B_DS_FULL + b), n & 1);
+                    ok = ok && mbar_wait_bounded(bar(B_T3_FULL), bi & 1);
+                    ok = ok && (bi < 2 || mbar_wait_bounded(bar(B_ACC_EMPTY + b), (n - 1) & 1));
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_out(bi);
+                }
             }
             if (!ok) bt_report(a.err, BERR_MMA);
         }

@@ -14,7 +14,8 @@
 //   warp 4   : TMA producer — the Q tile once, then one K and one V block at a time (128-byte swizzle; V with
 //              the 32-byte-chunk variant, the one layout an MN-major tf32 operand may have);
 //   warps 6-9: converters (above);
-//   warp 5   : one thread issues tcgen05.mma.  S_j = Q.K_j^T (M128 x N128, operands from shared memory, both
+//   warps 5, 10: one thread each issues tcgen05.mma — warp 5 the scores, warp 10 the P.V products.
+//              S_j = Q.K_j^T (M128 x N128, operands from shared memory, both
 //              K-major) goes to one of two TMEM score buffers; O_j = P_j.V_j takes P from TENSOR MEMORY (the
 //              TS form) and V as an MN-major shared-memory operand, i.e. exactly as the TMA load leaves it — V
 //              is never transposed.  N = 128 runs the tf32 pipe at its full rate (N = 64 does not: measured
@@ -27,9 +28,9 @@
 //              stays small enough for the instruction cache, which a fully unrolled row (the first version)
 //              did not — its warps spent most of their time waiting for instructions.  The split of P uses
 //              integer masking, not cvt: conversions share the 16-lane pipe with ex2 and halved its rate.
-// The score matrix never leaves the SM.  Issue order S_0 S_1 O_0 S_2 O_1 ...: the pipe computes the next
-// block's scores while the softmax warps work on this one; in-order execution of the MMAs is what makes the
-// score buffer (aliased by P hi) safe to overwrite two blocks later.
+// The score matrix never leaves the SM.  The scores run up to two blocks ahead of the softmax warps; the score
+// buffer (aliased by P hi) of block j is overwritten by the scores of block j + 2 only once the P.V product that
+// read it has retired (its completion barrier is what the score issuer waits for).
 #include "sdpa.cuh"
 
 #include "gemm_tc.cuh"
@@ -40,7 +41,7 @@
 
 namespace axb {
 
-static constexpr int TQ = 128, TKV = 128, ST_THREADS = 320;
+static constexpr int TQ = 128, TKV = 128, ST_THREADS = 352;
 static constexpr int ST_HEADER = 1024;
 static constexpr int SLAB = 128 * 128;  // bytes of one 32-column slab of a 128-row tile
 
@@ -238,7 +239,7 @@ __global__ void __launch_bounds__(ST_THREADS, 1) sdpa_tc_kernel(const __grid_con
             }
             if (!ok) report_err(a.err, SERR_PRODUCER);
         }
-    } else if (warp >= 6) {
+    } else if (warp >= 6 && warp < 10) {
         // ---------------------------------------------------------- converters
         // lo = tf32(x - (x cut to tf32)) at the same offset of the lo plane.  x itself stays where TMA put it and
         // serves as the hi operand: the tensor core ignores the 13 low mantissa bits of a tf32 container
@@ -280,8 +281,11 @@ __global__ void __launch_bounds__(ST_THREADS, 1) sdpa_tc_kernel(const __grid_con
             mbar_arrive(bar(B_V_FULL));
         }
         if (!ok) report_err(a.err, SERR_CONVERT);
-    } else if (warp == 5) {
-        // ---------------------------------------------------------- MMA issuer
+    } else if (warp == 5 || warp == 10) {
+        // --------------------------------------------------------- MMA issuers
+        // Two issuing threads: warp 5 the score products, warp 10 the P.V products.  A tcgen05.mma of this size costs the
+        // issuing thread more time than the tensor pipe (time stamps: 75 cycles per score MMA, 58 per P.V MMA with the
+        // pipe 39 % busy), so one thread issuing both kinds in turn was one of the loop's long chains.
         if (lane == 0) {
             const uint64_t desc_k = smem_desc_kmajor(0, 128);
             const uint64_t desc_mn = smem_desc_mnmajor_sw128_32b(0, SLAB, 512);
@@ -327,27 +331,28 @@ __global__ void __launch_bounds__(ST_THREADS, 1) sdpa_tc_kernel(const __grid_con
                 tc_commit(bar(B_O_FULL + b));
                 tc_commit(bar(B_V_EMPTY));
             };
-            bool ok = mbar_wait_bounded(bar(B_Q_FULL), 0) && mbar_wait_bounded(bar(B_K_FULL), 0);
-            if (ok) {
-                tc_fence_after_sync();
-                issue_qk(0);
-            }
-            for (int j = 0; ok && j < nb; ++j) {
-                if (j + 1 < nb) {
-                    // the score buffer of block j+1 held P hi of block j-1: its P.V was issued before this
-                    // point and MMAs execute in order, so nothing else has to be waited for
-                    ok = mbar_wait_bounded(bar(B_K_FULL), (j + 1) & 1);
+            bool ok = true;
+            if (warp == 5) {
+                ok = mbar_wait_bounded(bar(B_Q_FULL), 0);
+                for (int j = 0; ok && j < nb; ++j) {
+                    // score buffer j % 2 held P hi of block j - 2, the A operand of that block's P.V, which the other
+                    // thread issues: wait until it has retired
+                    if (j >= 2) ok = mbar_wait_bounded(bar(B_O_FULL + (j & 1)), ((j - 2) >> 1) & 1);
+                    ok = ok && mbar_wait_bounded(bar(B_K_FULL), j & 1);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    issue_qk(j + 1);
+                    issue_qk(j);
                 }
-                const int b = j & 1, n = j >> 1;
-                ok = mbar_wait_bounded(bar(B_P_FULL + b), n & 1);
-                ok = ok && mbar_wait_bounded(bar(B_V_FULL), j & 1);
-                ok = ok && (j < 2 || mbar_wait_bounded(bar(B_O_EMPTY + b), (n - 1) & 1));
-                if (!ok) break;
-                tc_fence_after_sync();
-                issue_pv(j);
+            } else {
+                for (int j = 0; ok && j < nb; ++j) {
+                    const int b = j & 1, n = j >> 1;
+                    ok = mbar_wait_bounded(bar(B_P_FULL + b), n & 1);
+                    ok = ok && mbar_wait_bounded(bar(B_V_FULL), j & 1);
+                    ok = ok && (j < 2 || mbar_wait_bounded(bar(B_O_EMPTY + b), (n - 1) & 1));
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_pv(j);
+                }
             }
             if (!ok) report_err(a.err, SERR_MMA);
         }
