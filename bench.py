@@ -405,6 +405,11 @@ def headline(ctx, args):
     def e2e_pipelined():
         eng.gemm_host(hA, hB, hC)   # the host-operand entry: chunked uploads overlap the GEMM and the download
 
+    # the host-side ceiling of this step: a plain pinned upload of one operand on every rank at the same time (the ranks
+    # of one box share the host's memory and PCIe root ports), max over ranks
+    ms_up, _ = ctx.timed(lambda: eng.memcpy_h2d(A, hA.data_ptr(), nbytes), 3, 1)
+    h2d_gbs = nbytes / (ms_up / 3 * 1e-3) / 1e9
+
     e2e_steps = max(1, min(K, 8))
     ms_serial, _ = ctx.timed(e2e_serial, e2e_steps, 1)
     ms_e2e, per_e2e = ctx.timed(e2e_pipelined, e2e_steps, 1)
@@ -418,7 +423,11 @@ def headline(ctx, args):
            "parity_checked": e2e_same, "parity": "sampled rows bit-identical to the device-resident call",
            "serial_value": ctx.world * FLOP_HEADLINE / (ms_serial / e2e_steps * 1e-3) / 1e12,
            "serial_ms_per_step": ms_serial / e2e_steps,
-           "serial_api": "axb_memcpy_h2d x2 + axb_gemm + axb_memcpy_d2h, one after the other (the vtable's order)"}
+           "serial_api": "axb_memcpy_h2d x2 + axb_gemm + axb_memcpy_d2h, one after the other (the vtable's order)",
+           # what the host delivers: pinned H2D rate per GPU with all ranks uploading at once (slowest rank), and the
+           # step time that rate alone allows (the step uploads 2 operands)
+           "h2d_gbs_per_gpu_all_ranks_at_once": h2d_gbs, "h2d_gbs_aggregate": h2d_gbs * ctx.world,
+           "upload_floor_ms": 2 * nbytes / (h2d_gbs * 1e9) * 1e3}
     del hA, hB, hC
     line = {
         "metric": "gemm_fp32_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": ctx.world, "steps": K, "warmup": W,
