@@ -842,7 +842,7 @@ def run_suite(ctx, names, shared):
 def compact(entry):
     """The few numbers of a suite record that belong in the headline line."""
     keep = {k: entry.get(k) for k in ("name", "value", "unit", "ms_per_step", "ms_median", "ms_min", "kernel_ms", "kernel_ms_min",
-                                      "parity_checked", "scaling", "error") if entry.get(k) is not None}
+                                      "graph_ms_per_call", "parity_checked", "scaling", "error") if entry.get(k) is not None}
     if "unit" in keep:
         keep["unit"] = keep["unit"].split(" (")[0]
     r = entry.get("roofline")
