@@ -254,6 +254,20 @@ __global__ void __launch_bounds__(ST_THREADS) skinny_tma_kernel(const __grid_con
                 }
         }
         __syncthreads();
+        if (a.ksplit > 1 && a.cluster) {
+            // the common case keeps the strip sums in shared memory for the cluster hand-over: four columns per thread
+            // and pass (128-bit loads of the eight warp sums, one 128-bit store)
+            for (int o4 = tid; o4 < RM * (COLS / 4); o4 += ST_THREADS) {
+                const int mi = o4 / (COLS / 4), c = (o4 - mi * (COLS / 4)) * 4;
+                float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int w = 0; w < ST_CONSUMERS; ++w) {
+                    const float4 v = *reinterpret_cast<const float4 *>(red + (w * RM + mi) * COLS + c);
+                    s4.x += v.x; s4.y += v.y; s4.z += v.z; s4.w += v.w;
+                }
+                *reinterpret_cast<float4 *>(xs + (m0 + mi) * COLS + c) = s4;
+            }
+        } else
         for (int o = tid; o < RM * COLS; o += ST_THREADS) {
             const int mi = o / COLS, c = o - mi * COLS;
             const int m = m0 + mi;
@@ -283,6 +297,16 @@ __global__ void __launch_bounds__(ST_THREADS) skinny_tma_kernel(const __grid_con
         // [ksplit][per_owner], behind the X slice: a peer that finishes early pushes while this CTA still reads X
         float *inbox = xs + skinny_tma_x_floats(MT, a.kchunk);
         const uint32_t me = cluster_cta_rank();
+        if (((ncols | per_owner) & 3) == 0) {
+            // whole strips: four outputs per remote store (an owner's share and a row both start at multiples of four)
+            for (int o = tid * 4; o < total; o += ST_THREADS * 4) {
+                const int m = o / ncols, c = o - m * ncols;
+                const int owner = o / per_owner, idx = o - owner * per_owner;
+                const uint32_t dst = map_to_cta(smem_u32(inbox + (int)me * per_owner + idx), (uint32_t)owner);
+                const float4 v = *reinterpret_cast<const float4 *>(xs + m * COLS + c);
+                asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+            }
+        } else
         for (int o = tid; o < total; o += ST_THREADS) {
             const int m = o / ncols, c = o - m * ncols;
             const int owner = o / per_owner, idx = o - owner * per_owner;
