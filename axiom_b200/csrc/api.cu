@@ -748,6 +748,30 @@ extern "C" int axb_gemm_prepared(const float *A, const axb_weight *W, const floa
                        &W->op);
 }
 
+extern "C" int axb_gemm_prepared_scatter(const float *A, int chunks, int64_t chunk_k, const axb_weight *W, const float *bias,
+                                         float *C, float *const *C_more, int n_more, int64_t M, float alpha, float beta, int act)
+{
+    if (!W) return fail(AXB_ERR_NULL_ARG, "gemm_prepared_scatter: NULL weight");
+    if (W->trans) return fail(AXB_ERR_INVALID_SHAPE, "gemm_prepared_scatter: the weight must be prepared from its [K, N] form");
+    if (chunks < 0 || (chunks > 0 && (chunk_k < 1 || (chunk_k % 4) != 0 || (int64_t)chunks * chunk_k != W->K)))
+        return fail(AXB_ERR_INVALID_SHAPE, "gemm_prepared_scatter: chunks * chunk_k must equal the weight's K, chunk_k a multiple of 4");
+    if (M < 0) return fail(AXB_ERR_INVALID_SHAPE, "gemm_prepared_scatter: negative dimension");
+    if (M == 0) return AXB_OK;
+    if (!A || !C || (n_more > 0 && !C_more)) return fail(AXB_ERR_NULL_ARG, "gemm_prepared_scatter: NULL operand");
+    if (n_more < 0 || n_more > TC_MAX_EXTRA) return fail(AXB_ERR_INVALID_SHAPE, "gemm_prepared_scatter: at most %d extra destinations", TC_MAX_EXTRA);
+    for (int i = 0; i < n_more; ++i)
+        if (!C_more[i]) return fail(AXB_ERR_NULL_ARG, "gemm_prepared_scatter: NULL destination %d", i);
+    if (act < AXB_ACT_NONE || act > AXB_ACT_GELU) return fail(AXB_ERR_INVALID_SHAPE, "gemm_prepared_scatter: unknown activation %d", act);
+    if (M > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "gemm_prepared_scatter: dimension exceeds 2^31-1");
+    int st = ensure_ready();
+    if (st) return st;
+    if (W->device != cur().device) return fail(AXB_ERR_BACKEND, "gemm_prepared_scatter: the weight was prepared on device %d", W->device);
+    if (W->mode != cur().fp32_mode)
+        return fail(AXB_ERR_BACKEND, "gemm_prepared_scatter: the weight was prepared in fp32 mode %d, the engine is in mode %d", W->mode, cur().fp32_mode);
+    return gemm_tc_f32(A, W->src, bias, C, M, W->N, W->K, 0, 0, alpha, beta, act, C_more, n_more, chunks > 0 ? chunk_k : 0,
+                       chunks > 0 ? M * chunk_k : 0, nullptr, nullptr, &W->op);
+}
+
 // C_host = A_host . B_host with the transfers pipelined against the tensor-core work: B goes up first and is
 // split once; A goes up in row chunks on a copy stream, each chunk is split and multiplied as soon as it has
 // landed, and its rows of C go back on a second copy stream while the next chunk is in flight.  Row chunks of

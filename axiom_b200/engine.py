@@ -27,7 +27,7 @@ EXPORTS = [
     "axb_skinny_gemm_static", "axb_skinny_gemm_static_error", "axb_gemm_bias_act_scatter", "axb_gemm_gathered_scatter", "axb_ipc_get_handle", "axb_ipc_open_handle",
     "axb_ipc_close_handle",
     "axb_bias_add", "axb_relu", "axb_gelu", "axb_qgemm_w8a32", "axb_qgemm_w8a8", "axb_quantize_rows",
-    "axb_sdpa_fwd", "axb_kv_cache_append", "axb_kv_cache_attend", "axb_qkv_head_gemm", "axb_sdpa_bwd", "axb_conv_gemm", "axb_conv_gemm_batched", "axb_qdense_w8a32",
+    "axb_sdpa_fwd", "axb_kv_cache_append", "axb_kv_cache_attend", "axb_qkv_head_gemm", "axb_sdpa_bwd", "axb_conv_gemm", "axb_conv_gemm_batched", "axb_gemm_prepared_scatter", "axb_qdense_w8a32",
     "axb_qgemm_w8a32_qw", "axb_bias_add_nd", "axb_head_interleave_qkv_split", "axb_head_interleave", "axb_head_deinterleave",
     "axb_head_deinterleave_qkv_merge", "axb_qkv_cache_build", "axb_bias_cache_build", "axb_pointer_on_device",
     "axb_weight_prepare", "axb_weight_release", "axb_gemm_prepared",
@@ -196,6 +196,14 @@ class Engine:
         arr = (C.c_void_p * max(len(more), 1))(*[(_ptr(m).value if m is not None else None) for m in more])
         self._check(self.lib.axb_gemm_gathered_scatter(_ptr(A_gathered), int(chunks), _i64(chunk_k), _ptr(B), _ptr(bias), _ptr(out),
                                                        arr, len(more), _i64(M), _i64(N), _f(alpha), _f(beta), ACT[act]))
+        return out
+
+    def gemm_prepared_scatter(self, A, chunks, chunk_k, weight, bias, out, more, M, alpha=1.0, beta=0.0, act="none"):
+        """gemm_bias_act_scatter (chunks = 0, A a plain [M, K] matrix) or gemm_gathered_scatter (A a [chunks][M][chunk_k]
+        gather buffer) with a weight prepared by weight_prepare."""
+        arr = (C.c_void_p * max(len(more), 1))(*[(_ptr(m).value if m is not None else None) for m in more])
+        self._check(self.lib.axb_gemm_prepared_scatter(_ptr(A), int(chunks), _i64(chunk_k), weight, _ptr(bias), _ptr(out), arr,
+                                                       len(more), _i64(M), _f(alpha), _f(beta), ACT[act]))
         return out
 
     def storage_alloc(self, nbytes):

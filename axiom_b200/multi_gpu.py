@@ -59,27 +59,39 @@ class RowShardedMLP:
 class ColumnShardedMLP:
     """The same chain with every layer's output columns split over the ranks and one all-gather per layer."""
 
-    def __init__(self, engine, weight_slabs, bias_slabs, world, rank, all_gather, act="gelu"):
+    def __init__(self, engine, weight_slabs, bias_slabs, world, rank, all_gather, act="gelu", prepare=False):
         """weight_slabs[l]: this rank's [K_l, N_l/g] column slab of layer l (contiguous); bias_slabs[l]: [N_l/g].
-        all_gather(dst[g, M, n], src[M, n]) performs the collective (torch.distributed.all_gather_into_tensor)."""
+        all_gather(dst[g, M, n], src[M, n]) performs the collective (torch.distributed.all_gather_into_tensor).
+        prepare: keep every slab's tensor-core operand planes (the slabs must then stay unchanged until close())."""
         self.engine, self.world, self.rank, self.act = engine, world, rank, act
         self.weight_slabs, self.bias_slabs, self.all_gather = list(weight_slabs), list(bias_slabs), all_gather
+        self.prepared = [engine.weight_prepare(W) for W in self.weight_slabs] if prepare else None
+
+    def close(self):
+        for w in self.prepared or []:
+            self.engine.weight_release(w)
+        self.prepared = None
 
     def forward(self, x_full, new_empty):
         """x_full: the full [M, K_0] input on every rank.  Returns the gathered [g, M, N_last/g] output."""
         g = self.world
         gathered = None
-        for W, b in zip(self.weight_slabs, self.bias_slabs):
+        for l, (W, b) in enumerate(zip(self.weight_slabs, self.bias_slabs)):
             n = W.shape[1]
             if gathered is None:
                 M, K = x_full.shape
                 slab = new_empty((M, n))
-                self.engine.gemm_bias_act(x_full, W, b, slab, M, n, K, act=self.act)
+                if self.prepared is not None:
+                    self.engine.gemm_prepared(x_full, self.prepared[l], b, slab, M, act=self.act)
+                else:
+                    self.engine.gemm_bias_act(x_full, W, b, slab, M, n, K, act=self.act)
             else:
                 # the previous layer's gather buffer [g][M][k] is read in place as the [M, g*k] operand
                 _, M, kc = gathered.shape
                 slab = new_empty((M, n))
-                if hasattr(self.engine, "gemm_gathered_scatter"):
+                if self.prepared is not None:
+                    self.engine.gemm_prepared_scatter(gathered, g, kc, self.prepared[l], b, slab, [], M, act=self.act)
+                elif hasattr(self.engine, "gemm_gathered_scatter"):
                     self.engine.gemm_gathered_scatter(gathered, g, kc, W, b, slab, [], M, n, act=self.act)
                 else:   # engines without the gathered-operand entry: g accumulating calls over the K-chunks
                     for c in range(g):
@@ -110,10 +122,12 @@ class PeerScatterColumnMLP:
     buffers of all layers but the last; with a single layer the caller must not start the next step before
     its peers have consumed the output, e.g. by a barrier of its own)."""
 
-    def __init__(self, engine, weight_slabs, bias_slabs, world, rank, batch, dist, act="gelu"):
+    def __init__(self, engine, weight_slabs, bias_slabs, world, rank, batch, dist, act="gelu", prepare=False):
         import torch
         self.engine, self.world, self.rank, self.act, self.dist = engine, world, rank, act, dist
         self.weight_slabs, self.bias_slabs, self.batch = list(weight_slabs), list(bias_slabs), batch
+        # prepare: the slabs' operand planes are made once (the slabs must then stay unchanged until close())
+        self.prepared = [engine.weight_prepare(W) for W in self.weight_slabs] if prepare else None
         self._token = torch.zeros(1, device="cuda")
         self.local, self.peers, self._opened = [], [], []
         for W in self.weight_slabs:
@@ -144,7 +158,10 @@ class PeerScatterColumnMLP:
             slab = new_empty((M, n))
             # every rank's gather buffer, at the slab this rank owns
             dests = [p + self.rank * M * n * 4 for p in self.peers[l]]
-            if l == 0:
+            if self.prepared is not None:
+                src, chunks, kc = (x_full, 0, 0) if l == 0 else (self.local[l - 1], g, prev_n)
+                self.engine.gemm_prepared_scatter(src, chunks, kc, self.prepared[l], b, slab, dests, M, act=self.act)
+            elif l == 0:
                 self.engine.gemm_bias_act_scatter(x_full, W, b, slab, dests, M, n, x_full.shape[1], act=self.act)
             else:
                 self.engine.gemm_gathered_scatter(self.local[l - 1], g, prev_n, W, b, slab, dests, M, n, act=self.act)
@@ -167,6 +184,9 @@ class PeerScatterColumnMLP:
             eng_stream.wait_stream(cur)
 
     def close(self):
+        for w in self.prepared or []:
+            self.engine.weight_release(w)
+        self.prepared = None
         self.dist.barrier()
         for q in self._opened:
             self.engine.ipc_close_handle(q)

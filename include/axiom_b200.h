@@ -158,6 +158,12 @@ AXB_API int axb_gemm_bias_act_scatter(const float *A, const float *B, const floa
 AXB_API int axb_gemm_gathered_scatter(const float *A_gathered, int chunks, int64_t chunk_k, const float *B,
                                       const float *bias, float *C, float *const *C_more, int n_more, int64_t M,
                                       int64_t N, float alpha, float beta, int act);
+/* Both of the above with the weight's operand planes prepared once (axb_weight_prepare from the [K, N] form): the
+   tensor-core GEMM whose epilogue also stores to C_more, reading A either as a plain [M, K] matrix (chunks = 0) or out
+   of a gather buffer [chunks][M][chunk_k] with chunks * chunk_k = K.  Same bits as the unprepared calls. */
+AXB_API int axb_gemm_prepared_scatter(const float *A, int chunks, int64_t chunk_k, const axb_weight_t *W, const float *bias,
+                                      float *C, float *const *C_more, int n_more, int64_t M, float alpha, float beta,
+                                      int act);
 /* Share a device allocation made with axb_storage_alloc with the other processes of the box:
    the owner exports a 64-byte handle, a peer opens it (peer access is enabled on first use) and gets a
    pointer valid on ITS device context; close before the owner frees. */

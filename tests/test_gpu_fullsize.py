@@ -156,3 +156,30 @@ def test_gathered_operand_gemm(engine, oracle):
                          act="relu")
     assert torch.equal(out, want) and torch.equal(extra, want)
     assert nerr(out.cpu().numpy(), np.maximum(oracle.gemm_f64(A, B) + bias, 0)) <= 1e-5
+
+
+@pytest.mark.parametrize("shape", [(300, 200, 4, 96), (1024, 1024, 8, 128), (2560, 2560, 2, 256)])
+def test_prepared_weight_scatter(engine, oracle, shape):
+    """axb_gemm_prepared_scatter (the weight's operand planes made once) gives the bits of axb_gemm_bias_act on the same
+    operands, from a plain left operand and from a [g][M][kc] gather buffer, in C and in every extra destination."""
+    M, N, g, kc = shape
+    K = g * kc
+    A, B, bias = oracle.uniform((M, K), 7), oracle.uniform((K, N), 13), oracle.uniform((N,), 29)
+    Ad, Bd, bd = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda(), torch.from_numpy(bias).cuda()
+    want = torch.empty((M, N), device="cuda")
+    engine.gemm_bias_act(Ad, Bd, bd, want, M, N, K, act="gelu")
+    w = engine.weight_prepare(Bd)
+    try:
+        out, extra = torch.full((M, N), float("nan"), device="cuda"), torch.full((M, N), float("nan"), device="cuda")
+        engine.gemm_prepared_scatter(Ad, 0, 0, w, bd, out, [extra], M, act="gelu")
+        assert torch.equal(out, want) and torch.equal(extra, want)
+        gathered = torch.from_numpy(np.ascontiguousarray(A.reshape(M, g, kc).transpose(1, 0, 2))).cuda()
+        out2, extra2 = torch.full((M, N), float("nan"), device="cuda"), torch.full((M, N), float("nan"), device="cuda")
+        engine.gemm_prepared_scatter(gathered, g, kc, w, bd, out2, [extra2], M, act="gelu")
+        assert torch.equal(out2, want) and torch.equal(extra2, want)
+        from axiom_b200.engine import EngineError
+        with pytest.raises(EngineError):
+            engine.gemm_prepared_scatter(gathered, g, kc + 4, w, bd, out2, [], M)      # chunks * chunk_k != K
+    finally:
+        engine.weight_release(w)
+    assert engine.device_error() == 0
