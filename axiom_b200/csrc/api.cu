@@ -1392,6 +1392,35 @@ extern "C" int axb_qkv_head_gemm(const float *X, const float *Wqkv, const float 
     return e ? cuda_fail("qkv_head_gemm: head split", e) : AXB_OK;
 }
 
+extern "C" int axb_dattn_head_gemm_nt(const float *dout, const float *Wo, int64_t B, int64_t S, int64_t H, int64_t dk, float *dO_head)
+{
+    if (!dout || !Wo || !dO_head) return fail(AXB_ERR_NULL_ARG, "dattn_head_gemm_nt: NULL");
+    if (B < 0 || S < 0 || H <= 0 || dk <= 0) return fail(AXB_ERR_INVALID_SHAPE, "dattn_head_gemm_nt: bad shape");
+    const int64_t rows = B * S, D = H * dk;
+    if (rows > INT32_MAX || D > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "dattn_head_gemm_nt: dimension exceeds 2^31-1");
+    int st = ensure_ready();
+    if (st) return st;
+    if (rows == 0) return AXB_OK;
+    float *outs[3] = { dO_head, dO_head, dO_head };   // one D-wide column block: only the first destination is used
+    if (rows > 32 && dk % 32 == 0) {
+        // one launch: dout . Wo^T on the tensor cores, the epilogue stores head-major
+        const int64_t shape[3] = { S, H, dk };
+        return gemm_tc_f32(dout, Wo, nullptr, nullptr, rows, D, D, 0, 1, 1.0f, 0.0f, AXB_ACT_NONE, nullptr, 0, 0, 0, shape, outs);
+    }
+    const size_t need = (size_t)rows * D * sizeof(float);
+    if (need > cur().aux_bytes) {
+        if (cur().aux) { cudaStreamSynchronize(cur().stream); cudaFree(cur().aux); cur().aux = nullptr; cur().aux_bytes = 0; }
+        cudaError_t e = cudaMalloc(&cur().aux, need);
+        if (e != cudaSuccess) return fail(AXB_ERR_ALLOC, "dattn_head_gemm_nt: scratch of %zu bytes: %s", need, cudaGetErrorString(e));
+        cur().aux_bytes = need;
+    }
+    st = axb_gemm_bias_act(dout, Wo, nullptr, (float *)cur().aux, rows, D, D, 0, 1, 1.0f, 0.0f, AXB_ACT_NONE);
+    if (st) return st;
+    int e = launch_head_layout(true, (float *)cur().aux, outs, nullptr, 1, B, S, H, dk, cur().sm_count, cur().stream);
+    cur().launches++;
+    return e ? cuda_fail("dattn_head_gemm_nt: head layout", e) : AXB_OK;
+}
+
 // ------------------------------------------------------- attention layout passes
 
 static int head_layout_call(const char *what, bool to_head, const float *flat, float *const head[3], const float *bias,

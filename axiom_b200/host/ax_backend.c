@@ -267,6 +267,22 @@ static axb_status be_qkv_head_gemm(const axb_ax_tensor_t *X, const axb_ax_tensor
     return done(axb_qkv_head_gemm(fptr(X), fptr(Wqkv), bias_p, B, S, H, dk, fptr(Qh), fptr(Kh), fptr(Vh)));
 }
 
+/* shape rules of the CPU implementation (src/compute/backends/cpu_opt.c:6527-6560) */
+static axb_status be_dattn_head_gemm_nt(const axb_ax_tensor_t *dout, const axb_ax_tensor_t *Wo, int64_t B, int64_t S, int64_t H,
+                                        int64_t dk, axb_ax_tensor_t *dO_head)
+{
+    axb_status st;
+    if ((st = check_f32(dout, "dattn_head_gemm_nt", 2)) || (st = check_f32(Wo, "dattn_head_gemm_nt", 2)) ||
+        (st = check_f32(dO_head, "dattn_head_gemm_nt", 3)))
+        return st;
+    const int64_t D = H * dk;
+    if (dout->shape[0] != B * S || dout->shape[1] != D || Wo->shape[0] != D || Wo->shape[1] != D)
+        return report(ST_SHAPE, "dattn_head_gemm_nt: dout must be [B*S, H*dk] and Wo [H*dk, H*dk]");
+    if (dO_head->shape[0] != B * H || dO_head->shape[1] != S || dO_head->shape[2] != dk)
+        return report(ST_SHAPE, "dattn_head_gemm_nt: dO_head must be [B*H, S, dk]");
+    return done(axb_dattn_head_gemm_nt(fptr(dout), fptr(Wo), B, S, H, dk, fptr(dO_head)));
+}
+
 /* shape rules of the reference's CUDA implementation (src/compute/backends/cuda/ops_conv.cu:113-142); params->input
    is a raw pointer into the (device-resident) batched input, as the conv layer passes it */
 static axb_status be_conv_gemm(const axb_ax_tensor_t *weight, const axb_ax_conv_params_t *params, axb_ax_tensor_t *out)
@@ -415,6 +431,7 @@ static const axb_ax_backend_ops_t ops_table = {
     .gemm_nt = be_gemm_nt,
     .gemm_tn = be_gemm_tn,
     .qkv_head_gemm = be_qkv_head_gemm,
+    .dattn_head_gemm_nt = be_dattn_head_gemm_nt,
     .gemm_relu = be_gemm_relu,
     .gemm_ex = be_gemm_ex,
     .bias_add = be_bias_add,

@@ -331,6 +331,13 @@ AXB_API int axb_sdpa_bwd(const float *Q, const float *K, const float *V, const f
    For dk % 32 == 0 the GEMM's epilogue stores head-major itself (one launch, no [B*S, 3D] intermediate). */
 AXB_API int axb_qkv_head_gemm(const float *X, const float *Wqkv, const float *bqkv, int64_t B, int64_t S, int64_t H,
                               int64_t dk, float *Qh, float *Kh, float *Vh);
+/* Slot dattn_head_gemm_nt of ax_backend_ops_t (include/axiom/internal/backend_ops.h:114-129; ax_compute_dattn_head_gemm_nt,
+   src/compute/dispatch.c:553-567; CPU implementation src/compute/backends/cpu_opt.c:6506-6600) — the backward mirror:
+     dattn = dout[B*S, D] . Wo[D, D]^T,   dO_head[B*H, S, dk] = dattn stored head-major (overwritten), D = H*dk.
+   For dk % 32 == 0 one tensor-core launch whose epilogue stores head-major (no [B*S, D] intermediate); otherwise the
+   product into scratch and the layout pass. */
+AXB_API int axb_dattn_head_gemm_nt(const float *dout, const float *Wo, int64_t B, int64_t S, int64_t H, int64_t dk,
+                                   float *dO_head);
 
 /* ---- attention layout passes and fused-parameter builders ---------------------
    The remaining attention slots of ax_cuda_extension_t (include/axiom/internal/cuda_extension.h:41-88; stock

@@ -77,7 +77,9 @@ typedef struct {
     axb_status (*qkv_head_gemm)(const axb_ax_tensor_t *X, const axb_ax_tensor_t *Wqkv, const axb_ax_tensor_t *bqkv,
                                 int64_t B, int64_t S, int64_t H, int64_t dk, axb_ax_tensor_t *Qh, axb_ax_tensor_t *Kh,
                                 axb_ax_tensor_t *Vh);   /* backend_ops.h:107-113 */
-    axb_opaque_fn dattn_head_gemm_nt, mha_output_proj_fused;
+    axb_status (*dattn_head_gemm_nt)(const axb_ax_tensor_t *dout, const axb_ax_tensor_t *Wo, int64_t B, int64_t S, int64_t H,
+                                     int64_t dk, axb_ax_tensor_t *dO_head);   /* backend_ops.h:114-129 */
+    axb_opaque_fn mha_output_proj_fused;
     axb_status (*gemm_relu)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, const axb_ax_tensor_t *bias,
                             axb_ax_tensor_t *out);
     axb_status (*gemm_ex)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, float alpha, float beta,

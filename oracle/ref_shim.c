@@ -345,6 +345,30 @@ SHIM_API int ref_device_qkv_head_gemm(const float *X, const float *Wqkv, const f
     return rc;
 }
 
+/* ax_compute_dattn_head_gemm_nt (src/compute/dispatch.c:553-567): dout[B*S, D], Wo[D, D] -> dO_head [B*H, S, dk], on the
+   CPU backend (device = 0) or through the registered backend on device tensors made by the reference (device = 1). */
+SHIM_API int ref_dattn_head_gemm_nt(const float *dout, const float *Wo, int64_t B, int64_t S, int64_t H, int64_t dk,
+                                    float *dO_head, int device)
+{
+    const int64_t D = H * dk, n = B * H * S * dk;
+    int64_t hshape[3] = { B * H, S, dk };
+    int rc = 0;
+    if (device) use_cuda(1); else ax_compute_set_backend(AX_BACKEND_CPU_SIMD);
+    ax_tensor_t *d = t2(dout, B * S, D), *w = t2(Wo, D, D), *o = ax_tensor_from_array(dO_head, hshape, 3, AX_FLOAT32);
+    if (device) { d = to_dev(d); w = to_dev(w); o = to_dev(o); }
+    if (!d || !w || !o) rc = 100;
+    if (!rc) rc = ax_compute_has_dattn_head_gemm_nt() ? (int)ax_compute_dattn_head_gemm_nt(d, w, B, S, H, dk, o) : 200;
+    if (!rc) {
+        if (device) { ax_device_synchronize(AX_DEVICE_CUDA); rc = copy_back(o, dO_head, n); }
+        else memcpy(dO_head, tdata(o), (size_t)n * sizeof(float));
+    }
+    if (d) ax_tensor_destroy(d);
+    if (w) ax_tensor_destroy(w);
+    if (o) ax_tensor_destroy(o);
+    if (device) use_cuda(0);
+    return rc;
+}
+
 /* ax_compute_qkv_head_gemm (include/axiom/compute.h:150-170) on the active CPU backend: X[B*S, D],
    Wqkv[D, 3D], bqkv[3D] or NULL -> Qh, Kh, Vh [B*H, S, dk]. */
 SHIM_API int ref_qkv_head_gemm(const float *X, const float *Wqkv, const float *bqkv, int64_t B, int64_t S,

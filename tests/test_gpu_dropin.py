@@ -125,6 +125,22 @@ def test_conv_gemm_slot(dropin, reference, oracle, geom):
     assert nerr(got, want) <= 1e-5
 
 
+@pytest.mark.parametrize("shape", [(2, 64, 4, 32), (1, 40, 3, 16), (2, 128, 4, 64)])
+def test_dattn_head_gemm_nt_slot(dropin, reference, oracle, shape):
+    """ax_compute_dattn_head_gemm_nt on device tensors made by the reference lands in the dattn_head_gemm_nt slot (one
+    tensor-core launch with a head-major epilogue for head dims that are multiples of 32, product + layout pass
+    otherwise) and equals the reference's CPU implementation."""
+    B, S, H, dk = shape
+    D = H * dk
+    dout, Wo = oracle.uniform((B * S, D), 7), oracle.normal((D, D), 13, sigma=1.0 / np.sqrt(D))
+    got, want = np.full((B * H, S, dk), np.nan, np.float32), np.zeros((B * H, S, dk), np.float32)
+    rc = dropin.ref_dattn_head_gemm_nt(p(dout), p(Wo), i64(B), i64(S), i64(H), i64(dk), p(got), 1)
+    assert rc == 0, (rc, dropin.ref_last_error())
+    assert dropin.ref_dattn_head_gemm_nt(p(dout), p(Wo), i64(B), i64(S), i64(H), i64(dk), p(want), 0) == 0
+    np.testing.assert_allclose(got, want, atol=1e-3, rtol=1e-4)
+    assert nerr(got, want) <= 1e-5
+
+
 @pytest.mark.parametrize("geom", [(3, 8, 4, 12, 12, 3, 3, 1, 1, 1, 1), (2, 16, 4, 9, 9, 3, 3, 2, 2, 0, 0), (4, 12, 6, 10, 16, 1, 1, 1, 1, 0, 0)])
 def test_conv_gemm_batched_extension_slot(dropin, reference, oracle, geom):
     """The conv_gemm_batched slot, called as the reference's conv layer calls it on a device (N samples back to back,

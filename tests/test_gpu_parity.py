@@ -533,6 +533,21 @@ def test_conv_implicit_gemm(engine, oracle, geom, mode):
     assert engine.device_error() == 0
 
 
+@pytest.mark.parametrize("shape", [(8, 1024, 16, 64), (2, 100, 5, 32), (3, 50, 4, 24), (1, 16, 2, 8), (4, 256, 8, 96)])
+def test_dattn_head_gemm_nt(engine, oracle, shape):
+    """dO_head = head-major(dout . Wo^T) against float64 (config-4 layer shape, ragged rows, head dims that are not
+    multiples of 32, a skinny input)."""
+    B, S, H, dk = shape
+    D = H * dk
+    dout, Wo = oracle.uniform((B * S, D), 7), oracle.normal((D, D), 13, sigma=1.0 / np.sqrt(D))
+    ref = oracle.gemm_f64(dout, np.ascontiguousarray(Wo.T))                                # [B*S, D]
+    want = ref.reshape(B, S, H, dk).transpose(0, 2, 1, 3).reshape(B * H, S, dk)
+    out = torch.full((B * H, S, dk), float("nan"), device="cuda")
+    engine.dattn_head_gemm_nt(dev(dout), dev(Wo), B, S, H, dk, out)
+    assert nerr(host(out), want) <= TOL_SPLIT
+    assert engine.device_error() == 0
+
+
 @pytest.mark.parametrize("geom", [(8, 256, 256, 56, 56, 3, 3, 1, 1, 1, 1),   # a ResNet stage at batch 8: one implicit GEMM, 128 x 256 tiles
                                   (3, 40, 20, 12, 20, 5, 5, 1, 1, 2, 2),      # patches of the last tile run into the next sample and past the end
                                   (5, 16, 3, 6, 8, 3, 3, 1, 1, 1, 1),         # samples smaller than one patch row
