@@ -1421,6 +1421,73 @@ extern "C" int axb_dattn_head_gemm_nt(const float *dout, const float *Wo, int64_
     return e ? cuda_fail("dattn_head_gemm_nt: head layout", e) : AXB_OK;
 }
 
+// aux scratch of at least `need` bytes (grown on demand; the stream is drained before the old block is freed)
+static int ensure_aux(const char *what, size_t need)
+{
+    if (need <= cur().aux_bytes) return AXB_OK;
+    if (cur().aux) { cudaStreamSynchronize(cur().stream); cudaFree(cur().aux); cur().aux = nullptr; cur().aux_bytes = 0; }
+    cudaError_t e = cudaMalloc(&cur().aux, need);
+    if (e != cudaSuccess) return fail(AXB_ERR_ALLOC, "%s: scratch of %zu bytes: %s", what, need, cudaGetErrorString(e));
+    cur().aux_bytes = need;
+    return AXB_OK;
+}
+
+// dW{q,k,v} += x^T . dQKV[:, {0,1,2}*D : +D]; `scratch_off` bytes at the start of aux are in use by the caller
+static int dwqkv_split_acc_any(const char *what, const float *x_flat, const float *dQKV, int64_t rows, int64_t D, float *dWq,
+                               float *dWk, float *dWv, size_t scratch_off)
+{
+    float *outs[3] = { dWq, dWk, dWv };
+    if (D % 32 == 0) {
+        // one launch: x^T . dQKV on the tensor cores; the epilogue treats the three D-wide column blocks as three
+        // destinations (the head-major scatter with one head of D columns and D rows per "batch") and adds to them
+        const int64_t shape[3] = { D, 1, D };
+        return gemm_tc_f32(x_flat, dQKV, nullptr, nullptr, D, 3 * D, rows, 1, 0, 1.0f, 1.0f, AXB_ACT_NONE, nullptr, 0, 0, 0, shape, outs);
+    }
+    // other widths: the [D, 3D] product into scratch, then one pass that adds its column blocks to the gradients
+    const size_t need = scratch_off + (size_t)D * 3 * D * sizeof(float);
+    int st = ensure_aux(what, need);
+    if (st) return st;
+    float *prod = reinterpret_cast<float *>(reinterpret_cast<char *>(cur().aux) + scratch_off);
+    st = axb_gemm_bias_act(x_flat, dQKV, nullptr, prod, D, 3 * D, rows, 1, 0, 1.0f, 0.0f, AXB_ACT_NONE);
+    if (st) return st;
+    int e = launch_head_layout(true, prod, outs, nullptr, 3, 1, D, 1, D, cur().sm_count, cur().stream, true);
+    cur().launches++;
+    return e ? cuda_fail(what, e) : AXB_OK;
+}
+
+extern "C" int axb_dwqkv_split_acc(const float *x_flat, const float *dQKV, int64_t rows, int64_t D, float *dWq, float *dWk,
+                                   float *dWv)
+{
+    if (!x_flat || !dQKV || !dWq || !dWk || !dWv) return fail(AXB_ERR_NULL_ARG, "dwqkv_split_acc: NULL");
+    if (rows < 0 || D <= 0) return fail(AXB_ERR_INVALID_SHAPE, "dwqkv_split_acc: bad shape");
+    if (rows > INT32_MAX || 3 * D > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "dwqkv_split_acc: dimension exceeds 2^31-1");
+    int st = ensure_ready();
+    if (st) return st;
+    if (rows == 0) return AXB_OK;   // an empty sum: the gradients keep their values
+    return dwqkv_split_acc_any("dwqkv_split_acc", x_flat, dQKV, rows, D, dWq, dWk, dWv, 0);
+}
+
+extern "C" int axb_dwqkv_split_acc_hm(const float *x_flat, const float *dQh, const float *dKh, const float *dVh, int64_t B,
+                                      int64_t S, int64_t H, int64_t dk, float *dWq, float *dWk, float *dWv)
+{
+    if (!x_flat || !dQh || !dKh || !dVh || !dWq || !dWk || !dWv) return fail(AXB_ERR_NULL_ARG, "dwqkv_split_acc_hm: NULL");
+    if (B < 0 || S < 0 || H <= 0 || dk <= 0) return fail(AXB_ERR_INVALID_SHAPE, "dwqkv_split_acc_hm: bad shape");
+    const int64_t rows = B * S, D = H * dk;
+    if (rows > INT32_MAX || 3 * D > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "dwqkv_split_acc_hm: dimension exceeds 2^31-1");
+    int st = ensure_ready();
+    if (st) return st;
+    if (rows == 0) return AXB_OK;
+    // the three head-major gradients are gathered into the flat [rows, 3D] matrix the contraction walks
+    const size_t merged = round_up((size_t)rows * 3 * D * sizeof(float), 256);
+    st = ensure_aux("dwqkv_split_acc_hm", merged + (D % 32 == 0 ? 0 : (size_t)D * 3 * D * sizeof(float)));
+    if (st) return st;
+    float *heads[3] = { const_cast<float *>(dQh), const_cast<float *>(dKh), const_cast<float *>(dVh) };
+    int e = launch_head_layout(false, (float *)cur().aux, heads, nullptr, 3, B, S, H, dk, cur().sm_count, cur().stream);
+    cur().launches++;
+    if (e) return cuda_fail("dwqkv_split_acc_hm: merge", e);
+    return dwqkv_split_acc_any("dwqkv_split_acc_hm", x_flat, (const float *)cur().aux, rows, D, dWq, dWk, dWv, merged);
+}
+
 // ------------------------------------------------------- attention layout passes
 
 static int head_layout_call(const char *what, bool to_head, const float *flat, float *const head[3], const float *bias,

@@ -12,8 +12,9 @@ int launch_bias_add(const float *in, const float *bias, int axis, float *out, in
                     int sm_count, cudaStream_t st, int64_t period = 0);
 
 // head_layout.cu: rows of dk floats between the flat [B*S, nslot*H*dk] matrix and head-major [B*H, S, dk] buffers.
-// to_head: flat -> head[0..nslot) (+ bias[nslot*H*dk] when given); otherwise head[0..nslot) -> flat.
+// to_head: flat -> head[0..nslot) (+ bias[nslot*H*dk] when given; accumulate adds to what head[] holds);
+// otherwise head[0..nslot) -> flat.
 int launch_head_layout(bool to_head, float *flat, float *const head[3], const float *bias, int nslot, int64_t B,
-                       int64_t S, int64_t H, int64_t dk, int sm_count, cudaStream_t st);
+                       int64_t S, int64_t H, int64_t dk, int sm_count, cudaStream_t st, bool accumulate = false);
 
 }  // namespace axb

@@ -880,8 +880,7 @@ static int launch_common(int kind, const TcOperand &A, const TcOperand &B, const
     if (ep.hs_dk > 0) {
         ka.hs_dk = ep.hs_dk; ka.hs_S = ep.hs_S; ka.hs_H = ep.hs_H;
         for (int i = 0; i < 3; ++i) ka.hs_out[i] = ep.hs_out[i];
-        ka.beta = 0.0f;
-        ka.n_extra = 0;
+        ka.n_extra = 0;   // beta applies to the scattered destinations (store_piece_f32 reads back where it writes)
     }
     if (cv) {
         const int es = kind == KIND_TF32 ? 4 : 2;

@@ -33,7 +33,7 @@ struct TcEpilogue {
     // rank's output slab straight into its peers' gather buffers over NVLink
     float *c_extra[TC_MAX_EXTRA];
     int n_extra;
-    // fp32 kinds, head-major scatter (hs_dk > 0; C, ldc, beta and c_extra are then unused): output column
+    // fp32 kinds, head-major scatter (hs_dk > 0; C, ldc and c_extra are then unused, beta reads the scattered place): output column
     // which*H*dk + h*dk + d of row b*S + s goes to hs_out[which][(b*H + h)*S + s][d] — the [B*H, S, dk] layout of
     // the attention kernels.  hs_dk must be a multiple of 32 (a 32-column store never straddles two heads).
     int hs_dk = 0, hs_S = 0, hs_H = 0;

@@ -15,6 +15,7 @@ struct HeadLayoutArgs {
     const float *bias;  // [nslot*D] or nullptr (split direction only)
     int64_t rows;       // B*S
     int nslot, S, H, dk;
+    int accumulate;     // split direction only: add to what the head-major side holds instead of overwriting it
 };
 
 // TO_HEAD: flat -> head-major (+ bias); otherwise head-major -> flat.  VEC = floats per access (4 or 1).
@@ -42,12 +43,18 @@ __global__ void __launch_bounds__(256) head_layout_kernel(HeadLayoutArgs a)
                     const float4 bv = __ldg(reinterpret_cast<const float4 *>(a.bias + (int64_t)which * D + (int64_t)h * a.dk + d));
                     v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
                 }
+                if (a.accumulate) {
+                    const float4 o = *reinterpret_cast<const float4 *>(hp + hi);
+                    v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+                }
                 *reinterpret_cast<float4 *>(hp + hi) = v;
             } else {
                 *reinterpret_cast<float4 *>(a.flat + fi) = *reinterpret_cast<const float4 *>(hp + hi);
             }
         } else {
-            if (TO_HEAD) hp[hi] = a.flat[fi] + (a.bias ? __ldg(a.bias + (int64_t)which * D + (int64_t)h * a.dk + d) : 0.0f);
+            if (TO_HEAD)
+                hp[hi] = a.flat[fi] + (a.bias ? __ldg(a.bias + (int64_t)which * D + (int64_t)h * a.dk + d) : 0.0f) +
+                         (a.accumulate ? hp[hi] : 0.0f);
             else a.flat[fi] = hp[hi];
         }
     }
@@ -56,9 +63,10 @@ __global__ void __launch_bounds__(256) head_layout_kernel(HeadLayoutArgs a)
 static inline bool hl_aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
 int launch_head_layout(bool to_head, float *flat, float *const head[3], const float *bias, int nslot, int64_t B,
-                       int64_t S, int64_t H, int64_t dk, int sm_count, cudaStream_t st)
+                       int64_t S, int64_t H, int64_t dk, int sm_count, cudaStream_t st, bool accumulate)
 {
     HeadLayoutArgs a;
+    a.accumulate = (accumulate && to_head) ? 1 : 0;
     a.flat = flat;
     for (int i = 0; i < 3; ++i) a.head[i] = i < nslot ? head[i] : nullptr;
     a.bias = bias;

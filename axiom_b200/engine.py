@@ -27,7 +27,7 @@ EXPORTS = [
     "axb_skinny_gemm_static", "axb_skinny_gemm_static_error", "axb_gemm_bias_act_scatter", "axb_gemm_gathered_scatter", "axb_ipc_get_handle", "axb_ipc_open_handle",
     "axb_ipc_close_handle",
     "axb_bias_add", "axb_relu", "axb_gelu", "axb_qgemm_w8a32", "axb_qgemm_w8a8", "axb_quantize_rows",
-    "axb_sdpa_fwd", "axb_kv_cache_append", "axb_kv_cache_attend", "axb_qkv_head_gemm", "axb_sdpa_bwd", "axb_conv_gemm", "axb_conv_gemm_batched", "axb_gemm_prepared_scatter", "axb_dattn_head_gemm_nt", "axb_qdense_w8a32",
+    "axb_sdpa_fwd", "axb_kv_cache_append", "axb_kv_cache_attend", "axb_qkv_head_gemm", "axb_sdpa_bwd", "axb_conv_gemm", "axb_conv_gemm_batched", "axb_gemm_prepared_scatter", "axb_dattn_head_gemm_nt", "axb_dwqkv_split_acc", "axb_dwqkv_split_acc_hm", "axb_qdense_w8a32",
     "axb_qgemm_w8a32_qw", "axb_bias_add_nd", "axb_head_interleave_qkv_split", "axb_head_interleave", "axb_head_deinterleave",
     "axb_head_deinterleave_qkv_merge", "axb_qkv_cache_build", "axb_bias_cache_build", "axb_pointer_on_device",
     "axb_weight_prepare", "axb_weight_release", "axb_gemm_prepared",
@@ -334,6 +334,16 @@ class Engine:
         """dO_head[B*H, S, dk] = head-major(dout[B*S, D] . Wo[D, D]^T)."""
         self._check(self.lib.axb_dattn_head_gemm_nt(_ptr(dout), _ptr(Wo), _i64(B), _i64(S), _i64(H), _i64(dk), _ptr(dO_head)))
         return dO_head
+
+    def dwqkv_split_acc(self, x_flat, dQKV, dWq, dWk, dWv):
+        """dW{q,k,v}[D, D] += x_flat[rows, D]^T . the three D-wide column blocks of dQKV[rows, 3D]."""
+        rows, D = x_flat.shape
+        self._check(self.lib.axb_dwqkv_split_acc(_ptr(x_flat), _ptr(dQKV), _i64(rows), _i64(D), _ptr(dWq), _ptr(dWk), _ptr(dWv)))
+
+    def dwqkv_split_acc_hm(self, x_flat, dQh, dKh, dVh, B, S, H, dk, dWq, dWk, dWv):
+        """The same with the three gradients head-major [B*H, S, dk]."""
+        self._check(self.lib.axb_dwqkv_split_acc_hm(_ptr(x_flat), _ptr(dQh), _ptr(dKh), _ptr(dVh), _i64(B), _i64(S), _i64(H),
+                                                    _i64(dk), _ptr(dWq), _ptr(dWk), _ptr(dWv)))
 
     def conv_gemm_batched(self, weight, inp, kh, kw, sh, sw, ph, pw, out):
         """weight [C_out, C_in*kh*kw], inp [N, C_in, H, W], out [N, C_out, out_h*out_w]."""

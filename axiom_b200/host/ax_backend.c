@@ -283,6 +283,49 @@ static axb_status be_dattn_head_gemm_nt(const axb_ax_tensor_t *dout, const axb_a
     return done(axb_dattn_head_gemm_nt(fptr(dout), fptr(Wo), B, S, H, dk, fptr(dO_head)));
 }
 
+/* shape rules of the CPU implementations (src/compute/backends/cpu_opt.c:6062-6119) */
+static axb_status check_dw3(const char *what, int64_t D, axb_ax_tensor_t *dWq, axb_ax_tensor_t *dWk, axb_ax_tensor_t *dWv)
+{
+    axb_status st;
+    if ((st = check_f32(dWq, what, 2)) || (st = check_f32(dWk, what, 2)) || (st = check_f32(dWv, what, 2))) return st;
+    if (dWq->shape[0] != D || dWq->shape[1] != D || dWk->shape[0] != D || dWk->shape[1] != D || dWv->shape[0] != D ||
+        dWv->shape[1] != D)
+        return report(ST_SHAPE, "dwqkv_split_acc: the three gradients must be [D, D]");
+    return 0;
+}
+
+static axb_status be_dwqkv_split_acc(const axb_ax_tensor_t *x_flat, const axb_ax_tensor_t *dQKV, axb_ax_tensor_t *dWq,
+                                     axb_ax_tensor_t *dWk, axb_ax_tensor_t *dWv)
+{
+    axb_status st;
+    if ((st = check_f32(x_flat, "dwqkv_split_acc", 2)) || (st = check_f32(dQKV, "dwqkv_split_acc", 2))) return st;
+    const int64_t rows = x_flat->shape[0], D = x_flat->shape[1];
+    if (dQKV->shape[0] != rows || dQKV->shape[1] != 3 * D)
+        return report(ST_SHAPE, "dwqkv_split_acc: dQKV must be [rows, 3*D] for x_flat [rows, D]");
+    if ((st = check_dw3("dwqkv_split_acc", D, dWq, dWk, dWv))) return st;
+    return done(axb_dwqkv_split_acc(fptr(x_flat), fptr(dQKV), rows, D, fptr(dWq), fptr(dWk), fptr(dWv)));
+}
+
+static axb_status be_dwqkv_split_acc_hm(const axb_ax_tensor_t *x_flat, const axb_ax_tensor_t *dQh, const axb_ax_tensor_t *dKh,
+                                        const axb_ax_tensor_t *dVh, int64_t B, int64_t S, int64_t H, int64_t dk,
+                                        axb_ax_tensor_t *dWq, axb_ax_tensor_t *dWk, axb_ax_tensor_t *dWv)
+{
+    axb_status st;
+    if ((st = check_f32(x_flat, "dwqkv_split_acc_hm", 2)) || (st = check_f32(dQh, "dwqkv_split_acc_hm", 3)) ||
+        (st = check_f32(dKh, "dwqkv_split_acc_hm", 3)) || (st = check_f32(dVh, "dwqkv_split_acc_hm", 3)))
+        return st;
+    const int64_t D = H * dk;
+    if (x_flat->shape[0] != B * S || x_flat->shape[1] != D)
+        return report(ST_SHAPE, "dwqkv_split_acc_hm: x_flat must be [B*S, H*dk]");
+    const axb_ax_tensor_t *hm[3] = { dQh, dKh, dVh };
+    for (int i = 0; i < 3; i++)
+        if (hm[i]->shape[0] != B * H || hm[i]->shape[1] != S || hm[i]->shape[2] != dk)
+            return report(ST_SHAPE, "dwqkv_split_acc_hm: dQh, dKh, dVh must be [B*H, S, dk]");
+    if ((st = check_dw3("dwqkv_split_acc_hm", D, dWq, dWk, dWv))) return st;
+    return done(axb_dwqkv_split_acc_hm(fptr(x_flat), fptr(dQh), fptr(dKh), fptr(dVh), B, S, H, dk, fptr(dWq), fptr(dWk),
+                                       fptr(dWv)));
+}
+
 /* shape rules of the reference's CUDA implementation (src/compute/backends/cuda/ops_conv.cu:113-142); params->input
    is a raw pointer into the (device-resident) batched input, as the conv layer passes it */
 static axb_status be_conv_gemm(const axb_ax_tensor_t *weight, const axb_ax_conv_params_t *params, axb_ax_tensor_t *out)
@@ -430,6 +473,8 @@ static const axb_ax_backend_ops_t ops_table = {
     .gemm = be_gemm,
     .gemm_nt = be_gemm_nt,
     .gemm_tn = be_gemm_tn,
+    .dwqkv_split_acc = be_dwqkv_split_acc,
+    .dwqkv_split_acc_hm = be_dwqkv_split_acc_hm,
     .qkv_head_gemm = be_qkv_head_gemm,
     .dattn_head_gemm_nt = be_dattn_head_gemm_nt,
     .gemm_relu = be_gemm_relu,

@@ -338,6 +338,19 @@ AXB_API int axb_qkv_head_gemm(const float *X, const float *Wqkv, const float *bq
    product into scratch and the layout pass. */
 AXB_API int axb_dattn_head_gemm_nt(const float *dout, const float *Wo, int64_t B, int64_t S, int64_t H, int64_t dk,
                                    float *dO_head);
+/* Slots dwqkv_split_acc and dwqkv_split_acc_hm of ax_backend_ops_t (include/axiom/internal/backend_ops.h:66-95;
+   ax_compute_dwqkv_split_acc[_hm], src/compute/dispatch.c:463-515; CPU implementations
+   src/compute/backends/cpu_opt.c:6062-6119; caller mha_backward, src/core/attention.c:805-818) — the weight gradients of
+   the fused q|k|v projection, ACCUMULATED into the three [D, D] gradients without a [D, 3D] intermediate:
+     dWq += x_flat[rows, D]^T . dQKV[rows, 3D][:, 0:D],   dWk += ... [:, D:2D],   dWv += ... [:, 2D:3D].
+   The _hm form takes the three gradients head-major (dQh, dKh, dVh each [B*H, S, dk], rows = B*S, D = H*dk) and gathers
+   them into the flat matrix first.  For D % 32 == 0 one tensor-core launch whose epilogue adds each D-wide column block
+   to its own destination; otherwise the product into scratch and one accumulating pass.  rows == 0 leaves the
+   gradients as they are. */
+AXB_API int axb_dwqkv_split_acc(const float *x_flat, const float *dQKV, int64_t rows, int64_t D, float *dWq, float *dWk,
+                                float *dWv);
+AXB_API int axb_dwqkv_split_acc_hm(const float *x_flat, const float *dQh, const float *dKh, const float *dVh, int64_t B,
+                                   int64_t S, int64_t H, int64_t dk, float *dWq, float *dWk, float *dWv);
 
 /* ---- attention layout passes and fused-parameter builders ---------------------
    The remaining attention slots of ax_cuda_extension_t (include/axiom/internal/cuda_extension.h:41-88; stock

@@ -73,7 +73,11 @@ typedef struct {
     axb_status (*gemm)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, axb_ax_tensor_t *out);
     axb_status (*gemm_nt)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, axb_ax_tensor_t *out);
     axb_status (*gemm_tn)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, axb_ax_tensor_t *out);
-    axb_opaque_fn dwqkv_split_acc, dwqkv_split_acc_hm;
+    axb_status (*dwqkv_split_acc)(const axb_ax_tensor_t *x_flat, const axb_ax_tensor_t *dQKV, axb_ax_tensor_t *dWq,
+                                  axb_ax_tensor_t *dWk, axb_ax_tensor_t *dWv);   /* backend_ops.h:66-80 */
+    axb_status (*dwqkv_split_acc_hm)(const axb_ax_tensor_t *x_flat, const axb_ax_tensor_t *dQh, const axb_ax_tensor_t *dKh,
+                                     const axb_ax_tensor_t *dVh, int64_t B, int64_t S, int64_t H, int64_t dk,
+                                     axb_ax_tensor_t *dWq, axb_ax_tensor_t *dWk, axb_ax_tensor_t *dWv);   /* backend_ops.h:82-95 */
     axb_status (*qkv_head_gemm)(const axb_ax_tensor_t *X, const axb_ax_tensor_t *Wqkv, const axb_ax_tensor_t *bqkv,
                                 int64_t B, int64_t S, int64_t H, int64_t dk, axb_ax_tensor_t *Qh, axb_ax_tensor_t *Kh,
                                 axb_ax_tensor_t *Vh);   /* backend_ops.h:107-113 */

@@ -369,6 +369,45 @@ SHIM_API int ref_dattn_head_gemm_nt(const float *dout, const float *Wo, int64_t 
     return rc;
 }
 
+/* ax_compute_dwqkv_split_acc / _hm (src/compute/dispatch.c:463-515): the three [D, D] gradients in dW (dWq | dWk | dWv back
+   to back, holding the values to accumulate into) += x_flat[rows, D]^T . the column blocks of dQKV.  hm = 0: dq points
+   at dQKV [rows, 3D] (dk_, dv unused); hm = 1: dq, dk_, dv are head-major [B*H, S, dk].  device as above. */
+SHIM_API int ref_dwqkv_split_acc(const float *x_flat, const float *dq, const float *dk_, const float *dv, int hm, int64_t B,
+                                 int64_t S, int64_t H, int64_t dk, float *dW, int device)
+{
+    const int64_t D = H * dk, rows = B * S;
+    int64_t hshape[3] = { B * H, S, dk };
+    int rc = 0;
+    if (device) use_cuda(1); else ax_compute_set_backend(AX_BACKEND_CPU_SIMD);
+    ax_tensor_t *x = t2(x_flat, rows, D), *g[3] = { NULL, NULL, NULL }, *w[3];
+    if (hm) {
+        g[0] = ax_tensor_from_array((float *)dq, hshape, 3, AX_FLOAT32);
+        g[1] = ax_tensor_from_array((float *)dk_, hshape, 3, AX_FLOAT32);
+        g[2] = ax_tensor_from_array((float *)dv, hshape, 3, AX_FLOAT32);
+    } else {
+        g[0] = t2(dq, rows, 3 * D);
+    }
+    for (int i = 0; i < 3; i++) w[i] = t2(dW + (size_t)i * D * D, D, D);
+    if (device) {
+        x = to_dev(x);
+        for (int i = 0; i < 3; i++) { if (g[i]) g[i] = to_dev(g[i]); w[i] = to_dev(w[i]); }
+    }
+    if (!x || !g[0] || (hm && (!g[1] || !g[2])) || !w[0] || !w[1] || !w[2]) rc = 100;
+    if (!rc) {
+        if (hm) rc = ax_compute_has_dwqkv_split_acc_hm() ? (int)ax_compute_dwqkv_split_acc_hm(x, g[0], g[1], g[2], B, S, H, dk, w[0], w[1], w[2]) : 200;
+        else rc = ax_compute_has_dwqkv_split_acc() ? (int)ax_compute_dwqkv_split_acc(x, g[0], w[0], w[1], w[2]) : 200;
+    }
+    if (!rc && device) ax_device_synchronize(AX_DEVICE_CUDA);
+    for (int i = 0; i < 3 && !rc; i++) {
+        if (device) rc = copy_back(w[i], dW + (size_t)i * D * D, D * D);
+        else memcpy(dW + (size_t)i * D * D, tdata(w[i]), (size_t)(D * D) * sizeof(float));
+    }
+    if (x) ax_tensor_destroy(x);
+    for (int i = 0; i < 3; i++) { if (g[i]) ax_tensor_destroy(g[i]); if (w[i]) ax_tensor_destroy(w[i]); }
+    if (device) use_cuda(0);
+    return rc;
+}
+
 /* ax_compute_qkv_head_gemm (include/axiom/compute.h:150-170) on the active CPU backend: X[B*S, D],
    Wqkv[D, 3D], bqkv[3D] or NULL -> Qh, Kh, Vh [B*H, S, dk]. */
 SHIM_API int ref_qkv_head_gemm(const float *X, const float *Wqkv, const float *bqkv, int64_t B, int64_t S,

@@ -29,7 +29,7 @@ SAME(ax_tensor_t, axb_ax_tensor_t, dtype); SAME(ax_tensor_t, axb_ax_tensor_t, of
 SAME(ax_tensor_t, axb_ax_tensor_t, layout);
 _Static_assert(sizeof(struct ax_backend_ops) == sizeof(axb_ax_backend_ops_t), "vtable size");
 #define SLOT(f) SAME(struct ax_backend_ops, axb_ax_backend_ops_t, f)
-SLOT(name); SLOT(add); SLOT(mul_scalar); SLOT(gemm); SLOT(gemm_nt); SLOT(gemm_tn); SLOT(dwqkv_split_acc); SLOT(dattn_head_gemm_nt);
+SLOT(name); SLOT(add); SLOT(mul_scalar); SLOT(gemm); SLOT(gemm_nt); SLOT(gemm_tn); SLOT(dwqkv_split_acc); SLOT(dwqkv_split_acc_hm); SLOT(qkv_head_gemm); SLOT(dattn_head_gemm_nt);
 SLOT(mha_output_proj_fused); SLOT(gemm_relu); SLOT(gemm_ex); SLOT(add_relu); SLOT(softmax_rowwise); SLOT(bias_add);
 SLOT(conv_gemm); SLOT(sum); SLOT(argmax); SLOT(equal); SLOT(fill); SLOT(copy); SLOT(relu); SLOT(sigmoid);
 SLOT(leaky_relu); SLOT(gelu_op); SLOT(swish_op); SLOT(adam_update); SLOT(sgd_update); SLOT(device); SLOT(init);
@@ -85,6 +85,7 @@ def test_tables_are_filled(backend):
     assert not any(slots[i] for i in range(1, 13))
     ext = (ctypes.c_void_p * 12).from_address(backend.axb_cuda_extension())
     assert ext[7] and ext[8] and ext[9] and not ext[10] and not ext[11]   # sdpa_fwd, sdpa_bwd, conv_gemm_batched set; Winograd NULL
+    assert slots[16] and slots[17]                     # dwqkv_split_acc, dwqkv_split_acc_hm
     assert slots[18] and slots[19] and not slots[20]   # qkv_head_gemm, dattn_head_gemm_nt set; mha_output_proj_fused NULL
 
 

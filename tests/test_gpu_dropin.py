@@ -141,6 +141,35 @@ def test_dattn_head_gemm_nt_slot(dropin, reference, oracle, shape):
     assert nerr(got, want) <= 1e-5
 
 
+@pytest.mark.parametrize("shape", [(2, 64, 4, 32), (1, 40, 3, 16), (2, 128, 4, 64)])
+@pytest.mark.parametrize("head_major", [0, 1])
+def test_dwqkv_split_acc_slots(dropin, reference, oracle, shape, head_major):
+    """ax_compute_dwqkv_split_acc[_hm] on device tensors made by the reference land in the two slots and accumulate
+    into the three gradients what the reference's CPU implementation accumulates."""
+    B, S, H, dk = shape
+    D, rows = H * dk, B * S
+    x, dqkv = oracle.uniform((rows, D), 7), oracle.normal((rows, 3 * D), 13, sigma=0.5)
+    start = np.stack([oracle.uniform((D, D), 20 + i) for i in range(3)])
+    if head_major:
+        g = [np.ascontiguousarray(dqkv[:, i * D:(i + 1) * D].reshape(B, S, H, dk).transpose(0, 2, 1, 3)).reshape(B * H, S, dk)
+             for i in range(3)]
+    else:
+        g = [dqkv, dqkv, dqkv]
+    got, want = start.copy(), start.copy()
+    rc = dropin.ref_dwqkv_split_acc(p(x), p(g[0]), p(g[1]), p(g[2]), head_major, i64(B), i64(S), i64(H), i64(dk), p(got), 1)
+    assert rc == 0, (rc, dropin.ref_last_error())
+    rc = dropin.ref_dwqkv_split_acc(p(x), p(g[0]), p(g[1]), p(g[2]), head_major, i64(B), i64(S), i64(H), i64(dk), p(want), 0)
+    if rc and head_major:
+        # the reference's CPU head-major form refuses widths that are not a multiple of its column panel
+        # (src/compute/backends/cpu_opt.c:5841-5853); its flat form is the same sum
+        want = start.copy()
+        rc = dropin.ref_dwqkv_split_acc(p(x), p(dqkv), p(dqkv), p(dqkv), 0, i64(B), i64(S), i64(H), i64(dk), p(want), 0)
+    assert rc == 0
+    assert np.abs(want - start).max() > 0.1
+    np.testing.assert_allclose(got, want, atol=1e-3, rtol=1e-4)
+    assert nerr(got, want) <= 1e-5
+
+
 @pytest.mark.parametrize("geom", [(3, 8, 4, 12, 12, 3, 3, 1, 1, 1, 1), (2, 16, 4, 9, 9, 3, 3, 2, 2, 0, 0), (4, 12, 6, 10, 16, 1, 1, 1, 1, 0, 0)])
 def test_conv_gemm_batched_extension_slot(dropin, reference, oracle, geom):
     """The conv_gemm_batched slot, called as the reference's conv layer calls it on a device (N samples back to back,

@@ -548,6 +548,29 @@ def test_dattn_head_gemm_nt(engine, oracle, shape):
     assert engine.device_error() == 0
 
 
+@pytest.mark.parametrize("shape", [(8, 1024, 16, 64), (2, 100, 5, 32), (3, 50, 4, 24), (1, 16, 2, 8), (2, 300, 1, 32), (4, 256, 8, 96)])
+@pytest.mark.parametrize("head_major", [False, True])
+def test_dwqkv_split_acc(engine, oracle, shape, head_major):
+    """dW{q,k,v} += x^T . dQKV column blocks against float64, on top of gradients that already hold values (config-4
+    layer shape — split K —, ragged rows, widths that are not multiples of 32, one 32-wide tile), flat and head-major."""
+    B, S, H, dk = shape
+    D, rows = H * dk, B * S
+    x, dqkv = oracle.uniform((rows, D), 7), oracle.normal((rows, 3 * D), 13, sigma=0.5)
+    start = [oracle.uniform((D, D), 20 + i) for i in range(3)]
+    grads = [dev(g.copy()) for g in start]
+    if head_major:
+        hm = [dev(np.ascontiguousarray(dqkv[:, i * D:(i + 1) * D].reshape(B, S, H, dk).transpose(0, 2, 1, 3)).reshape(B * H, S, dk))
+              for i in range(3)]
+        engine.dwqkv_split_acc_hm(dev(x), *hm, B, S, H, dk, *grads)
+    else:
+        engine.dwqkv_split_acc(dev(x), dev(dqkv), *grads)
+    prod = oracle.gemm_f64(np.ascontiguousarray(x.T), dqkv)                                 # [D, 3D]
+    for i in range(3):
+        want = start[i].astype(np.float64) + prod[:, i * D:(i + 1) * D]
+        assert nerr(host(grads[i]), want) <= TOL_SPLIT, (i, nerr(host(grads[i]), want))
+    assert engine.device_error() == 0
+
+
 @pytest.mark.parametrize("geom", [(8, 256, 256, 56, 56, 3, 3, 1, 1, 1, 1),   # a ResNet stage at batch 8: one implicit GEMM, 128 x 256 tiles
                                   (3, 40, 20, 12, 20, 5, 5, 1, 1, 2, 2),      # patches of the last tile run into the next sample and past the end
                                   (5, 16, 3, 6, 8, 3, 3, 1, 1, 1, 1),         # samples smaller than one patch row
