@@ -1488,6 +1488,32 @@ extern "C" int axb_dwqkv_split_acc_hm(const float *x_flat, const float *dQh, con
     return dwqkv_split_acc_any("dwqkv_split_acc_hm", x_flat, (const float *)cur().aux, rows, D, dWq, dWk, dWv, merged);
 }
 
+extern "C" int axb_mha_output_proj_fused(const float *attn_flat, const float *Wo, const float *bo, const float *dout, float *y,
+                                         float *dattn, float *dWo_acc, float *dbo_acc, int64_t rows, int64_t D)
+{
+    if (!attn_flat || !Wo || !dout || !dattn || !dWo_acc) return fail(AXB_ERR_NULL_ARG, "mha_output_proj_fused: NULL");
+    if (rows < 0 || D <= 0) return fail(AXB_ERR_INVALID_SHAPE, "mha_output_proj_fused: bad shape");
+    if (rows > INT32_MAX || D > INT32_MAX) return fail(AXB_ERR_INVALID_SHAPE, "mha_output_proj_fused: dimension exceeds 2^31-1");
+    int st = ensure_ready();
+    if (st) return st;
+    if (rows == 0) return AXB_OK;
+    // forward: y = attn . Wo + bo (bias in the epilogue); skipped without y
+    if (y && (st = axb_gemm_bias_act(attn_flat, Wo, bo, y, rows, D, D, 0, 0, 1.0f, 0.0f, AXB_ACT_NONE))) return st;
+    // dattn = dout . Wo^T
+    if ((st = axb_gemm_bias_act(dout, Wo, nullptr, dattn, rows, D, D, 0, 1, 1.0f, 0.0f, AXB_ACT_NONE))) return st;
+    // dWo += attn^T . dout
+    if ((st = axb_gemm_bias_act(attn_flat, dout, nullptr, dWo_acc, D, D, rows, 1, 0, 1.0f, 1.0f, AXB_ACT_NONE))) return st;
+    if (dbo_acc) {
+        // dbo += column sums of dout = ones[1, rows] . dout: the bandwidth-bound one-row route reads dout once
+        if ((st = ensure_aux("mha_output_proj_fused", (size_t)rows * sizeof(float)))) return st;
+        int e = launch_fill((float *)cur().aux, rows, 1.0f, cur().sm_count, cur().stream);
+        cur().launches++;
+        if (e) return cuda_fail("mha_output_proj_fused: fill", e);
+        if ((st = axb_gemm_bias_act((const float *)cur().aux, dout, nullptr, dbo_acc, 1, D, rows, 0, 0, 1.0f, 1.0f, AXB_ACT_NONE))) return st;
+    }
+    return AXB_OK;
+}
+
 // ------------------------------------------------------- attention layout passes
 
 static int head_layout_call(const char *what, bool to_head, const float *flat, float *const head[3], const float *bias,

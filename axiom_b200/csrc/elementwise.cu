@@ -69,7 +69,19 @@ static inline int ew_grid(int64_t items, int sm_count)
     return (int)(b < 1 ? 1 : b);
 }
 
+__global__ void __launch_bounds__(256) fill_kernel(float *__restrict__ out, int64_t n, float value)
+{
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) out[i] = value;
+}
+
 static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+int launch_fill(float *out, int64_t n, float value, int sm_count, cudaStream_t st)
+{
+    if (n <= 0) return 0;
+    fill_kernel<<<ew_grid(n, sm_count), 256, 0, st>>>(out, n, value);
+    return (int)cudaGetLastError();
+}
 
 int launch_unary(int op, const float *in, float *out, int64_t n, int sm_count, cudaStream_t st)
 {

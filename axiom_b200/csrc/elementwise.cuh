@@ -7,6 +7,7 @@ namespace axb {
 
 int launch_unary(int op /*0 relu, 1 gelu*/, const float *in, float *out, int64_t n, int sm_count,
                  cudaStream_t st);
+int launch_fill(float *out, int64_t n, float value, int sm_count, cudaStream_t st);
 // axis 0: out[i,j] = in[i,j] + bias[i % period] (period 0 = M); axis 1: + bias[j]
 int launch_bias_add(const float *in, const float *bias, int axis, float *out, int64_t M, int64_t N,
                     int sm_count, cudaStream_t st, int64_t period = 0);

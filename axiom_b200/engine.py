@@ -27,7 +27,7 @@ EXPORTS = [
     "axb_skinny_gemm_static", "axb_skinny_gemm_static_error", "axb_gemm_bias_act_scatter", "axb_gemm_gathered_scatter", "axb_ipc_get_handle", "axb_ipc_open_handle",
     "axb_ipc_close_handle",
     "axb_bias_add", "axb_relu", "axb_gelu", "axb_qgemm_w8a32", "axb_qgemm_w8a8", "axb_quantize_rows",
-    "axb_sdpa_fwd", "axb_kv_cache_append", "axb_kv_cache_attend", "axb_qkv_head_gemm", "axb_sdpa_bwd", "axb_conv_gemm", "axb_conv_gemm_batched", "axb_gemm_prepared_scatter", "axb_dattn_head_gemm_nt", "axb_dwqkv_split_acc", "axb_dwqkv_split_acc_hm", "axb_qdense_w8a32",
+    "axb_sdpa_fwd", "axb_kv_cache_append", "axb_kv_cache_attend", "axb_qkv_head_gemm", "axb_sdpa_bwd", "axb_conv_gemm", "axb_conv_gemm_batched", "axb_gemm_prepared_scatter", "axb_dattn_head_gemm_nt", "axb_dwqkv_split_acc", "axb_dwqkv_split_acc_hm", "axb_mha_output_proj_fused", "axb_qdense_w8a32",
     "axb_qgemm_w8a32_qw", "axb_bias_add_nd", "axb_head_interleave_qkv_split", "axb_head_interleave", "axb_head_deinterleave",
     "axb_head_deinterleave_qkv_merge", "axb_qkv_cache_build", "axb_bias_cache_build", "axb_pointer_on_device",
     "axb_weight_prepare", "axb_weight_release", "axb_gemm_prepared",
@@ -344,6 +344,13 @@ class Engine:
         """The same with the three gradients head-major [B*H, S, dk]."""
         self._check(self.lib.axb_dwqkv_split_acc_hm(_ptr(x_flat), _ptr(dQh), _ptr(dKh), _ptr(dVh), _i64(B), _i64(S), _i64(H),
                                                     _i64(dk), _ptr(dWq), _ptr(dWk), _ptr(dWv)))
+
+    def mha_output_proj_fused(self, attn_flat, Wo, bo, dout, y, dattn, dWo_acc, dbo_acc):
+        """y = attn.Wo + bo (y None: skipped); dattn = dout.Wo^T; dWo_acc += attn^T.dout; dbo_acc += column sums of dout."""
+        rows, D = attn_flat.shape
+        opt = lambda t: _ptr(t) if t is not None else None
+        self._check(self.lib.axb_mha_output_proj_fused(_ptr(attn_flat), _ptr(Wo), opt(bo), _ptr(dout), opt(y), _ptr(dattn),
+                                                       _ptr(dWo_acc), opt(dbo_acc), _i64(rows), _i64(D)))
 
     def conv_gemm_batched(self, weight, inp, kh, kw, sh, sw, ph, pw, out):
         """weight [C_out, C_in*kh*kw], inp [N, C_in, H, W], out [N, C_out, out_h*out_w]."""

@@ -326,6 +326,27 @@ static axb_status be_dwqkv_split_acc_hm(const axb_ax_tensor_t *x_flat, const axb
                                        fptr(dWv)));
 }
 
+/* shape rules of the CPU implementation (src/compute/backends/cpu_opt.c:6825-6857): y, bo and dbo_acc are optional */
+static axb_status be_mha_output_proj_fused(const axb_ax_tensor_t *attn_flat, const axb_ax_tensor_t *Wo, const axb_ax_tensor_t *bo,
+                                           const axb_ax_tensor_t *dout, axb_ax_tensor_t *y, axb_ax_tensor_t *dattn,
+                                           axb_ax_tensor_t *dWo_acc, axb_ax_tensor_t *dbo_acc)
+{
+    static const char what[] = "mha_output_proj_fused";
+    axb_status st;
+    if ((st = check_f32(attn_flat, what, 2)) || (st = check_f32(Wo, what, 2)) || (st = check_f32(dout, what, 2)) ||
+        (st = check_f32(dattn, what, 2)) || (st = check_f32(dWo_acc, what, 2)))
+        return st;
+    if ((y && (st = check_f32(y, what, 2))) || (bo && (st = check_f32(bo, what, 1))) || (dbo_acc && (st = check_f32(dbo_acc, what, 1))))
+        return st;
+    const int64_t rows = attn_flat->shape[0], D = attn_flat->shape[1];
+    if (Wo->shape[0] != D || Wo->shape[1] != D || dout->shape[0] != rows || dout->shape[1] != D || dattn->shape[0] != rows ||
+        dattn->shape[1] != D || dWo_acc->shape[0] != D || dWo_acc->shape[1] != D || (y && (y->shape[0] != rows || y->shape[1] != D)) ||
+        (bo && bo->shape[0] != D) || (dbo_acc && dbo_acc->shape[0] != D))
+        return report(ST_SHAPE, "mha_output_proj_fused: attn_flat, dout, y, dattn [rows, D]; Wo, dWo_acc [D, D]; bo, dbo_acc [D]");
+    return done(axb_mha_output_proj_fused(fptr(attn_flat), fptr(Wo), (y && bo) ? fptr(bo) : NULL, fptr(dout), y ? fptr(y) : NULL,
+                                          fptr(dattn), fptr(dWo_acc), dbo_acc ? fptr(dbo_acc) : NULL, rows, D));
+}
+
 /* shape rules of the reference's CUDA implementation (src/compute/backends/cuda/ops_conv.cu:113-142); params->input
    is a raw pointer into the (device-resident) batched input, as the conv layer passes it */
 static axb_status be_conv_gemm(const axb_ax_tensor_t *weight, const axb_ax_conv_params_t *params, axb_ax_tensor_t *out)
@@ -477,6 +498,7 @@ static const axb_ax_backend_ops_t ops_table = {
     .dwqkv_split_acc_hm = be_dwqkv_split_acc_hm,
     .qkv_head_gemm = be_qkv_head_gemm,
     .dattn_head_gemm_nt = be_dattn_head_gemm_nt,
+    .mha_output_proj_fused = be_mha_output_proj_fused,
     .gemm_relu = be_gemm_relu,
     .gemm_ex = be_gemm_ex,
     .bias_add = be_bias_add,

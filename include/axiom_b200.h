@@ -351,6 +351,17 @@ AXB_API int axb_dwqkv_split_acc(const float *x_flat, const float *dQKV, int64_t 
                                 float *dWv);
 AXB_API int axb_dwqkv_split_acc_hm(const float *x_flat, const float *dQh, const float *dKh, const float *dVh, int64_t B,
                                    int64_t S, int64_t H, int64_t dk, float *dWq, float *dWk, float *dWv);
+/* Slot mha_output_proj_fused of ax_backend_ops_t (include/axiom/internal/backend_ops.h:131-150;
+   ax_compute_mha_output_proj_fused and ax_compute_output_proj_bwd_fused, src/compute/dispatch.c:577-634; CPU implementation
+   src/compute/backends/cpu_opt.c:6819) — the output projection of the attention layer, forward and backward in one call:
+     y[rows, D]     = attn_flat[rows, D] . Wo[D, D] + bo[D]      (skipped when y is NULL; bo may be NULL)
+     dattn[rows, D] = dout[rows, D] . Wo^T                        (overwritten)
+     dWo_acc[D, D] += attn_flat^T . dout                          (accumulated)
+     dbo_acc[D]    += column sums of dout                         (accumulated; skipped when dbo_acc is NULL)
+   Three tensor-core launches (bias and the accumulation in their epilogues) and, for dbo, one pass of the one-row
+   bandwidth-bound route over dout. */
+AXB_API int axb_mha_output_proj_fused(const float *attn_flat, const float *Wo, const float *bo, const float *dout, float *y,
+                                      float *dattn, float *dWo_acc, float *dbo_acc, int64_t rows, int64_t D);
 
 /* ---- attention layout passes and fused-parameter builders ---------------------
    The remaining attention slots of ax_cuda_extension_t (include/axiom/internal/cuda_extension.h:41-88; stock

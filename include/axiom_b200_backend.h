@@ -83,7 +83,9 @@ typedef struct {
                                 axb_ax_tensor_t *Vh);   /* backend_ops.h:107-113 */
     axb_status (*dattn_head_gemm_nt)(const axb_ax_tensor_t *dout, const axb_ax_tensor_t *Wo, int64_t B, int64_t S, int64_t H,
                                      int64_t dk, axb_ax_tensor_t *dO_head);   /* backend_ops.h:114-129 */
-    axb_opaque_fn mha_output_proj_fused;
+    axb_status (*mha_output_proj_fused)(const axb_ax_tensor_t *attn_flat, const axb_ax_tensor_t *Wo, const axb_ax_tensor_t *bo,
+                                        const axb_ax_tensor_t *dout, axb_ax_tensor_t *y, axb_ax_tensor_t *dattn,
+                                        axb_ax_tensor_t *dWo_acc, axb_ax_tensor_t *dbo_acc);   /* backend_ops.h:131-150 */
     axb_status (*gemm_relu)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, const axb_ax_tensor_t *bias,
                             axb_ax_tensor_t *out);
     axb_status (*gemm_ex)(const axb_ax_tensor_t *a, const axb_ax_tensor_t *b, float alpha, float beta,

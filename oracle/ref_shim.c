@@ -408,6 +408,35 @@ SHIM_API int ref_dwqkv_split_acc(const float *x_flat, const float *dq, const flo
     return rc;
 }
 
+/* ax_compute_mha_output_proj_fused (src/compute/dispatch.c:577-601): attn, dout [rows, D], Wo [D, D], bo [D] or NULL ->
+   y [rows, D] (NULL skips the forward product), dattn [rows, D] overwritten, dWo [D, D] and dbo [D] (or NULL) accumulated
+   into the values they hold.  device as above. */
+SHIM_API int ref_mha_output_proj_fused(const float *attn, const float *Wo, const float *bo, const float *dout, float *y,
+                                       float *dattn, float *dWo, float *dbo, int64_t rows, int64_t D, int device)
+{
+    int rc = 0;
+    if (device) use_cuda(1); else ax_compute_set_backend(AX_BACKEND_CPU_SIMD);
+    ax_tensor_t *t[8] = { t2(attn, rows, D), t2(Wo, D, D), bo ? t1(bo, D) : NULL, t2(dout, rows, D), y ? t2(y, rows, D) : NULL,
+                          t2(dattn, rows, D), t2(dWo, D, D), dbo ? t1(dbo, D) : NULL };
+    const int want[8] = { 1, 1, bo != NULL, 1, y != NULL, 1, 1, dbo != NULL };
+    float *back[8] = { NULL, NULL, NULL, NULL, y, dattn, dWo, dbo };
+    const int64_t count[8] = { 0, 0, 0, 0, rows * D, rows * D, D * D, D };
+    for (int i = 0; i < 8; i++) {
+        if (device && t[i]) t[i] = to_dev(t[i]);
+        if (want[i] && !t[i]) rc = 100;
+    }
+    if (!rc) rc = ax_compute_has_mha_output_proj_fused() ? (int)ax_compute_mha_output_proj_fused(t[0], t[1], t[2], t[3], t[4], t[5], t[6], t[7]) : 200;
+    if (!rc && device) ax_device_synchronize(AX_DEVICE_CUDA);
+    for (int i = 4; i < 8 && !rc; i++) {
+        if (!t[i]) continue;
+        if (device) rc = copy_back(t[i], back[i], count[i]);
+        else memcpy(back[i], tdata(t[i]), (size_t)count[i] * sizeof(float));
+    }
+    for (int i = 0; i < 8; i++) if (t[i]) ax_tensor_destroy(t[i]);
+    if (device) use_cuda(0);
+    return rc;
+}
+
 /* ax_compute_qkv_head_gemm (include/axiom/compute.h:150-170) on the active CPU backend: X[B*S, D],
    Wqkv[D, 3D], bqkv[3D] or NULL -> Qh, Kh, Vh [B*H, S, dk]. */
 SHIM_API int ref_qkv_head_gemm(const float *X, const float *Wqkv, const float *bqkv, int64_t B, int64_t S,

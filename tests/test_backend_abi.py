@@ -86,7 +86,8 @@ def test_tables_are_filled(backend):
     ext = (ctypes.c_void_p * 12).from_address(backend.axb_cuda_extension())
     assert ext[7] and ext[8] and ext[9] and not ext[10] and not ext[11]   # sdpa_fwd, sdpa_bwd, conv_gemm_batched set; Winograd NULL
     assert slots[16] and slots[17]                     # dwqkv_split_acc, dwqkv_split_acc_hm
-    assert slots[18] and slots[19] and not slots[20]   # qkv_head_gemm, dattn_head_gemm_nt set; mha_output_proj_fused NULL
+    assert slots[18] and slots[19] and slots[20]       # qkv_head_gemm, dattn_head_gemm_nt, mha_output_proj_fused
+    assert not slots[23]                               # add_relu (gemm_relu 21 and gemm_ex 22 are set)
 
 
 def test_registers_with_the_reference_dispatcher(backend, reference):

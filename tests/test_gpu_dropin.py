@@ -170,6 +170,26 @@ def test_dwqkv_split_acc_slots(dropin, reference, oracle, shape, head_major):
     assert nerr(got, want) <= 1e-5
 
 
+@pytest.mark.parametrize("rows,D", [(128, 128), (40, 48), (256, 256)])
+@pytest.mark.parametrize("forward", [1, 0])
+def test_mha_output_proj_fused_slot(dropin, reference, oracle, rows, D, forward):
+    """ax_compute_mha_output_proj_fused (and, with y and bo NULL, ax_compute_output_proj_bwd_fused's call) on device
+    tensors made by the reference lands in the slot and equals the reference's CPU implementation."""
+    attn, dout = oracle.uniform((rows, D), 7), oracle.normal((rows, D), 13, sigma=0.5)
+    Wo, bo = oracle.normal((D, D), 17, sigma=1.0 / np.sqrt(D)), oracle.uniform((D,), 19)
+    res = []
+    for device in (1, 0):
+        y, dattn = np.full((rows, D), np.nan, np.float32), np.full((rows, D), np.nan, np.float32)
+        dWo, dbo = oracle.uniform((D, D), 23), oracle.uniform((D,), 29)
+        rc = dropin.ref_mha_output_proj_fused(p(attn), p(Wo), p(bo) if forward else None, p(dout), p(y) if forward else None,
+                                              p(dattn), p(dWo), p(dbo), i64(rows), i64(D), device)
+        assert rc == 0, (device, rc, dropin.ref_last_error())
+        res.append((y, dattn, dWo, dbo))
+    for got, want in zip(res[0][0 if forward else 1:], res[1][0 if forward else 1:]):
+        np.testing.assert_allclose(got, want, atol=1e-3, rtol=1e-4)
+        assert nerr(got, want) <= 1e-5
+
+
 @pytest.mark.parametrize("geom", [(3, 8, 4, 12, 12, 3, 3, 1, 1, 1, 1), (2, 16, 4, 9, 9, 3, 3, 2, 2, 0, 0), (4, 12, 6, 10, 16, 1, 1, 1, 1, 0, 0)])
 def test_conv_gemm_batched_extension_slot(dropin, reference, oracle, geom):
     """The conv_gemm_batched slot, called as the reference's conv layer calls it on a device (N samples back to back,

@@ -571,6 +571,27 @@ def test_dwqkv_split_acc(engine, oracle, shape, head_major):
     assert engine.device_error() == 0
 
 
+@pytest.mark.parametrize("rows,D", [(8192, 1024), (200, 160), (50, 96), (16, 20), (1, 64)])
+@pytest.mark.parametrize("forward", [True, False])
+def test_mha_output_proj_fused(engine, oracle, rows, D, forward):
+    """The attention layer's output projection, forward and backward in one call, against float64: y (with bias; skipped
+    when forward is off), dattn, and dWo / dbo accumulated on top of values already there."""
+    attn, dout = oracle.uniform((rows, D), 7), oracle.normal((rows, D), 13, sigma=0.5)
+    Wo, bo = oracle.normal((D, D), 17, sigma=1.0 / np.sqrt(D)), oracle.uniform((D,), 19)
+    dWo0, dbo0 = oracle.uniform((D, D), 23), oracle.uniform((D,), 29)
+    y = torch.full((rows, D), float("nan"), device="cuda") if forward else None
+    dattn = torch.full((rows, D), float("nan"), device="cuda")
+    dWo, dbo = dev(dWo0.copy()), dev(dbo0.copy())
+    engine.mha_output_proj_fused(dev(attn), dev(Wo), dev(bo) if forward else None, dev(dout), y, dattn, dWo, dbo)
+    if forward:
+        assert nerr(host(y), oracle.gemm_f64(attn, Wo) + bo.astype(np.float64)) <= TOL_SPLIT
+    assert nerr(host(dattn), oracle.gemm_f64(dout, np.ascontiguousarray(Wo.T))) <= TOL_SPLIT
+    assert nerr(host(dWo), dWo0.astype(np.float64) + oracle.gemm_f64(np.ascontiguousarray(attn.T), dout)) <= TOL_SPLIT
+    want_dbo = dbo0.astype(np.float64) + dout.astype(np.float64).sum(axis=0)
+    assert np.abs(host(dbo) - want_dbo).max() <= 1e-5 * max(1.0, np.abs(dout).sum(axis=0).max())
+    assert engine.device_error() == 0
+
+
 @pytest.mark.parametrize("geom", [(8, 256, 256, 56, 56, 3, 3, 1, 1, 1, 1),   # a ResNet stage at batch 8: one implicit GEMM, 128 x 256 tiles
                                   (3, 40, 20, 12, 20, 5, 5, 1, 1, 2, 2),      # patches of the last tile run into the next sample and past the end
                                   (5, 16, 3, 6, 8, 3, 3, 1, 1, 1, 1),         # samples smaller than one patch row
