@@ -400,7 +400,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
                                 stg[lane * 8 + (j4 ^ (lane & 7))] = make_float4(sum[c * 32 + 4 * j4], sum[c * 32 + 4 * j4 + 1],
                                                                                 sum[c * 32 + 4 * j4 + 2], sum[c * 32 + 4 * j4 + 3]);
                             __syncwarp();
-                            if (p.tma_store) store_piece_f32_tma(p, &tm.c, stg, row0, col0, lane);
+                            if (p.tma_store) store_piece_f32_tma(p, tm.c, stg, row0, col0, lane);
                             else if (p.cv_taps > 0) store_piece_f32_conv(p, stg, row0, col0, lane);
                             else store_piece_f32(p, stg, row0, col0, lane, rows_aligned);
                         }
@@ -901,9 +901,23 @@ static int launch_common(int kind, const TcOperand &A, const TcOperand &B, const
     // plain aligned fp32 output that is not read back: the staging tiles leave through TMA stores
     if (kind != KIND_I8 && ep.out_mode == OUT_F32 && ep.hs_dk == 0 && ka.n_extra == 0 && ep.beta == 0.0f && ep.C &&
         (reinterpret_cast<uintptr_t>(ep.C) & 15) == 0 && ep.ldc % 4 == 0) {
-        int e = encode_f32_store_tmap(&tm.c, reinterpret_cast<float *>(ep.C), M, N, ep.ldc);
+        int e = encode_f32_store_tmap(&tm.c[0], reinterpret_cast<float *>(ep.C), M, N, ep.ldc);
         if (e) return e;
         ka.tma_store = 1;
+    } else if (kind != KIND_I8 && ep.out_mode == OUT_F32 && ep.hs_dk > 0 && ep.beta == 0.0f && ep.hs_S % 32 == 0 &&
+               ep.hs_dk % 32 == 0 && M % ep.hs_S == 0 && N % (ep.hs_H * ep.hs_dk) == 0 && N / (ep.hs_H * ep.hs_dk) <= 3) {
+        // head-major scatter of whole 32 x 32 pieces: one store map per destination, each seen as a matrix of
+        // B*H*S rows of dk floats (a piece never straddles a batch, S % 32 == 0, or a head, dk % 32 == 0)
+        const int nwhich = (int)(N / (ep.hs_H * ep.hs_dk));
+        bool ok = true;
+        for (int i = 0; i < nwhich; ++i) ok = ok && ep.hs_out[i] && (reinterpret_cast<uintptr_t>(ep.hs_out[i]) & 15) == 0;
+        if (ok && (M / ep.hs_S) * ep.hs_H * ep.hs_S <= INT32_MAX) {
+            for (int i = 0; i < nwhich; ++i) {
+                int e = encode_f32_store_tmap(&tm.c[i], ep.hs_out[i], (M / ep.hs_S) * ep.hs_H * ep.hs_S, ep.hs_dk, ep.hs_dk);
+                if (e) return e;
+            }
+            ka.tma_store = 1;
+        }
     }
     const int64_t work = mt * nt * ka.ksplit;
     const int grid = (int)(work < sm_count ? work : sm_count);

@@ -256,7 +256,7 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
                                 stg[lane * 8 + (j4 ^ (lane & 7))] = make_float4(sum[c * 32 + 4 * j4], sum[c * 32 + 4 * j4 + 1],
                                                                                 sum[c * 32 + 4 * j4 + 2], sum[c * 32 + 4 * j4 + 3]);
                             __syncwarp();
-                            if (p.tma_store) store_piece_f32_tma(p, &tm.c, stg, row0, col0, lane);
+                            if (p.tma_store) store_piece_f32_tma(p, tm.c, stg, row0, col0, lane);
                             else store_piece_f32(p, stg, row0, col0, lane, rows_aligned);
                         }
                     }

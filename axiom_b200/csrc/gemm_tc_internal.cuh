@@ -21,7 +21,9 @@ static constexpr int EPI_STAGING_BYTES = 8 * 4096;   // fp32 kinds: one 32 x 32 
 struct alignas(64) TmapPack {
     CUtensorMap a[TC_MAX_PLANES];
     CUtensorMap b[TC_MAX_PLANES];
-    CUtensorMap c;   // fp32 output [M, N], box 32 x 32, 128-byte swizzle (valid when KernelArgs::tma_store)
+    // fp32 output, box 32 x 32, 128-byte swizzle (valid when KernelArgs::tma_store): c[0] over C [M, N]; with the
+    // head-major scatter c[which] over hs_out[which] seen as a matrix of B*H*S rows of hs_dk floats
+    CUtensorMap c[3];
 };
 
 struct KernelArgs {
@@ -42,7 +44,7 @@ struct KernelArgs {
     float *c_extra[TC_MAX_EXTRA];
     int n_extra;
     int hs_dk, hs_S, hs_H;   // head-major scatter of the output (hs_dk > 0), see TcEpilogue
-    int tma_store;           // fp32 output leaves through TMA stores of the staging tiles (plain C, beta == 0, aligned)
+    int tma_store;           // fp32 output leaves through TMA stores of the staging tiles (beta == 0, aligned; plain C or head-major)
     float *hs_out[3];
     // split-K (ksplit > 1): work item w = tile * ksplit + slice covers k-blocks [slice * kb_per_slice, ...); every
     // slice leaves its partial sums in sk_scratch and counts itself in on sk_counters[tile]; the slice that counts
@@ -203,7 +205,16 @@ static __device__ __forceinline__ void store_piece_f32_tma(const KernelArgs &p, 
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-        tma_store_2d(tmc, smem_u32(stg), col0, (int32_t)row0);
+        if (p.hs_dk > 0) {
+            // head-major: the piece's 32 rows (b, s0..s0+31: hs_S % 32 == 0) and 32 columns (head h, d0..d0+31) are a
+            // 32 x 32 box at row (b*H + h)*S + s0 of destination `which`
+            const int D = p.hs_H * p.hs_dk;
+            const int which = col0 / D, rem = col0 - which * D, h = rem / p.hs_dk, d0 = rem - h * p.hs_dk;
+            const long long b = row0 / p.hs_S, s0 = row0 - b * p.hs_S;
+            tma_store_2d(tmc + which, smem_u32(stg), d0, (int32_t)((b * p.hs_H + h) * p.hs_S + s0));
+        } else {
+            tma_store_2d(tmc, smem_u32(stg), col0, (int32_t)row0);
+        }
         tma_store_commit();
     }
 }
