@@ -1014,39 +1014,38 @@ extern "C" int axb_qdense_w8a32(const float *a, const int8_t *q, const float *sc
     }
     if (K % 16 == 0 && K <= 65536 && 4 * M <= INT32_MAX &&
         ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(q)) & 15) == 0) {
-        // activations as four int8 digit planes [4][M][K] = the A operand of one int8 GEMM against the weights as they
-        // are; the s32 result [4M, N] is recombined with 64-bit integers (exact), then scale, bias, activation
-        const size_t dig_bytes = (size_t)4 * M * K, acc_bytes = (size_t)4 * M * N * sizeof(int32_t);
-        st = ensure_ws(round_up((size_t)M * sizeof(float), 1024) + round_up(dig_bytes, 1024) + round_up(acc_bytes, 1024) + kSplitScratch);
+        // activations as four int8 digit rows per row, interleaved [M][4][K] = the B operand of one int8 GEMM whose A
+        // operand is the weights as they are: the thread that holds accumulator row n has the four digit sums of an
+        // output (m, n) side by side, recombines them with 64-bit integers (exact), applies scale, bias and activation
+        // and stores out[m][n] — no s32 intermediate, no recombination pass
+        const size_t dig_bytes = (size_t)4 * M * K;
+        st = ensure_ws(round_up((size_t)M * sizeof(float), 1024) + round_up(dig_bytes, 1024) + kSplitScratch);
         if (st) return st;
         Carver carve{ (char *)cur().ws };
         const TcSplitK sk = take_splitk(carve);
         float *inv_s = (float *)carve.take((size_t)M * sizeof(float));
         int8_t *digits = (int8_t *)carve.take(dig_bytes);
-        int32_t *acc = (int32_t *)carve.take(acc_bytes);
         mark(0);
-        int e = launch_qx_digits(a, M, K, M, digits, inv_s, cur().stream);
+        int e = launch_qx_digits(a, M, K, 0, digits, inv_s, cur().stream);
         cur().launches++;
         if (e) return cuda_fail("w8a32 digits", e);
         TcOperand opa, opb;
         opa.nplanes = opb.nplanes = 1;
-        opa.plane[0] = digits; opa.rows = 4 * M; opa.pitch_elems = K;
-        opb.plane[0] = q; opb.rows = N; opb.pitch_elems = K;
+        opa.plane[0] = q; opa.rows = N; opa.pitch_elems = K;
+        opb.plane[0] = digits; opb.rows = 4 * M; opb.pitch_elems = K;
         TcProducts prod;
         memset(&prod, 0, sizeof prod);
         prod.n = 1;
         TcEpilogue ep;
         ep.n_extra = 0;
-        ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = nullptr; ep.colscale = nullptr; ep.act = ACT_NONE;
-        ep.out_mode = OUT_S32_ONLY; ep.C = nullptr; ep.acc_out = acc; ep.ldc = N;
+        ep.alpha = 1.0f; ep.beta = 0.0f; ep.bias = bias; ep.colscale = scales; ep.act = act;
+        ep.out_mode = OUT_DIGITS_T; ep.C = out; ep.acc_out = nullptr; ep.ldc = N;
+        ep.dg_inv_s = inv_s; ep.dg_rows = (int)M;
         mark(1);
-        e = launch_gemm_tc(KIND_I8, opa, opb, prod, 4 * M, N, K, ep, cur().err_word, cur().sm_count, cur().stream, &sk);
-        cur().launches++;
-        if (e) return cuda_fail("w8a32 digit gemm", e);
-        e = launch_qx_combine(acc, inv_s, scales, bias, act, out, M, N, cur().sm_count, cur().stream);
+        e = launch_gemm_tc(KIND_I8, opa, opb, prod, N, 4 * M, K, ep, cur().err_word, cur().sm_count, cur().stream, &sk);
         mark(2);
         cur().launches++;
-        return e ? cuda_fail("w8a32 combine", e) : AXB_OK;
+        return e ? cuda_fail("w8a32 digit gemm", e) : AXB_OK;
     }
     // activations: bf16 hi/mid/lo (exact to 24 bits); weights: int8 widened to bf16 (exact)
     const int amode = cur().fp32_mode == AXB_FP32_BF16 ? SPLIT_BF16X1 : SPLIT_BF16X3;

@@ -872,6 +872,7 @@ static int launch_common(int kind, const TcOperand &A, const TcOperand &B, const
         ka.sk_cluster = (pl.ksplit == 2 && kind != KIND_I8 && mt * nt * 2 <= sm_count) ? 1 : 0;
     }
     ka.alpha = ep.alpha; ka.beta = ep.beta; ka.bias = ep.bias; ka.colscale = ep.colscale;
+    ka.dg_inv_s = ep.dg_inv_s; ka.dg_rows = ep.dg_rows;
     ka.rq_a_scale = ep.rq_a_scale; ka.rq_out_scale = ep.rq_out_scale;
     ka.act = ep.act; ka.out_mode = ep.out_mode; ka.C = ep.C; ka.acc_out = ep.acc_out;
     ka.ldc = ep.ldc; ka.err = err_word;

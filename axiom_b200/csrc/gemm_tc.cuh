@@ -8,7 +8,11 @@ namespace axb {
 
 enum { TC_MAX_PLANES = 3, TC_MAX_PRODUCTS = 6, TC_MAX_EXTRA = 8 };
 enum { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU = 2 };
-enum { OUT_F32 = 0, OUT_I8_REQUANT = 1, OUT_S32_ONLY = 2 };
+// OUT_DIGITS_T (int8 kind): the B operand is four int8 digit planes of fp32 activations, interleaved per activation row
+// (B row 4*m + j = digit j of row m), the A operand the int8 weights [n][K]; accumulator row n, columns 4*m .. 4*m+3 are
+// recombined with 64-bit integers by the thread that holds them and out[m][n] = act(total * colscale[n] * dg_inv_s[m] +
+// bias[n]) is stored TRANSPOSED (C = out, ldc = its pitch; colscale and bias are indexed by the GEMM's row).
+enum { OUT_F32 = 0, OUT_I8_REQUANT = 1, OUT_S32_ONLY = 2, OUT_DIGITS_T = 3 };
 
 // One logical operand = up to three K-major planes [rows, k] whose sum is the
 // value (a single plane for bf16 / int8; hi+lo for the split-precision modes).
@@ -38,6 +42,9 @@ struct TcEpilogue {
     // the attention kernels.  hs_dk must be a multiple of 32 (a 32-column store never straddles two heads).
     int hs_dk = 0, hs_S = 0, hs_H = 0;
     float *hs_out[3] = { nullptr, nullptr, nullptr };
+    // OUT_DIGITS_T: 2^-s of every activation row (the digits are the row's values on the grid 2^-s) and the row count
+    const float *dg_inv_s = nullptr;
+    int dg_rows = 0;
 };
 
 struct TcProducts {

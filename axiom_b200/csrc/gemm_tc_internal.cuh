@@ -2,6 +2,7 @@
 // (gemm_tc.cu: one CTA per tile; gemm_tc2.cu: a CTA pair per tile).
 #pragma once
 #include "gemm_tc.cuh"
+#include "qskinny_tc.cuh"
 #include "ptx.cuh"
 
 #include <cuda.h>
@@ -43,6 +44,8 @@ struct KernelArgs {
     int *err;
     float *c_extra[TC_MAX_EXTRA];
     int n_extra;
+    const float *dg_inv_s;   // OUT_DIGITS_T, see TcEpilogue
+    int dg_rows;
     int hs_dk, hs_S, hs_H;   // head-major scatter of the output (hs_dk > 0), see TcEpilogue
     int tma_store;           // fp32 output leaves through TMA stores of the staging tiles (beta == 0, aligned; plain C or head-major)
     float *hs_out[3];
@@ -345,6 +348,22 @@ __device__ __forceinline__ int splitk_exchange(const KernelArgs &p, T (&v)[HALF]
 // division per lane instead of 32 per thread — and the row loops fetch it with a shuffle.
 __device__ __forceinline__ void store_piece_i8(const KernelArgs &p, const int *r, long long row, bool row_ok, int col0)
 {
+    if (p.out_mode == OUT_DIGITS_T) {
+        // columns 4*m + j of this thread's accumulator row n are the four digit planes of activation row m: recombined
+        // here in 64-bit integers (exact), scaled, and stored transposed — the lanes of a warp are 32 consecutive n of
+        // one output row m, whole 128-byte lines
+        const int m0 = col0 >> 2;
+        const float sc = row_ok ? __ldg(p.colscale + row) : 0.0f, bs = (row_ok && p.bias) ? __ldg(p.bias + row) : 0.0f;
+        float *out = reinterpret_cast<float *>(p.C);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int m = m0 + i;
+            const long long t = (long long)r[4 * i] + ((long long)r[4 * i + 1] << 8) + ((long long)r[4 * i + 2] << 16) +
+                                ((long long)r[4 * i + 3] << 24);
+            if (row_ok && m < p.dg_rows) out[(long long)m * p.ldc + row] = qt_finish(t, __ldg(p.dg_inv_s + m), sc, bs, p.act);
+        }
+        return;
+    }
     const bool full = col0 + 32 <= p.N;
     if (p.acc_out && row_ok) {
         int32_t *dst = p.acc_out + row * p.ldc + col0;

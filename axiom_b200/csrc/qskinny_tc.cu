@@ -88,6 +88,8 @@ __device__ __forceinline__ float qx_absmax(const float4 &v, bool &bad)
     return fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
 }
 
+// MP > 0: digit plane j of row m at (j * MP + m) * K (four planes of MP rows); MP == 0: the four digit rows of a row
+// side by side, digit j of row m at (4 * m + j) * K
 template <int QX_THREADS>
 __global__ void __launch_bounds__(QX_THREADS) qx_digits_kernel(const float *__restrict__ a, int K, int MP,
                                                                int8_t *__restrict__ digits, float *__restrict__ inv_s)
@@ -128,8 +130,8 @@ __global__ void __launch_bounds__(QX_THREADS) qx_digits_kernel(const float *__re
     // a row with an infinity or a NaN comes out as NaN
     if (tid == 0) inv_s[m] = finite ? __uint_as_float((uint32_t)(127 - sexp) << 23) : __int_as_float(0x7FC00000);
 
-    const size_t plane4 = ((size_t)MP * K) >> 2;
-    uint32_t *dst = reinterpret_cast<uint32_t *>(digits + (size_t)m * K);
+    const size_t plane4 = MP > 0 ? ((size_t)MP * K) >> 2 : (size_t)K >> 2;
+    uint32_t *dst = reinterpret_cast<uint32_t *>(digits + (size_t)m * K * (MP > 0 ? 1 : 4));
 #pragma unroll
     for (int r = 0; r < QX_CACHE; ++r) {
         const int i = tid + QX_THREADS * r;
@@ -142,19 +144,6 @@ __global__ void __launch_bounds__(QX_THREADS) qx_digits_kernel(const float *__re
 __device__ __forceinline__ void qt_report(int *err, int code)
 {
     if (err) atomicCAS(err, 0, code);
-}
-
-// total * scale * 2^-s, then the dense layer's bias and activation.  The 64-bit total (|total| < 2^55) is cut
-// into a signed head and 24 low bits, which convert with 32-bit instructions: the epilogue is a handful of warps
-// running dependent chains, so its instruction count is what it costs.
-__device__ __forceinline__ float qt_finish(long long total, float inv_s, float scale, float bias, int act)
-{
-    const float head = (float)(int)(total >> 24);
-    const float tail = (float)(int)((unsigned)total & 0xFFFFFFu);
-    float v = fmaf(head, 16777216.0f, tail) * scale * inv_s + bias;
-    if (act == 1) v = fmaxf(v, 0.0f);
-    else if (act == 2) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
-    return v;
 }
 
 template <int MP>
@@ -383,69 +372,11 @@ static int launch_inst(const QtMaps &tm, const QtArgs &a, int kb_total, dim3 gri
     return (int)cudaLaunchKernelEx(&cfg, kern, tm, a, kb_total);
 }
 
-// ------------------------------------------------------------------------- large M: the digits as a GEMM operand
-// For M > 64 the four digit planes [4][M][K] are the A operand of ONE int8 GEMM on the dense tcgen05 core
-// ([4M, K] x [N, K]^T -> s32 [4M, N]); this kernel recombines the four row blocks of that result:
-//     out[m,n] = act(scale[n] * 2^-s[m] * sum_j 256^j * acc[j*M + m, n] + bias[n]).
-__global__ void __launch_bounds__(256) qx_combine_kernel(const int32_t *__restrict__ acc, const float *__restrict__ inv_s,
-                                                         const float *__restrict__ scales, const float *__restrict__ bias,
-                                                         int act, float *__restrict__ out, int M, int64_t N)
-{
-    const int64_t n4 = (N + 3) >> 2;
-    const int64_t total = (int64_t)M * n4;
-    const bool vec = (N & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
-                     (reinterpret_cast<uintptr_t>(acc) & 15) == 0;
-    for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
-        const int m = (int)(i / n4);
-        const int64_t n = (i - (int64_t)m * n4) << 2;
-        const float is = __ldg(inv_s + m);
-        int d[4][4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int32_t *src = acc + ((int64_t)j * M + m) * N + n;
-            if (vec) {
-                const int4 v = __ldcs(reinterpret_cast<const int4 *>(src));
-                d[j][0] = v.x; d[j][1] = v.y; d[j][2] = v.z; d[j][3] = v.w;
-            } else {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) d[j][e] = n + e < N ? src[e] : 0;
-            }
-        }
-        float y[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const long long t = (long long)d[0][e] + ((long long)d[1][e] << 8) + ((long long)d[2][e] << 16) +
-                                ((long long)d[3][e] << 24);
-            const int64_t c = n + e < N ? n + e : N - 1;
-            y[e] = qt_finish(t, is, __ldg(scales + c), bias ? __ldg(bias + c) : 0.0f, act);
-        }
-        float *dst = out + (int64_t)m * N + n;
-        if (vec) {
-            *reinterpret_cast<float4 *>(dst) = make_float4(y[0], y[1], y[2], y[3]);
-        } else {
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-                if (n + e < N) dst[e] = y[e];
-        }
-    }
-}
-
 int launch_qx_digits(const float *act_in, int64_t M, int64_t K, int64_t plane_rows, int8_t *digits, float *inv_s,
                      cudaStream_t st)
 {
     if (M <= 64) qx_digits_kernel<1024><<<(unsigned)M, 1024, 0, st>>>(act_in, (int)K, (int)plane_rows, digits, inv_s);
     else qx_digits_kernel<256><<<(unsigned)M, 256, 0, st>>>(act_in, (int)K, (int)plane_rows, digits, inv_s);
-    return (int)cudaGetLastError();
-}
-
-int launch_qx_combine(const int32_t *acc, const float *inv_s, const float *scales, const float *bias, int act, float *out,
-                      int64_t M, int64_t N, int sm_count, cudaStream_t st)
-{
-    const int64_t total = M * ((N + 3) >> 2);
-    int64_t blocks = (total + 255) / 256;
-    const int64_t cap = (int64_t)sm_count * 16;
-    if (blocks > cap) blocks = cap;
-    qx_combine_kernel<<<(unsigned)blocks, 256, 0, st>>>(acc, inv_s, scales, bias, act, out, (int)M, N);
     return (int)cudaGetLastError();
 }
 

@@ -16,12 +16,25 @@ size_t qskinny_tc_workspace_bytes(int64_t M, int64_t K);
 int launch_qskinny_tc(const float *a, const int8_t *q, const float *scales, const float *bias, int act, float *out,
                       int64_t M, int64_t N, int64_t K, void *workspace, int *err, int sm_count, cudaStream_t st);
 
-// M > 64: the same digit planes as the A operand of one int8 GEMM.  launch_qx_digits writes digits[4][plane_rows][K]
-// (row m of plane j at (j * plane_rows + m) * K) and 2^-s per row; launch_qx_combine turns the s32 result
-// [4 * M, N] of digits x weights^T into out[M, N] with the per-column scale, bias and activation.
+// M > 64: the same digit planes as an operand of one int8 GEMM.  launch_qx_digits writes digits[4][plane_rows][K]
+// (row m of plane j at (j * plane_rows + m) * K; plane_rows == 0: interleaved, digit j of row m at (4 * m + j) * K)
+// and 2^-s per row.  The interleaved form is the B operand of the int8 GEMM core, whose epilogue recombines the four
+// digit sums of every output (OUT_DIGITS_T).
 int launch_qx_digits(const float *a, int64_t M, int64_t K, int64_t plane_rows, int8_t *digits, float *inv_s,
                      cudaStream_t st);
-int launch_qx_combine(const int32_t *acc, const float *inv_s, const float *scales, const float *bias, int act, float *out,
-                      int64_t M, int64_t N, int sm_count, cudaStream_t st);
+
+#ifdef __CUDACC__
+// Exact integer sum of digit products -> fp32 result: total * 2^-s * scale (+ bias) -> activation.  |total| < 2^47 is cut
+// into a signed head and 24 low bits, which convert with 32-bit instructions.
+__device__ __forceinline__ float qt_finish(long long total, float inv_s, float scale, float bias, int act)
+{
+    const float head = (float)(int)(total >> 24);
+    const float tail = (float)(int)((unsigned)total & 0xFFFFFFu);
+    float v = fmaf(head, 16777216.0f, tail) * scale * inv_s + bias;
+    if (act == 1) v = fmaxf(v, 0.0f);
+    else if (act == 2) v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    return v;
+}
+#endif
 
 }  // namespace axb
