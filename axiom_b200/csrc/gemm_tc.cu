@@ -835,7 +835,8 @@ static int launch_common(int kind, const TcOperand &A, const TcOperand &B, const
         snprintf(g_err, sizeof g_err, "launch_gemm_tc: bad operand description");
         return (int)cudaErrorInvalidValue;
     }
-    const TcPlan pl = make_plan(kind, prod, M, N, K, sm_count, splitk, cv == nullptr);
+    // (a convolution takes CTA pairs too: each CTA's 128 columns of a tile are two whole patches)
+    const TcPlan pl = make_plan(kind, prod, M, N, K, sm_count, splitk, cv == nullptr || kind != KIND_I8);
     const int bn = pl.bn, swb = pl.swb;
     const bool use_pair = pl.pair;
     const int64_t mt = pl.mt, nt = pl.nt;

@@ -96,6 +96,51 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
             const int k_blocks = p.k_blocks, stages = p.stages, npa = p.npa, npb = p.npb;
             const uint32_t sbytes = (uint32_t)stage_bytes;
             grid_dep_wait();   // the operand planes come from the kernel before this one
+            if (!do_a && p.cv_taps > 0) {
+                // implicit convolution (see gemm_tc.cu): this CTA's 128 columns of the tile are two 64-pixel patches;
+                // a stage of B is, per plane, one box per patch at the window offset of the stage's tap
+                constexpr int NPATCH = (BN / 2) / 64, PATCH_BYTES = 64 * SWB;
+                const int cblocks = p.cv_cblocks, kw = p.cv_kw, pw = p.cv_pw, phh = 64 / p.cv_pw;
+                for (int t = pair; t < total_tiles && ok; t += npairs) {
+                    int mt, nt;
+                    tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
+                    int x0[NPATCH], y0[NPATCH], n0[NPATCH];
+#pragma unroll
+                    for (int q = 0; q < NPATCH; ++q) {
+                        // (a patch past the last one reads sample `batch`: outside the tensor, all zeros)
+                        const int patch = (nt * BN + (int)rank * (BN / 2)) / 64 + q, n = patch / p.cv_npatch_s,
+                                  rem = patch - n * p.cv_npatch_s, py = rem / p.cv_px;
+                        n0[q] = n;
+                        x0[q] = (rem - py * p.cv_px) * pw - p.cv_pad_w;
+                        y0[q] = py * phh - p.cv_pad_h;
+                    }
+                    int cb = 0, ky = 0, kx = 0;
+                    for (int kb = 0; kb < k_blocks; ++kb) {
+                        if (!mbar_wait_bounded(bar_empty + 8 * s, ph ^ 1u)) {
+                            report(p.err, ERR_PRODUCER_WAIT);
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t fb = map_to_cta(bar_full + 8 * s, 0);
+                        uint32_t dst = stage0 + s * sbytes + npa * A_BYTES;
+                        for (int i = 0; i < npb; ++i)
+#pragma unroll
+                            for (int q = 0; q < NPATCH; ++q, dst += PATCH_BYTES)
+                                tma_load_4d_pair(dst, &tm.b[i], fb, cb * BKE, x0[q] + kx, y0[q] + ky, n0[q]);
+                        if (++cb == cblocks) {
+                            cb = 0;
+                            if (++kx == kw) {
+                                kx = 0;
+                                ++ky;
+                            }
+                        }
+                        if (++s == (uint32_t)stages) {
+                            s = 0;
+                            ph ^= 1u;
+                        }
+                    }
+                }
+            } else
             for (int t = pair; t < total_tiles && ok; t += npairs) {
                 int mt, nt;
                 tile_coords(t, p.m_tiles, p.n_tiles, mt, nt);
@@ -257,6 +302,7 @@ gemm_tc_pair_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__
                                                                                 sum[c * 32 + 4 * j4 + 2], sum[c * 32 + 4 * j4 + 3]);
                             __syncwarp();
                             if (p.tma_store) store_piece_f32_tma(p, tm.c, stg, row0, col0, lane);
+                            else if (p.cv_taps > 0) store_piece_f32_conv(p, stg, row0, col0, lane);
                             else store_piece_f32(p, stg, row0, col0, lane, rows_aligned);
                         }
                     }

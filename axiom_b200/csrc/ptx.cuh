@@ -503,4 +503,16 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void *tmap,
         : "memory");
 }
 
+// the 4-D form (the image windows of an implicit convolution), same completion rule
+__device__ __forceinline__ void tma_load_4d_pair(uint32_t dst, const void *tmap, uint32_t bar, int32_t crd0, int32_t crd1,
+                                                 int32_t crd2, int32_t crd3)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        :
+        : "r"(dst), "l"(tmap), "r"(bar), "r"(crd0), "r"(crd1), "r"(crd2), "r"(crd3)
+        : "memory");
+}
+
 }  // namespace axb

@@ -592,7 +592,7 @@ def test_mha_output_proj_fused(engine, oracle, rows, D, forward):
     assert engine.device_error() == 0
 
 
-@pytest.mark.parametrize("geom", [(8, 256, 256, 56, 56, 3, 3, 1, 1, 1, 1),   # a ResNet stage at batch 8: one implicit GEMM, 128 x 256 tiles
+@pytest.mark.parametrize("geom", [(8, 256, 256, 56, 56, 3, 3, 1, 1, 1, 1),   # a ResNet stage at batch 8: one implicit GEMM on CTA pairs (98 tiles of 256 x 256)
                                   (3, 40, 20, 12, 20, 5, 5, 1, 1, 2, 2),      # patches of the last tile run into the next sample and past the end
                                   (5, 16, 3, 6, 8, 3, 3, 1, 1, 1, 1),         # samples smaller than one patch row
                                   (2, 24, 8, 15, 15, 3, 3, 2, 2, 1, 1),       # strided: samples one by one through the gathered form
