@@ -29,7 +29,7 @@
 
 namespace axb {
 
-static constexpr int QT_THREADS = 576;
+static constexpr int QT_THREADS = 608;   // warp 0: TMA producer, 1 and 18: MMA issuers, 2..17: drain
 static constexpr int QT_BN = 128;                    // weight rows per CTA
 static constexpr int QT_KB = 128;                    // k per stage: one 128-byte swizzled row
 static constexpr int QT_W_BYTES = QT_BN * QT_KB;     // 16 KB
@@ -154,7 +154,10 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
     constexpr uint32_t X_BYTES = NB * 128;
     constexpr uint32_t STAGE = QT_W_BYTES + X_BYTES;
     constexpr int STAGES = qt_stages(MP);
-    constexpr uint32_t TCOLS = NB < 32 ? 32 : NB;
+    // two MMA issuers with an accumulator set each up to 32 rows; at 64 rows (N = 256) the MMAs themselves fill the
+    // issuing thread's time and a second set only lengthens the drain (measured: 26.5 us against 24.6)
+    constexpr bool TWO = MP <= 32;
+    constexpr uint32_t TCOLS = (TWO ? 2 : 1) * NB < 32 ? 32 : (TWO ? 2 : 1) * NB;
     enum { B_FULL = 0, B_EMPTY = STAGES, B_ACC = 2 * STAGES };
 
     extern __shared__ uint8_t smem_raw[];
@@ -179,7 +182,7 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
             mbar_init(bar(B_FULL + s), 1);
             mbar_init(bar(B_EMPTY + s), 1);
         }
-        mbar_init(bar(B_ACC), 1);
+        mbar_init(bar(B_ACC), TWO ? 2 : 1);   // one arrival per MMA issuer
         mbar_fence_init();
         // The weights depend on nothing this call computes: the first ring of weight tiles is requested before
         // anything else happens in this CTA — before tensor memory is allocated and long before the digits of the
@@ -206,7 +209,7 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
     const int64_t col = n0 + t_row;
     const bool col_ok = col < a.N;
     float col_scale = 0.0f, col_bias = 0.0f;    // inputs of the call, not of the pre-pass: loaded ahead of the K loop
-    if (warp >= 2 && col_ok) {
+    if (warp >= 2 && warp < 18 && col_ok) {
         col_scale = __ldg(a.scales + col);
         if (a.bias) col_bias = __ldg(a.bias + col);
     }
@@ -232,30 +235,38 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
                 tma_load_3d(st + QT_W_BYTES, &tm.x, bar(B_FULL + s), k0, 0, 0);
             }
         }
-    } else if (warp == 1) {
-        // ---------------------------------------------------------- MMA issuer
-        if (lane == 0) {
+    } else if (warp == 1 || warp == 18) {
+        // --------------------------------------------------------- MMA issuers
+        // Two threads, even and odd k-blocks, each into its own accumulator columns (the integer sums are added by the
+        // drain warps): a k-block costs the issuing THREAD ~600 cycles — four MMAs at ~70, the commit ~120, barrier
+        // and fence ~200 — while the tensor pipe needs a fraction of that, and with one issuer that, not the memory
+        // system, paced the stream (16 KB per 0.4 us and SM: 5.1 TB/s over 128 SMs).
+        if (lane == 0 && (TWO || warp == 1)) {
+            const int par = warp == 1 ? 0 : 1;
             const uint64_t desc = smem_desc_kmajor(0, 128);
             const uint32_t idesc = make_idesc<KIND_I8>(QT_BN, NB);
+            const uint32_t acc = tmem + (uint32_t)(par * NB);
             bool ok = true;
             uint32_t accf = 0u;
-            for (int i = 0; i < nkb; ++i) {
+            for (int i = par; i < nkb; i += TWO ? 2 : 1) {
                 const int s = i % STAGES;
                 if (!mbar_wait_bounded(bar(B_FULL + s), (i / STAGES) & 1)) { ok = false; break; }
                 tc_fence_after_sync();
                 const uint32_t st = stage_addr(s);
 #pragma unroll
                 for (int ks = 0; ks < QT_KB / 32; ++ks) {
-                    tc_mma<KIND_I8>(tmem, desc | (uint64_t)(((st + ks * 32) & 0x3FFFFu) >> 4),
+                    tc_mma<KIND_I8>(acc, desc | (uint64_t)(((st + ks * 32) & 0x3FFFFu) >> 4),
                                     desc | (uint64_t)(((st + QT_W_BYTES + ks * 32) & 0x3FFFFu) >> 4), idesc, accf);
                     accf = 1u;
                 }
                 tc_commit(bar(B_EMPTY + s));
             }
-            if (ok && nkb > 0) tc_commit(bar(B_ACC));
+            // both issuers arrive on the accumulator barrier: through the pipe when MMAs are in flight, plainly otherwise
+            if (ok && accf) tc_commit(bar(B_ACC));
+            else if (ok) mbar_arrive(bar(B_ACC));
             if (!ok) qt_report(a.err, QERR_MMA);
         }
-    } else {
+    } else if (warp < 18) {
         // --------------------------------------------------------------- drain
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         grid_dep_wait();   // the row scales come from the pre-pass
@@ -276,6 +287,16 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
 #pragma unroll
                 for (int j = 0; j < 4; ++j) tmem_ld_32x32_x4(lane_base + (uint32_t)(j * MP + 4 * g), d[j]);
                 tmem_ld_wait();
+                if (TWO && nkb >= 2) {   // the odd k-blocks' sums (|sum| of both stays below 2^31 for K <= 65536)
+                    uint32_t e[4][4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) tmem_ld_32x32_x4(lane_base + (uint32_t)(NB + j * MP + 4 * g), e[j]);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) d[j][u] += e[j][u];
+                }
             } else {
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
@@ -304,7 +325,7 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
 
     if (nslices > 1) {
         cluster_sync_all();   // release / acquire: every slice's partial sums have landed
-        if (warp >= 2 && col_ok) {
+        if (warp >= 2 && warp < 18 && col_ok) {
             // integer sums of the rows this slice owns, out of its own shared memory: nobody reads a peer after the
             // barrier, so a CTA may leave as soon as it is done
             for (int r = quarter; r < rows_owned; r += 4) {
