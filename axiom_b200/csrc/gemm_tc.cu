@@ -38,16 +38,29 @@ namespace axb {
 
 // SPLITK: compiled with the split-K hand-over (KernelArgs::ksplit > 1 allowed); the plain variant keeps the
 // epilogue's registers for itself.
+// Integer tiles of up to 128 columns have a SECOND MMA-issuing thread (warp 11, one warp more than the other
+// instantiations): a 128-byte k-block of such a tile is four short MMAs, and what it costs is the issuing thread's own
+// time — ~70 cycles per MMA, ~120 for the commit, ~200 for barrier and fence, 500-600 cycles against 256 of the tensor
+// pipe.  The two threads take even and odd k-blocks into an accumulator set each; integer sums are exact, so the
+// epilogue's addition of the two sets changes no bit.  (The fp32 kinds keep one issuer: two chains would change the
+// order of the rounded additions and with it the bits that tile shapes otherwise share.)
+template <int KIND, int BN>
+struct TwoIssuers {
+    static constexpr bool value = KIND == KIND_I8 && BN <= 128;
+};
+
 template <int KIND, int BN, int SWB, int NPROD, bool SPLITK>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(NUM_THREADS + (TwoIssuers<KIND, BN>::value ? 32 : 0), 1)
 gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ KernelArgs p)
 {
+    constexpr bool TWO = TwoIssuers<KIND, BN>::value;
+    constexpr int ACC_STRIDE = TWO ? 2 * BN : BN;   // columns between the ping and the pong accumulator
     constexpr int A_BYTES = BM * SWB;   // one A plane of one stage
     constexpr int B_BYTES = BN * SWB;
     constexpr int ES = KIND == KIND_TF32 ? 4 : (KIND == KIND_BF16 ? 2 : 1);
     constexpr int BKE = SWB / ES;       // k elements per stage
     constexpr int KSTEPS = SWB / 32;    // one MMA consumes 32 bytes of K
-    constexpr int TMEM_COLS = 2 * BN;
+    constexpr int TMEM_COLS = 2 * ACC_STRIDE;
     constexpr uint32_t IDESC = make_idesc<KIND>(BM, BN);
 
     extern __shared__ uint8_t smem_raw[];
@@ -74,7 +87,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
             mbar_init(bar_empty + 8 * s, 1);
         }
         for (int a = 0; a < 2; ++a) {
-            mbar_init(bar_tfull + 8 * a, 1);
+            mbar_init(bar_tfull + 8 * a, TWO ? 2 : 1);   // one arrival per MMA issuer
             mbar_init(bar_tempty + 8 * a, 8);
         }
         mbar_fence_init();
@@ -181,8 +194,8 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
                 }
             }
         }
-    } else if (warp == 1) {
-        // -------------------------------------------------------- MMA issuer
+    } else if (warp == 1 || (TWO && warp == B_PRODUCER_WARP + 1)) {
+        // ------------------------------------------------------- MMA issuer(s)
         // K is cut into chunks of p.chunk_kb k-blocks; every chunk starts a
         // fresh TMEM accumulator (ping-pong) that the epilogue warps drain and
         // add up in registers.  The tensor core truncates when it accumulates,
@@ -198,6 +211,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
             const uint32_t prod_a = p.prod_a, prod_b = p.prod_b;
             const uint64_t desc_hi = smem_desc_kmajor(0, SWB);
             const uint32_t npa_bytes = p.npa * A_BYTES, sbytes = (uint32_t)stage_bytes;
+            const int par = (TWO && warp != 1) ? 1 : 0;   // with two issuers: this one's k-blocks of a chunk (even / odd)
             for (int w = blockIdx.x; w < items && ok; w += gridDim.x) {
                 const int kb_lo = (w % ksplit) * p.kb_per_slice, kb_hi = min(k_blocks, kb_lo + p.kb_per_slice);
                 for (int kb0 = kb_lo; kb0 < kb_hi && ok; kb0 += chunk_kb, ++vt) {
@@ -208,25 +222,33 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
                         break;
                     }
                     tc_fence_after_sync();
-                    const uint32_t d_tmem = tmem_base + acc * BN;
+                    const uint32_t d_tmem = tmem_base + acc * ACC_STRIDE + par * BN;
                     const int kb1 = min(kb_hi, kb0 + chunk_kb);
+                    bool issued = false;
                     for (int kb = kb0; kb < kb1; ++kb) {
-                        if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
-                            report(p.err, ERR_MMA_WAIT_FULL);
-                            ok = false;
-                            break;
+                        if (!TWO || ((kb - kb0) & 1) == par) {
+                            if (!mbar_wait_bounded(bar_full + 8 * s, ph)) {
+                                report(p.err, ERR_MMA_WAIT_FULL);
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after_sync();
+                            const uint32_t sa = stage0 + s * sbytes;
+                            issue_stage_mmas<KIND, SWB, NPROD, false, A_BYTES, B_BYTES>(
+                                d_tmem, sa, sa + npa_bytes, prod_a, prod_b, desc_hi, IDESC, !issued);
+                            issued = true;
+                            tc_commit(bar_empty + 8 * s);
                         }
-                        tc_fence_after_sync();
-                        const uint32_t sa = stage0 + s * sbytes;
-                        issue_stage_mmas<KIND, SWB, NPROD, false, A_BYTES, B_BYTES>(
-                            d_tmem, sa, sa + npa_bytes, prod_a, prod_b, desc_hi, IDESC, kb == kb0);
-                        tc_commit(bar_empty + 8 * s);
                         if (++s == (uint32_t)stages) {
                             s = 0;
                             ph ^= 1u;
                         }
                     }
-                    if (ok) tc_commit(bar_tfull + 8 * acc);
+                    if (ok) {
+                        // (an issuer without a k-block in this chunk arrives plainly: nothing of its own is in flight)
+                        if (issued || !TWO) tc_commit(bar_tfull + 8 * acc);
+                        else mbar_arrive(bar_tfull + 8 * acc);
+                    }
                 }
             }
         }
@@ -272,8 +294,15 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
                         if (col0 >= p.N) break;  // warp-uniform
                         uint32_t r[32];
                         __syncwarp();  // the TMEM load is warp-collective: reconverge after masked stores
-                        tmem_ld_32x32(lane_addr + acc * BN + c * 32, r);
+                        tmem_ld_32x32(lane_addr + acc * ACC_STRIDE + c * 32, r);
                         tmem_ld_wait();
+                        if (TWO && kb_hi - kb_lo >= 2) {   // the odd k-blocks' sums
+                            uint32_t r2[32];
+                            tmem_ld_32x32(lane_addr + acc * ACC_STRIDE + BN + c * 32, r2);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) r[j] += r2[j];
+                        }
                         store_piece_i8(p, reinterpret_cast<const int *>(r), row, row_ok, col0);
                     }
                     tc_fence_before_sync();
@@ -286,8 +315,15 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
 #pragma unroll
                         for (int c = 0; c < PIECES; ++c) {
                             uint32_t r[32];
-                            tmem_ld_32x32(lane_addr + acc * BN + c * 32, r);
+                            tmem_ld_32x32(lane_addr + acc * ACC_STRIDE + c * 32, r);
                             tmem_ld_wait();
+                            if (TWO && kb_hi - kb_lo >= 2) {
+                                uint32_t r2[32];
+                                tmem_ld_32x32(lane_addr + acc * ACC_STRIDE + BN + c * 32, r2);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) r[j] += r2[j];
+                            }
 #pragma unroll
                             for (int j = 0; j < 32; ++j) v[c * 32 + j] = (int)r[j];
                         }
@@ -325,7 +361,7 @@ gemm_tc_kernel(const __grid_constant__ TmapPack tm, const __grid_constant__ Kern
 #pragma unroll
                     for (int c = 0; c < PIECES; ++c) {
                         uint32_t r[32];
-                        tmem_ld_32x32(lane_addr + acc * BN + c * 32, r);
+                        tmem_ld_32x32(lane_addr + acc * ACC_STRIDE + c * 32, r);
                         tmem_ld_wait();
 #pragma unroll
                         for (int j = 0; j < 32; ++j) sum[c * 32 + j] += __uint_as_float(r[j]);
@@ -650,7 +686,7 @@ static int launch_inst(const TmapPack &tm, KernelArgs &ka, int stage_bytes, int 
     // tail; the TMA producers wait for the pre-pass to have finished before the first load
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.blockDim = dim3(NUM_THREADS + (TwoIssuers<KIND, BN>::value ? 32 : 0));
     cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = stream;
     cudaLaunchAttribute at[2];
