@@ -649,9 +649,10 @@ def test_w8a32_skinny_tensor_core_kernel(engine, oracle, shape):
 
 @pytest.mark.parametrize("shape", [(65, 1024, 1024), (129, 1000, 1168), (70, 1001, 1024), (512, 2048, 512)])
 def test_w8a32_digit_planes_as_gemm_operand(engine, oracle, shape):
-    """M > 64: the four int8 digit planes of the activations are the A operand of one int8 GEMM on the dense core; its
-    s32 result [4M, N] is recombined in 64-bit integers.  Ragged M, N (also not a multiple of 4: scalar path of the
-    combine kernel) and K, an outlier, and a row with an infinity."""
+    """M > 64: the four int8 digit rows of every activation row, interleaved, are the B operand of one int8 GEMM on the
+    dense core against the weights as the A operand; the epilogue recombines the four digit sums of an output in 64-bit
+    integers and stores it transposed.  Ragged M, N (also not a multiple of 4) and K, an outlier, and a row with an
+    infinity."""
     M, N, K = shape
     a, w = oracle.uniform((M, K), 7), oracle.uniform((N, K), 13)
     a[1, 3] = 1000.0
