@@ -935,14 +935,16 @@ static int launch_common(int kind, const TcOperand &A, const TcOperand &B, const
         // the output leaves through store_piece_f32_conv
         ka.ldc = cv->out_h * cv->out_w;
         ka.cv_out_w = (int)cv->out_w;
-    } else
-    // plain aligned fp32 output that is not read back: the staging tiles leave through TMA stores
-    if (kind != KIND_I8 && ep.out_mode == OUT_F32 && ep.hs_dk == 0 && ka.n_extra == 0 && ep.beta == 0.0f && ep.C &&
+    }
+    // aligned fp32 output that is not read back: the staging tiles leave through TMA stores; beta == 1 without bias and
+    // activation (the accumulating calls of a backward pass) is a reduce-add of the same tiles
+    const int tma_mode = cv ? 0 : (ep.beta == 0.0f ? 1 : ((ep.beta == 1.0f && !ep.bias && ep.act == ACT_NONE) ? 2 : 0));
+    if (kind != KIND_I8 && ep.out_mode == OUT_F32 && ep.hs_dk == 0 && ka.n_extra == 0 && tma_mode && ep.C &&
         (reinterpret_cast<uintptr_t>(ep.C) & 15) == 0 && ep.ldc % 4 == 0) {
         int e = encode_f32_store_tmap(&tm.c[0], reinterpret_cast<float *>(ep.C), M, N, ep.ldc);
         if (e) return e;
-        ka.tma_store = 1;
-    } else if (kind != KIND_I8 && ep.out_mode == OUT_F32 && ep.hs_dk > 0 && ep.beta == 0.0f && ep.hs_S % 32 == 0 &&
+        ka.tma_store = tma_mode;
+    } else if (kind != KIND_I8 && ep.out_mode == OUT_F32 && ep.hs_dk > 0 && tma_mode && ep.hs_S % 32 == 0 &&
                ep.hs_dk % 32 == 0 && M % ep.hs_S == 0 && N % (ep.hs_H * ep.hs_dk) == 0 && N / (ep.hs_H * ep.hs_dk) <= 3) {
         // head-major scatter of whole 32 x 32 pieces: one store map per destination, each seen as a matrix of
         // B*H*S rows of dk floats (a piece never straddles a batch, S % 32 == 0, or a head, dk % 32 == 0)
@@ -954,7 +956,7 @@ static int launch_common(int kind, const TcOperand &A, const TcOperand &B, const
                 int e = encode_f32_store_tmap(&tm.c[i], ep.hs_out[i], (M / ep.hs_S) * ep.hs_H * ep.hs_S, ep.hs_dk, ep.hs_dk);
                 if (e) return e;
             }
-            ka.tma_store = 1;
+            ka.tma_store = tma_mode;
         }
     }
     const int64_t work = mt * nt * ka.ksplit;

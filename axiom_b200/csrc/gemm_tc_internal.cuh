@@ -47,7 +47,10 @@ struct KernelArgs {
     const float *dg_inv_s;   // OUT_DIGITS_T, see TcEpilogue
     int dg_rows;
     int hs_dk, hs_S, hs_H;   // head-major scatter of the output (hs_dk > 0), see TcEpilogue
-    int tma_store;           // fp32 output leaves through TMA stores of the staging tiles (beta == 0, aligned; plain C or head-major)
+    // fp32 output leaves through TMA copies of the staging tiles (aligned; plain C or head-major): 1 = stores (beta == 0),
+    // 2 = reduce-adds (beta == 1 without bias and activation: C += alpha * sums, one rounded addition per element in
+    // the memory system, C is never read into the SM)
+    int tma_store;
     float *hs_out[3];
     // split-K (ksplit > 1): work item w = tile * ksplit + slice covers k-blocks [slice * kb_per_slice, ...); every
     // slice leaves its partial sums in sk_scratch and counts itself in on sk_counters[tile]; the slice that counts
@@ -214,7 +217,11 @@ static __device__ __forceinline__ void store_piece_f32_tma(const KernelArgs &p, 
             const int D = p.hs_H * p.hs_dk;
             const int which = col0 / D, rem = col0 - which * D, h = rem / p.hs_dk, d0 = rem - h * p.hs_dk;
             const long long b = row0 / p.hs_S, s0 = row0 - b * p.hs_S;
-            tma_store_2d(tmc + which, smem_u32(stg), d0, (int32_t)((b * p.hs_H + h) * p.hs_S + s0));
+            const int32_t r0 = (int32_t)((b * p.hs_H + h) * p.hs_S + s0);
+            if (p.tma_store == 2) tma_reduce_add_2d(tmc + which, smem_u32(stg), d0, r0);
+            else tma_store_2d(tmc + which, smem_u32(stg), d0, r0);
+        } else if (p.tma_store == 2) {
+            tma_reduce_add_2d(tmc, smem_u32(stg), col0, (int32_t)row0);
         } else {
             tma_store_2d(tmc, smem_u32(stg), col0, (int32_t)row0);
         }

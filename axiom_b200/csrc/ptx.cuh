@@ -300,6 +300,15 @@ __device__ __forceinline__ void tma_store_2d(const void *tmap, uint32_t src, int
                  : "memory");
 }
 
+// The same box ADDED to what global memory holds (one rounded fp32 addition per element, done by the memory system:
+// nothing is read back into the SM).  Same coordinate rules as the store.
+__device__ __forceinline__ void tma_reduce_add_2d(const void *tmap, uint32_t src, int32_t crd0, int32_t crd1)
+{
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap),
+                 "r"(src), "r"(crd0), "r"(crd1)
+                 : "memory");
+}
+
 __device__ __forceinline__ void tma_store_commit()
 {
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
