@@ -672,7 +672,26 @@ def w_attention(ctx, shared):
                     value=fl / (t["ms_per_step"] * 1e-3) / 1e12, unit="TFLOP/s",
                     roofline=tensor_roof(fl / (t["kernel_ms"] * 1e-3) / 1e12, bf16 / 6, "measured bf16 burst / 2 / 3"),
                     parity_checked=bool(e <= 1e-5), parity_nerr=e))
-    del Xq, Wq, hd3, gq, gk, gv, dOt
+    # the layer's backward GEMMs on the same shapes: the fused projection's weight gradients accumulated into the three
+    # [D, D] gradients (x^T . dQKV with beta = 1: the epilogue leaves as TMA reduce-adds), and dattn = dout . Wo^T stored
+    # head-major
+    dQKV = ctx.normal((Bq * Sq, 3 * Dq), 0.5)
+    g0 = [ctx.uniform((Dq, Dq)) for _ in range(3)]
+    grads = [g.clone() for g in g0]
+    calls = [0]
+
+    def dw():
+        calls[0] += 1
+        eng.dwqkv_split_acc(Xq, dQKV, *grads)
+    t = ctx.core_time(dw, 10, 2)
+    rows = sample_rows(Dq, 2)
+    prod = ctx.oracle.gemm_f64(np.ascontiguousarray(host(Xq).T[rows]), host(dQKV))            # rows of x^T . dQKV
+    e = max(nerr(host(grads[i][rows]), host(g0[i][rows]).astype(np.float64) + calls[0] * prod[:, i * Dq:(i + 1) * Dq]) for i in range(3))
+    out.append(dict(t, name="dwqkv_acc", workload="dWq,dWk,dWv [1024x1024] += X[8192x1024]^T . dQKV[8192x3072] column blocks (one launch, "
+                    "accumulating epilogue)", value=fl / (t["ms_per_step"] * 1e-3) / 1e12, unit="TFLOP/s",
+                    roofline=tensor_roof(fl / (t["kernel_ms"] * 1e-3) / 1e12, bf16 / 6, "measured bf16 burst / 2 / 3"),
+                    parity_checked=bool(e <= 1e-5), parity_nerr=e, parity="sampled rows after every timed call against float64"))
+    del Xq, Wq, hd3, gq, gk, gv, dOt, dQKV, grads, g0
     # single-token decode against a KV cache: config-4 heads, 4096 cached tokens = 268 MB of K and V
     kc, vc = (ctx.normal((BH, 4096, dk)) for _ in range(2))
     qn, on = ctx.normal((BH, dk)), torch.empty((BH, dk), device="cuda")
