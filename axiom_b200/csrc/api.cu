@@ -78,8 +78,9 @@ inline Engine &cur()
     return g_engines[d];
 }
 
-// split-K scratch of the tensor-core GEMM: room for one partial tile per SM (148 x 128 x 256 fp32 < 20 MiB)
-constexpr size_t kSplitScratch = (size_t)20 << 20;
+// split-K scratch of the tensor-core GEMM: one partial tile per work item (up to 147 tiles x 4 slices of 128 x 256 fp32 would be 74 MiB;
+// the planner cuts K less finely when the scratch does not hold that)
+constexpr size_t kSplitScratch = (size_t)64 << 20;
 constexpr int kSplitCounters = 1024;
 
 int fail(int status, const char *fmt, ...)

@@ -710,10 +710,10 @@ template <int KIND, int SWB, int NPROD>
 static int launch_bn(int bn, const TmapPack &tm, KernelArgs &ka, int npa, int npb, int grid, cudaStream_t st)
 {
     const int sb = npa * BM * SWB + npb * bn * SWB;
-    // K is split only on 128- and 64-column tiles (a problem that takes 256-column tiles has enough of them)
     const bool split = ka.ksplit > 1;
     switch (bn) {
-    case 256: return launch_inst<KIND, 256, SWB, NPROD, false>(tm, ka, sb, grid, st);
+    case 256: return split ? launch_inst<KIND, 256, SWB, NPROD, true>(tm, ka, sb, grid, st)
+                           : launch_inst<KIND, 256, SWB, NPROD, false>(tm, ka, sb, grid, st);
     case 128: return split ? launch_inst<KIND, 128, SWB, NPROD, true>(tm, ka, sb, grid, st)
                            : launch_inst<KIND, 128, SWB, NPROD, false>(tm, ka, sb, grid, st);
     default: return split ? launch_inst<KIND, 64, SWB, NPROD, true>(tm, ka, sb, grid, st)
@@ -790,6 +790,27 @@ static TcPlan make_plan(int kind, const TcProducts &prod, int64_t M, int64_t N, 
         if (tiles > splitk->n_counters) want = 1;
         if (want >= 2) {
             pl.kb_per_slice = (int)((units + want - 1) / want) * unit;
+            pl.ksplit = (pl.k_blocks + pl.kb_per_slice - 1) / pl.kb_per_slice;
+        }
+    }
+    // 256-column tiles that leave the last wave part empty (between half a wave and a whole one, e.g. the 96 tiles of a
+    // 1024 x 3072 weight gradient on 148 SMs): K is cut so that tile x slice items fill whole waves — 96 x 3 = 288 items
+    // are 1.95 rounds of a third of the work each instead of one round at 65 % occupancy.  Taken when it lifts the
+    // occupancy of the rounds by a sixth or more AND a slice keeps at least eight accumulator chunks: the hand-over of a
+    // 128 x 256 partial tile costs as much as several chunks (measured: K = 8192 254 -> 211 us; K = 4096 no gain; K = 2560
+    // with four slices 85 -> 119 us).
+    if (can_split && !use_pair && bn == 256 && pl.ksplit == 1 && tiles * 2 > slots && tiles < slots) {
+        const int unit = (kind != KIND_I8 && pl.chunk_kb < pl.k_blocks) ? pl.chunk_kb : 4;
+        const int64_t units = (pl.k_blocks + unit - 1) / unit;
+        const size_t slice_bytes = (size_t)BM * bn * 4;
+        auto occupancy = [&](int64_t ks) { return (double)(tiles * ks) / (double)(((tiles * ks + slots - 1) / slots) * slots); };
+        int64_t best = 1;
+        for (int64_t ks = 2; ks <= 4; ++ks) {
+            if (units / ks < 8 || slice_bytes * (size_t)tiles * (size_t)ks > splitk->scratch_bytes || tiles > splitk->n_counters) break;
+            if (occupancy(ks) > occupancy(best) + 1e-9) best = ks;
+        }
+        if (best > 1 && occupancy(best) >= occupancy(1) * (7.0 / 6.0)) {
+            pl.kb_per_slice = (int)((units + best - 1) / best) * unit;
             pl.ksplit = (pl.k_blocks + pl.kb_per_slice - 1) / pl.kb_per_slice;
         }
     }
@@ -906,7 +927,7 @@ static int launch_common(int kind, const TcOperand &A, const TcOperand &B, const
         ka.sk_scratch = splitk->scratch;
         ka.sk_counters = splitk->counters;
         // two slices of an fp32 tile meet in shared memory (one work item per CTA: mt * nt * 2 <= sm_count by the plan)
-        ka.sk_cluster = (pl.ksplit == 2 && kind != KIND_I8 && mt * nt * 2 <= sm_count) ? 1 : 0;
+        ka.sk_cluster = (pl.ksplit == 2 && kind != KIND_I8 && bn <= 128 && mt * nt * 2 <= sm_count) ? 1 : 0;
     }
     ka.alpha = ep.alpha; ka.beta = ep.beta; ka.bias = ep.bias; ka.colscale = ep.colscale;
     ka.dg_inv_s = ep.dg_inv_s; ka.dg_rows = ep.dg_rows;

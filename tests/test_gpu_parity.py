@@ -698,9 +698,12 @@ def test_qdense_w8a32(engine, oracle, shape, act):
                                    (256, 3136, 2304), (33, 520, 1536),
                                    # two slices per tile (the pair of CTAs meets in shared memory): ragged edges,
                                    # slices of unequal length, K shorter than two chunks, 64-column tiles
-                                   (1000, 900, 1100), (640, 1408, 520), (896, 1024, 300), (7000, 64, 2048)])
+                                   (1000, 900, 1100), (640, 1408, 520), (896, 1024, 300), (7000, 64, 2048),
+                                   # 96 tiles of 128 x 256 on 148 SMs: three slices per tile fill two whole rounds
+                                   (1024, 3072, 6144), (1000, 3000, 6200)])
 def test_split_k_fp32_vs_oracle_and_repeatable(engine, oracle, shape):
-    """Problems with too few 128-column tiles to fill the GPU cut K into slices.  Two slices are a thread-block cluster
+    """Problems with too few 128-column tiles to fill the GPU — or with 256-column tiles that leave the last round of
+    work part empty — cut K into slices.  Two slices are a thread-block cluster
     and meet in shared memory (each CTA finishes one column half); more meet in scratch, where the slice that arrives
     last adds all partial tiles in slice order.  Either way the result is inside the fp32 tolerance AND bitwise
     repeatable, with every epilogue form (bias + GELU, alpha/beta, transposed operands)."""
@@ -745,6 +748,24 @@ def test_split_k_int8_bit_exact(engine, oracle, shape):
     engine.qgemm_w8a8(dev(a), 0.02, dev(b), dev(bs), out_scale, q, acc)
     np.testing.assert_array_equal(host(acc), acc_ref)
     np.testing.assert_array_equal(host(q), q_ref)
+    assert engine.device_error() == 0
+
+
+def test_split_k_int8_wave_filling_sampled_rows(engine, oracle):
+    """100 tiles of 128 x 256 with a long K: K is cut so that tile x slice items fill whole rounds of the 148 SMs; sampled
+    rows against the oracle, bit-exact, and the whole result repeatable."""
+    M, N, K = 1280, 2560, 16384
+    a, b, bs = oracle.int8((M, K), 7), oracle.int8((N, K), 13), oracle.frange((N,), 17, 0.001, 0.02)
+    out_scale = 0.02 * 0.0105 * 73.0 * np.sqrt(K)
+    rows = np.array([0, 127, 128, 640, 1279])
+    acc_ref, q_ref = oracle.qgemm_w8a8(np.ascontiguousarray(a[rows]), 0.02, b, bs, out_scale)
+    q, acc = torch.zeros((M, N), dtype=torch.int8, device="cuda"), torch.zeros((M, N), dtype=torch.int32, device="cuda")
+    engine.qgemm_w8a8(dev(a), 0.02, dev(b), dev(bs), out_scale, q, acc)
+    np.testing.assert_array_equal(host(acc)[rows], acc_ref)
+    np.testing.assert_array_equal(host(q)[rows], q_ref)
+    q2 = torch.zeros((M, N), dtype=torch.int8, device="cuda")
+    engine.qgemm_w8a8(dev(a), 0.02, dev(b), dev(bs), out_scale, q2, None)
+    assert torch.equal(q, q2)
     assert engine.device_error() == 0
 
 
