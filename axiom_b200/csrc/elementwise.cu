@@ -33,19 +33,23 @@ __global__ void __launch_bounds__(256) unary_kernel(const float *__restrict__ in
 
 // out[i,j] = in[i,j] + bias[axis == 0 ? i % period : j]; in-place safe (each element read then written by one
 // thread).  period < M serves a broadcast axis in the middle of an n-d tensor viewed as [outer*axis_len, inner].
+// IDX: 32-bit indices when the tensor has fewer than 2^31 accesses — the row / column split of every access is an
+// integer division, and the 64-bit one costs enough instructions to hold the kernel at three quarters of the copy rate
+template <typename IDX>
 __global__ void __launch_bounds__(256) bias_add_kernel(const float *in, const float *__restrict__ bias,
                                                        int axis, float *out, int64_t M, int64_t N, int64_t period,
                                                        bool vec)
 {
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const IDX stride = (IDX)gridDim.x * (IDX)blockDim.x;
+    const IDX t = (IDX)blockIdx.x * (IDX)blockDim.x + (IDX)threadIdx.x;
+    const IDX per = (IDX)period;
     if (vec) {  // N % 4 == 0 and 16-byte aligned pointers
-        const int64_t n4 = N / 4, total = M * n4;
-        for (int64_t i = t; i < total; i += stride) {
-            const int64_t r = i / n4, c = (i - r * n4) * 4;
+        const IDX n4 = (IDX)(N / 4), total = (IDX)(M * (N / 4));
+        for (IDX i = t; i < total; i += stride) {
+            const IDX r = i / n4, c = (i - r * n4) * 4;
             float4 v = reinterpret_cast<const float4 *>(in)[i];
             if (axis == 0) {
-                const float b = __ldg(bias + r % period);
+                const float b = __ldg(bias + r % per);
                 v.x += b; v.y += b; v.z += b; v.w += b;
             } else {
                 const float4 b = __ldg(reinterpret_cast<const float4 *>(bias + c));
@@ -54,9 +58,10 @@ __global__ void __launch_bounds__(256) bias_add_kernel(const float *in, const fl
             reinterpret_cast<float4 *>(out)[i] = v;
         }
     } else {
-        for (int64_t i = t; i < M * N; i += stride) {
-            const int64_t r = i / N, c = i - r * N;
-            out[i] = in[i] + __ldg(bias + (axis == 0 ? r % period : c));
+        const IDX n = (IDX)N, total = (IDX)(M * N);
+        for (IDX i = t; i < total; i += stride) {
+            const IDX r = i / n, c = i - r * n;
+            out[i] = in[i] + __ldg(bias + (axis == 0 ? r % per : c));
         }
     }
 }
@@ -100,7 +105,9 @@ int launch_bias_add(const float *in, const float *bias, int axis, float *out, in
     if (period <= 0) period = M;
     const bool vec = (N % 4 == 0) && aligned16(in) && aligned16(out) && aligned16(bias);
     const int g = ew_grid(vec ? M * N / 4 : M * N, sm_count);
-    bias_add_kernel<<<g, 256, 0, st>>>(in, bias, axis, out, M, N, period, vec);
+    // (the loop index runs up to total + grid size: keep that inside 31 bits too)
+    if (M * N < ((int64_t)1 << 30)) bias_add_kernel<uint32_t><<<g, 256, 0, st>>>(in, bias, axis, out, M, N, period, vec);
+    else bias_add_kernel<int64_t><<<g, 256, 0, st>>>(in, bias, axis, out, M, N, period, vec);
     return (int)cudaGetLastError();
 }
 

@@ -18,29 +18,33 @@ struct HeadLayoutArgs {
     int accumulate;     // split direction only: add to what the head-major side holds instead of overwriting it
 };
 
-// TO_HEAD: flat -> head-major (+ bias); otherwise head-major -> flat.  VEC = floats per access (4 or 1).
-template <bool TO_HEAD, int VEC>
+// TO_HEAD: flat -> head-major (+ bias); otherwise head-major -> flat.  VEC = floats per access (4 or 1).  IDX: 32-bit
+// indices when every offset stays below 2^31 (four integer divisions per access: in 64 bits they, not memory, paced
+// the kernel — 3.5 TB/s on the config-4 layer).
+template <bool TO_HEAD, int VEC, typename IDX>
 __global__ void __launch_bounds__(256) head_layout_kernel(HeadLayoutArgs a)
 {
-    const int dkv = a.dk / VEC;                             // accesses per head row
-    const int64_t D = (int64_t)a.H * a.dk;
-    const int64_t per_row = (int64_t)a.nslot * a.H * dkv;   // accesses per flat row
-    const int64_t total = a.rows * per_row;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t row = i / per_row;
-        int64_t c = i - row * per_row;                      // access index inside the flat row
-        const int which = (int)(c / ((int64_t)a.H * dkv));
-        c -= (int64_t)which * a.H * dkv;
-        const int h = (int)(c / dkv), d = (int)(c - (int64_t)h * dkv) * VEC;
-        const int64_t b = row / a.S, s = row - b * a.S;
-        const int64_t fi = row * a.nslot * D + (int64_t)which * D + (int64_t)h * a.dk + d;
-        const int64_t hi = ((b * a.H + h) * a.S + s) * a.dk + d;
+    const IDX dkv = (IDX)(a.dk / VEC);                      // accesses per head row
+    const IDX H = (IDX)a.H, S = (IDX)a.S, dk = (IDX)a.dk, nslot = (IDX)a.nslot;
+    const IDX D = H * dk;
+    const IDX per_slot = H * dkv, per_row = nslot * per_slot;   // accesses per slot and per flat row
+    const IDX total = (IDX)a.rows * per_row;
+    const IDX stride = (IDX)gridDim.x * (IDX)blockDim.x;
+    for (IDX i = (IDX)blockIdx.x * (IDX)blockDim.x + (IDX)threadIdx.x; i < total; i += stride) {
+        const IDX row = i / per_row;
+        IDX c = i - row * per_row;                          // access index inside the flat row
+        const IDX which = c / per_slot;
+        c -= which * per_slot;
+        const IDX h = c / dkv, d = (c - h * dkv) * VEC;
+        const IDX b = row / S, s = row - b * S;
+        const IDX fi = row * nslot * D + which * D + h * dk + d;
+        const IDX hi = ((b * H + h) * S + s) * dk + d;
         float *hp = a.head[which];
         if (VEC == 4) {
             if (TO_HEAD) {
                 float4 v = *reinterpret_cast<const float4 *>(a.flat + fi);
                 if (a.bias) {
-                    const float4 bv = __ldg(reinterpret_cast<const float4 *>(a.bias + (int64_t)which * D + (int64_t)h * a.dk + d));
+                    const float4 bv = __ldg(reinterpret_cast<const float4 *>(a.bias + which * D + h * dk + d));
                     v.x += bv.x; v.y += bv.y; v.z += bv.z; v.w += bv.w;
                 }
                 if (a.accumulate) {
@@ -53,7 +57,7 @@ __global__ void __launch_bounds__(256) head_layout_kernel(HeadLayoutArgs a)
             }
         } else {
             if (TO_HEAD)
-                hp[hi] = a.flat[fi] + (a.bias ? __ldg(a.bias + (int64_t)which * D + (int64_t)h * a.dk + d) : 0.0f) +
+                hp[hi] = a.flat[fi] + (a.bias ? __ldg(a.bias + which * D + h * dk + d) : 0.0f) +
                          (a.accumulate ? hp[hi] : 0.0f);
             else a.flat[fi] = hp[hi];
         }
@@ -80,13 +84,20 @@ int launch_head_layout(bool to_head, float *flat, float *const head[3], const fl
     int64_t blocks = (items + 255) / 256;
     if (blocks > (int64_t)sm_count * 16) blocks = (int64_t)sm_count * 16;
     const unsigned g = (unsigned)blocks;
+    const bool narrow = total < ((int64_t)1 << 30);   // every offset and the loop index (total + grid size) inside 31 bits
+#define AXB_HL_LAUNCH(TH, V)                                                          \
+    do {                                                                              \
+        if (narrow) head_layout_kernel<TH, V, uint32_t><<<g, 256, 0, st>>>(a);        \
+        else head_layout_kernel<TH, V, int64_t><<<g, 256, 0, st>>>(a);                \
+    } while (0)
     if (to_head) {
-        if (vec) head_layout_kernel<true, 4><<<g, 256, 0, st>>>(a);
-        else head_layout_kernel<true, 1><<<g, 256, 0, st>>>(a);
+        if (vec) AXB_HL_LAUNCH(true, 4);
+        else AXB_HL_LAUNCH(true, 1);
     } else {
-        if (vec) head_layout_kernel<false, 4><<<g, 256, 0, st>>>(a);
-        else head_layout_kernel<false, 1><<<g, 256, 0, st>>>(a);
+        if (vec) AXB_HL_LAUNCH(false, 4);
+        else AXB_HL_LAUNCH(false, 1);
     }
+#undef AXB_HL_LAUNCH
     return (int)cudaGetLastError();
 }
 
