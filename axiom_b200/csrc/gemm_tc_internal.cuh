@@ -101,17 +101,20 @@ __device__ __forceinline__ float *out_piece_ptr(const KernelArgs &p, long long r
     return p.hs_out[which] + ((b * p.hs_H + h) * p.hs_S + s) * p.hs_dk + d0;
 }
 
-// GELU, tanh form (ax_gelu: src/core/activations.c:267-333).  tanh(u) = 1 - 2 / (exp(2u) + 1) on the fast
-// exponential and reciprocal: a dozen instructions instead of libm's tanhf, absolute error below 1e-6 * |v| — the
-// epilogue warps evaluate 128 of these per thread and tile while the next tile's accumulators wait for them.
+// GELU, tanh form (ax_gelu: src/core/activations.c:267-333): 0.5 v (1 + tanh(u)) = v / (1 + exp(-2u)),
+// u = 0.79788456 (v + 0.044715 v^3), on the fast exponential and reciprocal: eight dependent instructions, two of them
+// on the special-function pipe, absolute error below 1e-6 * |v|.  exp(-2u) = 2^(-k w) with w = v + 0.044715 v^3 and
+// k = 2 * 0.79788456 * log2(e); it overflows to +inf for very negative v (result -0) and underflows to 0 for large v
+// (result v).
 __device__ __forceinline__ float gelu_tanh(float v)
 {
-    const float u = 0.7978845608028654f * (v + 0.044715f * v * v * v);
-    const float e = __expf(2.0f * u);                       // +inf for large u (tanh -> 1), 0 for very negative (-> -1)
-    const float t = 1.0f - __fdividef(2.0f, e + 1.0f);
-    return 0.5f * v * (1.0f + t);
+    const float w = fmaf(0.044715f * v * v, v, v);
+    float t;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(t) : "f"(-2.302208198f * w));
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + t));
+    return v * r;
 }
-
 
 // fp32 epilogue of one warp's 32 x 32 piece.  The sums arrive row-per-lane (that is how TMEM is read); they are
 // laid into a shared-memory tile (16-byte chunks XOR-swizzled, no bank conflicts either way) and read back so that
@@ -185,6 +188,38 @@ __device__ __forceinline__ bool epi_rows_aligned(const KernelArgs &p)
     return (al & 15) == 0;
 }
 
+// Scale, bias and activation applied IN a warp's staging tile (lane -> 16-byte column group lane & 7 of rows lane >> 3,
+// + 4, ...).  One copy per kernel (not inlined: the piece loop around it is unrolled four times), the activation chosen
+// once, and the eight groups of a lane handled four at a time — loads first, then sixteen independent chains, then the
+// stores: with one group per step the exponential / reciprocal chains of the GELU ran one after the other and the pass
+// (28 k cycles per tile with the stores' turn-around) outlasted the two accumulator chunks the MMAs can run ahead.
+static __device__ __noinline__ void epi_staging_pass(float4 *stg, int lane, float alpha, float4 cs, float4 bs, int act)
+{
+    const int ch = lane & 7, r0 = lane >> 3;
+#pragma unroll 1
+    for (int h = 0; h < 2; ++h) {
+        float4 v[4];
+        int idx[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int r = (h * 4 + j) * 4 + r0;
+            idx[j] = r * 8 + (ch ^ (r & 7));
+            v[j] = stg[idx[j]];
+            // (the same expression as the plain-store path, so that both give the same bits)
+            v[j] = make_float4(v[j].x * alpha * cs.x + bs.x, v[j].y * alpha * cs.y + bs.y, v[j].z * alpha * cs.z + bs.z, v[j].w * alpha * cs.w + bs.w);
+        }
+        if (act == ACT_GELU) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = make_float4(gelu_tanh(v[j].x), gelu_tanh(v[j].y), gelu_tanh(v[j].z), gelu_tanh(v[j].w));
+        } else if (act == ACT_RELU) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = make_float4(fmaxf(v[j].x, 0.0f), fmaxf(v[j].y, 0.0f), fmaxf(v[j].z, 0.0f), fmaxf(v[j].w, 0.0f));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) stg[idx[j]] = v[j];
+    }
+}
+
 // The same epilogue when C is a plain aligned matrix that is not read back: the arithmetic is done IN the staging
 // tile (rolled loop, shared memory only) and the tile leaves as one TMA store — the staging layout is the 128-byte
 // swizzle the tensor map names, rows and columns past M and N are clipped by the hardware, and the warp does not
@@ -200,13 +235,7 @@ static __device__ __forceinline__ void store_piece_f32_tma(const KernelArgs &p, 
             if (p.colscale && colv + e < p.N) cs[e] = __ldg(p.colscale + colv + e);
             if (p.bias && colv + e < p.N) bs[e] = __ldg(p.bias + colv + e);
         }
-#pragma unroll 2
-        for (int it = 0; it < 8; ++it) {
-            const int r = it * 4 + (lane >> 3), idx = r * 8 + (ch ^ (r & 7));
-            const float4 v = stg[idx];
-            stg[idx] = make_float4(epi_act(v.x * p.alpha * cs[0] + bs[0], p.act), epi_act(v.y * p.alpha * cs[1] + bs[1], p.act),
-                                   epi_act(v.z * p.alpha * cs[2] + bs[2], p.act), epi_act(v.w * p.alpha * cs[3] + bs[3], p.act));
-        }
+        epi_staging_pass(stg, lane, p.alpha, make_float4(cs[0], cs[1], cs[2], cs[3]), make_float4(bs[0], bs[1], bs[2], bs[3]), p.act);
     }
     fence_proxy_async_smem();
     __syncwarp();
