@@ -167,3 +167,42 @@ def test_host_validation_of_the_gemm_slot(backend):
     assert gemm(ctypes.byref(_tensor(buf, (4, 3), device=1)), ctypes.byref(ok), ctypes.byref(ok)) == 3       # K mismatch
     assert len(seen) == 6 and all(m for _, m in seen)
     backend.axb_backend_set_hooks(None, None)
+
+
+def test_host_validation_of_the_attention_projection_slots(backend):
+    """The attention-projection slots refuse wrong shapes, ranks, dtypes and host-resident tensors with axiom's status
+    codes before anything reaches a kernel (shape rules of src/compute/backends/cpu_opt.c:6062-6119, 6527-6560, 6825-6857)."""
+    backend.axb_backend_ops.restype = ctypes.c_void_p
+    slots = (ctypes.c_void_p * 58).from_address(backend.axb_backend_ops())
+    T, I64 = ctypes.POINTER(_Tensor), ctypes.c_int64
+    dwqkv = ctypes.CFUNCTYPE(ctypes.c_int, T, T, T, T, T)(slots[16])
+    dwqkv_hm = ctypes.CFUNCTYPE(ctypes.c_int, T, T, T, T, I64, I64, I64, I64, T, T, T)(slots[17])
+    dattn = ctypes.CFUNCTYPE(ctypes.c_int, T, T, I64, I64, I64, I64, T)(slots[19])
+    outproj = ctypes.CFUNCTYPE(ctypes.c_int, T, T, T, T, T, T, T, T)(slots[20])
+    seen = []
+    cb = ctypes.CFUNCTYPE(None, ctypes.c_int, ctypes.c_char_p)(lambda st, msg: seen.append((st, msg)))
+    backend.axb_backend_set_hooks(None, cb)
+    buf = (ctypes.c_float * 4096)()
+    t = lambda *shape, **kw: ctypes.byref(_tensor(buf, shape, device=kw.get("device", 1), dtype=kw.get("dtype", 0)))
+    B, S, H, dk, D, rows = 2, 4, 2, 4, 8, 8
+    # dwqkv_split_acc(x_flat [rows, D], dQKV [rows, 3D], dWq, dWk, dWv [D, D])
+    assert dwqkv(None, t(rows, 3 * D), t(D, D), t(D, D), t(D, D)) == 1
+    assert dwqkv(t(rows, D), t(rows, 2 * D), t(D, D), t(D, D), t(D, D)) == 3          # dQKV is not [rows, 3D]
+    assert dwqkv(t(rows, D), t(rows, 3 * D), t(D, D), t(D, D + 1), t(D, D)) == 3      # a gradient is not [D, D]
+    assert dwqkv(t(rows, D), t(rows, 3 * D, dtype=1), t(D, D), t(D, D), t(D, D)) == 4
+    assert dwqkv(t(rows, D, device=0), t(rows, 3 * D), t(D, D), t(D, D), t(D, D)) == 9  # on the host
+    # the head-major form: dQh, dKh, dVh [B*H, S, dk]
+    assert dwqkv_hm(t(rows, D), t(B * H, S, dk), t(B * H, S, dk), t(B * H, S + 1, dk), B, S, H, dk, t(D, D), t(D, D), t(D, D)) == 3
+    assert dwqkv_hm(t(rows + 1, D), t(B * H, S, dk), t(B * H, S, dk), t(B * H, S, dk), B, S, H, dk, t(D, D), t(D, D), t(D, D)) == 3
+    assert dwqkv_hm(t(rows, D), t(B * H * S, dk), t(B * H, S, dk), t(B * H, S, dk), B, S, H, dk, t(D, D), t(D, D), t(D, D)) == 3  # rank
+    # dattn_head_gemm_nt(dout [B*S, D], Wo [D, D], dO_head [B*H, S, dk])
+    assert dattn(t(rows, D), t(D, D + 1), B, S, H, dk, t(B * H, S, dk)) == 3
+    assert dattn(t(rows, D), t(D, D), B, S, H, dk, t(B * H, S, dk + 1)) == 3
+    # mha_output_proj_fused(attn, Wo, bo?, dout, y?, dattn, dWo, dbo?)
+    assert outproj(t(rows, D), t(D, D), None, t(rows, D), None, None, t(D, D), None) == 1       # dattn is required
+    assert outproj(t(rows, D), t(D, D), t(D + 1), t(rows, D), t(rows, D), t(rows, D), t(D, D), None) == 3   # bo length
+    assert outproj(t(rows, D), t(D, D), None, t(rows + 1, D), None, t(rows, D), t(D, D), None) == 3          # dout rows
+    assert outproj(t(rows, D), t(D, D), None, t(rows, D), None, t(rows, D), t(D, D), t(D, device=0)) == 9   # dbo on the host
+    assert len(seen) == 14 and all(m for _, m in seen)
+    backend.axb_backend_set_hooks(None, None)
+
