@@ -130,6 +130,38 @@ __device__ __forceinline__ float epi_act(float x, int act)
     return x;
 }
 
+// Scale, bias and activation applied IN a warp's staging tile (lane -> 16-byte column group lane & 7 of rows lane >> 3,
+// + 4, ...).  One copy per kernel (not inlined: the piece loop around it is unrolled four times), the activation chosen
+// once, and the eight groups of a lane handled four at a time — loads first, then sixteen independent chains, then the
+// stores: with one group per step the exponential / reciprocal chains of the GELU ran one after the other and the pass
+// (28 k cycles per tile with the stores' turn-around) outlasted the two accumulator chunks the MMAs can run ahead.
+static __device__ __noinline__ void epi_staging_pass(float4 *stg, int lane, float alpha, float4 cs, float4 bs, int act)
+{
+    const int ch = lane & 7, r0 = lane >> 3;
+#pragma unroll 1
+    for (int h = 0; h < 2; ++h) {
+        float4 v[4];
+        int idx[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int r = (h * 4 + j) * 4 + r0;
+            idx[j] = r * 8 + (ch ^ (r & 7));
+            v[j] = stg[idx[j]];
+            // (the same expression as the plain-store path, so that both give the same bits)
+            v[j] = make_float4(v[j].x * alpha * cs.x + bs.x, v[j].y * alpha * cs.y + bs.y, v[j].z * alpha * cs.z + bs.z, v[j].w * alpha * cs.w + bs.w);
+        }
+        if (act == ACT_GELU) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = make_float4(gelu_tanh(v[j].x), gelu_tanh(v[j].y), gelu_tanh(v[j].z), gelu_tanh(v[j].w));
+        } else if (act == ACT_RELU) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = make_float4(fmaxf(v[j].x, 0.0f), fmaxf(v[j].y, 0.0f), fmaxf(v[j].z, 0.0f), fmaxf(v[j].w, 0.0f));
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) stg[idx[j]] = v[j];
+    }
+}
+
 static __device__ __forceinline__ void store_piece_f32(const KernelArgs &p, const float4 *stg, long long row0, int col0, int lane,
                                              bool aligned)
 {
@@ -138,6 +170,25 @@ static __device__ __forceinline__ void store_piece_f32(const KernelArgs &p, cons
         float cs[4] = { 1.f, 1.f, 1.f, 1.f }, bs[4] = { 0.f, 0.f, 0.f, 0.f };
         if (p.colscale) { cs[0] = __ldg(p.colscale + colv); cs[1] = __ldg(p.colscale + colv + 1); cs[2] = __ldg(p.colscale + colv + 2); cs[3] = __ldg(p.colscale + colv + 3); }
         if (p.bias) { bs[0] = __ldg(p.bias + colv); bs[1] = __ldg(p.bias + colv + 1); bs[2] = __ldg(p.bias + colv + 2); bs[3] = __ldg(p.bias + colv + 3); }
+        if (p.beta == 0.0f) {
+            // nothing is read back: the arithmetic is done in the staging tile by the same pass the TMA-store path uses
+            // (the same code, so the same bits), and what is left is a copy of finished 16-byte groups to every
+            // destination — with the activation inline, a GELU in front of eight peer stores per group held the
+            // epilogue warps longer than the two accumulator chunks the MMAs can run ahead
+            if (p.alpha != 1.0f || p.colscale || p.bias || p.act != ACT_NONE)
+                epi_staging_pass(const_cast<float4 *>(stg), lane, p.alpha, make_float4(cs[0], cs[1], cs[2], cs[3]),
+                                 make_float4(bs[0], bs[1], bs[2], bs[3]), p.act);
+#pragma unroll 2
+            for (int it = 0; it < 8; ++it) {
+                const int r = it * 4 + (lane >> 3);
+                if (row0 + r >= p.M) continue;
+                const float4 o = stg[r * 8 + (ch ^ (r & 7))];
+                *reinterpret_cast<float4 *>(out_piece_ptr(p, row0 + r, col0) + ch * 4) = o;
+                for (int e = 0; e < p.n_extra; ++e)
+                    *reinterpret_cast<float4 *>(p.c_extra[e] + (row0 + r) * p.ldc + colv) = o;
+            }
+            return;
+        }
 #pragma unroll 2
         for (int it = 0; it < 8; ++it) {
             const int r = it * 4 + (lane >> 3);
@@ -186,38 +237,6 @@ __device__ __forceinline__ bool epi_rows_aligned(const KernelArgs &p)
         for (int e = 0; e < p.n_extra; ++e) al |= reinterpret_cast<uintptr_t>(p.c_extra[e]);
     }
     return (al & 15) == 0;
-}
-
-// Scale, bias and activation applied IN a warp's staging tile (lane -> 16-byte column group lane & 7 of rows lane >> 3,
-// + 4, ...).  One copy per kernel (not inlined: the piece loop around it is unrolled four times), the activation chosen
-// once, and the eight groups of a lane handled four at a time — loads first, then sixteen independent chains, then the
-// stores: with one group per step the exponential / reciprocal chains of the GELU ran one after the other and the pass
-// (28 k cycles per tile with the stores' turn-around) outlasted the two accumulator chunks the MMAs can run ahead.
-static __device__ __noinline__ void epi_staging_pass(float4 *stg, int lane, float alpha, float4 cs, float4 bs, int act)
-{
-    const int ch = lane & 7, r0 = lane >> 3;
-#pragma unroll 1
-    for (int h = 0; h < 2; ++h) {
-        float4 v[4];
-        int idx[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int r = (h * 4 + j) * 4 + r0;
-            idx[j] = r * 8 + (ch ^ (r & 7));
-            v[j] = stg[idx[j]];
-            // (the same expression as the plain-store path, so that both give the same bits)
-            v[j] = make_float4(v[j].x * alpha * cs.x + bs.x, v[j].y * alpha * cs.y + bs.y, v[j].z * alpha * cs.z + bs.z, v[j].w * alpha * cs.w + bs.w);
-        }
-        if (act == ACT_GELU) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = make_float4(gelu_tanh(v[j].x), gelu_tanh(v[j].y), gelu_tanh(v[j].z), gelu_tanh(v[j].w));
-        } else if (act == ACT_RELU) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = make_float4(fmaxf(v[j].x, 0.0f), fmaxf(v[j].y, 0.0f), fmaxf(v[j].z, 0.0f), fmaxf(v[j].w, 0.0f));
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) stg[idx[j]] = v[j];
-    }
 }
 
 // The same epilogue when C is a plain aligned matrix that is not read back: the arithmetic is done IN the staging
