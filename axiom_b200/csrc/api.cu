@@ -1362,6 +1362,17 @@ extern "C" int axb_kv_cache_attend(const float *K_cache, const float *V_cache, c
 
 // ------------------------------------------------------- attention projections
 
+// aux scratch of at least `need` bytes (grown on demand; the stream is drained before the old block is freed)
+static int ensure_aux(const char *what, size_t need)
+{
+    if (need <= cur().aux_bytes) return AXB_OK;
+    if (cur().aux) { cudaStreamSynchronize(cur().stream); cudaFree(cur().aux); cur().aux = nullptr; cur().aux_bytes = 0; }
+    cudaError_t e = cudaMalloc(&cur().aux, need);
+    if (e != cudaSuccess) return fail(AXB_ERR_ALLOC, "%s: scratch of %zu bytes: %s", what, need, cudaGetErrorString(e));
+    cur().aux_bytes = need;
+    return AXB_OK;
+}
+
 extern "C" int axb_qkv_head_gemm(const float *X, const float *Wqkv, const float *bqkv, int64_t B, int64_t S, int64_t H,
                                  int64_t dk, float *Qh, float *Kh, float *Vh)
 {
@@ -1379,13 +1390,7 @@ extern "C" int axb_qkv_head_gemm(const float *X, const float *Wqkv, const float 
         return gemm_tc_f32(X, Wqkv, bqkv, nullptr, rows, 3 * D, D, 0, 0, 1.0f, 0.0f, AXB_ACT_NONE, nullptr, 0, 0, 0, shape, outs);
     }
     // other head dims and skinny inputs: the product (bias fused) into a scratch matrix, then the layout pass
-    const size_t need = (size_t)rows * 3 * D * sizeof(float);
-    if (need > cur().aux_bytes) {
-        if (cur().aux) { cudaStreamSynchronize(cur().stream); cudaFree(cur().aux); cur().aux = nullptr; cur().aux_bytes = 0; }
-        cudaError_t e = cudaMalloc(&cur().aux, need);
-        if (e != cudaSuccess) return fail(AXB_ERR_ALLOC, "qkv_head_gemm: scratch of %zu bytes: %s", need, cudaGetErrorString(e));
-        cur().aux_bytes = need;
-    }
+    if ((st = ensure_aux("qkv_head_gemm", (size_t)rows * 3 * D * sizeof(float)))) return st;
     st = axb_gemm_bias_act(X, Wqkv, bqkv, (float *)cur().aux, rows, 3 * D, D, 0, 0, 1.0f, 0.0f, AXB_ACT_NONE);
     if (st) return st;
     int e = launch_head_layout(true, (float *)cur().aux, outs, nullptr, 3, B, S, H, dk, cur().sm_count, cur().stream);
@@ -1408,29 +1413,12 @@ extern "C" int axb_dattn_head_gemm_nt(const float *dout, const float *Wo, int64_
         const int64_t shape[3] = { S, H, dk };
         return gemm_tc_f32(dout, Wo, nullptr, nullptr, rows, D, D, 0, 1, 1.0f, 0.0f, AXB_ACT_NONE, nullptr, 0, 0, 0, shape, outs);
     }
-    const size_t need = (size_t)rows * D * sizeof(float);
-    if (need > cur().aux_bytes) {
-        if (cur().aux) { cudaStreamSynchronize(cur().stream); cudaFree(cur().aux); cur().aux = nullptr; cur().aux_bytes = 0; }
-        cudaError_t e = cudaMalloc(&cur().aux, need);
-        if (e != cudaSuccess) return fail(AXB_ERR_ALLOC, "dattn_head_gemm_nt: scratch of %zu bytes: %s", need, cudaGetErrorString(e));
-        cur().aux_bytes = need;
-    }
+    if ((st = ensure_aux("dattn_head_gemm_nt", (size_t)rows * D * sizeof(float)))) return st;
     st = axb_gemm_bias_act(dout, Wo, nullptr, (float *)cur().aux, rows, D, D, 0, 1, 1.0f, 0.0f, AXB_ACT_NONE);
     if (st) return st;
     int e = launch_head_layout(true, (float *)cur().aux, outs, nullptr, 1, B, S, H, dk, cur().sm_count, cur().stream);
     cur().launches++;
     return e ? cuda_fail("dattn_head_gemm_nt: head layout", e) : AXB_OK;
-}
-
-// aux scratch of at least `need` bytes (grown on demand; the stream is drained before the old block is freed)
-static int ensure_aux(const char *what, size_t need)
-{
-    if (need <= cur().aux_bytes) return AXB_OK;
-    if (cur().aux) { cudaStreamSynchronize(cur().stream); cudaFree(cur().aux); cur().aux = nullptr; cur().aux_bytes = 0; }
-    cudaError_t e = cudaMalloc(&cur().aux, need);
-    if (e != cudaSuccess) return fail(AXB_ERR_ALLOC, "%s: scratch of %zu bytes: %s", what, need, cudaGetErrorString(e));
-    cur().aux_bytes = need;
-    return AXB_OK;
 }
 
 // dW{q,k,v} += x^T . dQKV[:, {0,1,2}*D : +D]; `scratch_off` bytes at the start of aux are in use by the caller
