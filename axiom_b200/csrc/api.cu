@@ -991,18 +991,25 @@ extern "C" int axb_qdense_w8a32(const float *a, const int8_t *q, const float *sc
     if (st) return st;
     if (M == 0) return AXB_OK;
     // a single activation row too once the layer is large: the fp32-FMA GEMV tops out at 3.7 TB/s (instruction issue),
-    // the tensor-core kernel streams faster, and from 2^25 weights on that outweighs its second launch (measured:
-    // 8192 x 4096 12.3 us against 13.0, 4096 x 4096 10.8 against 8.7)
-    const bool tc_route = M >= 2 ? N * K >= (1 << 20) : N * K >= (1 << 25);
+    // the tensor-core kernel — one launch up to four rows, it makes the activations' digits itself — streams faster
+    // from 2^24 weights on (measured: 16384 x 4096 13.6 us against 18.0, 8192 x 4096 9.3 against 13.0, 4096 x 4096
+    // 8.0 against 8.8)
+    const bool tc_route = M >= 2 ? N * K >= (1 << 20) : N * K >= (1 << 24);
     if (tc_route && qskinny_tc_applicable(M, N, K, a, q)) {
         // skinny activations as four int8 digit planes, weights streamed once into kind::i8 MMAs
         st = ensure_ws(qskinny_tc_workspace_bytes(M, K));
         if (st) return st;
         mark(0);
         mark(1);
-        int e = launch_qskinny_tc(a, q, scales, bias, act, out, M, N, K, cur().ws, cur().err_word, cur().sm_count, cur().stream);
+        // (a call of up to 4 rows is one kernel that lets its successor start early: as on the fp32 skinny route, the
+        // successor may only do so when this call's output is not what it streams as weights)
+        const char *w_lo = reinterpret_cast<const char *>(q), *w_hi = w_lo + (size_t)N * K;
+        const int pdl = !(cur().chain_lo && w_lo < cur().chain_hi && cur().chain_lo < w_hi);
+        cur().chain_lo = reinterpret_cast<const char *>(out);
+        cur().chain_hi = cur().chain_lo + (size_t)M * N * sizeof(float);
+        int e = launch_qskinny_tc(a, q, scales, bias, act, out, M, N, K, cur().ws, cur().err_word, cur().sm_count, cur().stream, pdl);
         mark(2);
-        cur().launches += 2;
+        cur().launches += M <= 4 ? 1 : 2;
         return e ? cuda_fail("w8a32 skinny", e) : AXB_OK;
     }
     if (qgemv_w8a32_applicable(M, N, K, q) && (reinterpret_cast<uintptr_t>(a) & 15) == 0) {

@@ -26,6 +26,7 @@
 
 #include <cuda.h>
 #include <math.h>
+#include <string.h>
 
 namespace axb {
 
@@ -45,6 +46,8 @@ struct QtArgs {
     int M;
     int64_t N;
     int act;
+    const float *x;   // FUSED kernels: the fp32 activations [M][K] themselves (no digit planes in memory)
+    int K;
 };
 
 enum { QERR_PRODUCER = 31, QERR_MMA = 32, QERR_DRAIN = 33 };
@@ -146,10 +149,17 @@ __device__ __forceinline__ void qt_report(int *err, int code)
     if (err) atomicCAS(err, 0, code);
 }
 
-template <int MP>
+// FUSED (used up to 4 rows): no digit pre-pass.  The sixteen drain warps, idle while the weights stream, make the digits
+// themselves: every CTA finds the rows' largest magnitudes (M x K floats out of L2), then the warp that owns ring stage w
+// writes the digit tiles of k-blocks w, w + stages, ... straight into the ring's X slots in the layout TMA would have left there (128-byte rows,
+// 16-byte chunks XOR-ed with the row's low bits) and arrives on the stage's barrier beside the weight tile's bytes.
+// One launch instead of two, and the ~2.7 us between the end of a pre-pass and the moment its dependents may read
+// what it wrote are gone.
+template <int MP, bool FUSED>
 __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_constant__ QtMaps tm, const QtArgs a,
                                                                    int kb_total)
 {
+    static_assert(!FUSED || MP == 8, "the fused digit maker serves the 8-row variant");
     constexpr int NB = 4 * MP;                                   // MMA N: digit plane j, row m at column j*MP + m
     constexpr uint32_t X_BYTES = NB * 128;
     constexpr uint32_t STAGE = QT_W_BYTES + X_BYTES;
@@ -179,8 +189,12 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
-            mbar_init(bar(B_FULL + s), 1);
+            mbar_init(bar(B_FULL + s), FUSED ? 2 : 1);   // the weight tile's bytes (+ the warp that wrote the digits)
             mbar_init(bar(B_EMPTY + s), 1);
+        }
+        if (FUSED) {
+#pragma unroll
+            for (int m = 0; m < 10; ++m) reinterpret_cast<volatile uint32_t *>(base_ptr + 576)[m] = 0u;   // row maxima, bad-row mask
         }
         mbar_init(bar(B_ACC), TWO ? 2 : 1);   // one arrival per MMA issuer
         mbar_fence_init();
@@ -189,10 +203,11 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
         // pre-pass (which may still be running: this kernel is its programmatic dependent) are needed.
         tma_prefetch_desc(&tm.w);
         for (int i = 0; i < pre; ++i) {
-            mbar_arrive_expect_tx(bar(B_FULL + i), STAGE);
+            mbar_arrive_expect_tx(bar(B_FULL + i), FUSED ? QT_W_BYTES : STAGE);
             tma_load_3d(stage_addr(i), &tm.w, bar(B_FULL + i), kpos(i), (int32_t)n0, 0);
         }
-        tma_prefetch_desc(&tm.x);
+        if (FUSED) grid_dep_launch();   // a call queued behind this one may request ITS weights now
+        else tma_prefetch_desc(&tm.x);
     }
     if (warp == 1) {
         tmem_alloc(base + 512, TCOLS);
@@ -209,7 +224,7 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
     const int64_t col = n0 + t_row;
     const bool col_ok = col < a.N;
     float col_scale = 0.0f, col_bias = 0.0f;    // inputs of the call, not of the pre-pass: loaded ahead of the K loop
-    if (warp >= 2 && warp < 18 && col_ok) {
+    if (!FUSED && warp >= 2 && warp < 18 && col_ok) {
         col_scale = __ldg(a.scales + col);
         if (a.bias) col_bias = __ldg(a.bias + col);
     }
@@ -222,17 +237,19 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
     if (warp == 0) {
         // ------------------------------------------------------------ producer
         if (lane == 0) {
-            grid_dep_wait();   // the digits
-            for (int i = 0; i < pre; ++i)
-                tma_load_3d(stage_addr(i) + QT_W_BYTES, &tm.x, bar(B_FULL + i), kpos(i), 0, 0);
+            if (!FUSED) {
+                grid_dep_wait();   // the digits
+                for (int i = 0; i < pre; ++i)
+                    tma_load_3d(stage_addr(i) + QT_W_BYTES, &tm.x, bar(B_FULL + i), kpos(i), 0, 0);
+            }
             for (int i = pre; i < nkb; ++i) {
                 const int s = i % STAGES, n = i / STAGES;
                 if (!mbar_wait_bounded(bar(B_EMPTY + s), (n - 1) & 1)) { qt_report(a.err, QERR_PRODUCER); break; }
                 const uint32_t st = stage_addr(s);
                 const int k0 = kpos(i);
-                mbar_arrive_expect_tx(bar(B_FULL + s), STAGE);
+                mbar_arrive_expect_tx(bar(B_FULL + s), FUSED ? QT_W_BYTES : STAGE);
                 tma_load_3d(st, &tm.w, bar(B_FULL + s), k0, (int32_t)n0, 0);
-                tma_load_3d(st + QT_W_BYTES, &tm.x, bar(B_FULL + s), k0, 0, 0);
+                if (!FUSED) tma_load_3d(st + QT_W_BYTES, &tm.x, bar(B_FULL + s), k0, 0, 0);
             }
         }
     } else if (warp == 1 || warp == 18) {
@@ -269,9 +286,84 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
     } else if (warp < 18) {
         // --------------------------------------------------------------- drain
         const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-        grid_dep_wait();   // the row scales come from the pre-pass
+        grid_dep_wait();   // the row scales come from the pre-pass (FUSED: the activations from the kernel before)
         const int dt = threadIdx.x - 64;
-        if (dt < MP) s_inv[dt] = dt < a.M ? __ldg(a.inv_s + dt) : 0.0f;
+        if constexpr (FUSED) {
+            if (col_ok) {
+                col_scale = __ldg(a.scales + col);
+                if (a.bias) col_bias = __ldg(a.bias + col);
+            }
+            // ---- the rows' largest magnitudes (every CTA for itself: M x K floats, L2 hits after the first CTA)
+            uint32_t *s_maxbits = reinterpret_cast<uint32_t *>(base_ptr + 576);   // [8] |x| bit patterns, [8] bad-row mask
+            float *s_mul = reinterpret_cast<float *>(base_ptr + 640);             // [8] 2^s
+            const int K = a.K, k4n = K >> 2;
+            for (int m = 0; m < a.M; ++m) {
+                const float4 *row = reinterpret_cast<const float4 *>(a.x + (int64_t)m * K);
+                float mx = 0.0f;
+                bool bad = false;
+                for (int i = dt; i < k4n; i += 512) mx = fmaxf(mx, qx_absmax(__ldg(row + i), bad));
+                if (bad) mx = INFINITY;
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+                if (lane == 0) atomicMax(s_maxbits + m, __float_as_uint(mx));   // non-negative floats order like their bits
+            }
+            asm volatile("bar.sync 1, 512;" ::: "memory");
+            if (dt < MP) {
+                const float mx = __uint_as_float(s_maxbits[dt]);
+                const bool finite = mx < INFINITY;
+                int sexp = 0;
+                if (mx > 0.0f && finite) {
+                    const int e = (int)(__float_as_uint(mx) >> 23) - 127;   // floor(log2 mx) for normal mx
+                    sexp = min(29 - e, 126);
+                }
+                s_mul[dt] = (finite && dt < a.M) ? __uint_as_float((uint32_t)(sexp + 127) << 23) : 0.0f;
+                // a row with an infinity or a NaN comes out as NaN
+                s_inv[dt] = dt < a.M ? (finite ? __uint_as_float((uint32_t)(127 - sexp) << 23) : __int_as_float(0x7FC00000)) : 0.0f;
+            }
+            asm volatile("bar.sync 1, 512;" ::: "memory");
+            // ---- digit tiles: warp w < STAGES owns ring stage w and makes k-blocks w, w + STAGES, ... (one warp per
+            // stage, so that it sees every release of its stage in turn: a waiter that skipped a phase would be fooled
+            // by the barrier's parity); lane l makes the four k at 4l of every row
+            const int w16 = warp - 2;
+            for (int i = w16; i < nkb && w16 < STAGES; i += STAGES) {
+                const int s = i % STAGES, n = i / STAGES;
+                if (n >= 1) {
+                    const bool got = mbar_wait_warp_bounded(bar(B_EMPTY + s), (n - 1) & 1);
+                    if (!got) { qt_report(a.err, QERR_PRODUCER); break; }
+                }
+                const int k = kpos(i) + 4 * lane;
+                uint8_t *xs = base_ptr + 1024 + (size_t)s * STAGE + QT_W_BYTES;
+                const int chunk = lane >> 2, within = (lane & 3) * 4;
+#pragma unroll
+                for (int m = 0; m < MP; ++m) {
+                    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+                    const bool live = m < a.M && k < K;   // padding rows and the K tail are zero digits
+                    if (live) v = __ldg(reinterpret_cast<const float4 *>(a.x + (int64_t)m * K + k));
+                    const float sc = s_mul[m];
+                    const float xv[4] = { v.x, v.y, v.z, v.w };
+                    uint32_t pk[4] = { 0u, 0u, 0u, 0u };
+#pragma unroll
+                    for (int e = 0; e < 4 && live; ++e) {
+                        int t = __float2int_rn(xv[e] * sc);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int d = (int)(int8_t)(t & 0xFF);
+                            t = (t - d) >> 8;
+                            pk[j] |= (uint32_t)(d & 0xFF) << (8 * e);
+                        }
+                    }
+                    // row j*MP + m of the tile: its low three bits are m (MP == 8), the chunk index is XOR-ed with them
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+                        *reinterpret_cast<uint32_t *>(xs + (j * MP + m) * 128 + ((chunk ^ m) << 4) + within) = pk[j];
+                }
+                fence_proxy_async_smem();   // generic-proxy writes before the tensor core reads them
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar(B_FULL + s));
+            }
+        } else {
+            if (dt < MP) s_inv[dt] = dt < a.M ? __ldg(a.inv_s + dt) : 0.0f;
+        }
         asm volatile("bar.sync 1, 512;" ::: "memory");   // the sixteen drain warps
         bool have = nkb > 0;
         if (have && !mbar_wait_warp_bounded(bar(B_ACC), 0)) {
@@ -363,11 +455,11 @@ size_t qskinny_tc_workspace_bytes(int64_t M, int64_t K)
     return (size_t)4 * mp * K + 1024;
 }
 
-template <int MP>
-static int launch_inst(const QtMaps &tm, const QtArgs &a, int kb_total, dim3 grid, cudaStream_t st)
+template <int MP, bool FUSED = false>
+static int launch_inst(const QtMaps &tm, const QtArgs &a, int kb_total, dim3 grid, cudaStream_t st, int pdl = 1)
 {
     const size_t smem = 1024 + (size_t)qt_stages(MP) * (QT_W_BYTES + 4 * MP * 128) + (size_t)(MP + 8) * 1024 + 1024;
-    auto kern = qskinny_tc_kernel<MP>;
+    auto kern = qskinny_tc_kernel<MP, FUSED>;
     static bool attr_set[64] = {};
     int dev = 0;
     cudaGetDevice(&dev);
@@ -389,7 +481,7 @@ static int launch_inst(const QtMaps &tm, const QtArgs &a, int kb_total, dim3 gri
     at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // may start under the digit pre-pass
     at[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
-    cfg.numAttrs = 2;
+    cfg.numAttrs = pdl ? 2 : 1;
     return (int)cudaLaunchKernelEx(&cfg, kern, tm, a, kb_total);
 }
 
@@ -402,21 +494,29 @@ int launch_qx_digits(const float *act_in, int64_t M, int64_t K, int64_t plane_ro
 }
 
 int launch_qskinny_tc(const float *act_in, const int8_t *q, const float *scales, const float *bias, int act, float *out,
-                      int64_t M, int64_t N, int64_t K, void *workspace, int *err, int sm_count, cudaStream_t st)
+                      int64_t M, int64_t N, int64_t K, void *workspace, int *err, int sm_count, cudaStream_t st, int pdl)
 {
     const int mp = M <= 8 ? 8 : M <= 16 ? 16 : M <= 32 ? 32 : 64;
+    // up to four rows the tensor-core kernel makes the digits itself, one launch (measured against the pre-pass form,
+    // W[16384 x 4096]: M = 1 14.2 against 16.4 us, M = 2 14.9 / 16.4, M = 4 16.7 / 16.5, M = 8 20.0 / 16.6 — every CTA
+    // converts all the rows, and from eight rows on that is slower than one pre-pass for all)
+    const bool fused = M <= 4;
     float *inv_s = reinterpret_cast<float *>(workspace);
     int8_t *digits = reinterpret_cast<int8_t *>(workspace) + 1024;
-    qx_digits_kernel<1024><<<(unsigned)M, 1024, 0, st>>>(act_in, (int)K, mp, digits, inv_s);
-    int e = (int)cudaGetLastError();
-    if (e) return e;
-
+    int e = 0;
+    if (!fused) {
+        qx_digits_kernel<1024><<<(unsigned)M, 1024, 0, st>>>(act_in, (int)K, mp, digits, inv_s);
+        e = (int)cudaGetLastError();
+        if (e) return e;
+    }
     QtMaps tm;
+    memset(&tm, 0, sizeof tm);
     e = encode_i8_batched_tmap(&tm.w, q, 1, N, K, K, N * K, QT_BN, 1);
-    if (!e) e = encode_i8_batched_tmap(&tm.x, digits, 4, M, K, K, (int64_t)mp * K, mp, 4);
+    if (!e && !fused) e = encode_i8_batched_tmap(&tm.x, digits, 4, M, K, K, (int64_t)mp * K, mp, 4);
     if (e) return e;
     QtArgs a;
     a.scales = scales; a.bias = bias; a.inv_s = inv_s; a.out = out; a.err = err; a.M = (int)M; a.N = N; a.act = act;
+    a.x = act_in; a.K = (int)K;
     const int tiles = (int)((N + QT_BN - 1) / QT_BN);
     const int kb_total = (int)((K + QT_KB - 1) / QT_KB);
     // K-slices: fill the GPU once, at most 8 per cluster, at least two k-blocks each, none empty
@@ -427,6 +527,7 @@ int launch_qskinny_tc(const float *act_in, const int8_t *q, const float *scales,
     const int per = (kb_total + slices - 1) / slices;
     slices = (kb_total + per - 1) / per;
     dim3 grid((unsigned)tiles, (unsigned)slices);
+    if (fused) return launch_inst<8, true>(tm, a, kb_total, grid, st, pdl);
     switch (mp) {
     case 8: return launch_inst<8>(tm, a, kb_total, grid, st);
     case 16: return launch_inst<16>(tm, a, kb_total, grid, st);

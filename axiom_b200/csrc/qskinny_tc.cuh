@@ -11,10 +11,12 @@ bool qskinny_tc_applicable(int64_t M, int64_t N, int64_t K, const float *a, cons
 // bytes of device scratch one call needs (digit planes of the activations + one scale per row)
 size_t qskinny_tc_workspace_bytes(int64_t M, int64_t K);
 // out = act(scale[n] * sum_k a*q (+ bias[n])); bias may be null, act 0 none / 1 ReLU / 2 GELU (tanh form).
-// Two launches on `st`: the digit pre-pass and the tensor-core kernel, which is launched as a programmatic dependent
-// and requests its first weight tiles while the pre-pass runs.  `err` receives a code if a wait in the kernel runs out.
+// M <= 4: ONE launch — the tensor-core kernel makes the digits itself; it releases its own dependents early, and is
+// launched as a programmatic dependent when `pdl` says the kernel before it did not write these weights (it requests
+// its first weight tiles before that kernel has finished; everything else waits).  M > 4: two launches on `st`, the
+// digit pre-pass and the tensor-core kernel, which requests its first weight tiles while the pre-pass runs.  `err` receives a code if a wait in the kernel runs out.
 int launch_qskinny_tc(const float *a, const int8_t *q, const float *scales, const float *bias, int act, float *out,
-                      int64_t M, int64_t N, int64_t K, void *workspace, int *err, int sm_count, cudaStream_t st);
+                      int64_t M, int64_t N, int64_t K, void *workspace, int *err, int sm_count, cudaStream_t st, int pdl);
 
 // M > 64: the same digit planes as an operand of one int8 GEMM.  launch_qx_digits writes digits[4][plane_rows][K]
 // (row m of plane j at (j * plane_rows + m) * K; plane_rows == 0: interleaved, digit j of row m at (4 * m + j) * K)

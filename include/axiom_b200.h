@@ -260,7 +260,7 @@ AXB_API int axb_gelu(const float *in, float *out, int64_t n);
 /* W8A32: out[M,N] = scales[n] * sum_k a[m,k] * q[n,k], q int8 [N,K], fp32 result.
    Device-pointer form of ax_qgemm_w8a32 (include/axiom/quantize.h:75-79,
    src/core/quantize.c:100-177); q/scales/N/K are the fields of ax_qweight_t.
-   M = 1 runs the reference's fp32 multiply-adds in a fixed order (layers under 2^25 weights).  Otherwise (K a
+   M = 1 runs the reference's fp32 multiply-adds in a fixed order (layers under 2^24 weights).  Otherwise (K a
    multiple of 16 up to 65536, 16-byte aligned operands) each activation row is first rounded to a fixed-point grid of 2^-30 of its largest
    magnitude and the products are exact integer arithmetic on the tensor cores: the result is within 1e-7 of the
    exact sum and does not depend on summation order; a row that holds an infinity or a NaN comes out as NaN. */

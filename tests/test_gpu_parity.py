@@ -620,7 +620,7 @@ def test_conv_gemm_batched(engine, oracle, geom):
                                    (2, 8192, 128), (64, 130, 8192), (7, 64, 16384), (48, 2048, 65536 // 64),
                                    (1, 16384, 4096)])
 def test_w8a32_skinny_tensor_core_kernel(engine, oracle, shape):
-    """2 <= M <= 64 with at least 2^20 weights (M = 1 from 2^25 weights): activations as four int8 digit planes,
+    """2 <= M <= 64 with at least 2^20 weights (M = 1 from 2^24 weights): activations as four int8 digit planes,
     kind::i8 MMAs.  Ragged N and K
     (zero-filled tiles), one and several K-slices per tile, an outlier 1000x the other activations in one row, and a
     row with an infinity (the reference's fp32 sum is NaN or infinite there; here the row is NaN)."""
