@@ -618,7 +618,10 @@ def test_conv_gemm_batched(engine, oracle, geom):
 @pytest.mark.parametrize("shape", [(2, 1024, 1024), (8, 4096, 4096), (9, 1000, 2048), (16, 2048, 1040), (17, 8200, 1168),
                                    (32, 16384, 512), (33, 1024, 1024), (64, 4096, 4096), (5, 128, 8192),
                                    (2, 8192, 128), (64, 130, 8192), (7, 64, 16384), (48, 2048, 65536 // 64),
-                                   (1, 16384, 4096)])
+                                   (1, 16384, 4096),
+                                   # up to four rows the kernel makes the digits itself: many uses of every ring stage,
+                                   # a ragged N with a K tail that is not a whole k-block, four rows on one slice
+                                   (3, 9728, 8192), (4, 600, 2064), (4, 16384, 1024)])
 def test_w8a32_skinny_tensor_core_kernel(engine, oracle, shape):
     """2 <= M <= 64 with at least 2^20 weights (M = 1 from 2^24 weights): activations as four int8 digit planes,
     kind::i8 MMAs.  Ragged N and K
