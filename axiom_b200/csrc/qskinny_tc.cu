@@ -297,15 +297,28 @@ __global__ void __launch_bounds__(QT_THREADS, 1) qskinny_tc_kernel(const __grid_
             uint32_t *s_maxbits = reinterpret_cast<uint32_t *>(base_ptr + 576);   // [8] |x| bit patterns, [8] bad-row mask
             float *s_mul = reinterpret_cast<float *>(base_ptr + 640);             // [8] 2^s
             const int K = a.K, k4n = K >> 2;
-            for (int m = 0; m < a.M; ++m) {
-                const float4 *row = reinterpret_cast<const float4 *>(a.x + (int64_t)m * K);
-                float mx = 0.0f;
-                bool bad = false;
-                for (int i = dt; i < k4n; i += 512) mx = fmaxf(mx, qx_absmax(__ldg(row + i), bad));
-                if (bad) mx = INFINITY;
+            {
+                // all rows' loads of a step are issued together: row after row, each row's loads waited for the previous
+                // row's reduction and the pass took one trip to L2 per row
+                float mx[MP];
+                bool bad[MP];
 #pragma unroll
-                for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-                if (lane == 0) atomicMax(s_maxbits + m, __float_as_uint(mx));   // non-negative floats order like their bits
+                for (int m = 0; m < MP; ++m) { mx[m] = 0.0f; bad[m] = false; }
+                const float4 *x4 = reinterpret_cast<const float4 *>(a.x);
+                for (int i = dt; i < k4n; i += 512) {
+#pragma unroll
+                    for (int m = 0; m < MP; ++m)
+                        if (m < a.M) mx[m] = fmaxf(mx[m], qx_absmax(__ldg(x4 + (int64_t)m * k4n + i), bad[m]));
+                }
+#pragma unroll
+                for (int m = 0; m < MP; ++m) {
+                    if (m < a.M) {
+                        float v = bad[m] ? INFINITY : mx[m];
+#pragma unroll
+                        for (int off = 16; off > 0; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
+                        if (lane == 0) atomicMax(s_maxbits + m, __float_as_uint(v));   // non-negative floats order like their bits
+                    }
+                }
             }
             asm volatile("bar.sync 1, 512;" ::: "memory");
             if (dt < MP) {
@@ -498,8 +511,8 @@ int launch_qskinny_tc(const float *act_in, const int8_t *q, const float *scales,
 {
     const int mp = M <= 8 ? 8 : M <= 16 ? 16 : M <= 32 ? 32 : 64;
     // up to four rows the tensor-core kernel makes the digits itself, one launch (measured against the pre-pass form,
-    // W[16384 x 4096]: M = 1 14.2 against 16.4 us, M = 2 14.9 / 16.4, M = 4 16.7 / 16.5, M = 8 20.0 / 16.6 — every CTA
-    // converts all the rows, and from eight rows on that is slower than one pre-pass for all)
+    // W[16384 x 4096]: M = 1 13.6 - 14.0 against 16.4 us, M = 2 14.4 / 16.4, M = 4 15.5 / 16.5, M = 8 17.1 / 16.6 — every
+    // CTA converts all the rows, and at eight rows that is no faster than one pre-pass for all)
     const bool fused = M <= 4;
     float *inv_s = reinterpret_cast<float *>(workspace);
     int8_t *digits = reinterpret_cast<int8_t *>(workspace) + 1024;
